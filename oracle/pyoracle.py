@@ -1,0 +1,219 @@
+"""ctypes loader for the CPU oracle (TEST INFRASTRUCTURE ONLY).
+
+Only the tests, the smoke check and the CPU-baseline leg of the benchmark import this.
+The shipped package never does.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+
+u32p = C.POINTER(C.c_uint32)
+u8p = C.POINTER(C.c_uint8)
+
+
+def build() -> str:
+    subprocess.run(["make", "-s", "-C", _HERE], check=True)
+    return os.path.join(_HERE, "libzkoracle.so")
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        path = os.path.join(_HERE, "libzkoracle.so")
+        if not os.path.exists(path):
+            build()
+        _LIB = C.CDLL(path)
+        _LIB.zko_tr_new.restype = C.c_void_p
+        _LIB.zko_tr_squeeze.restype = C.c_uint32
+        _LIB.zko_mle_evaluate.restype = C.c_uint32
+        _LIB.zko_from_field.restype = C.c_int64
+        _LIB.zko_mod_sqrt.restype = C.c_uint32
+    return _LIB
+
+
+def _u32(a):
+    a = np.ascontiguousarray(a, dtype=np.uint32)
+    return a, a.ctypes.data_as(u32p)
+
+
+def _u8(b: bytes):
+    arr = (C.c_uint8 * max(len(b), 1)).from_buffer_copy(b if len(b) else b"\0")
+    return arr
+
+
+def sha256(b: bytes) -> bytes:
+    out = (C.c_uint8 * 32)()
+    lib().zko_sha256(_u8(b), C.c_size_t(len(b)), out)
+    return bytes(out)
+
+
+def blake3(b: bytes, n: int = 32) -> bytes:
+    out = (C.c_uint8 * n)()
+    lib().zko_blake3(_u8(b), C.c_size_t(len(b)), out, C.c_size_t(n))
+    return bytes(out)
+
+
+def hash_values(v) -> bytes:
+    a, p = _u32(v)
+    out = (C.c_uint8 * 32)()
+    lib().zko_hash_values(p, C.c_size_t(a.size), out)
+    return bytes(out)
+
+
+def f_mul(a, b):
+    o = C.c_uint32()
+    lib().zko_f_mul(C.c_uint32(a), C.c_uint32(b), C.byref(o))
+    return o.value
+
+
+def f_inv(a):
+    o = C.c_uint32()
+    lib().zko_f_inv(C.c_uint32(a), C.byref(o))
+    return o.value
+
+
+def ef_mul(a, b):
+    a_, pa = _u32(a)
+    b_, pb = _u32(b)
+    o = np.zeros(4, np.uint32)
+    lib().zko_ef_mul(pa, pb, o.ctypes.data_as(u32p))
+    return o
+
+
+def ef_inv(a):
+    a_, pa = _u32(a)
+    o = np.zeros(4, np.uint32)
+    lib().zko_ef_inv(pa, o.ctypes.data_as(u32p))
+    return o
+
+
+def to_field(x: int) -> int:
+    o = C.c_uint32()
+    lib().zko_to_field(C.c_int64(x), C.byref(o))
+    return o.value
+
+
+def from_field(x: int) -> int:
+    return lib().zko_from_field(C.c_uint32(x))
+
+
+class Transcript:
+    """Mirror of the reference `Transcript` (rust/zk_ml_prover/src/proving/sumcheck.rs:110-206)."""
+
+    def __init__(self, label: bytes):
+        self.h = C.c_void_p(lib().zko_tr_new(_u8(label), C.c_size_t(len(label))))
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            lib().zko_tr_free(self.h)
+            self.h = None
+
+    def absorb(self, v: int):
+        lib().zko_tr_absorb_u32(self.h, C.c_uint32(v))
+
+    def absorb_many(self, vs):
+        a, p = _u32(vs)
+        lib().zko_tr_absorb_many(self.h, p, C.c_size_t(a.size))
+
+    def absorb_bytes(self, b: bytes):
+        lib().zko_tr_absorb_bytes(self.h, _u8(b), C.c_size_t(len(b)))
+
+    def squeeze(self) -> int:
+        return lib().zko_tr_squeeze(self.h)
+
+    def squeeze_ef(self):
+        o = np.zeros(4, np.uint32)
+        lib().zko_tr_squeeze_ef(self.h, o.ctypes.data_as(u32p))
+        return o
+
+
+def eq_evals(r):
+    a, p = _u32(r)
+    out = np.zeros(1 << a.size, np.uint32)
+    lib().zko_eq_evals(p, C.c_size_t(a.size), out.ctypes.data_as(u32p))
+    return out
+
+
+def eq_evals_ef(r):
+    a, p = _u32(r)
+    k = a.size // 4
+    out = np.zeros((1 << k, 4), np.uint32)
+    lib().zko_eq_evals_ef(p, C.c_size_t(k), out.ctypes.data_as(u32p))
+    return out
+
+
+def mle_evaluate(ev, pt) -> int:
+    a, pa = _u32(ev)
+    b, pb = _u32(pt)
+    return lib().zko_mle_evaluate(pa, C.c_size_t(a.size), pb, C.c_size_t(b.size))
+
+
+def mle_evaluate_ef(ev, pt):
+    a, pa = _u32(ev)
+    b, pb = _u32(pt)
+    o = np.zeros(4, np.uint32)
+    lib().zko_mle_evaluate_ef(pa, C.c_size_t(a.size), pb, C.c_size_t(b.size // 4), o.ctypes.data_as(u32p))
+    return o
+
+
+def mle_evaluate_efef(ev, pt):
+    a, pa = _u32(ev)
+    b, pb = _u32(pt)
+    o = np.zeros(4, np.uint32)
+    lib().zko_mle_evaluate_efef(pa, C.c_size_t(a.size // 4), pb, C.c_size_t(b.size // 4), o.ctypes.data_as(u32p))
+    return o
+
+
+# name -> (number of input tables, input widths (1 = base, 4 = EF), stored evals per round, output width)
+SUMCHECKS = {
+    "product": ("zko_prove_product", (1, 1), 3, 1),
+    "triple": ("zko_prove_triple", (1, 1, 1), 4, 1),
+    "product_ones": ("zko_prove_product_ones", (1,), 2, 1),
+    "product_ef": ("zko_prove_product_ef", (1, 1), 2, 4),
+    "product_ef_full": ("zko_prove_product_ef_full", (4, 4), 3, 4),
+    "product_ef_mixed": ("zko_prove_product_ef_mixed", (4, 1), 3, 4),
+    "triple_ef_full": ("zko_prove_triple_ef_full", (4, 4, 4), 3, 4),
+    "product_ones_ef_full": ("zko_prove_product_ones_ef_full", (4,), 2, 4),
+}
+
+
+def prove(kind: str, tr: Transcript, tables, num_vars: int):
+    """Run one sumcheck prover; returns (round_polys[nv, epr*w], challenges[nv, w], finals[k, w])."""
+    fn, widths, epr, w = SUMCHECKS[kind]
+    ptrs = []
+    keep = []
+    for t in tables:
+        a, p = _u32(t)
+        keep.append(a)
+        ptrs.append(p)
+    nfin = max(2, len(widths))
+    polys = np.zeros((num_vars, epr * w), np.uint32)
+    chal = np.zeros((num_vars, w), np.uint32)
+    fin = np.zeros((nfin, w), np.uint32)
+    getattr(lib(), fn)(tr.h, *ptrs, C.c_size_t(num_vars), polys.ctypes.data_as(u32p),
+                       chal.ctypes.data_as(u32p), fin.ctypes.data_as(u32p))
+    return polys, chal, fin
+
+
+def verify(kind: str, tr: Transcript, claimed, polys, chal, fin) -> bool:
+    """Verifier restatement for the matching prover kind (challenges may be an empty array)."""
+    _, widths, epr, w = SUMCHECKS[kind]
+    polys, pp = _u32(polys)
+    chal, pc = _u32(chal)
+    fin, pf = _u32(fin)
+    nv = polys.shape[0]
+    nchal = chal.size // w
+    triple = kind.startswith("triple")
+    if w == 1:
+        fn = lib().zko_verify_triple if triple else lib().zko_verify_product
+        return bool(fn(tr.h, C.c_uint32(int(claimed)), pp, C.c_size_t(nv), C.c_size_t(epr), pc, C.c_size_t(nchal), pf))
+    cl, pcl = _u32(claimed)
+    fn = lib().zko_verify_triple_ef if triple else lib().zko_verify_product_ef
+    return bool(fn(tr.h, pcl, pp, C.c_size_t(nv), C.c_size_t(epr), pc, C.c_size_t(nchal), pf))
