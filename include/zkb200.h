@@ -1,0 +1,108 @@
+/* zkb200 — C ABI of the B200 prover backend for zk_ml_prover's sumcheck hot path.
+ *
+ * Every entry point is `extern "C"`, takes plain pointers and sizes, and returns an int32
+ * status: 0 = ok, nonzero = one of the ZKB_E_* codes below (message via zkb_last_error).
+ * The reference's GPU seam turns a failed command buffer into a panic
+ * (rust/zk_ml_prover/src/gpu/metal_device.rs:36-45); a Rust shim over this ABI does the
+ * same with a nonzero status.  There is no CPU fallback: without a CUDA device every call
+ * that needs one fails with ZKB_E_CUDA.
+ *
+ * Field elements are canonical u32 in [0, 2^31-1).  Extension-field (M31^4) elements are four
+ * u32 in the reference's EFElement order [re(c0), im(c0), re(c1), im(c1)]
+ * (rust/zk_ml_prover/src/proving/sumcheck.rs:67-96).
+ *
+ * Pointer arguments named `*_dev` are device pointers of the context's GPU; everything else
+ * is host memory owned by the caller.  A context owns one CUDA stream; calls on one context
+ * are ordered, different contexts may be used concurrently from different threads (the
+ * reference calls its GPU kernels from rayon workers, gpu/metal_kernels.rs:22-44).
+ */
+#ifndef ZKB200_H
+#define ZKB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct zkb_ctx zkb_ctx;
+typedef struct zkb_transcript zkb_transcript;
+
+enum {
+    ZKB_OK = 0,
+    ZKB_E_CUDA = 1,         /* CUDA runtime error (no device, out of memory, launch failure) */
+    ZKB_E_ARG = 2,          /* bad argument (null pointer, size not a power of two, ...) */
+    ZKB_E_LOGUP_IDENTITY = 3,   /* "LogUp identity failed — invalid lookups" (lookup.rs:572-577, 733-738) */
+    ZKB_E_ALPHA_COLLISION = 4,  /* "alpha collision with lookup/table encoding" (lookup.rs:550-555, 712-717) */
+    ZKB_E_NOT_QR = 5,       /* "compute_r: d/sum_sq is not a quadratic residue" (transformer/mod.rs:182) */
+    ZKB_E_LENGTH = 6,       /* a length assertion of the reference failed (matmul.rs:161, 861) */
+    ZKB_E_TOO_LARGE = 7     /* request exceeds a documented fixed capacity */
+};
+
+/* Sumcheck prover kinds; one per reference function. */
+enum {
+    ZKB_SC_PRODUCT = 0,              /* prove_product / _parallel / _best      sumcheck.rs:211-272, 389-482, 815-828 */
+    ZKB_SC_TRIPLE = 1,               /* prove_triple / _parallel / _best       sumcheck.rs:277-354, 487-619, 831-845 */
+    ZKB_SC_PRODUCT_ONES = 2,         /* prove_product_ones / _parallel / _best sumcheck.rs:857-978 */
+    ZKB_SC_PRODUCT_EF = 3,           /* prove_product_ef                       sumcheck.rs:1204-1258 */
+    ZKB_SC_PRODUCT_EF_FULL = 4,      /* prove_product_ef_full                  sumcheck.rs:1262-1315 */
+    ZKB_SC_PRODUCT_EF_MIXED = 5,     /* prove_product_ef_mixed                 matmul.rs:889-944 */
+    ZKB_SC_TRIPLE_EF_FULL = 6,       /* prove_triple_ef_full                   sumcheck.rs:1318-1384 */
+    ZKB_SC_PRODUCT_ONES_EF_FULL = 7  /* prove_product_ones_ef_full             sumcheck.rs:1389-1435 */
+};
+
+/* ---- context (replaces MetalContext::get / MetalKernels::get, gpu/metal_device.rs:47-77) ---- */
+int32_t zkb_ctx_create(int32_t device, zkb_ctx** out);
+void zkb_ctx_destroy(zkb_ctx* ctx);
+const char* zkb_last_error(const zkb_ctx* ctx);
+int32_t zkb_ctx_sync(zkb_ctx* ctx);
+/* CUDA-event stopwatch on the context's stream (for benchmarks; device time, not wall clock). */
+int32_t zkb_timer_start(zkb_ctx* ctx);
+int32_t zkb_timer_stop_ms(zkb_ctx* ctx, float* ms);
+/* When enabled, sumcheck calls record one CUDA event per launch; read back with
+ * zkb_profile_read: ms[i] = device time of launch i of the most recent sumcheck call. */
+int32_t zkb_profile_enable(zkb_ctx* ctx, int32_t on);
+int32_t zkb_profile_read(zkb_ctx* ctx, float* ms, size_t cap, size_t* n);
+/* Number of kernels this context has launched since creation. */
+uint64_t zkb_launch_count(const zkb_ctx* ctx);
+
+/* ---- device buffers (replaces GpuBuffer::from_field_slice / to_field_vec, gpu/metal_buffer.rs:9-53) ---- */
+int32_t zkb_buf_alloc(zkb_ctx* ctx, size_t n_u32, uint32_t** out_dev);
+int32_t zkb_buf_upload_u32(zkb_ctx* ctx, const uint32_t* host, size_t n, uint32_t* dst_dev);
+int32_t zkb_buf_download_u32(zkb_ctx* ctx, const uint32_t* src_dev, size_t n, uint32_t* host);
+int32_t zkb_buf_free(zkb_ctx* ctx, uint32_t* dev);
+
+/* ---- transcript (device-resident mirror of Transcript, sumcheck.rs:110-206) ---- */
+int32_t zkb_tr_new(zkb_ctx* ctx, const uint8_t* label, size_t len, zkb_transcript** out);   /* Transcript::new   :115-119 */
+void zkb_tr_free(zkb_transcript* tr);
+int32_t zkb_tr_absorb_u32(zkb_transcript* tr, uint32_t v);                                  /* absorb             :121-123 */
+int32_t zkb_tr_absorb_many(zkb_transcript* tr, const uint32_t* host, size_t n);              /* absorb_many        :125-129 */
+int32_t zkb_tr_absorb_many_dev(zkb_transcript* tr, const uint32_t* dev, size_t n);
+int32_t zkb_tr_absorb_bytes(zkb_transcript* tr, const uint8_t* bytes, size_t n);             /* absorb_bytes       :177-179 */
+int32_t zkb_tr_squeeze(zkb_transcript* tr, uint32_t* out);                                  /* squeeze            :147-171 */
+int32_t zkb_tr_squeeze_ef(zkb_transcript* tr, uint32_t out[4]);                              /* squeeze_ef         :182-188 */
+/* Serialised SHA-256 stream state (h[8] LE u32, buflen u32, pad u32, total u64, buf[64]) so a
+ * host-side Transcript and the device one can hand the stream to each other. */
+#define ZKB_TR_STATE_BYTES 112
+int32_t zkb_tr_export(zkb_transcript* tr, uint8_t state[ZKB_TR_STATE_BYTES]);
+int32_t zkb_tr_import(zkb_transcript* tr, const uint8_t state[ZKB_TR_STATE_BYTES]);
+
+/* ---- sumcheck provers ----
+ * tables[i] holds 2^num_vars elements (u32 each for base-field inputs, 4 u32 each for EF
+ * inputs; which is fixed by `kind`).  `on_device` != 0: tables are device pointers and are
+ * left untouched.  Outputs (host memory):
+ *   round_polys  num_vars x (stored evals per round) x w   u32
+ *   challenges   num_vars x w                               u32
+ *   finals       (number of tables, min 2) x w              u32   (f(s), g(s)[, h(s)]; f(s)=1 for ONES)
+ * with w = 1 for base-field kinds and 4 for EF kinds; stored evals per round: PRODUCT 3
+ * [s0,s1,s2], TRIPLE 4, PRODUCT_ONES 2 [s0,s2], PRODUCT_EF 2 [s0,s2], PRODUCT_EF_FULL 3,
+ * PRODUCT_EF_MIXED 3, TRIPLE_EF_FULL 3 [s0,s2,s3], PRODUCT_ONES_EF_FULL 2 [s0,s2]. */
+int32_t zkb_sumcheck_prove(zkb_ctx* ctx, zkb_transcript* tr, int32_t kind, const uint32_t* const* tables,
+                           uint32_t num_vars, int32_t on_device, uint32_t* round_polys, uint32_t* challenges,
+                           uint32_t* finals);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ZKB200_H */

@@ -1,0 +1,90 @@
+// Host-side context: one CUDA stream, a growable scratch arena, the per-stream reduction
+// scratch of the sumcheck kernels, and error bookkeeping for the C ABI.
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <cstdio>
+#include <string>
+#include <vector>
+#include "../../include/zkb200.h"
+#include "sumcheck.cuh"
+
+namespace zkb {
+
+struct CudaFail { std::string msg; };
+
+#define ZKB_CUDA(expr)                                                                          \
+    do {                                                                                        \
+        cudaError_t _e = (expr);                                                                \
+        if (_e != cudaSuccess)                                                                  \
+            throw ::zkb::CudaFail{std::string(#expr) + ": " + cudaGetErrorString(_e)};          \
+    } while (0)
+
+struct ArgFail { int32_t code; std::string msg; };
+
+}  // namespace zkb
+
+struct zkb_ctx {
+    int device = 0;
+    int sm_count = 148;
+    cudaStream_t stream = nullptr;
+    zkb::u32* partials = nullptr;
+    unsigned int* counter = nullptr;
+    zkb::u32* status = nullptr;          // device status word(s) written by kernels
+    std::string err;
+    uint64_t launches = 0;
+
+    // scratch arena: bump allocation, rewound by the caller that opened the frame
+    struct Chunk { char* base; size_t cap; size_t used; };
+    std::vector<Chunk> chunks;
+
+    // stopwatch + per-launch profile
+    cudaEvent_t t0 = nullptr, t1 = nullptr;
+    bool profile = false;
+    std::vector<cudaEvent_t> prof_events;
+    size_t prof_used = 0;
+
+    void use() { ZKB_CUDA(cudaSetDevice(device)); }
+
+    void* scratch(size_t bytes) {
+        bytes = (bytes + 255) & ~size_t(255);
+        if (!chunks.empty()) {
+            Chunk& c = chunks.back();
+            if (c.used + bytes <= c.cap) { void* p = c.base + c.used; c.used += bytes; return p; }
+        }
+        size_t cap = bytes;
+        if (cap < (size_t(64) << 20)) cap = size_t(64) << 20;
+        char* p = nullptr;
+        ZKB_CUDA(cudaMalloc(&p, cap));
+        chunks.push_back(Chunk{p, cap, bytes});
+        return p;
+    }
+    // Rewind everything; if the arena fragmented into several chunks, replace them by one.
+    void scratch_reset() {
+        if (chunks.size() > 1) {
+            ZKB_CUDA(cudaStreamSynchronize(stream));
+            size_t total = 0;
+            for (auto& c : chunks) { total += c.cap; cudaFree(c.base); }
+            chunks.clear();
+            char* p = nullptr;
+            ZKB_CUDA(cudaMalloc(&p, total));
+            chunks.push_back(Chunk{p, total, 0});
+        } else if (!chunks.empty()) {
+            chunks[0].used = 0;
+        }
+    }
+    void prof_mark() {
+        if (!profile) return;
+        if (prof_used == prof_events.size()) {
+            cudaEvent_t e;
+            ZKB_CUDA(cudaEventCreate(&e));
+            prof_events.push_back(e);
+        }
+        ZKB_CUDA(cudaEventRecord(prof_events[prof_used++], stream));
+    }
+};
+
+struct zkb_transcript {
+    zkb_ctx* ctx;
+    zkb::TrState* dev;
+};

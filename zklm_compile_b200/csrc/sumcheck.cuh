@@ -1,0 +1,308 @@
+// Sumcheck round kernels: fold the tables with the previous challenge and, in the same pass,
+// accumulate the next round polynomial; the CTA that finishes last adds up the per-CTA
+// partials, advances the device transcript and publishes the next challenge.
+//
+// Protocols covered (reference: rust/zk_ml_prover/src/proving/sumcheck.rs):
+//   PRODUCT  sum f g      s0 = sum f0 g0, s1 = sum f1 g1, s2 = sum (2f1-f0)(2g1-g0)   (:211-272, :1204-1315)
+//   TRIPLE   sum f g h    s0..s3 at t = 0,1,2,3                                      (:277-354, :1318-1384)
+//   ONES     sum g        s0 = sum g0, s1 = sum g1, s2 = 2 s1 - s0                    (:857-902, :1389-1435)
+// with base-field (Fp) or extension-field (Fe) challenges.  Tables are folded MSB-first: the
+// pair of index j is (j, j + half).
+//
+// State between launches: tables of `size` elements plus a challenge that is still to be
+// folded in ("pending").  A round launch with FOLD reads the size-4h tables, writes the
+// size-2h folded tables (quarter j pairs with j + 2h -> lo, j + h with j + 3h -> hi; thread j
+// is the only reader and writer of those six slots, so in-place folding is race-free) and
+// reduces over the h pairs (lo, hi).  Round 0 has nothing to fold and only reduces.
+#pragma once
+#include "m31.cuh"
+#include "transcript.cuh"
+
+namespace zkb {
+
+enum ScKind { SC_PRODUCT = 0, SC_TRIPLE = 1, SC_ONES = 2 };
+
+template <int KIND> struct ScTraits;
+template <> struct ScTraits<SC_PRODUCT> { static constexpr int NT = 2, NACC = 3, NABS = 3; };
+template <> struct ScTraits<SC_TRIPLE>  { static constexpr int NT = 3, NACC = 4, NABS = 4; };
+template <> struct ScTraits<SC_ONES>    { static constexpr int NT = 1, NACC = 2, NABS = 3; };
+
+template <class T> struct Width;
+template <> struct Width<Fp> { static constexpr int W = 1; };
+template <> struct Width<Fe> { static constexpr int W = 4; };
+
+template <bool C, class A, class B> struct Sel { typedef A type; };
+template <class A, class B> struct Sel<false, A, B> { typedef B type; };
+
+constexpr int SC_MAX_GRID = 2048;   // upper bound on CTAs of a round launch (sizes `partials`)
+constexpr int SC_TAIL_THREADS = 1024;
+
+struct ScTables {
+    const void* src[3];
+    void* dst[3];
+};
+
+// Per-sumcheck device bookkeeping.
+struct ScIO {
+    TrState* tr;            // device transcript, advanced in place
+    u32* partials;          // [SC_MAX_GRID][16]
+    unsigned int* counter;  // ticket for "last CTA done"; left at 0
+    u32* polys;             // [num_vars][nstored][W]
+    u32* chal;              // [num_vars][W]
+    u32* fin;               // [NT][W]
+    u32 store_mask;         // bit k set: s_k is stored in the proof (all s_k are absorbed)
+    u32 nstored;
+};
+
+// ---- small conversions ---------------------------------------------------------------------
+__device__ __forceinline__ void to_words(Fp a, u32* w) { w[0] = a.v; }
+__device__ __forceinline__ void to_words(Fe a, u32* w) { w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; }
+__device__ __forceinline__ void from_words(Fp& a, const u32* w) { a.v = w[0]; }
+__device__ __forceinline__ void from_words(Fe& a, const u32* w) { a = Fe{w[0], w[1], w[2], w[3]}; }
+__device__ __forceinline__ void widen_to(Fp a, Fp& o) { o = a; }
+__device__ __forceinline__ void widen_to(Fp a, Fe& o) { o = fe_from(a); }
+__device__ __forceinline__ void widen_to(Fe a, Fe& o) { o = a; }
+template <class T> __device__ __forceinline__ T zero_of();
+template <> __device__ __forceinline__ Fp zero_of<Fp>() { return fp_zero(); }
+template <> __device__ __forceinline__ Fe zero_of<Fe>() { return fe_zero(); }
+
+template <class T> __device__ __forceinline__ T ld_el(const void* base, size_t i) {
+    return ld_fe(reinterpret_cast<const T*>(base) + i);
+}
+template <class T> __device__ __forceinline__ void st_el(void* base, size_t i, T v) {
+    st_fe(reinterpret_cast<T*>(base) + i, v);
+}
+
+// ---- per-pair accumulation -----------------------------------------------------------------
+template <int KIND, class T>
+__device__ __forceinline__ void sc_accumulate(T* acc, const T* lo, const T* hi) {
+    if constexpr (KIND == SC_PRODUCT) {
+        acc[0] = acc[0] + lo[0] * lo[1];
+        acc[1] = acc[1] + hi[0] * hi[1];
+        acc[2] = acc[2] + dbl_minus(hi[0], lo[0]) * dbl_minus(hi[1], lo[1]);
+    } else if constexpr (KIND == SC_TRIPLE) {
+        acc[0] = acc[0] + lo[0] * lo[1] * lo[2];
+        acc[1] = acc[1] + hi[0] * hi[1] * hi[2];
+        T f2 = dbl_minus(hi[0], lo[0]), g2 = dbl_minus(hi[1], lo[1]), h2 = dbl_minus(hi[2], lo[2]);
+        acc[2] = acc[2] + f2 * g2 * h2;
+        // value at t = 3: x2 + (x1 - x0) = 3 x1 - 2 x0 (sumcheck.rs:316-321, 1356-1359)
+        T f3 = f2 + (hi[0] - lo[0]), g3 = g2 + (hi[1] - lo[1]), h3 = h2 + (hi[2] - lo[2]);
+        acc[3] = acc[3] + f3 * g3 * h3;
+    } else {
+        acc[0] = acc[0] + lo[0];
+        acc[1] = acc[1] + hi[0];
+    }
+}
+
+// One (optionally folding) pass of the calling CTA(s) over pairs j in [j0, half) step `stride`.
+template <int KIND, class SrcT, class ChalT, bool FOLD>
+__device__ __forceinline__ void sc_pass(const ScTables& tb, size_t half, ChalT r, size_t j0, size_t stride,
+                                        typename Sel<FOLD, ChalT, SrcT>::type* acc) {
+    typedef typename Sel<FOLD, ChalT, SrcT>::type AccT;
+    constexpr int NT = ScTraits<KIND>::NT;
+    for (size_t j = j0; j < half; j += stride) {
+        AccT lo[NT], hi[NT];
+#pragma unroll
+        for (int t = 0; t < NT; t++) {
+            if constexpr (FOLD) {
+                SrcT a = ld_el<SrcT>(tb.src[t], j), b = ld_el<SrcT>(tb.src[t], j + 2 * half);
+                SrcT c = ld_el<SrcT>(tb.src[t], j + half), d = ld_el<SrcT>(tb.src[t], j + 3 * half);
+                ChalT l = lerp(a, b, r), h = lerp(c, d, r);
+                st_el<ChalT>(tb.dst[t], j, l);
+                st_el<ChalT>(tb.dst[t], j + half, h);
+                widen_to(l, lo[t]);
+                widen_to(h, hi[t]);
+            } else {
+                SrcT a = ld_el<SrcT>(tb.src[t], j), b = ld_el<SrcT>(tb.src[t], j + half);
+                widen_to(a, lo[t]);
+                widen_to(b, hi[t]);
+            }
+        }
+        sc_accumulate<KIND, AccT>(acc, lo, hi);
+    }
+}
+
+// Sum `nw` canonical words per thread across the CTA; result valid in thread 0 (and in red[] row 0).
+template <int NWORDS>
+__device__ __forceinline__ void block_sum_words(u32* v, u32* red /* [32][NWORDS] shared */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+#pragma unroll
+    for (int k = 0; k < NWORDS; k++) {
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) v[k] = add31(v[k], __shfl_down_sync(0xffffffffu, v[k], off));
+    }
+    if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < NWORDS; k++) red[warp * NWORDS + k] = v[k];
+    }
+    __syncthreads();
+    if (warp == 0) {
+#pragma unroll
+        for (int k = 0; k < NWORDS; k++) {
+            u32 x = lane < nwarps ? red[lane * NWORDS + k] : 0u;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) x = add31(x, __shfl_down_sync(0xffffffffu, x, off));
+            v[k] = x;
+        }
+    }
+    __syncthreads();
+}
+
+// Thread 0: turn the summed accumulators into the round message, advance the transcript,
+// emit the stored evaluations and the challenge.
+template <int KIND, class AccT, class ChalT>
+__device__ __forceinline__ ChalT sc_finish_round(const u32* words, const ScIO& io, u32 round, Tr& tr) {
+    constexpr int NACC = ScTraits<KIND>::NACC, NABS = ScTraits<KIND>::NABS;
+    constexpr int WA = Width<AccT>::W, WC = Width<ChalT>::W;
+    ChalT s[4];
+#pragma unroll
+    for (int k = 0; k < NACC; k++) {
+        AccT a;
+        from_words(a, words + k * WA);
+        widen_to(a, s[k]);
+    }
+    if constexpr (KIND == SC_ONES) s[2] = s[1] + s[1] - s[0];
+    u32* out = io.polys + (size_t)round * io.nstored * WC;
+#pragma unroll
+    for (int k = 0; k < NABS; k++) {
+        tr_absorb_el(tr, s[k]);
+        if (io.store_mask & (1u << k)) { to_words(s[k], out); out += WC; }
+    }
+    ChalT r;
+    tr_squeeze_el(tr, r);
+    to_words(r, io.chal + (size_t)round * WC);
+    return r;
+}
+
+// ---- multi-CTA round launch ----------------------------------------------------------------
+template <int KIND, class SrcT, class ChalT, bool FOLD>
+__global__ void __launch_bounds__(256) sc_round_kernel(ScTables tb, size_t half, u32 round, ScIO io) {
+    typedef typename Sel<FOLD, ChalT, SrcT>::type AccT;
+    constexpr int NACC = ScTraits<KIND>::NACC, WA = Width<AccT>::W, NW = NACC * WA;
+    __shared__ u32 red[32 * 16];
+    __shared__ __align__(16) unsigned char trbuf[64];
+    __shared__ bool is_last;
+
+    ChalT r = zero_of<ChalT>();
+    if constexpr (FOLD) from_words(r, io.chal + (size_t)(round - 1) * Width<ChalT>::W);
+
+    AccT acc[NACC];
+#pragma unroll
+    for (int k = 0; k < NACC; k++) acc[k] = zero_of<AccT>();
+    sc_pass<KIND, SrcT, ChalT, FOLD>(tb, half, r, (size_t)blockIdx.x * blockDim.x + threadIdx.x,
+                                     (size_t)gridDim.x * blockDim.x, acc);
+    u32 w[NW];
+#pragma unroll
+    for (int k = 0; k < NACC; k++) to_words(acc[k], w + k * WA);
+    block_sum_words<NW>(w, red);
+
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int k = 0; k < NW; k++) io.partials[(size_t)blockIdx.x * 16 + k] = w[k];
+        __threadfence();
+        unsigned int ticket = atomicAdd(io.counter, 1u);
+        is_last = (ticket == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+
+    u32 t[NW];
+#pragma unroll
+    for (int k = 0; k < NW; k++) t[k] = 0;
+    for (u32 b = threadIdx.x; b < gridDim.x; b += blockDim.x) {
+#pragma unroll
+        for (int k = 0; k < NW; k++) t[k] = add31(t[k], __ldcg(io.partials + (size_t)b * 16 + k));
+    }
+    block_sum_words<NW>(t, red);
+    if (threadIdx.x == 0) {
+        Tr tr;
+        tr_load(tr, io.tr, trbuf);
+        sc_finish_round<KIND, AccT, ChalT>(t, io, round, tr);
+        tr_store(tr, io.tr);
+        *io.counter = 0;
+    }
+}
+
+// ---- single-CTA tail: all remaining rounds and the final evaluations -------------------------
+// Entry state: tables in tb.src (type SrcT) of `size` elements; if `pending`, the challenge
+// of round `round - 1` still has to be folded in.  Runs rounds round .. num_vars-1, then folds
+// the last challenge into the two remaining elements of each table and writes the finals.
+template <int KIND, class SrcT, class ChalT>
+__global__ void __launch_bounds__(SC_TAIL_THREADS) sc_tail_kernel(ScTables tb, size_t size, u32 round, u32 num_vars,
+                                                                  int pending, ScIO io) {
+    constexpr int NT = ScTraits<KIND>::NT, NACC = ScTraits<KIND>::NACC;
+    constexpr int WC = Width<ChalT>::W, WS = Width<SrcT>::W;
+    __shared__ u32 red[32 * 16];
+    __shared__ __align__(16) unsigned char trbuf[64];
+    __shared__ u32 r_sh[4];
+
+    Tr tr;
+    if (threadIdx.x == 0) tr_load(tr, io.tr, trbuf);
+    ChalT r = zero_of<ChalT>();
+    if (pending) from_words(r, io.chal + (size_t)(round - 1) * WC);
+    bool in_src = true;           // tables still in their input buffers / input type
+    ScTables cur = tb;
+
+    for (; round < num_vars; round++) {
+        u32 w[16];
+        if (in_src) {
+            if (!pending) {
+                SrcT acc[NACC];
+#pragma unroll
+                for (int k = 0; k < NACC; k++) acc[k] = zero_of<SrcT>();
+                sc_pass<KIND, SrcT, ChalT, false>(cur, size / 2, r, threadIdx.x, blockDim.x, acc);
+#pragma unroll
+                for (int k = 0; k < NACC; k++) {
+                    ChalT e; widen_to(acc[k], e); to_words(e, w + k * WC);
+                }
+            } else {
+                ChalT acc[NACC];
+#pragma unroll
+                for (int k = 0; k < NACC; k++) acc[k] = zero_of<ChalT>();
+                sc_pass<KIND, SrcT, ChalT, true>(cur, size / 4, r, threadIdx.x, blockDim.x, acc);
+#pragma unroll
+                for (int k = 0; k < NACC; k++) to_words(acc[k], w + k * WC);
+                size /= 2;
+                in_src = false;
+#pragma unroll
+                for (int t = 0; t < NT; t++) cur.src[t] = cur.dst[t];
+            }
+        } else {
+            ChalT acc[NACC];
+#pragma unroll
+            for (int k = 0; k < NACC; k++) acc[k] = zero_of<ChalT>();
+            sc_pass<KIND, ChalT, ChalT, true>(cur, size / 4, r, threadIdx.x, blockDim.x, acc);
+#pragma unroll
+            for (int k = 0; k < NACC; k++) to_words(acc[k], w + k * WC);
+            size /= 2;
+        }
+        block_sum_words<NACC * WC>(w, red);
+        if (threadIdx.x == 0) {
+            ChalT rn = sc_finish_round<KIND, ChalT, ChalT>(w, io, round, tr);
+            to_words(rn, r_sh);
+        }
+        __syncthreads();
+        from_words(r, r_sh);
+        pending = 1;
+        __syncthreads();
+    }
+
+    if (threadIdx.x == 0) {
+        tr_store(tr, io.tr);
+        // size == 2 here: fold the last challenge in.
+#pragma unroll
+        for (int t = 0; t < NT; t++) {
+            ChalT v;
+            if (in_src) v = lerp(ld_el<SrcT>(cur.src[t], 0), ld_el<SrcT>(cur.src[t], 1), r);
+            else {
+                ChalT a = ld_el<ChalT>(cur.src[t], 0), b = ld_el<ChalT>(cur.src[t], 1);
+                v = a + r * (b - a);
+            }
+            to_words(v, io.fin + t * WC);
+        }
+    }
+    (void)WS;
+}
+
+}  // namespace zkb

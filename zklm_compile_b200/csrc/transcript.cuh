@@ -1,0 +1,171 @@
+// Device-resident Fiat-Shamir transcript: a SHA-256 stream that lives in global memory and is
+// advanced by one thread of whichever kernel finishes a protocol step, so challenges never
+// travel to the host.  Mirrors the reference `Transcript`
+// (rust/zk_ml_prover/src/proving/sumcheck.rs:110-206):
+//   new(label)      stream = label bytes
+//   absorb(u32)     4 little-endian bytes; absorb_bytes(raw)
+//   squeeze()       d = SHA-256(stream); stream := d; first of the four little-endian u64
+//                   windows of d below 2^64 - 4, reduced mod p
+//   squeeze_ef()    four squeezes -> (re c0, im c0, re c1, im c1)
+#pragma once
+#include "m31.cuh"
+
+namespace zkb {
+
+// Global-memory image of the stream.  `buf` holds the bytes not yet compressed.
+struct TrState {
+    u32 h[8];
+    u32 buflen;      // 0..63
+    u32 _pad;
+    u64 total;       // bytes absorbed into the current SHA-256 stream
+    unsigned char buf[64];
+};
+
+__constant__ u32 SHA_K[64] = {
+    0x428a2f98, 0x71374491, 0xb5c0fbcf, 0xe9b5dba5, 0x3956c25b, 0x59f111f1, 0x923f82a4, 0xab1c5ed5,
+    0xd807aa98, 0x12835b01, 0x243185be, 0x550c7dc3, 0x72be5d74, 0x80deb1fe, 0x9bdc06a7, 0xc19bf174,
+    0xe49b69c1, 0xefbe4786, 0x0fc19dc6, 0x240ca1cc, 0x2de92c6f, 0x4a7484aa, 0x5cb0a9dc, 0x76f988da,
+    0x983e5152, 0xa831c66d, 0xb00327c8, 0xbf597fc7, 0xc6e00bf3, 0xd5a79147, 0x06ca6351, 0x14292967,
+    0x27b70a85, 0x2e1b2138, 0x4d2c6dfc, 0x53380d13, 0x650a7354, 0x766a0abb, 0x81c2c92e, 0x92722c85,
+    0xa2bfe8a1, 0xa81a664b, 0xc24b8b70, 0xc76c51a3, 0xd192e819, 0xd6990624, 0xf40e3585, 0x106aa070,
+    0x19a4c116, 0x1e376c08, 0x2748774c, 0x34b0bcb5, 0x391c0cb3, 0x4ed8aa4a, 0x5b9cca4f, 0x682e6ff3,
+    0x748f82ee, 0x78a5636f, 0x84c87814, 0x8cc70208, 0x90befffa, 0xa4506ceb, 0xbef9a3f7, 0xc67178f2};
+
+__device__ __forceinline__ u32 rotr32(u32 x, int n) { return __funnelshift_r(x, x, n); }
+__device__ __forceinline__ u32 bswap32(u32 x) { return __byte_perm(x, 0, 0x0123); }
+
+// One SHA-256 compression of the 16 big-endian words in w[] into h[].
+__device__ __noinline__ void sha256_compress(u32* h, u32* w) {
+    u32 a = h[0], b = h[1], c = h[2], d = h[3], e = h[4], f = h[5], g = h[6], hh = h[7];
+#pragma unroll
+    for (int i = 0; i < 64; i++) {
+        if (i >= 16) {
+            u32 w15 = w[(i + 1) & 15], w2 = w[(i + 14) & 15];
+            u32 s0 = rotr32(w15, 7) ^ rotr32(w15, 18) ^ (w15 >> 3);
+            u32 s1 = rotr32(w2, 17) ^ rotr32(w2, 19) ^ (w2 >> 10);
+            w[i & 15] = w[i & 15] + s0 + w[(i + 9) & 15] + s1;
+        }
+        u32 S1 = rotr32(e, 6) ^ rotr32(e, 11) ^ rotr32(e, 25);
+        u32 ch = (e & f) ^ (~e & g);
+        u32 t1 = hh + S1 + ch + SHA_K[i] + w[i & 15];
+        u32 S0 = rotr32(a, 2) ^ rotr32(a, 13) ^ rotr32(a, 22);
+        u32 mj = (a & b) ^ (a & c) ^ (b & c);
+        hh = g; g = f; f = e; e = d + t1; d = c; c = b; b = a; a = t1 + S0 + mj;
+    }
+    h[0] += a; h[1] += b; h[2] += c; h[3] += d; h[4] += e; h[5] += f; h[6] += g; h[7] += hh;
+}
+
+// Working copy used by the single thread that advances the transcript.  `buf` points to 64
+// bytes of 4-byte-aligned scratch (shared memory in the kernels; byte stores are cheap there).
+struct Tr {
+    u32 h[8];
+    u32 buflen;
+    u64 total;
+    unsigned char* buf;
+};
+
+__device__ __forceinline__ void tr_iv(u32 h[8]) {
+    h[0] = 0x6a09e667u; h[1] = 0xbb67ae85u; h[2] = 0x3c6ef372u; h[3] = 0xa54ff53au;
+    h[4] = 0x510e527fu; h[5] = 0x9b05688cu; h[6] = 0x1f83d9abu; h[7] = 0x5be0cd19u;
+}
+__device__ __forceinline__ void tr_load(Tr& t, const TrState* g, unsigned char* scratch) {
+#pragma unroll
+    for (int i = 0; i < 8; i++) t.h[i] = g->h[i];
+    t.buflen = g->buflen;
+    t.total = g->total;
+    t.buf = scratch;
+    const u32* src = reinterpret_cast<const u32*>(g->buf);
+    u32* dst = reinterpret_cast<u32*>(scratch);
+#pragma unroll
+    for (int i = 0; i < 16; i++) dst[i] = src[i];
+}
+__device__ __forceinline__ void tr_store(const Tr& t, TrState* g) {
+#pragma unroll
+    for (int i = 0; i < 8; i++) g->h[i] = t.h[i];
+    g->buflen = t.buflen;
+    g->total = t.total;
+    u32* dst = reinterpret_cast<u32*>(g->buf);
+    const u32* src = reinterpret_cast<const u32*>(t.buf);
+#pragma unroll
+    for (int i = 0; i < 16; i++) dst[i] = src[i];
+}
+__device__ __forceinline__ void tr_flush_block(Tr& t) {
+    u32 w[16];
+    const u32* b = reinterpret_cast<const u32*>(t.buf);
+#pragma unroll
+    for (int i = 0; i < 16; i++) w[i] = bswap32(b[i]);
+    sha256_compress(t.h, w);
+    t.buflen = 0;
+}
+__device__ __forceinline__ void tr_absorb_byte(Tr& t, unsigned char c) {
+    t.buf[t.buflen++] = c;
+    t.total++;
+    if (t.buflen == 64) tr_flush_block(t);
+}
+__device__ __forceinline__ void tr_absorb_u32(Tr& t, u32 v) {
+    if ((t.buflen & 3) == 0) {           // aligned fast path: one word store
+        *reinterpret_cast<u32*>(t.buf + t.buflen) = v;
+        t.buflen += 4;
+        t.total += 4;
+        if (t.buflen == 64) tr_flush_block(t);
+    } else {
+        tr_absorb_byte(t, (unsigned char)v);
+        tr_absorb_byte(t, (unsigned char)(v >> 8));
+        tr_absorb_byte(t, (unsigned char)(v >> 16));
+        tr_absorb_byte(t, (unsigned char)(v >> 24));
+    }
+}
+__device__ __forceinline__ void tr_absorb_fe(Tr& t, Fe v) {
+    tr_absorb_u32(t, v.x); tr_absorb_u32(t, v.y); tr_absorb_u32(t, v.z); tr_absorb_u32(t, v.w);
+}
+__device__ __forceinline__ void tr_absorb_el(Tr& t, Fp v) { tr_absorb_u32(t, v.v); }
+__device__ __forceinline__ void tr_absorb_el(Tr& t, Fe v) { tr_absorb_fe(t, v); }
+__device__ inline void tr_absorb_bytes(Tr& t, const unsigned char* p, u32 n) {
+    for (u32 i = 0; i < n; i++) tr_absorb_byte(t, p[i]);
+}
+
+// Pad, compress, and restart the stream with the 32-byte digest as its first bytes.
+__device__ __forceinline__ void tr_finalize_reseed(Tr& t, u32 digest_be[8]) {
+    u64 bits = t.total * 8;
+    u32 n = t.buflen;
+    t.buf[n++] = 0x80;
+    while (n & 3) t.buf[n++] = 0;
+    u32* bw = reinterpret_cast<u32*>(t.buf);
+    if (n > 56) {
+        for (u32 i = n >> 2; i < 16; i++) bw[i] = 0;
+        tr_flush_block(t);
+        n = 0;
+    }
+    for (u32 i = n >> 2; i < 14; i++) bw[i] = 0;
+    bw[14] = bswap32((u32)(bits >> 32));
+    bw[15] = bswap32((u32)bits);
+    tr_flush_block(t);
+#pragma unroll
+    for (int i = 0; i < 8; i++) digest_be[i] = t.h[i];
+    tr_iv(t.h);
+#pragma unroll
+    for (int i = 0; i < 8; i++) bw[i] = bswap32(digest_be[i]);   // digest bytes in stream order
+    t.buflen = 32;
+    t.total = 32;
+}
+__device__ __forceinline__ u32 tr_squeeze(Tr& t) {
+    for (int guard = 0; guard < 64; guard++) {        // all four windows rejecting has probability 2^-248
+        u32 d[8];
+        tr_finalize_reseed(t, d);
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            u64 raw = (u64)bswap32(d[2 * c]) | ((u64)bswap32(d[2 * c + 1]) << 32);
+            if (raw < 0xfffffffffffffffcull) return red64(raw);
+        }
+    }
+    return 0;
+}
+__device__ __forceinline__ Fe tr_squeeze_fe(Tr& t) {
+    Fe r;
+    r.x = tr_squeeze(t); r.y = tr_squeeze(t); r.z = tr_squeeze(t); r.w = tr_squeeze(t);
+    return r;
+}
+__device__ __forceinline__ void tr_squeeze_el(Tr& t, Fp& r) { r.v = tr_squeeze(t); }
+__device__ __forceinline__ void tr_squeeze_el(Tr& t, Fe& r) { r = tr_squeeze_fe(t); }
+
+}  // namespace zkb
