@@ -72,6 +72,9 @@ int32_t zkb_buf_alloc(zkb_ctx* ctx, size_t n_u32, uint32_t** out_dev);
 int32_t zkb_buf_upload_u32(zkb_ctx* ctx, const uint32_t* host, size_t n, uint32_t* dst_dev);
 int32_t zkb_buf_download_u32(zkb_ctx* ctx, const uint32_t* src_dev, size_t n, uint32_t* host);
 int32_t zkb_buf_free(zkb_ctx* ctx, uint32_t* dev);
+/* Page-locked host memory, so that host-pointer calls copy at full PCIe rate. */
+int32_t zkb_host_alloc(zkb_ctx* ctx, size_t bytes, void** out_host);
+int32_t zkb_host_free(zkb_ctx* ctx, void* host);
 
 /* ---- transcript (device-resident mirror of Transcript, sumcheck.rs:110-206) ---- */
 int32_t zkb_tr_new(zkb_ctx* ctx, const uint8_t* label, size_t len, zkb_transcript** out);   /* Transcript::new   :115-119 */

@@ -281,6 +281,15 @@ int32_t zkb_buf_free(zkb_ctx* c, uint32_t* dev) {
     ZKB_TRY(c, { c->use(); ZKB_CUDA(cudaStreamSynchronize(c->stream)); ZKB_CUDA(cudaFree(dev)); });
 }
 
+int32_t zkb_host_alloc(zkb_ctx* c, size_t bytes, void** out) {
+    if (!c || !out) return ZKB_E_ARG;
+    ZKB_TRY(c, { c->use(); ZKB_CUDA(cudaHostAlloc(out, bytes ? bytes : 1, cudaHostAllocDefault)); });
+}
+int32_t zkb_host_free(zkb_ctx* c, void* host) {
+    if (!c) return ZKB_E_ARG;
+    ZKB_TRY(c, { c->use(); ZKB_CUDA(cudaFreeHost(host)); });
+}
+
 // ---- transcript
 int32_t zkb_tr_new(zkb_ctx* c, const uint8_t* label, size_t len, zkb_transcript** out) {
     if (!c || !out || (!label && len)) return ZKB_E_ARG;

@@ -85,6 +85,12 @@ class Context:
         check(self.h, _lib.lib().zkb_buf_upload_u32(self.h, a.ctypes.data_as(u32p), C.c_size_t(a.size), buf.ptr))
         return buf
 
+    def pinned_u32(self, n_u32: int) -> np.ndarray:
+        """numpy view of page-locked host memory (freed with the process)."""
+        p = C.c_void_p()
+        check(self.h, _lib.lib().zkb_host_alloc(self.h, C.c_size_t(n_u32 * 4), C.byref(p)))
+        return np.ctypeslib.as_array(C.cast(p, u32p), shape=(n_u32,))
+
     def alloc(self, n_u32: int, shape=None) -> "DeviceBuffer":
         return DeviceBuffer(self, n_u32, shape or (n_u32,))
 
