@@ -1,0 +1,180 @@
+// CPU ORACLE — TEST INFRASTRUCTURE ONLY.
+//
+// C entry points for the matmul / MLE-eval / element-wise / RMSNorm / LogUp / Qwen-layer
+// restatements.  Proofs come back as bincode bytes (oracle/bincode.hpp).
+#include "qwen_verify.hpp"
+#include <cstring>
+
+using namespace zko;
+
+static VF vf(const uint32_t* p, size_t n) { VF v(n); for (size_t i = 0; i < n; i++) v[i] = F(p[i]); return v; }
+static VEF vef(const uint32_t* p, size_t n) { VEF v(n); for (size_t i = 0; i < n; i++) v[i] = EF::from_u32x4(p + 4 * i); return v; }
+static Transcript& T(void* t) { return *static_cast<Transcript*>(t); }
+static size_t emit(const std::vector<uint8_t>& b, uint8_t* out, size_t cap) {
+    if (out && b.size() <= cap) memcpy(out, b.data(), b.size());
+    return b.size();
+}
+static void out_f(const VF& v, uint32_t* o) { for (size_t i = 0; i < v.size(); i++) o[i] = v[i].v; }
+
+extern "C" {
+
+void zko_commit_weights_fast(const uint32_t* w, size_t n, uint8_t* root) {
+    auto c = commit_weights_fast(vf(w, n));
+    memcpy(root, c.root.data(), 32);
+}
+void zko_matmul_forward(const uint32_t* w, const uint32_t* x, size_t m, size_t n, uint32_t* y) {
+    out_f(matmul_forward(vf(w, m * n), vf(x, n), m, n), y);
+}
+void zko_fold_eq_matvec(const uint32_t* w, size_t m, size_t n, const uint32_t* r, size_t log_m, uint32_t* out) {
+    out_f(fold_eq_matvec(vf(w, m * n), m, n, size_t(1) << log2_ceil(n), vf(r, log_m)), out);
+}
+void zko_fold_eq_matvec_ef(const uint32_t* w, size_t m, size_t n, const uint32_t* r, size_t log_m, uint32_t* out) {
+    VEF o = fold_eq_matvec_ef(vf(w, m * n), m, n, size_t(1) << log2_ceil(n), vef(r, log_m));
+    for (size_t i = 0; i < o.size(); i++) o[i].to_u32x4(out + 4 * i);
+}
+size_t zko_prove_matmul_succinct(void* t, const uint32_t* w, const uint32_t* x, const uint32_t* y, size_t m, size_t n,
+                                 uint8_t* out, size_t cap) {
+    Bin b; b.put(prove_matmul_succinct(vf(w, m * n), vf(x, n), vf(y, m), m, n, T(t)));
+    return emit(b.b, out, cap);
+}
+size_t zko_prove_matmul_succinct_ef(void* t, const uint32_t* w, const uint32_t* x, const uint32_t* y, size_t m, size_t n,
+                                    uint8_t* out, size_t cap) {
+    Bin b; b.put(prove_matmul_succinct_ef(vf(w, m * n), vf(x, n), vf(y, m), m, n, T(t)));
+    return emit(b.b, out, cap);
+}
+// prove + verify round trip of the restated verifier (1 = accepted)
+int zko_matmul_succinct_roundtrip(const uint32_t* w, const uint32_t* x, const uint32_t* y, size_t m, size_t n, int ef, int tamper) {
+    Transcript pt("rt"), vt("rt");
+    VF W = vf(w, m * n), X = vf(x, n), Y = vf(y, m);
+    if (ef) {
+        auto p = prove_matmul_succinct_ef(W, X, Y, m, n, pt);
+        if (tamper) p.matmul_proof.x_at_s[0] ^= 1;
+        return verify_matmul_succinct_ef(p, Y, m, n, vt).valid;
+    }
+    auto p = prove_matmul_succinct(W, X, Y, m, n, pt);
+    if (tamper) p.matmul_proof.x_at_s ^= 1;
+    return verify_matmul_succinct(p, Y, m, n, vt).valid;
+}
+size_t zko_prove_mle_eval_ef_base_bound(void* t, const uint32_t* w, size_t n, const uint32_t* point, size_t k,
+                                        const uint8_t* label, size_t label_len, uint8_t* out, size_t cap, uint32_t* claimed) {
+    VF W = vf(w, n);
+    WeightCommitment c = commit_weights_fast(padded(W, size_t(1) << k));
+    EF cl;
+    Bin b; b.put(prove_mle_eval_ef_base_bound(W, vef(point, k), std::string((const char*)label, label_len), c, T(t), &cl));
+    cl.to_u32x4(claimed);
+    return emit(b.b, out, cap);
+}
+size_t zko_prove_mle_eval_bound(void* t, const uint32_t* w, size_t n, const uint32_t* point, size_t k,
+                                const uint8_t* label, size_t label_len, uint8_t* out, size_t cap, uint32_t* claimed) {
+    VF W = vf(w, n);
+    WeightCommitment c = commit_weights_fast(padded(W, size_t(1) << k));
+    F cl;
+    Bin b; b.put(prove_mle_eval_bound(W, vf(point, k), std::string((const char*)label, label_len), c, T(t), &cl));
+    *claimed = cl.v;
+    return emit(b.b, out, cap);
+}
+size_t zko_prove_hadamard_ef(void* t, const uint32_t* a, const uint32_t* b_, const uint32_t* c, size_t n, const uint32_t* point,
+                             size_t k, uint8_t* out, size_t cap) {
+    Bin b; b.put(prove_hadamard_ef(vf(a, n), vf(b_, n), vf(c, n), vef(point, k), T(t)));
+    return emit(b.b, out, cap);
+}
+size_t zko_prove_add_ef(void* t, const uint32_t* a, const uint32_t* b_, const uint32_t* c, size_t n, const uint32_t* point,
+                        size_t k, uint8_t* out, size_t cap) {
+    Bin b; b.put(prove_add_ef(vf(a, n), vf(b_, n), vf(c, n), vef(point, k), T(t)));
+    return emit(b.b, out, cap);
+}
+int zko_elementwise_roundtrip(const uint32_t* a, const uint32_t* b_, const uint32_t* c, size_t n, int is_add, int tamper) {
+    Transcript pt("rt"), vt("rt");
+    size_t k = log2_ceil(n);
+    VEF point = pt.squeeze_ef_many(k);
+    vt.squeeze_ef_many(k);
+    if (is_add) {
+        auto p = prove_add_ef(vf(a, n), vf(b_, n), vf(c, n), point, pt);
+        if (tamper) p.c_eval[1] ^= 1;
+        return verify_add_ef(p, point, vt);
+    }
+    auto p = prove_hadamard_ef(vf(a, n), vf(b_, n), vf(c, n), point, pt);
+    if (tamper) p.c_eval[1] ^= 1;
+    return verify_hadamard_ef(p, point, vt);
+}
+// out/x_used: d u32 each; returns delta; -1000 on failure
+int32_t zko_rmsnorm_forward(const uint32_t* x, const uint32_t* gamma, size_t d, uint32_t* out, uint32_t* x_used) {
+    VF o, xu; int32_t delta = 0;
+    try { rmsnorm_forward(vf(x, d), vf(gamma, d), o, xu, delta); } catch (const ForwardFailure&) { return -1000; }
+    out_f(o, out); out_f(xu, x_used);
+    return delta;
+}
+void zko_requantize(const uint32_t* v, size_t n, uint32_t* out) { out_f(requantize_to_i16_field(vf(v, n)), out); }
+size_t zko_prove_rmsnorm_ef(void* t, const uint32_t* x, const uint32_t* gamma, const uint32_t* y, size_t d, int32_t delta,
+                            uint8_t* out, size_t cap) {
+    Bin b; b.put(prove_rmsnorm_ef(vf(x, d), vf(gamma, d), vf(y, d), delta, T(t)));
+    return emit(b.b, out, cap);
+}
+int zko_rmsnorm_roundtrip(const uint32_t* x, const uint32_t* gamma, const uint32_t* y, size_t d, int32_t delta, int tamper) {
+    Transcript pt("rt"), vt("rt");
+    auto p = prove_rmsnorm_ef(vf(x, d), vf(gamma, d), vf(y, d), delta, pt);
+    if (tamper) p.s_g[0] ^= 1;
+    return verify_rmsnorm_ef(p, vf(y, d), d, vt);
+}
+// returns proof length; 0 with *status = 3 (LogUp identity) or 4 (alpha collision) on the reference's panics
+size_t zko_prove_lookup_ef(void* t, const uint32_t* table_out, size_t n_table, const uint32_t* in, const uint32_t* outv, size_t n,
+                           uint8_t* out, size_t cap, int* status) {
+    *status = 0;
+    try {
+        Bin b; b.put(prove_lookup_ef(table_from_outputs(std::vector<uint32_t>(table_out, table_out + n_table)), vf(in, n), vf(outv, n), T(t)));
+        return emit(b.b, out, cap);
+    } catch (const LookupFailure& e) {
+        *status = std::string(e.what()).find("alpha") == 0 ? 4 : 3;
+        return 0;
+    }
+}
+int zko_lookup_roundtrip(const uint32_t* table_out, size_t n_table, const uint32_t* in, const uint32_t* outv, size_t n, int tamper) {
+    Transcript pt("rt"), vt("rt");
+    LookupTable tb = table_from_outputs(std::vector<uint32_t>(table_out, table_out + n_table));
+    auto p = prove_lookup_ef(tb, vf(in, n), vf(outv, n), pt);
+    if (tamper) p.h_at_s[2] ^= 1;
+    return verify_lookup_ef_with_data(p, n, vf(in, n), vf(outv, n), vt);
+}
+
+// ---- Qwen layer.  dims = {d_model, d_ff, num_q_heads, num_kv_heads, d_head, v_num_heads, v_d_head};
+// weights = {norm1_gamma, w_q, w_k, w_v, w_o, w_g_proj, norm2_gamma, w_gate, w_up, w_down}.
+static ModelConfig cfg_of(const uint64_t* d) {
+    ModelConfig c;
+    c.d_model = d[0]; c.d_ff = d[1]; c.num_q_heads = d[2]; c.num_kv_heads = d[3]; c.d_head = d[4]; c.v_num_heads = d[5]; c.v_d_head = d[6];
+    return c;
+}
+static QwenLayerWeights weights_of(const ModelConfig& c, const uint32_t* const* w) {
+    QwenLayerWeights W;
+    size_t dm = c.d_model, aod = c.attn_out_dim();
+    W.norm1_gamma = vf(w[0], dm); W.w_q = vf(w[1], c.q_dim() * dm); W.w_k = vf(w[2], c.k_dim() * dm);
+    W.w_v = vf(w[3], c.v_dim() * dm); W.w_o = vf(w[4], dm * aod); W.w_g_proj = vf(w[5], aod * dm);
+    W.norm2_gamma = vf(w[6], dm); W.w_gate = vf(w[7], c.d_ff * dm); W.w_up = vf(w[8], c.d_ff * dm); W.w_down = vf(w[9], dm * c.d_ff);
+    return W;
+}
+// Forward + prove one layer on a fresh transcript seeded as the reference's layer fan-out does
+// (label "qwen-layer-{idx}", then the 32-byte hash of the model input).  Writes the layer output
+// to y (d_model u32) and the bincode proof to out; returns its length.  verify != 0 also runs
+// the restated verifier and stores its verdict in *accepted.
+size_t zko_qwen_layer_prove(const uint64_t* dims, const uint32_t* const* weights, const uint32_t* x, const uint32_t* silu_out,
+                            const uint32_t* sigmoid_out, size_t n_table, uint32_t layer_idx, const uint8_t* input_hash,
+                            uint32_t* y, uint8_t* out, size_t cap, int verify, int* accepted) {
+    ModelConfig c = cfg_of(dims);
+    QwenLayerWeights W = weights_of(c, weights);
+    LookupTable silu = table_from_outputs(std::vector<uint32_t>(silu_out, silu_out + n_table));
+    LookupTable sigm = table_from_outputs(std::vector<uint32_t>(sigmoid_out, sigmoid_out + n_table));
+    VF X = vf(x, c.d_model);
+    QwenForwardTrace t = qwen_forward(X, W, c, silu, sigm);
+    out_f(t.output, y);
+    std::string seed = "qwen-layer-" + std::to_string(layer_idx);
+    Transcript tr(seed);
+    tr.absorb_bytes(input_hash, 32);
+    QwenLayerProofEF p = prove_qwen_layer_precommitted_ef(t, W, c, commit_qwen_layer(W), silu, sigm, tr);
+    if (verify) {
+        Transcript vt(seed);
+        vt.absorb_bytes(input_hash, 32);
+        *accepted = verify_qwen_layer_ef(p, X, t.output, W, c, silu, sigm, vt) ? 1 : 0;
+    }
+    return emit(serialize(p), out, cap);
+}
+
+}  // extern "C"

@@ -1,0 +1,184 @@
+// CPU ORACLE — TEST INFRASTRUCTURE ONLY.
+//
+// Matmul sub-protocol (y = W x), restating rust/zk_ml_prover/src/proving/matmul.rs for the
+// default build (no `pcs` feature: weights are bound by blake3 + an MLE-eval sumcheck), plus
+// the forward matvec of rust/zk_ml_prover/src/transformer/mod.rs:140-163.
+#pragma once
+#include "commit.hpp"
+
+namespace zko {
+
+// transformer/mod.rs:140-163 — y[i] = sum_j W[i,j] x[j] (+ bias), exact mod p.
+inline VF matmul_forward(const VF& w, const VF& x, size_t m, size_t n, const VF* bias = nullptr) {
+    VF y(m);
+    for (size_t i = 0; i < m; i++) {
+        unsigned __int128 acc = 0;
+        for (size_t j = 0; j < n; j++) acc += uint64_t(w[i * n + j].v) * x[j].v;
+        F v = F(uint32_t(uint64_t(acc % P31)));
+        if (bias) v += (*bias)[i];
+        y[i] = v;
+    }
+    return y;
+}
+
+// matmul.rs:76-128 — w_partial[j] = sum_i eq_r[i] W[i,j], zero-padded to n_pad.
+inline VF fold_eq_matvec(const VF& w, size_t m, size_t n, size_t n_pad, const VF& r_point) {
+    size_t m_pad = size_t(1) << r_point.size();
+    VF eq = eq_evals(r_point);
+    VF out(n_pad, F::zero());
+    size_t rows = m < m_pad ? m : m_pad;
+    for (size_t i = 0; i < rows; i++)
+        for (size_t j = 0; j < n; j++) out[j] += eq[i] * w[i * n + j];
+    return out;
+}
+// matmul.rs:743-835 — EF weights eq_r[i], base-field W; four independent base accumulators.
+inline VEF fold_eq_matvec_ef(const VF& w, size_t m, size_t n, size_t n_pad, const VEF& r_point) {
+    size_t m_pad = size_t(1) << r_point.size();
+    VEF eq = eq_evals_ef(r_point);
+    VEF out(n_pad, EF::zero());
+    size_t rows = m < m_pad ? m : m_pad;
+    for (size_t i = 0; i < rows; i++)
+        for (size_t j = 0; j < n; j++) out[j] += eq[i] * w[i * n + j];
+    return out;
+}
+
+// matmul.rs:24-31
+struct MatmulProof {
+    SumcheckProof sumcheck_proof;
+    uint32_t w_at_rs = 0, x_at_s = 0;
+    std::vector<uint32_t> r_point, s_point;
+};
+// matmul.rs:458-474
+struct SuccinctMatmulProof {
+    MatmulProof matmul_proof;
+    MleEvalProof w_eval_proof;
+    uint32_t w_claimed_value = 0;
+    WeightCommitment w_partial_commitment;
+    bool bound = false;
+    // basefold_proof: Option = None in the default build
+};
+
+// matmul.rs:134-180
+inline MatmulProof prove_matmul(const VF& w, const VF& x, const VF& y, size_t m, size_t n, Transcript& tr, VF* w_partial_out) {
+    size_t log_m = log2_ceil(m), log_n = log2_ceil(n), m_pad = size_t(1) << log_m, n_pad = size_t(1) << log_n;
+    VF y_pad = padded(y, m_pad), x_pad = padded(x, n_pad);
+    tr.absorb_many(y_pad);
+    VF r = tr.squeeze_many(log_m);
+    VF w_partial = fold_eq_matvec(w, m, n, n_pad, r);
+    Prod sc = prove_product(w_partial, x_pad, log_n, tr);
+    MatmulProof p;
+    p.sumcheck_proof = sc.proof;
+    p.w_at_rs = sc.f_at_s.v; p.x_at_s = sc.g_at_s.v;
+    for (F v : r) p.r_point.push_back(v.v);
+    p.s_point = sc.proof.challenges;
+    if (w_partial_out) *w_partial_out = w_partial;
+    return p;
+}
+// matmul.rs:482-511 with bind_weights' default branch (:346-355)
+inline SuccinctMatmulProof prove_matmul_succinct(const VF& w, const VF& x, const VF& y, size_t m, size_t n, Transcript& tr) {
+    VF w_partial;
+    SuccinctMatmulProof p;
+    p.matmul_proof = prove_matmul(w, x, y, m, n, tr, &w_partial);
+    VF s;
+    for (uint32_t v : p.matmul_proof.s_point) s.push_back(F(v));
+    p.w_partial_commitment = commit_weights_fast(w_partial);
+    tr.absorb_bytes(p.w_partial_commitment.root);
+    p.w_eval_proof = prove_mle_eval_no_merkle(w_partial, s, tr);
+    return p;
+}
+struct MatmulVerify { bool valid = false; VF x_claim_point; F x_claim_value; };
+// matmul.rs:604-707 (default branch)
+inline MatmulVerify verify_matmul_succinct(const SuccinctMatmulProof& p, const VF& y, size_t m, size_t n, Transcript& tr) {
+    MatmulVerify out;
+    size_t log_m = log2_ceil(m), m_pad = size_t(1) << log_m;
+    (void)n;
+    VF y_pad = padded(y, m_pad);
+    tr.absorb_many(y_pad);
+    VF r = tr.squeeze_many(log_m);
+    std::vector<uint32_t> r_raw;
+    for (F v : r) r_raw.push_back(v.v);
+    if (r_raw != p.matmul_proof.r_point) return out;
+    F claim = mle_evaluate(y_pad, r);
+    F w_at_rs(p.matmul_proof.w_at_rs), x_at_s(p.matmul_proof.x_at_s);
+    if (!verify_product_with_challenges(claim, p.matmul_proof.sumcheck_proof, w_at_rs, x_at_s, tr)) return out;
+    VF s;
+    for (uint32_t v : p.matmul_proof.s_point) s.push_back(F(v));
+    tr.absorb_bytes(p.w_partial_commitment.root);
+    if (!verify_mle_eval(w_at_rs, s, p.w_eval_proof, tr)) return out;
+    out.valid = true; out.x_claim_point = s; out.x_claim_value = x_at_s;
+    return out;
+}
+
+// matmul.rs:717-726
+struct MatmulProofEF {
+    SumcheckProofEF sumcheck_proof;
+    EFElement w_at_rs{}, x_at_s{};
+    std::vector<EFElement> r_point, s_point;
+};
+// matmul.rs:947-960
+struct SuccinctMatmulProofEF {
+    MatmulProofEF matmul_proof;
+    MleEvalProofEF w_eval_proof;
+    EFElement w_claimed_value{};
+    WeightCommitment w_partial_commitment;
+    bool bound = false;
+};
+
+// matmul.rs:838-885
+inline MatmulProofEF prove_matmul_ef(const VF& w, const VF& x, const VF& y, size_t m, size_t n, Transcript& tr, VEF* w_partial_out) {
+    size_t log_m = log2_ceil(m), log_n = log2_ceil(n), m_pad = size_t(1) << log_m, n_pad = size_t(1) << log_n;
+    VF y_pad = padded(y, m_pad), x_pad = padded(x, n_pad);
+    tr.absorb_many(y_pad);
+    VEF r = tr.squeeze_ef_many(log_m);
+    VEF w_partial = fold_eq_matvec_ef(w, m, n, n_pad, r);
+    ProdEF sc = prove_product_ef_mixed(w_partial, x_pad, log_n, tr);
+    MatmulProofEF p;
+    p.sumcheck_proof = sc.proof;
+    p.w_at_rs = sc.f_at_s.arr(); p.x_at_s = sc.g_at_s.arr();
+    for (EF v : r) p.r_point.push_back(v.arr());
+    p.s_point = sc.proof.challenges;
+    if (w_partial_out) *w_partial_out = w_partial;
+    return p;
+}
+// matmul.rs:963-997 with bind_weights_ef's default branch (:435-452)
+inline SuccinctMatmulProofEF prove_matmul_succinct_ef(const VF& w, const VF& x, const VF& y, size_t m, size_t n, Transcript& tr) {
+    VEF w_partial;
+    SuccinctMatmulProofEF p;
+    p.matmul_proof = prove_matmul_ef(w, x, y, m, n, tr, &w_partial);
+    VF base;
+    for (EF v : w_partial) { auto a = v.arr(); for (int k = 0; k < 4; k++) base.push_back(F(a[k])); }
+    VEF s;
+    for (auto& e : p.matmul_proof.s_point) s.push_back(ef_of(e));
+    p.w_partial_commitment = commit_weights_fast(base);
+    tr.absorb_bytes(p.w_partial_commitment.root);
+    p.w_eval_proof = prove_mle_eval_ef_with_claim_no_merkle(w_partial, s, tr);
+    return p;
+}
+struct MatmulVerifyEF { bool valid = false; VEF x_claim_point; EF x_claim_value; };
+// matmul.rs:1000-1117 (default branch)
+inline MatmulVerifyEF verify_matmul_succinct_ef(const SuccinctMatmulProofEF& p, const VF& y, size_t m, size_t n, Transcript& tr) {
+    MatmulVerifyEF out;
+    size_t log_m = log2_ceil(m), m_pad = size_t(1) << log_m;
+    (void)n;
+    VF y_pad = padded(y, m_pad);
+    tr.absorb_many(y_pad);
+    VEF r = tr.squeeze_ef_many(log_m);
+    if (!p.matmul_proof.r_point.empty()) {
+        std::vector<EFElement> rr;
+        for (EF v : r) rr.push_back(v.arr());
+        if (rr != p.matmul_proof.r_point) return out;
+    }
+    EF claim = mle_evaluate_ef(y_pad, r);
+    EF w_at_rs = ef_of(p.matmul_proof.w_at_rs), x_at_s = ef_of(p.matmul_proof.x_at_s);
+    VEF derived;
+    if (!verify_product_ef_with_challenges(claim, p.matmul_proof.sumcheck_proof, w_at_rs, x_at_s, tr, &derived)) return out;
+    VEF s;
+    if (p.matmul_proof.s_point.empty()) s = derived;
+    else for (auto& e : p.matmul_proof.s_point) s.push_back(ef_of(e));
+    tr.absorb_bytes(p.w_partial_commitment.root);
+    if (!verify_mle_eval_ef(w_at_rs, s, p.w_eval_proof, tr)) return out;
+    out.valid = true; out.x_claim_point = s; out.x_claim_value = x_at_s;
+    return out;
+}
+
+}  // namespace zko

@@ -217,3 +217,146 @@ def verify(kind: str, tr: Transcript, claimed, polys, chal, fin) -> bool:
     cl, pcl = _u32(claimed)
     fn = lib().zko_verify_triple_ef if triple else lib().zko_verify_product_ef
     return bool(fn(tr.h, pcl, pp, C.c_size_t(nv), C.c_size_t(epr), pc, C.c_size_t(nchal), pf))
+
+
+# ------------------------------------------------------------------------------------------
+# protocol-level entry points (proofs come back as bincode bytes)
+# ------------------------------------------------------------------------------------------
+def _bytes_call(fn, *args, cap=1 << 22):
+    buf = (C.c_uint8 * cap)()
+    fn.restype = C.c_size_t
+    n = fn(*args, buf, C.c_size_t(cap))
+    if n > cap:
+        return _bytes_call(fn, *args, cap=n)
+    return bytes(buf[:n])
+
+
+def commit_weights_fast(w) -> bytes:
+    a, p = _u32(w)
+    out = (C.c_uint8 * 32)()
+    lib().zko_commit_weights_fast(p, C.c_size_t(a.size), out)
+    return bytes(out)
+
+
+def matmul_forward(w, x, m, n):
+    W, pw = _u32(w)
+    X, px = _u32(x)
+    y = np.zeros(m, np.uint32)
+    lib().zko_matmul_forward(pw, px, C.c_size_t(m), C.c_size_t(n), y.ctypes.data_as(u32p))
+    return y
+
+
+def _log2_ceil(n):
+    return 1 if n <= 1 else (n - 1).bit_length()
+
+
+def fold_eq_matvec(w, m, n, r):
+    W, pw = _u32(w)
+    R, pr = _u32(r)
+    out = np.zeros(1 << _log2_ceil(n), np.uint32)
+    lib().zko_fold_eq_matvec(pw, C.c_size_t(m), C.c_size_t(n), pr, C.c_size_t(R.size), out.ctypes.data_as(u32p))
+    return out
+
+
+def fold_eq_matvec_ef(w, m, n, r):
+    W, pw = _u32(w)
+    R, pr = _u32(r)
+    out = np.zeros((1 << _log2_ceil(n), 4), np.uint32)
+    lib().zko_fold_eq_matvec_ef(pw, C.c_size_t(m), C.c_size_t(n), pr, C.c_size_t(R.size // 4), out.ctypes.data_as(u32p))
+    return out
+
+
+def prove_matmul_succinct(tr, w, x, y, m, n, ef=False) -> bytes:
+    W, pw = _u32(w); X, px = _u32(x); Y, py = _u32(y)
+    fn = lib().zko_prove_matmul_succinct_ef if ef else lib().zko_prove_matmul_succinct
+    return _bytes_call(fn, tr.h, pw, px, py, C.c_size_t(m), C.c_size_t(n))
+
+
+def matmul_succinct_roundtrip(w, x, y, m, n, ef, tamper=False) -> bool:
+    W, pw = _u32(w); X, px = _u32(x); Y, py = _u32(y)
+    return bool(lib().zko_matmul_succinct_roundtrip(pw, px, py, C.c_size_t(m), C.c_size_t(n), C.c_int(int(ef)), C.c_int(int(tamper))))
+
+
+def prove_mle_eval_bound(tr, w, point, label: bytes, ef=True):
+    W, pw = _u32(w); Pt, pp = _u32(point)
+    k = Pt.size // 4 if ef else Pt.size
+    claimed = np.zeros(4, np.uint32)
+    fn = lib().zko_prove_mle_eval_ef_base_bound if ef else lib().zko_prove_mle_eval_bound
+    fn.restype = C.c_size_t
+    cap = 1 << 20
+    buf = (C.c_uint8 * cap)()
+    n = fn(tr.h, pw, C.c_size_t(W.size), pp, C.c_size_t(k), _u8(label), C.c_size_t(len(label)), buf, C.c_size_t(cap),
+           claimed.ctypes.data_as(u32p))
+    return bytes(buf[:n]), (claimed if ef else int(claimed[0]))
+
+
+def prove_elementwise_ef(tr, a, b, c, point, add: bool) -> bytes:
+    A, pa = _u32(a); B, pb = _u32(b); Cc, pc = _u32(c); Pt, pp = _u32(point)
+    fn = lib().zko_prove_add_ef if add else lib().zko_prove_hadamard_ef
+    return _bytes_call(fn, tr.h, pa, pb, pc, C.c_size_t(A.size), pp, C.c_size_t(Pt.size // 4))
+
+
+def elementwise_roundtrip(a, b, c, add: bool, tamper=False) -> bool:
+    A, pa = _u32(a); B, pb = _u32(b); Cc, pc = _u32(c)
+    return bool(lib().zko_elementwise_roundtrip(pa, pb, pc, C.c_size_t(A.size), C.c_int(int(add)), C.c_int(int(tamper))))
+
+
+def rmsnorm_forward(x, gamma):
+    X, px = _u32(x); G, pg = _u32(gamma)
+    out = np.zeros(X.size, np.uint32); xu = np.zeros(X.size, np.uint32)
+    lib().zko_rmsnorm_forward.restype = C.c_int32
+    d = lib().zko_rmsnorm_forward(px, pg, C.c_size_t(X.size), out.ctypes.data_as(u32p), xu.ctypes.data_as(u32p))
+    return out, xu, d
+
+
+def requantize(v):
+    V, pv = _u32(v)
+    out = np.zeros(V.size, np.uint32)
+    lib().zko_requantize(pv, C.c_size_t(V.size), out.ctypes.data_as(u32p))
+    return out
+
+
+def prove_rmsnorm_ef(tr, x, gamma, y, delta) -> bytes:
+    X, px = _u32(x); G, pg = _u32(gamma); Y, py = _u32(y)
+    return _bytes_call(lib().zko_prove_rmsnorm_ef, tr.h, px, pg, py, C.c_size_t(X.size), C.c_int32(delta))
+
+
+def rmsnorm_roundtrip(x, gamma, y, delta, tamper=False) -> bool:
+    X, px = _u32(x); G, pg = _u32(gamma); Y, py = _u32(y)
+    return bool(lib().zko_rmsnorm_roundtrip(px, pg, py, C.c_size_t(X.size), C.c_int32(delta), C.c_int(int(tamper))))
+
+
+def prove_lookup_ef(tr, table_out, inputs, outputs):
+    """Returns (proof bytes, status): status 3 = LogUp identity failed, 4 = alpha collision."""
+    T, pt = _u32(table_out); I, pi = _u32(inputs); O, po = _u32(outputs)
+    st = C.c_int()
+    cap = 1 << 22
+    buf = (C.c_uint8 * cap)()
+    lib().zko_prove_lookup_ef.restype = C.c_size_t
+    n = lib().zko_prove_lookup_ef(tr.h, pt, C.c_size_t(T.size), pi, po, C.c_size_t(I.size), buf, C.c_size_t(cap), C.byref(st))
+    return bytes(buf[:n]), st.value
+
+
+def lookup_roundtrip(table_out, inputs, outputs, tamper=False) -> bool:
+    T, pt = _u32(table_out); I, pi = _u32(inputs); O, po = _u32(outputs)
+    return bool(lib().zko_lookup_roundtrip(pt, C.c_size_t(T.size), pi, po, C.c_size_t(I.size), C.c_int(int(tamper))))
+
+
+WEIGHT_NAMES = ["norm1_gamma", "w_q", "w_k", "w_v", "w_o", "w_g_proj", "norm2_gamma", "w_gate", "w_up", "w_down"]
+DIM_NAMES = ["d_model", "d_ff", "num_q_heads", "num_kv_heads", "d_head", "v_num_heads", "v_d_head"]
+
+
+def qwen_layer_prove(config: dict, weights: dict, x, silu_out, sigmoid_out, layer_idx: int, input_hash: bytes, verify=False):
+    """Forward + prove one layer; returns (y, proof bytes, accepted or None)."""
+    dims = (C.c_uint64 * 7)(*[int(config.get(k, 0)) for k in DIM_NAMES])
+    keep = [np.ascontiguousarray(weights[k], dtype=np.uint32) for k in WEIGHT_NAMES]
+    wp = (u32p * 10)(*[a.ctypes.data_as(u32p) for a in keep])
+    X, px = _u32(x); S, ps = _u32(silu_out); G, pg = _u32(sigmoid_out)
+    y = np.zeros(int(config["d_model"]), np.uint32)
+    acc = C.c_int(-1)
+    cap = 1 << 24
+    buf = (C.c_uint8 * cap)()
+    lib().zko_qwen_layer_prove.restype = C.c_size_t
+    n = lib().zko_qwen_layer_prove(dims, wp, px, ps, pg, C.c_size_t(S.size), C.c_uint32(layer_idx), _u8(input_hash),
+                                   y.ctypes.data_as(u32p), buf, C.c_size_t(cap), C.c_int(int(verify)), C.byref(acc))
+    return y, bytes(buf[:n]), (bool(acc.value) if verify else None)
