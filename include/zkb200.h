@@ -105,6 +105,58 @@ int32_t zkb_sumcheck_prove(zkb_ctx* ctx, zkb_transcript* tr, int32_t kind, const
                            uint32_t num_vars, int32_t on_device, uint32_t* round_polys, uint32_t* challenges,
                            uint32_t* finals);
 
+/* ---- field helpers, commitments, matrix kernels ---- */
+/* commit_weights_fast: blake3("weights" || LE u32 buffer)            weight_commitment.rs:82-107 */
+int32_t zkb_commit_weights_fast(zkb_ctx* ctx, const uint32_t* w, size_t n, int32_t on_device, uint8_t root[32]);
+/* eq_evals / eq_evals_ef: r has k (ef: 4k) words, out 2^k (ef: 4 * 2^k) words   m31_ops.rs:30-50, 175-191
+ * (replaces eq_evals_gpu / MetalKernels::eq_butterfly, m31_ops.rs:54-78, gpu/metal_kernels.rs:232-253) */
+int32_t zkb_eq_evals(zkb_ctx* ctx, const uint32_t* r, uint32_t k, int32_t ef, uint32_t* out);
+/* fold_eq_matvec / fold_eq_matvec_ef: out[j] = sum_i eq(r)[i] W[i][j], zero-padded to n_pad    matmul.rs:76-128, 743-835 */
+int32_t zkb_fold_eq_matvec(zkb_ctx* ctx, const uint32_t* W, size_t m, size_t n, const uint32_t* r, uint32_t log_m, int32_t ef,
+                           int32_t w_on_device, uint32_t* out);
+/* matmul_forward: y = W x mod p                                        transformer/mod.rs:140-163 */
+int32_t zkb_matvec_forward(zkb_ctx* ctx, const uint32_t* W, const uint32_t* x, size_t m, size_t n, int32_t w_on_device, uint32_t* y);
+/* rmsnorm_forward with the QR perturbation search                      transformer/mod.rs:245-288 */
+int32_t zkb_rmsnorm_forward(zkb_ctx* ctx, const uint32_t* x, const uint32_t* gamma, size_t d, uint32_t* out, uint32_t* x_used,
+                            int32_t* delta);
+
+/* ---- sub-protocol provers: host inputs, proof returned as the reference's bincode bytes.
+ * *len receives the proof length; ZKB_E_TOO_LARGE if it exceeds cap. ---- */
+/* prove_matmul_succinct_ef -> SuccinctMatmulProofEF                    matmul.rs:963-997 */
+int32_t zkb_prove_matmul_succinct_ef(zkb_ctx* ctx, zkb_transcript* tr, const uint32_t* W, const uint32_t* x, const uint32_t* y,
+                                     size_t m, size_t n, int32_t w_on_device, uint8_t* out, size_t cap, size_t* len);
+/* prove_hadamard_ef (is_add = 0) / prove_add_ef (is_add = 1); point = k EF challenges    elementwise.rs:429-480, 545-595 */
+int32_t zkb_prove_elementwise_ef(zkb_ctx* ctx, zkb_transcript* tr, int32_t is_add, const uint32_t* a, const uint32_t* b,
+                                 const uint32_t* c, size_t n, const uint32_t* point, uint32_t k, uint8_t* out, size_t cap, size_t* len);
+/* prove_rmsnorm_ef -> RmsNormProofEF                                   rmsnorm.rs:512-667 */
+int32_t zkb_prove_rmsnorm_ef(zkb_ctx* ctx, zkb_transcript* tr, const uint32_t* x, const uint32_t* gamma, const uint32_t* y, size_t d,
+                             int32_t delta, uint8_t* out, size_t cap, size_t* len);
+/* prove_lookup_ef -> LookupProofEF; table_out = output column of a 65536- or 256-entry table   lookup.rs:643-762 */
+int32_t zkb_prove_lookup_ef(zkb_ctx* ctx, zkb_transcript* tr, const uint32_t* table_out, size_t n_table, const uint32_t* inputs,
+                            const uint32_t* outputs, size_t n, uint8_t* out, size_t cap, size_t* len);
+
+/* ---- resident Qwen-style layer (QwenLayerWeights + commit_qwen_layer + trace)   transformer/qwen.rs:62-73, 148-161 ----
+ * dims = {d_model, d_ff, num_q_heads, num_kv_heads, d_head, v_num_heads, v_d_head};
+ * weights = {norm1_gamma, w_q, w_k, w_v, w_o, w_g_proj, norm2_gamma, w_gate, w_up, w_down} (host, row-major);
+ * the tables are the output columns of build_silu_table / build_sigmoid_table already on the device. */
+typedef struct zkb_qwen_layer zkb_qwen_layer;
+int32_t zkb_qwen_layer_create(zkb_ctx* ctx, const uint64_t dims[7], const uint32_t* const weights[10],
+                              const uint32_t* silu_table_dev, const uint32_t* sigmoid_table_dev, uint32_t n_table,
+                              zkb_qwen_layer** out);
+void zkb_qwen_layer_destroy(zkb_qwen_layer* layer);
+/* the eight 32-byte weight commitments in the order q, k, v, o, g_proj, gate, up, down */
+int32_t zkb_qwen_layer_commitments(zkb_qwen_layer* layer, uint8_t roots[256]);
+/* qwen_forward_indexed                                                  transformer/qwen.rs:211-325 */
+int32_t zkb_qwen_layer_forward(zkb_qwen_layer* layer, const uint32_t* x, int32_t x_on_device, uint32_t* y, int32_t y_on_device);
+const uint32_t* zkb_qwen_layer_output_dev(const zkb_qwen_layer* layer);
+/* prove_qwen_layer_precommitted_ef on a fresh transcript "qwen-layer-{idx}" || input_hash
+ * (transformer/qwen.rs:795-912, pipeline/prove.rs:166-168) -> QwenLayerProofEF bincode.
+ * prove_begin only enqueues GPU work; prove_end waits and serialises. */
+int32_t zkb_qwen_layer_prove_begin(zkb_qwen_layer* layer, uint32_t layer_idx, const uint8_t input_hash[32]);
+int32_t zkb_qwen_layer_prove_end(zkb_qwen_layer* layer, uint8_t* out, size_t cap, size_t* len);
+int32_t zkb_qwen_layer_prove(zkb_qwen_layer* layer, uint32_t layer_idx, const uint8_t input_hash[32], uint8_t* out, size_t cap,
+                             size_t* len);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,205 @@
+"""GPU parity of the protocol layer against the CPU oracle: every proof is compared as
+bincode bytes (bit-exact; all arithmetic is integer field arithmetic)."""
+import hashlib
+
+import numpy as np
+import pytest
+
+import zklm_compile_b200 as zk
+from zklm_compile_b200 import protocols as zp
+from zklm_compile_b200 import qwen as zq
+from oracle import pyoracle as O
+from tests.util import P, load_qwen_golden, rand_layer, small_table
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    c = zk.Context(0)
+    yield c
+    c.close()
+
+
+def rnd(rng, n):
+    return rng.integers(0, P, n, dtype=np.int64).astype(np.uint32)
+
+
+@pytest.mark.parametrize("n", [0, 1, 3, 250, 254, 255, 256, 257, 511, 512, 513, 1000, 4096, 70001, 1 << 20])
+def test_blake3_commit_matches_oracle(ctx, n):
+    w = rnd(np.random.default_rng(n), n)
+    assert zp.commit_weights_fast(ctx, w) == O.commit_weights_fast(w)
+
+
+@pytest.mark.parametrize("k", [1, 2, 5, 12])
+def test_eq_evals(ctx, k):
+    rng = np.random.default_rng(k)
+    r = rnd(rng, k)
+    assert zp.eq_evals(ctx, r).tolist() == O.eq_evals(r).tolist()
+    r4 = rnd(rng, 4 * k).reshape(k, 4)
+    assert zp.eq_evals_ef(ctx, r4).tolist() == O.eq_evals_ef(r4).tolist()
+
+
+def test_eq_evals_literal(ctx):
+    # rust/zk_ml_prover/src/field/m31_ops.rs:212-228
+    assert zp.eq_evals(ctx, [2, 3]).tolist() == [2, P - 3, P - 4, 6]
+
+
+@pytest.mark.parametrize("m,n", [(2, 2), (3, 5), (17, 9), (64, 64), (100, 260), (513, 1028), (700, 33)])
+@pytest.mark.parametrize("ef", [False, True])
+def test_fold_eq_matvec_and_forward(ctx, m, n, ef):
+    rng = np.random.default_rng(m * 1000 + n)
+    w = rnd(rng, m * n)
+    log_m = zp.log2_ceil(m)
+    r = rnd(rng, log_m * (4 if ef else 1))
+    got = zp.fold_eq_matvec(ctx, w, m, n, r, ef=ef)
+    exp = O.fold_eq_matvec_ef(w, m, n, r) if ef else O.fold_eq_matvec(w, m, n, r)
+    assert got.tolist() == exp.tolist()
+    x = rnd(rng, n)
+    assert zp.matmul_forward(ctx, w, x, m, n).tolist() == O.matmul_forward(w, x, m, n).tolist()
+
+
+def test_matmul_forward_extreme_values(ctx):
+    m, n = 8, 4096
+    w = np.full(m * n, P - 1, np.uint32)
+    x = np.full(n, P - 1, np.uint32)
+    assert zp.matmul_forward(ctx, w, x, m, n).tolist() == O.matmul_forward(w, x, m, n).tolist()
+    r = np.full(3, P - 1, np.uint32)
+    assert zp.fold_eq_matvec(ctx, w, m, n, r).tolist() == O.fold_eq_matvec(w, m, n, r).tolist()
+
+
+@pytest.mark.parametrize("m,n", [(2, 2), (3, 5), (17, 9), (64, 40), (300, 2100)])
+def test_matmul_succinct_ef_bytes(ctx, m, n):
+    rng = np.random.default_rng(m + n)
+    w, x = rnd(rng, m * n), rnd(rng, n)
+    y = O.matmul_forward(w, x, m, n)
+    t, o = zk.Transcript(ctx, b"mm"), O.Transcript(b"mm")
+    got = zp.prove_matmul_succinct_ef(w, x, y, m, n, t)
+    exp = O.prove_matmul_succinct(o, w, x, y, m, n, ef=True)
+    assert got == exp
+    assert t.squeeze() == o.squeeze()
+
+
+@pytest.mark.parametrize("n", [2, 7, 16, 100, 5000])
+@pytest.mark.parametrize("add", [False, True])
+def test_elementwise_ef_bytes(ctx, n, add):
+    rng = np.random.default_rng(n)
+    a, b = rnd(rng, n), rnd(rng, n)
+    c = ((a.astype(np.int64) + b) % P if add else (a.astype(object) * b.astype(object)) % P).astype(np.uint32)
+    k = zp.log2_ceil(n)
+    point = rnd(rng, 4 * k).reshape(k, 4)
+    t, o = zk.Transcript(ctx, b"ew"), O.Transcript(b"ew")
+    got = (zp.prove_add_ef if add else zp.prove_hadamard_ef)(a, b, c, point, t)
+    exp = O.prove_elementwise_ef(o, a, b, c, point, add)
+    assert got == exp
+    assert t.squeeze() == o.squeeze()
+
+
+@pytest.mark.parametrize("d", [4, 12, 16, 100, 2560])
+def test_rmsnorm_forward_and_proof_bytes(ctx, d):
+    rng = np.random.default_rng(d)
+    x = np.mod(rng.integers(-127, 128, d), P).astype(np.uint32)
+    gamma = np.mod(rng.integers(-127, 128, d), P).astype(np.uint32)
+    y, xu, delta = zp.rmsnorm_forward(ctx, x, gamma)
+    ey, exu, edelta = O.rmsnorm_forward(x, gamma)
+    assert delta == edelta and y.tolist() == ey.tolist() and xu.tolist() == exu.tolist()
+    t, o = zk.Transcript(ctx, b"rn"), O.Transcript(b"rn")
+    got = zp.prove_rmsnorm_ef(xu, gamma, y, delta, t)
+    exp = O.prove_rmsnorm_ef(o, xu, gamma, y, delta)
+    assert got == exp
+    assert t.squeeze() == o.squeeze()
+
+
+def test_rmsnorm_forward_needs_perturbation(ctx):
+    """Find seeded inputs whose d / sum_sq is not a residue, so the +-delta search runs."""
+    found = 0
+    for seed in range(60):
+        rng = np.random.default_rng(seed)
+        x = np.mod(rng.integers(-127, 128, 8), P).astype(np.uint32)
+        g = np.ones(8, np.uint32)
+        ey, exu, edelta = O.rmsnorm_forward(x, g)
+        y, xu, delta = zp.rmsnorm_forward(ctx, x, g)
+        assert delta == edelta and y.tolist() == ey.tolist() and xu.tolist() == exu.tolist()
+        found += delta != 0
+    assert found > 5
+
+
+@pytest.mark.parametrize("n_table,n", [(256, 10), (256, 300), (65536, 50), (65536, 4096), (65536, 9728)])
+def test_lookup_ef_bytes(ctx, n_table, n):
+    tab_in, tab_out = small_table(n_table, seed=3)
+    rng = np.random.default_rng(n)
+    idx = rng.integers(0, n_table, n)
+    ins, outs = tab_in[idx], tab_out[idx]
+    t, o = zk.Transcript(ctx, b"lk"), O.Transcript(b"lk")
+    got = zp.prove_lookup_ef(tab_out, ins, outs, t)
+    exp, st = O.prove_lookup_ef(o, tab_out, ins, outs)
+    assert st == 0 and got == exp
+    assert t.squeeze() == o.squeeze()
+
+
+def test_lookup_invalid_witness_is_an_error(ctx):
+    """The reference panics with "LogUp identity failed" (lookup.rs:733-738); the library returns
+    the matching status instead of a proof."""
+    tab_in, tab_out = small_table(256)
+    idx = np.arange(20)
+    outs = tab_out[idx].copy()
+    outs[5] = (int(outs[5]) + 1) % P
+    with pytest.raises(zk.ZkbError) as e:
+        zp.prove_lookup_ef(tab_out, tab_in[idx], outs, zk.Transcript(ctx, b"bad"))
+    assert e.value.code == 3
+
+
+def _check_layer(ctx, cfg, weights, x, silu, sigm, idx):
+    ih = hashlib.sha256(b"model-input").digest()
+    td = (ctx.upload(silu), ctx.upload(sigm))
+    layer = zq.QwenLayer(ctx, cfg, weights, *td)
+    y = layer.forward(x)
+    ey, eproof, ok = O.qwen_layer_prove(cfg, weights, x, silu, sigm, idx, ih, verify=True)
+    assert y.tolist() == ey.tolist()
+    roots = layer.commitments()
+    assert roots[0] == O.commit_weights_fast(weights["w_q"]) and roots[7] == O.commit_weights_fast(weights["w_down"])
+    proof = layer.prove(idx, ih)
+    assert ok, "oracle verifier rejected the oracle proof"
+    assert len(proof) == len(eproof)
+    assert proof == eproof, "layer proof bytes differ from the oracle"
+    # proving twice gives the same bytes (buffers are reused, nothing stale leaks)
+    assert layer.prove(idx, ih) == eproof
+    layer.close()
+
+
+def test_qwen_layer_golden_cases(ctx):
+    G = load_qwen_golden()
+    for ci, case in enumerate(G["cases"]):
+        _check_layer(ctx, case["config"], case["weights"], np.array(case["x"], np.uint32), G["silu"], G["sigmoid"], ci)
+
+
+@pytest.mark.parametrize("shape", [
+    dict(d_model=64, d_ff=96, heads=2, kv=2, d_head=16, v_heads=4, v_d_head=16),     # GDN-style, asymmetric V
+    dict(d_model=80, d_ff=200, heads=8, kv=2, d_head=8),                               # GQA full attention
+    dict(d_model=320, d_ff=1216, heads=2, kv=2, d_head=128, v_heads=4, v_d_head=128),  # 1/8-scale 4B GDN layer
+])
+def test_qwen_layer_random(ctx, shape):
+    cfg, weights, x = rand_layer(11, **shape)
+    G = load_qwen_golden()
+    _check_layer(ctx, cfg, weights, x, G["silu"], G["sigmoid"], 7)
+
+
+def test_qwen_model_two_layers_reverse_order(ctx):
+    G = load_qwen_golden()
+    shapes = [dict(d_model=64, d_ff=96, heads=2, kv=2, d_head=16, v_heads=4, v_d_head=16),
+              dict(d_model=64, d_ff=96, heads=4, kv=2, d_head=16)]
+    layers = [rand_layer(20 + i, **s) for i, s in enumerate(shapes)]
+    x = layers[0][2]
+    model = zq.QwenModel(0, [l[0] for l in layers], [l[1] for l in layers], G["silu"], G["sigmoid"])
+    y = model.forward(x)
+    proofs = model.prove()
+    ih = zq.hash_values(x)
+    assert ih == O.hash_values(x)
+    cur, exp = x, []
+    for i, (cfg, w, _) in enumerate(layers):
+        cur, pr, ok = O.qwen_layer_prove(cfg, w, cur, G["silu"], G["sigmoid"], i, ih, verify=True)
+        assert ok
+        exp.append(pr)
+    assert y.tolist() == cur.tolist()
+    assert proofs == exp[::-1]
+    model.close()

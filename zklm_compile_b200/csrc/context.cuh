@@ -38,6 +38,30 @@ struct zkb_ctx {
     struct Chunk { char* base; size_t cap; size_t used; };
     std::vector<Chunk> chunks;
 
+    // record buffer: every value a proof needs, written by kernels, fetched in one copy
+    zkb::u32* rec_dev = nullptr;
+    zkb::u32* rec_host = nullptr;        // pinned mirror
+    size_t rec_cap = 0, rec_used = 0;
+    size_t rec_alloc(size_t nwords) {
+        if (rec_used + nwords > rec_cap) throw zkb::ArgFail{ZKB_E_TOO_LARGE, "proof record buffer exhausted"};
+        size_t off = rec_used;
+        rec_used += nwords;
+        return off;
+    }
+    void rec_reset() { rec_used = 0; }
+    // Copy the used part of the record to the host and wait for it (the one sync of a proof).
+    void rec_fetch() {
+        if (rec_used) ZKB_CUDA(cudaMemcpyAsync(rec_host, rec_dev, rec_used * 4, cudaMemcpyDeviceToHost, stream));
+        ZKB_CUDA(cudaStreamSynchronize(stream));
+    }
+    // Status word written by kernels (0 = ok); reading it synchronises.
+    uint32_t read_status() {
+        uint32_t v = 0;
+        ZKB_CUDA(cudaMemcpyAsync(&v, status, 4, cudaMemcpyDeviceToHost, stream));
+        ZKB_CUDA(cudaStreamSynchronize(stream));
+        return v;
+    }
+
     // stopwatch + per-launch profile
     cudaEvent_t t0 = nullptr, t1 = nullptr;
     bool profile = false;

@@ -1,0 +1,240 @@
+// Protocol layer: enqueues the kernels of each sub-protocol in the reference's transcript
+// order and remembers where its outputs land in the record buffer; after the record has been
+// fetched, `put_*` turns them into the reference's bincode layout.
+//
+//   MLE-eval proofs   rust/zk_ml_prover/src/proving/weight_commitment.rs:349-374, 470-517
+//   matmul            rust/zk_ml_prover/src/proving/matmul.rs:838-997, 360-453 (default features)
+//   hadamard / add    rust/zk_ml_prover/src/proving/elementwise.rs:429-480, 545-595
+//   RMSNorm           rust/zk_ml_prover/src/proving/rmsnorm.rs:512-667
+//   LogUp             rust/zk_ml_prover/src/proving/lookup.rs:643-762
+//   gates             rust/zk_ml_prover/src/proving/sigmoid_gate.rs:90-114, swiglu.rs:99-118
+#pragma once
+#include "engine.cuh"
+
+namespace zkb {
+
+inline u32 log2_ceil_u(size_t n) { u32 k = 1; if (n <= 1) return 1; k = 0; while ((size_t(1) << k) < n) k++; return k; }
+
+// ---- bincode writer (bincode 1.3 defaults: LE fixed ints, u64 lengths, u8 Option tags) -------
+struct Ser {
+    std::vector<uint8_t> b;
+    const u32* rec = nullptr;     // fetched record
+    void u8(uint8_t v) { b.push_back(v); }
+    void u32le(u32 v) { for (int i = 0; i < 4; i++) b.push_back(uint8_t(v >> (8 * i))); }
+    void u64le(u64 v) { for (int i = 0; i < 8; i++) b.push_back(uint8_t(v >> (8 * i))); }
+    void words(size_t off, size_t n) { for (size_t i = 0; i < n; i++) u32le(rec[off + i]); }
+    void ef(size_t off) { words(off, 4); }
+    // 32-byte root stored as 8 LE words
+    void root(size_t off) { words(off, 8); }
+    // WeightCommitment {root, num_weights, log_height, kind = Blake3Fast}
+    void commitment(size_t root_off, u64 num_weights) {
+        root(root_off);
+        u64le(num_weights);
+        u64le(num_weights <= 1 ? 1 : log2_ceil_u(num_weights));
+        u32le(0);
+    }
+    // SumcheckProof / SumcheckProofEF with only the stored evaluations; challenges optional.
+    void sumcheck(const ScRec& r, bool with_challenges, long nv_override = -1) {
+        KindInfo ki = kind_info(r.kind);
+        u32 nv = nv_override >= 0 ? (u32)nv_override : r.nv;
+        u64le(nv);
+        for (u32 round = 0; round < nv; round++) {
+            u64le(ki.nstored);
+            for (u32 k = 0; k < ki.nabs; k++)
+                if (ki.mask & (1u << k)) words(r.polys + ((size_t)round * ki.nabs + k) * ki.w, ki.w);
+        }
+        if (with_challenges) { u64le(nv); words(r.chal, (size_t)nv * ki.w); }
+        else u64le(0);
+    }
+    // s0 + s1 of round 0 (the claimed sum), as EF words
+    void claimed_sum_ef(const ScRec& r) {
+        KindInfo ki = kind_info(r.kind);
+        for (int k = 0; k < 4; k++) u32le(add31(rec[r.polys + k], rec[r.polys + ki.w + k]));
+    }
+};
+
+// ---- MLE-eval proof ---------------------------------------------------------------------------
+struct EvalRec { ScRec sc; };
+// w: base-field device vector (`len` valid entries, MLE over 2^k), point: k EF challenges on device.
+// Absorbs label and root (8 words on device) first when label != nullptr.
+inline EvalRec prove_mle_eval_ef_base(zkb_ctx* c, TrState* tr, const u32* w, u32 len, const Fe* point, u32 k,
+                                      const char* label, const u32* root_dev) {
+    if (label) {
+        ScriptBuilder sb;
+        sb.str(label);
+        sb.words_dev(root_dev, 8);
+        sb.run(c, tr);
+    }
+    size_t n = size_t(1) << k;
+    Fe* eq = (Fe*)c->scratch(n * 16);
+    Fe* wef = (Fe*)c->scratch(n * 16);
+    WidenEqArgs a{};
+    a.src[0] = w; a.dst[0] = wef; a.len[0] = len; a.nsrc = 1; a.point = point; a.eq_out = eq; a.k = k;
+    widen_eq_kernel<<<grid_for(c, n), 256, 0, c->stream>>>(a);
+    ZKB_LAUNCHED(c);
+    const u32* tabs[3] = {(const u32*)eq, (const u32*)wef, nullptr};
+    ScOpts o;
+    o.clobber[0] = o.clobber[1] = true;
+    o.post_squeezes = 24;     // derive_query_indices (pcs.rs:442-451); the indices are not used
+    EvalRec r;
+    r.sc = sumcheck_enqueue(c, tr, ZKB_SC_PRODUCT_EF_FULL, tabs, k, o);
+    return r;
+}
+// EF weights (w_partial of a matmul); `w_ef` is clobbered.
+inline EvalRec prove_mle_eval_ef_ef(zkb_ctx* c, TrState* tr, Fe* w_ef, const Fe* point, u32 k) {
+    size_t n = size_t(1) << k;
+    Fe* eq = (Fe*)c->scratch(n * 16);
+    eq_evals_kernel<Fe><<<grid_for(c, n), 256, 0, c->stream>>>(point, k, eq);
+    ZKB_LAUNCHED(c);
+    const u32* tabs[3] = {(const u32*)eq, (const u32*)w_ef, nullptr};
+    ScOpts o;
+    o.clobber[0] = o.clobber[1] = true;
+    o.post_squeezes = 24;
+    EvalRec r;
+    r.sc = sumcheck_enqueue(c, tr, ZKB_SC_PRODUCT_EF_FULL, tabs, k, o);
+    return r;
+}
+// MleEvalProofEF {eval_sumcheck, eq_at_s, w_at_s}
+inline void put_eval(Ser& s, const EvalRec& e, bool with_challenges) {
+    s.sumcheck(e.sc, with_challenges);
+    s.ef(e.sc.fin);
+    s.ef(e.sc.fin + 4);
+}
+
+// ---- matmul -------------------------------------------------------------------------------------
+struct MatmulRec {
+    ScRec sc;            // product sumcheck over w_partial x x
+    size_t r_point = 0;  // log_m EF challenges
+    u32 log_m = 0, log_n = 0;
+    size_t root = 0;     // commitment of w_partial (interleaved coordinates)
+    u32 n_pad = 0;
+    EvalRec eval;
+};
+struct MatmulScratch { unsigned long long* acc; };
+
+// W: m x n row-major on device; x: n valid of n_pad (zero padded); y: m valid.
+inline MatmulRec prove_matmul_succinct_ef(zkb_ctx* c, TrState* tr, const u32* W, const u32* x, const u32* y, u32 m, u32 n) {
+    MatmulRec R;
+    R.log_m = log2_ceil_u(m); R.log_n = log2_ceil_u(n);
+    const size_t m_pad = size_t(1) << R.log_m, n_pad = size_t(1) << R.log_n;
+    R.n_pad = (u32)n_pad;
+    R.r_point = c->rec_alloc(4 * (size_t)R.log_m);
+    u32* r_dev = c->rec_dev + R.r_point;
+    {   // absorb_many(y_padded); r = squeeze_ef_many(log_m)     (matmul.rs:857-858)
+        ScriptBuilder sb;
+        sb.words_dev(y, m, (u32)m_pad);
+        sb.squeeze(r_dev, 4 * R.log_m);
+        sb.run(c, tr);
+    }
+    // eq table over the rows, then the one pass over W                     (matmul.rs:743-835)
+    Fe* eq_r = (Fe*)c->scratch(m_pad * 16);
+    eq_evals_kernel<Fe><<<grid_for(c, m_pad), 256, 0, c->stream>>>((const Fe*)r_dev, R.log_m, eq_r);
+    ZKB_LAUNCHED(c);
+    unsigned long long* acc = (unsigned long long*)c->scratch(n_pad * 4 * 8);
+    ZKB_CUDA(cudaMemsetAsync(acc, 0, n_pad * 4 * 8, c->stream));
+    Fe* w_partial = (Fe*)c->scratch(n_pad * 16);
+    {
+        const u32 col_ctas = (u32)((n + 511) / 512);
+        u32 want_rows = (u32)((c->sm_count * 6 + col_ctas - 1) / col_ctas);
+        if (want_rows < 1) want_rows = 1;
+        size_t rows_per = (m + want_rows - 1) / want_rows;
+        rows_per = (rows_per + FOLD_ROWS_TILE - 1) / FOLD_ROWS_TILE * FOLD_ROWS_TILE;
+        u32 row_ctas = (u32)((m + rows_per - 1) / rows_per);
+        dim3 grid(col_ctas, row_ctas);
+        fold_eq_matvec_kernel<4><<<grid, 128, 0, c->stream>>>(W, m, n, (const u32*)eq_r, rows_per, acc);
+        ZKB_LAUNCHED(c);
+        fold_finalize_kernel<4><<<grid_for(c, n_pad * 4), 256, 0, c->stream>>>(acc, n, n_pad, (u32*)w_partial);
+        ZKB_LAUNCHED(c);
+    }
+    // product sumcheck, full messages                                     (matmul.rs:889-944)
+    const u32* tabs[3] = {(const u32*)w_partial, x, nullptr};
+    R.sc = sumcheck_enqueue(c, tr, ZKB_SC_PRODUCT_EF_MIXED, tabs, R.log_n);
+    // default binding: blake3 of the interleaved coordinates, absorbed; then the EF MLE-eval
+    R.root = commit_small(c, (const u32*)w_partial, (u32)(4 * n_pad), nullptr, (u32)(4 * n_pad), tr);
+    R.eval = prove_mle_eval_ef_ef(c, tr, w_partial, (const Fe*)(c->rec_dev + R.sc.chal), R.log_n);
+    return R;
+}
+// SuccinctMatmulProofEF after strip_redundant (qwen.rs:745-750) when stripped = true.
+inline void put_matmul(Ser& s, const MatmulRec& R, bool stripped) {
+    // MatmulProofEF {sumcheck_proof, w_at_rs, x_at_s, r_point, s_point}
+    s.sumcheck(R.sc, !stripped);
+    s.ef(R.sc.fin); s.ef(R.sc.fin + 4);
+    if (stripped) { s.u64le(0); s.u64le(0); }
+    else {
+        s.u64le(R.log_m); s.words(R.r_point, 4 * (size_t)R.log_m);
+        s.u64le(R.log_n); s.words(R.sc.chal, 4 * (size_t)R.log_n);
+    }
+    put_eval(s, R.eval, !stripped);
+    for (int i = 0; i < 4; i++) s.u32le(0);                 // w_claimed_value
+    s.commitment(R.root, 4 * (u64)R.n_pad);                 // w_partial_commitment
+    s.u8(0);                                                // bound
+    s.u8(0);                                                // basefold_proof: None
+}
+
+// ---- hadamard / add -------------------------------------------------------------------------------
+struct HadamardRec { ScRec sc; size_t root = 0; EvalRec eval; u32 k = 0; };
+// a, b, c: base vectors with `len` valid entries, c zero-padded to 2^k on device; point: k EF on device.
+inline HadamardRec prove_hadamard_ef(zkb_ctx* c, TrState* tr, const u32* a, const u32* b, const u32* cvec, u32 len, const Fe* point, u32 k) {
+    HadamardRec R;
+    R.k = k;
+    size_t n = size_t(1) << k;
+    R.root = commit_small(c, cvec, (u32)n, nullptr, (u32)n, tr);
+    Fe* eq = (Fe*)c->scratch(n * 16);
+    Fe* aef = (Fe*)c->scratch(n * 16);
+    Fe* bef = (Fe*)c->scratch(n * 16);
+    WidenEqArgs w{};
+    w.src[0] = a; w.dst[0] = aef; w.len[0] = len; w.src[1] = b; w.dst[1] = bef; w.len[1] = len; w.nsrc = 2;
+    w.point = point; w.eq_out = eq; w.k = k;
+    widen_eq_kernel<<<grid_for(c, n), 256, 0, c->stream>>>(w);
+    ZKB_LAUNCHED(c);
+    const u32* tabs[3] = {(const u32*)eq, (const u32*)aef, (const u32*)bef};
+    ScOpts o;
+    o.clobber[0] = o.clobber[1] = o.clobber[2] = true;
+    R.sc = sumcheck_enqueue(c, tr, ZKB_SC_TRIPLE_EF_FULL, tabs, k, o);
+    R.eval = prove_mle_eval_ef_base(c, tr, cvec, (u32)n, point, k, "hadamard-c-eval-ef", c->rec_dev + R.root);
+    return R;
+}
+// HadamardProofEF {product_sumcheck, product_finals(3), c_eval, c_eval_proof, c_commitment}
+inline void put_hadamard(Ser& s, const HadamardRec& R, bool stripped) {
+    s.sumcheck(R.sc, !stripped);
+    s.ef(R.sc.fin); s.ef(R.sc.fin + 4); s.ef(R.sc.fin + 8);
+    s.claimed_sum_ef(R.eval.sc);      // c_eval = MLE of c at the point = sum eq . c = s0 + s1 of the eval sumcheck
+    put_eval(s, R.eval, true);
+    s.commitment(R.root, u64(1) << R.k);
+}
+
+struct AddRec { ScRec sa, sb; size_t root = 0; EvalRec eval; u32 k = 0; };
+inline AddRec prove_add_ef(zkb_ctx* c, TrState* tr, const u32* a, const u32* b, const u32* cvec, u32 len, const Fe* point, u32 k) {
+    AddRec R;
+    R.k = k;
+    size_t n = size_t(1) << k;
+    R.root = commit_small(c, cvec, (u32)n, nullptr, (u32)n, tr);
+    Fe* eq = (Fe*)c->scratch(n * 16);
+    Fe* aef = (Fe*)c->scratch(n * 16);
+    Fe* bef = (Fe*)c->scratch(n * 16);
+    WidenEqArgs w{};
+    w.src[0] = a; w.dst[0] = aef; w.len[0] = len; w.src[1] = b; w.dst[1] = bef; w.len[1] = len; w.nsrc = 2;
+    w.point = point; w.eq_out = eq; w.k = k;
+    widen_eq_kernel<<<grid_for(c, n), 256, 0, c->stream>>>(w);
+    ZKB_LAUNCHED(c);
+    const u32* ta[3] = {(const u32*)eq, (const u32*)aef, nullptr};
+    ScOpts oa;
+    oa.clobber[1] = true;             // eq is needed again by the second sumcheck
+    R.sa = sumcheck_enqueue(c, tr, ZKB_SC_PRODUCT_EF_FULL, ta, k, oa);
+    const u32* tb[3] = {(const u32*)eq, (const u32*)bef, nullptr};
+    ScOpts ob;
+    ob.clobber[0] = ob.clobber[1] = true;
+    R.sb = sumcheck_enqueue(c, tr, ZKB_SC_PRODUCT_EF_FULL, tb, k, ob);
+    R.eval = prove_mle_eval_ef_base(c, tr, cvec, (u32)n, point, k, "add-c-eval-ef", c->rec_dev + R.root);
+    return R;
+}
+// AddProofEF {a_sumcheck, a_finals(2), b_sumcheck, b_finals(2), c_eval, c_eval_proof, c_commitment}
+inline void put_add(Ser& s, const AddRec& R, bool stripped) {
+    s.sumcheck(R.sa, !stripped); s.ef(R.sa.fin); s.ef(R.sa.fin + 4);
+    s.sumcheck(R.sb, !stripped); s.ef(R.sb.fin); s.ef(R.sb.fin + 4);
+    s.claimed_sum_ef(R.eval.sc);
+    put_eval(s, R.eval, true);
+    s.commitment(R.root, u64(1) << R.k);
+}
+
+}  // namespace zkb

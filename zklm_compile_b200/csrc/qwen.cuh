@@ -1,0 +1,200 @@
+// One Qwen3.5-style layer at seq_len = 1: resident weights, forward trace on the device, and
+// the EF layer prover in the reference's transcript order.
+//
+//   qwen_forward_indexed               rust/zk_ml_prover/src/transformer/qwen.rs:211-325
+//   prove_qwen_layer_precommitted_ef   rust/zk_ml_prover/src/transformer/qwen.rs:795-912
+//   QwenLayerProofEF / strip_redundant rust/zk_ml_prover/src/transformer/qwen.rs:711-791
+//   per-layer transcript seed          rust/zk_ml_prover/src/pipeline/prove.rs:166-168
+#pragma once
+#include "protocols2.cuh"
+
+namespace zkb {
+
+struct QwenDims {
+    u32 d_model, d_ff, nq, nkv, d_head, v_heads, v_d_head;
+    u32 v_dim() const { return (v_heads ? v_heads : nkv) * (v_d_head ? v_d_head : d_head); }
+    u32 q_dim() const { return nq * d_head; }
+    u32 k_dim() const { return nkv * d_head; }
+    bool is_gqa() const { return nq != nkv; }
+    u32 aod() const { return is_gqa() ? q_dim() : v_dim(); }
+};
+
+enum { W_NORM1 = 0, W_Q, W_K, W_V, W_O, W_GPROJ, W_NORM2, W_GATE, W_UP, W_DOWN, W_COUNT };
+
+}  // namespace zkb
+
+struct zkb_qwen_layer {
+    zkb_ctx* ctx = nullptr;
+    zkb::QwenDims dm{};
+    zkb::u32* w[zkb::W_COUNT] = {};
+    size_t w_len[zkb::W_COUNT] = {};
+    zkb::u32* roots_dev = nullptr;        // 8 commitments x 8 words: q, k, v, o, g_proj, gate, up, down
+    zkb::u32 roots_host[64] = {};
+    const zkb::u32* silu = nullptr;       // table output columns (device), shared between layers
+    const zkb::u32* sigmoid = nullptr;
+    zkb::u32 n_table = 0;
+    // forward trace (device, each zero-padded to the next power of two)
+    zkb::u32 *x = nullptr, *norm1_x = nullptr, *norm1_out = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *attn_out = nullptr,
+             *g_raw = nullptr, *g_q = nullptr, *g_sig = nullptr, *gated_attn = nullptr, *gated_out = nullptr, *h = nullptr,
+             *norm2_x = nullptr, *norm2_out = nullptr, *gate_raw = nullptr, *gate_q = nullptr, *gate_silu = nullptr, *up = nullptr,
+             *swiglu = nullptr, *down = nullptr, *out = nullptr, *n1_scalars = nullptr, *n2_scalars = nullptr;
+    zkb::u32* trace_block = nullptr;
+    bool have_trace = false;
+    // pending proof
+    struct Pending;
+    Pending* pending = nullptr;
+};
+
+namespace zkb {
+
+inline size_t pad_pow2(size_t n) { return size_t(1) << log2_ceil_u(n); }
+
+inline void matvec_forward(zkb_ctx* c, const u32* W, const u32* x, u32 m, u32 n, u32* y, u32 m_pad) {
+    if (m_pad > m) ZKB_CUDA(cudaMemsetAsync(y + m, 0, (size_t)(m_pad - m) * 4, c->stream));
+    size_t warps = m;
+    int grid = grid_for(c, warps * 32, 256, 8);
+    matvec_forward_kernel<<<grid, 256, 0, c->stream>>>(W, x, m, n, y);
+    ZKB_LAUNCHED(c);
+}
+
+// Forward pass; the input x (d_model words) must already be in L->x.
+inline void qwen_forward(zkb_qwen_layer* L) {
+    zkb_ctx* c = L->ctx;
+    const QwenDims& d = L->dm;
+    const u32 dm = d.d_model, dmp = (u32)pad_pow2(dm), aod = d.aod(), aodp = (u32)pad_pow2(aod), dffp = (u32)pad_pow2(d.d_ff);
+    rmsnorm_forward_kernel<<<1, 1024, 0, c->stream>>>(L->x, L->w[W_NORM1], dm, dmp, L->norm1_out, L->norm1_x, L->n1_scalars, c->status);
+    ZKB_LAUNCHED(c);
+    matvec_forward(c, L->w[W_Q], L->norm1_out, d.q_dim(), dm, L->q, (u32)pad_pow2(d.q_dim()));
+    matvec_forward(c, L->w[W_K], L->norm1_out, d.k_dim(), dm, L->k, (u32)pad_pow2(d.k_dim()));
+    matvec_forward(c, L->w[W_V], L->norm1_out, d.v_dim(), dm, L->v, (u32)pad_pow2(d.v_dim()));
+    matvec_forward(c, L->w[W_GPROJ], L->norm1_out, aod, dm, L->g_raw, aodp);
+    if (d.is_gqa()) {
+        replicate_heads_kernel<<<grid_for(c, aodp), 256, 0, c->stream>>>(L->v, d.nq, d.nq / d.nkv, d.d_head, aodp, L->attn_out);
+        ZKB_LAUNCHED(c);
+    } else {
+        ZKB_CUDA(cudaMemcpyAsync(L->attn_out, L->v, (size_t)aodp * 4, cudaMemcpyDeviceToDevice, c->stream));
+    }
+    requant_lookup_mul_kernel<<<1, 1024, 0, c->stream>>>(L->g_raw, aod, aodp, L->sigmoid, L->n_table, L->attn_out, L->g_q, L->g_sig,
+                                                        L->gated_attn, c->status);
+    ZKB_LAUNCHED(c);
+    matvec_forward(c, L->w[W_O], L->gated_attn, dm, aod, L->gated_out, dmp);
+    add_vec_kernel<<<grid_for(c, dmp), 256, 0, c->stream>>>(L->x, L->gated_out, dm, dmp, L->h);
+    ZKB_LAUNCHED(c);
+    rmsnorm_forward_kernel<<<1, 1024, 0, c->stream>>>(L->h, L->w[W_NORM2], dm, dmp, L->norm2_out, L->norm2_x, L->n2_scalars, c->status);
+    ZKB_LAUNCHED(c);
+    matvec_forward(c, L->w[W_GATE], L->norm2_out, d.d_ff, dm, L->gate_raw, dffp);
+    matvec_forward(c, L->w[W_UP], L->norm2_out, d.d_ff, dm, L->up, dffp);
+    requant_lookup_mul_kernel<<<1, 1024, 0, c->stream>>>(L->gate_raw, d.d_ff, dffp, L->silu, L->n_table, L->up, L->gate_q, L->gate_silu,
+                                                        L->swiglu, c->status);
+    ZKB_LAUNCHED(c);
+    matvec_forward(c, L->w[W_DOWN], L->swiglu, dm, d.d_ff, L->down, dmp);
+    add_vec_kernel<<<grid_for(c, dmp), 256, 0, c->stream>>>(L->h, L->down, dm, dmp, L->out);
+    ZKB_LAUNCHED(c);
+    ZKB_CUDA(cudaGetLastError());
+    L->have_trace = true;
+}
+
+}  // namespace zkb
+
+struct zkb_qwen_layer::Pending {
+    zkb::RmsNormRec norm1, norm2;
+    zkb::MatmulRec mq, mk, mv, mo, mg, mgate, mup, mdown;
+    size_t seq1 = 0;
+    zkb::GateRec sig_gate, swiglu;
+    zkb::AddRec res1, res2;
+    size_t res1_point = 0, res2_point = 0;
+};
+
+namespace zkb {
+
+// Enqueue the whole layer proof (no synchronisation).
+inline void qwen_prove_enqueue(zkb_qwen_layer* L, u32 layer_idx, const uint8_t input_hash[32]) {
+    zkb_ctx* c = L->ctx;
+    const QwenDims& d = L->dm;
+    if (!L->have_trace) throw ArgFail{ZKB_E_ARG, "zkb_qwen_layer_prove: run the forward pass first"};
+    c->rec_reset();
+    c->scratch_reset();
+    delete L->pending;
+    L->pending = new zkb_qwen_layer::Pending();
+    auto& P = *L->pending;
+    const u32 dm = d.d_model, aod = d.aod();
+    TrState* tr = (TrState*)c->scratch(sizeof(TrState));
+    tr_init_kernel<<<1, 1, 0, c->stream>>>(tr);
+    ZKB_LAUNCHED(c);
+    {   // Transcript::new("qwen-layer-{idx}"); absorb input hash; dims; the eight roots
+        ScriptBuilder sb;
+        char seed[48];
+        snprintf(seed, sizeof seed, "qwen-layer-%u", layer_idx);
+        sb.str(seed);
+        sb.bytes(input_hash, 32);
+        sb.str("qwen-dims-v1");
+        u32 dims[12] = {d.d_model, d.d_ff, d.nq, d.nkv, d.d_head, d.v_heads, d.v_d_head, d.v_dim(), d.q_dim(), d.k_dim(), aod, d.is_gqa() ? 1u : 0u};
+        sb.bytes(dims, sizeof dims);
+        sb.words_dev(L->roots_dev, 64);
+        sb.run(c, tr);
+    }
+    P.norm1 = prove_rmsnorm_ef(c, tr, L->norm1_x, L->w[W_NORM1], L->norm1_out, dm, L->n1_scalars);
+    P.mq = prove_matmul_succinct_ef(c, tr, L->w[W_Q], L->norm1_out, L->q, d.q_dim(), dm);
+    P.mk = prove_matmul_succinct_ef(c, tr, L->w[W_K], L->norm1_out, L->k, d.k_dim(), dm);
+    P.mv = prove_matmul_succinct_ef(c, tr, L->w[W_V], L->norm1_out, L->v, d.v_dim(), dm);
+    P.seq1 = c->rec_alloc(2);
+    seq1_consistency_kernel<<<1, 1024, 0, c->stream>>>(tr, L->attn_out, aod, log2_ceil_u(aod), L->v, d.v_dim(), log2_ceil_u(d.v_dim()),
+                                                      d.is_gqa() ? 1u : 0u, log2_ceil_u(d.nkv), log2_ceil_u(d.d_head), c->rec_dev + P.seq1);
+    ZKB_LAUNCHED(c);
+    P.mo = prove_matmul_succinct_ef(c, tr, L->w[W_O], L->gated_attn, L->gated_out, dm, aod);
+    P.mg = prove_matmul_succinct_ef(c, tr, L->w[W_GPROJ], L->norm1_out, L->g_raw, aod, dm);
+    // prove_sigmoid_gate_ef(gate = g_q, gate_sigmoid = g_sig, input = attn_out, output = gated_attn)
+    P.sig_gate = prove_gate_ef(c, tr, L->sigmoid, L->n_table, L->g_q, L->g_sig, L->attn_out, L->g_sig, L->gated_attn, aod);
+    const u32 log_d = log2_ceil_u(dm);
+    P.res1_point = c->rec_alloc(4 * (size_t)log_d);
+    { ScriptBuilder sb; sb.squeeze(c->rec_dev + P.res1_point, 4 * log_d); sb.run(c, tr); }
+    P.res1 = prove_add_ef(c, tr, L->x, L->gated_out, L->h, dm, (const Fe*)(c->rec_dev + P.res1_point), log_d);
+    P.norm2 = prove_rmsnorm_ef(c, tr, L->norm2_x, L->w[W_NORM2], L->norm2_out, dm, L->n2_scalars);
+    P.mgate = prove_matmul_succinct_ef(c, tr, L->w[W_GATE], L->norm2_out, L->gate_raw, d.d_ff, dm);
+    P.mup = prove_matmul_succinct_ef(c, tr, L->w[W_UP], L->norm2_out, L->up, d.d_ff, dm);
+    // prove_swiglu_ef(gate = gate_q, gate_silu, up, output = swiglu): hadamard(gate_silu, up)
+    P.swiglu = prove_gate_ef(c, tr, L->silu, L->n_table, L->gate_q, L->gate_silu, L->gate_silu, L->up, L->swiglu, d.d_ff);
+    P.mdown = prove_matmul_succinct_ef(c, tr, L->w[W_DOWN], L->swiglu, L->down, dm, d.d_ff);
+    P.res2_point = c->rec_alloc(4 * (size_t)log_d);
+    { ScriptBuilder sb; sb.squeeze(c->rec_dev + P.res2_point, 4 * log_d); sb.run(c, tr); }
+    P.res2 = prove_add_ef(c, tr, L->h, L->down, L->out, dm, (const Fe*)(c->rec_dev + P.res2_point), log_d);
+    ZKB_CUDA(cudaGetLastError());
+}
+
+// Wait for the enqueued proof and serialise QwenLayerProofEF (after strip_redundant) as bincode.
+inline std::vector<uint8_t> qwen_prove_finish(zkb_qwen_layer* L, uint32_t* status_out) {
+    zkb_ctx* c = L->ctx;
+    if (!L->pending) throw ArgFail{ZKB_E_ARG, "no proof enqueued"};
+    c->rec_fetch();
+    *status_out = c->read_status();
+    auto& P = *L->pending;
+    const QwenDims& d = L->dm;
+    Ser s;
+    s.rec = c->rec_host;
+    put_rmsnorm(s, P.norm1, true);
+    put_matmul(s, P.mq, true); put_matmul(s, P.mk, true); put_matmul(s, P.mv, true);
+    // RowAttentionProof {row_proofs: [], num_heads, seq_len, d_head, seq1_consistency: Some{..}}
+    s.u64le(0); s.u64le(d.nq); s.u64le(1); s.u64le(d.d_head);
+    s.u8(1); s.u32le(s.rec[P.seq1]); s.u32le(s.rec[P.seq1 + 1]); s.u8(d.is_gqa() ? 1 : 0);
+    put_matmul(s, P.mo, true); put_matmul(s, P.mg, true);
+    put_gate(s, P.sig_gate, true);
+    put_add(s, P.res1, true);
+    put_rmsnorm(s, P.norm2, true);
+    put_matmul(s, P.mgate, true); put_matmul(s, P.mup, true);
+    put_gate(s, P.swiglu, true);
+    put_matmul(s, P.mdown, true);
+    put_add(s, P.res2, true);
+    for (int i = 0; i < 8; i++) {       // weight commitments of the unpadded matrices
+        static const int widx[8] = {W_Q, W_K, W_V, W_O, W_GPROJ, W_GATE, W_UP, W_DOWN};
+        for (int k = 0; k < 8; k++) s.u32le(L->roots_host[8 * i + k]);
+        u64 nw = L->w_len[widx[i]];
+        s.u64le(nw);
+        s.u64le(nw <= 1 ? 1 : log2_ceil_u(nw));
+        s.u32le(0);
+    }
+    delete L->pending;
+    L->pending = nullptr;
+    return s.b;
+}
+
+}  // namespace zkb

@@ -47,12 +47,17 @@ struct ScIO {
     TrState* tr;            // device transcript, advanced in place
     u32* partials;          // [SC_MAX_GRID][16]
     unsigned int* counter;  // ticket for "last CTA done"; left at 0
-    u32* polys;             // [num_vars][nstored][W]
+    u32* polys;             // [num_vars][NABS][W]: every absorbed evaluation s_0.. of every round
     u32* chal;              // [num_vars][W]
     u32* fin;               // [NT][W]
-    u32 store_mask;         // bit k set: s_k is stored in the proof (all s_k are absorbed)
-    u32 nstored;
+    const u32* dyn_nv;      // tail only, optional: num_vars read from device memory (LogUp)
+    u32* status;            // optional status word (see check_zero_sum)
+    u32* post_out;          // optional destination of the post-squeezed challenges
+    u32 post_squeezes;      // base-field squeezes performed right after the final evaluations
+    u32 check_zero_sum;     // nonzero: flag status = 3 unless round 0 has s0 + s1 == 0 (LogUp identity)
 };
+__device__ __forceinline__ bool is_zero_el(Fp a) { return a.v == 0; }
+__device__ __forceinline__ bool is_zero_el(Fe a) { return (a.x | a.y | a.z | a.w) == 0; }
 
 // ---- small conversions ---------------------------------------------------------------------
 __device__ __forceinline__ void to_words(Fp a, u32* w) { w[0] = a.v; }
@@ -162,11 +167,12 @@ __device__ __forceinline__ ChalT sc_finish_round(const u32* words, const ScIO& i
         widen_to(a, s[k]);
     }
     if constexpr (KIND == SC_ONES) s[2] = s[1] + s[1] - s[0];
-    u32* out = io.polys + (size_t)round * io.nstored * WC;
+    if (io.check_zero_sum && round == 0 && !is_zero_el(s[0] + s[1])) atomicExch(io.status, 3u);
+    u32* out = io.polys + (size_t)round * NABS * WC;
 #pragma unroll
     for (int k = 0; k < NABS; k++) {
         tr_absorb_el(tr, s[k]);
-        if (io.store_mask & (1u << k)) { to_words(s[k], out); out += WC; }
+        to_words(s[k], out + k * WC);
     }
     ChalT r;
     tr_squeeze_el(tr, r);
@@ -237,6 +243,7 @@ __global__ void __launch_bounds__(SC_TAIL_THREADS) sc_tail_kernel(ScTables tb, s
     __shared__ __align__(16) unsigned char trbuf[64];
     __shared__ u32 r_sh[4];
 
+    if (io.dyn_nv) { num_vars = io.dyn_nv[0]; size = size_t(1) << num_vars; }
     Tr tr;
     if (threadIdx.x == 0) tr_load(tr, io.tr, trbuf);
     ChalT r = zero_of<ChalT>();
@@ -289,6 +296,10 @@ __global__ void __launch_bounds__(SC_TAIL_THREADS) sc_tail_kernel(ScTables tb, s
     }
 
     if (threadIdx.x == 0) {
+        for (u32 q = 0; q < io.post_squeezes; q++) {
+            u32 v = tr_squeeze(tr);
+            if (io.post_out) io.post_out[q] = v;
+        }
         tr_store(tr, io.tr);
         // size == 2 here: fold the last challenge in.
 #pragma unroll

@@ -1,160 +1,9 @@
 // C ABI of the backend (see include/zkb200.h) and the host-side launch logic.
-#include "context.cuh"
+#include "qwen.cuh"
 #include <cstring>
 #include <new>
 
 using namespace zkb;
-
-// =============================================================================================
-// transcript kernels
-// =============================================================================================
-struct ByteChunk { unsigned char b[256]; };
-
-__global__ void tr_init_kernel(TrState* st) {
-    u32 h[8];
-    tr_iv(h);
-    for (int i = 0; i < 8; i++) st->h[i] = h[i];
-    st->buflen = 0; st->_pad = 0; st->total = 0;
-    for (int i = 0; i < 64; i++) st->buf[i] = 0;
-}
-__global__ void tr_absorb_bytes_kernel(TrState* st, ByteChunk c, u32 n) {
-    __shared__ __align__(16) unsigned char trbuf[64];
-    Tr tr;
-    tr_load(tr, st, trbuf);
-    tr_absorb_bytes(tr, c.b, n);
-    tr_store(tr, st);
-}
-// One warp: lanes stage 512-word tiles into shared memory, lane 0 runs the hash chain.
-__global__ void tr_absorb_words_kernel(TrState* st, const u32* __restrict__ v, size_t n) {
-    __shared__ __align__(16) unsigned char trbuf[64];
-    __shared__ u32 tile[512];
-    Tr tr;
-    if (threadIdx.x == 0) tr_load(tr, st, trbuf);
-    for (size_t base = 0; base < n; base += 512) {
-        size_t m = n - base < 512 ? n - base : 512;
-        for (size_t i = threadIdx.x; i < m; i += blockDim.x) tile[i] = v[base + i];
-        __syncwarp();
-        if (threadIdx.x == 0)
-            for (size_t i = 0; i < m; i++) tr_absorb_u32(tr, tile[i]);
-        __syncwarp();
-    }
-    if (threadIdx.x == 0) tr_store(tr, st);
-}
-__global__ void tr_squeeze_kernel(TrState* st, u32* out, u32 count) {
-    __shared__ __align__(16) unsigned char trbuf[64];
-    Tr tr;
-    tr_load(tr, st, trbuf);
-    for (u32 i = 0; i < count; i++) out[i] = tr_squeeze(tr);
-    tr_store(tr, st);
-}
-
-// =============================================================================================
-// sumcheck launch logic
-// =============================================================================================
-namespace {
-
-constexpr size_t MULTI_MIN_HALF = 2048;   // below this many pairs the single-CTA tail takes over
-
-template <int KIND, class SrcT, class ChalT>
-void run_sumcheck(zkb_ctx* c, ScTables tb, u32 num_vars, ScIO io) {
-    size_t size = size_t(1) << num_vars;
-    bool pending = false, in_src = true;
-    u32 round = 0;
-    const int max_grid = c->sm_count * 8 < SC_MAX_GRID ? c->sm_count * 8 : SC_MAX_GRID;
-    c->prof_used = 0;
-    c->prof_mark();
-    while (round < num_vars) {
-        size_t half = pending ? size / 4 : size / 2;
-        if (half < MULTI_MIN_HALF) break;
-        size_t want = (half + 255) / 256;
-        int grid = (int)(want < (size_t)max_grid ? want : (size_t)max_grid);
-        if (!pending) {
-            sc_round_kernel<KIND, SrcT, ChalT, false><<<grid, 256, 0, c->stream>>>(tb, half, round, io);
-        } else if (in_src) {
-            sc_round_kernel<KIND, SrcT, ChalT, true><<<grid, 256, 0, c->stream>>>(tb, half, round, io);
-            for (int t = 0; t < 3; t++) tb.src[t] = tb.dst[t];
-            in_src = false;
-            size /= 2;
-        } else {
-            sc_round_kernel<KIND, ChalT, ChalT, true><<<grid, 256, 0, c->stream>>>(tb, half, round, io);
-            size /= 2;
-        }
-        c->launches++;
-        c->prof_mark();
-        pending = true;
-        round++;
-    }
-    if (in_src)
-        sc_tail_kernel<KIND, SrcT, ChalT><<<1, SC_TAIL_THREADS, 0, c->stream>>>(tb, size, round, num_vars, pending ? 1 : 0, io);
-    else
-        sc_tail_kernel<KIND, ChalT, ChalT><<<1, SC_TAIL_THREADS, 0, c->stream>>>(tb, size, round, num_vars, 1, io);
-    c->launches++;
-    c->prof_mark();
-    ZKB_CUDA(cudaGetLastError());
-}
-
-__global__ void widen_kernel(const u32* __restrict__ in, Fe* out, size_t n) {
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
-        st_fe(out + i, Fe{in[i], 0, 0, 0});
-}
-
-struct KindInfo { int nt; int in_w[3]; int w; u32 mask; u32 nstored; };
-KindInfo kind_info(int kind) {
-    switch (kind) {
-        case ZKB_SC_PRODUCT:              return {2, {1, 1, 0}, 1, 0b0111, 3};
-        case ZKB_SC_TRIPLE:               return {3, {1, 1, 1}, 1, 0b1111, 4};
-        case ZKB_SC_PRODUCT_ONES:         return {1, {1, 0, 0}, 1, 0b0101, 2};
-        case ZKB_SC_PRODUCT_EF:           return {2, {1, 1, 0}, 4, 0b0101, 2};
-        case ZKB_SC_PRODUCT_EF_FULL:      return {2, {4, 4, 0}, 4, 0b0111, 3};
-        case ZKB_SC_PRODUCT_EF_MIXED:     return {2, {4, 1, 0}, 4, 0b0111, 3};
-        case ZKB_SC_TRIPLE_EF_FULL:       return {3, {4, 4, 4}, 4, 0b1101, 3};
-        case ZKB_SC_PRODUCT_ONES_EF_FULL: return {1, {4, 0, 0}, 4, 0b0101, 2};
-    }
-    throw ArgFail{ZKB_E_ARG, "unknown sumcheck kind"};
-}
-
-}  // namespace
-
-namespace zkb {
-
-// Enqueue one sumcheck on device tables; outputs go to device memory at out_polys / out_chal /
-// out_fin.  No synchronisation.  `tables_dev` are left untouched; working copies come from the
-// context's scratch arena (the caller rewinds it).
-void sumcheck_enqueue(zkb_ctx* c, TrState* tr, int kind, const u32* const* tables_dev, u32 num_vars,
-                      u32* out_polys, u32* out_chal, u32* out_fin) {
-    KindInfo ki = kind_info(kind);
-    if (num_vars < 1 || num_vars > 40) throw ArgFail{ZKB_E_ARG, "num_vars out of range"};
-    const size_t n = size_t(1) << num_vars;
-    ScTables tb{};
-    const size_t dst_elems = n / 2 > 2 ? n / 2 : 2;
-    for (int t = 0; t < ki.nt; t++) {
-        tb.src[t] = tables_dev[t];
-        tb.dst[t] = c->scratch(dst_elems * 4 * ki.w);
-    }
-    if (kind == ZKB_SC_PRODUCT_EF_MIXED) {      // widen g once; then it is PRODUCT_EF_FULL with the same message layout
-        Fe* g = (Fe*)c->scratch(n * 16);
-        int grid = (int)((n + 255) / 256 < 1184 ? (n + 255) / 256 : 1184);
-        widen_kernel<<<grid, 256, 0, c->stream>>>(tables_dev[1], g, n);
-        c->launches++;
-        tb.src[1] = g;
-    }
-    ScIO io{};
-    io.tr = tr; io.partials = c->partials; io.counter = c->counter;
-    io.polys = out_polys; io.chal = out_chal; io.fin = out_fin;
-    io.store_mask = ki.mask; io.nstored = ki.nstored;
-    switch (kind) {
-        case ZKB_SC_PRODUCT:              run_sumcheck<SC_PRODUCT, Fp, Fp>(c, tb, num_vars, io); break;
-        case ZKB_SC_TRIPLE:               run_sumcheck<SC_TRIPLE, Fp, Fp>(c, tb, num_vars, io); break;
-        case ZKB_SC_PRODUCT_ONES:         run_sumcheck<SC_ONES, Fp, Fp>(c, tb, num_vars, io); break;
-        case ZKB_SC_PRODUCT_EF:           run_sumcheck<SC_PRODUCT, Fp, Fe>(c, tb, num_vars, io); break;
-        case ZKB_SC_PRODUCT_EF_FULL:
-        case ZKB_SC_PRODUCT_EF_MIXED:     run_sumcheck<SC_PRODUCT, Fe, Fe>(c, tb, num_vars, io); break;
-        case ZKB_SC_TRIPLE_EF_FULL:       run_sumcheck<SC_TRIPLE, Fe, Fe>(c, tb, num_vars, io); break;
-        case ZKB_SC_PRODUCT_ONES_EF_FULL: run_sumcheck<SC_ONES, Fe, Fe>(c, tb, num_vars, io); break;
-    }
-}
-
-}  // namespace zkb
 
 // =============================================================================================
 // C ABI
@@ -187,6 +36,9 @@ int32_t zkb_ctx_create(int32_t device, zkb_ctx** out) {
         ZKB_CUDA(cudaMemsetAsync(c->counter, 0, 64, c->stream));
         ZKB_CUDA(cudaMalloc(&c->status, 64));
         ZKB_CUDA(cudaMemsetAsync(c->status, 0, 64, c->stream));
+        c->rec_cap = size_t(1) << 20;                       // 4 MiB of proof record
+        ZKB_CUDA(cudaMalloc(&c->rec_dev, c->rec_cap * 4));
+        ZKB_CUDA(cudaHostAlloc(&c->rec_host, c->rec_cap * 4, cudaHostAllocDefault));
         ZKB_CUDA(cudaEventCreate(&c->t0));
         ZKB_CUDA(cudaEventCreate(&c->t1));
         ZKB_CUDA(cudaStreamSynchronize(c->stream));
@@ -211,6 +63,8 @@ void zkb_ctx_destroy(zkb_ctx* c) {
     if (c->partials) cudaFree(c->partials);
     if (c->counter) cudaFree(c->counter);
     if (c->status) cudaFree(c->status);
+    if (c->rec_dev) cudaFree(c->rec_dev);
+    if (c->rec_host) cudaFreeHost(c->rec_host);
     if (c->t0) cudaEventDestroy(c->t0);
     if (c->t1) cudaEventDestroy(c->t1);
     if (c->stream) cudaStreamDestroy(c->stream);
@@ -419,20 +273,22 @@ int32_t zkb_sumcheck_prove(zkb_ctx* c, zkb_transcript* t, int32_t kind, const ui
                 dev_tabs[i] = d;
             }
         }
-        const size_t npoly = (size_t)num_vars * ki.nstored * ki.w, nchal = (size_t)num_vars * ki.w;
-        const int nfin = ki.nt < 2 ? 2 : ki.nt;
-        u32* out = (u32*)c->scratch((npoly + nchal + 3 * 4) * 4);
-        u32* d_fin = out + npoly + nchal;
-        // For ONES the first final is the constant 1 (sumcheck.rs:901, 1434); the kernel writes g(s) to slot 0.
-        sumcheck_enqueue(c, t->dev, kind, dev_tabs, num_vars, out, out + npoly, d_fin);
-        ZKB_CUDA(cudaMemcpyAsync(round_polys, out, npoly * 4, cudaMemcpyDeviceToHost, c->stream));
-        ZKB_CUDA(cudaMemcpyAsync(challenges, out + npoly, nchal * 4, cudaMemcpyDeviceToHost, c->stream));
-        if (ki.nt == 1) {
+        c->rec_reset();
+        ScRec r = sumcheck_enqueue(c, t->dev, kind, dev_tabs, num_vars);
+        c->rec_fetch();
+        const u32* rec = c->rec_host;
+        size_t k = 0;
+        for (u32 round = 0; round < num_vars; round++)
+            for (u32 e = 0; e < ki.nabs; e++)
+                if (ki.mask & (1u << e))
+                    for (int wd = 0; wd < ki.w; wd++) round_polys[k++] = rec[r.polys + ((size_t)round * ki.nabs + e) * ki.w + wd];
+        memcpy(challenges, rec + r.chal, (size_t)num_vars * ki.w * 4);
+        if (ki.nt == 1) {   // f == 1: first final is the constant one (sumcheck.rs:901, 1434); the kernel writes g(s) to slot 0
             memset(finals, 0, ki.w * 4);
             finals[0] = 1;
-            ZKB_CUDA(cudaMemcpyAsync(finals + ki.w, d_fin, ki.w * 4, cudaMemcpyDeviceToHost, c->stream));
+            memcpy(finals + ki.w, rec + r.fin, ki.w * 4);
         } else {
-            ZKB_CUDA(cudaMemcpyAsync(finals, d_fin, (size_t)nfin * ki.w * 4, cudaMemcpyDeviceToHost, c->stream));
+            memcpy(finals, rec + r.fin, (size_t)ki.nt * ki.w * 4);
         }
         ZKB_CUDA(cudaStreamSynchronize(c->stream));
         c->scratch_reset();
@@ -440,3 +296,6 @@ int32_t zkb_sumcheck_prove(zkb_ctx* c, zkb_transcript* t, int32_t kind, const ui
 }
 
 }  // extern "C"
+
+#include "abi_protocols.cuh"
+#include "abi_layer.cuh"

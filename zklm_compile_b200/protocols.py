@@ -1,0 +1,158 @@
+"""Host-side mirror of the reference's sub-protocol provers over the C ABI.
+
+Each `prove_*` returns the proof as the reference's bincode bytes (the layout of the serde
+structs in rust/zk_ml_prover/src/proving/*.rs), so two implementations can be compared byte
+for byte.  Names and argument order follow the reference functions cited per function.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from ._lib import check, u32p
+from .sumcheck import Context, DeviceBuffer, Transcript
+
+
+def _a(x):
+    a = np.ascontiguousarray(x, dtype=np.uint32)
+    return a, a.ctypes.data_as(u32p)
+
+
+def log2_ceil(n: int) -> int:
+    """rust/zk_ml_prover/src/field/common.rs:16-21"""
+    return 1 if n <= 1 else (n - 1).bit_length()
+
+
+def _proof_call(ctx: Context, fn, *args, cap: int = 1 << 22) -> bytes:
+    buf = (C.c_uint8 * cap)()
+    n = C.c_size_t()
+    st = fn(*args, buf, C.c_size_t(cap), C.byref(n))
+    if st == 7 and n.value > cap:
+        return _proof_call(ctx, fn, *args, cap=n.value)
+    check(ctx.h, st)
+    return bytes(buf[:n.value])
+
+
+def commit_weights_fast(ctx: Context, weights) -> bytes:
+    """weight_commitment.rs:82-107 -> 32-byte root."""
+    out = (C.c_uint8 * 32)()
+    if isinstance(weights, DeviceBuffer):
+        check(ctx.h, _lib.lib().zkb_commit_weights_fast(ctx.h, weights.ptr, C.c_size_t(weights.n), C.c_int32(1), out))
+    else:
+        w, pw = _a(weights)
+        check(ctx.h, _lib.lib().zkb_commit_weights_fast(ctx.h, pw, C.c_size_t(w.size), C.c_int32(0), out))
+    return bytes(out)
+
+
+def eq_evals(ctx: Context, r) -> np.ndarray:
+    """m31_ops.rs:30-50"""
+    a, pa = _a(r)
+    out = np.zeros(1 << a.size, np.uint32)
+    check(ctx.h, _lib.lib().zkb_eq_evals(ctx.h, pa, C.c_uint32(a.size), C.c_int32(0), out.ctypes.data_as(u32p)))
+    return out
+
+
+def eq_evals_ef(ctx: Context, r) -> np.ndarray:
+    """m31_ops.rs:175-191; r is (k, 4)."""
+    a, pa = _a(r)
+    k = a.size // 4
+    out = np.zeros((1 << k, 4), np.uint32)
+    check(ctx.h, _lib.lib().zkb_eq_evals(ctx.h, pa, C.c_uint32(k), C.c_int32(1), out.ctypes.data_as(u32p)))
+    return out
+
+
+def fold_eq_matvec(ctx: Context, w_flat, m: int, n: int, r_point, ef: bool = False) -> np.ndarray:
+    """matmul.rs:76-128 (ef=False) / :743-835 (ef=True)."""
+    r, pr = _a(r_point)
+    log_m = r.size // (4 if ef else 1)
+    n_pad = 1 << log2_ceil(n)
+    out = np.zeros((n_pad, 4) if ef else n_pad, np.uint32)
+    if isinstance(w_flat, DeviceBuffer):
+        pw, on = w_flat.ptr, 1
+    else:
+        w, pw = _a(w_flat)
+        on = 0
+    check(ctx.h, _lib.lib().zkb_fold_eq_matvec(ctx.h, pw, C.c_size_t(m), C.c_size_t(n), pr, C.c_uint32(log_m), C.c_int32(int(ef)),
+                                                C.c_int32(on), out.ctypes.data_as(u32p)))
+    return out
+
+
+def matmul_forward(ctx: Context, w_flat, x, m: int, n: int) -> np.ndarray:
+    """transformer/mod.rs:140-163"""
+    xv, px = _a(x)
+    y = np.zeros(m, np.uint32)
+    if isinstance(w_flat, DeviceBuffer):
+        pw, on = w_flat.ptr, 1
+    else:
+        w, pw = _a(w_flat)
+        on = 0
+    check(ctx.h, _lib.lib().zkb_matvec_forward(ctx.h, pw, px, C.c_size_t(m), C.c_size_t(n), C.c_int32(on), y.ctypes.data_as(u32p)))
+    return y
+
+
+def rmsnorm_forward(ctx: Context, x, gamma):
+    """transformer/mod.rs:245-288 -> (output, perturbed_input, delta)."""
+    xv, px = _a(x)
+    g, pg = _a(gamma)
+    out = np.zeros(xv.size, np.uint32)
+    xu = np.zeros(xv.size, np.uint32)
+    delta = C.c_int32()
+    check(ctx.h, _lib.lib().zkb_rmsnorm_forward(ctx.h, px, pg, C.c_size_t(xv.size), out.ctypes.data_as(u32p), xu.ctypes.data_as(u32p),
+                                                 C.byref(delta)))
+    return out, xu, delta.value
+
+
+def prove_matmul_succinct_ef(w_flat, x_vals, y_vals, m: int, n: int, transcript: Transcript) -> bytes:
+    """matmul.rs:963-997 -> SuccinctMatmulProofEF."""
+    ctx = transcript.ctx
+    x, px = _a(x_vals)
+    y, py = _a(y_vals)
+    if isinstance(w_flat, DeviceBuffer):
+        pw, on = w_flat.ptr, 1
+    else:
+        w, pw = _a(w_flat)
+        on = 0
+    return _proof_call(ctx, _lib.lib().zkb_prove_matmul_succinct_ef, ctx.h, transcript.h, pw, px, py, C.c_size_t(m), C.c_size_t(n),
+                       C.c_int32(on))
+
+
+def _elementwise(is_add, a, b, c, point, transcript):
+    ctx = transcript.ctx
+    av, pa = _a(a)
+    bv, pb = _a(b)
+    cv, pc = _a(c)
+    pt, pp = _a(point)
+    return _proof_call(ctx, _lib.lib().zkb_prove_elementwise_ef, ctx.h, transcript.h, C.c_int32(is_add), pa, pb, pc, C.c_size_t(av.size),
+                       pp, C.c_uint32(pt.size // 4))
+
+
+def prove_hadamard_ef(a, b, c, point, transcript: Transcript) -> bytes:
+    """elementwise.rs:429-480 -> HadamardProofEF."""
+    return _elementwise(0, a, b, c, point, transcript)
+
+
+def prove_add_ef(a, b, c, point, transcript: Transcript) -> bytes:
+    """elementwise.rs:545-595 -> AddProofEF."""
+    return _elementwise(1, a, b, c, point, transcript)
+
+
+def prove_rmsnorm_ef(x, gamma, y, perturbation_delta: int, transcript: Transcript) -> bytes:
+    """rmsnorm.rs:512-667 -> RmsNormProofEF."""
+    ctx = transcript.ctx
+    xv, px = _a(x)
+    g, pg = _a(gamma)
+    yv, py = _a(y)
+    return _proof_call(ctx, _lib.lib().zkb_prove_rmsnorm_ef, ctx.h, transcript.h, px, pg, py, C.c_size_t(xv.size),
+                       C.c_int32(perturbation_delta))
+
+
+def prove_lookup_ef(table_outputs, inputs, outputs, transcript: Transcript) -> bytes:
+    """lookup.rs:643-762 -> LookupProofEF.  Raises ZkbError with the reference's panic messages
+    (status 3: LogUp identity failed, status 4: alpha collision)."""
+    ctx = transcript.ctx
+    t, pt = _a(table_outputs)
+    i, pi = _a(inputs)
+    o, po = _a(outputs)
+    return _proof_call(ctx, _lib.lib().zkb_prove_lookup_ef, ctx.h, transcript.h, pt, C.c_size_t(t.size), pi, po, C.c_size_t(i.size))

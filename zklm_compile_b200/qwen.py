@@ -1,0 +1,135 @@
+"""Resident Qwen3.5-style layers and the multi-layer prove loop.
+
+Mirrors, for seq_len = 1:
+  QwenLayerWeights / commit_qwen_layer   rust/zk_ml_prover/src/transformer/qwen.rs:62-73, 148-161
+  qwen_forward_indexed                   rust/zk_ml_prover/src/transformer/qwen.rs:211-325
+  prove_qwen_layer_precommitted_ef       rust/zk_ml_prover/src/transformer/qwen.rs:795-912
+  the per-layer fan-out                  rust/zk_ml_prover/src/pipeline/prove.rs:158-189
+"""
+from __future__ import annotations
+
+import ctypes as C
+import hashlib
+from concurrent.futures import ThreadPoolExecutor
+
+import numpy as np
+
+from . import _lib
+from ._lib import check, u32p
+from .sumcheck import Context, DeviceBuffer
+
+WEIGHT_NAMES = ["norm1_gamma", "w_q", "w_k", "w_v", "w_o", "w_g_proj", "norm2_gamma", "w_gate", "w_up", "w_down"]
+DIM_NAMES = ["d_model", "d_ff", "num_q_heads", "num_kv_heads", "d_head", "v_num_heads", "v_d_head"]
+
+
+def hash_values(values) -> bytes:
+    """rust/zk_ml_prover/src/field/common.rs:78-85: SHA-256(len u32 LE || values u32 LE)."""
+    a = np.ascontiguousarray(values, dtype="<u4")
+    return hashlib.sha256(len(a).to_bytes(4, "little") + a.tobytes()).digest()
+
+
+class QwenLayer:
+    """One layer with its weights resident in HBM and its eight weight commitments computed at
+    load time (the reference excludes `commit_qwen_layer` from prove time,
+    rust/zk_ml_prover/src/pipeline/mod.rs:224-229)."""
+
+    def __init__(self, ctx: Context, config: dict, weights: dict, silu_table: DeviceBuffer, sigmoid_table: DeviceBuffer):
+        self.ctx = ctx
+        self.config = dict(config)
+        self.h = C.c_void_p()
+        dims = (C.c_uint64 * 7)(*[int(config.get(k, 0)) for k in DIM_NAMES])
+        keep = [np.ascontiguousarray(weights[k], dtype=np.uint32) for k in WEIGHT_NAMES]
+        wp = (u32p * 10)(*[a.ctypes.data_as(u32p) for a in keep])
+        self._tables = (silu_table, sigmoid_table)
+        check(ctx.h, _lib.lib().zkb_qwen_layer_create(ctx.h, dims, wp, silu_table.ptr, sigmoid_table.ptr, C.c_uint32(silu_table.n),
+                                                       C.byref(self.h)))
+        self.d_model = int(config["d_model"])
+
+    def close(self):
+        if self.h.value and self.ctx.h.value:
+            _lib.lib().zkb_qwen_layer_destroy.restype = None
+            _lib.lib().zkb_qwen_layer_destroy(self.h)
+            self.h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def commitments(self):
+        buf = (C.c_uint8 * 256)()
+        check(self.ctx.h, _lib.lib().zkb_qwen_layer_commitments(self.h, buf))
+        b = bytes(buf)
+        return [b[32 * i:32 * i + 32] for i in range(8)]
+
+    def forward(self, x) -> np.ndarray:
+        a = np.ascontiguousarray(x, dtype=np.uint32)
+        y = np.zeros(self.d_model, np.uint32)
+        check(self.ctx.h, _lib.lib().zkb_qwen_layer_forward(self.h, a.ctypes.data_as(u32p), C.c_int32(0), y.ctypes.data_as(u32p), C.c_int32(0)))
+        return y
+
+    def forward_from(self, prev: "QwenLayer"):
+        """Forward with the previous layer's device-resident output as input (no host copy)."""
+        _lib.lib().zkb_qwen_layer_output_dev.restype = u32p
+        src = _lib.lib().zkb_qwen_layer_output_dev(prev.h)
+        check(self.ctx.h, _lib.lib().zkb_qwen_layer_forward(self.h, src, C.c_int32(1), None, C.c_int32(0)))
+
+    def output(self) -> np.ndarray:
+        _lib.lib().zkb_qwen_layer_output_dev.restype = u32p
+        src = _lib.lib().zkb_qwen_layer_output_dev(self.h)
+        y = np.zeros(self.d_model, np.uint32)
+        check(self.ctx.h, _lib.lib().zkb_buf_download_u32(self.ctx.h, src, C.c_size_t(self.d_model), y.ctypes.data_as(u32p)))
+        return y
+
+    def prove_begin(self, layer_idx: int, input_hash: bytes):
+        ih = (C.c_uint8 * 32).from_buffer_copy(input_hash)
+        check(self.ctx.h, _lib.lib().zkb_qwen_layer_prove_begin(self.h, C.c_uint32(layer_idx), ih))
+
+    def prove_end(self, cap: int = 1 << 20) -> bytes:
+        buf = (C.c_uint8 * cap)()
+        n = C.c_size_t()
+        check(self.ctx.h, _lib.lib().zkb_qwen_layer_prove_end(self.h, buf, C.c_size_t(cap), C.byref(n)))
+        return bytes(buf[:n.value])
+
+    def prove(self, layer_idx: int, input_hash: bytes) -> bytes:
+        """QwenLayerProofEF as bincode bytes; `forward` must have run."""
+        self.prove_begin(layer_idx, input_hash)
+        return self.prove_end()
+
+
+class QwenModel:
+    """A stack of layers on one GPU, one context (stream) per layer so that the independent
+    per-layer proofs overlap on the device."""
+
+    def __init__(self, device: int, configs, weights_list, silu_out, sigmoid_out):
+        self.device = device
+        self.ctxs = [Context(device) for _ in configs]
+        self.tables = (self.ctxs[0].upload(silu_out), self.ctxs[0].upload(sigmoid_out))
+        self.layers = [QwenLayer(c, cfg, w, *self.tables) for c, cfg, w in zip(self.ctxs, configs, weights_list)]
+        self.pool = ThreadPoolExecutor(max_workers=min(8, max(1, len(self.layers))))
+
+    def forward(self, x):
+        """Sequential forward through the resident layers; returns the final output."""
+        self.input_hash = hash_values(x)
+        self.layers[0].forward(x)
+        for prev, cur in zip(self.layers, self.layers[1:]):
+            cur.forward_from(prev)
+        return self.layers[-1].output()
+
+    def prove(self, layer_indices=None):
+        """Proofs of all layers, in reverse layer order as the reference collects them
+        (pipeline/prove.rs:183-188).  Enqueue from a few host threads, then collect."""
+        idx = list(range(len(self.layers))) if layer_indices is None else list(layer_indices)
+        list(self.pool.map(lambda i: self.layers[i].prove_begin(idx[i] if layer_indices else i, self.input_hash), range(len(self.layers))))
+        proofs = [l.prove_end() for l in self.layers]
+        return proofs[::-1]
+
+    def close(self):
+        self.pool.shutdown()
+        for l in self.layers:
+            l.close()
+        for t in self.tables:
+            t.free()
+        for c in self.ctxs:
+            c.close()
