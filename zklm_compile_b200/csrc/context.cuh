@@ -42,7 +42,9 @@ struct zkb_ctx {
     zkb::u32* rec_dev = nullptr;
     zkb::u32* rec_host = nullptr;        // pinned mirror
     size_t rec_cap = 0, rec_used = 0;
+    // Slots are 16-byte aligned: challenge slots are read back by kernels as EF elements (uint4 loads).
     size_t rec_alloc(size_t nwords) {
+        nwords = (nwords + 3) & ~size_t(3);
         if (rec_used + nwords > rec_cap) throw zkb::ArgFail{ZKB_E_TOO_LARGE, "proof record buffer exhausted"};
         size_t off = rec_used;
         rec_used += nwords;
