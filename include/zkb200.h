@@ -64,6 +64,11 @@ int32_t zkb_timer_stop_ms(zkb_ctx* ctx, float* ms);
  * zkb_profile_read: ms[i] = device time of launch i of the most recent sumcheck call. */
 int32_t zkb_profile_enable(zkb_ctx* ctx, int32_t on);
 int32_t zkb_profile_read(zkb_ctx* ctx, float* ms, size_t cap, size_t* n);
+/* While profiling is enabled the bandwidth-bound matrix kernels are bracketed by CUDA events.
+ * zkb_profile_ranges sums them per tag since the last call: ms[tag], bytes[tag] (algorithmic
+ * bytes = 4 m n per launch), count[tag]; arrays of ZKB_RANGE_COUNT entries.  Synchronises. */
+enum { ZKB_RANGE_FOLD_EQ_MATVEC = 0, ZKB_RANGE_MATVEC_FORWARD = 1, ZKB_RANGE_COUNT = 2 };
+int32_t zkb_profile_ranges(zkb_ctx* ctx, double* ms, double* bytes, uint64_t* count);
 /* Number of kernels this context has launched since creation. */
 uint64_t zkb_launch_count(const zkb_ctx* ctx);
 

@@ -31,6 +31,10 @@ def build(verbose: bool = False) -> str:
 
 _lib = None
 
+# The per-layer proofs run on one CUDA stream each; the default of 8 hardware work queues would
+# make streams share a queue and serialise behind each other.  Must be set before CUDA starts.
+os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
+
 
 def lib():
     global _lib

@@ -70,6 +70,27 @@ struct zkb_ctx {
     std::vector<cudaEvent_t> prof_events;
     size_t prof_used = 0;
 
+    // tagged event pairs around the bandwidth-bound kernels (only when profiling is on)
+    struct Range { int tag; double bytes; cudaEvent_t a, b; };
+    std::vector<Range> ranges;
+    std::vector<cudaEvent_t> ev_pool;
+    cudaEvent_t ev_get() {
+        if (!ev_pool.empty()) { cudaEvent_t e = ev_pool.back(); ev_pool.pop_back(); return e; }
+        cudaEvent_t e;
+        ZKB_CUDA(cudaEventCreate(&e));
+        return e;
+    }
+    int range_begin(int tag, double bytes) {
+        if (!profile) return -1;
+        Range r{tag, bytes, ev_get(), ev_get()};
+        ZKB_CUDA(cudaEventRecord(r.a, stream));
+        ranges.push_back(r);
+        return (int)ranges.size() - 1;
+    }
+    void range_end(int id) {
+        if (id >= 0) ZKB_CUDA(cudaEventRecord(ranges[id].b, stream));
+    }
+
     void use() { ZKB_CUDA(cudaSetDevice(device)); }
 
     void* scratch(size_t bytes) {

@@ -141,7 +141,9 @@ inline MatmulRec prove_matmul_succinct_ef(zkb_ctx* c, TrState* tr, const u32* W,
         rows_per = (rows_per + FOLD_ROWS_TILE - 1) / FOLD_ROWS_TILE * FOLD_ROWS_TILE;
         u32 row_ctas = (u32)((m + rows_per - 1) / rows_per);
         dim3 grid(col_ctas, row_ctas);
+        int rg = c->range_begin(ZKB_RANGE_FOLD_EQ_MATVEC, 4.0 * m * n);
         fold_eq_matvec_kernel<4><<<grid, 128, 0, c->stream>>>(W, m, n, (const u32*)eq_r, rows_per, acc);
+        c->range_end(rg);
         ZKB_LAUNCHED(c);
         fold_finalize_kernel<4><<<grid_for(c, n_pad * 4), 256, 0, c->stream>>>(acc, n, n_pad, (u32*)w_partial);
         ZKB_LAUNCHED(c);

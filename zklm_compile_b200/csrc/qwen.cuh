@@ -53,7 +53,9 @@ inline void matvec_forward(zkb_ctx* c, const u32* W, const u32* x, u32 m, u32 n,
     if (m_pad > m) ZKB_CUDA(cudaMemsetAsync(y + m, 0, (size_t)(m_pad - m) * 4, c->stream));
     size_t warps = m;
     int grid = grid_for(c, warps * 32, 256, 8);
+    int rg = c->range_begin(ZKB_RANGE_MATVEC_FORWARD, 4.0 * m * n);
     matvec_forward_kernel<<<grid, 256, 0, c->stream>>>(W, x, m, n, y);
+    c->range_end(rg);
     ZKB_LAUNCHED(c);
 }
 

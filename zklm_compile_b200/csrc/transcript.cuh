@@ -34,25 +34,76 @@ __constant__ u32 SHA_K[64] = {
 __device__ __forceinline__ u32 rotr32(u32 x, int n) { return __funnelshift_r(x, x, n); }
 __device__ __forceinline__ u32 bswap32(u32 x) { return __byte_perm(x, 0, 0x0123); }
 
-// One SHA-256 compression of the 16 big-endian words in w[] into h[].
-__device__ __noinline__ void sha256_compress(u32* h, u32* w) {
-    u32 a = h[0], b = h[1], c = h[2], d = h[3], e = h[4], f = h[5], g = h[6], hh = h[7];
-#pragma unroll
-    for (int i = 0; i < 64; i++) {
-        if (i >= 16) {
-            u32 w15 = w[(i + 1) & 15], w2 = w[(i + 14) & 15];
-            u32 s0 = rotr32(w15, 7) ^ rotr32(w15, 18) ^ (w15 >> 3);
-            u32 s1 = rotr32(w2, 17) ^ rotr32(w2, 19) ^ (w2 >> 10);
-            w[i & 15] = w[i & 15] + s0 + w[(i + 9) & 15] + s1;
-        }
-        u32 S1 = rotr32(e, 6) ^ rotr32(e, 11) ^ rotr32(e, 25);
-        u32 ch = (e & f) ^ (~e & g);
-        u32 t1 = hh + S1 + ch + SHA_K[i] + w[i & 15];
-        u32 S0 = rotr32(a, 2) ^ rotr32(a, 13) ^ rotr32(a, 22);
-        u32 mj = (a & b) ^ (a & c) ^ (b & c);
-        hh = g; g = f; f = e; e = d + t1; d = c; c = b; b = a; a = t1 + S0 + mj;
+// One SHA-256 compression.  The chaining value travels in registers (by value), the message
+// block is read from 16 little-endian words of shared memory and byte-swapped on the fly; the
+// 64 rounds are fully unrolled with the working variables renamed instead of moved, and the
+// message schedule is kept in a 16-register window.  One thread runs this; the rounds are a
+// strict dependency chain, so the remaining lever is instruction count, not parallelism.
+struct Sha8 { u32 v[8]; };
+
+#define ZKB_SHA_RND(a, b, c, d, e, f, g, h, kw)                                   \
+    {                                                                             \
+        u32 t1 = h + (rotr32(e, 6) ^ rotr32(e, 11) ^ rotr32(e, 25)) + ((e & f) ^ (~e & g)) + (kw); \
+        u32 t2 = (rotr32(a, 2) ^ rotr32(a, 13) ^ rotr32(a, 22)) + ((a & b) ^ (a & c) ^ (b & c));   \
+        d += t1;                                                                  \
+        h = t1 + t2;                                                              \
     }
-    h[0] += a; h[1] += b; h[2] += c; h[3] += d; h[4] += e; h[5] += f; h[6] += g; h[7] += hh;
+#define ZKB_SHA_SCHED(i) \
+    (w[(i) & 15] += (rotr32(w[((i) + 1) & 15], 7) ^ rotr32(w[((i) + 1) & 15], 18) ^ (w[((i) + 1) & 15] >> 3)) + w[((i) + 9) & 15] + \
+                    (rotr32(w[((i) + 14) & 15], 17) ^ rotr32(w[((i) + 14) & 15], 19) ^ (w[((i) + 14) & 15] >> 10)))
+
+__device__ __noinline__ Sha8 sha256_compress(Sha8 hin, const u32* __restrict__ blk) {
+    u32 w[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) w[i] = bswap32(blk[i]);
+    u32 a = hin.v[0], b = hin.v[1], c = hin.v[2], d = hin.v[3], e = hin.v[4], f = hin.v[5], g = hin.v[6], h = hin.v[7];
+#pragma unroll
+    for (int i = 0; i < 64; i += 8) {
+        if (i >= 16) { ZKB_SHA_SCHED(i); }     ZKB_SHA_RND(a, b, c, d, e, f, g, h, SHA_K[i] + w[i & 15]);
+        if (i >= 16) { ZKB_SHA_SCHED(i + 1); } ZKB_SHA_RND(h, a, b, c, d, e, f, g, SHA_K[i + 1] + w[(i + 1) & 15]);
+        if (i >= 16) { ZKB_SHA_SCHED(i + 2); } ZKB_SHA_RND(g, h, a, b, c, d, e, f, SHA_K[i + 2] + w[(i + 2) & 15]);
+        if (i >= 16) { ZKB_SHA_SCHED(i + 3); } ZKB_SHA_RND(f, g, h, a, b, c, d, e, SHA_K[i + 3] + w[(i + 3) & 15]);
+        if (i >= 16) { ZKB_SHA_SCHED(i + 4); } ZKB_SHA_RND(e, f, g, h, a, b, c, d, SHA_K[i + 4] + w[(i + 4) & 15]);
+        if (i >= 16) { ZKB_SHA_SCHED(i + 5); } ZKB_SHA_RND(d, e, f, g, h, a, b, c, SHA_K[i + 5] + w[(i + 5) & 15]);
+        if (i >= 16) { ZKB_SHA_SCHED(i + 6); } ZKB_SHA_RND(c, d, e, f, g, h, a, b, SHA_K[i + 6] + w[(i + 6) & 15]);
+        if (i >= 16) { ZKB_SHA_SCHED(i + 7); } ZKB_SHA_RND(b, c, d, e, f, g, h, a, SHA_K[i + 7] + w[(i + 7) & 15]);
+    }
+    Sha8 o;
+    o.v[0] = hin.v[0] + a; o.v[1] = hin.v[1] + b; o.v[2] = hin.v[2] + c; o.v[3] = hin.v[3] + d;
+    o.v[4] = hin.v[4] + e; o.v[5] = hin.v[5] + f; o.v[6] = hin.v[6] + g; o.v[7] = hin.v[7] + h;
+    return o;
+}
+
+// The 64 rounds alone, with K[t] + W[t] read from shared memory.  The message schedule of a
+// block depends only on the block, not on the chaining value, so when many known blocks are
+// absorbed in a row the lanes of a warp expand 32 schedules side by side and one lane then runs
+// only the (inherently serial) rounds.
+constexpr int SHA_KW_STRIDE = 65;    // padded so 32 lanes writing their own row do not share a bank
+__device__ __noinline__ Sha8 sha256_rounds(Sha8 hin, const u32* __restrict__ kw) {
+    u32 a = hin.v[0], b = hin.v[1], c = hin.v[2], d = hin.v[3], e = hin.v[4], f = hin.v[5], g = hin.v[6], h = hin.v[7];
+#pragma unroll
+    for (int i = 0; i < 64; i += 8) {
+        ZKB_SHA_RND(a, b, c, d, e, f, g, h, kw[i]);
+        ZKB_SHA_RND(h, a, b, c, d, e, f, g, kw[i + 1]);
+        ZKB_SHA_RND(g, h, a, b, c, d, e, f, kw[i + 2]);
+        ZKB_SHA_RND(f, g, h, a, b, c, d, e, kw[i + 3]);
+        ZKB_SHA_RND(e, f, g, h, a, b, c, d, kw[i + 4]);
+        ZKB_SHA_RND(d, e, f, g, h, a, b, c, kw[i + 5]);
+        ZKB_SHA_RND(c, d, e, f, g, h, a, b, kw[i + 6]);
+        ZKB_SHA_RND(b, c, d, e, f, g, h, a, kw[i + 7]);
+    }
+    Sha8 o;
+    o.v[0] = hin.v[0] + a; o.v[1] = hin.v[1] + b; o.v[2] = hin.v[2] + c; o.v[3] = hin.v[3] + d;
+    o.v[4] = hin.v[4] + e; o.v[5] = hin.v[5] + f; o.v[6] = hin.v[6] + g; o.v[7] = hin.v[7] + h;
+    return o;
+}
+// Lane-local: expand the schedule of one block (16 big-endian words) into K + W.
+__device__ __forceinline__ void sha256_expand_kw(const u32* __restrict__ blk_be, u32* kw) {
+    u32 w[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) { w[i] = blk_be[i]; kw[i] = SHA_K[i] + w[i]; }
+#pragma unroll
+    for (int i = 16; i < 64; i++) { ZKB_SHA_SCHED(i); kw[i] = SHA_K[i] + w[i & 15]; }
 }
 
 // Working copy used by the single thread that advances the transcript.  `buf` points to 64
@@ -90,11 +141,12 @@ __device__ __forceinline__ void tr_store(const Tr& t, TrState* g) {
     for (int i = 0; i < 16; i++) dst[i] = src[i];
 }
 __device__ __forceinline__ void tr_flush_block(Tr& t) {
-    u32 w[16];
-    const u32* b = reinterpret_cast<const u32*>(t.buf);
+    Sha8 h;
 #pragma unroll
-    for (int i = 0; i < 16; i++) w[i] = bswap32(b[i]);
-    sha256_compress(t.h, w);
+    for (int i = 0; i < 8; i++) h.v[i] = t.h[i];
+    h = sha256_compress(h, reinterpret_cast<const u32*>(t.buf));
+#pragma unroll
+    for (int i = 0; i < 8; i++) t.h[i] = h.v[i];
     t.buflen = 0;
 }
 __device__ __forceinline__ void tr_absorb_byte(Tr& t, unsigned char c) {
@@ -167,5 +219,50 @@ __device__ __forceinline__ Fe tr_squeeze_fe(Tr& t) {
 }
 __device__ __forceinline__ void tr_squeeze_el(Tr& t, Fp& r) { r.v = tr_squeeze(t); }
 __device__ __forceinline__ void tr_squeeze_el(Tr& t, Fe& r) { r = tr_squeeze_fe(t); }
+
+// Warp-cooperative absorb of `total` u32 words produced by load(g), g in [0, total) (any lane may
+// call load).  `tr` is meaningful in lane 0 only; tile (512 words) and kw (32 * SHA_KW_STRIDE
+// words) are shared-memory scratch.  Must be called by all 32 lanes of one warp.
+template <class Load>
+__device__ __forceinline__ void tr_absorb_stream_warp(Tr& tr, u32 total, Load load, u32* tile, u32* kw) {
+    const int lane = threadIdx.x & 31;
+    __syncwarp();                      // lane 0's earlier writes to the stream buffer become visible
+    const u32 buflen = __shfl_sync(0xffffffffu, tr.buflen, 0);
+    u32* bufw = reinterpret_cast<u32*>(__shfl_sync(0xffffffffu, (unsigned long long)tr.buf, 0));
+    if (buflen & 3) {                  // byte-misaligned stream: plain path
+        for (u32 base = 0; base < total; base += 512) {
+            u32 m = total - base < 512 ? total - base : 512;
+            for (u32 i = lane; i < m; i += 32) tile[i] = load(base + i);
+            __syncwarp();
+            if (lane == 0) for (u32 i = 0; i < m; i++) tr_absorb_u32(tr, tile[i]);
+            __syncwarp();
+        }
+        return;
+    }
+    u32 have = buflen >> 2, pos = 0;
+    while (have + (total - pos) >= 16) {
+        u32 nb = (have + (total - pos)) / 16;
+        if (nb > 32) nb = 32;
+        for (u32 j = lane; j < nb * 16; j += 32) tile[j] = bswap32(j < have ? bufw[j] : load(pos + j - have));
+        __syncwarp();
+        if ((u32)lane < nb) sha256_expand_kw(tile + lane * 16, kw + lane * SHA_KW_STRIDE);
+        __syncwarp();
+        if (lane == 0) {
+            Sha8 h;
+#pragma unroll
+            for (int i = 0; i < 8; i++) h.v[i] = tr.h[i];
+            for (u32 b = 0; b < nb; b++) h = sha256_rounds(h, kw + b * SHA_KW_STRIDE);
+#pragma unroll
+            for (int i = 0; i < 8; i++) tr.h[i] = h.v[i];
+        }
+        __syncwarp();
+        pos += nb * 16 - have;
+        have = 0;
+    }
+    const u32 rest = total - pos;
+    for (u32 j = lane; j < rest; j += 32) bufw[have + j] = load(pos + j);
+    __syncwarp();
+    if (lane == 0) { tr.buflen = (have + rest) * 4; tr.total += (u64)total * 4; }
+}
 
 }  // namespace zkb

@@ -25,20 +25,16 @@ __global__ void tr_absorb_bytes_kernel(TrState* st, ByteChunk c, u32 n) {
     tr_absorb_bytes(tr, c.b, n);
     tr_store(tr, st);
 }
-// One warp: lanes stage 512-word tiles into shared memory, lane 0 runs the hash chain.
-__global__ void tr_absorb_words_kernel(TrState* st, const u32* __restrict__ v, size_t n) {
+// One warp: lanes expand the message schedules, lane 0 runs the hash chain.
+__global__ void __launch_bounds__(32) tr_absorb_words_kernel(TrState* st, const u32* __restrict__ v, size_t n) {
     __shared__ __align__(16) unsigned char trbuf[64];
     __shared__ u32 tile[512];
+    __shared__ u32 kw[32 * SHA_KW_STRIDE];
     Tr tr;
+    tr.buf = trbuf; tr.buflen = 0; tr.total = 0;
     if (threadIdx.x == 0) tr_load(tr, st, trbuf);
-    for (size_t base = 0; base < n; base += 512) {
-        size_t m = n - base < 512 ? n - base : 512;
-        for (size_t i = threadIdx.x; i < m; i += blockDim.x) tile[i] = v[base + i];
-        __syncwarp();
-        if (threadIdx.x == 0)
-            for (size_t i = 0; i < m; i++) tr_absorb_u32(tr, tile[i]);
-        __syncwarp();
-    }
+    __syncwarp();
+    tr_absorb_stream_warp(tr, (u32)n, [=](u32 g) -> u32 { return v[g]; }, tile, kw);
     if (threadIdx.x == 0) tr_store(tr, st);
 }
 __global__ void tr_squeeze_kernel(TrState* st, u32* out, u32 count) {
@@ -77,9 +73,12 @@ struct TrScript {
 __global__ void __launch_bounds__(32) tr_script_kernel(TrState* st, TrScript sc) {
     __shared__ __align__(16) unsigned char trbuf[64];
     __shared__ u32 tile[512];
+    __shared__ u32 kw[32 * SHA_KW_STRIDE];
     const int lane = threadIdx.x;
     Tr tr;
+    tr.buf = trbuf; tr.buflen = 0; tr.total = 0;
     if (lane == 0) tr_load(tr, st, trbuf);
+    __syncwarp();
     for (u32 o = 0; o < sc.nops; o++) {
         const TrOp& op = sc.ops[o];
         if (op.kind == TROP_BYTES) {
@@ -94,20 +93,14 @@ __global__ void __launch_bounds__(32) tr_script_kernel(TrState* st, TrScript sc)
         } else {
             // streamed absorbs: total logical words
             u32 total = op.kind == TROP_WORDS_DEV ? op.pad : (op.kind == TROP_PAIRS_DEV ? 2 * op.n : op.n / 4);
-            for (u32 base = 0; base < total; base += 512) {
-                u32 m = total - base < 512 ? total - base : 512;
-                for (u32 i = lane; i < m; i += 32) {
-                    u32 g = base + i, v;
-                    if (op.kind == TROP_WORDS_DEV) v = g < op.n ? op.ptr[g] : 0u;
-                    else if (op.kind == TROP_PAIRS_DEV) v = (g & 1) ? op.ptr2[g >> 1] : op.ptr[g >> 1];
-                    else v = op.ptr[g];
-                    tile[i] = v;
-                }
-                __syncwarp();
-                if (lane == 0)
-                    for (u32 i = 0; i < m; i++) tr_absorb_u32(tr, tile[i]);
-                __syncwarp();
-            }
+            const u32 kind = op.kind, n = op.n;
+            const u32* p1 = op.ptr;
+            const u32* p2 = op.ptr2;
+            tr_absorb_stream_warp(tr, total, [=](u32 g) -> u32 {
+                if (kind == TROP_WORDS_DEV) return g < n ? p1[g] : 0u;
+                if (kind == TROP_PAIRS_DEV) return (g & 1) ? p2[g >> 1] : p1[g >> 1];
+                return p1[g];
+            }, tile, kw);
         }
     }
     if (lane == 0) tr_store(tr, st);

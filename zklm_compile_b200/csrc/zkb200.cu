@@ -1,5 +1,6 @@
 // C ABI of the backend (see include/zkb200.h) and the host-side launch logic.
 #include "qwen.cuh"
+#include <cstdlib>
 #include <cstring>
 #include <new>
 
@@ -22,6 +23,8 @@ int32_t zkb_ctx_create(int32_t device, zkb_ctx** out) {
     zkb_ctx* c = new (std::nothrow) zkb_ctx();
     if (!c) return ZKB_E_CUDA;
     c->device = device;
+    // one hardware work queue per stream (up to 32), so per-layer streams do not share a queue
+    setenv("CUDA_DEVICE_MAX_CONNECTIONS", "32", 0);
     try {
         int count = 0;
         ZKB_CUDA(cudaGetDeviceCount(&count));
@@ -60,6 +63,8 @@ void zkb_ctx_destroy(zkb_ctx* c) {
     if (c->stream) cudaStreamSynchronize(c->stream);
     for (auto& ch : c->chunks) cudaFree(ch.base);
     for (auto e : c->prof_events) cudaEventDestroy(e);
+    for (auto& r : c->ranges) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
+    for (auto e : c->ev_pool) cudaEventDestroy(e);
     if (c->partials) cudaFree(c->partials);
     if (c->counter) cudaFree(c->counter);
     if (c->status) cudaFree(c->status);
@@ -106,6 +111,23 @@ int32_t zkb_profile_read(zkb_ctx* c, float* ms, size_t cap, size_t* n) {
         *n = cnt;
         for (size_t i = 0; i < cnt && i < cap; i++)
             ZKB_CUDA(cudaEventElapsedTime(ms + i, c->prof_events[i], c->prof_events[i + 1]));
+    });
+}
+
+int32_t zkb_profile_ranges(zkb_ctx* c, double* ms, double* bytes, uint64_t* count) {
+    if (!c || !ms || !bytes || !count) return ZKB_E_ARG;
+    ZKB_TRY(c, {
+        c->use();
+        ZKB_CUDA(cudaStreamSynchronize(c->stream));
+        for (int i = 0; i < ZKB_RANGE_COUNT; i++) { ms[i] = 0; bytes[i] = 0; count[i] = 0; }
+        for (auto& r : c->ranges) {
+            float t = 0;
+            ZKB_CUDA(cudaEventElapsedTime(&t, r.a, r.b));
+            if (r.tag >= 0 && r.tag < ZKB_RANGE_COUNT) { ms[r.tag] += t; bytes[r.tag] += r.bytes; count[r.tag]++; }
+            c->ev_pool.push_back(r.a);
+            c->ev_pool.push_back(r.b);
+        }
+        c->ranges.clear();
     });
 }
 

@@ -75,6 +75,14 @@ class Context:
         check(self.h, _lib.lib().zkb_profile_read(self.h, buf, C.c_size_t(256), C.byref(n)))
         return [buf[i] for i in range(min(n.value, 256))]
 
+    def profile_ranges(self):
+        """{tag: (ms, algorithmic bytes, launches)} for the bracketed matrix kernels since the last call."""
+        ms = (C.c_double * 2)()
+        by = (C.c_double * 2)()
+        cnt = (C.c_uint64 * 2)()
+        check(self.h, _lib.lib().zkb_profile_ranges(self.h, ms, by, cnt))
+        return {"fold_eq_matvec": (ms[0], by[0], cnt[0]), "matvec_forward": (ms[1], by[1], cnt[1])}
+
     @property
     def launches(self) -> int:
         return int(_lib.lib().zkb_launch_count(self.h))
