@@ -11,7 +11,7 @@
 
 namespace zkb {
 
-constexpr size_t MULTI_MIN_HALF = 2048;   // below this many pairs the single-CTA tail takes over
+constexpr size_t MULTI_MIN_HALF = 4096;   // below this many pairs the single-CTA tail takes over
 
 struct KindInfo { int nt; int in_w[3]; int w; u32 mask; u32 nstored; u32 nabs; };
 inline KindInfo kind_info(int kind) {

@@ -72,7 +72,7 @@ __global__ void __launch_bounds__(256) b3_commit_multi_kernel(B3Prefix pre, B3Mu
 __global__ void __launch_bounds__(1024) seq1_consistency_kernel(TrState* st, const u32* __restrict__ attn_out, u32 attn_len, u32 log_attn,
                                                                 const u32* __restrict__ v, u32 v_len, u32 log_v, u32 is_gqa, u32 log_kv,
                                                                 u32 log_d, u32* out2) {
-    __shared__ __align__(16) unsigned char trbuf[64];
+    __shared__ __align__(16) unsigned char trbuf[TR_SCRATCH_BYTES];
     __shared__ Fp r_s[32], rv_s[32];
     __shared__ u32 red[64];
     Tr tr;

@@ -186,7 +186,7 @@ __global__ void __launch_bounds__(256) sc_round_kernel(ScTables tb, size_t half,
     typedef typename Sel<FOLD, ChalT, SrcT>::type AccT;
     constexpr int NACC = ScTraits<KIND>::NACC, WA = Width<AccT>::W, NW = NACC * WA;
     __shared__ u32 red[32 * 16];
-    __shared__ __align__(16) unsigned char trbuf[64];
+    __shared__ __align__(16) unsigned char trbuf[TR_SCRATCH_BYTES];
     __shared__ bool is_last;
 
     ChalT r = zero_of<ChalT>();
@@ -240,7 +240,7 @@ __global__ void __launch_bounds__(SC_TAIL_THREADS) sc_tail_kernel(ScTables tb, s
     constexpr int NT = ScTraits<KIND>::NT, NACC = ScTraits<KIND>::NACC;
     constexpr int WC = Width<ChalT>::W, WS = Width<SrcT>::W;
     __shared__ u32 red[32 * 16];
-    __shared__ __align__(16) unsigned char trbuf[64];
+    __shared__ __align__(16) unsigned char trbuf[TR_SCRATCH_BYTES];
     __shared__ u32 r_sh[4];
 
     if (io.dyn_nv) { num_vars = io.dyn_nv[0]; size = size_t(1) << num_vars; }

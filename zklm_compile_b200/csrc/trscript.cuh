@@ -19,7 +19,7 @@ __global__ void tr_init_kernel(TrState* st) {
     for (int i = 0; i < 64; i++) st->buf[i] = 0;
 }
 __global__ void tr_absorb_bytes_kernel(TrState* st, ByteChunk c, u32 n) {
-    __shared__ __align__(16) unsigned char trbuf[64];
+    __shared__ __align__(16) unsigned char trbuf[TR_SCRATCH_BYTES];
     Tr tr;
     tr_load(tr, st, trbuf);
     tr_absorb_bytes(tr, c.b, n);
@@ -27,7 +27,7 @@ __global__ void tr_absorb_bytes_kernel(TrState* st, ByteChunk c, u32 n) {
 }
 // One warp: lanes expand the message schedules, lane 0 runs the hash chain.
 __global__ void __launch_bounds__(32) tr_absorb_words_kernel(TrState* st, const u32* __restrict__ v, size_t n) {
-    __shared__ __align__(16) unsigned char trbuf[64];
+    __shared__ __align__(16) unsigned char trbuf[TR_SCRATCH_BYTES];
     __shared__ u32 tile[512];
     __shared__ u32 kw[32 * SHA_KW_STRIDE];
     Tr tr;
@@ -38,7 +38,7 @@ __global__ void __launch_bounds__(32) tr_absorb_words_kernel(TrState* st, const 
     if (threadIdx.x == 0) tr_store(tr, st);
 }
 __global__ void tr_squeeze_kernel(TrState* st, u32* out, u32 count) {
-    __shared__ __align__(16) unsigned char trbuf[64];
+    __shared__ __align__(16) unsigned char trbuf[TR_SCRATCH_BYTES];
     Tr tr;
     tr_load(tr, st, trbuf);
     for (u32 i = 0; i < count; i++) out[i] = tr_squeeze(tr);
@@ -71,7 +71,7 @@ struct TrScript {
 };
 
 __global__ void __launch_bounds__(32) tr_script_kernel(TrState* st, TrScript sc) {
-    __shared__ __align__(16) unsigned char trbuf[64];
+    __shared__ __align__(16) unsigned char trbuf[TR_SCRATCH_BYTES];
     __shared__ u32 tile[512];
     __shared__ u32 kw[32 * SHA_KW_STRIDE];
     const int lane = threadIdx.x;
@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(32) tr_script_kernel(TrState* st, TrScript sc)
 // device-resident length (LogUp's number of active table entries).
 __global__ void __launch_bounds__(1024) b3_commit_kernel(B3Prefix pre, const u32* __restrict__ words, u32 n_words,
                                                          const u32* n_words_dev, u32* cvs_scratch, u32* root_out, TrState* absorb_into) {
-    __shared__ __align__(16) unsigned char trbuf[64];
+    __shared__ __align__(16) unsigned char trbuf[TR_SCRATCH_BYTES];
     if (n_words_dev) n_words = n_words_dev[0];
     b3_hash_block(pre, words, n_words, cvs_scratch);
     if (threadIdx.x == 0) {
