@@ -69,6 +69,10 @@ class QwenLayer:
         check(self.ctx.h, _lib.lib().zkb_qwen_layer_forward(self.h, a.ctypes.data_as(u32p), C.c_int32(0), y.ctypes.data_as(u32p), C.c_int32(0)))
         return y
 
+    def forward_dev(self, x: DeviceBuffer):
+        """Forward with a device-resident input vector."""
+        check(self.ctx.h, _lib.lib().zkb_qwen_layer_forward(self.h, x.ptr, C.c_int32(1), None, C.c_int32(0)))
+
     def forward_from(self, prev: "QwenLayer"):
         """Forward with the previous layer's device-resident output as input (no host copy)."""
         _lib.lib().zkb_qwen_layer_output_dev.restype = u32p
@@ -100,28 +104,45 @@ class QwenLayer:
 
 class QwenModel:
     """A stack of layers on one GPU, one context (stream) per layer so that the independent
-    per-layer proofs overlap on the device."""
+    per-layer proofs overlap on the device.  `weights` is a list of weight dicts or a callable
+    i -> dict (so that only one layer's host copy is alive at a time); `first_layer` is the
+    global index of this stack's first layer when a model is sharded over several GPUs."""
 
-    def __init__(self, device: int, configs, weights_list, silu_out, sigmoid_out):
+    def __init__(self, device: int, configs, weights, silu_out, sigmoid_out, first_layer: int = 0):
         self.device = device
+        self.first_layer = first_layer
         self.ctxs = [Context(device) for _ in configs]
         self.tables = (self.ctxs[0].upload(silu_out), self.ctxs[0].upload(sigmoid_out))
-        self.layers = [QwenLayer(c, cfg, w, *self.tables) for c, cfg, w in zip(self.ctxs, configs, weights_list)]
+        self.layers = []
+        for i, (c, cfg) in enumerate(zip(self.ctxs, configs)):
+            w = weights(i) if callable(weights) else weights[i]
+            self.layers.append(QwenLayer(c, cfg, w, *self.tables))
+            del w
         self.pool = ThreadPoolExecutor(max_workers=min(8, max(1, len(self.layers))))
+        self.input_hash = bytes(32)
 
-    def forward(self, x):
-        """Sequential forward through the resident layers; returns the final output."""
-        self.input_hash = hash_values(x)
-        self.layers[0].forward(x)
+    def forward(self, x, input_hash: bytes = None):
+        """Sequential forward through the resident layers.  x: host vector or DeviceBuffer.
+        `input_hash` is the hash of the *model* input (defaults to hash_values(x))."""
+        if isinstance(x, DeviceBuffer):
+            if input_hash is None:
+                raise ValueError("input_hash is required with a device-resident input")
+            self.input_hash = input_hash
+            self.layers[0].forward_dev(x)
+        else:
+            self.input_hash = input_hash if input_hash is not None else hash_values(x)
+            self.layers[0].forward(x)
         for prev, cur in zip(self.layers, self.layers[1:]):
             cur.forward_from(prev)
+
+    def output(self) -> np.ndarray:
         return self.layers[-1].output()
 
-    def prove(self, layer_indices=None):
-        """Proofs of all layers, in reverse layer order as the reference collects them
-        (pipeline/prove.rs:183-188).  Enqueue from a few host threads, then collect."""
-        idx = list(range(len(self.layers))) if layer_indices is None else list(layer_indices)
-        list(self.pool.map(lambda i: self.layers[i].prove_begin(idx[i] if layer_indices else i, self.input_hash), range(len(self.layers))))
+    def prove(self):
+        """Proofs of this stack's layers, in reverse layer order as the reference collects them
+        (pipeline/prove.rs:183-188).  Enqueued from a few host threads, then collected."""
+        n = len(self.layers)
+        list(self.pool.map(lambda i: self.layers[i].prove_begin(self.first_layer + i, self.input_hash), range(n)))
         proofs = [l.prove_end() for l in self.layers]
         return proofs[::-1]
 
