@@ -265,7 +265,9 @@ def run_qwen(zk, args, rank, world, local, dist, barrier, max_over_ranks):
 
     def step(host_input):
         """forward (activation hops rank to rank) + prove my layers + gather on rank 0."""
-        if model:
+        if model and world == 1:
+            proofs = model.forward_and_prove(x_pinned if host_input else x_dev, ih)
+        elif model:
             if rank == 0:
                 model.forward(x_pinned if host_input else x_dev, ih)
             else:

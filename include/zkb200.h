@@ -153,6 +153,11 @@ void zkb_qwen_layer_destroy(zkb_qwen_layer* layer);
 int32_t zkb_qwen_layer_commitments(zkb_qwen_layer* layer, uint8_t roots[256]);
 /* qwen_forward_indexed                                                  transformer/qwen.rs:211-325 */
 int32_t zkb_qwen_layer_forward(zkb_qwen_layer* layer, const uint32_t* x, int32_t x_on_device, uint32_t* y, int32_t y_on_device);
+/* Same forward, fully asynchronous, for a chain of layers that live on different contexts:
+ * with prev != NULL the input is prev's device-resident output and this layer's stream waits
+ * for prev's forward through a CUDA event (prev's forward must already have been issued);
+ * with prev == NULL the input is x.  Errors surface at zkb_qwen_layer_prove_end. */
+int32_t zkb_qwen_layer_forward_async(zkb_qwen_layer* layer, zkb_qwen_layer* prev, const uint32_t* x, int32_t x_on_device);
 const uint32_t* zkb_qwen_layer_output_dev(const zkb_qwen_layer* layer);
 /* prove_qwen_layer_precommitted_ef on a fresh transcript "qwen-layer-{idx}" || input_hash
  * (transformer/qwen.rs:795-912, pipeline/prove.rs:166-168) -> QwenLayerProofEF bincode.

@@ -203,4 +203,7 @@ def test_qwen_model_two_layers_reverse_order(ctx):
         exp.append(pr)
     assert y.tolist() == cur.tolist()
     assert proofs == exp[::-1]
+    # the overlapped path (forward of layer i+1 behind an event, proofs enqueued right away) gives the same bytes
+    assert model.forward_and_prove(x) == exp[::-1]
+    assert model.forward_and_prove(model.ctxs[0].upload(x), ih) == exp[::-1]
     model.close()

@@ -29,6 +29,7 @@ int32_t zkb_qwen_layer_create(zkb_ctx* c, const uint64_t dims[7], const uint32_t
             ZKB_CUDA(cudaMemcpyAsync(L->w[i], weights[i], lens[i] * 4, cudaMemcpyHostToDevice, c->stream));
         }
         // commit_qwen_layer (qwen.rs:148-161): blake3 of each unpadded matrix
+        ZKB_CUDA(cudaEventCreateWithFlags(&L->fwd_done, cudaEventDisableTiming));
         ZKB_CUDA(cudaMalloc(&L->roots_dev, 64 * 4));
         static const int widx[8] = {W_Q, W_K, W_V, W_O, W_GPROJ, W_GATE, W_UP, W_DOWN};
         for (int i = 0; i < 8; i++) {
@@ -72,6 +73,7 @@ void zkb_qwen_layer_destroy(zkb_qwen_layer* L) {
         cudaStreamSynchronize(L->ctx->stream);
     }
     for (int i = 0; i < W_COUNT; i++) if (L->w[i]) cudaFree(L->w[i]);
+    if (L->fwd_done) cudaEventDestroy(L->fwd_done);
     if (L->roots_dev) cudaFree(L->roots_dev);
     if (L->trace_block) cudaFree(L->trace_block);
     delete L->pending;
@@ -100,6 +102,29 @@ int32_t zkb_qwen_layer_forward(zkb_qwen_layer* L, const uint32_t* x, int32_t x_o
         if (rc) return rc;
     });
 }
+// Asynchronous forward for a chain of layers on different contexts: the input is the previous
+// layer's device-resident output (prev != NULL; this layer's stream waits for prev's forward
+// through an event, the host does not) or x (host or device, prev == NULL).  Nothing is waited
+// for and no status is read; errors of the forward pass surface at zkb_qwen_layer_prove_end.
+// The caller must have issued prev's forward before this call.
+int32_t zkb_qwen_layer_forward_async(zkb_qwen_layer* L, zkb_qwen_layer* prev, const uint32_t* x, int32_t x_on_device) {
+    if (!L || (!prev && !x)) return ZKB_E_ARG;
+    zkb_ctx* c = L->ctx;
+    ZKB_TRY(c, {
+        c->use();
+        clear_status(c);
+        const size_t bytes = (size_t)L->dm.d_model * 4;
+        if (prev) {
+            if (prev->dm.d_model != L->dm.d_model) throw ArgFail{ZKB_E_ARG, "layer widths differ"};
+            ZKB_CUDA(cudaStreamWaitEvent(c->stream, prev->fwd_done, 0));
+            ZKB_CUDA(cudaMemcpyAsync(L->x, prev->out, bytes, cudaMemcpyDeviceToDevice, c->stream));
+        } else {
+            ZKB_CUDA(cudaMemcpyAsync(L->x, x, bytes, x_on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, c->stream));
+        }
+        qwen_forward(L);
+        ZKB_CUDA(cudaEventRecord(L->fwd_done, c->stream));
+    });
+}
 // Device address of the layer output (d_model words), so the next layer can read it in place.
 const uint32_t* zkb_qwen_layer_output_dev(const zkb_qwen_layer* L) { return L ? L->out : nullptr; }
 
@@ -109,7 +134,6 @@ int32_t zkb_qwen_layer_prove_begin(zkb_qwen_layer* L, uint32_t layer_idx, const 
     zkb_ctx* c = L->ctx;
     ZKB_TRY(c, {
         c->use();
-        clear_status(c);
         qwen_prove_enqueue(L, layer_idx, input_hash);
     });
 }

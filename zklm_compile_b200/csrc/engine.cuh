@@ -8,6 +8,7 @@
 #include "logup.cuh"
 #include "forward.cuh"
 #include <cstring>
+#include <type_traits>
 
 namespace zkb {
 
@@ -67,10 +68,20 @@ void run_sumcheck(zkb_ctx* c, ScTables tb, u32 num_vars, ScIO io, bool dynamic) 
         if (half < MULTI_MIN_HALF) break;
         size_t want = (half + 255) / 256;
         int grid = (int)(want < (size_t)max_grid ? want : (size_t)max_grid);
+        // base-field tables of a product sumcheck: vectorised launches (4 pair indices per thread)
+        constexpr bool base_product_t = KIND == SC_PRODUCT && std::is_same<SrcT, Fp>::value;
+        const bool base_product = base_product_t && ((((uintptr_t)tb.src[0]) | ((uintptr_t)tb.src[1])) & 15) == 0;   // 16-byte loads
+        int vgrid = (int)(((half + 3) / 4 + 255) / 256 < (size_t)max_grid ? ((half + 3) / 4 + 255) / 256 : (size_t)max_grid);
         if (!pending) {
-            sc_round_kernel<KIND, SrcT, ChalT, false><<<grid, 256, 0, c->stream>>>(tb, half, round, io);
+            if constexpr (base_product_t) {
+                if (base_product) sc_product_base_kernel<ChalT, false><<<vgrid, 256, 0, c->stream>>>(tb, half, round, io);
+                else sc_round_kernel<KIND, SrcT, ChalT, false><<<grid, 256, 0, c->stream>>>(tb, half, round, io);
+            } else sc_round_kernel<KIND, SrcT, ChalT, false><<<grid, 256, 0, c->stream>>>(tb, half, round, io);
         } else if (in_src) {
-            sc_round_kernel<KIND, SrcT, ChalT, true><<<grid, 256, 0, c->stream>>>(tb, half, round, io);
+            if constexpr (base_product_t && std::is_same<ChalT, Fe>::value) {
+                if (base_product) sc_product_base_kernel<Fe, true><<<vgrid, 256, 0, c->stream>>>(tb, half, round, io);
+                else sc_round_kernel<KIND, SrcT, ChalT, true><<<grid, 256, 0, c->stream>>>(tb, half, round, io);
+            } else sc_round_kernel<KIND, SrcT, ChalT, true><<<grid, 256, 0, c->stream>>>(tb, half, round, io);
             for (int t = 0; t < 3; t++) tb.src[t] = tb.dst[t];
             in_src = false;
             size /= 2;

@@ -22,25 +22,21 @@ struct Fp { u32 v; };
 struct Fe { u32 x, y, z, w; };
 
 // ---- base field ---------------------------------------------------------------------------
-ZKB_HD u32 add31(u32 a, u32 b) { u32 s = a + b; return s >= ZKB_P ? s - ZKB_P : s; }
-ZKB_HD u32 sub31(u32 a, u32 b) { return a >= b ? a - b : a + ZKB_P - b; }
+// Reductions use 2^31 == 1 and 2^32 == 2 (mod p) and an unsigned-min for the final conditional
+// subtraction; on the GPU the multiply pipe is the idle one, so 2*hi + lo is one multiply-add.
+ZKB_HD u32 umin32(u32 a, u32 b) { return a < b ? a : b; }
+ZKB_HD u32 add31(u32 a, u32 b) { u32 s = a + b; return umin32(s, s - ZKB_P); }          // a, b < p
+ZKB_HD u32 sub31(u32 a, u32 b) { u32 d = a - b; return umin32(d, d + ZKB_P); }          // a, b < p
 ZKB_HD u32 neg31(u32 a) { return a ? ZKB_P - a : 0u; }
 // Any 64-bit value -> canonical.
 ZKB_HD u32 red64(u64 v) {
-    u32 lo = (u32)v & ZKB_P;
-    u32 mid = (u32)(v >> 31) & ZKB_P;
-    u32 hi = (u32)(v >> 62);
-    u32 s = lo + mid;                       // <= 2^32 - 2
-    s = (s & ZKB_P) + (s >> 31) + hi;       // <= 2^31 + 3
-    return s >= ZKB_P ? s - ZKB_P : s;
+    u64 t = (u64)(u32)(v >> 32) * 2u + (u32)v;          // == v (mod p), < 2^33 + 2^32
+    u32 tl = (u32)t, th = (u32)(t >> 32);               // th <= 2
+    u32 s = (tl & ZKB_P) + (tl >> 31) + 2u * th;        // < 2^31 + 5
+    return umin32(s, s - ZKB_P);
 }
-// Product of two canonical values (< 2^62).
-ZKB_HD u32 mul31(u32 a, u32 b) {
-    u64 p = (u64)a * b;
-    u32 s = ((u32)p & ZKB_P) + (u32)(p >> 31);   // < 2^32
-    s = (s & ZKB_P) + (s >> 31);
-    return s >= ZKB_P ? s - ZKB_P : s;
-}
+// Product of two values below 2^32 whose product is below 2^63 (canonical inputs: < 2^62).
+ZKB_HD u32 mul31(u32 a, u32 b) { return red64((u64)a * b); }
 ZKB_HD u32 pow31(u32 a, u32 e) {
     u32 r = 1;
     while (e) { if (e & 1) r = mul31(r, a); a = mul31(a, a); e >>= 1; }

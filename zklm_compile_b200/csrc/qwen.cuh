@@ -40,6 +40,7 @@ struct zkb_qwen_layer {
              *swiglu = nullptr, *down = nullptr, *out = nullptr, *n1_scalars = nullptr, *n2_scalars = nullptr;
     zkb::u32* trace_block = nullptr;
     bool have_trace = false;
+    cudaEvent_t fwd_done = nullptr;      // recorded after the forward kernels; the next layer's stream waits on it
     // pending proof
     struct Pending;
     Pending* pending = nullptr;

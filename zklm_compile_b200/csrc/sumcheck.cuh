@@ -230,6 +230,120 @@ __global__ void __launch_bounds__(256) sc_round_kernel(ScTables tb, size_t half,
     }
 }
 
+// ---- product sumcheck over base-field tables: the two bandwidth-critical launches --------------
+// Round 0 (nothing to fold) and round 1 (fold the first EF challenge into base-field tables)
+// of PRODUCT sumchecks whose inputs are M31 vectors.  Four consecutive pair indices per thread
+// (16-byte loads), products accumulated unreduced in 64 bits.
+//
+// Round 1 never multiplies in EF per element.  With lo = a + r (b - a), hi = c + r (d - c) the
+// three sums are quadratics in r with base-field coefficients,
+//     sum lo_f lo_g = A0 + r A1 + r^2 A2,   A0 = sum a_f a_g, A1 = sum (a_f e_g + a_g e_f), A2 = sum e_f e_g
+// (e = b - a), likewise for hi (c, d - c) and for 2 hi - lo; the nine coefficient sums are
+// reduced like any other partial and the finishing CTA evaluates the quadratics once.
+__device__ __forceinline__ u64 fold62(u64 t) { return (u64)((u32)t & ZKB_P) + (u32)(t >> 31); }   // t < 2^63 -> < 2^33, same residue
+__device__ __forceinline__ void ld4(const void* base, size_t j, u32* o) {
+    uint4 t = *reinterpret_cast<const uint4*>(reinterpret_cast<const u32*>(base) + j);
+    o[0] = t.x; o[1] = t.y; o[2] = t.z; o[3] = t.w;
+}
+
+template <class ChalT, bool FOLD>
+__global__ void __launch_bounds__(256) sc_product_base_kernel(ScTables tb, size_t half, u32 round, ScIO io) {
+    constexpr int NACC = FOLD ? 9 : 3;
+    __shared__ u32 red[32 * 16];
+    __shared__ __align__(16) unsigned char trbuf[TR_SCRATCH_BYTES];
+    __shared__ bool is_last;
+    Fe r = fe_zero();
+    if constexpr (FOLD) from_words(r, io.chal + (size_t)(round - 1) * 4);
+
+    u64 acc[NACC];
+#pragma unroll
+    for (int k = 0; k < NACC; k++) acc[k] = 0;
+    const size_t stride = (size_t)gridDim.x * blockDim.x * 4;
+    for (size_t j = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; j < half; j += stride) {
+        if constexpr (!FOLD) {
+            u32 f0[4], f1[4], g0[4], g1[4];
+            ld4(tb.src[0], j, f0); ld4(tb.src[0], j + half, f1);
+            ld4(tb.src[1], j, g0); ld4(tb.src[1], j + half, g1);
+#pragma unroll
+            for (int v = 0; v < 4; v++) {
+                u32 f2 = sub31(add31(f1[v], f1[v]), f0[v]), g2 = sub31(add31(g1[v], g1[v]), g0[v]);
+                acc[0] += fold62((u64)f0[v] * g0[v]);
+                acc[1] += fold62((u64)f1[v] * g1[v]);
+                acc[2] += fold62((u64)f2 * g2);
+            }
+        } else {
+            u32 fa[4], fb[4], fc[4], fd[4], ga[4], gb[4], gc[4], gd[4];
+            ld4(tb.src[0], j, fa); ld4(tb.src[0], j + 2 * half, fb); ld4(tb.src[0], j + half, fc); ld4(tb.src[0], j + 3 * half, fd);
+            ld4(tb.src[1], j, ga); ld4(tb.src[1], j + 2 * half, gb); ld4(tb.src[1], j + half, gc); ld4(tb.src[1], j + 3 * half, gd);
+#pragma unroll
+            for (int v = 0; v < 4; v++) {
+                const u32 ef = sub31(fb[v], fa[v]), eg = sub31(gb[v], ga[v]);       // lo = a + r e
+                const u32 hf = sub31(fd[v], fc[v]), hg = sub31(gd[v], gc[v]);       // hi = c + r h
+                // folded tables (EF = base + r * base)
+                Fe lf = r * Fp{ef}; lf.x = add31(lf.x, fa[v]);
+                Fe lg = r * Fp{eg}; lg.x = add31(lg.x, ga[v]);
+                Fe uf = r * Fp{hf}; uf.x = add31(uf.x, fc[v]);
+                Fe ug = r * Fp{hg}; ug.x = add31(ug.x, gc[v]);
+                st_el<Fe>(tb.dst[0], j + v, lf); st_el<Fe>(tb.dst[0], j + half + v, uf);
+                st_el<Fe>(tb.dst[1], j + v, lg); st_el<Fe>(tb.dst[1], j + half + v, ug);
+                // coefficient sums
+                acc[0] += fold62((u64)fa[v] * ga[v]);
+                acc[1] += fold62((u64)fa[v] * eg + (u64)ga[v] * ef);
+                acc[2] += fold62((u64)ef * eg);
+                acc[3] += fold62((u64)fc[v] * gc[v]);
+                acc[4] += fold62((u64)fc[v] * hg + (u64)gc[v] * hf);
+                acc[5] += fold62((u64)hf * hg);
+                const u32 pf = sub31(add31(fc[v], fc[v]), fa[v]), pg = sub31(add31(gc[v], gc[v]), ga[v]);   // 2 hi - lo at r = 0
+                const u32 qf = sub31(add31(hf, hf), ef), qg = sub31(add31(hg, hg), eg);                     // its slope in r
+                acc[6] += fold62((u64)pf * pg);
+                acc[7] += fold62((u64)pf * qg + (u64)pg * qf);
+                acc[8] += fold62((u64)qf * qg);
+            }
+        }
+    }
+    u32 w[NACC];
+#pragma unroll
+    for (int k = 0; k < NACC; k++) w[k] = red64(acc[k]);
+    block_sum_words<NACC>(w, red);
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int k = 0; k < NACC; k++) io.partials[(size_t)blockIdx.x * 16 + k] = w[k];
+        __threadfence();
+        unsigned int ticket = atomicAdd(io.counter, 1u);
+        is_last = (ticket == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    u32 t[NACC];
+#pragma unroll
+    for (int k = 0; k < NACC; k++) t[k] = 0;
+    for (u32 b = threadIdx.x; b < gridDim.x; b += blockDim.x) {
+#pragma unroll
+        for (int k = 0; k < NACC; k++) t[k] = add31(t[k], __ldcg(io.partials + (size_t)b * 16 + k));
+    }
+    block_sum_words<NACC>(t, red);
+    if (threadIdx.x == 0) {
+        Tr tr;
+        tr_load(tr, io.tr, trbuf);
+        if constexpr (FOLD) {
+            const Fe r2 = r * r;
+            u32 ew[12];
+#pragma unroll
+            for (int k = 0; k < 3; k++) {
+                Fe s = r * Fp{t[3 * k + 1]} + r2 * Fp{t[3 * k + 2]};
+                s.x = add31(s.x, t[3 * k]);
+                to_words(s, ew + 4 * k);
+            }
+            sc_finish_round<SC_PRODUCT, Fe, Fe>(ew, io, round, tr);
+        } else {
+            sc_finish_round<SC_PRODUCT, Fp, ChalT>(t, io, round, tr);
+        }
+        tr_store(tr, io.tr);
+        *io.counter = 0;
+    }
+}
+
 // ---- single-CTA tail: all remaining rounds and the final evaluations -------------------------
 // Entry state: tables in tb.src (type SrcT) of `size` elements; if `pending`, the challenge
 // of round `round - 1` still has to be folded in.  Runs rounds round .. num_vars-1, then folds

@@ -79,6 +79,17 @@ class QwenLayer:
         src = _lib.lib().zkb_qwen_layer_output_dev(prev.h)
         check(self.ctx.h, _lib.lib().zkb_qwen_layer_forward(self.h, src, C.c_int32(1), None, C.c_int32(0)))
 
+    def forward_async(self, prev: "QwenLayer" = None, x=None):
+        """Enqueue the forward pass without waiting: input is `prev`'s device-resident output, or
+        `x` (host array or DeviceBuffer).  `prev.forward_async` must already have been called."""
+        if prev is not None:
+            check(self.ctx.h, _lib.lib().zkb_qwen_layer_forward_async(self.h, prev.h, None, C.c_int32(0)))
+        elif isinstance(x, DeviceBuffer):
+            check(self.ctx.h, _lib.lib().zkb_qwen_layer_forward_async(self.h, None, x.ptr, C.c_int32(1)))
+        else:
+            self._x_keep = np.ascontiguousarray(x, dtype=np.uint32)
+            check(self.ctx.h, _lib.lib().zkb_qwen_layer_forward_async(self.h, None, self._x_keep.ctypes.data_as(u32p), C.c_int32(0)))
+
     def output(self) -> np.ndarray:
         _lib.lib().zkb_qwen_layer_output_dev.restype = u32p
         src = _lib.lib().zkb_qwen_layer_output_dev(self.h)
@@ -143,6 +154,41 @@ class QwenModel:
         (pipeline/prove.rs:183-188).  Enqueued from a few host threads, then collected."""
         n = len(self.layers)
         list(self.pool.map(lambda i: self.layers[i].prove_begin(self.first_layer + i, self.input_hash), range(n)))
+        proofs = [l.prove_end() for l in self.layers]
+        return proofs[::-1]
+
+    def forward_and_prove(self, x, input_hash: bytes = None):
+        """Forward pass and all layer proofs with the two overlapped: every layer's proof is
+        enqueued right behind its own forward, the forward of the next layer only waits (on the
+        GPU) for the previous layer's forward.  Returns the proofs in reverse layer order."""
+        import threading
+        if isinstance(x, DeviceBuffer):
+            if input_hash is None:
+                raise ValueError("input_hash is required with a device-resident input")
+            self.input_hash = input_hash
+        else:
+            self.input_hash = input_hash if input_hash is not None else hash_values(x)
+        n = len(self.layers)
+        issued = [threading.Event() for _ in range(n)]
+        failed = []
+
+        def task(i):
+            try:
+                if i:
+                    issued[i - 1].wait()
+                    if failed:
+                        raise RuntimeError("an earlier layer failed")
+                    self.layers[i].forward_async(prev=self.layers[i - 1])
+                else:
+                    self.layers[0].forward_async(x=x)
+            except Exception as e:       # never leave the next layer waiting
+                failed.append(e)
+                issued[i].set()
+                raise
+            issued[i].set()
+            self.layers[i].prove_begin(self.first_layer + i, self.input_hash)
+
+        list(self.pool.map(task, range(n)))
         proofs = [l.prove_end() for l in self.layers]
         return proofs[::-1]
 
