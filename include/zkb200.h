@@ -57,6 +57,8 @@ int32_t zkb_ctx_create(int32_t device, zkb_ctx** out);
 void zkb_ctx_destroy(zkb_ctx* ctx);
 const char* zkb_last_error(const zkb_ctx* ctx);
 int32_t zkb_ctx_sync(zkb_ctx* ctx);
+/* The context's cudaStream_t (as an opaque pointer), for callers that enqueue their own work in order with the library's. */
+void* zkb_ctx_stream(zkb_ctx* ctx);
 /* CUDA-event stopwatch on the context's stream (for benchmarks; device time, not wall clock). */
 int32_t zkb_timer_start(zkb_ctx* ctx);
 int32_t zkb_timer_stop_ms(zkb_ctx* ctx, float* ms);
@@ -166,6 +168,25 @@ int32_t zkb_qwen_layer_prove_begin(zkb_qwen_layer* layer, uint32_t layer_idx, co
 int32_t zkb_qwen_layer_prove_end(zkb_qwen_layer* layer, uint8_t* out, size_t cap, size_t* len);
 int32_t zkb_qwen_layer_prove(zkb_qwen_layer* layer, uint32_t layer_idx, const uint8_t input_hash[32], uint8_t* out, size_t cap,
                              size_t* len);
+
+/* ---- allocation-free weight fold ----
+ * No counterpart in the reference: it exists for callers that must not allocate device memory
+ * once they are running (a serving loop with a fixed memory plan, a host that forbids cudaMalloc
+ * after start-up, code about to be captured into a CUDA graph).  Computes
+ *     out[j] = sum_{i<m} eq[i] * W[i][j]   for j < n,   out[j] = 0 for n <= j < n_pad
+ * with eq an array of at least m M31^4 elements (4 u32 each), W an m x n row-major u32 matrix
+ * and out n_pad M31^4 elements (n_pad = n rounded up to a power of two) - the same values as
+ * zkb_fold_eq_matvec with ef = 1 fed the eq table of r.  All three pointers are device memory
+ * of the CURRENT device; `stream` is a cudaStream_t (NULL = default stream); work is only
+ * enqueued.  It calls no cudaMalloc / cudaFree: its 64-bit accumulators live in a fixed
+ * 512 KiB device array inside the library (present on every GPU that loads it), which limits
+ * n_pad to 16384 columns - wider matrices are refused with ZKB_E_TOO_LARGE and a message in
+ * `err` (optional buffer of err_cap bytes).  The first call on each device looks up that
+ * array's device address; make that first call before starting any stream capture.  All calls
+ * share the one array: it is cleared at the start of each call, and two calls whose GPU work
+ * overlaps (different streams, different threads) corrupt each other - serialise them. */
+int32_t zkb_fold_eq_matvec_ef_noalloc(const uint32_t* W_dev, size_t m, size_t n, const uint32_t* eq_dev, uint32_t* out_dev,
+                                      void* stream, char* err, size_t err_cap);
 
 #ifdef __cplusplus
 }

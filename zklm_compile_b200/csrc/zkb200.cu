@@ -2,6 +2,7 @@
 #include "qwen.cuh"
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <new>
 
 using namespace zkb;
@@ -78,6 +79,8 @@ void zkb_ctx_destroy(zkb_ctx* c) {
 
 const char* zkb_last_error(const zkb_ctx* c) { return c ? c->err.c_str() : "null context"; }
 uint64_t zkb_launch_count(const zkb_ctx* c) { return c ? c->launches : 0; }
+
+void* zkb_ctx_stream(zkb_ctx* c) { return c ? (void*)c->stream : nullptr; }
 
 int32_t zkb_ctx_sync(zkb_ctx* c) {
     if (!c) return ZKB_E_ARG;
@@ -321,3 +324,72 @@ int32_t zkb_sumcheck_prove(zkb_ctx* c, zkb_transcript* t, int32_t kind, const ui
 
 #include "abi_protocols.cuh"
 #include "abi_layer.cuh"
+
+// =============================================================================================
+// Allocation-free weight fold
+// =============================================================================================
+// Some callers may not allocate device memory at all: code running inside a CUDA-graph capture
+// or a real-time inference loop whose memory plan was fixed at start-up, and hosts that hand
+// this library a pre-carved arena and forbid cudaMalloc afterwards (an allocation can
+// synchronise the device and fragment their pool).  For them this one entry point does the
+// weight fold  out[j] = sum_i eq[i] * W[i][j]  (EF weights eq, base-field matrix W) without
+// allocating: the 64-bit column accumulators that the regular path takes from the context's
+// arena live in the fixed array below, which every GPU that loads the library holds until exit.
+constexpr size_t ZKB_NOALLOC_MAX_COLS = 16384;                                  // padded column count
+static __device__ __align__(256) unsigned long long g_noalloc_fold_acc[ZKB_NOALLOC_MAX_COLS * 4];   // 512 KiB
+
+namespace {
+struct NoallocDev { unsigned long long* acc = nullptr; int sm_count = 0; bool ready = false; };
+NoallocDev g_noalloc_dev[64];
+std::mutex g_noalloc_mu;
+
+void set_err(char* err, size_t cap, const std::string& msg) {
+    if (err && cap) { size_t n = msg.size() < cap - 1 ? msg.size() : cap - 1; memcpy(err, msg.data(), n); err[n] = 0; }
+}
+}  // namespace
+
+extern "C" int32_t zkb_fold_eq_matvec_ef_noalloc(const uint32_t* W_dev, size_t m, size_t n, const uint32_t* eq_dev, uint32_t* out_dev,
+                                                 void* stream, char* err, size_t err_cap) {
+    if (!W_dev || !eq_dev || !out_dev || m == 0 || n == 0) { set_err(err, err_cap, "null pointer or empty matrix"); return ZKB_E_ARG; }
+    const size_t n_pad = size_t(1) << log2_ceil_u(n);
+    if (n_pad > ZKB_NOALLOC_MAX_COLS) {
+        set_err(err, err_cap, "zkb_fold_eq_matvec_ef_noalloc: " + std::to_string(n) + " columns pad to " + std::to_string(n_pad) +
+                                  ", above the fixed scratch capacity of " + std::to_string(ZKB_NOALLOC_MAX_COLS) + " columns");
+        return ZKB_E_TOO_LARGE;
+    }
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) { set_err(err, err_cap, std::string("cudaGetDevice: ") + cudaGetErrorString(e)); return ZKB_E_CUDA; }
+    NoallocDev& D = g_noalloc_dev[dev];
+    {   // first call on this device: resolve the device address of the scratch array (the name
+        // itself is only a host-side handle) with this device current
+        std::lock_guard<std::mutex> lock(g_noalloc_mu);
+        if (!D.ready) {
+            unsigned long long* p = nullptr;
+            e = cudaGetSymbolAddress((void**)&p, g_noalloc_fold_acc);
+            if (e != cudaSuccess || !p) { set_err(err, err_cap, std::string("cudaGetSymbolAddress: ") + cudaGetErrorString(e)); return ZKB_E_CUDA; }
+            int sms = 0;
+            e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+            if (e != cudaSuccess || sms <= 0) { set_err(err, err_cap, std::string("cudaDeviceGetAttribute: ") + cudaGetErrorString(e)); return ZKB_E_CUDA; }
+            D.acc = p; D.sm_count = sms; D.ready = true;
+        }
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    // the array keeps whatever the previous call left: the accumulators must start at zero
+    e = cudaMemsetAsync(D.acc, 0, n_pad * 4 * sizeof(unsigned long long), s);
+    if (e != cudaSuccess) { set_err(err, err_cap, std::string("cudaMemsetAsync: ") + cudaGetErrorString(e)); return ZKB_E_CUDA; }
+    const u32 col_ctas = (u32)((n + 511) / 512);
+    u32 want_rows = (u32)((D.sm_count * 6 + col_ctas - 1) / col_ctas);
+    if (want_rows < 1) want_rows = 1;
+    size_t rows_per = (m + want_rows - 1) / want_rows;
+    rows_per = (rows_per + FOLD_ROWS_TILE - 1) / FOLD_ROWS_TILE * FOLD_ROWS_TILE;
+    dim3 grid(col_ctas, (u32)((m + rows_per - 1) / rows_per));
+    fold_eq_matvec_kernel<4><<<grid, 128, 0, s>>>(W_dev, m, n, eq_dev, rows_per, D.acc);
+    size_t fin_items = n_pad * 4;
+    int fin_grid = (int)((fin_items + 255) / 256);
+    if (fin_grid > D.sm_count * 8) fin_grid = D.sm_count * 8;
+    fold_finalize_kernel<4><<<fin_grid, 256, 0, s>>>(D.acc, n, n_pad, out_dev);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) { set_err(err, err_cap, std::string("kernel launch: ") + cudaGetErrorString(e)); return ZKB_E_CUDA; }
+    return ZKB_OK;
+}

@@ -156,3 +156,16 @@ def prove_lookup_ef(table_outputs, inputs, outputs, transcript: Transcript) -> b
     i, pi = _a(inputs)
     o, po = _a(outputs)
     return _proof_call(ctx, _lib.lib().zkb_prove_lookup_ef, ctx.h, transcript.h, pt, C.c_size_t(t.size), pi, po, C.c_size_t(i.size))
+
+
+def fold_eq_matvec_ef_noalloc(w_dev: DeviceBuffer, m: int, n: int, eq_dev: DeviceBuffer, out_dev: DeviceBuffer, stream=None):
+    """Weight fold for callers that may not allocate GPU memory while running (fixed memory
+    plans, hosts that forbid cudaMalloc after start-up).  All three buffers are device memory
+    the caller already owns; the library's own scratch is a fixed 512 KiB array, so the padded
+    column count is limited to 16384.  Work is enqueued on `stream` (default stream if None);
+    calls must not overlap on the GPU."""
+    err = C.create_string_buffer(256)
+    fn = _lib.lib().zkb_fold_eq_matvec_ef_noalloc
+    st = fn(w_dev.ptr, C.c_size_t(m), C.c_size_t(n), eq_dev.ptr, out_dev.ptr, C.c_void_p(stream), err, C.c_size_t(256))
+    if st != 0:
+        raise _lib.ZkbError(st, err.value.decode(errors="replace"))

@@ -58,6 +58,14 @@ class Context:
     def sync(self):
         check(self.h, _lib.lib().zkb_ctx_sync(self.h))
 
+    @property
+    def stream(self) -> int:
+        """The context's cudaStream_t as an integer handle."""
+        fn = _lib.lib().zkb_ctx_stream
+        fn.restype = C.c_void_p
+        fn.argtypes = [C.c_void_p]
+        return fn(self.h) or 0
+
     def timer_start(self):
         check(self.h, _lib.lib().zkb_timer_start(self.h))
 
