@@ -70,35 +70,42 @@ __global__ void __launch_bounds__(128) fold_eq_matvec_kernel(const u32* __restri
         for (int t = threadIdx.x; t < rows * NC; t += blockDim.x) eq_s[t] = eq[rb * NC + t];
         __syncthreads();
         if (j0 < n) {
-            int since = 0;
-            for (int rr = 0; rr < rows; rr++) {
+            // three rows per step: their 16-byte loads are issued together (more bytes in flight per
+            // thread), their products (< 2^62 each) are summed unreduced and folded once
+            int rr = 0;
+            for (; rr + 3 <= rows; rr += 3) {
+                u32 w[3][4];
+#pragma unroll
+                for (int q = 0; q < 3; q++) {
+                    const u32* row = W + (rb + rr + q) * n;
+                    if (vec) {
+                        uint4 t = *reinterpret_cast<const uint4*>(row + j0);
+                        w[q][0] = t.x; w[q][1] = t.y; w[q][2] = t.z; w[q][3] = t.w;
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 4; c++) w[q][c] = (j0 + c < n) ? row[j0 + c] : 0u;
+                    }
+                }
+#pragma unroll
+                for (int k = 0; k < NC; k++) {
+                    const u32 e0 = eq_s[rr * NC + k], e1 = eq_s[(rr + 1) * NC + k], e2 = eq_s[(rr + 2) * NC + k];
+#pragma unroll
+                    for (int c = 0; c < 4; c++)
+                        a[c][k] = part_reduce(a[c][k] + (u64)e0 * w[0][c] + (u64)e1 * w[1][c] + (u64)e2 * w[2][c]);
+                }
+            }
+            for (; rr < rows; rr++) {
                 const u32* row = W + (rb + rr) * n;
                 u32 w[4];
-                if (vec) {
-                    uint4 t = *reinterpret_cast<const uint4*>(row + j0);
-                    w[0] = t.x; w[1] = t.y; w[2] = t.z; w[3] = t.w;
-                } else {
 #pragma unroll
-                    for (int c = 0; c < 4; c++) w[c] = (j0 + c < n) ? row[j0 + c] : 0u;
-                }
+                for (int c = 0; c < 4; c++) w[c] = (j0 + c < n) ? row[j0 + c] : 0u;
 #pragma unroll
                 for (int k = 0; k < NC; k++) {
                     const u32 e = eq_s[rr * NC + k];
 #pragma unroll
-                    for (int c = 0; c < 4; c++) a[c][k] += (u64)e * w[c];
-                }
-                if (++since == 3) {
-                    since = 0;
-#pragma unroll
-                    for (int c = 0; c < 4; c++)
-#pragma unroll
-                        for (int k = 0; k < NC; k++) a[c][k] = part_reduce(a[c][k]);
+                    for (int c = 0; c < 4; c++) a[c][k] = part_reduce(a[c][k] + (u64)e * w[c]);
                 }
             }
-#pragma unroll
-            for (int c = 0; c < 4; c++)
-#pragma unroll
-                for (int k = 0; k < NC; k++) a[c][k] = part_reduce(a[c][k]);
         }
     }
     if (j0 < n) {

@@ -22,17 +22,20 @@ struct Fp { u32 v; };
 struct Fe { u32 x, y, z, w; };
 
 // ---- base field ---------------------------------------------------------------------------
-// Reductions use 2^31 == 1 and 2^32 == 2 (mod p) and an unsigned-min for the final conditional
-// subtraction; on the GPU the multiply pipe is the idle one, so 2*hi + lo is one multiply-add.
+// The final conditional subtraction is an unsigned min (two instructions).  Measured on B200:
+// folding with 2^32 == 2 through a 64-bit multiply-add is slower than the three-limb fold below
+// (the wide multiply pipe is the scarce one), so reductions stay shift/mask/add.
 ZKB_HD u32 umin32(u32 a, u32 b) { return a < b ? a : b; }
 ZKB_HD u32 add31(u32 a, u32 b) { u32 s = a + b; return umin32(s, s - ZKB_P); }          // a, b < p
 ZKB_HD u32 sub31(u32 a, u32 b) { u32 d = a - b; return umin32(d, d + ZKB_P); }          // a, b < p
 ZKB_HD u32 neg31(u32 a) { return a ? ZKB_P - a : 0u; }
-// Any 64-bit value -> canonical.
+// Any 64-bit value -> canonical: v = lo + mid 2^31 + hi 2^62 == lo + mid + hi.
 ZKB_HD u32 red64(u64 v) {
-    u64 t = (u64)(u32)(v >> 32) * 2u + (u32)v;          // == v (mod p), < 2^33 + 2^32
-    u32 tl = (u32)t, th = (u32)(t >> 32);               // th <= 2
-    u32 s = (tl & ZKB_P) + (tl >> 31) + 2u * th;        // < 2^31 + 5
+    u32 lo = (u32)v & ZKB_P;
+    u32 mid = (u32)(v >> 31) & ZKB_P;
+    u32 hi = (u32)(v >> 62);
+    u32 s = lo + mid;                       // <= 2^32 - 2
+    s = (s & ZKB_P) + (s >> 31) + hi;       // <= 2^31 + 3
     return umin32(s, s - ZKB_P);
 }
 // Product of two values below 2^32 whose product is below 2^63 (canonical inputs: < 2^62).

@@ -169,11 +169,12 @@ __device__ __forceinline__ ChalT sc_finish_round(const u32* words, const ScIO& i
     if constexpr (KIND == SC_ONES) s[2] = s[1] + s[1] - s[0];
     if (io.check_zero_sum && round == 0 && !is_zero_el(s[0] + s[1])) atomicExch(io.status, 3u);
     u32* out = io.polys + (size_t)round * NABS * WC;
+    u32 msg[NABS * WC];
 #pragma unroll
-    for (int k = 0; k < NABS; k++) {
-        tr_absorb_el(tr, s[k]);
-        to_words(s[k], out + k * WC);
-    }
+    for (int k = 0; k < NABS; k++) to_words(s[k], msg + k * WC);
+    tr_absorb_words<NABS * WC>(tr, msg);
+#pragma unroll
+    for (int k = 0; k < NABS * WC; k++) out[k] = msg[k];
     ChalT r;
     tr_squeeze_el(tr, r);
     to_words(r, io.chal + (size_t)round * WC);

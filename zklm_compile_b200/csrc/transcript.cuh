@@ -180,8 +180,28 @@ __device__ __forceinline__ void tr_absorb_u32(Tr& t, u32 v) {
         tr_absorb_byte(t, (unsigned char)(v >> 24));
     }
 }
+// N words at once; when the stream is word-aligned (the common case) this is N plain stores
+// plus at most one compression, instead of N rounds of per-byte bookkeeping.
+template <int N>
+__device__ __forceinline__ void tr_absorb_words(Tr& t, const u32* w) {
+    if ((t.buflen & 3) == 0) {
+        u32* bw = reinterpret_cast<u32*>(t.buf);
+        u32 pos = t.buflen >> 2;
+#pragma unroll
+        for (int i = 0; i < N; i++) {
+            bw[pos++] = w[i];
+            if (pos == 16) { t.buflen = 64; tr_flush_block(t); pos = 0; }
+        }
+        t.buflen = pos << 2;
+        t.total += 4 * N;
+    } else {
+#pragma unroll
+        for (int i = 0; i < N; i++) tr_absorb_u32(t, w[i]);
+    }
+}
 __device__ __forceinline__ void tr_absorb_fe(Tr& t, Fe v) {
-    tr_absorb_u32(t, v.x); tr_absorb_u32(t, v.y); tr_absorb_u32(t, v.z); tr_absorb_u32(t, v.w);
+    u32 w[4] = {v.x, v.y, v.z, v.w};
+    tr_absorb_words<4>(t, w);
 }
 __device__ __forceinline__ void tr_absorb_el(Tr& t, Fp v) { tr_absorb_u32(t, v.v); }
 __device__ __forceinline__ void tr_absorb_el(Tr& t, Fe v) { tr_absorb_fe(t, v); }
@@ -216,7 +236,23 @@ __device__ __forceinline__ void tr_finalize_reseed(Tr& t, u32 digest_be[8]) {
 __device__ __forceinline__ u32 tr_squeeze(Tr& t) {
     for (int guard = 0; guard < 64; guard++) {        // all four windows rejecting has probability 2^-248
         u32 d[8];
-        tr_finalize_reseed(t, d);
+        if (t.buflen == 32 && t.total == 32) {
+            // stream == one 32-byte digest (the state right after a squeeze): the padded block is fixed
+            u32* bw = reinterpret_cast<u32*>(t.buf);
+            bw[8] = 0x00000080u;
+#pragma unroll
+            for (int i = 9; i < 15; i++) bw[i] = 0;
+            bw[15] = 0x00010000u;                     // 256 bits, big-endian
+            tr_flush_block(t);
+#pragma unroll
+            for (int i = 0; i < 8; i++) d[i] = t.h[i];
+            tr_iv(t.h);
+#pragma unroll
+            for (int i = 0; i < 8; i++) bw[i] = bswap32(d[i]);
+            t.buflen = 32;
+        } else {
+            tr_finalize_reseed(t, d);
+        }
 #pragma unroll
         for (int c = 0; c < 4; c++) {
             u64 raw = (u64)bswap32(d[2 * c]) | ((u64)bswap32(d[2 * c + 1]) << 32);
