@@ -267,21 +267,15 @@ def run_qwen(zk, args, rank, world, local, dist, barrier, max_over_ranks):
         if model and world == 1:
             proofs = model.forward_and_prove(x_pinned if host_input else x_dev, ih)
         elif model:
+            def hand_over(y):
+                if rank + 1 < world and hi < L:
+                    dist.send(torch.from_numpy(y.astype(np.int32)).to(f"cuda:{local}"), dst=rank + 1)
             if rank == 0:
-                model.forward(x_pinned if host_input else x_dev, ih)
+                proofs = model.forward_and_prove(x_pinned if host_input else x_dev, ih, on_forward_done=hand_over)
             else:
                 dist.recv(act, src=rank - 1)
                 torch.cuda.synchronize()
-                buf = zk.DeviceBuffer.__new__(zk.DeviceBuffer)
-                buf.ctx, buf.n, buf.shape = ctx0, d_model, (d_model,)
-                import ctypes
-                buf.ptr = ctypes.cast(act.data_ptr(), ctypes.POINTER(ctypes.c_uint32))
-                model.forward(buf, ih)
-                buf.ptr = None
-            if world > 1 and rank + 1 < world and hi < L:
-                y = torch.from_numpy(model.output().astype(np.int32)).to(f"cuda:{local}")
-                dist.send(y, dst=rank + 1)
-            proofs = model.prove()
+                proofs = model.forward_and_prove(act.cpu().numpy().astype(np.uint32), ih, on_forward_done=hand_over)
         else:
             proofs = []
         if world > 1:

@@ -160,6 +160,9 @@ int32_t zkb_qwen_layer_forward(zkb_qwen_layer* layer, const uint32_t* x, int32_t
  * for prev's forward through a CUDA event (prev's forward must already have been issued);
  * with prev == NULL the input is x.  Errors surface at zkb_qwen_layer_prove_end. */
 int32_t zkb_qwen_layer_forward_async(zkb_qwen_layer* layer, zkb_qwen_layer* prev, const uint32_t* x, int32_t x_on_device);
+/* Waits for the layer's (asynchronous) forward pass only - not for a proof queued behind it -
+ * and copies the layer output (d_model words) to the host. */
+int32_t zkb_qwen_layer_read_output(zkb_qwen_layer* layer, uint32_t* y_host);
 const uint32_t* zkb_qwen_layer_output_dev(const zkb_qwen_layer* layer);
 /* prove_qwen_layer_precommitted_ef on a fresh transcript "qwen-layer-{idx}" || input_hash
  * (transformer/qwen.rs:795-912, pipeline/prove.rs:166-168) -> QwenLayerProofEF bincode.

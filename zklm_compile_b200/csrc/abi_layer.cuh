@@ -125,6 +125,17 @@ int32_t zkb_qwen_layer_forward_async(zkb_qwen_layer* L, zkb_qwen_layer* prev, co
         ZKB_CUDA(cudaEventRecord(L->fwd_done, c->stream));
     });
 }
+// Wait for this layer's forward pass only (not for a proof queued behind it on the same
+// stream) and copy its output (d_model words) to host memory.
+int32_t zkb_qwen_layer_read_output(zkb_qwen_layer* L, uint32_t* y_host) {
+    if (!L || !y_host) return ZKB_E_ARG;
+    zkb_ctx* c = L->ctx;
+    ZKB_TRY(c, {
+        c->use();
+        ZKB_CUDA(cudaEventSynchronize(L->fwd_done));
+        ZKB_CUDA(cudaMemcpy(y_host, L->out, (size_t)L->dm.d_model * 4, cudaMemcpyDeviceToHost));
+    });
+}
 // Device address of the layer output (d_model words), so the next layer can read it in place.
 const uint32_t* zkb_qwen_layer_output_dev(const zkb_qwen_layer* L) { return L ? L->out : nullptr; }
 

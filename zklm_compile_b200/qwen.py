@@ -90,6 +90,12 @@ class QwenLayer:
             self._x_keep = np.ascontiguousarray(x, dtype=np.uint32)
             check(self.ctx.h, _lib.lib().zkb_qwen_layer_forward_async(self.h, None, self._x_keep.ctypes.data_as(u32p), C.c_int32(0)))
 
+    def read_output_after_forward(self) -> np.ndarray:
+        """Output of an asynchronous forward, without waiting for a proof queued behind it."""
+        y = np.zeros(self.d_model, np.uint32)
+        check(self.ctx.h, _lib.lib().zkb_qwen_layer_read_output(self.h, y.ctypes.data_as(u32p)))
+        return y
+
     def output(self) -> np.ndarray:
         _lib.lib().zkb_qwen_layer_output_dev.restype = u32p
         src = _lib.lib().zkb_qwen_layer_output_dev(self.h)
@@ -157,10 +163,12 @@ class QwenModel:
         proofs = [l.prove_end() for l in self.layers]
         return proofs[::-1]
 
-    def forward_and_prove(self, x, input_hash: bytes = None):
+    def forward_and_prove(self, x, input_hash: bytes = None, on_forward_done=None):
         """Forward pass and all layer proofs with the two overlapped: every layer's proof is
         enqueued right behind its own forward, the forward of the next layer only waits (on the
-        GPU) for the previous layer's forward.  Returns the proofs in reverse layer order."""
+        GPU) for the previous layer's forward.  Returns the proofs in reverse layer order.
+        `on_forward_done(output)` is called as soon as the last layer's forward has finished,
+        while the proofs are still running (used to hand the activation to the next GPU)."""
         import threading
         if isinstance(x, DeviceBuffer):
             if input_hash is None:
@@ -188,7 +196,13 @@ class QwenModel:
             issued[i].set()
             self.layers[i].prove_begin(self.first_layer + i, self.input_hash)
 
-        list(self.pool.map(task, range(n)))
+        futures = [self.pool.submit(task, i) for i in range(n)]
+        if on_forward_done is not None:
+            issued[n - 1].wait()
+            if not failed:
+                on_forward_done(self.layers[-1].read_output_after_forward())
+        for f in futures:
+            f.result()
         proofs = [l.prove_end() for l in self.layers]
         return proofs[::-1]
 
