@@ -1,0 +1,111 @@
+// CPU ORACLE — TEST INFRASTRUCTURE ONLY.
+//
+// C entry points for the Merkle tree and Basefold restatements (oracle/pcs.hpp,
+// oracle/basefold.hpp).  Proofs come back as bincode bytes in serde field order:
+//   BasefoldCommitment   { root: [u8;16], num_coeffs: u64, log_n: u64 }                      basefold.rs:39-47
+//   BasefoldOpeningProof { fold_roots: Vec<[u8;16]>, fold_queries: Vec<FoldLevelQueries>,
+//                          final_value: u32, final_coeffs: Vec<u32> }                        basefold.rs:50-64
+//   FoldLevelQueries     { prev_batch_proof, folded_batch_proof }                            basefold.rs:73-81
+//   BatchMerkleProof     { indices: Vec<u32>, values: Vec<u32>, auth_nodes: Vec<Vec<[u8;16]>> }   pcs.rs:43-53
+#include "basefold.hpp"
+#include "bincode.hpp"
+#include <cstring>
+
+using namespace zko;
+
+static VF vf(const uint32_t* p, size_t n) { VF v(n); for (size_t i = 0; i < n; i++) v[i] = F(p[i]); return v; }
+static Transcript& T(void* t) { return *static_cast<Transcript*>(t); }
+static size_t emit(const std::vector<uint8_t>& b, uint8_t* out, size_t cap) {
+    if (out && b.size() <= cap) memcpy(out, b.data(), b.size());
+    return b.size();
+}
+static void put(Bin& b, const BatchMerkleProof& p) {
+    b.vec_u32(p.indices);
+    b.vec_u32(p.values);
+    b.u64(p.auth_nodes.size());
+    for (auto& lvl : p.auth_nodes) { b.u64(lvl.size()); for (auto& d : lvl) b.bytes(d); }
+}
+static void put(Bin& b, const BasefoldCommitment& c) { b.bytes(c.root); b.u64(c.num_coeffs); b.u64(c.log_n); }
+static void put(Bin& b, const BasefoldOpeningProof& p) {
+    b.u64(p.fold_roots.size());
+    for (auto& d : p.fold_roots) b.bytes(d);
+    b.u64(p.fold_queries.size());
+    for (auto& q : p.fold_queries) { put(b, q.prev_batch_proof); put(b, q.folded_batch_proof); }
+    b.u32(p.final_value);
+    b.vec_u32(p.final_coeffs);
+}
+
+extern "C" {
+
+void zko_aes128_encrypt(const uint8_t* key, const uint8_t* in, uint8_t* out) { aes::encrypt128(key, in, out); }
+void zko_hash_node(const uint8_t* l, const uint8_t* r, int kind, uint8_t* out) {
+    Digest a, b;
+    memcpy(a.data(), l, 16); memcpy(b.data(), r, 16);
+    Digest o = hash_node(a, b, kind);
+    memcpy(out, o.data(), 16);
+}
+void zko_merkle_root(const uint32_t* v, size_t n, int kind, uint8_t* root) {
+    MerkleTree t(vf(v, n), kind);
+    memcpy(root, t.root().data(), 16);
+}
+// Every internal layer, concatenated from layer 1 (n_pad / 2 nodes) to the root.
+size_t zko_merkle_layers(const uint32_t* v, size_t n, int kind, uint8_t* out, size_t cap) {
+    MerkleTree t(vf(v, n), kind);
+    std::vector<uint8_t> b;
+    for (size_t k = 1; k < t.layers.size(); k++) for (auto& d : t.layers[k]) b.insert(b.end(), d.begin(), d.end());
+    return emit(b, out, cap);
+}
+size_t zko_merkle_batch_open(const uint32_t* v, size_t n, int kind, const uint64_t* idx, size_t n_idx, uint8_t* out, size_t cap) {
+    MerkleTree t(vf(v, n), kind);
+    Bin b;
+    put(b, t.batch_open(std::vector<size_t>(idx, idx + n_idx)));
+    return emit(b.b, out, cap);
+}
+// 1 = batch proof of the given positions verifies against the tree's root; tamper flips a value bit.
+int zko_merkle_batch_roundtrip(const uint32_t* v, size_t n, int kind, const uint64_t* idx, size_t n_idx, int tamper) {
+    MerkleTree t(vf(v, n), kind);
+    auto p = t.batch_open(std::vector<size_t>(idx, idx + n_idx));
+    if (tamper == 1) p.values[0] ^= 1;
+    if (tamper == 2) { for (auto& l : p.auth_nodes) if (!l.empty()) { l[0][3] ^= 4; break; } }
+    bool single = true;
+    for (size_t i = 0; i < n_idx; i++) {
+        auto o = t.open(idx[i]);
+        single = single && verify_merkle_opening(t.root(), idx[i], o.first, o.second, t.log_height, kind);
+    }
+    return (verify_batch_opening(t.root(), p, t.log_height, kind) ? 1 : 0) | (single ? 2 : 0);
+}
+void zko_basefold_tables(size_t log_n, uint32_t* t_flat, uint32_t* w_flat) {
+    auto tb = basefold_tables(log_n);
+    for (size_t i = 0; i < tb->t_flat.size(); i++) { t_flat[i] = tb->t_flat[i].v; w_flat[i] = tb->w_flat[i].v; }
+}
+void zko_basefold_encode(const uint32_t* c, size_t log_n, uint32_t* cw) {
+    auto tb = basefold_tables(log_n);
+    VF o = basefold_encode(vf(c, size_t(1) << log_n), log_n, *tb);
+    for (size_t i = 0; i < o.size(); i++) cw[i] = o[i].v;
+}
+// bincode(BasefoldCommitment) followed by bincode(BasefoldOpeningProof)
+size_t zko_basefold_commit_and_prove(void* t, const uint32_t* c, size_t n, const uint32_t* point, size_t n_point, int kind,
+                                     uint8_t* out, size_t cap) {
+    auto r = basefold_commit_and_prove(vf(c, n), vf(point, n_point), T(t), kind);
+    Bin b;
+    put(b, r.first); put(b, r.second);
+    return emit(b.b, out, cap);
+}
+// prove, then verify with a fresh transcript of the same label; claimed = MLE(coeffs)(point).
+// tamper: 0 none, 1 final value, 2 a fold root, 3 an opened value, 4 wrong claimed value.
+int zko_basefold_roundtrip(const uint32_t* c, size_t n, const uint32_t* point, size_t n_point, int kind, int tamper) {
+    Transcript pt("bf"), vt("bf");
+    VF co = vf(c, n), pnt = vf(point, n_point);
+    auto r = basefold_commit_and_prove(co, pnt, pt, kind);
+    size_t log_n = r.first.log_n;
+    F claimed = mle_evaluate(padded(co, size_t(1) << log_n), pnt);
+    if (F(r.second.final_value) != claimed) return -1;
+    if (tamper == 1) r.second.final_value ^= 1;
+    if (tamper == 2) r.second.fold_roots[r.second.fold_roots.size() / 2][5] ^= 1;
+    if (tamper == 3) r.second.fold_queries[0].prev_batch_proof.values[0] ^= 2;
+    if (tamper == 4) claimed = claimed + F::one();
+    vt.absorb_bytes(r.first.root);
+    return basefold_verify_opening(r.first, claimed, pnt, r.second, vt, kind) ? 1 : 0;
+}
+
+}  // extern "C"

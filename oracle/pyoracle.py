@@ -360,3 +360,74 @@ def qwen_layer_prove(config: dict, weights: dict, x, silu_out, sigmoid_out, laye
     n = lib().zko_qwen_layer_prove(dims, wp, px, ps, pg, C.c_size_t(S.size), C.c_uint32(layer_idx), _u8(input_hash),
                                    y.ctypes.data_as(u32p), buf, C.c_size_t(cap), C.c_int(int(verify)), C.byref(acc))
     return y, bytes(buf[:n]), (bool(acc.value) if verify else None)
+
+
+# ---- Merkle tree and Basefold (oracle/pcs.hpp, oracle/basefold.hpp) ------------------------------
+NODE_BLAKE3, NODE_AES_MMO = 0, 1
+
+
+def aes128_encrypt(key: bytes, block: bytes) -> bytes:
+    out = (C.c_uint8 * 16)()
+    lib().zko_aes128_encrypt(_u8(key), _u8(block), out)
+    return bytes(out)
+
+
+def hash_node(left: bytes, right: bytes, kind: int) -> bytes:
+    out = (C.c_uint8 * 16)()
+    lib().zko_hash_node(_u8(left), _u8(right), C.c_int(kind), out)
+    return bytes(out)
+
+
+def merkle_root(values, kind: int) -> bytes:
+    V, pv = _u32(values)
+    out = (C.c_uint8 * 16)()
+    lib().zko_merkle_root(pv, C.c_size_t(V.size), C.c_int(kind), out)
+    return bytes(out)
+
+
+def merkle_layers(values, kind: int) -> bytes:
+    V, pv = _u32(values)
+    return _bytes_call(lib().zko_merkle_layers, pv, C.c_size_t(V.size), C.c_int(kind), cap=max(1 << 16, 40 * V.size))
+
+
+def _u64arr(idx):
+    a = np.ascontiguousarray(idx, dtype=np.uint64)
+    return a, a.ctypes.data_as(C.POINTER(C.c_uint64))
+
+
+def merkle_batch_open(values, kind: int, indices) -> bytes:
+    V, pv = _u32(values); I, pi = _u64arr(indices)
+    return _bytes_call(lib().zko_merkle_batch_open, pv, C.c_size_t(V.size), C.c_int(kind), pi, C.c_size_t(I.size))
+
+
+def merkle_batch_roundtrip(values, kind: int, indices, tamper=0) -> int:
+    """bit 0: batch proof verifies; bit 1: every single-path opening verifies."""
+    V, pv = _u32(values); I, pi = _u64arr(indices)
+    return int(lib().zko_merkle_batch_roundtrip(pv, C.c_size_t(V.size), C.c_int(kind), pi, C.c_size_t(I.size), C.c_int(tamper)))
+
+
+def basefold_tables(log_n: int):
+    total = (1 << log_n) - 1
+    t = np.zeros(total, np.uint32); w = np.zeros(total, np.uint32)
+    lib().zko_basefold_tables(C.c_size_t(log_n), t.ctypes.data_as(u32p), w.ctypes.data_as(u32p))
+    return t, w
+
+
+def basefold_encode(coeffs, log_n: int):
+    Cf, pc = _u32(coeffs)
+    assert Cf.size == 1 << log_n
+    cw = np.zeros(2 << log_n, np.uint32)
+    lib().zko_basefold_encode(pc, C.c_size_t(log_n), cw.ctypes.data_as(u32p))
+    return cw
+
+
+def basefold_commit_and_prove(tr, coeffs, point, kind: int) -> bytes:
+    """bincode(BasefoldCommitment) || bincode(BasefoldOpeningProof)."""
+    Cf, pc = _u32(coeffs); Pt, pp = _u32(point)
+    return _bytes_call(lib().zko_basefold_commit_and_prove, tr.h, pc, C.c_size_t(Cf.size), pp, C.c_size_t(Pt.size), C.c_int(kind),
+                       cap=1 << 22)
+
+
+def basefold_roundtrip(coeffs, point, kind: int, tamper=0) -> int:
+    Cf, pc = _u32(coeffs); Pt, pp = _u32(point)
+    return int(lib().zko_basefold_roundtrip(pc, C.c_size_t(Cf.size), pp, C.c_size_t(Pt.size), C.c_int(kind), C.c_int(tamper)))
