@@ -172,6 +172,41 @@ int32_t zkb_qwen_layer_prove_end(zkb_qwen_layer* layer, uint8_t* out, size_t cap
 int32_t zkb_qwen_layer_prove(zkb_qwen_layer* layer, uint32_t layer_idx, const uint8_t input_hash[32], uint8_t* out, size_t cap,
                              size_t* len);
 
+/* ---- Merkle trees and the Basefold commitment (features pcs / pcs-full of the reference) -------
+ * Digests are 16 bytes.  node_hash selects the reference's hash_node variant
+ * (rust/zk_ml_prover/src/proving/pcs.rs:87-135): ZKB_NODE_BLAKE3 = blake3(L || R)[..16], what the
+ * reference computes on every target except aarch64; ZKB_NODE_AES_MMO = its aarch64 AES-based
+ * compression.  Leaves are the u32 values zero-padded to 16 bytes (pcs.rs:71-75); a vector of n
+ * values makes a tree over 2^max(1, ceil(log2 n)) leaves, zero-padded (pcs.rs:143-153). */
+#define ZKB_NODE_BLAKE3 0
+#define ZKB_NODE_AES_MMO 1
+
+/* MerkleTree::new(values).root() (pcs.rs:143-201). */
+int32_t zkb_merkle_root(zkb_ctx* ctx, const uint32_t* values, size_t n, int32_t on_device, int32_t node_hash, uint8_t root[16]);
+/* Every internal layer of MerkleTree::new(values), from the parents of the leaves up to the
+ * root, 16 bytes per node (pcs.rs:156-196).  *len = (2^h - 1) * 16. */
+int32_t zkb_merkle_layers(zkb_ctx* ctx, const uint32_t* values, size_t n, int32_t on_device, int32_t node_hash, uint8_t* out, size_t cap,
+                          size_t* len);
+/* MerkleTree::new(values).batch_open(indices) (pcs.rs:290-337) as bincode(BatchMerkleProof):
+ * indices and values in caller order, then per level the digests of the unknown siblings. */
+int32_t zkb_merkle_batch_open(zkb_ctx* ctx, const uint32_t* values, size_t n, int32_t on_device, int32_t node_hash,
+                              const uint64_t* indices, size_t n_idx, uint8_t* out, size_t cap, size_t* len);
+
+/* generate_tables(log_n, table_seed(log_n)) (basefold.rs:106-143, 323-328): t_flat and
+ * w_flat = 1 / (2 t), 2^log_n - 1 words each, to host memory.  Tables are generated once per
+ * (device, log_n) and stay resident, as the reference caches them (basefold.rs:377-393). */
+int32_t zkb_basefold_tables(zkb_ctx* ctx, uint32_t log_n, uint32_t* t_flat, uint32_t* w_flat);
+/* encode (basefold.rs:169-238) of n coefficients zero-padded to 2^log_n: 2 * 2^log_n words. */
+int32_t zkb_basefold_encode(zkb_ctx* ctx, const uint32_t* coeffs, size_t n, int32_t on_device, uint32_t* codeword,
+                            int32_t out_on_device);
+/* commit_and_prove (basefold.rs:368-396; the _with_tables and _vec variants compute the same):
+ * encode, Merkle-commit, absorb the root, then the opening at `point` (n_point words; rounds
+ * beyond n_point squeeze their challenge, basefold.rs:508-513).  coeffs and point are both host
+ * or both device memory.  Output: bincode(BasefoldCommitment) followed by
+ * bincode(BasefoldOpeningProof).  The transcript advances exactly as in the reference. */
+int32_t zkb_basefold_commit_and_prove(zkb_ctx* ctx, zkb_transcript* tr, const uint32_t* coeffs, size_t n, const uint32_t* point,
+                                      uint32_t n_point, int32_t on_device, int32_t node_hash, uint8_t* out, size_t cap, size_t* len);
+
 /* ---- allocation-free weight fold ----
  * No counterpart in the reference: it exists for callers that must not allocate device memory
  * once they are running (a serving loop with a fixed memory plan, a host that forbids cudaMalloc

@@ -1,0 +1,97 @@
+"""GPU parity of the Merkle tree and the Basefold commitment against the CPU oracle: roots,
+layers, codewords and whole proofs are compared bit for bit, for both node hashes."""
+import numpy as np
+import pytest
+
+import zklm_compile_b200 as zk
+from zklm_compile_b200 import pcs as zp
+from oracle import pyoracle as O
+from tests.util import P
+
+pytestmark = pytest.mark.gpu
+KINDS = [zp.NODE_BLAKE3, zp.NODE_AES_MMO]
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    c = zk.Context(0)
+    yield c
+    c.close()
+
+
+def rnd(seed, n):
+    return np.random.default_rng(seed).integers(0, P, n, dtype=np.int64).astype(np.uint32)
+
+
+@pytest.mark.parametrize("kind", KINDS)
+@pytest.mark.parametrize("n", [1, 2, 3, 5, 64, 1000, 1024, 1025, 2048, 5000, 1 << 16, (1 << 20) + 7])
+def test_merkle_root_and_layers(ctx, kind, n):
+    v = rnd(n, n)
+    assert zp.merkle_root(ctx, v, kind) == O.merkle_root(v, kind)
+    if n <= 5000:
+        assert zp.merkle_layers(ctx, v, kind) == O.merkle_layers(v, kind)
+
+
+@pytest.mark.parametrize("kind", KINDS)
+def test_merkle_batch_open_bytes(ctx, kind):
+    v = rnd(7, 3000)
+    for idx in ([3, 3, 2, 2999, 4095, 2048, 0, 1], [17], list(range(40)), [4095, 0]):
+        assert zp.merkle_batch_open(ctx, v, idx, kind) == O.merkle_batch_open(v, kind, idx)
+    v2 = rnd(8, 2)
+    assert zp.merkle_batch_open(ctx, v2, [1, 0, 1], kind) == O.merkle_batch_open(v2, kind, [1, 0, 1])
+
+
+@pytest.mark.parametrize("log_n", [1, 2, 5, 11, 14])
+def test_basefold_tables(ctx, log_n):
+    t, w = zp.basefold_tables(ctx, log_n)
+    to, wo = O.basefold_tables(log_n)
+    assert t.tolist() == to.tolist() and w.tolist() == wo.tolist()
+
+
+@pytest.mark.parametrize("n", [1, 2, 3, 100, 4096, 5000, 1 << 13, 1 << 16, (1 << 18) - 5, 1 << 19])
+def test_basefold_encode(ctx, n):
+    c = rnd(100 + n, n)
+    log_n = 1 if n <= 1 else (n - 1).bit_length()
+    padded = np.zeros(1 << log_n, np.uint32)
+    padded[:n] = c
+    assert np.array_equal(zp.basefold_encode(ctx, c), O.basefold_encode(padded, log_n))
+
+
+@pytest.mark.parametrize("kind", KINDS)
+@pytest.mark.parametrize("n", [1, 2, 5, 64, 300, 1024, 3000, 1 << 14])
+def test_basefold_commit_and_prove_bytes(ctx, kind, n):
+    c = rnd(200 + n, n)
+    log_n = 1 if n <= 1 else (n - 1).bit_length()
+    pt = rnd(300 + n, log_n)
+    tg = zk.Transcript(ctx, b"bf-parity")
+    to = O.Transcript(b"bf-parity")
+    assert zp.basefold_commit_and_prove(ctx, tg, c, pt, kind) == O.basefold_commit_and_prove(to, c, pt, kind)
+    assert tg.squeeze() == to.squeeze()          # transcripts left in the same state
+
+
+def test_basefold_short_point_squeezes_challenges(ctx):
+    c = rnd(5, 700)
+    pt = rnd(6, 4)
+    tg = zk.Transcript(ctx, b"bf-short")
+    to = O.Transcript(b"bf-short")
+    assert zp.basefold_commit_and_prove(ctx, tg, c, pt) == O.basefold_commit_and_prove(to, c, pt, O.NODE_BLAKE3)
+    assert tg.squeeze() == to.squeeze()
+
+
+def test_basefold_large_final_value_is_mle_evaluation(ctx):
+    # size-independent property at 2^22 coefficients: the proof's final value is the multilinear
+    # evaluation, which for a point of zeros and ones is a single coefficient
+    n = 1 << 22
+    c = rnd(9, n)
+    log_n = 22
+    bits = [1, 0, 1, 1, 0, 0, 1, 0, 1, 1, 1, 0, 0, 1, 0, 1, 0, 0, 1, 1, 0, 1]
+    idx = int("".join(map(str, bits)), 2)
+    tg = zk.Transcript(ctx, b"bf-large")
+    blob = zp.basefold_commit_and_prove(ctx, tg, c, np.array(bits, np.uint32))
+    assert int.from_bytes(blob[16:24], "little") == n and int.from_bytes(blob[24:32], "little") == log_n
+    final_value = int.from_bytes(blob[-12:-8], "little")
+    assert final_value == int(c[idx])
+    assert blob[-8:] == bytes(8)
+    # commitment root = Merkle root of the codeword
+    cw = zp.basefold_encode(ctx, c)
+    assert blob[:16] == zp.merkle_root(ctx, cw)

@@ -1,5 +1,6 @@
 // C ABI of the backend (see include/zkb200.h) and the host-side launch logic.
 #include "qwen.cuh"
+#include "basefold.cuh"
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
@@ -324,6 +325,7 @@ int32_t zkb_sumcheck_prove(zkb_ctx* c, zkb_transcript* t, int32_t kind, const ui
 
 #include "abi_protocols.cuh"
 #include "abi_layer.cuh"
+#include "abi_pcs.cuh"
 
 // =============================================================================================
 // Allocation-free weight fold

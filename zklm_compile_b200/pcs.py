@@ -1,0 +1,76 @@
+"""Host-side mirror of the reference's Merkle tree and Basefold commitment over the C ABI
+(rust/zk_ml_prover/src/proving/pcs.rs, basefold.rs).  Results are the reference's values or
+the bincode bytes of its proof structs."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from ._lib import check, u32p
+from .protocols import _a, _proof_call, log2_ceil
+from .sumcheck import Context, DeviceBuffer, Transcript
+
+NODE_BLAKE3, NODE_AES_MMO = 0, 1
+
+
+def _src(values):
+    if isinstance(values, DeviceBuffer):
+        return values, values.ptr, values.n, 1
+    a, pa = _a(values)
+    return a, pa, a.size, 0
+
+
+def merkle_root(ctx: Context, values, node_hash: int = NODE_BLAKE3) -> bytes:
+    """MerkleTree::new(values).root(), pcs.rs:143-201."""
+    keep, p, n, dev = _src(values)
+    out = (C.c_uint8 * 16)()
+    check(ctx.h, _lib.lib().zkb_merkle_root(ctx.h, p, C.c_size_t(n), C.c_int32(dev), C.c_int32(node_hash), out))
+    return bytes(out)
+
+
+def merkle_layers(ctx: Context, values, node_hash: int = NODE_BLAKE3) -> bytes:
+    """All internal layers, parents of the leaves first (pcs.rs:156-196)."""
+    keep, p, n, dev = _src(values)
+    h = log2_ceil(n)
+    return _proof_call(ctx, _lib.lib().zkb_merkle_layers, ctx.h, p, C.c_size_t(n), C.c_int32(dev), C.c_int32(node_hash),
+                       cap=16 << h)
+
+
+def merkle_batch_open(ctx: Context, values, indices, node_hash: int = NODE_BLAKE3) -> bytes:
+    """MerkleTree::batch_open, pcs.rs:290-337 -> bincode(BatchMerkleProof)."""
+    keep, p, n, dev = _src(values)
+    idx = np.ascontiguousarray(indices, dtype=np.uint64)
+    return _proof_call(ctx, _lib.lib().zkb_merkle_batch_open, ctx.h, p, C.c_size_t(n), C.c_int32(dev), C.c_int32(node_hash),
+                       idx.ctypes.data_as(C.POINTER(C.c_uint64)), C.c_size_t(idx.size))
+
+
+def basefold_tables(ctx: Context, log_n: int):
+    """generate_tables(log_n, table_seed(log_n)), basefold.rs:106-143 -> (t_flat, w_flat)."""
+    total = (1 << log_n) - 1
+    t = np.zeros(total, np.uint32)
+    w = np.zeros(total, np.uint32)
+    check(ctx.h, _lib.lib().zkb_basefold_tables(ctx.h, C.c_uint32(log_n), t.ctypes.data_as(u32p), w.ctypes.data_as(u32p)))
+    return t, w
+
+
+def basefold_encode(ctx: Context, coeffs) -> np.ndarray:
+    """encode, basefold.rs:169-238 (coefficients zero-padded to a power of two, at least 2)."""
+    keep, p, n, dev = _src(coeffs)
+    cw = np.zeros(2 << log2_ceil(n), np.uint32)
+    check(ctx.h, _lib.lib().zkb_basefold_encode(ctx.h, p, C.c_size_t(n), C.c_int32(dev), cw.ctypes.data_as(u32p), C.c_int32(0)))
+    return cw
+
+
+def basefold_commit_and_prove(ctx: Context, tr: Transcript, coeffs, point, node_hash: int = NODE_BLAKE3) -> bytes:
+    """commit_and_prove, basefold.rs:368-396 -> bincode(BasefoldCommitment) || bincode(BasefoldOpeningProof)."""
+    keep, p, n, dev = _src(coeffs)
+    if dev:
+        assert isinstance(point, DeviceBuffer)
+        pp, npt = point.ptr, point.n
+    else:
+        pt, pp = _a(point)
+        npt = pt.size
+    return _proof_call(ctx, _lib.lib().zkb_basefold_commit_and_prove, ctx.h, tr.h, p, C.c_size_t(n), pp, C.c_uint32(npt),
+                       C.c_int32(dev), C.c_int32(node_hash), cap=1 << 22)
