@@ -132,6 +132,17 @@ int32_t zkb_rmsnorm_forward(zkb_ctx* ctx, const uint32_t* x, const uint32_t* gam
 /* prove_matmul_succinct_ef -> SuccinctMatmulProofEF                    matmul.rs:963-997 */
 int32_t zkb_prove_matmul_succinct_ef(zkb_ctx* ctx, zkb_transcript* tr, const uint32_t* W, const uint32_t* x, const uint32_t* y,
                                      size_t m, size_t n, int32_t w_on_device, uint8_t* out, size_t cap, size_t* len);
+/* The same prover under one of the reference's compile-time weight-binding modes
+ * (bind_weights_ef, matmul.rs:360-453): ZKB_BIND_BLAKE3 = default build (identical to the call
+ * above), ZKB_BIND_PCS = feature pcs (Basefold of w_partial), ZKB_BIND_PCS_FULL = feature
+ * pcs-full (Basefold of the row-padded matrix W).  In the PCS modes basefold_proof is Some(..)
+ * and node_hash (ZKB_NODE_*) selects the Merkle node hash. */
+#define ZKB_BIND_BLAKE3 0
+#define ZKB_BIND_PCS 1
+#define ZKB_BIND_PCS_FULL 2
+int32_t zkb_prove_matmul_succinct_ef_bind(zkb_ctx* ctx, zkb_transcript* tr, const uint32_t* W, const uint32_t* x, const uint32_t* y,
+                                          size_t m, size_t n, int32_t w_on_device, int32_t bind_mode, int32_t node_hash, uint8_t* out,
+                                          size_t cap, size_t* len);
 /* prove_hadamard_ef (is_add = 0) / prove_add_ef (is_add = 1); point = k EF challenges    elementwise.rs:429-480, 545-595 */
 int32_t zkb_prove_elementwise_ef(zkb_ctx* ctx, zkb_transcript* tr, int32_t is_add, const uint32_t* a, const uint32_t* b,
                                  const uint32_t* c, size_t n, const uint32_t* point, uint32_t k, uint8_t* out, size_t cap, size_t* len);
@@ -164,6 +175,10 @@ int32_t zkb_qwen_layer_forward_async(zkb_qwen_layer* layer, zkb_qwen_layer* prev
  * and copies the layer output (d_model words) to the host. */
 int32_t zkb_qwen_layer_read_output(zkb_qwen_layer* layer, uint32_t* y_host);
 const uint32_t* zkb_qwen_layer_output_dev(const zkb_qwen_layer* layer);
+/* Selects what the reference fixes at compile time for the layer's eight matmul proofs: the
+ * weight binding (ZKB_BIND_*, features pcs / pcs-full, matmul.rs:360-453) and the Merkle node
+ * hash (ZKB_NODE_*, pcs.rs:87-135).  Default after create: ZKB_BIND_BLAKE3. */
+int32_t zkb_qwen_layer_set_binding(zkb_qwen_layer* layer, int32_t bind_mode, int32_t node_hash);
 /* prove_qwen_layer_precommitted_ef on a fresh transcript "qwen-layer-{idx}" || input_hash
  * (transformer/qwen.rs:795-912, pipeline/prove.rs:166-168) -> QwenLayerProofEF bincode.
  * prove_begin only enqueues GPU work; prove_end waits and serialises. */

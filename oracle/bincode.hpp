@@ -50,9 +50,26 @@ struct Bin {
     void put(const MatmulProofEF& p) {                      // matmul.rs:717-726
         put(p.sumcheck_proof); ef(p.w_at_rs); ef(p.x_at_s); vec_ef(p.r_point); vec_ef(p.s_point);
     }
+    void put(const BatchMerkleProof& p) {                   // pcs.rs:43-53
+        vec_u32(p.indices);
+        vec_u32(p.values);
+        u64(p.auth_nodes.size());
+        for (auto& lvl : p.auth_nodes) { u64(lvl.size()); for (auto& d : lvl) bytes(d); }
+    }
+    void put(const BasefoldCommitment& c) { bytes(c.root); u64(c.num_coeffs); u64(c.log_n); }   // basefold.rs:39-47
+    void put(const BasefoldOpeningProof& p) {               // basefold.rs:50-64, 73-81
+        u64(p.fold_roots.size());
+        for (auto& d : p.fold_roots) bytes(d);
+        u64(p.fold_queries.size());
+        for (auto& q : p.fold_queries) { put(q.prev_batch_proof); put(q.folded_batch_proof); }
+        u32(p.final_value);
+        vec_u32(p.final_coeffs);
+    }
     void put(const SuccinctMatmulProofEF& p) {              // matmul.rs:947-960
         put(p.matmul_proof); put(p.w_eval_proof); ef(p.w_claimed_value); put(p.w_partial_commitment);
-        u8(p.bound ? 1 : 0); u8(0);
+        u8(p.bound ? 1 : 0);
+        u8(p.has_basefold ? 1 : 0);
+        if (p.has_basefold) put(p.basefold_proof);
     }
     void put(const HadamardProofEF& p) {                    // elementwise.rs:415-426
         put(p.product_sumcheck); ef(p.fin_eq); ef(p.fin_a); ef(p.fin_b); ef(p.c_eval);

@@ -7,7 +7,6 @@
 //                          final_value: u32, final_coeffs: Vec<u32> }                        basefold.rs:50-64
 //   FoldLevelQueries     { prev_batch_proof, folded_batch_proof }                            basefold.rs:73-81
 //   BatchMerkleProof     { indices: Vec<u32>, values: Vec<u32>, auth_nodes: Vec<Vec<[u8;16]>> }   pcs.rs:43-53
-#include "basefold.hpp"
 #include "bincode.hpp"
 #include <cstring>
 
@@ -19,22 +18,6 @@ static size_t emit(const std::vector<uint8_t>& b, uint8_t* out, size_t cap) {
     if (out && b.size() <= cap) memcpy(out, b.data(), b.size());
     return b.size();
 }
-static void put(Bin& b, const BatchMerkleProof& p) {
-    b.vec_u32(p.indices);
-    b.vec_u32(p.values);
-    b.u64(p.auth_nodes.size());
-    for (auto& lvl : p.auth_nodes) { b.u64(lvl.size()); for (auto& d : lvl) b.bytes(d); }
-}
-static void put(Bin& b, const BasefoldCommitment& c) { b.bytes(c.root); b.u64(c.num_coeffs); b.u64(c.log_n); }
-static void put(Bin& b, const BasefoldOpeningProof& p) {
-    b.u64(p.fold_roots.size());
-    for (auto& d : p.fold_roots) b.bytes(d);
-    b.u64(p.fold_queries.size());
-    for (auto& q : p.fold_queries) { put(b, q.prev_batch_proof); put(b, q.folded_batch_proof); }
-    b.u32(p.final_value);
-    b.vec_u32(p.final_coeffs);
-}
-
 extern "C" {
 
 void zko_aes128_encrypt(const uint8_t* key, const uint8_t* in, uint8_t* out) { aes::encrypt128(key, in, out); }
@@ -58,7 +41,7 @@ size_t zko_merkle_layers(const uint32_t* v, size_t n, int kind, uint8_t* out, si
 size_t zko_merkle_batch_open(const uint32_t* v, size_t n, int kind, const uint64_t* idx, size_t n_idx, uint8_t* out, size_t cap) {
     MerkleTree t(vf(v, n), kind);
     Bin b;
-    put(b, t.batch_open(std::vector<size_t>(idx, idx + n_idx)));
+    b.put(t.batch_open(std::vector<size_t>(idx, idx + n_idx)));
     return emit(b.b, out, cap);
 }
 // 1 = batch proof of the given positions verifies against the tree's root; tamper flips a value bit.
@@ -88,7 +71,7 @@ size_t zko_basefold_commit_and_prove(void* t, const uint32_t* c, size_t n, const
                                      uint8_t* out, size_t cap) {
     auto r = basefold_commit_and_prove(vf(c, n), vf(point, n_point), T(t), kind);
     Bin b;
-    put(b, r.first); put(b, r.second);
+    b.put(r.first); b.put(r.second);
     return emit(b.b, out, cap);
 }
 // prove, then verify with a fresh transcript of the same label; claimed = MLE(coeffs)(point).
@@ -107,5 +90,8 @@ int zko_basefold_roundtrip(const uint32_t* c, size_t n, const uint32_t* point, s
     vt.absorb_bytes(r.first.root);
     return basefold_verify_opening(r.first, claimed, pnt, r.second, vt, kind) ? 1 : 0;
 }
+
+// Process-wide stand-ins for the reference's cargo features and target architecture.
+void zko_set_features(int bind_mode, int node_kind) { features().bind_mode = bind_mode; features().node_kind = node_kind; }
 
 }  // extern "C"

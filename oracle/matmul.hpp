@@ -4,7 +4,7 @@
 // default build (no `pcs` feature: weights are bound by blake3 + an MLE-eval sumcheck), plus
 // the forward matvec of rust/zk_ml_prover/src/transformer/mod.rs:140-163.
 #pragma once
-#include "commit.hpp"
+#include "basefold.hpp"
 
 namespace zko {
 
@@ -122,7 +122,19 @@ struct SuccinctMatmulProofEF {
     EFElement w_claimed_value{};
     WeightCommitment w_partial_commitment;
     bool bound = false;
+    bool has_basefold = false;                 // basefold_proof: Option<BasefoldOpeningProof> (matmul.rs:958-959)
+    BasefoldOpeningProof basefold_proof;
 };
+
+// The reference picks its weight binding at compile time (cargo features, matmul.rs:360-453):
+//   BIND_BLAKE3    default build: blake3 of w_partial, no Basefold            matmul.rs:441-443
+//   BIND_PCS       feature pcs: Basefold of w_partial (4 n_pad base words)     matmul.rs:422-438
+//   BIND_PCS_FULL  feature pcs-full: Basefold of the row-padded matrix W       matmul.rs:372-403
+// and its Merkle node hash by target architecture (pcs.rs:87-135).  The oracle keeps both as
+// a process-wide setting, the analogue of "which binary was built".
+enum BindMode : int { BIND_BLAKE3 = 0, BIND_PCS = 1, BIND_PCS_FULL = 2 };
+struct Features { int bind_mode = BIND_BLAKE3; int node_kind = NODE_BLAKE3; };
+inline Features& features() { static Features f; return f; }
 
 // matmul.rs:838-885
 inline MatmulProofEF prove_matmul_ef(const VF& w, const VF& x, const VF& y, size_t m, size_t n, Transcript& tr, VEF* w_partial_out) {
@@ -140,7 +152,9 @@ inline MatmulProofEF prove_matmul_ef(const VF& w, const VF& x, const VF& y, size
     if (w_partial_out) *w_partial_out = w_partial;
     return p;
 }
-// matmul.rs:963-997 with bind_weights_ef's default branch (:435-452)
+// matmul.rs:963-997 with bind_weights_ef (matmul.rs:360-453).  In the PCS modes the evaluation
+// point is squeezed from the transcript (one base-field value per variable) and the 16-byte
+// Merkle root is stored zero-padded in the 32-byte commitment.
 inline SuccinctMatmulProofEF prove_matmul_succinct_ef(const VF& w, const VF& x, const VF& y, size_t m, size_t n, Transcript& tr) {
     VEF w_partial;
     SuccinctMatmulProofEF p;
@@ -149,13 +163,36 @@ inline SuccinctMatmulProofEF prove_matmul_succinct_ef(const VF& w, const VF& x, 
     for (EF v : w_partial) { auto a = v.arr(); for (int k = 0; k < 4; k++) base.push_back(F(a[k])); }
     VEF s;
     for (auto& e : p.matmul_proof.s_point) s.push_back(ef_of(e));
-    p.w_partial_commitment = commit_weights_fast(base);
+    const int mode = features().bind_mode;
+    if (mode == BIND_BLAKE3) {
+        p.w_partial_commitment = commit_weights_fast(base);
+    } else {
+        VF coeffs;
+        size_t num_coeffs;
+        if (mode == BIND_PCS_FULL) {
+            size_t m_pad = size_t(1) << log2_ceil(m), n_pad = size_t(1) << log2_ceil(n);
+            coeffs.assign(m_pad * n_pad, F::zero());
+            for (size_t i = 0; i < m; i++) for (size_t j = 0; j < n; j++) coeffs[i * n_pad + j] = w[i * n + j];
+            num_coeffs = w.size();       // commit_and_prove_vec records the caller's count (matmul.rs:392)
+        } else {
+            coeffs = base;
+            num_coeffs = base.size();
+        }
+        VF bf_point = tr.squeeze_many(log2_ceil(coeffs.size()));
+        auto r = basefold_commit_and_prove(coeffs, bf_point, tr, features().node_kind);
+        memcpy(p.w_partial_commitment.root.data(), r.first.root.data(), 16);
+        p.w_partial_commitment.num_weights = num_coeffs;
+        p.w_partial_commitment.log_height = r.first.log_n;
+        p.w_partial_commitment.kind = 0;
+        p.has_basefold = true;
+        p.basefold_proof = std::move(r.second);
+    }
     tr.absorb_bytes(p.w_partial_commitment.root);
     p.w_eval_proof = prove_mle_eval_ef_with_claim_no_merkle(w_partial, s, tr);
     return p;
 }
 struct MatmulVerifyEF { bool valid = false; VEF x_claim_point; EF x_claim_value; };
-// matmul.rs:1000-1117 (default branch)
+// matmul.rs:1000-1117 (Basefold branch :1061-1093, default branch :1094-1104)
 inline MatmulVerifyEF verify_matmul_succinct_ef(const SuccinctMatmulProofEF& p, const VF& y, size_t m, size_t n, Transcript& tr) {
     MatmulVerifyEF out;
     size_t log_m = log2_ceil(m), m_pad = size_t(1) << log_m;
@@ -175,6 +212,16 @@ inline MatmulVerifyEF verify_matmul_succinct_ef(const SuccinctMatmulProofEF& p, 
     VEF s;
     if (p.matmul_proof.s_point.empty()) s = derived;
     else for (auto& e : p.matmul_proof.s_point) s.push_back(ef_of(e));
+    if (p.has_basefold) {
+        BasefoldCommitment c;
+        memcpy(c.root.data(), p.w_partial_commitment.root.data(), 16);
+        c.num_coeffs = p.w_partial_commitment.num_weights;
+        c.log_n = p.w_partial_commitment.log_height;
+        if (c.log_n > 40) return out;
+        VF bf_point = tr.squeeze_many(c.log_n);
+        tr.absorb_bytes(c.root);
+        if (!basefold_verify_opening(c, F(p.basefold_proof.final_value), bf_point, p.basefold_proof, tr, features().node_kind)) return out;
+    }
     tr.absorb_bytes(p.w_partial_commitment.root);
     if (!verify_mle_eval_ef(w_at_rs, s, p.w_eval_proof, tr)) return out;
     out.valid = true; out.x_claim_point = s; out.x_claim_value = x_at_s;

@@ -431,3 +431,22 @@ def basefold_commit_and_prove(tr, coeffs, point, kind: int) -> bytes:
 def basefold_roundtrip(coeffs, point, kind: int, tamper=0) -> int:
     Cf, pc = _u32(coeffs); Pt, pp = _u32(point)
     return int(lib().zko_basefold_roundtrip(pc, C.c_size_t(Cf.size), pp, C.c_size_t(Pt.size), C.c_int(kind), C.c_int(tamper)))
+
+
+BIND_BLAKE3, BIND_PCS, BIND_PCS_FULL = 0, 1, 2
+
+
+class features:
+    """`with features(bind_mode, node_kind):` runs the oracle as the reference built with the
+    matching cargo feature (default / pcs / pcs-full) for a target with that Merkle node hash."""
+
+    def __init__(self, bind_mode: int = BIND_BLAKE3, node_kind: int = NODE_BLAKE3):
+        self.v = (bind_mode, node_kind)
+
+    def __enter__(self):
+        lib().zko_set_features(C.c_int(self.v[0]), C.c_int(self.v[1]))
+        return self
+
+    def __exit__(self, *a):
+        lib().zko_set_features(C.c_int(0), C.c_int(0))
+        return False

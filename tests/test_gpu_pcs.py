@@ -95,3 +95,40 @@ def test_basefold_large_final_value_is_mle_evaluation(ctx):
     # commitment root = Merkle root of the codeword
     cw = zp.basefold_encode(ctx, c)
     assert blob[:16] == zp.merkle_root(ctx, cw)
+
+
+@pytest.mark.parametrize("kind", KINDS)
+@pytest.mark.parametrize("mode", [0, 1, 2])
+@pytest.mark.parametrize("m,n", [(4, 4), (5, 7), (33, 100), (128, 64)])
+def test_matmul_binding_modes_bytes(ctx, kind, mode, m, n):
+    from zklm_compile_b200 import protocols as zpr
+    rng = np.random.default_rng(m * 1000 + n)
+    w = rng.integers(0, P, m * n, dtype=np.int64).astype(np.uint32)
+    x = rng.integers(0, P, n, dtype=np.int64).astype(np.uint32)
+    y = O.matmul_forward(w, x, m, n)
+    tg = zk.Transcript(ctx, b"mm-bind")
+    to = O.Transcript(b"mm-bind")
+    got = zpr.prove_matmul_succinct_ef(w, x, y, m, n, tg, bind_mode=mode, node_hash=kind)
+    with O.features(mode, kind):
+        assert got == O.prove_matmul_succinct(to, w, x, y, m, n, ef=True)
+    assert tg.squeeze() == to.squeeze()
+
+
+@pytest.mark.parametrize("mode,kind", [(1, 0), (2, 0), (2, 1)])
+def test_qwen_layer_with_basefold_binding_bytes(ctx, mode, kind):
+    import hashlib
+    from zklm_compile_b200 import qwen as zq
+    from tests.util import load_qwen_golden, rand_layer
+    G = load_qwen_golden()
+    cfg, weights, x = rand_layer(31, d_model=64, d_ff=96, heads=2, kv=2, d_head=16, v_heads=4, v_d_head=16)
+    ih = hashlib.sha256(b"model-input").digest()
+    layer = zq.QwenLayer(ctx, cfg, weights, ctx.upload(G["silu"]), ctx.upload(G["sigmoid"]))
+    layer.set_binding(mode, kind)
+    y = layer.forward(x)
+    with O.features(mode, kind):
+        ey, eproof, ok = O.qwen_layer_prove(cfg, weights, x, G["silu"], G["sigmoid"], 3, ih, verify=True)
+    assert ok and y.tolist() == ey.tolist()
+    proof = layer.prove(3, ih)
+    assert len(proof) == len(eproof) and proof == eproof
+    assert layer.prove(3, ih) == eproof
+    layer.close()

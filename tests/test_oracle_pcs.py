@@ -117,3 +117,38 @@ def test_basefold_proof_is_deterministic_and_short_point_squeezes():
     assert int.from_bytes(a[32:40], "little") == 7
     # a point shorter than log_n: remaining challenges are squeezed (basefold.rs:508-513)
     assert O.basefold_roundtrip(c, pt[:3], O.NODE_BLAKE3) in (-1, 0, 1)
+
+
+@pytest.mark.parametrize("kind", KINDS)
+@pytest.mark.parametrize("mode", [O.BIND_BLAKE3, O.BIND_PCS, O.BIND_PCS_FULL])
+@pytest.mark.parametrize("m,n", [(4, 4), (5, 7), (16, 12)])
+def test_matmul_binding_modes_roundtrip(mode, m, n, kind):
+    rng = np.random.default_rng(m * 100 + n)
+    w = rng.integers(0, P, m * n, dtype=np.uint32)
+    x = rng.integers(0, P, n, dtype=np.uint32)
+    y = O.matmul_forward(w, x, m, n)
+    plain = O.prove_matmul_succinct(O.Transcript(b"t"), w, x, y, m, n, ef=True)
+    with O.features(mode, kind):
+        assert O.matmul_succinct_roundtrip(w, x, y, m, n, True)
+        assert not O.matmul_succinct_roundtrip(w, x, y, m, n, True, tamper=True)
+        a = O.prove_matmul_succinct(O.Transcript(b"t"), w, x, y, m, n, ef=True)
+    # the default mode ends with basefold_proof = None; the PCS modes append Some(proof)
+    if mode == O.BIND_BLAKE3:
+        assert a == plain and a[-1] == 0
+    else:
+        assert len(a) > len(plain) + 500
+
+
+@pytest.mark.parametrize("mode", [O.BIND_PCS, O.BIND_PCS_FULL])
+def test_qwen_layer_with_basefold_binding_verifies(mode):
+    import hashlib
+    from tests.util import rand_layer, small_table
+    cfg, weights, x = rand_layer(3, 16, 32, 2, 1, 8)
+    tin, silu = small_table(65536, 1)
+    _, sig = small_table(65536, 2)
+    ih = hashlib.sha256(b"in").digest()
+    y0, plain, ok0 = O.qwen_layer_prove(cfg, weights, x, silu, sig, 0, ih, verify=True)
+    with O.features(mode, O.NODE_BLAKE3):
+        y, proof, ok = O.qwen_layer_prove(cfg, weights, x, silu, sig, 0, ih, verify=True)
+    assert ok0 and ok and y.tolist() == y0.tolist()
+    assert len(proof) > len(plain) + 8 * 500

@@ -80,6 +80,14 @@ void zkb_qwen_layer_destroy(zkb_qwen_layer* L) {
     delete L;
 }
 
+// Weight binding used by the layer's eight matmul proofs from now on.
+int32_t zkb_qwen_layer_set_binding(zkb_qwen_layer* L, int32_t bind_mode, int32_t node_hash) {
+    if (!L || bind_mode < BIND_BLAKE3 || bind_mode > BIND_PCS_FULL || (node_hash != NODE_BLAKE3 && node_hash != NODE_AES_MMO)) return ZKB_E_ARG;
+    L->bind_mode = bind_mode;
+    L->node_hash = node_hash;
+    return ZKB_OK;
+}
+
 int32_t zkb_qwen_layer_commitments(zkb_qwen_layer* L, uint8_t roots[256]) {
     if (!L || !roots) return ZKB_E_ARG;
     memcpy(roots, L->roots_host, 256);

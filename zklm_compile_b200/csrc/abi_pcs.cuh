@@ -124,8 +124,8 @@ int32_t zkb_basefold_commit_and_prove(zkb_ctx* c, zkb_transcript* tr, const uint
         BfPending pd = basefold_enqueue(c, tr->dev, CoefSrc{d, 1, (u32)n, log_n}, n, log_n, pt, n_point, node_hash);
         c->rec_fetch();
         Ser s;
-        put_basefold_commitment(s, c, pd);
-        put_basefold_proof(s, c, pd);
+        put_basefold_commitment(s, c->rec_host, pd);
+        put_basefold_proof(s, c->rec_host, pd);
         c->scratch_reset();
         int32_t rc = emit(c, s.b, out, cap, len);
         if (rc) return rc;

@@ -116,8 +116,9 @@ int32_t zkb_matvec_forward(zkb_ctx* c, const uint32_t* W, const uint32_t* x, siz
     });
 }
 
-int32_t zkb_prove_matmul_succinct_ef(zkb_ctx* c, zkb_transcript* t, const uint32_t* W, const uint32_t* x, const uint32_t* y, size_t m,
-                                     size_t n, int32_t w_on_device, uint8_t* out, size_t cap, size_t* len) {
+int32_t zkb_prove_matmul_succinct_ef_bind(zkb_ctx* c, zkb_transcript* t, const uint32_t* W, const uint32_t* x, const uint32_t* y, size_t m,
+                                          size_t n, int32_t w_on_device, int32_t bind_mode, int32_t node_hash, uint8_t* out, size_t cap,
+                                          size_t* len) {
     if (!c || !t || !W || !x || !y || m == 0 || n == 0) return ZKB_E_ARG;
     ZKB_TRY(c, {
         c->use();
@@ -126,7 +127,7 @@ int32_t zkb_prove_matmul_succinct_ef(zkb_ctx* c, zkb_transcript* t, const uint32
         const u32* dW = w_on_device ? W : up_pad(c, W, m * n, m * n);
         u32* dx = up_pad(c, x, n, n_pad);
         u32* dy = up_pad(c, y, m, m);
-        MatmulRec R = prove_matmul_succinct_ef(c, t->dev, dW, dx, dy, (u32)m, (u32)n);
+        MatmulRec R = prove_matmul_succinct_ef(c, t->dev, dW, dx, dy, (u32)m, (u32)n, bind_mode, node_hash);
         c->rec_fetch();
         Ser s; s.rec = c->rec_host;
         put_matmul(s, R, false);
@@ -134,6 +135,10 @@ int32_t zkb_prove_matmul_succinct_ef(zkb_ctx* c, zkb_transcript* t, const uint32
         int32_t rc = emit(c, s.b, out, cap, len);
         if (rc) return rc;
     });
+}
+int32_t zkb_prove_matmul_succinct_ef(zkb_ctx* c, zkb_transcript* t, const uint32_t* W, const uint32_t* x, const uint32_t* y, size_t m,
+                                     size_t n, int32_t w_on_device, uint8_t* out, size_t cap, size_t* len) {
+    return zkb_prove_matmul_succinct_ef_bind(c, t, W, x, y, m, n, w_on_device, BIND_BLAKE3, NODE_BLAKE3, out, cap, len);
 }
 
 int32_t zkb_prove_elementwise_ef(zkb_ctx* c, zkb_transcript* t, int32_t is_add, const uint32_t* a, const uint32_t* b, const uint32_t* cv,

@@ -16,7 +16,7 @@
 // Merkle tree over its output.  The whole opening runs without host round trips: challenges,
 // roots, query positions and the raw authentication paths are written to the proof record.
 #pragma once
-#include "protocols.cuh"
+#include "engine.cuh"
 #include "merkle.cuh"
 #include <map>
 #include <mutex>
@@ -367,6 +367,7 @@ inline BfPending basefold_enqueue(zkb_ctx* c, TrState* tr, CoefSrc src, size_t n
 // BatchMerkleProof (pcs.rs:43-53) of `positions` from raw paths: indices and values in caller
 // order; per level the digests of the siblings that are not themselves known, ascending
 // (pcs.rs:299-330).  raw[i] points at the path record of positions[i].
+template <class Ser>
 inline void put_batch_proof(Ser& s, const std::vector<size_t>& positions, const std::vector<const u32*>& raw, u32 h) {
     s.u64le(positions.size());
     for (size_t p : positions) s.u32le((u32)p);
@@ -391,23 +392,26 @@ inline void put_batch_proof(Ser& s, const std::vector<size_t>& positions, const 
         known.swap(next);
     }
 }
+template <class Ser>
 inline void put_digest(Ser& s, const u32* d) { for (int i = 0; i < 4; i++) s.u32le(d[i]); }
 
 // bincode(BasefoldCommitment) (basefold.rs:39-47)
-inline void put_basefold_commitment(Ser& s, const zkb_ctx* c, const BfPending& pd) {
-    put_digest(s, c->rec_host + pd.root_off);
+template <class Ser>
+inline void put_basefold_commitment(Ser& s, const u32* rec_host, const BfPending& pd) {
+    put_digest(s, rec_host + pd.root_off);
     s.u64le(pd.num_coeffs);
     s.u64le(pd.log_n);
 }
 // bincode(BasefoldOpeningProof) (basefold.rs:50-64)
-inline void put_basefold_proof(Ser& s, const zkb_ctx* c, const BfPending& pd) {
+template <class Ser>
+inline void put_basefold_proof(Ser& s, const u32* rec_host, const BfPending& pd) {
     const u32 log_n = pd.log_n;
     s.u64le(log_n);
-    for (u32 r = 0; r < log_n; r++) put_digest(s, c->rec_host + pd.round_off[r]);
+    for (u32 r = 0; r < log_n; r++) put_digest(s, rec_host + pd.round_off[r]);
     s.u64le(log_n);
     for (u32 r = 0; r < log_n; r++) {
         const u32 h_prev = log_n + 1 - r, h_fold = h_prev - 1;
-        const u32* rec = c->rec_host + pd.round_off[r];
+        const u32* rec = rec_host + pd.round_off[r];
         const u32* idx = rec + 4;
         const size_t prev_half = size_t(1) << (h_prev - 1);
         const size_t pw_prev = 2 + 4 * (size_t)(h_prev - 1), pw_fold = 2 + 4 * (size_t)(h_fold - 1);
@@ -423,7 +427,7 @@ inline void put_basefold_proof(Ser& s, const zkb_ctx* c, const BfPending& pd) {
         put_batch_proof(s, pp, pr, h_prev);
         put_batch_proof(s, fp, fr, h_fold);
     }
-    s.u32le(c->rec_host[pd.final_off]);
+    s.u32le(rec_host[pd.final_off]);
     s.u64le(0);                                   // final_coeffs: empty
 }
 

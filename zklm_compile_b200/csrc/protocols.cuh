@@ -9,7 +9,7 @@
 //   LogUp             rust/zk_ml_prover/src/proving/lookup.rs:643-762
 //   gates             rust/zk_ml_prover/src/proving/sigmoid_gate.rs:90-114, swiglu.rs:99-118
 #pragma once
-#include "engine.cuh"
+#include "basefold.cuh"
 
 namespace zkb {
 
@@ -109,12 +109,21 @@ struct MatmulRec {
     size_t root = 0;     // commitment of w_partial (interleaved coordinates)
     u32 n_pad = 0;
     EvalRec eval;
+    int bind = 0;        // BIND_*; in the PCS modes `bf` holds the Basefold opening and `root` is unused
+    BfPending bf;
 };
+// Weight-binding modes of bind_weights_ef (matmul.rs:360-453): the default build hashes
+// w_partial with blake3; feature pcs commits to w_partial with Basefold; feature pcs-full commits
+// to the row-padded matrix W itself.
+enum BindMode : int { BIND_BLAKE3 = 0, BIND_PCS = 1, BIND_PCS_FULL = 2 };
 struct MatmulScratch { unsigned long long* acc; };
 
 // W: m x n row-major on device; x: n valid of n_pad (zero padded); y: m valid.
-inline MatmulRec prove_matmul_succinct_ef(zkb_ctx* c, TrState* tr, const u32* W, const u32* x, const u32* y, u32 m, u32 n) {
+inline MatmulRec prove_matmul_succinct_ef(zkb_ctx* c, TrState* tr, const u32* W, const u32* x, const u32* y, u32 m, u32 n,
+                                          int bind = BIND_BLAKE3, int node_kind = NODE_BLAKE3) {
     MatmulRec R;
+    if (bind < BIND_BLAKE3 || bind > BIND_PCS_FULL) throw ArgFail{ZKB_E_ARG, "unknown weight-binding mode"};
+    R.bind = bind;
     R.log_m = log2_ceil_u(m); R.log_n = log2_ceil_u(n);
     const size_t m_pad = size_t(1) << R.log_m, n_pad = size_t(1) << R.log_n;
     R.n_pad = (u32)n_pad;
@@ -151,8 +160,23 @@ inline MatmulRec prove_matmul_succinct_ef(zkb_ctx* c, TrState* tr, const u32* W,
     // product sumcheck, full messages                                     (matmul.rs:889-944)
     const u32* tabs[3] = {(const u32*)w_partial, x, nullptr};
     R.sc = sumcheck_enqueue(c, tr, ZKB_SC_PRODUCT_EF_MIXED, tabs, R.log_n);
-    // default binding: blake3 of the interleaved coordinates, absorbed; then the EF MLE-eval
-    R.root = commit_small(c, (const u32*)w_partial, (u32)(4 * n_pad), nullptr, (u32)(4 * n_pad), tr);
+    if (bind == BIND_BLAKE3) {
+        // default binding: blake3 of the interleaved coordinates, absorbed; then the EF MLE-eval
+        R.root = commit_small(c, (const u32*)w_partial, (u32)(4 * n_pad), nullptr, (u32)(4 * n_pad), tr);
+    } else {
+        // Basefold at a base-field point squeezed from the transcript (matmul.rs:372-438), then the
+        // 32-byte commitment root (16-byte Merkle root, zero-padded) is absorbed (matmul.rs:446)
+        CoefSrc src = bind == BIND_PCS_FULL ? CoefSrc{W, m, n, R.log_n} : CoefSrc{(const u32*)w_partial, 1, (u32)(4 * n_pad), R.log_n + 2};
+        const u32 bf_log = bind == BIND_PCS_FULL ? R.log_m + R.log_n : R.log_n + 2;
+        const size_t num_coeffs = bind == BIND_PCS_FULL ? (size_t)m * n : 4 * n_pad;
+        u32* bf_point = (u32*)c->scratch((bf_log + 1) * 4);
+        ScriptBuilder sb;
+        sb.squeeze(bf_point, bf_log);
+        sb.run(c, tr);
+        R.bf = basefold_enqueue(c, tr, src, num_coeffs, bf_log, bf_point, bf_log, node_kind);
+        sb.words_dev(c->rec_dev + R.bf.root_off, 4, 8);
+        sb.run(c, tr);
+    }
     R.eval = prove_mle_eval_ef_ef(c, tr, w_partial, (const Fe*)(c->rec_dev + R.sc.chal), R.log_n);
     return R;
 }
@@ -168,9 +192,21 @@ inline void put_matmul(Ser& s, const MatmulRec& R, bool stripped) {
     }
     put_eval(s, R.eval, !stripped);
     for (int i = 0; i < 4; i++) s.u32le(0);                 // w_claimed_value
-    s.commitment(R.root, 4 * (u64)R.n_pad);                 // w_partial_commitment
-    s.u8(0);                                                // bound
-    s.u8(0);                                                // basefold_proof: None
+    if (R.bind == BIND_BLAKE3) {
+        s.commitment(R.root, 4 * (u64)R.n_pad);             // w_partial_commitment
+        s.u8(0);                                            // bound
+        s.u8(0);                                            // basefold_proof: None
+    } else {
+        // WeightCommitment {root = Merkle root || 16 zero bytes, num_weights, log_height, Blake3Fast} (matmul.rs:393-401)
+        s.words(R.bf.root_off, 4);
+        for (int i = 0; i < 4; i++) s.u32le(0);
+        s.u64le(R.bf.num_coeffs);
+        s.u64le(R.bf.log_n);
+        s.u32le(0);
+        s.u8(0);                                            // bound
+        s.u8(1);                                            // basefold_proof: Some
+        put_basefold_proof(s, s.rec, R.bf);
+    }
 }
 
 // ---- hadamard / add -------------------------------------------------------------------------------

@@ -33,6 +33,7 @@ struct zkb_qwen_layer {
     const zkb::u32* silu = nullptr;       // table output columns (device), shared between layers
     const zkb::u32* sigmoid = nullptr;
     zkb::u32 n_table = 0;
+    int bind_mode = 0, node_hash = 0;     // weight binding of the eight matmul proofs (BIND_*, NODE_*)
     // forward trace (device, each zero-padded to the next power of two)
     zkb::u32 *x = nullptr, *norm1_x = nullptr, *norm1_out = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *attn_out = nullptr,
              *g_raw = nullptr, *g_q = nullptr, *g_sig = nullptr, *gated_attn = nullptr, *gated_out = nullptr, *h = nullptr,
@@ -137,15 +138,15 @@ inline void qwen_prove_enqueue(zkb_qwen_layer* L, u32 layer_idx, const uint8_t i
         sb.run(c, tr);
     }
     P.norm1 = prove_rmsnorm_ef(c, tr, L->norm1_x, L->w[W_NORM1], L->norm1_out, dm, L->n1_scalars);
-    P.mq = prove_matmul_succinct_ef(c, tr, L->w[W_Q], L->norm1_out, L->q, d.q_dim(), dm);
-    P.mk = prove_matmul_succinct_ef(c, tr, L->w[W_K], L->norm1_out, L->k, d.k_dim(), dm);
-    P.mv = prove_matmul_succinct_ef(c, tr, L->w[W_V], L->norm1_out, L->v, d.v_dim(), dm);
+    P.mq = prove_matmul_succinct_ef(c, tr, L->w[W_Q], L->norm1_out, L->q, d.q_dim(), dm, L->bind_mode, L->node_hash);
+    P.mk = prove_matmul_succinct_ef(c, tr, L->w[W_K], L->norm1_out, L->k, d.k_dim(), dm, L->bind_mode, L->node_hash);
+    P.mv = prove_matmul_succinct_ef(c, tr, L->w[W_V], L->norm1_out, L->v, d.v_dim(), dm, L->bind_mode, L->node_hash);
     P.seq1 = c->rec_alloc(2);
     seq1_consistency_kernel<<<1, 1024, 0, c->stream>>>(tr, L->attn_out, aod, log2_ceil_u(aod), L->v, d.v_dim(), log2_ceil_u(d.v_dim()),
                                                       d.is_gqa() ? 1u : 0u, log2_ceil_u(d.nkv), log2_ceil_u(d.d_head), c->rec_dev + P.seq1);
     ZKB_LAUNCHED(c);
-    P.mo = prove_matmul_succinct_ef(c, tr, L->w[W_O], L->gated_attn, L->gated_out, dm, aod);
-    P.mg = prove_matmul_succinct_ef(c, tr, L->w[W_GPROJ], L->norm1_out, L->g_raw, aod, dm);
+    P.mo = prove_matmul_succinct_ef(c, tr, L->w[W_O], L->gated_attn, L->gated_out, dm, aod, L->bind_mode, L->node_hash);
+    P.mg = prove_matmul_succinct_ef(c, tr, L->w[W_GPROJ], L->norm1_out, L->g_raw, aod, dm, L->bind_mode, L->node_hash);
     // prove_sigmoid_gate_ef(gate = g_q, gate_sigmoid = g_sig, input = attn_out, output = gated_attn)
     P.sig_gate = prove_gate_ef(c, tr, L->sigmoid, L->n_table, L->g_q, L->g_sig, L->attn_out, L->g_sig, L->gated_attn, aod);
     const u32 log_d = log2_ceil_u(dm);
@@ -153,11 +154,11 @@ inline void qwen_prove_enqueue(zkb_qwen_layer* L, u32 layer_idx, const uint8_t i
     { ScriptBuilder sb; sb.squeeze(c->rec_dev + P.res1_point, 4 * log_d); sb.run(c, tr); }
     P.res1 = prove_add_ef(c, tr, L->x, L->gated_out, L->h, dm, (const Fe*)(c->rec_dev + P.res1_point), log_d);
     P.norm2 = prove_rmsnorm_ef(c, tr, L->norm2_x, L->w[W_NORM2], L->norm2_out, dm, L->n2_scalars);
-    P.mgate = prove_matmul_succinct_ef(c, tr, L->w[W_GATE], L->norm2_out, L->gate_raw, d.d_ff, dm);
-    P.mup = prove_matmul_succinct_ef(c, tr, L->w[W_UP], L->norm2_out, L->up, d.d_ff, dm);
+    P.mgate = prove_matmul_succinct_ef(c, tr, L->w[W_GATE], L->norm2_out, L->gate_raw, d.d_ff, dm, L->bind_mode, L->node_hash);
+    P.mup = prove_matmul_succinct_ef(c, tr, L->w[W_UP], L->norm2_out, L->up, d.d_ff, dm, L->bind_mode, L->node_hash);
     // prove_swiglu_ef(gate = gate_q, gate_silu, up, output = swiglu): hadamard(gate_silu, up)
     P.swiglu = prove_gate_ef(c, tr, L->silu, L->n_table, L->gate_q, L->gate_silu, L->gate_silu, L->up, L->swiglu, d.d_ff);
-    P.mdown = prove_matmul_succinct_ef(c, tr, L->w[W_DOWN], L->swiglu, L->down, dm, d.d_ff);
+    P.mdown = prove_matmul_succinct_ef(c, tr, L->w[W_DOWN], L->swiglu, L->down, dm, d.d_ff, L->bind_mode, L->node_hash);
     P.res2_point = c->rec_alloc(4 * (size_t)log_d);
     { ScriptBuilder sb; sb.squeeze(c->rec_dev + P.res2_point, 4 * log_d); sb.run(c, tr); }
     P.res2 = prove_add_ef(c, tr, L->h, L->down, L->out, dm, (const Fe*)(c->rec_dev + P.res2_point), log_d);

@@ -104,8 +104,13 @@ def rmsnorm_forward(ctx: Context, x, gamma):
     return out, xu, delta.value
 
 
-def prove_matmul_succinct_ef(w_flat, x_vals, y_vals, m: int, n: int, transcript: Transcript) -> bytes:
-    """matmul.rs:963-997 -> SuccinctMatmulProofEF."""
+BIND_BLAKE3, BIND_PCS, BIND_PCS_FULL = 0, 1, 2
+
+
+def prove_matmul_succinct_ef(w_flat, x_vals, y_vals, m: int, n: int, transcript: Transcript, bind_mode: int = BIND_BLAKE3,
+                             node_hash: int = 0) -> bytes:
+    """matmul.rs:963-997 -> SuccinctMatmulProofEF.  bind_mode selects what the reference fixes at
+    compile time (bind_weights_ef, matmul.rs:360-453): default build, feature pcs, feature pcs-full."""
     ctx = transcript.ctx
     x, px = _a(x_vals)
     y, py = _a(y_vals)
@@ -114,8 +119,8 @@ def prove_matmul_succinct_ef(w_flat, x_vals, y_vals, m: int, n: int, transcript:
     else:
         w, pw = _a(w_flat)
         on = 0
-    return _proof_call(ctx, _lib.lib().zkb_prove_matmul_succinct_ef, ctx.h, transcript.h, pw, px, py, C.c_size_t(m), C.c_size_t(n),
-                       C.c_int32(on))
+    return _proof_call(ctx, _lib.lib().zkb_prove_matmul_succinct_ef_bind, ctx.h, transcript.h, pw, px, py, C.c_size_t(m), C.c_size_t(n),
+                       C.c_int32(on), C.c_int32(bind_mode), C.c_int32(node_hash))
 
 
 def _elementwise(is_add, a, b, c, point, transcript):

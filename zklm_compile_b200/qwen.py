@@ -90,6 +90,11 @@ class QwenLayer:
             self._x_keep = np.ascontiguousarray(x, dtype=np.uint32)
             check(self.ctx.h, _lib.lib().zkb_qwen_layer_forward_async(self.h, None, self._x_keep.ctypes.data_as(u32p), C.c_int32(0)))
 
+    def set_binding(self, bind_mode: int, node_hash: int = 0):
+        """Weight binding of the matmul proofs: 0 default build, 1 feature pcs, 2 feature pcs-full
+        (bind_weights_ef, rust/zk_ml_prover/src/proving/matmul.rs:360-453)."""
+        check(self.ctx.h, _lib.lib().zkb_qwen_layer_set_binding(self.h, C.c_int32(bind_mode), C.c_int32(node_hash)))
+
     def read_output_after_forward(self) -> np.ndarray:
         """Output of an asynchronous forward, without waiting for a proof queued behind it."""
         y = np.zeros(self.d_model, np.uint32)
