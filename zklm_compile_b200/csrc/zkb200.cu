@@ -41,7 +41,7 @@ int32_t zkb_ctx_create(int32_t device, zkb_ctx** out) {
         ZKB_CUDA(cudaMemsetAsync(c->counter, 0, 64, c->stream));
         ZKB_CUDA(cudaMalloc(&c->status, 64));
         ZKB_CUDA(cudaMemsetAsync(c->status, 0, 64, c->stream));
-        c->rec_cap = size_t(1) << 20;                       // 4 MiB of proof record
+        c->rec_cap = size_t(1) << 21;                       // 8 MiB of proof record (a layer with eight Basefold openings needs ~4)
         ZKB_CUDA(cudaMalloc(&c->rec_dev, c->rec_cap * 4));
         ZKB_CUDA(cudaHostAlloc(&c->rec_host, c->rec_cap * 4, cudaHostAllocDefault));
         ZKB_CUDA(cudaEventCreate(&c->t0));
