@@ -18,6 +18,7 @@
 #pragma once
 #include "engine.cuh"
 #include "merkle.cuh"
+#include <algorithm>
 #include <map>
 #include <mutex>
 
@@ -323,9 +324,12 @@ inline BfPending basefold_enqueue(zkb_ctx* c, TrState* tr, CoefSrc src, size_t n
     uint4* treeB = (uint4*)c->scratch(mk_node_count(log_n) * 16 + 16);
     u32* alpha = (u32*)c->scratch((log_n + 1) * 4);
 
+    c->prof_mark();
     bf_encode(c, src, log_n, tb, cwA);
+    c->prof_mark();
     MkFold none{};
     mk_build(c, kind, MK_VALUES, cwA, 2 * n_pad, log_n + 1, treeA, none);
+    c->prof_mark();
     pd.root_off = c->rec_alloc(4);
     bf_begin_kernel<<<1, 1, 0, c->stream>>>(tr, treeA + mk_layer_offset(log_n + 1, log_n + 1), point_dev, n_point, alpha, c->rec_dev + pd.root_off);
     ZKB_LAUNCHED(c);
@@ -345,6 +349,7 @@ inline BfPending basefold_enqueue(zkb_ctx* c, TrState* tr, CoefSrc src, size_t n
         f.coef = src.p; f.coef_rows = src.rows; f.coef_cols = src.cols; f.coef_log_cols_pad = src.log_cols_pad;
         f.eval_from_coef = round == 0;
         mk_build(c, kind, MK_FOLD, nullptr, half, h_prev - 1, next_tree, f);
+        c->prof_mark();
         BfRound rp{};
         rp.tr = tr; rp.point = point_dev; rp.n_point = n_point; rp.round = round; rp.log_n = log_n;
         rp.alpha_next = round + 1 < log_n ? alpha + round + 1 : nullptr;
@@ -355,6 +360,7 @@ inline BfPending basefold_enqueue(zkb_ctx* c, TrState* tr, CoefSrc src, size_t n
         pd.round_off.push_back(off);
         bf_round_kernel<<<1, 256, 0, c->stream>>>(rp);
         ZKB_LAUNCHED(c);
+        c->prof_mark();
         std::swap(prev_cw, next_cw);
         std::swap(prev_tree, next_tree);
     }
@@ -373,16 +379,23 @@ inline void put_batch_proof(Ser& s, const std::vector<size_t>& positions, const 
     for (size_t p : positions) s.u32le((u32)p);
     s.u64le(positions.size());
     for (const u32* r : raw) s.u32le(r[0]);
-    std::map<size_t, size_t> known;            // node index at the current level -> a position that lies below it
-    for (size_t i = 0; i < positions.size(); i++) known.emplace(positions[i], i);
+    // (node index at the current level, a position that lies below it), ascending and unique
+    std::vector<std::pair<size_t, size_t>> known, next;
+    known.reserve(positions.size());
+    for (size_t i = 0; i < positions.size(); i++) known.emplace_back(positions[i], i);
+    std::sort(known.begin(), known.end());
+    known.erase(std::unique(known.begin(), known.end(), [](auto& a, auto& b) { return a.first == b.first; }), known.end());
     s.u64le(h);
+    std::vector<const u32*> lvl;
     for (u32 k = 0; k < h; k++) {
-        std::vector<const u32*> lvl;
-        std::vector<bool> leaf;
-        std::map<size_t, size_t> next;
-        for (auto& kv : known) {
-            next.emplace(kv.first >> 1, kv.second);
-            if (!known.count(kv.first ^ 1)) lvl.push_back(k == 0 ? raw[kv.second] + 1 : raw[kv.second] + 2 + 4 * (size_t)(k - 1));
+        lvl.clear();
+        next.clear();
+        for (size_t i = 0; i < known.size(); i++) {
+            const size_t node = known[i].first;
+            // the sibling, if known, is the neighbour in the sorted list
+            const bool sib_known = (node & 1) ? (i > 0 && known[i - 1].first == node - 1) : (i + 1 < known.size() && known[i + 1].first == node + 1);
+            if (!sib_known) lvl.push_back(k == 0 ? raw[known[i].second] + 1 : raw[known[i].second] + 2 + 4 * (size_t)(k - 1));
+            if (next.empty() || next.back().first != (node >> 1)) next.emplace_back(node >> 1, known[i].second);
         }
         s.u64le(lvl.size());
         for (const u32* d : lvl) {

@@ -55,9 +55,14 @@ def basefold_tables(ctx: Context, log_n: int):
     return t, w
 
 
-def basefold_encode(ctx: Context, coeffs) -> np.ndarray:
-    """encode, basefold.rs:169-238 (coefficients zero-padded to a power of two, at least 2)."""
+def basefold_encode(ctx: Context, coeffs, out: DeviceBuffer = None):
+    """encode, basefold.rs:169-238 (coefficients zero-padded to a power of two, at least 2).
+    With `out` (a device buffer of 2 * 2^log_n words) the codeword stays on the device."""
     keep, p, n, dev = _src(coeffs)
+    if out is not None:
+        assert out.n >= 2 << log2_ceil(n)
+        check(ctx.h, _lib.lib().zkb_basefold_encode(ctx.h, p, C.c_size_t(n), C.c_int32(dev), out.ptr, C.c_int32(1)))
+        return out
     cw = np.zeros(2 << log2_ceil(n), np.uint32)
     check(ctx.h, _lib.lib().zkb_basefold_encode(ctx.h, p, C.c_size_t(n), C.c_int32(dev), cw.ctypes.data_as(u32p), C.c_int32(0)))
     return cw

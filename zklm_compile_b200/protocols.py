@@ -32,7 +32,7 @@ def _proof_call(ctx: Context, fn, *args, cap: int = 1 << 22) -> bytes:
     if st == 7 and n.value > cap:
         return _proof_call(ctx, fn, *args, cap=n.value)
     check(ctx.h, st)
-    return bytes(buf[:n.value])
+    return C.string_at(buf, n.value)
 
 
 def commit_weights_fast(ctx: Context, weights) -> bytes:

@@ -94,6 +94,7 @@ class QwenLayer:
         """Weight binding of the matmul proofs: 0 default build, 1 feature pcs, 2 feature pcs-full
         (bind_weights_ef, rust/zk_ml_prover/src/proving/matmul.rs:360-453)."""
         check(self.ctx.h, _lib.lib().zkb_qwen_layer_set_binding(self.h, C.c_int32(bind_mode), C.c_int32(node_hash)))
+        self._bind_mode = bind_mode
 
     def read_output_after_forward(self) -> np.ndarray:
         """Output of an asynchronous forward, without waiting for a proof queued behind it."""
@@ -112,11 +113,18 @@ class QwenLayer:
         ih = (C.c_uint8 * 32).from_buffer_copy(input_hash)
         check(self.ctx.h, _lib.lib().zkb_qwen_layer_prove_begin(self.h, C.c_uint32(layer_idx), ih))
 
-    def prove_end(self, cap: int = 1 << 20) -> bytes:
-        buf = (C.c_uint8 * cap)()
+    def prove_end(self, cap: int = None) -> bytes:
+        if cap is None:      # eight Basefold openings make a layer proof of a few MB
+            cap = (1 << 20) if getattr(self, "_bind_mode", 0) == 0 else (1 << 24)
+        buf = getattr(self, "_proof_buf", None)
+        if buf is None or len(buf) < cap:
+            buf = self._proof_buf = (C.c_uint8 * cap)()
         n = C.c_size_t()
-        check(self.ctx.h, _lib.lib().zkb_qwen_layer_prove_end(self.h, buf, C.c_size_t(cap), C.byref(n)))
-        return bytes(buf[:n.value])
+        st = _lib.lib().zkb_qwen_layer_prove_end(self.h, buf, C.c_size_t(len(buf)), C.byref(n))
+        if st == 7 and n.value > len(buf):
+            raise _lib.ZkbError(7, f"layer proof needs {n.value} bytes; call prove_end(cap=...) with a larger buffer")
+        check(self.ctx.h, st)
+        return C.string_at(buf, n.value)
 
     def prove(self, layer_idx: int, input_hash: bytes) -> bytes:
         """QwenLayerProofEF as bincode bytes; `forward` must have run."""
