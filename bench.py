@@ -242,6 +242,40 @@ def run_sumcheck(zk, ctx, n, steps, warmup, rank, with_e2e, barrier=lambda: None
 # ------------------------------------------------------------------------------------------------
 # workload: Qwen3.5-4B-shape end-to-end prove
 # ------------------------------------------------------------------------------------------------
+def run_basefold(zk, ctx, n, reps=3):
+    """Basefold commitment + opening of one 2^n-coefficient table (the microbench config's
+    'Basefold commitment of f').  Algorithmic bytes: encode = n levels x (read + write of the 2^(n+1)
+    codeword); Merkle = read of the codeword + write of all digests."""
+    from zklm_compile_b200 import pcs as zp
+    rng = np.random.default_rng(1000 + n)
+    N = 1 << n
+    coeffs = ctx.upload(rng.integers(0, P, N, dtype=np.int64).astype(np.uint32))
+    point = ctx.upload(rng.integers(0, P, n, dtype=np.int64).astype(np.uint32))
+    cw = ctx.alloc(2 * N)
+    out = {"n": n, "node_hash": {}}
+    zp.basefold_encode(ctx, coeffs, out=cw)                    # generates and caches the tables
+    t_enc = []
+    for _ in range(reps):
+        ctx.timer_start(); zp.basefold_encode(ctx, coeffs, out=cw); t_enc.append(ctx.timer_stop_ms())
+    enc_ms = min(t_enc)
+    enc_bytes = n * 2 * (2 * N * 4)
+    out["encode_ms"] = round(enc_ms, 4)
+    out["encode_algorithmic_GBps"] = round(enc_bytes / enc_ms / 1e6, 1)
+    for name, kind in (("blake3", 0), ("aes_mmo", 1)):
+        t_mk, t_all = [], []
+        for _ in range(reps):
+            ctx.timer_start(); zp.merkle_root(ctx, cw, kind); t_mk.append(ctx.timer_stop_ms())
+            tr = zk.Transcript(ctx, b"bench-basefold")
+            ctx.timer_start(); blob = zp.basefold_commit_and_prove(ctx, tr, coeffs, point, kind); t_all.append(ctx.timer_stop_ms())
+        mk_bytes = 2 * N * 4 + (2 * N - 1) * 16
+        out["node_hash"][name] = {"merkle_ms": round(min(t_mk), 4), "merkle_GBps": round(mk_bytes / min(t_mk) / 1e6, 1),
+                                  "merkle_Mnodes_per_s": round((2 * N - 1) / min(t_mk) / 1e3, 1),
+                                  "commit_and_prove_ms": round(min(t_all), 3), "proof_bytes": len(blob)}
+    for b in (coeffs, point, cw):
+        b.free()
+    return out
+
+
 def run_qwen(zk, args, rank, world, local, dist, barrier, max_over_ranks):
     import torch  # only for the inter-rank hop of the activation vector and the proof gather
     from zklm_compile_b200 import qwen as zq, sharding, tables
@@ -361,6 +395,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--n-basefold", type=int, default=24, help="log2 coefficient count of the attached Basefold commitment")
     ap.add_argument("--no-micro", action="store_true")
     args = ap.parse_args()
     if args.impl == "ours":
@@ -454,10 +489,13 @@ def main():
         line.update({"value": r["value_gbps"], "ms_per_step": r["ms_per_step"], "scaling": "weak", "vs_baseline": None,
                      "roofline": r["roofline"], "e2e": r.get("e2e"), "gpu_launches": r["gpu_launches"], "clocks": sampler.stop(),
                      "algorithmic_bytes_per_step": r["algorithmic_bytes_per_step"]})
+        if not args.no_micro and rank == 0:
+            line["basefold_microbench"] = run_basefold(zk, micro_ctx, args.n_basefold)
     if qwen and not args.no_micro and rank == 0:
         m = run_sumcheck(zk, micro_ctx, args.n_micro, 5, 3, 0, False)
         line["sumcheck_microbench"] = {"metric": "sumcheck fold HBM GB/s", "n": m["n"], "value": m["value_gbps"], "unit": "GB/s",
                                        "ms_per_step": m["ms_per_step"], "roofline": m["roofline"]}
+        line["basefold_microbench"] = run_basefold(zk, micro_ctx, args.n_basefold)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         if qwen:
