@@ -37,7 +37,8 @@ enum {
     ZKB_E_ALPHA_COLLISION = 4,  /* "alpha collision with lookup/table encoding" (lookup.rs:550-555, 712-717) */
     ZKB_E_NOT_QR = 5,       /* "compute_r: d/sum_sq is not a quadratic residue" (transformer/mod.rs:182) */
     ZKB_E_LENGTH = 6,       /* a length assertion of the reference failed (matmul.rs:161, 861) */
-    ZKB_E_TOO_LARGE = 7     /* request exceeds a documented fixed capacity */
+    ZKB_E_TOO_LARGE = 7,    /* request exceeds a documented fixed capacity */
+    ZKB_E_TIMEOUT = 8       /* a peer GPU of a split sumcheck did not answer within the exchange's time limit */
 };
 
 /* Sumcheck prover kinds; one per reference function. */
@@ -186,6 +187,30 @@ int32_t zkb_qwen_layer_prove_begin(zkb_qwen_layer* layer, uint32_t layer_idx, co
 int32_t zkb_qwen_layer_prove_end(zkb_qwen_layer* layer, uint8_t* out, size_t cap, size_t* len);
 int32_t zkb_qwen_layer_prove(zkb_qwen_layer* layer, uint32_t layer_idx, const uint8_t input_hash[32], uint8_t* out, size_t cap,
                              size_t* len);
+
+/* ---- one sumcheck split over several GPUs (one process per GPU) ----------------------------
+ * No counterpart in the reference, which proves on one machine's cores; this is how a table
+ * too large or too slow for one GPU is proved by `world` GPUs (a power of two, at most 8).
+ * Rank g holds the elements j with j mod world == g of every table, stored contiguously.
+ * Folding is MSB-first, so all but the last log2(world) rounds fold pairs that live on one GPU;
+ * per round only the three or four partial sums cross NVLink, written by the round kernel
+ * itself into mailboxes in the peers' memory, and every rank advances an identical transcript.
+ * Set-up: every rank calls zkb_xch_create and zkb_xch_handle, the caller carries the 64-byte
+ * handles between the processes (e.g. an all-gather), every rank calls zkb_xch_connect with
+ * all of them.  A rank whose peer does not answer within the time limit (default 4 s) gets
+ * ZKB_E_TIMEOUT instead of a proof; the exchange object is then unusable. */
+typedef struct zkb_xch zkb_xch;
+int32_t zkb_xch_create(zkb_ctx* ctx, uint32_t world, uint32_t rank, zkb_xch** out);
+int32_t zkb_xch_handle(zkb_xch* xch, uint8_t handle[64]);
+int32_t zkb_xch_connect(zkb_xch* xch, const uint8_t* handles /* world x 64 bytes */);
+int32_t zkb_xch_set_timeout_ms(zkb_xch* xch, uint32_t ms);
+void zkb_xch_destroy(zkb_xch* xch);
+/* zkb_sumcheck_prove over tables of 2^num_vars elements of which this rank passes its slice of
+ * 2^num_vars / world elements.  Every rank makes the same call with transcripts in the same
+ * state; every rank receives the complete proof (identical to the single-GPU one) and ends
+ * with the same transcript state. */
+int32_t zkb_sumcheck_prove_split(zkb_ctx* ctx, zkb_xch* xch, zkb_transcript* tr, int32_t kind, const uint32_t* const* tables,
+                                 uint32_t num_vars, int32_t on_device, uint32_t* round_polys, uint32_t* challenges, uint32_t* finals);
 
 /* ---- Merkle trees and the Basefold commitment (features pcs / pcs-full of the reference) -------
  * Digests are 16 bytes.  node_hash selects the reference's hash_node variant

@@ -45,6 +45,8 @@ struct ScOpts {
     const u32* dyn_nv = nullptr;
     long dyn_off = -1;
     bool check_zero_sum = false;
+    const ScXch* xch = nullptr;    // device copy of the exchange descriptor: `tables_dev` are this GPU's slices
+    u32 xch_world = 1;
 };
 
 inline int grid_for(zkb_ctx* c, size_t items, int per_cta = 256, int ctas_per_sm = 8) {
@@ -57,13 +59,15 @@ inline int grid_for(zkb_ctx* c, size_t items, int per_cta = 256, int ctas_per_sm
 
 template <int KIND, class SrcT, class ChalT>
 void run_sumcheck(zkb_ctx* c, ScTables tb, u32 num_vars, ScIO io, bool dynamic) {
-    size_t size = size_t(1) << num_vars;
+    // split over several GPUs: the tables are this GPU's slice of 2^local_vars elements
+    const u32 local_vars = io.xch ? io.xch_local_vars : num_vars;
+    size_t size = size_t(1) << local_vars;
     bool pending = false, in_src = true;
     u32 round = 0;
     const int max_grid = c->sm_count * 8 < SC_MAX_GRID ? c->sm_count * 8 : SC_MAX_GRID;
     c->prof_used = 0;
     c->prof_mark();
-    while (!dynamic && round < num_vars) {
+    while (!dynamic && round < local_vars) {
         size_t half = pending ? size / 4 : size / 2;
         if (half < MULTI_MIN_HALF) break;
         size_t want = (half + 255) / 256;
@@ -113,7 +117,12 @@ __global__ void widen_kernel(const u32* __restrict__ in, Fe* out, size_t n) {
 inline ScRec sumcheck_enqueue(zkb_ctx* c, TrState* tr, int kind, const u32* const* tables_dev, u32 num_vars, const ScOpts& o = ScOpts()) {
     KindInfo ki = kind_info(kind);
     if (num_vars < 1 || num_vars > 34) throw ArgFail{ZKB_E_ARG, "num_vars out of range"};
-    const size_t n = size_t(1) << num_vars;
+    u32 log_world = 0;
+    while ((1u << log_world) < o.xch_world) log_world++;
+    if (o.xch && ((1u << log_world) != o.xch_world || num_vars < log_world + 1 || o.dyn_nv))
+        throw ArgFail{ZKB_E_ARG, "split sumcheck: world must be a power of two below 2^num_vars, static round count"};
+    const u32 local_vars = o.xch ? num_vars - log_world : num_vars;
+    const size_t n = size_t(1) << local_vars;      // elements per table held by this GPU
     const bool ef_inputs = ki.in_w[0] == 4;
     ScTables tb{};
     const size_t dst_elems = n / 2 > 2 ? n / 2 : 2;
@@ -142,6 +151,7 @@ inline ScRec sumcheck_enqueue(zkb_ctx* c, TrState* tr, int kind, const u32* cons
     io.post_squeezes = o.post_squeezes;
     io.post_out = o.post_off >= 0 ? c->rec_dev + o.post_off : nullptr;
     io.check_zero_sum = o.check_zero_sum ? 1u : 0u;
+    io.xch = o.xch; io.xch_local_vars = local_vars;
     const bool dyn = o.dyn_nv != nullptr;
     switch (kind) {
         case ZKB_SC_PRODUCT:              run_sumcheck<SC_PRODUCT, Fp, Fp>(c, tb, num_vars, io, dyn); break;

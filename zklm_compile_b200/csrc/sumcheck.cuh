@@ -17,6 +17,7 @@
 #pragma once
 #include "m31.cuh"
 #include "transcript.cuh"
+#include "exchange.cuh"
 
 namespace zkb {
 
@@ -55,6 +56,12 @@ struct ScIO {
     u32* post_out;          // optional destination of the post-squeezed challenges
     u32 post_squeezes;      // base-field squeezes performed right after the final evaluations
     u32 check_zero_sum;     // nonzero: flag status = 3 unless round 0 has s0 + s1 == 0 (LogUp identity)
+    // Sumcheck split over several GPUs (see exchange.cuh): the tables given to the kernels are
+    // this GPU's slice, `round` counts global rounds, the first xch_local_vars rounds are local
+    // ones whose sums are exchanged, then the per-GPU remainders are gathered and the last
+    // log2(world) rounds run identically on every GPU.  Null for an ordinary sumcheck.
+    const ScXch* xch;
+    u32 xch_local_vars;
 };
 __device__ __forceinline__ bool is_zero_el(Fp a) { return a.v == 0; }
 __device__ __forceinline__ bool is_zero_el(Fe a) { return (a.x | a.y | a.z | a.w) == 0; }
@@ -223,6 +230,7 @@ __global__ void __launch_bounds__(256) sc_round_kernel(ScTables tb, size_t half,
     }
     block_sum_words<NW>(t, red);
     if (threadIdx.x == 0) {
+        if (io.xch) xch_allreduce<NW>(*io.xch, io.xch->seq + round, t);
         Tr tr;
         tr_load(tr, io.tr, trbuf);
         sc_finish_round<KIND, AccT, ChalT>(t, io, round, tr);
@@ -325,6 +333,7 @@ __global__ void __launch_bounds__(256) sc_product_base_kernel(ScTables tb, size_
     }
     block_sum_words<NACC>(t, red);
     if (threadIdx.x == 0) {
+        if (io.xch) xch_allreduce<NACC>(*io.xch, io.xch->seq + round, t);
         Tr tr;
         tr_load(tr, io.tr, trbuf);
         if constexpr (FOLD) {
@@ -366,7 +375,13 @@ __global__ void __launch_bounds__(SC_TAIL_THREADS) sc_tail_kernel(ScTables tb, s
     bool in_src = true;           // tables still in their input buffers / input type
     ScTables cur = tb;
 
-    for (; round < num_vars; round++) {
+    // Split sumcheck: phase 0 runs the local rounds (sums exchanged), then the per-GPU remainders
+    // are gathered into `world`-element tables in shared memory and phase 1 runs the last rounds.
+    __shared__ __align__(16) u32 gathered[3][XCH_MAX_WORLD * 4];
+    const bool split = io.xch != nullptr && io.xch->world > 1;
+    u32 stop = split ? io.xch_local_vars : num_vars;
+    for (int phase = 0; phase < 2; phase++) {
+    for (; round < stop; round++) {
         u32 w[16];
         if (in_src) {
             if (!pending) {
@@ -394,13 +409,18 @@ __global__ void __launch_bounds__(SC_TAIL_THREADS) sc_tail_kernel(ScTables tb, s
             ChalT acc[NACC];
 #pragma unroll
             for (int k = 0; k < NACC; k++) acc[k] = zero_of<ChalT>();
-            sc_pass<KIND, ChalT, ChalT, true>(cur, size / 4, r, threadIdx.x, blockDim.x, acc);
+            if (pending) {
+                sc_pass<KIND, ChalT, ChalT, true>(cur, size / 4, r, threadIdx.x, blockDim.x, acc);
+                size /= 2;
+            } else {
+                sc_pass<KIND, ChalT, ChalT, false>(cur, size / 2, r, threadIdx.x, blockDim.x, acc);
+            }
 #pragma unroll
             for (int k = 0; k < NACC; k++) to_words(acc[k], w + k * WC);
-            size /= 2;
         }
         block_sum_words<NACC * WC>(w, red);
         if (threadIdx.x == 0) {
+            if (io.xch && phase == 0) xch_allreduce<NACC * WC>(*io.xch, io.xch->seq + round, w);
             ChalT rn = sc_finish_round<KIND, ChalT, ChalT>(w, io, round, tr);
             to_words(rn, r_sh);
         }
@@ -408,6 +428,40 @@ __global__ void __launch_bounds__(SC_TAIL_THREADS) sc_tail_kernel(ScTables tb, s
         from_words(r, r_sh);
         pending = 1;
         __syncthreads();
+    }
+    if (!split || phase == 1) break;
+    // size == 2: fold the last local challenge in, gather everybody's remainder (ordered by rank =
+    // the low index bits), and continue on the gathered tables with nothing pending.
+    if (threadIdx.x == 0) {
+        u32 mine[NT * WC];
+#pragma unroll
+        for (int t = 0; t < NT; t++) {
+            ChalT v;
+            if (in_src) v = lerp(ld_el<SrcT>(cur.src[t], 0), ld_el<SrcT>(cur.src[t], 1), r);
+            else {
+                ChalT a = ld_el<ChalT>(cur.src[t], 0), b = ld_el<ChalT>(cur.src[t], 1);
+                v = a + r * (b - a);
+            }
+            to_words(v, mine + t * WC);
+        }
+        u32 all[XCH_MAX_WORLD * NT * WC];
+        const u32 world = io.xch->world;
+        if (xch_allgather(*io.xch, io.xch->seq + io.xch_local_vars, mine, NT * WC, all)) {
+            for (u32 sdr = 0; sdr < world; sdr++)
+                for (int t = 0; t < NT; t++)
+                    for (int k = 0; k < WC; k++) gathered[t][sdr * WC + k] = all[sdr * NT * WC + t * WC + k];
+        } else {
+            for (int t = 0; t < NT; t++)
+                for (u32 k = 0; k < world * WC; k++) gathered[t][k] = 0;
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int t = 0; t < NT; t++) { cur.src[t] = gathered[t]; cur.dst[t] = gathered[t]; }
+    in_src = false;
+    pending = 0;
+    size = io.xch->world;
+    stop = num_vars;
     }
 
     if (threadIdx.x == 0) {

@@ -326,6 +326,7 @@ int32_t zkb_sumcheck_prove(zkb_ctx* c, zkb_transcript* t, int32_t kind, const ui
 #include "abi_protocols.cuh"
 #include "abi_layer.cuh"
 #include "abi_pcs.cuh"
+#include "abi_split.cuh"
 
 // =============================================================================================
 // Allocation-free weight fold
