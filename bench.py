@@ -239,6 +239,80 @@ def run_sumcheck(zk, ctx, n, steps, warmup, rank, with_e2e, barrier=lambda: None
     return res
 
 
+def run_sumcheck_split(zk, ctx, n, steps, warmup, rank, world, with_e2e, barrier, max_over_ranks, dist):
+    """One product sumcheck over two 2^n-element tables split over `world` GPUs (rank g owns the
+    elements j = g mod world); strong scaling: value = 72 * 2^n bytes / time of the slowest rank."""
+    import hashlib
+    from zklm_compile_b200 import split as zs
+    xch = zs.Exchange(ctx, world, rank)
+    N_local = (1 << n) // world
+    rng = np.random.default_rng(20251125 + rank)
+    f_host, g_host = ctx.pinned_u32(N_local), ctx.pinned_u32(N_local)
+    chunk = 1 << 24
+    for off in range(0, N_local, chunk):
+        m = min(chunk, N_local - off)
+        f_host[off:off + m] = rng.integers(0, P, m, dtype=np.int64).astype(np.uint32)
+        g_host[off:off + m] = rng.integers(0, P, m, dtype=np.int64).astype(np.uint32)
+    f_dev, g_dev = ctx.upload(f_host), ctx.upload(g_host)
+    per_launch_bytes, total_bytes = algorithmic_bytes(n)
+
+    def step(tabs):
+        return zs.sumcheck_prove_split(zk.SC_PRODUCT_EF, list(tabs), n, zk.Transcript(ctx, b"bench-product"), xch)
+
+    for _ in range(warmup):
+        ref = step((f_dev, g_dev))
+    ctx.profile(True)
+    ctx.sync(); barrier()
+    launches0, prof_acc = ctx.launches, None
+    ctx.timer_start()
+    for _ in range(steps):
+        out = step((f_dev, g_dev))
+        pr = np.array(ctx.profile_read())
+        prof_acc = pr if prof_acc is None else prof_acc + pr
+    ms_total = ctx.timer_stop_ms()
+    ctx.sync(); barrier()
+    launches = ctx.launches - launches0
+    ctx.profile(False)
+    assert out[0].round_polys.tolist() == ref[0].round_polys.tolist()
+    # every rank must hold the same proof
+    digest = hashlib.sha256(out[0].round_polys.tobytes() + out[0].challenges.tobytes()).hexdigest()
+    if dist is not None:
+        allv = [None] * world
+        dist.all_gather_object(allv, digest)
+        assert len(set(allv)) == 1, "ranks disagree on the proof"
+    ms_step = max_over_ranks(ms_total / steps)
+    prof = (prof_acc / steps).tolist()
+    fold = [(per_launch_bytes[i - 1] / world / (prof[i] * 1e-3) / 1e9, prof[i], i) for i in range(1, len(prof) - 1) if prof[i] > 0]
+    dom = max(fold, key=lambda t: t[1]) if fold else (0.0, 0.0, 0)
+    peak, src = load_peaks()
+    res = {"n": n, "value_gbps": round(total_bytes / (ms_step * 1e-3) / 1e9, 2), "ms_per_step": round(ms_step, 4),
+           "gpu_launches": int(launches), "algorithmic_bytes_per_step": total_bytes,
+           "roofline": {"bound": "hbm", "achieved": round(dom[0], 1), "peak": peak, "unit": "GB/s", "frac": round(dom[0] / peak, 4),
+                        "traffic": None, "peak_source": src,
+                        "kernel": f"sc_round_kernel fold launch {dom[2]} on one of {world} GPUs (its slice: "
+                                  f"{(per_launch_bytes[dom[2] - 1] if dom[2] else 0) // world} algorithmic bytes in {dom[1]:.4f} ms); "
+                                  "each launch also exchanges the round's partial sums with the peers",
+                        "per_launch_gbps_per_gpu": [round(t[0], 1) for t in fold[:12]], "per_launch_ms": [round(t, 4) for t in prof[:14]]}}
+    if with_e2e:
+        for _ in range(2):
+            step((f_host, g_host))
+        ctx.sync(); barrier()
+        ctx.timer_start()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            step((f_host, g_host))
+        ms_e2e = ctx.timer_stop_ms()
+        wall = (time.perf_counter() - t0) * 1e3
+        ms_e2e_step = max_over_ranks(ms_e2e / steps)
+        res["e2e"] = {"value": round(total_bytes / (ms_e2e_step * 1e-3) / 1e9, 2), "unit": "GB/s", "ms_per_step": round(ms_e2e_step, 3),
+                      "wall_ms_per_step": round(wall / steps, 3), "h2d_bytes_per_step": 2 * N_local * 4 * world,
+                      "d2h_bytes_per_step": (n * 12 + 8) * 4 * world}
+    barrier()
+    f_dev.free(); g_dev.free()
+    xch.close()
+    return res
+
+
 # ------------------------------------------------------------------------------------------------
 # workload: Qwen3.5-4B-shape end-to-end prove
 # ------------------------------------------------------------------------------------------------
@@ -388,7 +462,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default="qwen4b", choices=["qwen4b", "sumcheck"])
     ap.add_argument("--layers", type=int, default=32)
-    ap.add_argument("--n", type=int, default=28, help="sumcheck workload: log2 of the table length")
+    ap.add_argument("--n", "--log-n", dest="n", type=int, default=28, help="sumcheck workload: log2 of the table length")
     ap.add_argument("--n-micro", type=int, default=26, help="log2 table length of the attached sumcheck microbench")
     ap.add_argument("--n-cpu", type=int, default=24, help="sumcheck workload: log2 table length of the CPU sample")
     ap.add_argument("--cpu-layers", type=int, default=0, help="qwen4b: layers in the CPU sample (default: host cores, max 8)")
@@ -397,6 +471,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--n-basefold", type=int, default=24, help="log2 coefficient count of the attached Basefold commitment")
     ap.add_argument("--no-micro", action="store_true")
+    ap.add_argument("--replicas", action="store_true", help="sumcheck workload at N > 1: N independent sumchecks instead of one split sumcheck")
     args = ap.parse_args()
     if args.impl == "ours":
         args.warmup = max(args.warmup, 3)
@@ -418,7 +493,9 @@ def main():
         config = {"workload": f"isolated product-sumcheck microbench, two tables of 2^{args.n} M31 elements uniform in [0, 2^31-1), "
                               f"{args.n} rounds, seeded transcript 'bench-product'", "n": args.n,
                   "l2_policy": "inputs (2 x %d MiB) are larger than L2" % ((4 << args.n) >> 20),
-                  "parallelism": f"{world} independent sumchecks, one per GPU" if world > 1 else "single GPU"}
+                  "parallelism": ("single GPU" if world == 1 else f"{world} independent sumchecks, one per GPU" if args.replicas else
+                                  f"one sumcheck split over {world} GPUs by the low index bits; per-round sums exchanged by the round "
+                                  "kernels over NVLink peer memory")}
 
     if args.impl == "reference":
         if rank != 0:
@@ -485,8 +562,12 @@ def main():
         micro_ctx = zk.Context(local)
         sampler = ClockSampler(local)
         sampler.start()
-        r = run_sumcheck(zk, micro_ctx, args.n, args.steps, args.warmup, rank, not args.no_e2e, barrier, max_over_ranks, world)
-        line.update({"value": r["value_gbps"], "ms_per_step": r["ms_per_step"], "scaling": "weak", "vs_baseline": None,
+        if world > 1 and not args.replicas:
+            r = run_sumcheck_split(zk, micro_ctx, args.n, args.steps, args.warmup, rank, world, not args.no_e2e, barrier, max_over_ranks, dist)
+        else:
+            r = run_sumcheck(zk, micro_ctx, args.n, args.steps, args.warmup, rank, not args.no_e2e, barrier, max_over_ranks, world)
+        line.update({"value": r["value_gbps"], "ms_per_step": r["ms_per_step"],
+                     "scaling": "strong" if (world > 1 and not args.replicas) else "weak", "vs_baseline": None,
                      "roofline": r["roofline"], "e2e": r.get("e2e"), "gpu_launches": r["gpu_launches"], "clocks": sampler.stop(),
                      "algorithmic_bytes_per_step": r["algorithmic_bytes_per_step"]})
         if not args.no_micro and rank == 0:
