@@ -176,6 +176,10 @@ int32_t zkb_qwen_layer_forward_async(zkb_qwen_layer* layer, zkb_qwen_layer* prev
  * and copies the layer output (d_model words) to the host. */
 int32_t zkb_qwen_layer_read_output(zkb_qwen_layer* layer, uint32_t* y_host);
 const uint32_t* zkb_qwen_layer_output_dev(const zkb_qwen_layer* layer);
+/* The launch sequence of a layer proof depends only on the layer's shapes and binding mode, so
+ * from the second proof on it is replayed from a CUDA graph captured on the layer's stream
+ * (one graph launch instead of about two thousand kernel launches).  on = 0 switches that off. */
+int32_t zkb_qwen_layer_use_graph(zkb_qwen_layer* layer, int32_t on);
 /* Selects what the reference fixes at compile time for the layer's eight matmul proofs: the
  * weight binding (ZKB_BIND_*, features pcs / pcs-full, matmul.rs:360-453) and the Merkle node
  * hash (ZKB_NODE_*, pcs.rs:87-135).  Default after create: ZKB_BIND_BLAKE3. */
@@ -203,6 +207,10 @@ typedef struct zkb_xch zkb_xch;
 int32_t zkb_xch_create(zkb_ctx* ctx, uint32_t world, uint32_t rank, zkb_xch** out);
 int32_t zkb_xch_handle(zkb_xch* xch, uint8_t handle[64]);
 int32_t zkb_xch_connect(zkb_xch* xch, const uint8_t* handles /* world x 64 bytes */);
+/* Wires the peers of a multi-rank exchange to private buffers on this GPU that nobody writes:
+ * the next split sumcheck then runs into the time limit and returns ZKB_E_TIMEOUT.  For testing
+ * the time-out path in one process; not for production use. */
+int32_t zkb_xch_connect_loopback(zkb_xch* xch);
 int32_t zkb_xch_set_timeout_ms(zkb_xch* xch, uint32_t ms);
 void zkb_xch_destroy(zkb_xch* xch);
 /* zkb_sumcheck_prove over tables of 2^num_vars elements of which this rank passes its slice of

@@ -162,7 +162,16 @@ def _check_layer(ctx, cfg, weights, x, silu, sigm, idx):
     assert ok, "oracle verifier rejected the oracle proof"
     assert len(proof) == len(eproof)
     assert proof == eproof, "layer proof bytes differ from the oracle"
-    # proving twice gives the same bytes (buffers are reused, nothing stale leaks)
+    # proving twice gives the same bytes (buffers are reused, nothing stale leaks); the second
+    # proof captures the launch sequence into a graph, later ones replay it
+    assert layer.prove(idx, ih) == eproof
+    assert layer.prove(idx, ih) == eproof
+    # a replay with another layer index and input hash (the transcript seed is device-resident)
+    ih2 = hashlib.sha256(b"another-input").digest()
+    _, eproof2, _ = O.qwen_layer_prove(cfg, weights, x, silu, sigm, idx + 12, ih2)
+    assert layer.prove(idx + 12, ih2) == eproof2
+    # and launch-by-launch enqueueing still agrees
+    layer.use_graph(False)
     assert layer.prove(idx, ih) == eproof
     layer.close()
 

@@ -37,6 +37,30 @@ def test_split_world_of_one_matches_oracle(kind, nv):
     ctx.close()
 
 
+def test_silent_peer_times_out_and_context_stays_usable():
+    # a bounded wait that runs out: the peer's flag is never set, the kernel gives up after the
+    # limit, the host gets a status instead of a proof, and the GPU keeps working
+    import time
+    ctx = zk.Context(0)
+    xch = zs.Exchange(ctx, 2, 0, timeout_ms=300, loopback=True)
+    nv = 10
+    tables = rand_tables(zk.SC_PRODUCT_EF, nv, 5)
+    mine = [zs.slice_for_rank(t, 2, 0) for t in tables]
+    t0 = time.time()
+    with pytest.raises(zk.ZkbError) as e:
+        zs.sumcheck_prove_split(zk.SC_PRODUCT_EF, mine, nv, zk.Transcript(ctx, b"to"), xch)
+    assert e.value.code == 8                        # ZKB_E_TIMEOUT
+    with pytest.raises(zk.ZkbError):                # sticky: the next call fails at once
+        zs.sumcheck_prove_split(zk.SC_PRODUCT_EF, mine, nv, zk.Transcript(ctx, b"to"), xch)
+    assert time.time() - t0 < 5.0
+    xch.close()
+    tr, otr = zk.Transcript(ctx, b"after"), O.Transcript(b"after")
+    proof, *_ = zk.sumcheck_prove(zk.SC_PRODUCT_EF, tables, nv, tr)
+    polys, _, _ = O.prove("product_ef", otr, tables, nv)
+    assert proof.round_polys.reshape(nv, -1).tolist() == polys.tolist()
+    ctx.close()
+
+
 def _gpu_count():
     import torch
     return torch.cuda.device_count()

@@ -31,6 +31,8 @@ int32_t zkb_qwen_layer_create(zkb_ctx* c, const uint64_t dims[7], const uint32_t
         // commit_qwen_layer (qwen.rs:148-161): blake3 of each unpadded matrix
         ZKB_CUDA(cudaEventCreateWithFlags(&L->fwd_done, cudaEventDisableTiming));
         ZKB_CUDA(cudaMalloc(&L->roots_dev, 64 * 4));
+        ZKB_CUDA(cudaMalloc(&L->seed_dev, 128));
+        ZKB_CUDA(cudaHostAlloc(&L->seed_host, 128, cudaHostAllocDefault));
         static const int widx[8] = {W_Q, W_K, W_V, W_O, W_GPROJ, W_GATE, W_UP, W_DOWN};
         for (int i = 0; i < 8; i++) {
             commit_large(c, b3_prefix("weights", 7), L->w[widx[i]], L->w_len[widx[i]], L->roots_dev + 8 * i);
@@ -74,12 +76,22 @@ void zkb_qwen_layer_destroy(zkb_qwen_layer* L) {
     }
     for (int i = 0; i < W_COUNT; i++) if (L->w[i]) cudaFree(L->w[i]);
     if (L->fwd_done) cudaEventDestroy(L->fwd_done);
+    qwen_graph_drop(L);
+    if (L->seed_dev) cudaFree(L->seed_dev);
+    if (L->seed_host) cudaFreeHost(L->seed_host);
     if (L->roots_dev) cudaFree(L->roots_dev);
     if (L->trace_block) cudaFree(L->trace_block);
     delete L->pending;
     delete L;
 }
 
+// Replay of the captured launch sequence on (default) or off: with it off every proof is
+// enqueued launch by launch.
+int32_t zkb_qwen_layer_use_graph(zkb_qwen_layer* L, int32_t on) {
+    if (!L) return ZKB_E_ARG;
+    L->use_graph = on != 0;
+    return ZKB_OK;
+}
 // Weight binding used by the layer's eight matmul proofs from now on.
 int32_t zkb_qwen_layer_set_binding(zkb_qwen_layer* L, int32_t bind_mode, int32_t node_hash) {
     if (!L || bind_mode < BIND_BLAKE3 || bind_mode > BIND_PCS_FULL || (node_hash != NODE_BLAKE3 && node_hash != NODE_AES_MMO)) return ZKB_E_ARG;

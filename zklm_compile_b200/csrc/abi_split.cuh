@@ -9,6 +9,7 @@ struct zkb_xch {
     zkb::u32* local = nullptr;                       // mailbox + sticky word
     zkb::u32* peers[zkb::XCH_MAX_WORLD] = {};        // mapped peer mailboxes (peers[rank] == local)
     bool opened[zkb::XCH_MAX_WORLD] = {};
+    bool loopback[zkb::XCH_MAX_WORLD] = {};
     zkb::ScXch* dev = nullptr;                       // descriptor read by the kernels
     uint32_t seq = 1;
     unsigned long long timeout_ns = 4000000000ull;
@@ -72,6 +73,26 @@ int32_t zkb_xch_connect(zkb_xch* x, const uint8_t* handles) {
     });
 }
 
+// Loop-back wiring for a world of more than one rank inside a single process: every peer mailbox
+// is a private buffer on this GPU that nobody writes, so the first exchange runs into the time
+// limit.  Exists to exercise the time-out path (status ZKB_E_TIMEOUT, context still usable).
+int32_t zkb_xch_connect_loopback(zkb_xch* x) {
+    if (!x) return ZKB_E_ARG;
+    zkb_ctx* c = x->ctx;
+    ZKB_TRY(c, {
+        c->use();
+        for (uint32_t p = 0; p < x->world; p++) {
+            if (p == x->rank || x->peers[p]) continue;
+            u32* buf = nullptr;
+            ZKB_CUDA(cudaMalloc(&buf, (XCH_BOX_WORDS + 64) * 4));
+            ZKB_CUDA(cudaMemset(buf, 0, (XCH_BOX_WORDS + 64) * 4));
+            x->peers[p] = buf;
+            x->loopback[p] = true;
+        }
+        x->connected = true;
+    });
+}
+
 int32_t zkb_xch_set_timeout_ms(zkb_xch* x, uint32_t ms) {
     if (!x || ms == 0) return ZKB_E_ARG;
     x->timeout_ns = (unsigned long long)ms * 1000000ull;
@@ -86,6 +107,7 @@ void zkb_xch_destroy(zkb_xch* x) {
     }
     for (uint32_t p = 0; p < x->world; p++)
         if (x->opened[p]) cudaIpcCloseMemHandle(x->peers[p]);
+        else if (x->loopback[p]) cudaFree(x->peers[p]);
     if (x->local) cudaFree(x->local);
     if (x->dev) cudaFree(x->dev);
     delete x;

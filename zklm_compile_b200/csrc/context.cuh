@@ -93,12 +93,19 @@ struct zkb_ctx {
 
     void use() { ZKB_CUDA(cudaSetDevice(device)); }
 
+    // While a stream capture is open nothing may be allocated; arena_epoch changes whenever the
+    // arena's memory does, which invalidates captured graphs that hold addresses inside it.
+    bool capturing = false;
+    uint64_t arena_epoch = 0;
+
     void* scratch(size_t bytes) {
         bytes = (bytes + 255) & ~size_t(255);
         if (!chunks.empty()) {
             Chunk& c = chunks.back();
             if (c.used + bytes <= c.cap) { void* p = c.base + c.used; c.used += bytes; return p; }
         }
+        if (capturing) throw zkb::ArgFail{ZKB_E_TOO_LARGE, "scratch arena would have to grow during a stream capture"};
+        arena_epoch++;
         size_t cap = bytes;
         if (cap < (size_t(64) << 20)) cap = size_t(64) << 20;
         char* p = nullptr;
@@ -109,6 +116,7 @@ struct zkb_ctx {
     // Rewind everything; if the arena fragmented into several chunks, replace them by one.
     void scratch_reset() {
         if (chunks.size() > 1) {
+            arena_epoch++;
             ZKB_CUDA(cudaStreamSynchronize(stream));
             size_t total = 0;
             for (auto& c : chunks) { total += c.cap; cudaFree(c.base); }

@@ -185,6 +185,7 @@ struct ScriptBuilder {
     void words_dev(const u32* p, u32 n, u32 pad = 0) { push(TrOp{TROP_WORDS_DEV, n, pad > n ? pad : n, 0, p, nullptr}); }
     void pairs_dev(const u32* a, const u32* b, u32 n) { push(TrOp{TROP_PAIRS_DEV, n, 0, 0, a, b}); }
     void squeeze(u32* dst, u32 n) { push(TrOp{TROP_SQUEEZE, n, 0, 0, dst, nullptr}); }
+    void bytes_dev_n(const u32* p) { push(TrOp{TROP_BYTES_DEV_N, 0, 0, 0, p, nullptr}); }
     void run(zkb_ctx* c, TrState* tr) {
         if (!s.nops) return;
         tr_script_kernel<<<1, 32, 0, c->stream>>>(tr, s);

@@ -45,6 +45,19 @@ struct zkb_qwen_layer {
     // pending proof
     struct Pending;
     Pending* pending = nullptr;
+    // Transcript seed of the proof being enqueued, device-resident so that the launch sequence does
+    // not depend on it: [byte count, "qwen-layer-{idx}" bytes, 32 bytes of input hash].
+    zkb::u32* seed_dev = nullptr;
+    zkb::u32* seed_host = nullptr;        // pinned
+    // The launch sequence of a layer proof is fixed once its shapes, binding mode and arena are:
+    // it is captured into a CUDA graph on the second proof and replayed afterwards.
+    cudaGraphExec_t graph_exec = nullptr;
+    Pending* graph_pending = nullptr;     // record offsets of the captured sequence
+    size_t graph_rec_used = 0;
+    uint64_t graph_launches = 0, graph_epoch = 0;
+    int graph_bind = -1, graph_hash = -1;
+    uint64_t proofs_enqueued = 0;
+    bool use_graph = true;
 };
 
 namespace zkb {
@@ -111,26 +124,18 @@ struct zkb_qwen_layer::Pending {
 
 namespace zkb {
 
-// Enqueue the whole layer proof (no synchronisation).
-inline void qwen_prove_enqueue(zkb_qwen_layer* L, u32 layer_idx, const uint8_t input_hash[32]) {
+// The launches of one layer proof; record offsets go to P.  No synchronisation, no allocation
+// once the arena has its final size (so it can run under stream capture).
+inline void qwen_prove_launches(zkb_qwen_layer* L, zkb_qwen_layer::Pending& P) {
     zkb_ctx* c = L->ctx;
     const QwenDims& d = L->dm;
-    if (!L->have_trace) throw ArgFail{ZKB_E_ARG, "zkb_qwen_layer_prove: run the forward pass first"};
-    c->rec_reset();
-    c->scratch_reset();
-    delete L->pending;
-    L->pending = new zkb_qwen_layer::Pending();
-    auto& P = *L->pending;
     const u32 dm = d.d_model, aod = d.aod();
     TrState* tr = (TrState*)c->scratch(sizeof(TrState));
     tr_init_kernel<<<1, 1, 0, c->stream>>>(tr);
     ZKB_LAUNCHED(c);
     {   // Transcript::new("qwen-layer-{idx}"); absorb input hash; dims; the eight roots
         ScriptBuilder sb;
-        char seed[48];
-        snprintf(seed, sizeof seed, "qwen-layer-%u", layer_idx);
-        sb.str(seed);
-        sb.bytes(input_hash, 32);
+        sb.bytes_dev_n(L->seed_dev);
         sb.str("qwen-dims-v1");
         u32 dims[12] = {d.d_model, d.d_ff, d.nq, d.nkv, d.d_head, d.v_heads, d.v_d_head, d.v_dim(), d.q_dim(), d.k_dim(), aod, d.is_gqa() ? 1u : 0u};
         sb.bytes(dims, sizeof dims);
@@ -163,6 +168,87 @@ inline void qwen_prove_enqueue(zkb_qwen_layer* L, u32 layer_idx, const uint8_t i
     { ScriptBuilder sb; sb.squeeze(c->rec_dev + P.res2_point, 4 * log_d); sb.run(c, tr); }
     P.res2 = prove_add_ef(c, tr, L->h, L->down, L->out, dm, (const Fe*)(c->rec_dev + P.res2_point), log_d);
     ZKB_CUDA(cudaGetLastError());
+}
+
+inline void qwen_graph_drop(zkb_qwen_layer* L);
+
+// Enqueue the whole layer proof (no synchronisation): eagerly the first time (the arena grows to
+// its final size), captured into a graph the second time, replayed from then on.
+inline void qwen_prove_enqueue(zkb_qwen_layer* L, u32 layer_idx, const uint8_t input_hash[32]) {
+    zkb_ctx* c = L->ctx;
+    if (!L->have_trace) throw ArgFail{ZKB_E_ARG, "zkb_qwen_layer_prove: run the forward pass first"};
+    {   // seed block -> device
+        char seed[48];
+        int n = snprintf(seed, sizeof seed, "qwen-layer-%u", layer_idx);
+        unsigned char* b = reinterpret_cast<unsigned char*>(L->seed_host + 1);
+        memset(L->seed_host, 0, 128);
+        memcpy(b, seed, (size_t)n);
+        memcpy(b + n, input_hash, 32);
+        L->seed_host[0] = (u32)n + 32;
+        ZKB_CUDA(cudaMemcpyAsync(L->seed_dev, L->seed_host, 128, cudaMemcpyHostToDevice, c->stream));
+    }
+    c->rec_reset();
+    c->scratch_reset();
+    delete L->pending;
+    L->pending = nullptr;
+    const bool graph_ok = L->use_graph && !c->profile;
+    if (graph_ok && L->graph_exec && L->graph_epoch == c->arena_epoch && L->graph_bind == L->bind_mode && L->graph_hash == L->node_hash) {
+        L->pending = new zkb_qwen_layer::Pending(*L->graph_pending);
+        c->rec_used = L->graph_rec_used;
+        ZKB_CUDA(cudaGraphLaunch(L->graph_exec, c->stream));
+        c->launches += L->graph_launches;
+        L->proofs_enqueued++;
+        return;
+    }
+    qwen_graph_drop(L);
+    L->pending = new zkb_qwen_layer::Pending();
+    if (graph_ok && L->proofs_enqueued >= 1) {
+        const uint64_t launches0 = c->launches;
+        cudaGraph_t graph = nullptr;
+        c->capturing = true;
+        ZKB_CUDA(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+        bool fine = true;
+        std::string why;
+        try {
+            qwen_prove_launches(L, *L->pending);
+        } catch (const CudaFail& e) { fine = false; why = e.msg; }
+        catch (const ArgFail& e) { fine = false; why = e.msg; }
+        cudaError_t ce = cudaStreamEndCapture(c->stream, &graph);
+        c->capturing = false;
+        if (fine && ce == cudaSuccess && graph) {
+            cudaGraphExec_t exec = nullptr;
+            ce = cudaGraphInstantiate(&exec, graph, 0);
+            cudaGraphDestroy(graph);
+            if (ce == cudaSuccess) {
+                L->graph_exec = exec;
+                L->graph_pending = new zkb_qwen_layer::Pending(*L->pending);
+                L->graph_rec_used = c->rec_used;
+                L->graph_launches = c->launches - launches0;
+                L->graph_epoch = c->arena_epoch;
+                L->graph_bind = L->bind_mode; L->graph_hash = L->node_hash;
+                ZKB_CUDA(cudaGraphLaunch(exec, c->stream));
+                L->proofs_enqueued++;
+                return;
+            }
+        } else if (graph) {
+            cudaGraphDestroy(graph);
+        }
+        // capture did not work out (e.g. the arena had to grow): clear the sticky error, go on eagerly
+        cudaGetLastError();
+        L->use_graph = false;
+        c->launches = launches0;
+        c->rec_reset();
+        c->scratch_reset();
+        delete L->pending;
+        L->pending = new zkb_qwen_layer::Pending();
+    }
+    qwen_prove_launches(L, *L->pending);
+    L->proofs_enqueued++;
+}
+inline void qwen_graph_drop(zkb_qwen_layer* L) {
+    if (L->graph_exec) { cudaGraphExecDestroy(L->graph_exec); L->graph_exec = nullptr; }
+    delete L->graph_pending;
+    L->graph_pending = nullptr;
 }
 
 // Wait for the enqueued proof and serialise QwenLayerProofEF (after strip_redundant) as bincode.

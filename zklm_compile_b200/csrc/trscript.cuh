@@ -52,7 +52,8 @@ enum TrOpKind : u32 {
     TROP_PAIRS_DEV = 2,    // absorb a[i], b[i] interleaved, i < n (LogUp statement, lookup.rs:655-658)
     TROP_SQUEEZE = 3,      // squeeze `n` base-field challenges to ptr
     TROP_BYTES_DEV = 4,    // absorb `n` bytes from device memory (word aligned, n % 4 == 0)
-    TROP_WORD_DEV_N = 5    // absorb the u32 count stored at ptr[0] (device-resident length)
+    TROP_WORD_DEV_N = 5,   // absorb the u32 count stored at ptr[0] (device-resident length)
+    TROP_BYTES_DEV_N = 6   // absorb ptr[0] bytes stored from ptr + 1 on (device-resident, any length below 256)
 };
 struct TrOp {
     u32 kind;
@@ -90,6 +91,12 @@ __global__ void __launch_bounds__(32) tr_script_kernel(TrState* st, TrScript sc)
             }
         } else if (op.kind == TROP_WORD_DEV_N) {
             if (lane == 0) tr_absorb_u32(tr, op.ptr[0]);
+        } else if (op.kind == TROP_BYTES_DEV_N) {
+            if (lane == 0) {
+                u32 nb = op.ptr[0];
+                if (nb > 255) nb = 255;
+                tr_absorb_bytes(tr, reinterpret_cast<const unsigned char*>(op.ptr + 1), nb);
+            }
         } else {
             // streamed absorbs: total logical words
             u32 total = op.kind == TROP_WORDS_DEV ? op.pad : (op.kind == TROP_PAIRS_DEV ? 2 * op.n : op.n / 4);

@@ -90,6 +90,10 @@ class QwenLayer:
             self._x_keep = np.ascontiguousarray(x, dtype=np.uint32)
             check(self.ctx.h, _lib.lib().zkb_qwen_layer_forward_async(self.h, None, self._x_keep.ctypes.data_as(u32p), C.c_int32(0)))
 
+    def use_graph(self, on: bool):
+        """Replay of the captured launch sequence (default on) or launch-by-launch enqueueing."""
+        check(self.ctx.h, _lib.lib().zkb_qwen_layer_use_graph(self.h, C.c_int32(1 if on else 0)))
+
     def set_binding(self, bind_mode: int, node_hash: int = 0):
         """Weight binding of the matmul proofs: 0 default build, 1 feature pcs, 2 feature pcs-full
         (bind_weights_ef, rust/zk_ml_prover/src/proving/matmul.rs:360-453)."""

@@ -24,13 +24,15 @@ def slice_for_rank(table, world: int, rank: int, width: int = 1) -> np.ndarray:
 class Exchange:
     """Mailboxes of one rank, connected to its peers' (see include/zkb200.h, zkb_xch_*)."""
 
-    def __init__(self, ctx: Context, world: int, rank: int, gather_handles=None, timeout_ms: int = None):
+    def __init__(self, ctx: Context, world: int, rank: int, gather_handles=None, timeout_ms: int = None, loopback: bool = False):
         self.ctx, self.world, self.rank = ctx, world, rank
         self.h = C.c_void_p()
         check(ctx.h, _lib.lib().zkb_xch_create(ctx.h, C.c_uint32(world), C.c_uint32(rank), C.byref(self.h)))
         if timeout_ms:
             check(ctx.h, _lib.lib().zkb_xch_set_timeout_ms(self.h, C.c_uint32(timeout_ms)))
-        if world > 1:
+        if world > 1 and loopback:       # peers that never answer: only for exercising the time-out path
+            check(ctx.h, _lib.lib().zkb_xch_connect_loopback(self.h))
+        elif world > 1:
             mine = (C.c_uint8 * 64)()
             check(ctx.h, _lib.lib().zkb_xch_handle(self.h, mine))
             handles = (gather_handles or _gather_with_torch)(bytes(mine), world)
