@@ -144,6 +144,18 @@ int32_t zkb_prove_matmul_succinct_ef(zkb_ctx* ctx, zkb_transcript* tr, const uin
 int32_t zkb_prove_matmul_succinct_ef_bind(zkb_ctx* ctx, zkb_transcript* tr, const uint32_t* W, const uint32_t* x, const uint32_t* y,
                                           size_t m, size_t n, int32_t w_on_device, int32_t bind_mode, int32_t node_hash, uint8_t* out,
                                           size_t cap, size_t* len);
+/* Base-field twins (challenges in M31; the MLP / GPT-2 op-list mode of the reference):
+ * prove_matmul_succinct -> SuccinctMatmulProof                          matmul.rs:134-180, 482-511 */
+int32_t zkb_prove_matmul_succinct(zkb_ctx* ctx, zkb_transcript* tr, const uint32_t* W, const uint32_t* x, const uint32_t* y, size_t m,
+                                  size_t n, int32_t w_on_device, uint8_t* out, size_t cap, size_t* len);
+/* prove_mle_eval_no_merkle (label_len = 0) / prove_mle_eval_bound (label + 32-byte root absorbed first)
+ * -> MleEvalProof; w: n <= 2^k values, point: k challenges          weight_commitment.rs:177-206, 437-447 */
+int32_t zkb_prove_mle_eval(zkb_ctx* ctx, zkb_transcript* tr, const uint32_t* w, size_t n, const uint32_t* point, uint32_t k,
+                           const uint8_t* label, size_t label_len, const uint8_t root[32], uint8_t* out, size_t cap, size_t* len);
+/* prove_hadamard (is_add = 0) / prove_add (is_add = 1); point = k base-field challenges
+ * -> HadamardProof / AddProof                                          elementwise.rs:50-98, 189-235 */
+int32_t zkb_prove_elementwise(zkb_ctx* ctx, zkb_transcript* tr, int32_t is_add, const uint32_t* a, const uint32_t* b, const uint32_t* c,
+                              size_t n, const uint32_t* point, uint32_t k, uint8_t* out, size_t cap, size_t* len);
 /* prove_hadamard_ef (is_add = 0) / prove_add_ef (is_add = 1); point = k EF challenges    elementwise.rs:429-480, 545-595 */
 int32_t zkb_prove_elementwise_ef(zkb_ctx* ctx, zkb_transcript* tr, int32_t is_add, const uint32_t* a, const uint32_t* b,
                                  const uint32_t* c, size_t n, const uint32_t* point, uint32_t k, uint8_t* out, size_t cap, size_t* len);
@@ -153,6 +165,10 @@ int32_t zkb_prove_rmsnorm_ef(zkb_ctx* ctx, zkb_transcript* tr, const uint32_t* x
 /* prove_lookup_ef -> LookupProofEF; table_out = output column of a 65536- or 256-entry table   lookup.rs:643-762 */
 int32_t zkb_prove_lookup_ef(zkb_ctx* ctx, zkb_transcript* tr, const uint32_t* table_out, size_t n_table, const uint32_t* inputs,
                             const uint32_t* outputs, size_t n, uint8_t* out, size_t cap, size_t* len);
+
+/* prove_lookup (base-field challenges) -> LookupProof                                          lookup.rs:432-604 */
+int32_t zkb_prove_lookup(zkb_ctx* ctx, zkb_transcript* tr, const uint32_t* table_out, size_t n_table, const uint32_t* inputs,
+                         const uint32_t* outputs, size_t n, uint8_t* out, size_t cap, size_t* len);
 
 /* ---- resident Qwen-style layer (QwenLayerWeights + commit_qwen_layer + trace)   transformer/qwen.rs:62-73, 148-161 ----
  * dims = {d_model, d_ff, num_q_heads, num_kv_heads, d_head, v_num_heads, v_d_head};

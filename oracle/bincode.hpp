@@ -7,6 +7,7 @@
 // parity tests compare.
 #pragma once
 #include "layers2.hpp"
+#include "layers_base.hpp"
 
 namespace zko {
 
@@ -71,6 +72,14 @@ struct Bin {
         u8(p.has_basefold ? 1 : 0);
         if (p.has_basefold) put(p.basefold_proof);
     }
+    void put(const HadamardProof& p) {                      // elementwise.rs:31-44 (product_finals is a 3-tuple)
+        put(p.product_sumcheck); u32(p.fin_eq); u32(p.fin_a); u32(p.fin_b); u32(p.c_eval);
+        put(p.c_eval_proof); put(p.c_commitment);
+    }
+    void put(const AddProof& p) {                           // elementwise.rs:165-181
+        put(p.a_sumcheck); u32(p.a_fin_eq); u32(p.a_fin); put(p.b_sumcheck); u32(p.b_fin_eq); u32(p.b_fin); u32(p.c_eval);
+        put(p.c_eval_proof); put(p.c_commitment);
+    }
     void put(const HadamardProofEF& p) {                    // elementwise.rs:415-426
         put(p.product_sumcheck); ef(p.fin_eq); ef(p.fin_a); ef(p.fin_b); ef(p.c_eval);
         put(p.c_eval_proof); put(p.c_commitment);
@@ -78,6 +87,21 @@ struct Bin {
     void put(const AddProofEF& p) {                         // elementwise.rs:527-542
         put(p.a_sumcheck); ef(p.a_fin_eq); ef(p.a_fin); put(p.b_sumcheck); ef(p.b_fin_eq); ef(p.b_fin);
         ef(p.c_eval); put(p.c_eval_proof); put(p.c_commitment);
+    }
+    void put(const RmsNormProof& p) {                       // rmsnorm.rs:36-85
+        i32(p.perturbation_delta);
+        put(p.var_proof); u32(p.var_fin[0]); u32(p.var_fin[1]); u32(p.sum_sq_value);
+        put(p.h_sq_proof); for (uint32_t v : p.h_sq_fin) u32(v); u32(p.s_h);
+        put(p.g_sq_proof); for (uint32_t v : p.g_sq_fin) u32(v); u32(p.s_g);
+        put(p.g_prod_proof); for (uint32_t v : p.g_prod_fin) u32(v);
+        put(p.g_triple_proof); for (uint32_t v : p.g_triple_fin) u32(v); u32(p.t_g_claimed);
+        put(p.x_commitment); put(p.gamma_commitment); put(p.g_commitment); put(p.h_commitment);
+        put(p.x_var_eval_proof); u32(p.x_at_var_s);
+        put(p.g_prod_eval_proof); u32(p.g_at_prod_s);
+        put(p.x_triple_eval_proof); u32(p.x_at_triple_s);
+        put(p.gamma_triple_eval_proof); u32(p.gamma_at_triple_s);
+        put(p.h_sq_eval_proof); u32(p.h_at_sq_s);
+        put(p.g_sq_eval_proof); u32(p.g_at_gsq_s);
     }
     void put(const RmsNormProofEF& p) {                     // rmsnorm.rs:457-503
         i32(p.perturbation_delta);
@@ -93,6 +117,12 @@ struct Bin {
         put(p.gamma_triple_eval_proof); ef(p.gamma_at_triple_s);
         put(p.h_sq_eval_proof); ef(p.h_at_sq_s);
         put(p.g_sq_eval_proof); ef(p.g_at_gsq_s);
+    }
+    void put(const LookupProof& p) {                        // lookup.rs:39-85
+        put(p.table_commitment); put(p.multiplicity_commitment); put(p.sumcheck_proof); u32(p.fin_ones); u32(p.fin_h);
+        u32(p.alpha); u32(p.beta);
+        vec_u32(p.inputs); vec_u32(p.outputs); vec_u32(p.multiplicities);
+        bytes(p.external_data_digest);
     }
     void put(const LookupProofEF& p) {                      // lookup.rs:89-115
         put(p.table_commitment); put(p.multiplicity_commitment); put(p.sumcheck_proof); ef(p.h_at_s);

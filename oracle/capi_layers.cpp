@@ -73,6 +73,27 @@ size_t zko_prove_mle_eval_bound(void* t, const uint32_t* w, size_t n, const uint
     *claimed = cl.v;
     return emit(b.b, out, cap);
 }
+// base-field hadamard (is_add = 0) / add (is_add = 1)
+size_t zko_prove_elementwise(void* t, int is_add, const uint32_t* a, const uint32_t* b_, const uint32_t* c, size_t n, const uint32_t* point,
+                             size_t k, uint8_t* out, size_t cap) {
+    Bin b;
+    if (is_add) b.put(prove_add(vf(a, n), vf(b_, n), vf(c, n), vf(point, k), T(t)));
+    else b.put(prove_hadamard(vf(a, n), vf(b_, n), vf(c, n), vf(point, k), T(t)));
+    return emit(b.b, out, cap);
+}
+int zko_elementwise_base_roundtrip(int is_add, const uint32_t* a, const uint32_t* b_, const uint32_t* c, size_t n, const uint32_t* point, size_t k,
+                              int tamper) {
+    Transcript pt("ew"), vt("ew");
+    VF pnt = vf(point, k);
+    if (is_add) {
+        auto p = prove_add(vf(a, n), vf(b_, n), vf(c, n), pnt, pt);
+        if (tamper) p.b_fin ^= 1;
+        return verify_add(p, pnt, vt);
+    }
+    auto p = prove_hadamard(vf(a, n), vf(b_, n), vf(c, n), pnt, pt);
+    if (tamper) p.fin_a ^= 1;
+    return verify_hadamard(p, pnt, vt);
+}
 size_t zko_prove_hadamard_ef(void* t, const uint32_t* a, const uint32_t* b_, const uint32_t* c, size_t n, const uint32_t* point,
                              size_t k, uint8_t* out, size_t cap) {
     Bin b; b.put(prove_hadamard_ef(vf(a, n), vf(b_, n), vf(c, n), vef(point, k), T(t)));
@@ -127,6 +148,36 @@ size_t zko_prove_lookup_ef(void* t, const uint32_t* table_out, size_t n_table, c
         *status = std::string(e.what()).find("alpha") == 0 ? 4 : 3;
         return 0;
     }
+}
+size_t zko_prove_rmsnorm(void* t, const uint32_t* x, const uint32_t* gamma, const uint32_t* y, size_t d, int32_t delta, uint8_t* out, size_t cap) {
+    Bin b; b.put(prove_rmsnorm(vf(x, d), vf(gamma, d), vf(y, d), delta, T(t)));
+    return emit(b.b, out, cap);
+}
+int zko_rmsnorm_base_roundtrip(const uint32_t* x, const uint32_t* gamma, const uint32_t* y, size_t d, int32_t delta, int tamper) {
+    Transcript pt("rn"), vt("rn");
+    auto p = prove_rmsnorm(vf(x, d), vf(gamma, d), vf(y, d), delta, pt);
+    if (tamper == 1) p.s_g ^= 1;
+    if (tamper == 2) p.perturbation_delta += 1;
+    return verify_rmsnorm(p, vf(y, d), d, vt);
+}
+size_t zko_prove_lookup(void* t, const uint32_t* table_out, size_t n_table, const uint32_t* in, const uint32_t* outv, size_t n,
+                        uint8_t* out, size_t cap, int* status) {
+    *status = 0;
+    try {
+        Bin b; b.put(prove_lookup(table_from_outputs(std::vector<uint32_t>(table_out, table_out + n_table)), vf(in, n), vf(outv, n), T(t)));
+        return emit(b.b, out, cap);
+    } catch (const LookupFailure& e) {
+        *status = std::string(e.what()).find("alpha") == 0 ? 4 : 3;
+        return 0;
+    }
+}
+int zko_lookup_base_roundtrip(const uint32_t* table_out, size_t n_table, const uint32_t* in, const uint32_t* outv, size_t n, int tamper) {
+    Transcript pt("rt"), vt("rt");
+    LookupTable tb = table_from_outputs(std::vector<uint32_t>(table_out, table_out + n_table));
+    auto p = prove_lookup(tb, vf(in, n), vf(outv, n), pt);
+    if (tamper == 1) p.fin_h ^= 1;
+    if (tamper == 2) p.outputs[0] ^= 1;
+    return verify_lookup(p, n, vt);
 }
 int zko_lookup_roundtrip(const uint32_t* table_out, size_t n_table, const uint32_t* in, const uint32_t* outv, size_t n, int tamper) {
     Transcript pt("rt"), vt("rt");

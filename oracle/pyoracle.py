@@ -450,3 +450,42 @@ class features:
     def __exit__(self, *a):
         lib().zko_set_features(C.c_int(0), C.c_int(0))
         return False
+
+
+def prove_elementwise(tr, a, b, c, point, add: bool) -> bytes:
+    """Base-field prove_hadamard / prove_add as bincode bytes."""
+    A, pa = _u32(a); B, pb = _u32(b); Cc, pc = _u32(c); Pt, pp = _u32(point)
+    return _bytes_call(lib().zko_prove_elementwise, tr.h, C.c_int(int(add)), pa, pb, pc, C.c_size_t(A.size), pp, C.c_size_t(Pt.size))
+
+
+def elementwise_base_roundtrip(a, b, c, point, add: bool, tamper=False) -> bool:
+    A, pa = _u32(a); B, pb = _u32(b); Cc, pc = _u32(c); Pt, pp = _u32(point)
+    return bool(lib().zko_elementwise_base_roundtrip(C.c_int(int(add)), pa, pb, pc, C.c_size_t(A.size), pp, C.c_size_t(Pt.size),
+                                                C.c_int(int(tamper))))
+
+
+def prove_lookup(tr, table_out, inputs, outputs):
+    """Base-field prove_lookup (lookup.rs:432-604) -> (bincode bytes, status)."""
+    T, pt = _u32(table_out); I, pi = _u32(inputs); Oo, po = _u32(outputs)
+    st = C.c_int(0)
+    cap = 1 << 22
+    buf = (C.c_uint8 * cap)()
+    lib().zko_prove_lookup.restype = C.c_size_t
+    n = lib().zko_prove_lookup(tr.h, pt, C.c_size_t(T.size), pi, po, C.c_size_t(I.size), buf, C.c_size_t(cap), C.byref(st))
+    return bytes(buf[:n]), st.value
+
+
+def lookup_base_roundtrip(table_out, inputs, outputs, tamper=0) -> bool:
+    T, pt = _u32(table_out); I, pi = _u32(inputs); Oo, po = _u32(outputs)
+    return bool(lib().zko_lookup_base_roundtrip(pt, C.c_size_t(T.size), pi, po, C.c_size_t(I.size), C.c_int(tamper)))
+
+
+def prove_rmsnorm(tr, x, gamma, y, delta: int) -> bytes:
+    """Base-field prove_rmsnorm (rmsnorm.rs:96-246) as bincode bytes."""
+    X, px = _u32(x); G, pg = _u32(gamma); Y, py = _u32(y)
+    return _bytes_call(lib().zko_prove_rmsnorm, tr.h, px, pg, py, C.c_size_t(X.size), C.c_int32(delta))
+
+
+def rmsnorm_base_roundtrip(x, gamma, y, delta: int, tamper=0) -> bool:
+    X, px = _u32(x); G, pg = _u32(gamma); Y, py = _u32(y)
+    return bool(lib().zko_rmsnorm_base_roundtrip(px, pg, py, C.c_size_t(X.size), C.c_int32(delta), C.c_int(tamper)))

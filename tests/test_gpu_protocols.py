@@ -80,6 +80,32 @@ def test_matmul_succinct_ef_bytes(ctx, m, n):
     assert t.squeeze() == o.squeeze()
 
 
+@pytest.mark.parametrize("m,n", [(2, 2), (3, 5), (17, 9), (64, 40), (300, 2100), (1024, 1024)])
+def test_matmul_succinct_base_bytes(ctx, m, n):
+    rng = np.random.default_rng(m + 3 * n)
+    w, x = rnd(rng, m * n), rnd(rng, n)
+    y = O.matmul_forward(w, x, m, n)
+    t, o = zk.Transcript(ctx, b"mm-base"), O.Transcript(b"mm-base")
+    got = zp.prove_matmul_succinct(w, x, y, m, n, t)
+    exp = O.prove_matmul_succinct(o, w, x, y, m, n, ef=False)
+    assert got == exp
+    assert t.squeeze() == o.squeeze()
+
+
+@pytest.mark.parametrize("n,k", [(2, 1), (5, 3), (100, 7), (4096, 12), (5000, 13)])
+def test_mle_eval_bound_base_bytes(ctx, n, k):
+    rng = np.random.default_rng(n)
+    w, point = rnd(rng, n), rnd(rng, k)
+    padded = np.zeros(1 << k, np.uint32)
+    padded[:n] = w
+    root = O.commit_weights_fast(padded)
+    t, o = zk.Transcript(ctx, b"ev"), O.Transcript(b"ev")
+    got = zp.prove_mle_eval_bound(w, point, b"some-label", root, t)
+    exp, _ = O.prove_mle_eval_bound(o, w, point, b"some-label", ef=False)
+    assert got == exp
+    assert t.squeeze() == o.squeeze()
+
+
 @pytest.mark.parametrize("n", [2, 7, 16, 100, 5000])
 @pytest.mark.parametrize("add", [False, True])
 def test_elementwise_ef_bytes(ctx, n, add):
@@ -91,6 +117,21 @@ def test_elementwise_ef_bytes(ctx, n, add):
     t, o = zk.Transcript(ctx, b"ew"), O.Transcript(b"ew")
     got = (zp.prove_add_ef if add else zp.prove_hadamard_ef)(a, b, c, point, t)
     exp = O.prove_elementwise_ef(o, a, b, c, point, add)
+    assert got == exp
+    assert t.squeeze() == o.squeeze()
+
+
+@pytest.mark.parametrize("n", [2, 7, 16, 100, 5000, 20000])
+@pytest.mark.parametrize("add", [False, True])
+def test_elementwise_base_bytes(ctx, n, add):
+    rng = np.random.default_rng(n + 1)
+    a, b = rnd(rng, n), rnd(rng, n)
+    c = ((a.astype(np.int64) + b) % P if add else (a.astype(object) * b.astype(object)) % P).astype(np.uint32)
+    k = zp.log2_ceil(n)
+    point = rnd(rng, k)
+    t, o = zk.Transcript(ctx, b"ewb"), O.Transcript(b"ewb")
+    got = (zp.prove_add if add else zp.prove_hadamard)(a, b, c, point, t)
+    exp = O.prove_elementwise(o, a, b, c, point, add)
     assert got == exp
     assert t.squeeze() == o.squeeze()
 
@@ -135,6 +176,24 @@ def test_lookup_ef_bytes(ctx, n_table, n):
     exp, st = O.prove_lookup_ef(o, tab_out, ins, outs)
     assert st == 0 and got == exp
     assert t.squeeze() == o.squeeze()
+
+
+@pytest.mark.parametrize("n_table,n", [(256, 10), (256, 300), (65536, 50), (65536, 4096), (65536, 3072)])
+def test_lookup_base_bytes(ctx, n_table, n):
+    tab_in, tab_out = small_table(n_table, seed=5)
+    rng = np.random.default_rng(n + 7)
+    idx = rng.integers(0, n_table, n)
+    ins, outs = tab_in[idx], tab_out[idx]
+    t, o = zk.Transcript(ctx, b"lkb"), O.Transcript(b"lkb")
+    got = zp.prove_lookup(tab_out, ins, outs, t)
+    exp, st = O.prove_lookup(o, tab_out, ins, outs)
+    assert st == 0 and got == exp
+    assert t.squeeze() == o.squeeze()
+    bad = outs.copy()
+    bad[0] = (int(bad[0]) + 1) % P
+    with pytest.raises(zk.ZkbError) as e:
+        zp.prove_lookup(tab_out, ins, bad, zk.Transcript(ctx, b"lkb"))
+    assert e.value.code == 3
 
 
 def test_lookup_invalid_witness_is_an_error(ctx):

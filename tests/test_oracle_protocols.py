@@ -137,3 +137,45 @@ def test_layer_tamper_by_wrong_witness():
     ih = bytes(32)
     y, proof, ok = O.qwen_layer_prove(cfg, w, x, silu, sigm, 0, ih, verify=True)
     assert ok
+
+
+@pytest.mark.parametrize("n", [2, 5, 64, 300])
+@pytest.mark.parametrize("add", [False, True])
+def test_base_field_elementwise_roundtrip(n, add):
+    # elementwise.rs base-field tests (prove -> verify, tamper rejected)
+    rng = np.random.default_rng(n)
+    a = rng.integers(0, P, n, dtype=np.int64).astype(np.uint32)
+    b = rng.integers(0, P, n, dtype=np.int64).astype(np.uint32)
+    c = ((a.astype(np.int64) + b) % P if add else (a.astype(object) * b.astype(object)) % P).astype(np.uint32)
+    k = 1 if n <= 1 else (n - 1).bit_length()
+    point = rng.integers(0, P, k, dtype=np.int64).astype(np.uint32)
+    assert O.elementwise_base_roundtrip(a, b, c, point, add)
+    assert not O.elementwise_base_roundtrip(a, b, c, point, add, tamper=True)
+    wrong = c.copy(); wrong[0] = (int(wrong[0]) + 1) % P
+    assert not O.elementwise_base_roundtrip(a, b, wrong, point, add)
+
+
+@pytest.mark.parametrize("n_table,n", [(256, 10), (256, 300), (65536, 500)])
+def test_base_field_lookup_roundtrip(n_table, n):
+    tab_in, tab_out = small_table(n_table, seed=4)
+    rng = np.random.default_rng(n)
+    idx = rng.integers(0, n_table, n)
+    assert O.lookup_base_roundtrip(tab_out, tab_in[idx], tab_out[idx])
+    assert not O.lookup_base_roundtrip(tab_out, tab_in[idx], tab_out[idx], tamper=1)
+    assert not O.lookup_base_roundtrip(tab_out, tab_in[idx], tab_out[idx], tamper=2)
+    bad = tab_out[idx].copy()
+    bad[3] = (int(bad[3]) + 1) % P
+    proof, st = O.prove_lookup(O.Transcript(b"x"), tab_out, tab_in[idx], bad)
+    assert st == 3 and proof == b""
+
+
+@pytest.mark.parametrize("d", [4, 12, 100])
+def test_base_field_rmsnorm_roundtrip(d):
+    rng = np.random.default_rng(d)
+    x = np.mod(rng.integers(-127, 128, d), P).astype(np.uint32)
+    gamma = np.mod(rng.integers(-127, 128, d), P).astype(np.uint32)
+    y, xu, delta = O.rmsnorm_forward(x, gamma)
+    assert O.rmsnorm_base_roundtrip(xu, gamma, y, delta)
+    assert not O.rmsnorm_base_roundtrip(xu, gamma, y, delta, tamper=1)
+    wrong = y.copy(); wrong[1] = (int(wrong[1]) + 1) % P
+    assert not O.rmsnorm_base_roundtrip(xu, gamma, wrong, delta)

@@ -31,6 +31,7 @@ int32_t zkb_qwen_layer_create(zkb_ctx* c, const uint64_t dims[7], const uint32_t
         // commit_qwen_layer (qwen.rs:148-161): blake3 of each unpadded matrix
         ZKB_CUDA(cudaEventCreateWithFlags(&L->fwd_done, cudaEventDisableTiming));
         ZKB_CUDA(cudaMalloc(&L->roots_dev, 64 * 4));
+        if (const char* e = getenv("ZKB200_NO_GRAPH")) L->use_graph = !(e[0] && e[0] != '0');
         ZKB_CUDA(cudaMalloc(&L->seed_dev, 128));
         ZKB_CUDA(cudaHostAlloc(&L->seed_host, 128, cudaHostAllocDefault));
         static const int widx[8] = {W_Q, W_K, W_V, W_O, W_GPROJ, W_GATE, W_UP, W_DOWN};

@@ -81,16 +81,13 @@ int32_t zkb_fold_eq_matvec(zkb_ctx* c, const uint32_t* W, size_t m, size_t n, co
         unsigned long long* acc = (unsigned long long*)c->scratch(n_pad * w * 8);
         ZKB_CUDA(cudaMemsetAsync(acc, 0, n_pad * w * 8, c->stream));
         u32* res = (u32*)c->scratch(n_pad * w * 4);
-        const u32 col_ctas = (u32)((n + 511) / 512);
-        u32 want_rows = (u32)((c->sm_count * 6 + col_ctas - 1) / col_ctas);
-        size_t rows_per = (m + want_rows - 1) / want_rows;
-        rows_per = (rows_per + FOLD_ROWS_TILE - 1) / FOLD_ROWS_TILE * FOLD_ROWS_TILE;
-        dim3 grid(col_ctas, (u32)((m + rows_per - 1) / rows_per));
+        size_t rows_per = 0;
+        dim3 grid = fold_launch_dims(c->sm_count, m, n, &rows_per);
         if (ef) {
-            fold_eq_matvec_kernel<4><<<grid, 128, 0, c->stream>>>(dW, m, n, eq, rows_per, acc);
+            fold_eq_matvec_kernel<4><<<grid, FOLD_THREADS, 0, c->stream>>>(dW, m, n, eq, rows_per, acc);
             fold_finalize_kernel<4><<<grid_for(c, n_pad * 4), 256, 0, c->stream>>>(acc, n, n_pad, res);
         } else {
-            fold_eq_matvec_kernel<1><<<grid, 128, 0, c->stream>>>(dW, m, n, eq, rows_per, acc);
+            fold_eq_matvec_kernel<1><<<grid, FOLD_THREADS, 0, c->stream>>>(dW, m, n, eq, rows_per, acc);
             fold_finalize_kernel<1><<<grid_for(c, n_pad), 256, 0, c->stream>>>(acc, n, n_pad, res);
         }
         c->launches += 2;
@@ -139,6 +136,76 @@ int32_t zkb_prove_matmul_succinct_ef_bind(zkb_ctx* c, zkb_transcript* t, const u
 int32_t zkb_prove_matmul_succinct_ef(zkb_ctx* c, zkb_transcript* t, const uint32_t* W, const uint32_t* x, const uint32_t* y, size_t m,
                                      size_t n, int32_t w_on_device, uint8_t* out, size_t cap, size_t* len) {
     return zkb_prove_matmul_succinct_ef_bind(c, t, W, x, y, m, n, w_on_device, BIND_BLAKE3, NODE_BLAKE3, out, cap, len);
+}
+
+int32_t zkb_prove_matmul_succinct(zkb_ctx* c, zkb_transcript* t, const uint32_t* W, const uint32_t* x, const uint32_t* y, size_t m, size_t n,
+                                  int32_t w_on_device, uint8_t* out, size_t cap, size_t* len) {
+    if (!c || !t || !W || !x || !y || m == 0 || n == 0) return ZKB_E_ARG;
+    ZKB_TRY(c, {
+        c->use();
+        c->rec_reset();
+        const size_t n_pad = size_t(1) << log2_ceil_u(n);
+        const u32* dW = w_on_device ? W : up_pad(c, W, m * n, m * n);
+        u32* dx = up_pad(c, x, n, n_pad);
+        u32* dy = up_pad(c, y, m, m);
+        MatmulRec R = prove_matmul_succinct_base(c, t->dev, dW, dx, dy, (u32)m, (u32)n);
+        c->rec_fetch();
+        Ser s; s.rec = c->rec_host;
+        put_matmul_base(s, R);
+        c->scratch_reset();
+        int32_t rc = emit(c, s.b, out, cap, len);
+        if (rc) return rc;
+    });
+}
+// prove_mle_eval_bound / prove_mle_eval_no_merkle with base-field challenges.
+int32_t zkb_prove_mle_eval(zkb_ctx* c, zkb_transcript* t, const uint32_t* w, size_t n, const uint32_t* point, uint32_t k,
+                           const uint8_t* label, size_t label_len, const uint8_t root[32], uint8_t* out, size_t cap, size_t* len) {
+    if (!c || !t || (!w && n) || !point || k < 1 || k > 30 || n > (size_t(1) << k) || (label_len && (!label || !root)) || label_len > 63) return ZKB_E_ARG;
+    ZKB_TRY(c, {
+        c->use();
+        c->rec_reset();
+        u32* dw = up_pad(c, w, n, size_t(1) << k);
+        u32* dp = up_pad(c, point, k, (size_t)k + 4);
+        u32* droot = nullptr;
+        std::string lab;
+        if (label_len) {
+            lab.assign((const char*)label, label_len);
+            droot = up_pad(c, (const uint32_t*)root, 8, 8);
+        }
+        EvalRec R = prove_mle_eval_base(c, t->dev, dw, dp, k, label_len ? lab.c_str() : nullptr, droot);
+        c->rec_fetch();
+        Ser s; s.rec = c->rec_host;
+        put_eval_base(s, R);
+        c->scratch_reset();
+        int32_t rc = emit(c, s.b, out, cap, len);
+        if (rc) return rc;
+    });
+}
+
+// prove_hadamard (is_add = 0) / prove_add (is_add = 1) with base-field challenges.
+int32_t zkb_prove_elementwise(zkb_ctx* c, zkb_transcript* t, int32_t is_add, const uint32_t* a, const uint32_t* b, const uint32_t* cv, size_t n,
+                              const uint32_t* point, uint32_t k, uint8_t* out, size_t cap, size_t* len) {
+    if (!c || !t || !a || !b || !cv || !point || k < 1 || k > 28 || n > (size_t(1) << k)) return ZKB_E_ARG;
+    ZKB_TRY(c, {
+        c->use();
+        c->rec_reset();
+        const size_t np = size_t(1) << k;
+        u32* da = up_pad(c, a, n, np);
+        u32* db = up_pad(c, b, n, np);
+        u32* dc = up_pad(c, cv, n, np);
+        u32* dp = up_pad(c, point, k, (size_t)k + 4);
+        Ser s;
+        if (is_add) {
+            AddRec R = prove_add_base(c, t->dev, da, db, dc, dp, k);
+            c->rec_fetch(); s.rec = c->rec_host; put_add_base(s, R);
+        } else {
+            HadamardRec R = prove_hadamard_base(c, t->dev, da, db, dc, dp, k);
+            c->rec_fetch(); s.rec = c->rec_host; put_hadamard_base(s, R);
+        }
+        c->scratch_reset();
+        int32_t rc = emit(c, s.b, out, cap, len);
+        if (rc) return rc;
+    });
 }
 
 int32_t zkb_prove_elementwise_ef(zkb_ctx* c, zkb_transcript* t, int32_t is_add, const uint32_t* a, const uint32_t* b, const uint32_t* cv,
@@ -222,6 +289,28 @@ int32_t zkb_prove_lookup_ef(zkb_ctx* c, zkb_transcript* t, const uint32_t* table
         if (rc) return rc;
         Ser s; s.rec = c->rec_host;
         put_lookup(s, R, false, inputs, outputs);
+        rc = emit(c, s.b, out, cap, len);
+        if (rc) return rc;
+    });
+}
+
+int32_t zkb_prove_lookup(zkb_ctx* c, zkb_transcript* t, const uint32_t* table_out, size_t n_table, const uint32_t* inputs,
+                         const uint32_t* outputs, size_t n, uint8_t* out, size_t cap, size_t* len) {
+    if (!c || !t || !table_out || !inputs || !outputs || n == 0 || (n_table != 256 && n_table != 65536)) return ZKB_E_ARG;
+    ZKB_TRY(c, {
+        c->use();
+        c->rec_reset();
+        clear_status(c);
+        u32* dt = up_pad(c, table_out, n_table, n_table);
+        u32* di = up_pad(c, inputs, n, n); u32* dout = up_pad(c, outputs, n, n);
+        LookupRec R = prove_lookup_base(c, t->dev, dt, (u32)n_table, di, dout, (u32)n);
+        c->rec_fetch();
+        uint32_t st = c->read_status();
+        c->scratch_reset();
+        int32_t rc = status_to_code(c, st);
+        if (rc) return rc;
+        Ser s; s.rec = c->rec_host;
+        put_lookup_base(s, R, inputs, outputs);
         rc = emit(c, s.b, out, cap, len);
         if (rc) return rc;
     });

@@ -42,19 +42,25 @@ __global__ void eq_evals_kernel(const T* __restrict__ r, u32 k, T* out) {
 }
 
 // ---- fold_eq_matvec: acc[j] += eq[i] * W[i][j] -----------------------------------------------
-// grid.x tiles columns (blockDim.x * 4 per CTA), grid.y tiles rows.  Each CTA adds its partial
-// column sums (canonical, < 2^31) to 64-bit accumulators with atomicAdd; integer addition is
-// associative, so the result does not depend on the order.  NC = 1 (base eq) or 4 (EF eq).
-constexpr int FOLD_ROWS_TILE = 64;
+// grid.x tiles columns (128 * 4 per CTA), grid.y tiles rows.  A CTA is 4 row groups x 128 column
+// threads: group g takes rows g, g+4, ... of the CTA's row range, six rows per step so that six
+// 16-byte loads per thread are in flight (the kernel is bound by memory latency otherwise), the
+// four groups' column sums are added in shared memory and one group adds them to the 64-bit
+// accumulators with atomicAdd.  Integer addition is associative, so the result does not depend
+// on the order.  NC = 1 (base eq) or 4 (EF eq).
+constexpr int FOLD_ROWS_TILE = 24;       // granularity of the per-CTA row range (= FOLD_GROUPS * FOLD_UNROLL)
+constexpr int FOLD_GROUPS = 4;
+constexpr int FOLD_UNROLL = 6;
 
 __device__ __forceinline__ u64 part_reduce(u64 a) { return (a & ZKB_P) + (a >> 31); }   // keeps a < 2^34
 
 template <int NC>
-__global__ void __launch_bounds__(128) fold_eq_matvec_kernel(const u32* __restrict__ W, size_t m, size_t n,
-                                                            const u32* __restrict__ eq /* [m_pad][NC] */,
-                                                            size_t rows_per_cta, unsigned long long* acc /* [n][NC] */) {
-    __shared__ u32 eq_s[FOLD_ROWS_TILE * NC];
-    const size_t j0 = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+__global__ void __launch_bounds__(128 * FOLD_GROUPS) fold_eq_matvec_kernel(const u32* __restrict__ W, size_t m, size_t n,
+                                                                          const u32* __restrict__ eq /* [m_pad][NC] */,
+                                                                          size_t rows_per_cta, unsigned long long* acc /* [n][NC] */) {
+    __shared__ u32 sums[FOLD_GROUPS - 1][128][4 * NC];
+    const int tx = threadIdx.x & 127, g = threadIdx.x >> 7;
+    const size_t j0 = ((size_t)blockIdx.x * 128 + tx) * 4;
     const size_t r0 = (size_t)blockIdx.y * rows_per_cta;
     const size_t r1 = r0 + rows_per_cta < m ? r0 + rows_per_cta : m;
     const bool vec = (n % 4 == 0) && (j0 + 4 <= n);
@@ -64,60 +70,82 @@ __global__ void __launch_bounds__(128) fold_eq_matvec_kernel(const u32* __restri
 #pragma unroll
         for (int k = 0; k < NC; k++) a[c][k] = 0;
 
-    for (size_t rb = r0; rb < r1; rb += FOLD_ROWS_TILE) {
-        const int rows = (int)(r1 - rb < FOLD_ROWS_TILE ? r1 - rb : FOLD_ROWS_TILE);
-        __syncthreads();
-        for (int t = threadIdx.x; t < rows * NC; t += blockDim.x) eq_s[t] = eq[rb * NC + t];
-        __syncthreads();
-        if (j0 < n) {
-            // three rows per step: their 16-byte loads are issued together (more bytes in flight per
-            // thread), their products (< 2^62 each) are summed unreduced and folded once
-            int rr = 0;
-            for (; rr + 3 <= rows; rr += 3) {
-                u32 w[3][4];
+    if (j0 < n) {
+        size_t row = r0 + g;
+        // six rows per step: 6 products (< 2^62 each) do not fit one 64-bit sum, so fold after three
+        for (; row + (FOLD_UNROLL - 1) * FOLD_GROUPS < r1; row += FOLD_UNROLL * FOLD_GROUPS) {
+            u32 w[FOLD_UNROLL][4];
 #pragma unroll
-                for (int q = 0; q < 3; q++) {
-                    const u32* row = W + (rb + rr + q) * n;
-                    if (vec) {
-                        uint4 t = *reinterpret_cast<const uint4*>(row + j0);
-                        w[q][0] = t.x; w[q][1] = t.y; w[q][2] = t.z; w[q][3] = t.w;
-                    } else {
+            for (int q = 0; q < FOLD_UNROLL; q++) {
+                const u32* rp = W + (row + (size_t)q * FOLD_GROUPS) * n;
+                if (vec) {
+                    uint4 t = *reinterpret_cast<const uint4*>(rp + j0);
+                    w[q][0] = t.x; w[q][1] = t.y; w[q][2] = t.z; w[q][3] = t.w;
+                } else {
 #pragma unroll
-                        for (int c = 0; c < 4; c++) w[q][c] = (j0 + c < n) ? row[j0 + c] : 0u;
-                    }
-                }
-#pragma unroll
-                for (int k = 0; k < NC; k++) {
-                    const u32 e0 = eq_s[rr * NC + k], e1 = eq_s[(rr + 1) * NC + k], e2 = eq_s[(rr + 2) * NC + k];
-#pragma unroll
-                    for (int c = 0; c < 4; c++)
-                        a[c][k] = part_reduce(a[c][k] + (u64)e0 * w[0][c] + (u64)e1 * w[1][c] + (u64)e2 * w[2][c]);
+                    for (int c = 0; c < 4; c++) w[q][c] = (j0 + c < n) ? rp[j0 + c] : 0u;
                 }
             }
-            for (; rr < rows; rr++) {
-                const u32* row = W + (rb + rr) * n;
-                u32 w[4];
 #pragma unroll
-                for (int c = 0; c < 4; c++) w[c] = (j0 + c < n) ? row[j0 + c] : 0u;
+            for (int k = 0; k < NC; k++) {
+                u32 e[FOLD_UNROLL];
 #pragma unroll
-                for (int k = 0; k < NC; k++) {
-                    const u32 e = eq_s[rr * NC + k];
+                for (int q = 0; q < FOLD_UNROLL; q++) e[q] = __ldg(eq + (row + (size_t)q * FOLD_GROUPS) * NC + k);
 #pragma unroll
-                    for (int c = 0; c < 4; c++) a[c][k] = part_reduce(a[c][k] + (u64)e * w[c]);
+                for (int c = 0; c < 4; c++) {
+                    u64 t0 = (u64)e[0] * w[0][c] + (u64)e[1] * w[1][c] + (u64)e[2] * w[2][c];
+                    u64 t1 = (u64)e[3] * w[3][c] + (u64)e[4] * w[4][c] + (u64)e[5] * w[5][c];
+                    a[c][k] = part_reduce(a[c][k] + part_reduce(t0) + part_reduce(t1));
                 }
             }
         }
+        for (; row < r1; row += FOLD_GROUPS) {
+            const u32* rp = W + row * n;
+            u32 w[4];
+#pragma unroll
+            for (int c = 0; c < 4; c++) w[c] = (j0 + c < n) ? rp[j0 + c] : 0u;
+#pragma unroll
+            for (int k = 0; k < NC; k++) {
+                const u32 e = __ldg(eq + row * NC + k);
+#pragma unroll
+                for (int c = 0; c < 4; c++) a[c][k] = part_reduce(a[c][k] + (u64)e * w[c]);
+            }
+        }
     }
-    if (j0 < n) {
+    if (g > 0) {
+#pragma unroll
+        for (int c = 0; c < 4; c++)
+#pragma unroll
+            for (int k = 0; k < NC; k++) sums[g - 1][tx][c * NC + k] = red64(a[c][k]);
+    }
+    __syncthreads();
+    if (g == 0 && j0 < n) {
 #pragma unroll
         for (int c = 0; c < 4; c++) {
             if (j0 + c < n) {
 #pragma unroll
-                for (int k = 0; k < NC; k++) atomicAdd(acc + (j0 + c) * NC + k, (unsigned long long)red64(a[c][k]));
+                for (int k = 0; k < NC; k++) {
+                    u64 v = red64(a[c][k]);
+#pragma unroll
+                    for (int q = 0; q < FOLD_GROUPS - 1; q++) v += sums[q][tx][c * NC + k];
+                    atomicAdd(acc + (j0 + c) * NC + k, (unsigned long long)v);
+                }
             }
         }
     }
 }
+// Launch shape: 512 columns per CTA; rows split so that about two CTAs per SM exist.
+inline dim3 fold_launch_dims(int sm_count, size_t m, size_t n, size_t* rows_per_out) {
+    const unsigned col_ctas = (unsigned)((n + 511) / 512);
+    unsigned want_rows = (unsigned)((sm_count * 2 + col_ctas - 1) / col_ctas);
+    if (want_rows < 1) want_rows = 1;
+    size_t rows_per = (m + want_rows - 1) / want_rows;
+    rows_per = (rows_per + FOLD_ROWS_TILE - 1) / FOLD_ROWS_TILE * FOLD_ROWS_TILE;
+    *rows_per_out = rows_per;
+    return dim3(col_ctas, (unsigned)((m + rows_per - 1) / rows_per));
+}
+constexpr int FOLD_THREADS = 128 * FOLD_GROUPS;
+
 // acc -> canonical u32 (interleaved EF coordinates when NC = 4), zero beyond n up to n_pad.
 template <int NC>
 __global__ void fold_finalize_kernel(unsigned long long* acc, size_t n, size_t n_pad, u32* out) {
@@ -129,32 +157,64 @@ __global__ void fold_finalize_kernel(unsigned long long* acc, size_t n, size_t n
 }
 
 // ---- forward matvec: y[i] = sum_j W[i][j] x[j] (+ nothing; the Qwen path has no bias) ---------
-// One warp per row; x is read through the read-only cache (it is small and reused by every row).
+// WPR warps share a row (each a contiguous quarter / half / ... of it), so that short matrices
+// still put enough warps on every SM; every lane keeps four 16-byte loads in flight.  x is read
+// through the read-only cache (it is small and reused by every row).  CTA = 8 warps = 8 / WPR rows.
+template <int WPR>
 __global__ void __launch_bounds__(256) matvec_forward_kernel(const u32* __restrict__ W, const u32* __restrict__ x,
                                                              size_t m, size_t n, u32* y) {
-    const int lane = threadIdx.x & 31;
-    const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const size_t nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
-    for (size_t i = warp; i < m; i += nwarps) {
-        const u32* row = W + i * n;
+    __shared__ u32 part[8];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int sub = warp % WPR;                         // which part of the row
+    constexpr int RPC = 8 / WPR;                        // rows per CTA
+    for (size_t i0 = (size_t)blockIdx.x * RPC; i0 < m; i0 += (size_t)gridDim.x * RPC) {
+        const size_t i = i0 + warp / WPR;
         u64 acc = 0;
-        if (n % 4 == 0) {
-            int since = 0;
-            for (size_t j = (size_t)lane * 4; j < n; j += 128) {
-                uint4 w = *reinterpret_cast<const uint4*>(row + j);
-                uint4 v = __ldg(reinterpret_cast<const uint4*>(x + j));
-                u64 t = (u64)w.x * v.x + (u64)w.y * v.y;      // two products < 2^63
-                u64 u = (u64)w.z * v.z + (u64)w.w * v.w;
-                acc += part_reduce(t) + part_reduce(u);
-                if (++since == (1 << 20)) { since = 0; acc = part_reduce(acc); }
+        if (i < m) {
+            const u32* row = W + i * n;
+            if (n % 4 == 0) {
+                // this warp's span of 16-byte groups
+                const size_t groups = n / 4, per = (groups + WPR - 1) / WPR;
+                const size_t g0 = (size_t)sub * per, g1 = g0 + per < groups ? g0 + per : groups;
+                const uint4* rw = reinterpret_cast<const uint4*>(row);
+                const uint4* xv = reinterpret_cast<const uint4*>(x);
+                size_t gidx = g0 + lane;
+                for (; gidx + 96 < g1; gidx += 128) {
+                    uint4 w0 = rw[gidx], w1 = rw[gidx + 32], w2 = rw[gidx + 64], w3 = rw[gidx + 96];
+                    uint4 v0 = __ldg(xv + gidx), v1 = __ldg(xv + gidx + 32), v2 = __ldg(xv + gidx + 64), v3 = __ldg(xv + gidx + 96);
+                    acc += part_reduce((u64)w0.x * v0.x + (u64)w0.y * v0.y) + part_reduce((u64)w0.z * v0.z + (u64)w0.w * v0.w);
+                    acc += part_reduce((u64)w1.x * v1.x + (u64)w1.y * v1.y) + part_reduce((u64)w1.z * v1.z + (u64)w1.w * v1.w);
+                    acc += part_reduce((u64)w2.x * v2.x + (u64)w2.y * v2.y) + part_reduce((u64)w2.z * v2.z + (u64)w2.w * v2.w);
+                    acc += part_reduce((u64)w3.x * v3.x + (u64)w3.y * v3.y) + part_reduce((u64)w3.z * v3.z + (u64)w3.w * v3.w);
+                    acc = part_reduce(acc);             // 8 terms below 2^33 each: stays far below 2^64
+                }
+                for (; gidx < g1; gidx += 32) {
+                    uint4 w0 = rw[gidx];
+                    uint4 v0 = __ldg(xv + gidx);
+                    acc = part_reduce(acc + part_reduce((u64)w0.x * v0.x + (u64)w0.y * v0.y) + part_reduce((u64)w0.z * v0.z + (u64)w0.w * v0.w));
+                }
+            } else {
+                const size_t per = (n + WPR - 1) / WPR;
+                const size_t c0 = (size_t)sub * per, c1 = c0 + per < n ? c0 + per : n;
+                for (size_t j = c0 + lane; j < c1; j += 32) acc = part_reduce(acc + part_reduce((u64)row[j] * __ldg(x + j)));
             }
-        } else {
-            for (size_t j = lane; j < n; j += 32) acc += part_reduce((u64)row[j] * __ldg(x + j));
         }
         u32 r = red64(acc);
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) r = add31(r, __shfl_down_sync(0xffffffffu, r, off));
-        if (lane == 0) y[i] = r;
+        if (WPR == 1) {
+            if (lane == 0 && i < m) y[i] = r;
+        } else {
+            if (lane == 0) part[warp] = r;
+            __syncthreads();
+            if (lane == 0 && sub == 0 && i < m) {
+                u32 t = r;
+#pragma unroll
+                for (int q = 1; q < WPR; q++) t = add31(t, part[warp + q]);
+                y[i] = t;
+            }
+            __syncthreads();
+        }
     }
 }
 

@@ -73,6 +73,16 @@ __global__ void __launch_bounds__(1024) logup_compact_kernel(const u32* __restri
     }
 }
 
+// Base-field path: the committed active subtable is inp + beta * out (lookup.rs:466-481).
+__global__ void logup_encode_active_kernel(const u32* __restrict__ act_idx, const u32* __restrict__ dyn, const u32* __restrict__ table_out,
+                                           u32 n_table, const u32* __restrict__ beta, u32* out) {
+    const u32 n_active = dyn[0], b = beta[0];
+    for (u32 k = blockIdx.x * blockDim.x + threadIdx.x; k < n_active; k += gridDim.x * blockDim.x) {
+        u32 j = act_idx[k];
+        out[k] = add31(table_input_at(j, n_table), mul31(b, table_out[j]));
+    }
+}
+
 constexpr int LOGUP_BATCH = 4;
 
 template <class ChalT> struct LogupEnc;

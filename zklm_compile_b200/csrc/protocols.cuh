@@ -143,15 +143,10 @@ inline MatmulRec prove_matmul_succinct_ef(zkb_ctx* c, TrState* tr, const u32* W,
     ZKB_CUDA(cudaMemsetAsync(acc, 0, n_pad * 4 * 8, c->stream));
     Fe* w_partial = (Fe*)c->scratch(n_pad * 16);
     {
-        const u32 col_ctas = (u32)((n + 511) / 512);
-        u32 want_rows = (u32)((c->sm_count * 6 + col_ctas - 1) / col_ctas);
-        if (want_rows < 1) want_rows = 1;
-        size_t rows_per = (m + want_rows - 1) / want_rows;
-        rows_per = (rows_per + FOLD_ROWS_TILE - 1) / FOLD_ROWS_TILE * FOLD_ROWS_TILE;
-        u32 row_ctas = (u32)((m + rows_per - 1) / rows_per);
-        dim3 grid(col_ctas, row_ctas);
+        size_t rows_per = 0;
+        dim3 grid = fold_launch_dims(c->sm_count, m, n, &rows_per);
         int rg = c->range_begin(ZKB_RANGE_FOLD_EQ_MATVEC, 4.0 * m * n);
-        fold_eq_matvec_kernel<4><<<grid, 128, 0, c->stream>>>(W, m, n, (const u32*)eq_r, rows_per, acc);
+        fold_eq_matvec_kernel<4><<<grid, FOLD_THREADS, 0, c->stream>>>(W, m, n, (const u32*)eq_r, rows_per, acc);
         c->range_end(rg);
         ZKB_LAUNCHED(c);
         fold_finalize_kernel<4><<<grid_for(c, n_pad * 4), 256, 0, c->stream>>>(acc, n, n_pad, (u32*)w_partial);
@@ -207,6 +202,86 @@ inline void put_matmul(Ser& s, const MatmulRec& R, bool stripped) {
         s.u8(1);                                            // basefold_proof: Some
         put_basefold_proof(s, s.rec, R.bf);
     }
+}
+
+// ---- base-field twins: matmul with base-field challenges (MLP / GPT-2 op lists) --------------------
+// prove_mle_eval_no_merkle (weight_commitment.rs:177-206): eq table at a base-field point, the
+// full-message product sumcheck of (eq, w), then the 24 discarded query squeezes.  w: 2^k values
+// on device (already zero-padded); point: k base-field challenges on device.
+inline EvalRec prove_mle_eval_base(zkb_ctx* c, TrState* tr, const u32* w, const u32* point, u32 k, const char* label = nullptr,
+                                   const u32* root_dev = nullptr) {
+    if (label) {                       // prove_mle_eval_bound (weight_commitment.rs:437-447)
+        ScriptBuilder sb;
+        sb.str(label);
+        sb.words_dev(root_dev, 8);
+        sb.run(c, tr);
+    }
+    size_t n = size_t(1) << k;
+    Fp* eq = (Fp*)c->scratch(n * 4 + 16);
+    eq_evals_kernel<Fp><<<grid_for(c, n), 256, 0, c->stream>>>((const Fp*)point, k, eq);
+    ZKB_LAUNCHED(c);
+    const u32* tabs[3] = {(const u32*)eq, w, nullptr};
+    ScOpts o;
+    o.post_squeezes = 24;
+    EvalRec r;
+    r.sc = sumcheck_enqueue(c, tr, ZKB_SC_PRODUCT, tabs, k, o);
+    return r;
+}
+// MleEvalProof {eval_sumcheck, eq_at_s, w_at_s, merkle_opening: None} (weight_commitment.rs:65-73)
+inline void put_eval_base(Ser& s, const EvalRec& e) {
+    s.sumcheck(e.sc, true);
+    s.words(e.sc.fin, 1);
+    s.words(e.sc.fin + 1, 1);
+    s.u8(0);
+}
+// prove_matmul_succinct (matmul.rs:482-511) over prove_matmul (matmul.rs:134-180) with the
+// default weight binding (matmul.rs:346-355).
+inline MatmulRec prove_matmul_succinct_base(zkb_ctx* c, TrState* tr, const u32* W, const u32* x, const u32* y, u32 m, u32 n) {
+    MatmulRec R;
+    R.log_m = log2_ceil_u(m); R.log_n = log2_ceil_u(n);
+    const size_t m_pad = size_t(1) << R.log_m, n_pad = size_t(1) << R.log_n;
+    R.n_pad = (u32)n_pad;
+    R.r_point = c->rec_alloc(R.log_m);
+    u32* r_dev = c->rec_dev + R.r_point;
+    {
+        ScriptBuilder sb;
+        sb.words_dev(y, m, (u32)m_pad);
+        sb.squeeze(r_dev, R.log_m);
+        sb.run(c, tr);
+    }
+    Fp* eq_r = (Fp*)c->scratch(m_pad * 4 + 16);
+    eq_evals_kernel<Fp><<<grid_for(c, m_pad), 256, 0, c->stream>>>((const Fp*)r_dev, R.log_m, eq_r);
+    ZKB_LAUNCHED(c);
+    unsigned long long* acc = (unsigned long long*)c->scratch(n_pad * 8);
+    ZKB_CUDA(cudaMemsetAsync(acc, 0, n_pad * 8, c->stream));
+    u32* w_partial = (u32*)c->scratch(n_pad * 4 + 16);
+    {
+        size_t rows_per = 0;
+        dim3 grid = fold_launch_dims(c->sm_count, m, n, &rows_per);
+        int rg = c->range_begin(ZKB_RANGE_FOLD_EQ_MATVEC, 4.0 * m * n);
+        fold_eq_matvec_kernel<1><<<grid, FOLD_THREADS, 0, c->stream>>>(W, m, n, (const u32*)eq_r, rows_per, acc);
+        c->range_end(rg);
+        ZKB_LAUNCHED(c);
+        fold_finalize_kernel<1><<<grid_for(c, n_pad), 256, 0, c->stream>>>(acc, n, n_pad, w_partial);
+        ZKB_LAUNCHED(c);
+    }
+    const u32* tabs[3] = {w_partial, x, nullptr};
+    R.sc = sumcheck_enqueue(c, tr, ZKB_SC_PRODUCT, tabs, R.log_n);
+    R.root = commit_small(c, w_partial, (u32)n_pad, nullptr, (u32)n_pad, tr);
+    R.eval = prove_mle_eval_base(c, tr, w_partial, c->rec_dev + R.sc.chal, R.log_n);
+    return R;
+}
+// SuccinctMatmulProof (matmul.rs:458-474)
+inline void put_matmul_base(Ser& s, const MatmulRec& R) {
+    s.sumcheck(R.sc, true);
+    s.words(R.sc.fin, 1); s.words(R.sc.fin + 1, 1);
+    s.u64le(R.log_m); s.words(R.r_point, R.log_m);
+    s.u64le(R.log_n); s.words(R.sc.chal, R.log_n);
+    put_eval_base(s, R.eval);
+    s.u32le(0);                                             // w_claimed_value
+    s.commitment(R.root, (u64)R.n_pad);
+    s.u8(0);                                                // bound
+    s.u8(0);                                                // basefold_proof: None
 }
 
 // ---- hadamard / add -------------------------------------------------------------------------------
@@ -272,6 +347,55 @@ inline void put_add(Ser& s, const AddRec& R, bool stripped) {
     s.sumcheck(R.sb, !stripped); s.ef(R.sb.fin); s.ef(R.sb.fin + 4);
     s.claimed_sum_ef(R.eval.sc);
     put_eval(s, R.eval, true);
+    s.commitment(R.root, u64(1) << R.k);
+}
+
+// ---- base-field twins of hadamard / add (elementwise.rs:50-98, 189-235) ---------------------------
+// a, b, cvec: device vectors zero-padded to 2^k; point: k base-field challenges on device.
+inline HadamardRec prove_hadamard_base(zkb_ctx* c, TrState* tr, const u32* a, const u32* b, const u32* cvec, const u32* point, u32 k) {
+    HadamardRec R;
+    R.k = k;
+    size_t n = size_t(1) << k;
+    R.root = commit_small(c, cvec, (u32)n, nullptr, (u32)n, tr);
+    Fp* eq = (Fp*)c->scratch(n * 4 + 16);
+    eq_evals_kernel<Fp><<<grid_for(c, n), 256, 0, c->stream>>>((const Fp*)point, k, eq);
+    ZKB_LAUNCHED(c);
+    const u32* tabs[3] = {(const u32*)eq, a, b};
+    R.sc = sumcheck_enqueue(c, tr, ZKB_SC_TRIPLE, tabs, k);
+    R.eval = prove_mle_eval_base(c, tr, cvec, point, k, "hadamard-c-eval", c->rec_dev + R.root);
+    return R;
+}
+// c_eval = MLE of c at the point = s0 + s1 of round 0 of the eval sumcheck (sum of eq . c)
+inline void put_claimed_sum_base(Ser& s, const ScRec& r) { s.u32le(add31(s.rec[r.polys], s.rec[r.polys + 1])); }
+// HadamardProof {product_sumcheck, product_finals(3), c_eval, c_eval_proof, c_commitment} (elementwise.rs:31-44)
+inline void put_hadamard_base(Ser& s, const HadamardRec& R) {
+    s.sumcheck(R.sc, true);
+    s.words(R.sc.fin, 3);
+    put_claimed_sum_base(s, R.eval.sc);
+    put_eval_base(s, R.eval);
+    s.commitment(R.root, u64(1) << R.k);
+}
+inline AddRec prove_add_base(zkb_ctx* c, TrState* tr, const u32* a, const u32* b, const u32* cvec, const u32* point, u32 k) {
+    AddRec R;
+    R.k = k;
+    size_t n = size_t(1) << k;
+    R.root = commit_small(c, cvec, (u32)n, nullptr, (u32)n, tr);
+    Fp* eq = (Fp*)c->scratch(n * 4 + 16);
+    eq_evals_kernel<Fp><<<grid_for(c, n), 256, 0, c->stream>>>((const Fp*)point, k, eq);
+    ZKB_LAUNCHED(c);
+    const u32* ta[3] = {(const u32*)eq, a, nullptr};
+    R.sa = sumcheck_enqueue(c, tr, ZKB_SC_PRODUCT, ta, k);
+    const u32* tb[3] = {(const u32*)eq, b, nullptr};
+    R.sb = sumcheck_enqueue(c, tr, ZKB_SC_PRODUCT, tb, k);
+    R.eval = prove_mle_eval_base(c, tr, cvec, point, k, "add-c-eval", c->rec_dev + R.root);
+    return R;
+}
+// AddProof (elementwise.rs:165-181)
+inline void put_add_base(Ser& s, const AddRec& R) {
+    s.sumcheck(R.sa, true); s.words(R.sa.fin, 2);
+    s.sumcheck(R.sb, true); s.words(R.sb.fin, 2);
+    put_claimed_sum_base(s, R.eval.sc);
+    put_eval_base(s, R.eval);
     s.commitment(R.root, u64(1) << R.k);
 }
 

@@ -197,6 +197,83 @@ inline void put_lookup(Ser& s, const LookupRec& R, bool stripped, const u32* in_
     s.root(R.digest);
 }
 
+// Base-field twin (lookup.rs:432-604): challenges in M31, active subtable committed as
+// inp + beta * out, all-ones product sumcheck over base-field h.
+inline LookupRec prove_lookup_base(zkb_ctx* c, TrState* tr, const u32* table_out, u32 n_table, const u32* inputs, const u32* outputs, u32 n) {
+    LookupRec R;
+    R.n = n;
+    const u32 max_active = n < n_table ? n : n_table;
+    R.max_nv = log2_ceil_u((size_t)n + max_active);
+    const size_t cap = size_t(1) << R.max_nv;
+    R.chal = c->rec_alloc(2);
+    R.dyn = c->rec_alloc(4);
+    u32* chal = c->rec_dev + R.chal;
+    u32* dyn = c->rec_dev + R.dyn;
+    {
+        ScriptBuilder sb;
+        unsigned char zero[32] = {0};
+        sb.bytes(zero, 32);
+        sb.word(n);
+        sb.pairs_dev(inputs, outputs, n);
+        sb.squeeze(chal, 2);                                     // beta then alpha
+        sb.run(c, tr);
+    }
+    u32* mult = (u32*)c->scratch((size_t)n_table * 4);
+    u32* act_idx = (u32*)c->scratch((size_t)max_active * 4 + 16);
+    u32* act_mult = (u32*)c->scratch((size_t)max_active * 4 + 16);
+    u32* act_entry = (u32*)c->scratch((size_t)max_active * 4 + 16);
+    u32* act_enc = (u32*)c->scratch((size_t)max_active * 4 + 16);
+    ZKB_CUDA(cudaMemsetAsync(mult, 0, (size_t)n_table * 4, c->stream));
+    logup_hist_kernel<<<grid_for(c, n), 256, 0, c->stream>>>(inputs, n, n_table, mult);
+    ZKB_LAUNCHED(c);
+    logup_compact_kernel<<<1, 1024, 0, c->stream>>>(mult, table_out, n_table, n, act_idx, act_mult, act_entry, dyn);
+    ZKB_LAUNCHED(c);
+    logup_encode_active_kernel<<<grid_for(c, max_active), 256, 0, c->stream>>>(act_idx, dyn, table_out, n_table, chal, act_enc);
+    ZKB_LAUNCHED(c);
+    Fp* h = (Fp*)c->scratch(cap * 4 + 16);
+    logup_h_kernel<Fp><<<grid_for(c, cap / LOGUP_BATCH + 1), 256, 0, c->stream>>>(inputs, outputs, table_out, n_table, act_idx, act_mult, dyn,
+                                                                                   (const Fp*)chal, h, (u32)cap, c->status);
+    ZKB_LAUNCHED(c);
+    R.root_table = commit_small(c, act_enc, 0, dyn, max_active, tr);
+    R.root_mult = commit_small(c, act_mult, 0, dyn, max_active, tr);
+    const u32* tabs[3] = {(const u32*)h, nullptr, nullptr};
+    ScOpts o;
+    o.dyn_nv = dyn + 1;
+    o.dyn_off = (long)R.dyn;
+    o.check_zero_sum = true;
+    R.sc = sumcheck_enqueue(c, tr, ZKB_SC_PRODUCT_ONES, tabs, R.max_nv, o);
+    u32* cat = (u32*)c->scratch(((size_t)2 * n + 2) * 4);
+    logup_digest_concat_kernel<<<grid_for(c, 2 * (size_t)n + 2), 256, 0, c->stream>>>(inputs, outputs, n, cat);
+    ZKB_LAUNCHED(c);
+    R.digest = c->rec_alloc(8);
+    {
+        unsigned char pre[31];
+        memcpy(pre, "lookup-external-data-v1", 23);
+        u64 n64 = n;
+        memcpy(pre + 23, &n64, 8);
+        size_t max_chunks = ((size_t)(2 * n + 2) * 4 + 31 + 1023) / 1024 + 1;
+        u32* cvs = (u32*)c->scratch(max_chunks * 32);
+        b3_commit_kernel<<<1, 1024, 0, c->stream>>>(b3_prefix(pre, 31), cat, 2 * n + 2, nullptr, cvs, c->rec_dev + R.digest, nullptr);
+        ZKB_LAUNCHED(c);
+    }
+    return R;
+}
+// LookupProof (lookup.rs:39-85)
+inline void put_lookup_base(Ser& s, const LookupRec& R, const u32* in_host, const u32* out_host) {
+    const u32 n_active = s.rec[R.dyn], nv = s.rec[R.dyn + 1];
+    s.commitment(R.root_table, n_active);
+    s.commitment(R.root_mult, n_active);
+    s.sumcheck(R.sc, true, nv);
+    s.u32le(1);                              // ones_at_s
+    s.words(R.sc.fin, 1);                    // h_at_s
+    s.u32le(s.rec[R.chal + 1]);              // alpha
+    s.u32le(s.rec[R.chal]);                  // beta
+    s.u64le(R.n); for (u32 i = 0; i < R.n; i++) s.u32le(in_host[i]);
+    s.u64le(R.n); for (u32 i = 0; i < R.n; i++) s.u32le(out_host[i]);
+    s.u64le(0);                              // multiplicities: empty
+    s.root(R.digest);
+}
+
 // ---- lookup, squeeze the hadamard point, hadamard (sigmoid_gate.rs:90-114, swiglu.rs:99-118) ------
 struct GateRec { LookupRec lk; HadamardRec had; size_t point = 0; };
 inline GateRec prove_gate_ef(zkb_ctx* c, TrState* tr, const u32* table_out, u32 n_table, const u32* lk_in, const u32* lk_out,

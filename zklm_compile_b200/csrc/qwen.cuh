@@ -64,12 +64,27 @@ namespace zkb {
 
 inline size_t pad_pow2(size_t n) { return size_t(1) << log2_ceil_u(n); }
 
+// Warps per row: enough to give every SM about 32 warps even for short matrices.
+inline void launch_matvec_forward(zkb_ctx* c, const u32* W, const u32* x, size_t m, size_t n, u32* y) {
+    const size_t want_warps = (size_t)c->sm_count * 32;
+    int wpr = 1;
+    while (wpr < 8 && m * wpr < want_warps && n / (4 * (size_t)wpr * 2) >= 128) wpr *= 2;
+    const size_t rows_per_cta = 8 / wpr;
+    size_t ctas = (m + rows_per_cta - 1) / rows_per_cta;
+    const size_t cap = (size_t)c->sm_count * 8;
+    int grid = (int)(ctas < cap ? ctas : cap);
+    if (grid < 1) grid = 1;
+    switch (wpr) {
+        case 1: matvec_forward_kernel<1><<<grid, 256, 0, c->stream>>>(W, x, m, n, y); break;
+        case 2: matvec_forward_kernel<2><<<grid, 256, 0, c->stream>>>(W, x, m, n, y); break;
+        case 4: matvec_forward_kernel<4><<<grid, 256, 0, c->stream>>>(W, x, m, n, y); break;
+        default: matvec_forward_kernel<8><<<grid, 256, 0, c->stream>>>(W, x, m, n, y); break;
+    }
+}
 inline void matvec_forward(zkb_ctx* c, const u32* W, const u32* x, u32 m, u32 n, u32* y, u32 m_pad) {
     if (m_pad > m) ZKB_CUDA(cudaMemsetAsync(y + m, 0, (size_t)(m_pad - m) * 4, c->stream));
-    size_t warps = m;
-    int grid = grid_for(c, warps * 32, 256, 8);
     int rg = c->range_begin(ZKB_RANGE_MATVEC_FORWARD, 4.0 * m * n);
-    matvec_forward_kernel<<<grid, 256, 0, c->stream>>>(W, x, m, n, y);
+    launch_matvec_forward(c, W, x, m, n, y);
     c->range_end(rg);
     ZKB_LAUNCHED(c);
 }

@@ -381,13 +381,9 @@ extern "C" int32_t zkb_fold_eq_matvec_ef_noalloc(const uint32_t* W_dev, size_t m
     // the array keeps whatever the previous call left: the accumulators must start at zero
     e = cudaMemsetAsync(D.acc, 0, n_pad * 4 * sizeof(unsigned long long), s);
     if (e != cudaSuccess) { set_err(err, err_cap, std::string("cudaMemsetAsync: ") + cudaGetErrorString(e)); return ZKB_E_CUDA; }
-    const u32 col_ctas = (u32)((n + 511) / 512);
-    u32 want_rows = (u32)((D.sm_count * 6 + col_ctas - 1) / col_ctas);
-    if (want_rows < 1) want_rows = 1;
-    size_t rows_per = (m + want_rows - 1) / want_rows;
-    rows_per = (rows_per + FOLD_ROWS_TILE - 1) / FOLD_ROWS_TILE * FOLD_ROWS_TILE;
-    dim3 grid(col_ctas, (u32)((m + rows_per - 1) / rows_per));
-    fold_eq_matvec_kernel<4><<<grid, 128, 0, s>>>(W_dev, m, n, eq_dev, rows_per, D.acc);
+    size_t rows_per = 0;
+    dim3 grid = fold_launch_dims(D.sm_count, m, n, &rows_per);
+    fold_eq_matvec_kernel<4><<<grid, FOLD_THREADS, 0, s>>>(W_dev, m, n, eq_dev, rows_per, D.acc);
     size_t fin_items = n_pad * 4;
     int fin_grid = (int)((fin_items + 255) / 256);
     if (fin_grid > D.sm_count * 8) fin_grid = D.sm_count * 8;

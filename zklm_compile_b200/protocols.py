@@ -123,6 +123,51 @@ def prove_matmul_succinct_ef(w_flat, x_vals, y_vals, m: int, n: int, transcript:
                        C.c_int32(on), C.c_int32(bind_mode), C.c_int32(node_hash))
 
 
+def prove_matmul_succinct(w_flat, x_vals, y_vals, m: int, n: int, transcript: Transcript) -> bytes:
+    """matmul.rs:482-511 (base-field challenges) -> SuccinctMatmulProof."""
+    ctx = transcript.ctx
+    x, px = _a(x_vals)
+    y, py = _a(y_vals)
+    if isinstance(w_flat, DeviceBuffer):
+        pw, on = w_flat.ptr, 1
+    else:
+        w, pw = _a(w_flat)
+        on = 0
+    return _proof_call(ctx, _lib.lib().zkb_prove_matmul_succinct, ctx.h, transcript.h, pw, px, py, C.c_size_t(m), C.c_size_t(n),
+                       C.c_int32(on))
+
+
+def prove_mle_eval_bound(weights, point, label: bytes, root: bytes, transcript: Transcript) -> bytes:
+    """weight_commitment.rs:437-447 (label = b"" gives prove_mle_eval_no_merkle, :177-206) -> MleEvalProof."""
+    ctx = transcript.ctx
+    w, pw = _a(weights)
+    pt, pp = _a(point)
+    lab = (C.c_uint8 * max(1, len(label))).from_buffer_copy(label or b"\0")
+    rt = (C.c_uint8 * 32).from_buffer_copy(root or bytes(32))
+    return _proof_call(ctx, _lib.lib().zkb_prove_mle_eval, ctx.h, transcript.h, pw, C.c_size_t(w.size), pp, C.c_uint32(pt.size),
+                       lab, C.c_size_t(len(label)), rt)
+
+
+def _elementwise_base(is_add, a, b, c, point, transcript):
+    ctx = transcript.ctx
+    av, pa = _a(a)
+    bv, pb = _a(b)
+    cv, pc = _a(c)
+    pt, pp = _a(point)
+    return _proof_call(ctx, _lib.lib().zkb_prove_elementwise, ctx.h, transcript.h, C.c_int32(is_add), pa, pb, pc, C.c_size_t(av.size),
+                       pp, C.c_uint32(pt.size))
+
+
+def prove_hadamard(a, b, c, point, transcript: Transcript) -> bytes:
+    """elementwise.rs:50-98 (base-field challenges) -> HadamardProof."""
+    return _elementwise_base(0, a, b, c, point, transcript)
+
+
+def prove_add(a, b, c, point, transcript: Transcript) -> bytes:
+    """elementwise.rs:189-235 (base-field challenges) -> AddProof."""
+    return _elementwise_base(1, a, b, c, point, transcript)
+
+
 def _elementwise(is_add, a, b, c, point, transcript):
     ctx = transcript.ctx
     av, pa = _a(a)
@@ -161,6 +206,15 @@ def prove_lookup_ef(table_outputs, inputs, outputs, transcript: Transcript) -> b
     i, pi = _a(inputs)
     o, po = _a(outputs)
     return _proof_call(ctx, _lib.lib().zkb_prove_lookup_ef, ctx.h, transcript.h, pt, C.c_size_t(t.size), pi, po, C.c_size_t(i.size))
+
+
+def prove_lookup(table_outputs, inputs, outputs, transcript: Transcript) -> bytes:
+    """lookup.rs:432-604 (base-field challenges) -> LookupProof; same error statuses as prove_lookup_ef."""
+    ctx = transcript.ctx
+    t, pt = _a(table_outputs)
+    i, pi = _a(inputs)
+    o, po = _a(outputs)
+    return _proof_call(ctx, _lib.lib().zkb_prove_lookup, ctx.h, transcript.h, pt, C.c_size_t(t.size), pi, po, C.c_size_t(i.size))
 
 
 def fold_eq_matvec_ef_noalloc(w_dev: DeviceBuffer, m: int, n: int, eq_dev: DeviceBuffer, out_dev: DeviceBuffer, stream=None):
