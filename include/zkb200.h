@@ -166,6 +166,9 @@ int32_t zkb_prove_rmsnorm_ef(zkb_ctx* ctx, zkb_transcript* tr, const uint32_t* x
 int32_t zkb_prove_lookup_ef(zkb_ctx* ctx, zkb_transcript* tr, const uint32_t* table_out, size_t n_table, const uint32_t* inputs,
                             const uint32_t* outputs, size_t n, uint8_t* out, size_t cap, size_t* len);
 
+/* prove_rmsnorm (base-field challenges) -> RmsNormProof                                        rmsnorm.rs:96-246 */
+int32_t zkb_prove_rmsnorm(zkb_ctx* ctx, zkb_transcript* tr, const uint32_t* x, const uint32_t* gamma, const uint32_t* y, size_t d,
+                          int32_t delta, uint8_t* out, size_t cap, size_t* len);
 /* prove_lookup (base-field challenges) -> LookupProof                                          lookup.rs:432-604 */
 int32_t zkb_prove_lookup(zkb_ctx* ctx, zkb_transcript* tr, const uint32_t* table_out, size_t n_table, const uint32_t* inputs,
                          const uint32_t* outputs, size_t n, uint8_t* out, size_t cap, size_t* len);

@@ -151,6 +151,17 @@ def test_rmsnorm_forward_and_proof_bytes(ctx, d):
     assert t.squeeze() == o.squeeze()
 
 
+@pytest.mark.parametrize("d", [4, 12, 100, 768, 2560])
+def test_rmsnorm_base_proof_bytes(ctx, d):
+    rng = np.random.default_rng(d + 11)
+    x = np.mod(rng.integers(-127, 128, d), P).astype(np.uint32)
+    gamma = np.mod(rng.integers(-127, 128, d), P).astype(np.uint32)
+    y, xu, delta = O.rmsnorm_forward(x, gamma)
+    t, o = zk.Transcript(ctx, b"rnb"), O.Transcript(b"rnb")
+    assert zp.prove_rmsnorm(xu, gamma, y, delta, t) == O.prove_rmsnorm(o, xu, gamma, y, delta)
+    assert t.squeeze() == o.squeeze()
+
+
 def test_rmsnorm_forward_needs_perturbation(ctx):
     """Find seeded inputs whose d / sum_sq is not a residue, so the +-delta search runs."""
     found = 0

@@ -78,17 +78,16 @@ int32_t zkb_fold_eq_matvec(zkb_ctx* c, const uint32_t* W, size_t m, size_t n, co
         if (ef) eq_evals_kernel<Fe><<<grid_for(c, m_pad), 256, 0, c->stream>>>((const Fe*)dr, log_m, (Fe*)eq);
         else eq_evals_kernel<Fp><<<grid_for(c, m_pad), 256, 0, c->stream>>>((const Fp*)dr, log_m, (Fp*)eq);
         ZKB_LAUNCHED(c);
-        unsigned long long* acc = (unsigned long long*)c->scratch(n_pad * w * 8);
-        ZKB_CUDA(cudaMemsetAsync(acc, 0, n_pad * w * 8, c->stream));
         u32* res = (u32*)c->scratch(n_pad * w * 4);
         size_t rows_per = 0;
         dim3 grid = fold_launch_dims(c->sm_count, m, n, &rows_per);
+        u32* slabs = (u32*)c->scratch((size_t)grid.y * n * w * 4 + 16);
         if (ef) {
-            fold_eq_matvec_kernel<4><<<grid, FOLD_THREADS, 0, c->stream>>>(dW, m, n, eq, rows_per, acc);
-            fold_finalize_kernel<4><<<grid_for(c, n_pad * 4), 256, 0, c->stream>>>(acc, n, n_pad, res);
+            fold_eq_matvec_kernel<4, false><<<grid, FOLD_THREADS, 0, c->stream>>>(dW, m, n, eq, rows_per, nullptr, slabs);
+            fold_finalize_partials_kernel<4><<<grid_for(c, n_pad * 4), 256, 0, c->stream>>>(slabs, grid.y, n, n_pad, res);
         } else {
-            fold_eq_matvec_kernel<1><<<grid, FOLD_THREADS, 0, c->stream>>>(dW, m, n, eq, rows_per, acc);
-            fold_finalize_kernel<1><<<grid_for(c, n_pad), 256, 0, c->stream>>>(acc, n, n_pad, res);
+            fold_eq_matvec_kernel<1, false><<<grid, FOLD_THREADS, 0, c->stream>>>(dW, m, n, eq, rows_per, nullptr, slabs);
+            fold_finalize_partials_kernel<1><<<grid_for(c, n_pad), 256, 0, c->stream>>>(slabs, grid.y, n, n_pad, res);
         }
         c->launches += 2;
         ZKB_CUDA(cudaGetLastError());
@@ -266,6 +265,26 @@ int32_t zkb_prove_rmsnorm_ef(zkb_ctx* c, zkb_transcript* t, const uint32_t* x, c
         c->rec_fetch();
         Ser s; s.rec = c->rec_host;
         put_rmsnorm(s, R, false);
+        c->scratch_reset();
+        int32_t rc = emit(c, s.b, out, cap, len);
+        if (rc) return rc;
+    });
+}
+
+int32_t zkb_prove_rmsnorm(zkb_ctx* c, zkb_transcript* t, const uint32_t* x, const uint32_t* gamma, const uint32_t* y, size_t d, int32_t delta,
+                          uint8_t* out, size_t cap, size_t* len) {
+    if (!c || !t || !x || !gamma || !y || d == 0) return ZKB_E_ARG;
+    ZKB_TRY(c, {
+        c->use();
+        c->rec_reset();
+        const size_t n_pad = size_t(1) << log2_ceil_u(d);
+        u32* dx = up_pad(c, x, d, n_pad); u32* dg = up_pad(c, gamma, d, n_pad); u32* dy = up_pad(c, y, d, n_pad);
+        uint32_t sc_h[2] = {(uint32_t)delta, 0};
+        u32* sc = up_pad(c, sc_h, 2, 4);
+        RmsNormRec R = prove_rmsnorm_base(c, t->dev, dx, dg, dy, (u32)d, sc);
+        c->rec_fetch();
+        Ser s; s.rec = c->rec_host;
+        put_rmsnorm_base(s, R);
         c->scratch_reset();
         int32_t rc = emit(c, s.b, out, cap, len);
         if (rc) return rc;

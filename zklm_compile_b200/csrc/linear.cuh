@@ -42,29 +42,35 @@ __global__ void eq_evals_kernel(const T* __restrict__ r, u32 k, T* out) {
 }
 
 // ---- fold_eq_matvec: acc[j] += eq[i] * W[i][j] -----------------------------------------------
-// grid.x tiles columns (128 * 4 per CTA), grid.y tiles rows.  A CTA is 4 row groups x 128 column
-// threads: group g takes rows g, g+4, ... of the CTA's row range, six rows per step so that six
-// 16-byte loads per thread are in flight (the kernel is bound by memory latency otherwise), the
-// four groups' column sums are added in shared memory and one group adds them to the 64-bit
-// accumulators with atomicAdd.  Integer addition is associative, so the result does not depend
-// on the order.  NC = 1 (base eq) or 4 (EF eq).
-constexpr int FOLD_ROWS_TILE = 24;       // granularity of the per-CTA row range (= FOLD_GROUPS * FOLD_UNROLL)
-constexpr int FOLD_GROUPS = 4;
-constexpr int FOLD_UNROLL = 6;
+// grid.x tiles columns (128 * 4 per CTA), grid.y tiles rows.  A CTA is 2 row groups x 128 column
+// threads: group g takes rows g, g+2, ... of the CTA's row range, eight rows per step, so eight
+// 16-byte loads per thread are in flight.  Four products of canonical values fit one 64-bit
+// sum (4 (p-1)^2 < 2^64); each such sum is folded once (2^31 == 1) and added to a 64-bit
+// accumulator that is only reduced at the end.  The two groups' column sums meet in shared
+// memory and one group adds them to the global 64-bit accumulators with atomicAdd; integer
+// addition is associative, so the result does not depend on the order.  NC = 1 (base eq) or 4
+// (EF eq).
+constexpr int FOLD_GROUPS = 2;
+constexpr int FOLD_UNROLL = 8;
+constexpr int FOLD_ROWS_TILE = FOLD_GROUPS * FOLD_UNROLL;   // granularity of the per-CTA row range
 
 __device__ __forceinline__ u64 part_reduce(u64 a) { return (a & ZKB_P) + (a >> 31); }   // keeps a < 2^34
 
-template <int NC>
-__global__ void __launch_bounds__(128 * FOLD_GROUPS) fold_eq_matvec_kernel(const u32* __restrict__ W, size_t m, size_t n,
-                                                                          const u32* __restrict__ eq /* [m_pad][NC] */,
-                                                                          size_t rows_per_cta, unsigned long long* acc /* [n][NC] */) {
+// ATOMIC: column sums are added to 64-bit accumulators acc[n][NC] (zeroed by the caller).
+// Otherwise every row-CTA writes its own canonical sums to part[blockIdx.y][n * NC] (u32) and
+// fold_finalize_partials_kernel adds the slabs: no atomics (they serialise per address when a
+// hundred row-CTAs meet on one column) and nothing to clear.
+template <int NC, bool ATOMIC>
+__global__ void __launch_bounds__(128 * FOLD_GROUPS, 2) fold_eq_matvec_kernel(const u32* __restrict__ W, size_t m, size_t n,
+                                                                             const u32* __restrict__ eq /* [m_pad][NC] */,
+                                                                             size_t rows_per_cta, unsigned long long* acc, u32* part) {
     __shared__ u32 sums[FOLD_GROUPS - 1][128][4 * NC];
     const int tx = threadIdx.x & 127, g = threadIdx.x >> 7;
     const size_t j0 = ((size_t)blockIdx.x * 128 + tx) * 4;
     const size_t r0 = (size_t)blockIdx.y * rows_per_cta;
     const size_t r1 = r0 + rows_per_cta < m ? r0 + rows_per_cta : m;
     const bool vec = (n % 4 == 0) && (j0 + 4 <= n);
-    u64 a[4][NC];
+    u64 a[4][NC];                       // grows by less than 2^35 per step: no overflow for any m < 2^28
 #pragma unroll
     for (int c = 0; c < 4; c++)
 #pragma unroll
@@ -72,7 +78,6 @@ __global__ void __launch_bounds__(128 * FOLD_GROUPS) fold_eq_matvec_kernel(const
 
     if (j0 < n) {
         size_t row = r0 + g;
-        // six rows per step: 6 products (< 2^62 each) do not fit one 64-bit sum, so fold after three
         for (; row + (FOLD_UNROLL - 1) * FOLD_GROUPS < r1; row += FOLD_UNROLL * FOLD_GROUPS) {
             u32 w[FOLD_UNROLL][4];
 #pragma unroll
@@ -93,9 +98,9 @@ __global__ void __launch_bounds__(128 * FOLD_GROUPS) fold_eq_matvec_kernel(const
                 for (int q = 0; q < FOLD_UNROLL; q++) e[q] = __ldg(eq + (row + (size_t)q * FOLD_GROUPS) * NC + k);
 #pragma unroll
                 for (int c = 0; c < 4; c++) {
-                    u64 t0 = (u64)e[0] * w[0][c] + (u64)e[1] * w[1][c] + (u64)e[2] * w[2][c];
-                    u64 t1 = (u64)e[3] * w[3][c] + (u64)e[4] * w[4][c] + (u64)e[5] * w[5][c];
-                    a[c][k] = part_reduce(a[c][k] + part_reduce(t0) + part_reduce(t1));
+                    u64 t0 = (u64)e[0] * w[0][c] + (u64)e[1] * w[1][c] + (u64)e[2] * w[2][c] + (u64)e[3] * w[3][c];
+                    u64 t1 = (u64)e[4] * w[4][c] + (u64)e[5] * w[5][c] + (u64)e[6] * w[6][c] + (u64)e[7] * w[7][c];
+                    a[c][k] += part_reduce(t0) + part_reduce(t1);
                 }
             }
         }
@@ -108,7 +113,7 @@ __global__ void __launch_bounds__(128 * FOLD_GROUPS) fold_eq_matvec_kernel(const
             for (int k = 0; k < NC; k++) {
                 const u32 e = __ldg(eq + row * NC + k);
 #pragma unroll
-                for (int c = 0; c < 4; c++) a[c][k] = part_reduce(a[c][k] + (u64)e * w[c]);
+                for (int c = 0; c < 4; c++) a[c][k] += part_reduce((u64)e * w[c]);
             }
         }
     }
@@ -128,16 +133,18 @@ __global__ void __launch_bounds__(128 * FOLD_GROUPS) fold_eq_matvec_kernel(const
                     u64 v = red64(a[c][k]);
 #pragma unroll
                     for (int q = 0; q < FOLD_GROUPS - 1; q++) v += sums[q][tx][c * NC + k];
-                    atomicAdd(acc + (j0 + c) * NC + k, (unsigned long long)v);
+                    if (ATOMIC) atomicAdd(acc + (j0 + c) * NC + k, (unsigned long long)v);
+                    else part[(size_t)blockIdx.y * n * NC + (j0 + c) * NC + k] = red64(v);
                 }
             }
         }
     }
 }
-// Launch shape: 512 columns per CTA; rows split so that about two CTAs per SM exist.
+// Launch shape: 512 columns per CTA; rows split so that about four CTAs per SM exist.
 inline dim3 fold_launch_dims(int sm_count, size_t m, size_t n, size_t* rows_per_out) {
     const unsigned col_ctas = (unsigned)((n + 511) / 512);
-    unsigned want_rows = (unsigned)((sm_count * 2 + col_ctas - 1) / col_ctas);
+    unsigned want_rows = (unsigned)((sm_count * 4 + col_ctas - 1) / col_ctas);
+    if (want_rows > m / 32 + 1) want_rows = (unsigned)(m / 32 + 1);      // at least two steps per CTA
     if (want_rows < 1) want_rows = 1;
     size_t rows_per = (m + want_rows - 1) / want_rows;
     rows_per = (rows_per + FOLD_ROWS_TILE - 1) / FOLD_ROWS_TILE * FOLD_ROWS_TILE;
@@ -146,6 +153,16 @@ inline dim3 fold_launch_dims(int sm_count, size_t m, size_t n, size_t* rows_per_
 }
 constexpr int FOLD_THREADS = 128 * FOLD_GROUPS;
 
+// Sum of the row-CTAs' slabs -> canonical u32 (interleaved EF coordinates when NC = 4), zero beyond n.
+template <int NC>
+__global__ void fold_finalize_partials_kernel(const u32* __restrict__ part, u32 slabs, size_t n, size_t n_pad, u32* out) {
+    for (size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x; t < n_pad * NC; t += (size_t)gridDim.x * blockDim.x) {
+        u64 v = 0;
+        if (t < n * NC)
+            for (u32 r = 0; r < slabs; r++) v += part[(size_t)r * n * NC + t];
+        out[t] = red64(v);
+    }
+}
 // acc -> canonical u32 (interleaved EF coordinates when NC = 4), zero beyond n up to n_pad.
 template <int NC>
 __global__ void fold_finalize_kernel(unsigned long long* acc, size_t n, size_t n_pad, u32* out) {

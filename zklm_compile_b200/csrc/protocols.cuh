@@ -139,17 +139,16 @@ inline MatmulRec prove_matmul_succinct_ef(zkb_ctx* c, TrState* tr, const u32* W,
     Fe* eq_r = (Fe*)c->scratch(m_pad * 16);
     eq_evals_kernel<Fe><<<grid_for(c, m_pad), 256, 0, c->stream>>>((const Fe*)r_dev, R.log_m, eq_r);
     ZKB_LAUNCHED(c);
-    unsigned long long* acc = (unsigned long long*)c->scratch(n_pad * 4 * 8);
-    ZKB_CUDA(cudaMemsetAsync(acc, 0, n_pad * 4 * 8, c->stream));
     Fe* w_partial = (Fe*)c->scratch(n_pad * 16);
     {
         size_t rows_per = 0;
         dim3 grid = fold_launch_dims(c->sm_count, m, n, &rows_per);
         int rg = c->range_begin(ZKB_RANGE_FOLD_EQ_MATVEC, 4.0 * m * n);
-        fold_eq_matvec_kernel<4><<<grid, FOLD_THREADS, 0, c->stream>>>(W, m, n, (const u32*)eq_r, rows_per, acc);
+        u32* slabs = (u32*)c->scratch((size_t)grid.y * n * 4 * 4 + 16);
+        fold_eq_matvec_kernel<4, false><<<grid, FOLD_THREADS, 0, c->stream>>>(W, m, n, (const u32*)eq_r, rows_per, nullptr, slabs);
         c->range_end(rg);
         ZKB_LAUNCHED(c);
-        fold_finalize_kernel<4><<<grid_for(c, n_pad * 4), 256, 0, c->stream>>>(acc, n, n_pad, (u32*)w_partial);
+        fold_finalize_partials_kernel<4><<<grid_for(c, n_pad * 4), 256, 0, c->stream>>>(slabs, grid.y, n, n_pad, (u32*)w_partial);
         ZKB_LAUNCHED(c);
     }
     // product sumcheck, full messages                                     (matmul.rs:889-944)
@@ -252,17 +251,16 @@ inline MatmulRec prove_matmul_succinct_base(zkb_ctx* c, TrState* tr, const u32* 
     Fp* eq_r = (Fp*)c->scratch(m_pad * 4 + 16);
     eq_evals_kernel<Fp><<<grid_for(c, m_pad), 256, 0, c->stream>>>((const Fp*)r_dev, R.log_m, eq_r);
     ZKB_LAUNCHED(c);
-    unsigned long long* acc = (unsigned long long*)c->scratch(n_pad * 8);
-    ZKB_CUDA(cudaMemsetAsync(acc, 0, n_pad * 8, c->stream));
     u32* w_partial = (u32*)c->scratch(n_pad * 4 + 16);
     {
         size_t rows_per = 0;
         dim3 grid = fold_launch_dims(c->sm_count, m, n, &rows_per);
         int rg = c->range_begin(ZKB_RANGE_FOLD_EQ_MATVEC, 4.0 * m * n);
-        fold_eq_matvec_kernel<1><<<grid, FOLD_THREADS, 0, c->stream>>>(W, m, n, (const u32*)eq_r, rows_per, acc);
+        u32* slabs = (u32*)c->scratch((size_t)grid.y * n * 4 + 16);
+        fold_eq_matvec_kernel<1, false><<<grid, FOLD_THREADS, 0, c->stream>>>(W, m, n, (const u32*)eq_r, rows_per, nullptr, slabs);
         c->range_end(rg);
         ZKB_LAUNCHED(c);
-        fold_finalize_kernel<1><<<grid_for(c, n_pad), 256, 0, c->stream>>>(acc, n, n_pad, w_partial);
+        fold_finalize_partials_kernel<1><<<grid_for(c, n_pad), 256, 0, c->stream>>>(slabs, grid.y, n, n_pad, w_partial);
         ZKB_LAUNCHED(c);
     }
     const u32* tabs[3] = {w_partial, x, nullptr};

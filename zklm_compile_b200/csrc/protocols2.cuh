@@ -115,6 +115,85 @@ inline void put_rmsnorm(Ser& s, const RmsNormRec& R, bool stripped) {
     for (int i = 0; i < 6; i++) { put_eval(s, *ev[i], ch); s.claimed_sum_ef(ev[i]->sc); }
 }
 
+// Base-field twin (rmsnorm.rs:96-246): same sequence with challenges in M31; the tables stay
+// base-field vectors, so nothing is widened.
+inline RmsNormRec prove_rmsnorm_base(zkb_ctx* c, TrState* tr, const u32* x, const u32* gamma, const u32* y, u32 d, const u32* fwd_scalars) {
+    RmsNormRec R;
+    R.k = log2_ceil_u(d);
+    const u32 k = R.k;
+    const size_t n = size_t(1) << k;
+    u32* g = (u32*)c->scratch(n * 4);
+    u32* gamma_pad = (u32*)c->scratch(n * 4);
+    R.scalars = c->rec_alloc(2);
+    R.roots = c->rec_alloc(32);
+    u32* sc_dev = c->rec_dev + R.scalars;
+    pad_copy_kernel<<<grid_for(c, n), 256, 0, c->stream>>>(gamma, d, n, gamma_pad);
+    ZKB_LAUNCHED(c);
+    rmsnorm_prep_kernel<<<1, 1024, 0, c->stream>>>(x, gamma, d, (u32)n, g, sc_dev + 1);
+    ZKB_LAUNCHED(c);
+    ZKB_CUDA(cudaMemcpyAsync(sc_dev, fwd_scalars, 4, cudaMemcpyDeviceToDevice, c->stream));
+    B3Multi bm{};
+    const u32* vecs[4] = {x, gamma_pad, g, y};
+    for (int i = 0; i < 4; i++) {
+        bm.words[i] = vecs[i]; bm.n_words[i] = (u32)n; bm.root[i] = c->rec_dev + R.roots + 8 * i;
+        bm.cvs[i] = (u32*)c->scratch((n * 4 + 7 + 1023) / 1024 * 32 + 64);
+    }
+    b3_commit_multi_kernel<<<4, 256, 0, c->stream>>>(b3_prefix("weights", 7), bm);
+    ZKB_LAUNCHED(c);
+    {
+        ScriptBuilder sb;
+        sb.str("rmsnorm-pert-v1");
+        sb.words_dev(sc_dev, 1);
+        sb.words_dev(c->rec_dev + R.roots, 32);
+        sb.words_dev(sc_dev + 1, 1);
+        sb.run(c, tr);
+    }
+    const u32* root_x = c->rec_dev + R.roots, *root_gamma = root_x + 8, *root_g = root_x + 16, *root_h = root_x + 24;
+    const u32* tv[3] = {x, x, nullptr};
+    R.var = sumcheck_enqueue(c, tr, ZKB_SC_PRODUCT, tv, k);
+    R.x_var = prove_mle_eval_base(c, tr, x, c->rec_dev + R.var.chal, k, "rmsnorm-x-var", root_x);
+    R.gc_point = c->rec_alloc(k);
+    { ScriptBuilder sb; sb.squeeze(c->rec_dev + R.gc_point, k); sb.run(c, tr); }
+    Fp* eq = (Fp*)c->scratch(n * 4 + 16);
+    eq_evals_kernel<Fp><<<grid_for(c, n), 256, 0, c->stream>>>((const Fp*)(c->rec_dev + R.gc_point), k, eq);
+    ZKB_LAUNCHED(c);
+    const u32* tgp[3] = {(const u32*)eq, g, nullptr};
+    R.g_prod = sumcheck_enqueue(c, tr, ZKB_SC_PRODUCT, tgp, k);
+    R.g_prod_eval = prove_mle_eval_base(c, tr, g, c->rec_dev + R.g_prod.chal, k, "rmsnorm-g-prod", root_g);
+    const u32* tgt[3] = {(const u32*)eq, gamma_pad, x};
+    R.g_triple = sumcheck_enqueue(c, tr, ZKB_SC_TRIPLE, tgt, k);
+    const u32* s_gt = c->rec_dev + R.g_triple.chal;
+    R.x_triple = prove_mle_eval_base(c, tr, x, s_gt, k, "rmsnorm-x-triple", root_x);
+    R.gamma_triple = prove_mle_eval_base(c, tr, gamma_pad, s_gt, k, "rmsnorm-gamma-triple", root_gamma);
+    R.sq_point = c->rec_alloc(k);
+    { ScriptBuilder sb; sb.squeeze(c->rec_dev + R.sq_point, k); sb.run(c, tr); }
+    Fp* eq2 = (Fp*)c->scratch(n * 4 + 16);
+    eq_evals_kernel<Fp><<<grid_for(c, n), 256, 0, c->stream>>>((const Fp*)(c->rec_dev + R.sq_point), k, eq2);
+    ZKB_LAUNCHED(c);
+    const u32* ths[3] = {(const u32*)eq2, y, y};
+    R.h_sq = sumcheck_enqueue(c, tr, ZKB_SC_TRIPLE, ths, k);
+    R.h_sq_eval = prove_mle_eval_base(c, tr, y, c->rec_dev + R.h_sq.chal, k, "rmsnorm-h-sq", root_h);
+    const u32* tgs[3] = {(const u32*)eq2, g, g};
+    R.g_sq = sumcheck_enqueue(c, tr, ZKB_SC_TRIPLE, tgs, k);
+    R.g_sq_eval = prove_mle_eval_base(c, tr, g, c->rec_dev + R.g_sq.chal, k, "rmsnorm-g-sq", root_g);
+    return R;
+}
+// RmsNormProof in serde field order (rmsnorm.rs:36-85)
+inline void put_rmsnorm_base(Ser& s, const RmsNormRec& R) {
+    const u64 n = u64(1) << R.k;
+    s.u32le(s.rec[R.scalars]);
+    s.sumcheck(R.var, true); s.words(R.var.fin, 2);
+    s.u32le(s.rec[R.scalars + 1]);
+    s.sumcheck(R.h_sq, true); s.words(R.h_sq.fin, 3); put_claimed_sum_base(s, R.h_sq);
+    s.sumcheck(R.g_sq, true); s.words(R.g_sq.fin, 3); put_claimed_sum_base(s, R.g_sq);
+    s.sumcheck(R.g_prod, true); s.words(R.g_prod.fin, 2);
+    s.sumcheck(R.g_triple, true); s.words(R.g_triple.fin, 3);
+    put_claimed_sum_base(s, R.g_prod);                           // t_g_claimed
+    for (int i = 0; i < 4; i++) s.commitment(R.roots + 8 * i, n);
+    const EvalRec* ev[6] = {&R.x_var, &R.g_prod_eval, &R.x_triple, &R.gamma_triple, &R.h_sq_eval, &R.g_sq_eval};
+    for (int i = 0; i < 6; i++) { put_eval_base(s, *ev[i]); put_claimed_sum_base(s, ev[i]->sc); }
+}
+
 // ---- LogUp (lookup.rs:643-762) -------------------------------------------------------------------
 struct LookupRec {
     u32 n = 0, max_nv = 0;

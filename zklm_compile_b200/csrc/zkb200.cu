@@ -383,7 +383,7 @@ extern "C" int32_t zkb_fold_eq_matvec_ef_noalloc(const uint32_t* W_dev, size_t m
     if (e != cudaSuccess) { set_err(err, err_cap, std::string("cudaMemsetAsync: ") + cudaGetErrorString(e)); return ZKB_E_CUDA; }
     size_t rows_per = 0;
     dim3 grid = fold_launch_dims(D.sm_count, m, n, &rows_per);
-    fold_eq_matvec_kernel<4><<<grid, FOLD_THREADS, 0, s>>>(W_dev, m, n, eq_dev, rows_per, D.acc);
+    fold_eq_matvec_kernel<4, true><<<grid, FOLD_THREADS, 0, s>>>(W_dev, m, n, eq_dev, rows_per, D.acc, nullptr);
     size_t fin_items = n_pad * 4;
     int fin_grid = (int)((fin_items + 255) / 256);
     if (fin_grid > D.sm_count * 8) fin_grid = D.sm_count * 8;

@@ -198,6 +198,16 @@ def prove_rmsnorm_ef(x, gamma, y, perturbation_delta: int, transcript: Transcrip
                        C.c_int32(perturbation_delta))
 
 
+def prove_rmsnorm(x, gamma, y, perturbation_delta: int, transcript: Transcript) -> bytes:
+    """rmsnorm.rs:96-246 (base-field challenges) -> RmsNormProof."""
+    ctx = transcript.ctx
+    xv, px = _a(x)
+    g, pg = _a(gamma)
+    yv, py = _a(y)
+    return _proof_call(ctx, _lib.lib().zkb_prove_rmsnorm, ctx.h, transcript.h, px, pg, py, C.c_size_t(xv.size),
+                       C.c_int32(perturbation_delta))
+
+
 def prove_lookup_ef(table_outputs, inputs, outputs, transcript: Transcript) -> bytes:
     """lookup.rs:643-762 -> LookupProofEF.  Raises ZkbError with the reference's panic messages
     (status 3: LogUp identity failed, status 4: alpha collision)."""
