@@ -216,7 +216,10 @@ def run_sumcheck(zk, ctx, n, steps, warmup, rank, with_e2e, barrier=lambda: None
     res = {"n": n, "value_gbps": round(world * total_bytes / (ms_step * 1e-3) / 1e9, 2), "ms_per_step": round(ms_step, 4),
            "gpu_launches": int(launches), "algorithmic_bytes_per_step": total_bytes,
            "roofline": {"bound": "hbm", "achieved": round(dom[0], 1), "peak": peak, "unit": "GB/s", "frac": round(dom[0] / peak, 4),
-                        "traffic": None, "peak_source": src,
+                        "traffic": int(1.04 * per_launch_bytes[dom[2] - 1]) if dom[2] == 1 else int(0.95 * per_launch_bytes[dom[2] - 1]) if dom[2] else None,
+                        "traffic_source": "algorithmic bytes x the dram/algorithmic ratio ncu measured on this kernel at n = 25 "
+                                          "(1.04 for the round-1 launch, 0.95 for EF rounds; profiles/sumcheck_kernels_product_ef_n25.md)",
+                        "peak_source": src,
                         "kernel": f"sc_round_kernel fold launch {dom[2]} (folds round {dom[2] - 1}): "
                                   f"{per_launch_bytes[dom[2] - 1] if dom[2] else 0} algorithmic bytes in {dom[1]:.4f} ms",
                         "per_launch_gbps": [round(t[0], 1) for t in fold[:12]], "per_launch_ms": [round(t, 4) for t in prof[:14]]}}
@@ -441,7 +444,10 @@ def run_qwen(zk, args, rank, world, local, dist, barrier, max_over_ranks):
     def roof(name, label):
         ms, by, cnt = ranges[name]
         ach = by / (ms * 1e-3) / 1e9 if ms > 0 else 0.0
-        return {"bound": "hbm", "achieved": round(ach, 1), "peak": peak, "unit": "GB/s", "frac": round(ach / peak, 4), "traffic": None,
+        # DRAM bytes per launch from the ncu capture of these kernels on one layer: read + write = 1.00 x the
+        # algorithmic bytes for both (W is read once; see profiles/fold_eq_matvec_and_matvec_forward_qwen4b_layer.md)
+        return {"bound": "hbm", "achieved": round(ach, 1), "peak": peak, "unit": "GB/s", "frac": round(ach / peak, 4),
+                "traffic": round(by / cnt) if cnt else None, "traffic_source": "ncu dram__bytes_read+write / algorithmic = 1.00 on the same kernel",
                 "peak_source": src, "kernel": label, "launches": int(cnt), "avg_ms_per_launch": round(ms / cnt, 5) if cnt else None,
                 "algorithmic_bytes_per_launch_avg": round(by / cnt) if cnt else None}
 

@@ -199,6 +199,10 @@ const uint32_t* zkb_qwen_layer_output_dev(const zkb_qwen_layer* layer);
  * from the second proof on it is replayed from a CUDA graph captured on the layer's stream
  * (one graph launch instead of about two thousand kernel launches).  on = 0 switches that off. */
 int32_t zkb_qwen_layer_use_graph(zkb_qwen_layer* layer, int32_t on);
+/* What the next prove_begin will do: 0 = enqueue launch by launch, 1 = capture (once, slower),
+ * 2 = replay.  A host that drives many layers from several threads can use this to let the
+ * one-off captures happen one at a time. */
+int32_t zkb_qwen_layer_graph_state(const zkb_qwen_layer* layer);
 /* Selects what the reference fixes at compile time for the layer's eight matmul proofs: the
  * weight binding (ZKB_BIND_*, features pcs / pcs-full, matmul.rs:360-453) and the Merkle node
  * hash (ZKB_NODE_*, pcs.rs:87-135).  Default after create: ZKB_BIND_BLAKE3. */

@@ -93,6 +93,14 @@ int32_t zkb_qwen_layer_use_graph(zkb_qwen_layer* L, int32_t on) {
     L->use_graph = on != 0;
     return ZKB_OK;
 }
+// What the next zkb_qwen_layer_prove_begin will do: 0 = enqueue launch by launch, 1 = capture the
+// launch sequence into a graph (slower once; callers that drive several layers from several
+// threads may prefer to let captures happen one at a time), 2 = replay the captured graph.
+int32_t zkb_qwen_layer_graph_state(const zkb_qwen_layer* L) {
+    if (!L || !L->use_graph || L->ctx->profile) return 0;
+    if (L->graph_exec && L->graph_epoch == L->ctx->arena_epoch && L->graph_bind == L->bind_mode && L->graph_hash == L->node_hash) return 2;
+    return L->proofs_enqueued >= 1 ? 1 : 0;
+}
 // Weight binding used by the layer's eight matmul proofs from now on.
 int32_t zkb_qwen_layer_set_binding(zkb_qwen_layer* L, int32_t bind_mode, int32_t node_hash) {
     if (!L || bind_mode < BIND_BLAKE3 || bind_mode > BIND_PCS_FULL || (node_hash != NODE_BLAKE3 && node_hash != NODE_AES_MMO)) return ZKB_E_ARG;

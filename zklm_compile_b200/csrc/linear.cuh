@@ -158,8 +158,10 @@ template <int NC>
 __global__ void fold_finalize_partials_kernel(const u32* __restrict__ part, u32 slabs, size_t n, size_t n_pad, u32* out) {
     for (size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x; t < n_pad * NC; t += (size_t)gridDim.x * blockDim.x) {
         u64 v = 0;
-        if (t < n * NC)
+        if (t < n * NC) {
+#pragma unroll 8
             for (u32 r = 0; r < slabs; r++) v += part[(size_t)r * n * NC + t];
+        }
         out[t] = red64(v);
     }
 }
@@ -177,58 +179,76 @@ __global__ void fold_finalize_kernel(unsigned long long* acc, size_t n, size_t n
 // WPR warps share a row (each a contiguous quarter / half / ... of it), so that short matrices
 // still put enough warps on every SM; every lane keeps four 16-byte loads in flight.  x is read
 // through the read-only cache (it is small and reused by every row).  CTA = 8 warps = 8 / WPR rows.
+// Up to four matrices that share the input vector and the column count are handled by one launch
+// (the q / k / v / gate projections of a layer, or gate / up of its MLP): row i of the launch is
+// row i - first[t] of matrix t.
+struct MatvecBatch {
+    const u32* W[4];
+    u32* y[4];
+    u32 first[5];        // first[t] = rows before matrix t; first[count] = total rows
+    u32 count;
+};
+
 template <int WPR>
-__global__ void __launch_bounds__(256) matvec_forward_kernel(const u32* __restrict__ W, const u32* __restrict__ x,
-                                                             size_t m, size_t n, u32* y) {
+__device__ __forceinline__ u64 matvec_row_part(const u32* __restrict__ row, const u32* __restrict__ x, size_t n, int sub, int lane) {
+    u64 acc = 0;
+    if (n % 4 == 0) {
+        // this warp's span of 16-byte groups
+        const size_t groups = n / 4, per = (groups + WPR - 1) / WPR;
+        const size_t g0 = (size_t)sub * per, g1 = g0 + per < groups ? g0 + per : groups;
+        const uint4* rw = reinterpret_cast<const uint4*>(row);
+        const uint4* xv = reinterpret_cast<const uint4*>(x);
+        size_t gidx = g0 + lane;
+        for (; gidx + 96 < g1; gidx += 128) {
+            uint4 w0 = rw[gidx], w1 = rw[gidx + 32], w2 = rw[gidx + 64], w3 = rw[gidx + 96];
+            uint4 v0 = __ldg(xv + gidx), v1 = __ldg(xv + gidx + 32), v2 = __ldg(xv + gidx + 64), v3 = __ldg(xv + gidx + 96);
+            acc += part_reduce((u64)w0.x * v0.x + (u64)w0.y * v0.y) + part_reduce((u64)w0.z * v0.z + (u64)w0.w * v0.w);
+            acc += part_reduce((u64)w1.x * v1.x + (u64)w1.y * v1.y) + part_reduce((u64)w1.z * v1.z + (u64)w1.w * v1.w);
+            acc += part_reduce((u64)w2.x * v2.x + (u64)w2.y * v2.y) + part_reduce((u64)w2.z * v2.z + (u64)w2.w * v2.w);
+            acc += part_reduce((u64)w3.x * v3.x + (u64)w3.y * v3.y) + part_reduce((u64)w3.z * v3.z + (u64)w3.w * v3.w);
+            acc = part_reduce(acc);             // 8 terms below 2^33 each: stays far below 2^64
+        }
+        for (; gidx < g1; gidx += 32) {
+            uint4 w0 = rw[gidx];
+            uint4 v0 = __ldg(xv + gidx);
+            acc = part_reduce(acc + part_reduce((u64)w0.x * v0.x + (u64)w0.y * v0.y) + part_reduce((u64)w0.z * v0.z + (u64)w0.w * v0.w));
+        }
+    } else {
+        const size_t per = (n + WPR - 1) / WPR;
+        const size_t c0 = (size_t)sub * per, c1 = c0 + per < n ? c0 + per : n;
+        for (size_t j = c0 + lane; j < c1; j += 32) acc = part_reduce(acc + part_reduce((u64)row[j] * __ldg(x + j)));
+    }
+    return acc;
+}
+
+template <int WPR>
+__global__ void __launch_bounds__(256) matvec_forward_kernel(MatvecBatch mb, const u32* __restrict__ x, size_t n) {
     __shared__ u32 part[8];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int sub = warp % WPR;                         // which part of the row
     constexpr int RPC = 8 / WPR;                        // rows per CTA
+    const size_t m = mb.first[mb.count];
     for (size_t i0 = (size_t)blockIdx.x * RPC; i0 < m; i0 += (size_t)gridDim.x * RPC) {
         const size_t i = i0 + warp / WPR;
         u64 acc = 0;
+        u32 t = 0;
         if (i < m) {
-            const u32* row = W + i * n;
-            if (n % 4 == 0) {
-                // this warp's span of 16-byte groups
-                const size_t groups = n / 4, per = (groups + WPR - 1) / WPR;
-                const size_t g0 = (size_t)sub * per, g1 = g0 + per < groups ? g0 + per : groups;
-                const uint4* rw = reinterpret_cast<const uint4*>(row);
-                const uint4* xv = reinterpret_cast<const uint4*>(x);
-                size_t gidx = g0 + lane;
-                for (; gidx + 96 < g1; gidx += 128) {
-                    uint4 w0 = rw[gidx], w1 = rw[gidx + 32], w2 = rw[gidx + 64], w3 = rw[gidx + 96];
-                    uint4 v0 = __ldg(xv + gidx), v1 = __ldg(xv + gidx + 32), v2 = __ldg(xv + gidx + 64), v3 = __ldg(xv + gidx + 96);
-                    acc += part_reduce((u64)w0.x * v0.x + (u64)w0.y * v0.y) + part_reduce((u64)w0.z * v0.z + (u64)w0.w * v0.w);
-                    acc += part_reduce((u64)w1.x * v1.x + (u64)w1.y * v1.y) + part_reduce((u64)w1.z * v1.z + (u64)w1.w * v1.w);
-                    acc += part_reduce((u64)w2.x * v2.x + (u64)w2.y * v2.y) + part_reduce((u64)w2.z * v2.z + (u64)w2.w * v2.w);
-                    acc += part_reduce((u64)w3.x * v3.x + (u64)w3.y * v3.y) + part_reduce((u64)w3.z * v3.z + (u64)w3.w * v3.w);
-                    acc = part_reduce(acc);             // 8 terms below 2^33 each: stays far below 2^64
-                }
-                for (; gidx < g1; gidx += 32) {
-                    uint4 w0 = rw[gidx];
-                    uint4 v0 = __ldg(xv + gidx);
-                    acc = part_reduce(acc + part_reduce((u64)w0.x * v0.x + (u64)w0.y * v0.y) + part_reduce((u64)w0.z * v0.z + (u64)w0.w * v0.w));
-                }
-            } else {
-                const size_t per = (n + WPR - 1) / WPR;
-                const size_t c0 = (size_t)sub * per, c1 = c0 + per < n ? c0 + per : n;
-                for (size_t j = c0 + lane; j < c1; j += 32) acc = part_reduce(acc + part_reduce((u64)row[j] * __ldg(x + j)));
-            }
+            while (t + 1 < mb.count && i >= mb.first[t + 1]) t++;
+            acc = matvec_row_part<WPR>(mb.W[t] + (i - mb.first[t]) * n, x, n, sub, lane);
         }
         u32 r = red64(acc);
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) r = add31(r, __shfl_down_sync(0xffffffffu, r, off));
         if (WPR == 1) {
-            if (lane == 0 && i < m) y[i] = r;
+            if (lane == 0 && i < m) mb.y[t][i - mb.first[t]] = r;
         } else {
             if (lane == 0) part[warp] = r;
             __syncthreads();
             if (lane == 0 && sub == 0 && i < m) {
-                u32 t = r;
+                u32 v = r;
 #pragma unroll
-                for (int q = 1; q < WPR; q++) t = add31(t, part[warp + q]);
-                y[i] = t;
+                for (int q = 1; q < WPR; q++) v = add31(v, part[warp + q]);
+                mb.y[t][i - mb.first[t]] = v;
             }
             __syncthreads();
         }

@@ -65,7 +65,8 @@ namespace zkb {
 inline size_t pad_pow2(size_t n) { return size_t(1) << log2_ceil_u(n); }
 
 // Warps per row: enough to give every SM about 32 warps even for short matrices.
-inline void launch_matvec_forward(zkb_ctx* c, const u32* W, const u32* x, size_t m, size_t n, u32* y) {
+inline void launch_matvec_forward(zkb_ctx* c, const MatvecBatch& mb, const u32* x, size_t n) {
+    const size_t m = mb.first[mb.count];
     const size_t want_warps = (size_t)c->sm_count * 32;
     int wpr = 1;
     while (wpr < 8 && m * wpr < want_warps && n / (4 * (size_t)wpr * 2) >= 128) wpr *= 2;
@@ -75,16 +76,31 @@ inline void launch_matvec_forward(zkb_ctx* c, const u32* W, const u32* x, size_t
     int grid = (int)(ctas < cap ? ctas : cap);
     if (grid < 1) grid = 1;
     switch (wpr) {
-        case 1: matvec_forward_kernel<1><<<grid, 256, 0, c->stream>>>(W, x, m, n, y); break;
-        case 2: matvec_forward_kernel<2><<<grid, 256, 0, c->stream>>>(W, x, m, n, y); break;
-        case 4: matvec_forward_kernel<4><<<grid, 256, 0, c->stream>>>(W, x, m, n, y); break;
-        default: matvec_forward_kernel<8><<<grid, 256, 0, c->stream>>>(W, x, m, n, y); break;
+        case 1: matvec_forward_kernel<1><<<grid, 256, 0, c->stream>>>(mb, x, n); break;
+        case 2: matvec_forward_kernel<2><<<grid, 256, 0, c->stream>>>(mb, x, n); break;
+        case 4: matvec_forward_kernel<4><<<grid, 256, 0, c->stream>>>(mb, x, n); break;
+        default: matvec_forward_kernel<8><<<grid, 256, 0, c->stream>>>(mb, x, n); break;
     }
 }
-inline void matvec_forward(zkb_ctx* c, const u32* W, const u32* x, u32 m, u32 n, u32* y, u32 m_pad) {
-    if (m_pad > m) ZKB_CUDA(cudaMemsetAsync(y + m, 0, (size_t)(m_pad - m) * 4, c->stream));
+// y = W x for one matrix; the tail y[m..m_pad) is zeroed unless the caller keeps it zero itself.
+inline void matvec_forward(zkb_ctx* c, const u32* W, const u32* x, u32 m, u32 n, u32* y, u32 m_pad, bool zero_tail = true) {
+    if (zero_tail && m_pad > m) ZKB_CUDA(cudaMemsetAsync(y + m, 0, (size_t)(m_pad - m) * 4, c->stream));
+    MatvecBatch mb{};
+    mb.W[0] = W; mb.y[0] = y; mb.first[0] = 0; mb.first[1] = m; mb.count = 1;
     int rg = c->range_begin(ZKB_RANGE_MATVEC_FORWARD, 4.0 * m * n);
-    launch_matvec_forward(c, W, x, m, n, y);
+    launch_matvec_forward(c, mb, x, n);
+    c->range_end(rg);
+    ZKB_LAUNCHED(c);
+}
+// Several matrices with the same input and column count in one launch (tails must already be zero).
+inline void matvec_forward_batch(zkb_ctx* c, int count, const u32* const* W, u32* const* y, const u32* m, const u32* x, u32 n) {
+    MatvecBatch mb{};
+    u32 rows = 0;
+    for (int t = 0; t < count; t++) { mb.W[t] = W[t]; mb.y[t] = y[t]; mb.first[t] = rows; rows += m[t]; }
+    mb.first[count] = rows;
+    mb.count = (u32)count;
+    int rg = c->range_begin(ZKB_RANGE_MATVEC_FORWARD, 4.0 * rows * n);
+    launch_matvec_forward(c, mb, x, n);
     c->range_end(rg);
     ZKB_LAUNCHED(c);
 }
@@ -96,10 +112,14 @@ inline void qwen_forward(zkb_qwen_layer* L) {
     const u32 dm = d.d_model, dmp = (u32)pad_pow2(dm), aod = d.aod(), aodp = (u32)pad_pow2(aod), dffp = (u32)pad_pow2(d.d_ff);
     rmsnorm_forward_kernel<<<1, 1024, 0, c->stream>>>(L->x, L->w[W_NORM1], dm, dmp, L->norm1_out, L->norm1_x, L->n1_scalars, c->status);
     ZKB_LAUNCHED(c);
-    matvec_forward(c, L->w[W_Q], L->norm1_out, d.q_dim(), dm, L->q, (u32)pad_pow2(d.q_dim()));
-    matvec_forward(c, L->w[W_K], L->norm1_out, d.k_dim(), dm, L->k, (u32)pad_pow2(d.k_dim()));
-    matvec_forward(c, L->w[W_V], L->norm1_out, d.v_dim(), dm, L->v, (u32)pad_pow2(d.v_dim()));
-    matvec_forward(c, L->w[W_GPROJ], L->norm1_out, aod, dm, L->g_raw, aodp);
+    // The trace buffers were zeroed when the layer was created and nothing writes their padded
+    // tails, so no launch has to clear them.  q, k, v and the gate projection share norm1_out.
+    {
+        const u32* Wm[4] = {L->w[W_Q], L->w[W_K], L->w[W_V], L->w[W_GPROJ]};
+        u32* ym[4] = {L->q, L->k, L->v, L->g_raw};
+        const u32 mm[4] = {d.q_dim(), d.k_dim(), d.v_dim(), aod};
+        matvec_forward_batch(c, 4, Wm, ym, mm, L->norm1_out, dm);
+    }
     if (d.is_gqa()) {
         replicate_heads_kernel<<<grid_for(c, aodp), 256, 0, c->stream>>>(L->v, d.nq, d.nq / d.nkv, d.d_head, aodp, L->attn_out);
         ZKB_LAUNCHED(c);
@@ -109,17 +129,21 @@ inline void qwen_forward(zkb_qwen_layer* L) {
     requant_lookup_mul_kernel<<<1, 1024, 0, c->stream>>>(L->g_raw, aod, aodp, L->sigmoid, L->n_table, L->attn_out, L->g_q, L->g_sig,
                                                         L->gated_attn, c->status);
     ZKB_LAUNCHED(c);
-    matvec_forward(c, L->w[W_O], L->gated_attn, dm, aod, L->gated_out, dmp);
+    matvec_forward(c, L->w[W_O], L->gated_attn, dm, aod, L->gated_out, dmp, false);
     add_vec_kernel<<<grid_for(c, dmp), 256, 0, c->stream>>>(L->x, L->gated_out, dm, dmp, L->h);
     ZKB_LAUNCHED(c);
     rmsnorm_forward_kernel<<<1, 1024, 0, c->stream>>>(L->h, L->w[W_NORM2], dm, dmp, L->norm2_out, L->norm2_x, L->n2_scalars, c->status);
     ZKB_LAUNCHED(c);
-    matvec_forward(c, L->w[W_GATE], L->norm2_out, d.d_ff, dm, L->gate_raw, dffp);
-    matvec_forward(c, L->w[W_UP], L->norm2_out, d.d_ff, dm, L->up, dffp);
+    {
+        const u32* Wm[2] = {L->w[W_GATE], L->w[W_UP]};
+        u32* ym[2] = {L->gate_raw, L->up};
+        const u32 mm[2] = {d.d_ff, d.d_ff};
+        matvec_forward_batch(c, 2, Wm, ym, mm, L->norm2_out, dm);
+    }
     requant_lookup_mul_kernel<<<1, 1024, 0, c->stream>>>(L->gate_raw, d.d_ff, dffp, L->silu, L->n_table, L->up, L->gate_q, L->gate_silu,
                                                         L->swiglu, c->status);
     ZKB_LAUNCHED(c);
-    matvec_forward(c, L->w[W_DOWN], L->swiglu, dm, d.d_ff, L->down, dmp);
+    matvec_forward(c, L->w[W_DOWN], L->swiglu, dm, d.d_ff, L->down, dmp, false);
     add_vec_kernel<<<grid_for(c, dmp), 256, 0, c->stream>>>(L->h, L->down, dm, dmp, L->out);
     ZKB_LAUNCHED(c);
     ZKB_CUDA(cudaGetLastError());

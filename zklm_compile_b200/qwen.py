@@ -94,6 +94,10 @@ class QwenLayer:
         """Replay of the captured launch sequence (default on) or launch-by-launch enqueueing."""
         check(self.ctx.h, _lib.lib().zkb_qwen_layer_use_graph(self.h, C.c_int32(1 if on else 0)))
 
+    def graph_state(self) -> int:
+        """0: the next proof is enqueued launch by launch, 1: it will be captured into a graph, 2: replayed."""
+        return int(_lib.lib().zkb_qwen_layer_graph_state(self.h))
+
     def set_binding(self, bind_mode: int, node_hash: int = 0):
         """Weight binding of the matmul proofs: 0 default build, 1 feature pcs, 2 feature pcs-full
         (bind_weights_ef, rust/zk_ml_prover/src/proving/matmul.rs:360-453)."""
@@ -176,7 +180,12 @@ class QwenModel:
         """Proofs of this stack's layers, in reverse layer order as the reference collects them
         (pipeline/prove.rs:183-188).  Enqueued from a few host threads, then collected."""
         n = len(self.layers)
-        list(self.pool.map(lambda i: self.layers[i].prove_begin(self.first_layer + i, self.input_hash), range(n)))
+        begin = lambda i: self.layers[i].prove_begin(self.first_layer + i, self.input_hash)
+        if any(l.graph_state() == 1 for l in self.layers):      # one-off graph captures: one at a time
+            for i in range(n):
+                begin(i)
+        else:
+            list(self.pool.map(begin, range(n)))
         proofs = [l.prove_end() for l in self.layers]
         return proofs[::-1]
 
@@ -213,7 +222,13 @@ class QwenModel:
             issued[i].set()
             self.layers[i].prove_begin(self.first_layer + i, self.input_hash)
 
-        futures = [self.pool.submit(task, i) for i in range(n)]
+        if any(l.graph_state() == 1 for l in self.layers):
+            # one-off graph captures: keep them on this thread, one at a time
+            for i in range(n):
+                task(i)
+            futures = []
+        else:
+            futures = [self.pool.submit(task, i) for i in range(n)]
         if on_forward_done is not None:
             issued[n - 1].wait()
             if not failed:
