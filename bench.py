@@ -353,6 +353,33 @@ def run_basefold(zk, ctx, n, reps=3):
     return out
 
 
+def run_mlp(zk, ctx, steps, warmup, ef=True):
+    """Dense-4M shape: four 1024 x 1024 linears with a GELU lookup between them, input length 1024,
+    forward + proofs on one transcript per step; host input, proofs back on the host."""
+    from zklm_compile_b200 import mlp, tables
+    dims = [1024] * 5
+    rng = np.random.default_rng(4)
+    weights = [np.mod(rng.integers(-127, 128, dims[l + 1] * dims[l]), P).astype(np.uint32) for l in range(4)]
+    x = np.mod(rng.integers(-127, 128, dims[0]), P).astype(np.uint32)
+    chain = mlp.DenseChain(ctx, weights, dims, tables.build_gelu_table(1000))
+
+    def step():
+        tr = zk.Transcript(ctx, b"structured-ml-proof")
+        return chain.prove(chain.forward(x), tr, ef=ef)
+
+    for _ in range(warmup):
+        ref = step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        out = step()
+    wall = (time.perf_counter() - t0) * 1e3 / steps
+    assert out == ref
+    chain.close()
+    return {"workload": "Dense-4M shape: four 1024x1024 linears, GELU lookup (scale 1000) between, input 1024; "
+                        + ("EF challenges" if ef else "base-field challenges"),
+            "ms_per_step_wall": round(wall, 3), "proof_bytes": sum(len(p) for p in out), "ops": len(out)}
+
+
 def run_qwen(zk, args, rank, world, local, dist, barrier, max_over_ranks):
     import torch  # only for the inter-rank hop of the activation vector and the proof gather
     from zklm_compile_b200 import qwen as zq, sharding, tables
@@ -578,6 +605,7 @@ def main():
                      "algorithmic_bytes_per_step": r["algorithmic_bytes_per_step"]})
         if not args.no_micro and rank == 0:
             line["basefold_microbench"] = run_basefold(zk, micro_ctx, args.n_basefold)
+        line["dense4m"] = {"ef": run_mlp(zk, micro_ctx, 5, 3, True), "base": run_mlp(zk, micro_ctx, 5, 3, False)}
     if qwen and not args.no_micro and rank == 0:
         m = run_sumcheck(zk, micro_ctx, args.n_micro, 5, 3, 0, False)
         line["sumcheck_microbench"] = {"metric": "sumcheck fold HBM GB/s", "n": m["n"], "value": m["value_gbps"], "unit": "GB/s",

@@ -286,3 +286,34 @@ def test_qwen_model_two_layers_reverse_order(ctx):
     assert model.forward_and_prove(x) == exp[::-1]
     assert model.forward_and_prove(model.ctxs[0].upload(x), ih) == exp[::-1]
     model.close()
+
+
+@pytest.mark.parametrize("ef", [True, False])
+def test_dense_chain_matches_oracle(ctx, ef):
+    """The Dense-4M shape of the reference's benchmark at 1/16 scale: four linears with a lookup
+    activation between them, proved on one transcript; every proof byte-identical to the oracle's."""
+    from zklm_compile_b200 import mlp, tables
+    dims = [64, 64, 64, 64, 64]
+    rng = np.random.default_rng(17)
+    weights = [np.mod(rng.integers(-127, 128, dims[l + 1] * dims[l]), P).astype(np.uint32) for l in range(4)]
+    x = np.mod(rng.integers(-127, 128, dims[0]), P).astype(np.uint32)
+    table_out = tables.build_gelu_table(1000)
+    chain = mlp.DenseChain(ctx, weights, dims, table_out)
+    trace = chain.forward(x)
+    t, o = zk.Transcript(ctx, b"structured-ml-proof"), O.Transcript(b"structured-ml-proof")
+    proofs = chain.prove(trace, t, ef=ef)
+    cur, k = x, 0
+    for l in range(4):
+        m, n = dims[l + 1], dims[l]
+        y = O.matmul_forward(weights[l], cur, m, n)
+        assert y.tolist() == trace[l][1].tolist()
+        assert proofs[k] == O.prove_matmul_succinct(o, weights[l], cur, y, m, n, ef=ef); k += 1
+        if l < 3:
+            q = O.requantize(y)
+            assert q.tolist() == trace[l][2].tolist()
+            a = trace[l][3]
+            exp, st = (O.prove_lookup_ef if ef else O.prove_lookup)(o, table_out, q, a)
+            assert st == 0 and proofs[k] == exp; k += 1
+            cur = a
+    assert t.squeeze() == o.squeeze()
+    chain.close()

@@ -181,3 +181,16 @@ def test_sumcheck_prove_then_verify(kind, nv):
     bad = polys.copy()
     bad[-1, 0] ^= 1
     assert not O.verify(kind, O.Transcript(b"rt"), cl, bad, chal, fin)
+
+
+def test_host_requantize_matches_oracle():
+    """zklm_compile_b200.tables.requantize_to_i16_field (host-side statement logic of the dense chain)
+    against the oracle's restatement of rust/zk_ml_prover/src/transformer/mod.rs:293-324."""
+    import numpy as np
+    from zklm_compile_b200 import tables
+    from oracle import pyoracle as O
+    P = (1 << 31) - 1
+    rng = np.random.default_rng(1)
+    for scale in (1, 10, 32767, 32768, 40000, 10 ** 9):
+        v = np.mod(rng.integers(-scale, scale + 1, 700), P).astype(np.uint32)
+        assert tables.requantize_to_i16_field(v).tolist() == O.requantize(v).tolist()

@@ -61,3 +61,22 @@ def build_gelu_table(scale: int) -> np.ndarray:
     x = _inputs_i16() / float(scale)
     y = 0.5 * x * (1.0 + np.tanh(np.sqrt(2.0 / np.pi) * (x + 0.044715 * x ** 3)))
     return i16_to_field(quantize_i16(y, float(scale)))
+
+
+def requantize_to_i16_field(values) -> np.ndarray:
+    """rust/zk_ml_prover/src/transformer/mod.rs:293-324: centre the field values, scale so that the
+    largest magnitude maps to 32767 (integer division rounding half away from zero, truncating
+    like Rust's `/`), clamp to i16, embed in M31.  The reference's Python drivers supply these
+    requantised pairs to the prover (forward.rs:161-201), so this is host-side statement logic."""
+    P = (1 << 31) - 1
+    u = np.ascontiguousarray(values, dtype=np.uint32).astype(np.int64)
+    s = np.where(u > P // 2, u - P, u)
+    max_abs = max(int(np.max(np.abs(s))) if s.size else 1, 1)
+    if max_abs <= 32767:
+        scaled = s
+    else:
+        half = max_abs // 2
+        num = np.where(s >= 0, s * 32767 + half, s * 32767 - half)
+        scaled = np.sign(num) * (np.abs(num) // max_abs)          # truncation toward zero
+    scaled = np.clip(scaled, -32768, 32767)
+    return np.mod(scaled, P).astype(np.uint32)
