@@ -70,55 +70,9 @@ __global__ void __launch_bounds__(1024) rmsnorm_forward_kernel(const u32* __rest
 __device__ __forceinline__ long long centered(u32 v) { return v > ZKB_P / 2 ? (long long)v - (long long)ZKB_P : (long long)v; }
 __device__ __forceinline__ u32 to_field_i64(long long x) { return x >= 0 ? (u32)((unsigned long long)x % ZKB_P) : sub31(0u, (u32)((unsigned long long)(-x) % ZKB_P)); }
 
-// Single CTA: q = requantize(raw); t = table[q]; prod = other . t  (all zero-padded to n_pad).
-// `other_first` only documents the operand order of the product (it is commutative).
-__global__ void __launch_bounds__(1024) requant_lookup_mul_kernel(const u32* __restrict__ raw, u32 n, u32 n_pad,
-                                                                  const u32* __restrict__ table_out, u32 n_table,
-                                                                  const u32* __restrict__ other, u32* q_out, u32* t_out, u32* prod_out,
-                                                                  u32* status) {
-    __shared__ unsigned long long mx_s[32];
-    __shared__ unsigned long long mx_final;
-    unsigned long long mx = 1;
-    for (u32 i = threadIdx.x; i < n; i += blockDim.x) {
-        long long s = centered(raw[i]);
-        unsigned long long a = (unsigned long long)(s < 0 ? -s : s);
-        mx = a > mx ? a : mx;
-    }
-    for (int off = 16; off > 0; off >>= 1) {
-        unsigned long long o = __shfl_down_sync(0xffffffffu, mx, off);
-        mx = o > mx ? o : mx;
-    }
-    if ((threadIdx.x & 31) == 0) mx_s[threadIdx.x >> 5] = mx;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        unsigned long long m = 1;
-        for (u32 wv = 0; wv < (blockDim.x + 31) / 32; wv++) m = mx_s[wv] > m ? mx_s[wv] : m;
-        mx_final = m;
-    }
-    __syncthreads();
-    const long long max_abs = (long long)mx_final;
-    for (u32 i = threadIdx.x; i < n_pad; i += blockDim.x) {
-        u32 q = 0, t = 0, pr = 0;
-        if (i < n) {
-            long long v = centered(raw[i]), scaled;
-            if (max_abs <= 32767) scaled = v;
-            else {
-                long long half = max_abs / 2;
-                scaled = v >= 0 ? (v * 32767 + half) / max_abs : (v * 32767 - half) / max_abs;
-            }
-            scaled = scaled < -32768 ? -32768 : (scaled > 32767 ? 32767 : scaled);
-            q = to_field_i64(scaled);
-            u32 idx = field_to_table_index(q, n_table);
-            if (idx >= n_table) { atomicExch(status, (u32)ST_LOOKUP_KEY); idx = 0; }
-            t = table_out[idx];
-            pr = mul31(other[i], t);
-        }
-        q_out[i] = q; t_out[i] = t; prod_out[i] = pr;
-    }
-}
-
-// The same in two launches, so that the expensive part (64-bit divisions, table gathers) can use
-// the whole GPU: first the largest magnitude (one CTA, loads only), then the element-wise part.
+// q = requantize(raw); t = table[q]; prod = other . t  (all zero-padded to n_pad), in two launches,
+// so that the expensive part (64-bit divisions, table gathers) can use the whole GPU: first the
+// largest magnitude (one CTA, loads only), then the element-wise part.
 __global__ void __launch_bounds__(1024) absmax_kernel(const u32* __restrict__ raw, u32 n, unsigned long long* out) {
     __shared__ unsigned long long mx_s[32];
     unsigned long long mx = 1;

@@ -197,7 +197,6 @@ __global__ void __launch_bounds__(MK_THREADS) mk_tile_kernel(const u32* __restri
 // Raw authentication data of opened positions: for position p of a tree of height h over
 // `values`, out = [value, sibling value, sibling digest at level 1, ..., level h-1] (2 + 4 (h-1)
 // words).  The host drops the digests a batch proof does not need (pcs.rs:290-337).
-__device__ __forceinline__ size_t mk_path_words(u32 h) { return 2 + 4 * (size_t)(h - 1); }
 __device__ inline void mk_gather_path(const u32* __restrict__ values, size_t n_valid, const uint4* __restrict__ nodes, u32 h, size_t p,
                                       u32* out, int lane, int nlanes) {
     for (u32 k = lane; k <= h; k += nlanes) {

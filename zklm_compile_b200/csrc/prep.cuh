@@ -29,13 +29,6 @@ __global__ void widen_eq_kernel(WidenEqArgs a) {
         if (a.point) st_fe(a.eq_out + i, eq_at_index<Fe>(a.point, a.k, i));
     }
 }
-// Base-field twin: eq table at a base point (tables stay base, nothing to widen).
-__global__ void eq_base_kernel(const Fp* __restrict__ point, u32 k, Fp* out) {
-    const size_t n = size_t(1) << k;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
-        out[i] = eq_at_index<Fp>(point, k, i);
-}
-
 // out[i] = a[i] * b[i] (i < n), zero up to n_pad; optionally also sum_i x[i]^2 into *sumsq
 // (single CTA; rmsnorm.rs:532-540: g = gamma . x and sum_sq).
 __global__ void __launch_bounds__(1024) rmsnorm_prep_kernel(const u32* __restrict__ x, const u32* __restrict__ gamma, u32 d, u32 n_pad,

@@ -116,7 +116,6 @@ struct MatmulRec {
 // w_partial with blake3; feature pcs commits to w_partial with Basefold; feature pcs-full commits
 // to the row-padded matrix W itself.
 enum BindMode : int { BIND_BLAKE3 = 0, BIND_PCS = 1, BIND_PCS_FULL = 2 };
-struct MatmulScratch { unsigned long long* acc; };
 
 // W: m x n row-major on device; x: n valid of n_pad (zero padded); y: m valid.
 inline MatmulRec prove_matmul_succinct_ef(zkb_ctx* c, TrState* tr, const u32* W, const u32* x, const u32* y, u32 m, u32 n,

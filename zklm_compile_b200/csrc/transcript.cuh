@@ -111,14 +111,6 @@ __device__ __forceinline__ void sha256_expand_kw(const u32* __restrict__ blk_be,
 // words for the expanded schedule (K + W) of the block being compressed.
 constexpr int TR_SCRATCH_BYTES = 64 + 64 * 4;
 
-// Byte-swap and expand one 64-byte block (16 little-endian words) into K + W.
-__device__ __noinline__ void sha256_expand_block(const u32* __restrict__ blk_le, u32* __restrict__ kw) {
-    u32 w[16];
-#pragma unroll
-    for (int i = 0; i < 16; i++) { w[i] = bswap32(blk_le[i]); kw[i] = SHA_K[i] + w[i]; }
-#pragma unroll
-    for (int i = 16; i < 64; i++) { ZKB_SHA_SCHED(i); kw[i] = SHA_K[i] + w[i & 15]; }
-}
 struct Tr {
     u32 h[8];
     u32 buflen;
