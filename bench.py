@@ -605,12 +605,13 @@ def main():
                      "algorithmic_bytes_per_step": r["algorithmic_bytes_per_step"]})
         if not args.no_micro and rank == 0:
             line["basefold_microbench"] = run_basefold(zk, micro_ctx, args.n_basefold)
-        line["dense4m"] = {"ef": run_mlp(zk, micro_ctx, 5, 3, True), "base": run_mlp(zk, micro_ctx, 5, 3, False)}
+            line["dense4m"] = {"ef": run_mlp(zk, micro_ctx, 5, 3, True), "base": run_mlp(zk, micro_ctx, 5, 3, False)}
     if qwen and not args.no_micro and rank == 0:
         m = run_sumcheck(zk, micro_ctx, args.n_micro, 5, 3, 0, False)
         line["sumcheck_microbench"] = {"metric": "sumcheck fold HBM GB/s", "n": m["n"], "value": m["value_gbps"], "unit": "GB/s",
                                        "ms_per_step": m["ms_per_step"], "roofline": m["roofline"]}
         line["basefold_microbench"] = run_basefold(zk, micro_ctx, args.n_basefold)
+        line["dense4m"] = {"ef": run_mlp(zk, micro_ctx, 5, 3, True), "base": run_mlp(zk, micro_ctx, 5, 3, False)}
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         if qwen:
