@@ -425,11 +425,6 @@ def run_qwen(zk, args, rank, world, local, dist, barrier, max_over_ranks):
 
     for _ in range(args.warmup):
         ref = step(False)
-    # CUDA events around the matrix kernels of two layers only (one of each shape): enough for the
-    # per-launch roofline figures, and the timed region is not slowed by thousands of event records
-    prof_ctxs = [model.ctxs[j] for j in sorted({0, min(3, len(my) - 1)})] if model else []
-    for c in prof_ctxs:
-        c.profile(True)
     sampler = ClockSampler(local)
     sampler.start()
     ctx0.sync(); barrier()
@@ -441,6 +436,15 @@ def run_qwen(zk, args, rank, world, local, dist, barrier, max_over_ranks):
     barrier()
     clocks = sampler.stop()
     launches = (sum(c.launches for c in model.ctxs) if model else 0) - launches0
+    # Per-launch figures of the two kernels that stream the weights: two more steps with CUDA events
+    # around those kernels on two layers (one of each shape), outside the timed region because the
+    # event records slow a step down (and profiled layers are enqueued launch by launch)
+    prof_ctxs = [model.ctxs[j] for j in sorted({0, min(3, len(my) - 1)})] if model else []
+    for c in prof_ctxs:
+        c.profile(True)
+    for _ in range(2):
+        step(False)
+    ctx0.sync(); barrier()
     ranges = {"fold_eq_matvec": [0.0, 0.0, 0], "matvec_forward": [0.0, 0.0, 0]}
     for c in prof_ctxs:
         for k, (ms, by, cnt) in c.profile_ranges().items():

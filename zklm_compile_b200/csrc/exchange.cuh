@@ -4,10 +4,11 @@
 // j = j' W + g as a contiguous local table indexed by j'.  Folding is MSB-first (pairs j,
 // j + half), so while half >= W both partners of a pair live on the same GPU and a round is
 // purely local except for its three or four partial sums.  Those are exchanged here, inside
-// the kernel that produced them: the CTA that finishes the local reduction stores its sums
-// into a mailbox in every peer's memory (plain stores through peer mappings over NVLink, no
-// multicast), publishes a sequence number with release semantics, waits for the W sequence
-// numbers in its own mailbox, adds the W vectors and advances its own copy of the transcript.
+// the kernel that produced them: one warp of the CTA that finishes the local reduction stores
+// its sums into a mailbox in every peer's memory (lane p serves peer p; plain stores through
+// peer mappings over NVLink, nothing broadcast by hardware), publishes a sequence number with
+// release semantics, waits for the W sequence numbers in its own mailbox (lane s polls sender s),
+// adds the W vectors and advances its own copy of the transcript.
 // Field addition of canonical values is associative and commutative, so every GPU gets the
 // same round message and therefore the same challenge; no broadcast is needed.
 //
@@ -55,39 +56,51 @@ __device__ __forceinline__ u32 xch_ld_relaxed(const u32* p) {
 }
 __device__ __forceinline__ u32* xch_cell(u32* box, u32 slot, u32 sender) { return box + ((size_t)slot * XCH_MAX_WORLD + sender) * XCH_WORDS; }
 
-// Called by ONE thread.  Sends `mine` (nw <= XCH_FLAG words) to every rank under sequence
-// number `seq` and collects everybody's words into all[s * nw + k].  Returns false after a
-// timeout (now or earlier on this GPU); `all` is then unspecified.
-__device__ inline bool xch_allgather(const ScXch& x, u32 seq, const u32* mine, int nw, u32* all) {
+// Called by all 32 lanes of ONE warp; `mine` (nw <= XCH_FLAG words) is taken from lane 0.  Lane p
+// sends to rank p and lane s waits for sender s, so the stores, the release and the polls of the
+// up to eight peers proceed in parallel.  Afterwards lane s (s < world) holds rank s's words in
+// got[0..nw).  Returns false (in every lane) after a time-out, now or earlier on this GPU.
+template <int NW>
+__device__ __forceinline__ bool xch_exchange_warp(const ScXch& x, u32 seq, const u32* mine_lane0, u32* got) {
+    const int lane = threadIdx.x & 31;
     const u32 slot = seq & 1;
-    for (u32 p = 0; p < x.world; p++) {
-        u32* cell = xch_cell(x.box[p], slot, x.rank);
-        for (int k = 0; k < nw; k++) xch_st_relaxed(cell + k, mine[k]);
+    u32 mine[NW];
+#pragma unroll
+    for (int k = 0; k < NW; k++) mine[k] = __shfl_sync(0xffffffffu, mine_lane0[k], 0);
+    if (lane < (int)x.world) {
+        u32* cell = xch_cell(x.box[lane], slot, x.rank);
+#pragma unroll
+        for (int k = 0; k < NW; k++) xch_st_relaxed(cell + k, mine[k]);
+        xch_st_release(cell + XCH_FLAG, seq);       // orders this lane's payload stores before the flag, system scope
     }
-    // release: the payload stores above are ordered before each flag store at system scope
-    for (u32 p = 0; p < x.world; p++) xch_st_release(xch_cell(x.box[p], slot, x.rank) + XCH_FLAG, seq);
     bool ok = xch_ld_relaxed(x.sticky) == 0;
-    const unsigned long long t0 = xch_now_ns();
-    for (u32 s = 0; s < x.world && ok; s++) {
-        const u32* cell = xch_cell(x.box[x.rank], slot, s);
-        while (xch_ld_acquire(cell + XCH_FLAG) != seq) {
+#pragma unroll
+    for (int k = 0; k < NW; k++) got[k] = 0;
+    if (lane < (int)x.world) {
+        const u32* cell = xch_cell(x.box[x.rank], slot, (u32)lane);
+        const unsigned long long t0 = xch_now_ns();
+        while (ok && xch_ld_acquire(cell + XCH_FLAG) != seq) {
             if (xch_now_ns() - t0 > x.timeout_ns) { ok = false; xch_st_relaxed(x.sticky, 1u); break; }
             __nanosleep(100);
         }
-        if (ok) for (int k = 0; k < nw; k++) all[s * nw + k] = xch_ld_relaxed(cell + k);
+        if (ok) {
+#pragma unroll
+            for (int k = 0; k < NW; k++) got[k] = xch_ld_relaxed(cell + k);
+        }
     }
-    return ok;
+    return __all_sync(0xffffffffu, ok);
 }
-// Sum of the canonical words of all ranks, in place.
+// Sum of the canonical words of all ranks; input and result in lane 0's t[0..NW).
 template <int NW>
-__device__ inline void xch_allreduce(const ScXch& x, u32 seq, u32* t) {
-    u32 all[XCH_MAX_WORLD * NW];
-    if (!xch_allgather(x, seq, t, NW, all)) return;
+__device__ __forceinline__ void xch_allreduce_warp(const ScXch& x, u32 seq, u32* t) {
+    u32 got[NW];
+    const bool ok = xch_exchange_warp<NW>(x, seq, t, got);
 #pragma unroll
     for (int k = 0; k < NW; k++) {
-        u32 a = 0;
-        for (u32 s = 0; s < x.world; s++) a = add31(a, all[s * NW + k]);
-        t[k] = a;
+        u32 v = got[k];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) v = add31(v, __shfl_down_sync(0xffffffffu, v, off));
+        if (ok && (threadIdx.x & 31) == 0) t[k] = v;
     }
 }
 

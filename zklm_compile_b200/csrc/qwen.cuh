@@ -245,9 +245,14 @@ inline void qwen_prove_enqueue(zkb_qwen_layer* L, u32 layer_idx, const uint8_t i
         L->proofs_enqueued++;
         return;
     }
-    qwen_graph_drop(L);
     L->pending = new zkb_qwen_layer::Pending();
-    if (graph_ok && L->proofs_enqueued >= 1) {
+    if (!graph_ok) {                   // profiling or graphs switched off: launch by launch, keep any captured graph
+        qwen_prove_launches(L, *L->pending);
+        L->proofs_enqueued++;
+        return;
+    }
+    qwen_graph_drop(L);
+    if (L->proofs_enqueued >= 1) {
         const uint64_t launches0 = c->launches;
         cudaGraph_t graph = nullptr;
         c->capturing = true;

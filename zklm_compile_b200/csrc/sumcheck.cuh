@@ -229,8 +229,8 @@ __global__ void __launch_bounds__(256) sc_round_kernel(ScTables tb, size_t half,
         for (int k = 0; k < NW; k++) t[k] = add31(t[k], __ldcg(io.partials + (size_t)b * 16 + k));
     }
     block_sum_words<NW>(t, red);
+    if (io.xch && threadIdx.x < 32) xch_allreduce_warp<NW>(*io.xch, io.xch->seq + round, t);
     if (threadIdx.x == 0) {
-        if (io.xch) xch_allreduce<NW>(*io.xch, io.xch->seq + round, t);
         Tr tr;
         tr_load(tr, io.tr, trbuf);
         sc_finish_round<KIND, AccT, ChalT>(t, io, round, tr);
@@ -332,8 +332,8 @@ __global__ void __launch_bounds__(256) sc_product_base_kernel(ScTables tb, size_
         for (int k = 0; k < NACC; k++) t[k] = add31(t[k], __ldcg(io.partials + (size_t)b * 16 + k));
     }
     block_sum_words<NACC>(t, red);
+    if (io.xch && threadIdx.x < 32) xch_allreduce_warp<NACC>(*io.xch, io.xch->seq + round, t);
     if (threadIdx.x == 0) {
-        if (io.xch) xch_allreduce<NACC>(*io.xch, io.xch->seq + round, t);
         Tr tr;
         tr_load(tr, io.tr, trbuf);
         if constexpr (FOLD) {
@@ -419,8 +419,8 @@ __global__ void __launch_bounds__(SC_TAIL_THREADS) sc_tail_kernel(ScTables tb, s
             for (int k = 0; k < NACC; k++) to_words(acc[k], w + k * WC);
         }
         block_sum_words<NACC * WC>(w, red);
+        if (io.xch && phase == 0 && threadIdx.x < 32) xch_allreduce_warp<NACC * WC>(*io.xch, io.xch->seq + round, w);
         if (threadIdx.x == 0) {
-            if (io.xch && phase == 0) xch_allreduce<NACC * WC>(*io.xch, io.xch->seq + round, w);
             ChalT rn = sc_finish_round<KIND, ChalT, ChalT>(w, io, round, tr);
             to_words(rn, r_sh);
         }
@@ -432,27 +432,30 @@ __global__ void __launch_bounds__(SC_TAIL_THREADS) sc_tail_kernel(ScTables tb, s
     if (!split || phase == 1) break;
     // size == 2: fold the last local challenge in, gather everybody's remainder (ordered by rank =
     // the low index bits), and continue on the gathered tables with nothing pending.
-    if (threadIdx.x == 0) {
+    if (threadIdx.x < 32) {
         u32 mine[NT * WC];
 #pragma unroll
-        for (int t = 0; t < NT; t++) {
-            ChalT v;
-            if (in_src) v = lerp(ld_el<SrcT>(cur.src[t], 0), ld_el<SrcT>(cur.src[t], 1), r);
-            else {
-                ChalT a = ld_el<ChalT>(cur.src[t], 0), b = ld_el<ChalT>(cur.src[t], 1);
-                v = a + r * (b - a);
+        for (int k = 0; k < NT * WC; k++) mine[k] = 0;
+        if (threadIdx.x == 0) {
+#pragma unroll
+            for (int t = 0; t < NT; t++) {
+                ChalT v;
+                if (in_src) v = lerp(ld_el<SrcT>(cur.src[t], 0), ld_el<SrcT>(cur.src[t], 1), r);
+                else {
+                    ChalT a = ld_el<ChalT>(cur.src[t], 0), b = ld_el<ChalT>(cur.src[t], 1);
+                    v = a + r * (b - a);
+                }
+                to_words(v, mine + t * WC);
             }
-            to_words(v, mine + t * WC);
         }
-        u32 all[XCH_MAX_WORLD * NT * WC];
-        const u32 world = io.xch->world;
-        if (xch_allgather(*io.xch, io.xch->seq + io.xch_local_vars, mine, NT * WC, all)) {
-            for (u32 sdr = 0; sdr < world; sdr++)
-                for (int t = 0; t < NT; t++)
-                    for (int k = 0; k < WC; k++) gathered[t][sdr * WC + k] = all[sdr * NT * WC + t * WC + k];
-        } else {
+        u32 got[NT * WC];
+        const bool ok = xch_exchange_warp<NT * WC>(*io.xch, io.xch->seq + io.xch_local_vars, mine, got);
+        const u32 sdr = threadIdx.x;                  // lane s holds rank s's remainder
+        if (sdr < io.xch->world) {
+#pragma unroll
             for (int t = 0; t < NT; t++)
-                for (u32 k = 0; k < world * WC; k++) gathered[t][k] = 0;
+#pragma unroll
+                for (int k = 0; k < WC; k++) gathered[t][sdr * WC + k] = ok ? got[t * WC + k] : 0u;
         }
     }
     __syncthreads();
