@@ -4,9 +4,11 @@
 #pragma once
 #include "context.cuh"
 #include "trscript.cuh"
+#include "sumcheck_pipe.cuh"
 #include "prep.cuh"
 #include "logup.cuh"
 #include "forward.cuh"
+#include <cstdlib>
 #include <cstring>
 #include <type_traits>
 
@@ -57,6 +59,12 @@ inline int grid_for(zkb_ctx* c, size_t items, int per_cta = 256, int ctas_per_sm
 }
 #define ZKB_LAUNCHED(c) do { (c)->launches++; } while (0)
 
+// ZKB200_PLAIN_TAIL=1 in the environment selects the plain tail everywhere (for comparisons).
+inline bool pipe_tail_enabled() {
+    static const bool on = [] { const char* e = getenv("ZKB200_PLAIN_TAIL"); return !(e && e[0] && e[0] != '0'); }();
+    return on;
+}
+
 template <int KIND, class SrcT, class ChalT>
 void run_sumcheck(zkb_ctx* c, ScTables tb, u32 num_vars, ScIO io, bool dynamic) {
     // split over several GPUs: the tables are this GPU's slice of 2^local_vars elements
@@ -98,7 +106,12 @@ void run_sumcheck(zkb_ctx* c, ScTables tb, u32 num_vars, ScIO io, bool dynamic) 
         pending = true;
         round++;
     }
-    if (in_src)
+    // product sumchecks over EF tables: the tail that overlaps the table work with the hash chain
+    constexpr bool pipe_t = KIND == SC_PRODUCT && std::is_same<ChalT, Fe>::value;
+    const bool pipe = pipe_t && pipe_tail_enabled() && !io.xch && !dynamic && !io.dyn_nv && (!in_src || std::is_same<SrcT, Fe>::value);
+    if (pipe) {
+        if constexpr (pipe_t) sc_tail_product_pipe_kernel<<<1, PIPE_THREADS, 0, c->stream>>>(tb, size, round, num_vars, pending ? 1 : 0, io);
+    } else if (in_src)
         sc_tail_kernel<KIND, SrcT, ChalT><<<1, SC_TAIL_THREADS, 0, c->stream>>>(tb, size, round, num_vars, pending ? 1 : 0, io);
     else
         sc_tail_kernel<KIND, ChalT, ChalT><<<1, SC_TAIL_THREADS, 0, c->stream>>>(tb, size, round, num_vars, 1, io);
