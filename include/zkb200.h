@@ -191,6 +191,13 @@ int32_t zkb_qwen_layer_forward(zkb_qwen_layer* layer, const uint32_t* x, int32_t
  * for prev's forward through a CUDA event (prev's forward must already have been issued);
  * with prev == NULL the input is x.  Errors surface at zkb_qwen_layer_prove_end. */
 int32_t zkb_qwen_layer_forward_async(zkb_qwen_layer* layer, zkb_qwen_layer* prev, const uint32_t* x, int32_t x_on_device);
+/* A model may give all its layers one shared stream for their forward passes (zkb_stream_create
+ * with high_priority = 1): the forward chain then runs back to back and ahead of the proof
+ * kernels of earlier layers; each layer's own stream waits for its forward before proving, and
+ * a later forward waits for the layer's previous proof.  NULL returns to the layer's own stream. */
+int32_t zkb_stream_create(zkb_ctx* ctx, int32_t high_priority, void** out);
+void zkb_stream_destroy(void* stream);
+int32_t zkb_qwen_layer_set_forward_stream(zkb_qwen_layer* layer, void* stream);
 /* Waits for the layer's (asynchronous) forward pass only - not for a proof queued behind it -
  * and copies the layer output (d_model words) to the host. */
 int32_t zkb_qwen_layer_read_output(zkb_qwen_layer* layer, uint32_t* y_host);

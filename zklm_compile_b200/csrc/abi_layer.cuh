@@ -30,6 +30,7 @@ int32_t zkb_qwen_layer_create(zkb_ctx* c, const uint64_t dims[7], const uint32_t
         }
         // commit_qwen_layer (qwen.rs:148-161): blake3 of each unpadded matrix
         ZKB_CUDA(cudaEventCreateWithFlags(&L->fwd_done, cudaEventDisableTiming));
+        ZKB_CUDA(cudaEventCreateWithFlags(&L->own_idle, cudaEventDisableTiming));
         ZKB_CUDA(cudaMalloc(&L->roots_dev, 64 * 4));
         if (const char* e = getenv("ZKB200_NO_GRAPH")) L->use_graph = !(e[0] && e[0] != '0');
         ZKB_CUDA(cudaMalloc(&L->seed_dev, 128));
@@ -77,6 +78,7 @@ void zkb_qwen_layer_destroy(zkb_qwen_layer* L) {
     }
     for (int i = 0; i < W_COUNT; i++) if (L->w[i]) cudaFree(L->w[i]);
     if (L->fwd_done) cudaEventDestroy(L->fwd_done);
+    if (L->own_idle) cudaEventDestroy(L->own_idle);
     qwen_graph_drop(L);
     if (L->seed_dev) cudaFree(L->seed_dev);
     if (L->seed_host) cudaFreeHost(L->seed_host);
@@ -125,6 +127,7 @@ int32_t zkb_qwen_layer_forward(zkb_qwen_layer* L, const uint32_t* x, int32_t x_o
         clear_status(c);
         ZKB_CUDA(cudaMemcpyAsync(L->x, x, (size_t)L->dm.d_model * 4, x_on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, c->stream));
         qwen_forward(L);
+        L->fwd_on_shared = false;
         if (y) ZKB_CUDA(cudaMemcpyAsync(y, L->out, (size_t)L->dm.d_model * 4, y_on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost, c->stream));
         uint32_t st = c->read_status();
         int32_t rc = status_to_code(c, st);
@@ -143,16 +146,45 @@ int32_t zkb_qwen_layer_forward_async(zkb_qwen_layer* L, zkb_qwen_layer* prev, co
         c->use();
         clear_status(c);
         const size_t bytes = (size_t)L->dm.d_model * 4;
+        // with a shared forward stream the kernels below go there; the context's own stream is put
+        // back before returning (a context is driven by one host thread at a time)
+        cudaStream_t own = c->stream;
+        cudaStream_t S = L->fwd_stream ? L->fwd_stream : own;
+        if (L->fwd_stream) ZKB_CUDA(cudaStreamWaitEvent(S, L->own_idle, 0));      // not before the layer's previous proof has finished with the trace
+        struct Restore { zkb_ctx* c; cudaStream_t s; ~Restore() { c->stream = s; } } restore{c, own};
+        c->stream = S;
         if (prev) {
             if (prev->dm.d_model != L->dm.d_model) throw ArgFail{ZKB_E_ARG, "layer widths differ"};
-            ZKB_CUDA(cudaStreamWaitEvent(c->stream, prev->fwd_done, 0));
-            ZKB_CUDA(cudaMemcpyAsync(L->x, prev->out, bytes, cudaMemcpyDeviceToDevice, c->stream));
+            if (!(L->fwd_stream && prev->fwd_stream == L->fwd_stream)) ZKB_CUDA(cudaStreamWaitEvent(S, prev->fwd_done, 0));
+            ZKB_CUDA(cudaMemcpyAsync(L->x, prev->out, bytes, cudaMemcpyDeviceToDevice, S));
         } else {
-            ZKB_CUDA(cudaMemcpyAsync(L->x, x, bytes, x_on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, c->stream));
+            ZKB_CUDA(cudaMemcpyAsync(L->x, x, bytes, x_on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, S));
         }
         qwen_forward(L);
-        ZKB_CUDA(cudaEventRecord(L->fwd_done, c->stream));
+        ZKB_CUDA(cudaEventRecord(L->fwd_done, S));
+        L->fwd_on_shared = L->fwd_stream != nullptr;
     });
+}
+// Shared forward stream (see zkb_stream_create): pass NULL to go back to the layer's own stream.
+int32_t zkb_qwen_layer_set_forward_stream(zkb_qwen_layer* L, void* stream) {
+    if (!L) return ZKB_E_ARG;
+    L->fwd_stream = (cudaStream_t)stream;
+    return ZKB_OK;
+}
+// A stream of the highest (high_priority != 0) or default priority on the context's device.
+int32_t zkb_stream_create(zkb_ctx* c, int32_t high_priority, void** out) {
+    if (!c || !out) return ZKB_E_ARG;
+    ZKB_TRY(c, {
+        c->use();
+        int lo = 0, hi = 0;
+        ZKB_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+        cudaStream_t s = nullptr;
+        ZKB_CUDA(cudaStreamCreateWithPriority(&s, cudaStreamNonBlocking, high_priority ? hi : lo));
+        *out = (void*)s;
+    });
+}
+void zkb_stream_destroy(void* stream) {
+    if (stream) cudaStreamDestroy((cudaStream_t)stream);
 }
 // Wait for this layer's forward pass only (not for a proof queued behind it on the same
 // stream) and copy its output (d_model words) to host memory.

@@ -42,6 +42,12 @@ struct zkb_qwen_layer {
     zkb::u32* trace_block = nullptr;
     bool have_trace = false;
     cudaEvent_t fwd_done = nullptr;      // recorded after the forward kernels; the next layer's stream waits on it
+    // Optional stream shared by the forward passes of a whole model (high priority, layers in order):
+    // the forward chain then runs back to back, ahead of the proof kernels of earlier layers, and
+    // this layer's own stream only waits for fwd_done before its proof.
+    cudaStream_t fwd_stream = nullptr;
+    cudaEvent_t own_idle = nullptr;      // recorded on the layer's own stream behind every enqueued proof
+    bool fwd_on_shared = false;          // the last forward ran on fwd_stream: the proof has to wait for fwd_done
     // pending proof
     struct Pending;
     Pending* pending = nullptr;
@@ -219,9 +225,13 @@ inline void qwen_graph_drop(zkb_qwen_layer* L);
 
 // Enqueue the whole layer proof (no synchronisation): eagerly the first time (the arena grows to
 // its final size), captured into a graph the second time, replayed from then on.
-inline void qwen_prove_enqueue(zkb_qwen_layer* L, u32 layer_idx, const uint8_t input_hash[32]) {
+inline void qwen_prove_enqueue_inner(zkb_qwen_layer* L, u32 layer_idx, const uint8_t input_hash[32]) {
     zkb_ctx* c = L->ctx;
     if (!L->have_trace) throw ArgFail{ZKB_E_ARG, "zkb_qwen_layer_prove: run the forward pass first"};
+    if (L->fwd_on_shared) {            // the forward ran on the shared stream: order the proof behind it
+        ZKB_CUDA(cudaStreamWaitEvent(c->stream, L->fwd_done, 0));
+        L->fwd_on_shared = false;
+    }
     {   // seed block -> device
         char seed[48];
         int n = snprintf(seed, sizeof seed, "qwen-layer-%u", layer_idx);
@@ -294,6 +304,11 @@ inline void qwen_prove_enqueue(zkb_qwen_layer* L, u32 layer_idx, const uint8_t i
     }
     qwen_prove_launches(L, *L->pending);
     L->proofs_enqueued++;
+}
+inline void qwen_prove_enqueue(zkb_qwen_layer* L, u32 layer_idx, const uint8_t input_hash[32]) {
+    qwen_prove_enqueue_inner(L, layer_idx, input_hash);
+    // a later forward on a shared stream must not overwrite the trace while this proof reads it
+    ZKB_CUDA(cudaEventRecord(L->own_idle, L->ctx->stream));
 }
 inline void qwen_graph_drop(zkb_qwen_layer* L) {
     if (L->graph_exec) { cudaGraphExecDestroy(L->graph_exec); L->graph_exec = nullptr; }

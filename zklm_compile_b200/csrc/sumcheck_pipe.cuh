@@ -102,6 +102,7 @@ __global__ void __launch_bounds__(PIPE_THREADS) sc_tail_product_pipe_kernel(ScTa
     __shared__ u32 r_sh[4];
     __shared__ u32 cw[PIPE_WORKER_WARPS][PIPE_NW];
     __shared__ u32 csum[2][PIPE_NW];
+    __shared__ u32 w_sh[12];
 
     Tr tr;
     if (threadIdx.x == 0) tr_load(tr, io.tr, trbuf);
@@ -145,14 +146,17 @@ __global__ void __launch_bounds__(PIPE_THREADS) sc_tail_product_pipe_kernel(ScTa
         first = false;
         from_words(r, r_sh);                         // r_k
         if (n == 2) break;                           // round k was the last one
-        if (threadIdx.x == 0) {
-            const u32* c = csum[k & 1];
-            const Fe r2 = r * r;
-#pragma unroll
-            for (int j = 0; j < 3; j++) {
+        if (threadIdx.x < 32) {                      // three lanes evaluate the three quadratics, lane 0 collects
+            if (threadIdx.x < 3) {
+                const u32* c = csum[k & 1] + 12 * threadIdx.x;
                 Fe c0, c1, c2;
-                from_words(c0, c + 12 * j); from_words(c1, c + 12 * j + 4); from_words(c2, c + 12 * j + 8);
-                to_words(c0 + r * c1 + r2 * c2, w + 4 * j);
+                from_words(c0, c); from_words(c1, c + 4); from_words(c2, c + 8);
+                to_words(c0 + r * (c1 + r * c2), w_sh + 4 * threadIdx.x);
+            }
+            __syncwarp();
+            if (threadIdx.x == 0) {
+#pragma unroll
+                for (int i = 0; i < 12; i++) w[i] = w_sh[i];
             }
         }
         k++;

@@ -158,6 +158,12 @@ class QwenModel:
             del w
         self.pool = ThreadPoolExecutor(max_workers=min(8, max(1, len(self.layers))))
         self.input_hash = bytes(32)
+        # one high-priority stream for the forward passes of all layers (used by forward_and_prove)
+        self._fwd_stream = C.c_void_p()
+        if self.layers:
+            check(self.ctxs[0].h, _lib.lib().zkb_stream_create(self.ctxs[0].h, C.c_int32(1), C.byref(self._fwd_stream)))
+            for l in self.layers:
+                check(l.ctx.h, _lib.lib().zkb_qwen_layer_set_forward_stream(l.h, self._fwd_stream))
 
     def forward(self, x, input_hash: bytes = None):
         """Sequential forward through the resident layers.  x: host vector or DeviceBuffer.
@@ -242,6 +248,10 @@ class QwenModel:
         self.pool.shutdown()
         for l in self.layers:
             l.close()
+        if self._fwd_stream.value:
+            _lib.lib().zkb_stream_destroy.restype = None
+            _lib.lib().zkb_stream_destroy(self._fwd_stream)
+            self._fwd_stream = C.c_void_p()
         for t in self.tables:
             t.free()
         for c in self.ctxs:
