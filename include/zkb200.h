@@ -222,6 +222,14 @@ int32_t zkb_qwen_layer_prove_end(zkb_qwen_layer* layer, uint8_t* out, size_t cap
 int32_t zkb_qwen_layer_prove(zkb_qwen_layer* layer, uint32_t layer_idx, const uint8_t input_hash[32], uint8_t* out, size_t cap,
                              size_t* len);
 
+/* Tells a context that it shares the GPU with many other contexts that run at the same time (one
+ * per layer of a model).  Its kernels then leave half of every SM free: single-CTA kernels use
+ * 512 threads, wide kernels two or three CTAs per SM (the weight fold one).  Without this a wide
+ * kernel fills every SM's register file and every other context's single-CTA kernels - the
+ * serial transcript steps - wait for it to drain.  Off by default (a lone context is fastest
+ * with the greedy shapes). */
+int32_t zkb_ctx_set_shared(zkb_ctx* ctx, int32_t on);
+
 /* ---- one sumcheck split over several GPUs (one process per GPU) ----------------------------
  * No counterpart in the reference, which proves on one machine's cores; this is how a table
  * too large or too slow for one GPU is proved by `world` GPUs (a power of two, at most 8).

@@ -83,10 +83,10 @@ int32_t zkb_fold_eq_matvec(zkb_ctx* c, const uint32_t* W, size_t m, size_t n, co
         dim3 grid = fold_launch_dims(c->sm_count, m, n, &rows_per);
         u32* slabs = (u32*)c->scratch((size_t)grid.y * n * w * 4 + 16);
         if (ef) {
-            fold_eq_matvec_kernel<4, false><<<grid, FOLD_THREADS, 0, c->stream>>>(dW, m, n, eq, rows_per, nullptr, slabs);
+            fold_eq_matvec_kernel<4, false><<<fold_grid(grid, c->sm_count, c->polite), FOLD_THREADS, 0, c->stream>>>(dW, m, n, eq, rows_per, nullptr, slabs);
             fold_finalize_partials_kernel<4><<<grid_for(c, n_pad * 4), 256, 0, c->stream>>>(slabs, grid.y, n, n_pad, res);
         } else {
-            fold_eq_matvec_kernel<1, false><<<grid, FOLD_THREADS, 0, c->stream>>>(dW, m, n, eq, rows_per, nullptr, slabs);
+            fold_eq_matvec_kernel<1, false><<<fold_grid(grid, c->sm_count, c->polite), FOLD_THREADS, 0, c->stream>>>(dW, m, n, eq, rows_per, nullptr, slabs);
             fold_finalize_partials_kernel<1><<<grid_for(c, n_pad), 256, 0, c->stream>>>(slabs, grid.y, n, n_pad, res);
         }
         c->launches += 2;
@@ -237,7 +237,7 @@ int32_t zkb_rmsnorm_forward(zkb_ctx* c, const uint32_t* x, const uint32_t* gamma
         clear_status(c);
         u32* dx = up_pad(c, x, d, d); u32* dg = up_pad(c, gamma, d, d);
         u32* dout = (u32*)c->scratch(d * 4); u32* dxu = (u32*)c->scratch(d * 4); u32* sc = (u32*)c->scratch(16);
-        rmsnorm_forward_kernel<<<1, 1024, 0, c->stream>>>(dx, dg, (u32)d, (u32)d, dout, dxu, sc, c->status);
+        rmsnorm_forward_kernel<<<1, c->single_cta_threads(), 0, c->stream>>>(dx, dg, (u32)d, (u32)d, dout, dxu, sc, c->status);
         ZKB_LAUNCHED(c);
         u32 h[2];
         ZKB_CUDA(cudaMemcpyAsync(out, dout, d * 4, cudaMemcpyDeviceToHost, c->stream));

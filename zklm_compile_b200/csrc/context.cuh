@@ -93,6 +93,15 @@ struct zkb_ctx {
 
     void use() { ZKB_CUDA(cudaSetDevice(device)); }
 
+    // "Polite" launch shapes, for contexts that run next to many others on the same GPU (one per
+    // layer of a model): every kernel leaves half of each SM's registers and thread slots free -
+    // single-CTA kernels use 512 threads, wide kernels a few CTAs per SM - so that another
+    // context's latency-critical single-CTA kernel (a transcript step, a sumcheck tail) never
+    // has to wait for a wide kernel to drain before it finds an SM.
+    bool polite = false;
+    int single_cta_threads() const { return polite ? 512 : 1024; }
+    int wide_ctas_per_sm(int greedy, int shared) const { return polite ? shared : greedy; }
+
     // While a stream capture is open nothing may be allocated; arena_epoch changes whenever the
     // arena's memory does, which invalidates captured graphs that hold addresses inside it.
     bool capturing = false;

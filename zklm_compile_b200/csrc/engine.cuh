@@ -53,7 +53,7 @@ struct ScOpts {
 
 inline int grid_for(zkb_ctx* c, size_t items, int per_cta = 256, int ctas_per_sm = 8) {
     size_t want = (items + per_cta - 1) / per_cta;
-    size_t cap = (size_t)c->sm_count * ctas_per_sm;
+    size_t cap = (size_t)c->sm_count * c->wide_ctas_per_sm(ctas_per_sm, ctas_per_sm < 3 ? ctas_per_sm : 3);
     if (want < 1) want = 1;
     return (int)(want < cap ? want : cap);
 }
@@ -72,7 +72,8 @@ void run_sumcheck(zkb_ctx* c, ScTables tb, u32 num_vars, ScIO io, bool dynamic) 
     size_t size = size_t(1) << local_vars;
     bool pending = false, in_src = true;
     u32 round = 0;
-    const int max_grid = c->sm_count * 8 < SC_MAX_GRID ? c->sm_count * 8 : SC_MAX_GRID;
+    const int per_sm = c->wide_ctas_per_sm(8, 2);
+    const int max_grid = c->sm_count * per_sm < SC_MAX_GRID ? c->sm_count * per_sm : SC_MAX_GRID;
     c->prof_used = 0;
     c->prof_mark();
     while (!dynamic && round < local_vars) {
@@ -83,7 +84,9 @@ void run_sumcheck(zkb_ctx* c, ScTables tb, u32 num_vars, ScIO io, bool dynamic) 
         // base-field tables of a product sumcheck: vectorised launches (4 pair indices per thread)
         constexpr bool base_product_t = KIND == SC_PRODUCT && std::is_same<SrcT, Fp>::value;
         const bool base_product = base_product_t && ((((uintptr_t)tb.src[0]) | ((uintptr_t)tb.src[1])) & 15) == 0;   // 16-byte loads
-        int vgrid = (int)(((half + 3) / 4 + 255) / 256 < (size_t)max_grid ? ((half + 3) / 4 + 255) / 256 : (size_t)max_grid);
+        // the folding variant of the vectorised kernel needs 98 registers: one CTA per SM when sharing
+        const size_t vcap = (pending && c->polite) ? (size_t)c->sm_count : (size_t)max_grid;
+        int vgrid = (int)(((half + 3) / 4 + 255) / 256 < vcap ? ((half + 3) / 4 + 255) / 256 : vcap);
         if (!pending) {
             if constexpr (base_product_t) {
                 if (base_product) sc_product_base_kernel<ChalT, false><<<vgrid, 256, 0, c->stream>>>(tb, half, round, io);
@@ -110,11 +113,11 @@ void run_sumcheck(zkb_ctx* c, ScTables tb, u32 num_vars, ScIO io, bool dynamic) 
     constexpr bool pipe_t = KIND == SC_PRODUCT && std::is_same<ChalT, Fe>::value;
     const bool pipe = pipe_t && pipe_tail_enabled() && !io.xch && !dynamic && !io.dyn_nv && (!in_src || std::is_same<SrcT, Fe>::value);
     if (pipe) {
-        if constexpr (pipe_t) sc_tail_product_pipe_kernel<<<1, PIPE_THREADS, 0, c->stream>>>(tb, size, round, num_vars, pending ? 1 : 0, io);
+        if constexpr (pipe_t) sc_tail_product_pipe_kernel<<<1, c->polite ? PIPE_THREADS / 2 : PIPE_THREADS, 0, c->stream>>>(tb, size, round, num_vars, pending ? 1 : 0, io);
     } else if (in_src)
-        sc_tail_kernel<KIND, SrcT, ChalT><<<1, SC_TAIL_THREADS, 0, c->stream>>>(tb, size, round, num_vars, pending ? 1 : 0, io);
+        sc_tail_kernel<KIND, SrcT, ChalT><<<1, c->single_cta_threads(), 0, c->stream>>>(tb, size, round, num_vars, pending ? 1 : 0, io);
     else
-        sc_tail_kernel<KIND, ChalT, ChalT><<<1, SC_TAIL_THREADS, 0, c->stream>>>(tb, size, round, num_vars, 1, io);
+        sc_tail_kernel<KIND, ChalT, ChalT><<<1, c->single_cta_threads(), 0, c->stream>>>(tb, size, round, num_vars, 1, io);
     ZKB_LAUNCHED(c);
     c->prof_mark();
     ZKB_CUDA(cudaGetLastError());
@@ -220,7 +223,7 @@ inline size_t commit_small(zkb_ctx* c, const u32* words, u32 n_words, const u32*
     size_t off = c->rec_alloc(8);
     size_t max_chunks = ((size_t)max_words * 4 + 7 + 1023) / 1024 + 1;
     u32* cvs = (u32*)c->scratch(max_chunks * 32);
-    b3_commit_kernel<<<1, 1024, 0, c->stream>>>(b3_prefix("weights", 7), words, n_words, n_words_dev, cvs, c->rec_dev + off, absorb_into);
+    b3_commit_kernel<<<1, c->single_cta_threads(), 0, c->stream>>>(b3_prefix("weights", 7), words, n_words, n_words_dev, cvs, c->rec_dev + off, absorb_into);
     ZKB_LAUNCHED(c);
     return off;
 }

@@ -57,7 +57,7 @@ constexpr int FOLD_ROWS_TILE = FOLD_GROUPS * FOLD_UNROLL;   // granularity of th
 __device__ __forceinline__ u64 part_reduce(u64 a) { return (a & ZKB_P) + (a >> 31); }   // keeps a < 2^34
 
 // ATOMIC: column sums are added to 64-bit accumulators acc[n][NC] (zeroed by the caller).
-// Otherwise every row-CTA writes its own canonical sums to part[blockIdx.y][n * NC] (u32) and
+// Otherwise every row tile writes its own canonical sums to part[row tile][n * NC] (u32) and
 // fold_finalize_partials_kernel adds the slabs: no atomics (they serialise per address when a
 // hundred row-CTAs meet on one column) and nothing to clear.
 template <int NC, bool ATOMIC>
@@ -66,10 +66,15 @@ __global__ void __launch_bounds__(128 * FOLD_GROUPS, 2) fold_eq_matvec_kernel(co
                                                                              size_t rows_per_cta, unsigned long long* acc, u32* part) {
     __shared__ u32 sums[FOLD_GROUPS - 1][128][4 * NC];
     const int tx = threadIdx.x & 127, g = threadIdx.x >> 7;
-    const size_t j0 = ((size_t)blockIdx.x * 128 + tx) * 4;
-    const size_t r0 = (size_t)blockIdx.y * rows_per_cta;
+    const bool vec_n = (n % 4 == 0);
+    // gridDim.x CTAs walk the (column tile, row tile) pairs; with as many CTAs as tiles this is one tile each
+    const size_t col_tiles = (n + 511) / 512, row_tiles = (m + rows_per_cta - 1) / rows_per_cta;
+    for (size_t tile = blockIdx.x; tile < col_tiles * row_tiles; tile += gridDim.x) {
+    const size_t tile_x = tile % col_tiles, tile_y = tile / col_tiles;
+    const size_t j0 = (tile_x * 128 + tx) * 4;
+    const size_t r0 = tile_y * rows_per_cta;
     const size_t r1 = r0 + rows_per_cta < m ? r0 + rows_per_cta : m;
-    const bool vec = (n % 4 == 0) && (j0 + 4 <= n);
+    const bool vec = vec_n && (j0 + 4 <= n);
     u64 a[4][NC];                       // grows by less than 2^35 per step: no overflow for any m < 2^28
 #pragma unroll
     for (int c = 0; c < 4; c++)
@@ -134,13 +139,17 @@ __global__ void __launch_bounds__(128 * FOLD_GROUPS, 2) fold_eq_matvec_kernel(co
 #pragma unroll
                     for (int q = 0; q < FOLD_GROUPS - 1; q++) v += sums[q][tx][c * NC + k];
                     if (ATOMIC) atomicAdd(acc + (j0 + c) * NC + k, (unsigned long long)v);
-                    else part[(size_t)blockIdx.y * n * NC + (j0 + c) * NC + k] = red64(v);
+                    else part[tile_y * n * NC + (j0 + c) * NC + k] = red64(v);
                 }
             }
         }
     }
+    __syncthreads();                    // sums[] is reused by the next tile
+    }
 }
-// Launch shape: 512 columns per CTA; rows split so that about four CTAs per SM exist.
+// Tiling: 512 columns per tile; rows split so that about four tiles per SM exist.  Returns
+// (column tiles, row tiles); the launch uses column tiles * row tiles CTAs, or fewer CTAs that
+// walk the tiles (fold_grid).
 inline dim3 fold_launch_dims(int sm_count, size_t m, size_t n, size_t* rows_per_out) {
     const unsigned col_ctas = (unsigned)((n + 511) / 512);
     unsigned want_rows = (unsigned)((sm_count * 4 + col_ctas - 1) / col_ctas);
@@ -152,6 +161,12 @@ inline dim3 fold_launch_dims(int sm_count, size_t m, size_t n, size_t* rows_per_
     return dim3(col_ctas, (unsigned)((m + rows_per - 1) / rows_per));
 }
 constexpr int FOLD_THREADS = 128 * FOLD_GROUPS;
+// CTAs of the launch: all tiles at once, or one CTA per SM when the GPU is shared with other contexts
+// (the kernel needs 128 registers x 256 threads = half of an SM's register file).
+inline unsigned fold_grid(dim3 tiles, int sm_count, bool polite) {
+    unsigned t = tiles.x * tiles.y;
+    return polite && t > (unsigned)sm_count ? (unsigned)sm_count : t;
+}
 
 // Sum of the row-CTAs' slabs -> canonical u32 (interleaved EF coordinates when NC = 4), zero beyond n.
 template <int NC>

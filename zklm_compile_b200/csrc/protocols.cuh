@@ -144,7 +144,7 @@ inline MatmulRec prove_matmul_succinct_ef(zkb_ctx* c, TrState* tr, const u32* W,
         dim3 grid = fold_launch_dims(c->sm_count, m, n, &rows_per);
         int rg = c->range_begin(ZKB_RANGE_FOLD_EQ_MATVEC, 4.0 * m * n);
         u32* slabs = (u32*)c->scratch((size_t)grid.y * n * 4 * 4 + 16);
-        fold_eq_matvec_kernel<4, false><<<grid, FOLD_THREADS, 0, c->stream>>>(W, m, n, (const u32*)eq_r, rows_per, nullptr, slabs);
+        fold_eq_matvec_kernel<4, false><<<fold_grid(grid, c->sm_count, c->polite), FOLD_THREADS, 0, c->stream>>>(W, m, n, (const u32*)eq_r, rows_per, nullptr, slabs);
         c->range_end(rg);
         ZKB_LAUNCHED(c);
         fold_finalize_partials_kernel<4><<<grid_for(c, n_pad * 4), 256, 0, c->stream>>>(slabs, grid.y, n, n_pad, (u32*)w_partial);
@@ -256,7 +256,7 @@ inline MatmulRec prove_matmul_succinct_base(zkb_ctx* c, TrState* tr, const u32* 
         dim3 grid = fold_launch_dims(c->sm_count, m, n, &rows_per);
         int rg = c->range_begin(ZKB_RANGE_FOLD_EQ_MATVEC, 4.0 * m * n);
         u32* slabs = (u32*)c->scratch((size_t)grid.y * n * 4 + 16);
-        fold_eq_matvec_kernel<1, false><<<grid, FOLD_THREADS, 0, c->stream>>>(W, m, n, (const u32*)eq_r, rows_per, nullptr, slabs);
+        fold_eq_matvec_kernel<1, false><<<fold_grid(grid, c->sm_count, c->polite), FOLD_THREADS, 0, c->stream>>>(W, m, n, (const u32*)eq_r, rows_per, nullptr, slabs);
         c->range_end(rg);
         ZKB_LAUNCHED(c);
         fold_finalize_partials_kernel<1><<<grid_for(c, n_pad), 256, 0, c->stream>>>(slabs, grid.y, n, n_pad, w_partial);

@@ -27,7 +27,7 @@ inline RmsNormRec prove_rmsnorm_ef(zkb_ctx* c, TrState* tr, const u32* x, const 
     u32* sc_dev = c->rec_dev + R.scalars;
     pad_copy_kernel<<<grid_for(c, n), 256, 0, c->stream>>>(gamma, d, n, gamma_pad);
     ZKB_LAUNCHED(c);
-    rmsnorm_prep_kernel<<<1, 1024, 0, c->stream>>>(x, gamma, d, (u32)n, g, sc_dev + 1);
+    rmsnorm_prep_kernel<<<1, c->single_cta_threads(), 0, c->stream>>>(x, gamma, d, (u32)n, g, sc_dev + 1);
     ZKB_LAUNCHED(c);
     ZKB_CUDA(cudaMemcpyAsync(sc_dev, fwd_scalars, 4, cudaMemcpyDeviceToDevice, c->stream));   // delta
     B3Multi bm{};
@@ -129,7 +129,7 @@ inline RmsNormRec prove_rmsnorm_base(zkb_ctx* c, TrState* tr, const u32* x, cons
     u32* sc_dev = c->rec_dev + R.scalars;
     pad_copy_kernel<<<grid_for(c, n), 256, 0, c->stream>>>(gamma, d, n, gamma_pad);
     ZKB_LAUNCHED(c);
-    rmsnorm_prep_kernel<<<1, 1024, 0, c->stream>>>(x, gamma, d, (u32)n, g, sc_dev + 1);
+    rmsnorm_prep_kernel<<<1, c->single_cta_threads(), 0, c->stream>>>(x, gamma, d, (u32)n, g, sc_dev + 1);
     ZKB_LAUNCHED(c);
     ZKB_CUDA(cudaMemcpyAsync(sc_dev, fwd_scalars, 4, cudaMemcpyDeviceToDevice, c->stream));
     B3Multi bm{};
@@ -229,7 +229,7 @@ inline LookupRec prove_lookup_ef(zkb_ctx* c, TrState* tr, const u32* table_out, 
     ZKB_CUDA(cudaMemsetAsync(mult, 0, (size_t)n_table * 4, c->stream));
     logup_hist_kernel<<<grid_for(c, n), 256, 0, c->stream>>>(inputs, n, n_table, mult);
     ZKB_LAUNCHED(c);
-    logup_compact_kernel<<<1, 1024, 0, c->stream>>>(mult, table_out, n_table, n, act_idx, act_mult, act_entry, dyn);
+    logup_compact_kernel<<<1, c->single_cta_threads(), 0, c->stream>>>(mult, table_out, n_table, n, act_idx, act_mult, act_entry, dyn);
     ZKB_LAUNCHED(c);
     Fe* h = (Fe*)c->scratch(cap * 16);
     logup_h_kernel<Fe><<<grid_for(c, cap / LOGUP_BATCH + 1), 256, 0, c->stream>>>(inputs, outputs, table_out, n_table, act_idx, act_mult, dyn,
@@ -256,7 +256,7 @@ inline LookupRec prove_lookup_ef(zkb_ctx* c, TrState* tr, const u32* table_out, 
         memcpy(pre + 23, &n64, 8);
         size_t max_chunks = ((size_t)(2 * n + 2) * 4 + 31 + 1023) / 1024 + 1;
         u32* cvs = (u32*)c->scratch(max_chunks * 32);
-        b3_commit_kernel<<<1, 1024, 0, c->stream>>>(b3_prefix(pre, 31), cat, 2 * n + 2, nullptr, cvs, c->rec_dev + R.digest, nullptr);
+        b3_commit_kernel<<<1, c->single_cta_threads(), 0, c->stream>>>(b3_prefix(pre, 31), cat, 2 * n + 2, nullptr, cvs, c->rec_dev + R.digest, nullptr);
         ZKB_LAUNCHED(c);
     }
     return R;
@@ -305,7 +305,7 @@ inline LookupRec prove_lookup_base(zkb_ctx* c, TrState* tr, const u32* table_out
     ZKB_CUDA(cudaMemsetAsync(mult, 0, (size_t)n_table * 4, c->stream));
     logup_hist_kernel<<<grid_for(c, n), 256, 0, c->stream>>>(inputs, n, n_table, mult);
     ZKB_LAUNCHED(c);
-    logup_compact_kernel<<<1, 1024, 0, c->stream>>>(mult, table_out, n_table, n, act_idx, act_mult, act_entry, dyn);
+    logup_compact_kernel<<<1, c->single_cta_threads(), 0, c->stream>>>(mult, table_out, n_table, n, act_idx, act_mult, act_entry, dyn);
     ZKB_LAUNCHED(c);
     logup_encode_active_kernel<<<grid_for(c, max_active), 256, 0, c->stream>>>(act_idx, dyn, table_out, n_table, chal, act_enc);
     ZKB_LAUNCHED(c);
@@ -332,7 +332,7 @@ inline LookupRec prove_lookup_base(zkb_ctx* c, TrState* tr, const u32* table_out
         memcpy(pre + 23, &n64, 8);
         size_t max_chunks = ((size_t)(2 * n + 2) * 4 + 31 + 1023) / 1024 + 1;
         u32* cvs = (u32*)c->scratch(max_chunks * 32);
-        b3_commit_kernel<<<1, 1024, 0, c->stream>>>(b3_prefix(pre, 31), cat, 2 * n + 2, nullptr, cvs, c->rec_dev + R.digest, nullptr);
+        b3_commit_kernel<<<1, c->single_cta_threads(), 0, c->stream>>>(b3_prefix(pre, 31), cat, 2 * n + 2, nullptr, cvs, c->rec_dev + R.digest, nullptr);
         ZKB_LAUNCHED(c);
     }
     return R;

@@ -78,7 +78,7 @@ inline void launch_matvec_forward(zkb_ctx* c, const MatvecBatch& mb, const u32* 
     while (wpr < 8 && m * wpr < want_warps && n / (4 * (size_t)wpr * 2) >= 128) wpr *= 2;
     const size_t rows_per_cta = 8 / wpr;
     size_t ctas = (m + rows_per_cta - 1) / rows_per_cta;
-    const size_t cap = (size_t)c->sm_count * 8;
+    const size_t cap = (size_t)c->sm_count * c->wide_ctas_per_sm(8, 3);
     int grid = (int)(ctas < cap ? ctas : cap);
     if (grid < 1) grid = 1;
     switch (wpr) {
@@ -116,7 +116,7 @@ inline void qwen_forward(zkb_qwen_layer* L) {
     zkb_ctx* c = L->ctx;
     const QwenDims& d = L->dm;
     const u32 dm = d.d_model, dmp = (u32)pad_pow2(dm), aod = d.aod(), aodp = (u32)pad_pow2(aod), dffp = (u32)pad_pow2(d.d_ff);
-    rmsnorm_forward_kernel<<<1, 1024, 0, c->stream>>>(L->x, L->w[W_NORM1], dm, dmp, L->norm1_out, L->norm1_x, L->n1_scalars, c->status);
+    rmsnorm_forward_kernel<<<1, c->single_cta_threads(), 0, c->stream>>>(L->x, L->w[W_NORM1], dm, dmp, L->norm1_out, L->norm1_x, L->n1_scalars, c->status);
     ZKB_LAUNCHED(c);
     // The trace buffers were zeroed when the layer was created and nothing writes their padded
     // tails, so no launch has to clear them.  q, k, v and the gate projection share norm1_out.
@@ -133,7 +133,7 @@ inline void qwen_forward(zkb_qwen_layer* L) {
         ZKB_CUDA(cudaMemcpyAsync(L->attn_out, L->v, (size_t)aodp * 4, cudaMemcpyDeviceToDevice, c->stream));
     }
     unsigned long long* mx = reinterpret_cast<unsigned long long*>(L->n1_scalars + 4);   // two 8-byte slots after the scalars
-    absmax_kernel<<<1, 1024, 0, c->stream>>>(L->g_raw, aod, mx);
+    absmax_kernel<<<1, c->single_cta_threads(), 0, c->stream>>>(L->g_raw, aod, mx);
     ZKB_LAUNCHED(c);
     requant_lookup_mul_apply_kernel<<<grid_for(c, aodp), 256, 0, c->stream>>>(L->g_raw, aod, aodp, mx, L->sigmoid, L->n_table, L->attn_out,
                                                                              L->g_q, L->g_sig, L->gated_attn, c->status);
@@ -141,7 +141,7 @@ inline void qwen_forward(zkb_qwen_layer* L) {
     matvec_forward(c, L->w[W_O], L->gated_attn, dm, aod, L->gated_out, dmp, false);
     add_vec_kernel<<<grid_for(c, dmp), 256, 0, c->stream>>>(L->x, L->gated_out, dm, dmp, L->h);
     ZKB_LAUNCHED(c);
-    rmsnorm_forward_kernel<<<1, 1024, 0, c->stream>>>(L->h, L->w[W_NORM2], dm, dmp, L->norm2_out, L->norm2_x, L->n2_scalars, c->status);
+    rmsnorm_forward_kernel<<<1, c->single_cta_threads(), 0, c->stream>>>(L->h, L->w[W_NORM2], dm, dmp, L->norm2_out, L->norm2_x, L->n2_scalars, c->status);
     ZKB_LAUNCHED(c);
     {
         const u32* Wm[2] = {L->w[W_GATE], L->w[W_UP]};
@@ -150,7 +150,7 @@ inline void qwen_forward(zkb_qwen_layer* L) {
         matvec_forward_batch(c, 2, Wm, ym, mm, L->norm2_out, dm);
     }
     unsigned long long* mx2 = reinterpret_cast<unsigned long long*>(L->n2_scalars + 4);
-    absmax_kernel<<<1, 1024, 0, c->stream>>>(L->gate_raw, d.d_ff, mx2);
+    absmax_kernel<<<1, c->single_cta_threads(), 0, c->stream>>>(L->gate_raw, d.d_ff, mx2);
     ZKB_LAUNCHED(c);
     requant_lookup_mul_apply_kernel<<<grid_for(c, dffp), 256, 0, c->stream>>>(L->gate_raw, d.d_ff, dffp, mx2, L->silu, L->n_table, L->up,
                                                                               L->gate_q, L->gate_silu, L->swiglu, c->status);
@@ -198,7 +198,7 @@ inline void qwen_prove_launches(zkb_qwen_layer* L, zkb_qwen_layer::Pending& P) {
     P.mk = prove_matmul_succinct_ef(c, tr, L->w[W_K], L->norm1_out, L->k, d.k_dim(), dm, L->bind_mode, L->node_hash);
     P.mv = prove_matmul_succinct_ef(c, tr, L->w[W_V], L->norm1_out, L->v, d.v_dim(), dm, L->bind_mode, L->node_hash);
     P.seq1 = c->rec_alloc(2);
-    seq1_consistency_kernel<<<1, 1024, 0, c->stream>>>(tr, L->attn_out, aod, log2_ceil_u(aod), L->v, d.v_dim(), log2_ceil_u(d.v_dim()),
+    seq1_consistency_kernel<<<1, c->single_cta_threads(), 0, c->stream>>>(tr, L->attn_out, aod, log2_ceil_u(aod), L->v, d.v_dim(), log2_ceil_u(d.v_dim()),
                                                       d.is_gqa() ? 1u : 0u, log2_ceil_u(d.nkv), log2_ceil_u(d.d_head), c->rec_dev + P.seq1);
     ZKB_LAUNCHED(c);
     P.mo = prove_matmul_succinct_ef(c, tr, L->w[W_O], L->gated_attn, L->gated_out, dm, aod, L->bind_mode, L->node_hash);

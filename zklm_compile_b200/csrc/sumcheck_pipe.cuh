@@ -16,12 +16,12 @@
 
 namespace zkb {
 
-constexpr int PIPE_THREADS = 512;                                 // 128 registers per thread: the worker pass keeps 36 sums
-constexpr int PIPE_WORKER_WARPS = PIPE_THREADS / 32 - 1;          // 15
-constexpr int PIPE_WORKERS = PIPE_WORKER_WARPS * 32;              // 480
+constexpr int PIPE_THREADS = 512;                                 // at most; 128 registers per thread (the worker pass keeps 36 sums)
+constexpr int PIPE_MAX_WORKER_WARPS = PIPE_THREADS / 32 - 1;      // 15
 constexpr int PIPE_NW = 36;                                       // nine EF coefficient sums
 
-__device__ __forceinline__ void pipe_worker_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(PIPE_WORKERS) : "memory"); }
+// Barrier 1 among the worker warps only (all threads but warp 0); blockDim.x is a multiple of 32.
+__device__ __forceinline__ void pipe_worker_barrier() { asm volatile("bar.sync 1, %0;" ::"r"((int)blockDim.x - 32) : "memory"); }
 
 // Coefficient sums of the next round over one pair index: quarters (a, b, c, d) of f and g.
 __device__ __forceinline__ void pipe_accum(Fe* C, Fe fa, Fe fb, Fe fc, Fe fd, Fe ga, Fe gb, Fe gc, Fe gd) {
@@ -33,19 +33,21 @@ __device__ __forceinline__ void pipe_accum(Fe* C, Fe fa, Fe fb, Fe fc, Fe fd, Fe
     C[6] = C[6] + pf * pg;  C[7] = C[7] + pf * qg + pg * qf;  C[8] = C[8] + qf * qg;
 }
 
-// Workers only (threads 32..PIPE_THREADS-1).  Tables of size n at (rf, rg); if `fold`, they are first
+// Workers only (threads 32..blockDim.x-1; at least two worker warps, so that 36 threads can add the rows).  Tables of size n at (rf, rg); if `fold`, they are first
 // folded with r into size n / 2 at (wf, wg) (in place allowed) and the sums are taken over the
 // folded tables.  Leaves the 36 summed words in out[] (shared memory) when the result size is >= 4.
 __device__ __forceinline__ void pipe_worker_pass(const Fe* rf, const Fe* rg, Fe* wf, Fe* wg, size_t n, bool fold, Fe r,
                                                  u32 (*cw)[PIPE_NW], u32* out) {
     const int wid = threadIdx.x - 32;
+    const size_t workers = blockDim.x - 32;
+    const int worker_warps = (int)(workers >> 5);
     const size_t m = fold ? n / 2 : n;              // size of the tables the sums run over
     Fe C[9];
 #pragma unroll
     for (int i = 0; i < 9; i++) C[i] = fe_zero();
     if (m >= 4) {
         const size_t q = m / 4;                     // pair indices of the next round
-        for (size_t j = wid; j < q; j += PIPE_WORKERS) {
+        for (size_t j = wid; j < q; j += workers) {
             Fe fa, fb, fc, fd, ga, gb, gc, gd;
             if (fold) {
                 // folded element x is lerp(T[x], T[x + n/2], r); this thread owns x = j, j+q, j+2q, j+3q
@@ -89,7 +91,7 @@ __device__ __forceinline__ void pipe_worker_pass(const Fe* rf, const Fe* rg, Fe*
         pipe_worker_barrier();
         if (wid < PIPE_NW) {
             u32 v = 0;
-            for (int rw = 0; rw < PIPE_WORKER_WARPS; rw++) v = add31(v, cw[rw][wid]);
+            for (int rw = 0; rw < worker_warps; rw++) v = add31(v, cw[rw][wid]);
             out[wid] = v;
         }
     }
@@ -100,7 +102,7 @@ __global__ void __launch_bounds__(PIPE_THREADS) sc_tail_product_pipe_kernel(ScTa
     __shared__ u32 red[32 * 16];
     __shared__ __align__(16) unsigned char trbuf[TR_SCRATCH_BYTES];
     __shared__ u32 r_sh[4];
-    __shared__ u32 cw[PIPE_WORKER_WARPS][PIPE_NW];
+    __shared__ u32 cw[PIPE_MAX_WORKER_WARPS][PIPE_NW];
     __shared__ u32 csum[2][PIPE_NW];
     __shared__ u32 w_sh[12];
 

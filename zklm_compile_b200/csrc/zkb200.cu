@@ -280,6 +280,14 @@ int32_t zkb_tr_import(zkb_transcript* t, const uint8_t state[ZKB_TR_STATE_BYTES]
 }
 
 // ---- sumcheck
+// Launch shapes for a context that shares the GPU with many others (see zkb_ctx::polite).
+int32_t zkb_ctx_set_shared(zkb_ctx* c, int32_t on) {
+    if (!c) return ZKB_E_ARG;
+    c->polite = on != 0;
+    c->arena_epoch++;                  // captured graphs hold the old launch shapes
+    return ZKB_OK;
+}
+
 int32_t zkb_sumcheck_prove(zkb_ctx* c, zkb_transcript* t, int32_t kind, const uint32_t* const* tables,
                            uint32_t num_vars, int32_t on_device, uint32_t* round_polys, uint32_t* challenges,
                            uint32_t* finals) {
@@ -383,7 +391,7 @@ extern "C" int32_t zkb_fold_eq_matvec_ef_noalloc(const uint32_t* W_dev, size_t m
     if (e != cudaSuccess) { set_err(err, err_cap, std::string("cudaMemsetAsync: ") + cudaGetErrorString(e)); return ZKB_E_CUDA; }
     size_t rows_per = 0;
     dim3 grid = fold_launch_dims(D.sm_count, m, n, &rows_per);
-    fold_eq_matvec_kernel<4, true><<<grid, FOLD_THREADS, 0, s>>>(W_dev, m, n, eq_dev, rows_per, D.acc, nullptr);
+    fold_eq_matvec_kernel<4, true><<<fold_grid(grid, D.sm_count, false), FOLD_THREADS, 0, s>>>(W_dev, m, n, eq_dev, rows_per, D.acc, nullptr);
     size_t fin_items = n_pad * 4;
     int fin_grid = (int)((fin_items + 255) / 256);
     if (fin_grid > D.sm_count * 8) fin_grid = D.sm_count * 8;

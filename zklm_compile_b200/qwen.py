@@ -150,6 +150,9 @@ class QwenModel:
         self.device = device
         self.first_layer = first_layer
         self.ctxs = [Context(device) for _ in configs]
+        if len(self.ctxs) > 1:           # the layers' streams run side by side: share the SMs
+            for c in self.ctxs:
+                c.set_shared(True)
         self.tables = (self.ctxs[0].upload(silu_out), self.ctxs[0].upload(sigmoid_out))
         self.layers = []
         for i, (c, cfg) in enumerate(zip(self.ctxs, configs)):

@@ -58,6 +58,11 @@ class Context:
     def sync(self):
         check(self.h, _lib.lib().zkb_ctx_sync(self.h))
 
+    def set_shared(self, on: bool = True):
+        """This context runs next to many others on the same GPU: use launch shapes that leave half
+        of every SM free (see zkb_ctx_set_shared in include/zkb200.h)."""
+        check(self.h, _lib.lib().zkb_ctx_set_shared(self.h, C.c_int32(1 if on else 0)))
+
     @property
     def stream(self) -> int:
         """The context's cudaStream_t as an integer handle."""
