@@ -226,8 +226,9 @@ int32_t zkb_qwen_layer_prove(zkb_qwen_layer* layer, uint32_t layer_idx, const ui
  * per layer of a model).  Its kernels then leave half of every SM free: single-CTA kernels use
  * 512 threads, wide kernels two or three CTAs per SM (the weight fold one).  Without this a wide
  * kernel fills every SM's register file and every other context's single-CTA kernels - the
- * serial transcript steps - wait for it to drain.  Off by default (a lone context is fastest
- * with the greedy shapes). */
+ * serial transcript steps - may wait for it to drain.  Off by default: a lone context is fastest
+ * with the greedy shapes, and on B200 the 32-layer 4B-shape proof was measured slower with it
+ * (34.9 ms against 32.7 ms), the wide kernels losing more than the small ones gain. */
 int32_t zkb_ctx_set_shared(zkb_ctx* ctx, int32_t on);
 
 /* ---- one sumcheck split over several GPUs (one process per GPU) ----------------------------
