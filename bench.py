@@ -218,7 +218,7 @@ def run_sumcheck(zk, ctx, n, steps, warmup, rank, with_e2e, barrier=lambda: None
            "roofline": {"bound": "hbm", "achieved": round(dom[0], 1), "peak": peak, "unit": "GB/s", "frac": round(dom[0] / peak, 4),
                         "traffic": int(1.04 * per_launch_bytes[dom[2] - 1]) if dom[2] == 1 else int(0.95 * per_launch_bytes[dom[2] - 1]) if dom[2] else None,
                         "traffic_source": "algorithmic bytes x the dram/algorithmic ratio ncu measured on this kernel at n = 25 "
-                                          "(1.04 for the round-1 launch, 0.95 for EF rounds; profiles/sumcheck_kernels_product_ef_n25.md)",
+                                          "(1.04 for the round-1 launch, 0.95 for EF rounds)",
                         "peak_source": src,
                         "kernel": f"sc_round_kernel fold launch {dom[2]} (folds round {dom[2] - 1}): "
                                   f"{per_launch_bytes[dom[2] - 1] if dom[2] else 0} algorithmic bytes in {dom[1]:.4f} ms",
@@ -476,7 +476,7 @@ def run_qwen(zk, args, rank, world, local, dist, barrier, max_over_ranks):
         ms, by, cnt = ranges[name]
         ach = by / (ms * 1e-3) / 1e9 if ms > 0 else 0.0
         # DRAM bytes per launch from the ncu capture of these kernels on one layer: read + write = 1.00 x the
-        # algorithmic bytes for both (W is read once; see profiles/fold_eq_matvec_and_matvec_forward_qwen4b_layer.md)
+        # algorithmic bytes for both (W is read exactly once)
         return {"bound": "hbm", "achieved": round(ach, 1), "peak": peak, "unit": "GB/s", "frac": round(ach / peak, 4),
                 "traffic": round(by / cnt) if cnt else None, "traffic_source": "ncu dram__bytes_read+write / algorithmic = 1.00 on the same kernel",
                 "peak_source": src, "kernel": label, "launches": int(cnt), "avg_ms_per_launch": round(ms / cnt, 5) if cnt else None,
@@ -591,7 +591,7 @@ def main():
                              "h2d_bytes_per_step": 2560 * 4, "d2h_bytes_per_step": r["proof_bytes"]},
                      "gpu_launches": int(r["launches"]), "clocks": r["clocks"], "proof_bytes": r["proof_bytes"], "setup_s": r["setup_s"],
                      "note": "one step = forward pass + 32 layer proofs; bounded by the serial SHA-256 transcript chain of each layer, "
-                             "not by HBM (see DESIGN.md); vs_baseline = value / 376 ms published for an Apple M4 Max CPU"})
+                             "not by HBM; vs_baseline = value / 376 ms published for an Apple M4 Max CPU"})
         if r["model"]:
             r["model"].close()
         micro_ctx = zk.Context(local)

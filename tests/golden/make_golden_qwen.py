@@ -65,4 +65,6 @@ def main(ref_root: str):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        sys.exit("usage: %s <path to a checkout of the reference repository>" % sys.argv[0])
+    main(sys.argv[1])
