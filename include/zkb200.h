@@ -72,6 +72,13 @@ int32_t zkb_profile_read(zkb_ctx* ctx, float* ms, size_t cap, size_t* n);
  * bytes = 4 m n per launch), count[tag]; arrays of ZKB_RANGE_COUNT entries.  Synchronises. */
 enum { ZKB_RANGE_FOLD_EQ_MATVEC = 0, ZKB_RANGE_MATVEC_FORWARD = 1, ZKB_RANGE_COUNT = 2 };
 int32_t zkb_profile_ranges(zkb_ctx* ctx, double* ms, double* bytes, uint64_t* count);
+/* Launch trace (a debugging aid, off by default): while on, every launch site of the context
+ * records an event behind its kernel, also inside a captured layer graph, whose replays refresh
+ * the time stamps.  zkb_trace_dump waits for the context's stream and writes "index,site,ms" lines
+ * (site = source file:line of the launch, ms = time since the first traced launch of `base`, or of
+ * `ctx` itself when base is NULL) to `path`.  Enabling or disabling clears the log. */
+int32_t zkb_trace_enable(zkb_ctx* ctx, int32_t on);
+int32_t zkb_trace_dump(zkb_ctx* ctx, zkb_ctx* base, const char* path);
 /* Number of kernels this context has launched since creation. */
 uint64_t zkb_launch_count(const zkb_ctx* ctx);
 

@@ -70,6 +70,23 @@ struct zkb_ctx {
     std::vector<cudaEvent_t> prof_events;
     size_t prof_used = 0;
 
+    // Launch trace: when on, every launch site records an event behind its kernel (as an event-record
+    // node when the stream is being captured, so replays of the graph refresh the time stamps).
+    struct TraceEntry { const char* file; int line; cudaEvent_t ev; };
+    bool trace = false;
+    std::vector<TraceEntry> trace_log;
+    void launched(const char* file, int line) {
+        launches++;
+        if (!trace) return;
+        cudaEvent_t e = ev_get();
+        ZKB_CUDA(cudaEventRecordWithFlags(e, stream, capturing ? cudaEventRecordExternal : cudaEventRecordDefault));
+        trace_log.push_back(TraceEntry{file, line, e});
+    }
+    void trace_clear() {
+        for (auto& t : trace_log) ev_pool.push_back(t.ev);
+        trace_log.clear();
+    }
+
     // tagged event pairs around the bandwidth-bound kernels (only when profiling is on)
     struct Range { int tag; double bytes; cudaEvent_t a, b; };
     std::vector<Range> ranges;
@@ -99,7 +116,14 @@ struct zkb_ctx {
     // context's latency-critical single-CTA kernel (a transcript step, a sumcheck tail) never
     // has to wait for a wide kernel to drain before it finds an SM.
     bool polite = false;
-    int single_cta_threads() const { return polite ? 512 : 1024; }
+    int single_cta_threads() const {
+        static const int env = [] { const char* e = getenv("ZKB200_SINGLE_THREADS"); return e ? atoi(e) : 0; }();
+        return env ? env : (polite ? 512 : 1024);
+    }
+    int pipe_threads(int full) const {
+        static const int env = [] { const char* e = getenv("ZKB200_PIPE_THREADS"); return e ? atoi(e) : 0; }();
+        return env ? env : (polite ? full / 2 : full);
+    }
     int wide_ctas_per_sm(int greedy, int shared) const { return polite ? shared : greedy; }
 
     // While a stream capture is open nothing may be allocated; arena_epoch changes whenever the

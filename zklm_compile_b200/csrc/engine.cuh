@@ -57,7 +57,7 @@ inline int grid_for(zkb_ctx* c, size_t items, int per_cta = 256, int ctas_per_sm
     if (want < 1) want = 1;
     return (int)(want < cap ? want : cap);
 }
-#define ZKB_LAUNCHED(c) do { (c)->launches++; } while (0)
+#define ZKB_LAUNCHED(c) (c)->launched(__FILE__, __LINE__)
 
 // ZKB200_PLAIN_TAIL=1 in the environment selects the plain tail everywhere (for comparisons).
 inline bool pipe_tail_enabled() {
@@ -113,7 +113,7 @@ void run_sumcheck(zkb_ctx* c, ScTables tb, u32 num_vars, ScIO io, bool dynamic) 
     constexpr bool pipe_t = KIND == SC_PRODUCT && std::is_same<ChalT, Fe>::value;
     const bool pipe = pipe_t && pipe_tail_enabled() && !io.xch && !dynamic && !io.dyn_nv && (!in_src || std::is_same<SrcT, Fe>::value);
     if (pipe) {
-        if constexpr (pipe_t) sc_tail_product_pipe_kernel<<<1, c->polite ? PIPE_THREADS / 2 : PIPE_THREADS, 0, c->stream>>>(tb, size, round, num_vars, pending ? 1 : 0, io);
+        if constexpr (pipe_t) sc_tail_product_pipe_kernel<<<1, c->pipe_threads(PIPE_THREADS), 0, c->stream>>>(tb, size, round, num_vars, pending ? 1 : 0, io);
     } else if (in_src)
         sc_tail_kernel<KIND, SrcT, ChalT><<<1, c->single_cta_threads(), 0, c->stream>>>(tb, size, round, num_vars, pending ? 1 : 0, io);
     else
@@ -204,7 +204,7 @@ struct ScriptBuilder {
     void bytes_dev_n(const u32* p) { push(TrOp{TROP_BYTES_DEV_N, 0, 0, 0, p, nullptr}); }
     void run(zkb_ctx* c, TrState* tr) {
         if (!s.nops) return;
-        tr_script_kernel<<<1, 32, 0, c->stream>>>(tr, s);
+        tr_script_kernel<<<1, TRSCRIPT_THREADS, 0, c->stream>>>(tr, s);
         ZKB_LAUNCHED(c);
         s.nops = 0; inl_used = 0;
     }

@@ -255,6 +255,7 @@ inline void qwen_prove_enqueue_inner(zkb_qwen_layer* L, u32 layer_idx, const uin
         L->proofs_enqueued++;
         return;
     }
+    c->trace_clear();                  // a new launch sequence starts (replays above keep the captured one)
     L->pending = new zkb_qwen_layer::Pending();
     if (!graph_ok) {                   // profiling or graphs switched off: launch by launch, keep any captured graph
         qwen_prove_launches(L, *L->pending);
@@ -299,6 +300,7 @@ inline void qwen_prove_enqueue_inner(zkb_qwen_layer* L, u32 layer_idx, const uin
         c->launches = launches0;
         c->rec_reset();
         c->scratch_reset();
+        c->trace_clear();
         delete L->pending;
         L->pending = new zkb_qwen_layer::Pending();
     }

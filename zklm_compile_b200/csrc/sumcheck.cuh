@@ -367,6 +367,7 @@ __global__ void __launch_bounds__(SC_TAIL_THREADS) sc_tail_kernel(ScTables tb, s
     __shared__ __align__(16) unsigned char trbuf[TR_SCRATCH_BYTES];
     __shared__ u32 r_sh[4];
 
+    ZKB_STAMP_BEGIN
     if (io.dyn_nv) { num_vars = io.dyn_nv[0]; size = size_t(1) << num_vars; }
     Tr tr;
     if (threadIdx.x == 0) tr_load(tr, io.tr, trbuf);
@@ -486,6 +487,7 @@ __global__ void __launch_bounds__(SC_TAIL_THREADS) sc_tail_kernel(ScTables tb, s
         }
     }
     (void)WS;
+    ZKB_STAMP_END(io.tr, 2);
 }
 
 }  // namespace zkb

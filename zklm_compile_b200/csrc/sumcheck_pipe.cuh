@@ -106,6 +106,7 @@ __global__ void __launch_bounds__(PIPE_THREADS) sc_tail_product_pipe_kernel(ScTa
     __shared__ u32 csum[2][PIPE_NW];
     __shared__ u32 w_sh[12];
 
+    ZKB_STAMP_BEGIN
     Tr tr;
     if (threadIdx.x == 0) tr_load(tr, io.tr, trbuf);
     Fe r = fe_zero();
@@ -177,6 +178,7 @@ __global__ void __launch_bounds__(PIPE_THREADS) sc_tail_product_pipe_kernel(ScTa
         to_words(fv, io.fin);
         to_words(gv, io.fin + 4);
     }
+    ZKB_STAMP_END(io.tr, 1);
 }
 
 }  // namespace zkb

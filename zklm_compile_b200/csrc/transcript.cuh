@@ -12,6 +12,26 @@
 
 namespace zkb {
 
+#ifdef ZKB_STAMP
+// Experiment build only: start / end time stamps of the serial hash kernels, by transcript.
+struct StampRec { const void* key; unsigned long long t0, t1; unsigned kind, smid; };
+constexpr unsigned STAMP_CAP = 1u << 16;
+__device__ StampRec g_stamps[STAMP_CAP];
+__device__ unsigned g_stamp_n;
+__device__ __forceinline__ unsigned long long stamp_now() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+__device__ __forceinline__ void stamp_put(const void* key, unsigned kind, unsigned long long t0) {
+    unsigned smid; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    unsigned i = atomicAdd(&g_stamp_n, 1u);
+    if (i < STAMP_CAP) g_stamps[i] = StampRec{key, t0, stamp_now(), kind, smid};
+}
+#define ZKB_STAMP_BEGIN unsigned long long stamp_t0 = stamp_now();
+#define ZKB_STAMP_END(key, kind) do { if (threadIdx.x == 0) stamp_put(key, kind, stamp_t0); } while (0)
+#else
+#define ZKB_STAMP_BEGIN
+#define ZKB_STAMP_END(key, kind) do { } while (0)
+#endif
+
+
 // Global-memory image of the stream.  `buf` holds the bytes not yet compressed.
 struct TrState {
     u32 h[8];
@@ -57,17 +77,30 @@ __device__ __noinline__ Sha8 sha256_compress(Sha8 hin, const u32* __restrict__ b
 #pragma unroll
     for (int i = 0; i < 16; i++) w[i] = bswap32(blk[i]);
     u32 a = hin.v[0], b = hin.v[1], c = hin.v[2], d = hin.v[3], e = hin.v[4], f = hin.v[5], g = hin.v[6], h = hin.v[7];
+#define ZKB_SHA_RND8(k0, i)                                                 \
+    ZKB_SHA_RND(a, b, c, d, e, f, g, h, SHA_K[(k0) + (i)] + w[(i)]);         \
+    ZKB_SHA_RND(h, a, b, c, d, e, f, g, SHA_K[(k0) + (i) + 1] + w[(i) + 1]); \
+    ZKB_SHA_RND(g, h, a, b, c, d, e, f, SHA_K[(k0) + (i) + 2] + w[(i) + 2]); \
+    ZKB_SHA_RND(f, g, h, a, b, c, d, e, SHA_K[(k0) + (i) + 3] + w[(i) + 3]); \
+    ZKB_SHA_RND(e, f, g, h, a, b, c, d, SHA_K[(k0) + (i) + 4] + w[(i) + 4]); \
+    ZKB_SHA_RND(d, e, f, g, h, a, b, c, SHA_K[(k0) + (i) + 5] + w[(i) + 5]); \
+    ZKB_SHA_RND(c, d, e, f, g, h, a, b, SHA_K[(k0) + (i) + 6] + w[(i) + 6]); \
+    ZKB_SHA_RND(b, c, d, e, f, g, h, a, SHA_K[(k0) + (i) + 7] + w[(i) + 7]);
+    ZKB_SHA_RND8(0, 0)
+    ZKB_SHA_RND8(0, 8)
+    // Rounds 16..63 as a loop of three 16-round bodies (the schedule window and the renamed working
+    // variables both come back to the same registers every 16 rounds): the loop body stays in the
+    // instruction cache next to whatever else runs on the SM, a fully unrolled compression does not.
+#pragma unroll 1
+    for (int k0 = 16; k0 < 64; k0 += 16) {
 #pragma unroll
-    for (int i = 0; i < 64; i += 8) {
-        if (i >= 16) { ZKB_SHA_SCHED(i); }     ZKB_SHA_RND(a, b, c, d, e, f, g, h, SHA_K[i] + w[i & 15]);
-        if (i >= 16) { ZKB_SHA_SCHED(i + 1); } ZKB_SHA_RND(h, a, b, c, d, e, f, g, SHA_K[i + 1] + w[(i + 1) & 15]);
-        if (i >= 16) { ZKB_SHA_SCHED(i + 2); } ZKB_SHA_RND(g, h, a, b, c, d, e, f, SHA_K[i + 2] + w[(i + 2) & 15]);
-        if (i >= 16) { ZKB_SHA_SCHED(i + 3); } ZKB_SHA_RND(f, g, h, a, b, c, d, e, SHA_K[i + 3] + w[(i + 3) & 15]);
-        if (i >= 16) { ZKB_SHA_SCHED(i + 4); } ZKB_SHA_RND(e, f, g, h, a, b, c, d, SHA_K[i + 4] + w[(i + 4) & 15]);
-        if (i >= 16) { ZKB_SHA_SCHED(i + 5); } ZKB_SHA_RND(d, e, f, g, h, a, b, c, SHA_K[i + 5] + w[(i + 5) & 15]);
-        if (i >= 16) { ZKB_SHA_SCHED(i + 6); } ZKB_SHA_RND(c, d, e, f, g, h, a, b, SHA_K[i + 6] + w[(i + 6) & 15]);
-        if (i >= 16) { ZKB_SHA_SCHED(i + 7); } ZKB_SHA_RND(b, c, d, e, f, g, h, a, SHA_K[i + 7] + w[(i + 7) & 15]);
+        for (int j = 0; j < 8; j++) ZKB_SHA_SCHED(j);
+        ZKB_SHA_RND8(k0, 0)
+#pragma unroll
+        for (int j = 8; j < 16; j++) ZKB_SHA_SCHED(j);
+        ZKB_SHA_RND8(k0, 8)
     }
+#undef ZKB_SHA_RND8
     Sha8 o;
     o.v[0] = hin.v[0] + a; o.v[1] = hin.v[1] + b; o.v[2] = hin.v[2] + c; o.v[3] = hin.v[3] + d;
     o.v[4] = hin.v[4] + e; o.v[5] = hin.v[5] + f; o.v[6] = hin.v[6] + g; o.v[7] = hin.v[7] + h;
@@ -81,16 +114,19 @@ __device__ __noinline__ Sha8 sha256_compress(Sha8 hin, const u32* __restrict__ b
 constexpr int SHA_KW_STRIDE = 65;    // padded so 32 lanes writing their own row do not share a bank
 __device__ __noinline__ Sha8 sha256_rounds(Sha8 hin, const u32* __restrict__ kw) {
     u32 a = hin.v[0], b = hin.v[1], c = hin.v[2], d = hin.v[3], e = hin.v[4], f = hin.v[5], g = hin.v[6], h = hin.v[7];
+#pragma unroll 1
+    for (int i = 0; i < 64; i += 16) {
 #pragma unroll
-    for (int i = 0; i < 64; i += 8) {
-        ZKB_SHA_RND(a, b, c, d, e, f, g, h, kw[i]);
-        ZKB_SHA_RND(h, a, b, c, d, e, f, g, kw[i + 1]);
-        ZKB_SHA_RND(g, h, a, b, c, d, e, f, kw[i + 2]);
-        ZKB_SHA_RND(f, g, h, a, b, c, d, e, kw[i + 3]);
-        ZKB_SHA_RND(e, f, g, h, a, b, c, d, kw[i + 4]);
-        ZKB_SHA_RND(d, e, f, g, h, a, b, c, kw[i + 5]);
-        ZKB_SHA_RND(c, d, e, f, g, h, a, b, kw[i + 6]);
-        ZKB_SHA_RND(b, c, d, e, f, g, h, a, kw[i + 7]);
+        for (int j = 0; j < 16; j += 8) {
+            ZKB_SHA_RND(a, b, c, d, e, f, g, h, kw[i + j]);
+            ZKB_SHA_RND(h, a, b, c, d, e, f, g, kw[i + j + 1]);
+            ZKB_SHA_RND(g, h, a, b, c, d, e, f, kw[i + j + 2]);
+            ZKB_SHA_RND(f, g, h, a, b, c, d, e, kw[i + j + 3]);
+            ZKB_SHA_RND(e, f, g, h, a, b, c, d, kw[i + j + 4]);
+            ZKB_SHA_RND(d, e, f, g, h, a, b, c, kw[i + j + 5]);
+            ZKB_SHA_RND(c, d, e, f, g, h, a, b, kw[i + j + 6]);
+            ZKB_SHA_RND(b, c, d, e, f, g, h, a, kw[i + j + 7]);
+        }
     }
     Sha8 o;
     o.v[0] = hin.v[0] + a; o.v[1] = hin.v[1] + b; o.v[2] = hin.v[2] + c; o.v[3] = hin.v[3] + d;
@@ -304,6 +340,60 @@ __device__ __forceinline__ void tr_absorb_stream_warp(Tr& tr, u32 total, Load lo
     for (u32 j = lane; j < rest; j += 32) bufw[have + j] = load(pos + j);
     __syncwarp();
     if (lane == 0) { tr.buflen = (have + rest) * 4; tr.total += (u64)total * 4; }
+}
+
+// The same absorb for a CTA of two warps with the loads and the schedule expansion taken off the
+// hash chain: while lane 0 of warp 0 runs the rounds of one batch (up to 32 blocks, about 35 us),
+// warp 1 fetches the next batch's words and expands its schedules into the other half of the
+// double-buffered scratch; the two meet at a CTA barrier per batch.  Called by all 64 threads with
+// identical arguments; `tr` is meaningful in thread 0; `bufw` is the stream buffer (shared
+// memory) that tr.buf points to; tile holds 2 x 512 words, kw 2 x 32 x SHA_KW_STRIDE, bc 1 word.
+template <class Load>
+__device__ __forceinline__ void tr_absorb_stream_2w(Tr& tr, u32 total, Load load, u32* bufw, u32* tile, u32* kw, u32* bc) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) bc[0] = tr.buflen;
+    __syncthreads();                   // also: thread 0's earlier writes to the stream buffer become visible
+    const u32 buflen = bc[0];
+    if (buflen & 3) {                  // byte-misaligned stream: plain path on warp 0
+        if (warp == 0) tr_absorb_stream_warp(tr, total, load, tile, kw);
+        __syncthreads();
+        return;
+    }
+    auto produce = [&](u32 slot, u32 have, u32 pos, u32 nb) {   // warp 1: words [pos, ...) after `have` buffered ones
+        u32* t = tile + slot * 512;
+        u32* k = kw + slot * 32 * SHA_KW_STRIDE;
+        for (u32 j = lane; j < nb * 16; j += 32) t[j] = bswap32(j < have ? bufw[j] : load(pos + j - have));
+        __syncwarp();
+        if ((u32)lane < nb) sha256_expand_kw(t + lane * 16, k + lane * SHA_KW_STRIDE);
+    };
+    u32 have = buflen >> 2, pos = 0;
+    u32 nb = (have + total) / 16;
+    if (nb > 32) nb = 32;
+    if (nb && warp == 1) produce(0, have, 0, nb);
+    __syncthreads();
+    u32 slot = 0;
+    while (nb) {
+        const u32 next_pos = pos + nb * 16 - have;
+        u32 next_nb = (total - next_pos) / 16;
+        if (next_nb > 32) next_nb = 32;
+        if (warp == 1) {
+            if (next_nb) produce(slot ^ 1, 0, next_pos, next_nb);
+        } else if (lane == 0) {
+            const u32* k = kw + slot * 32 * SHA_KW_STRIDE;
+            Sha8 h;
+#pragma unroll
+            for (int i = 0; i < 8; i++) h.v[i] = tr.h[i];
+            for (u32 b = 0; b < nb; b++) h = sha256_rounds(h, k + b * SHA_KW_STRIDE);
+#pragma unroll
+            for (int i = 0; i < 8; i++) tr.h[i] = h.v[i];
+        }
+        __syncthreads();
+        pos = next_pos; have = 0; nb = next_nb; slot ^= 1;
+    }
+    const u32 rest = total - pos;      // fewer than 16 - have words: they stay in the stream buffer
+    if (warp == 0) for (u32 j = lane; j < rest; j += 32) bufw[have + j] = load(pos + j);
+    if (threadIdx.x == 0) { tr.buflen = (have + rest) * 4; tr.total += (u64)total * 4; }
+    __syncthreads();
 }
 
 }  // namespace zkb

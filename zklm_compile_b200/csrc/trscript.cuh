@@ -71,28 +71,29 @@ struct TrScript {
     u32 nops;
 };
 
-__global__ void __launch_bounds__(32) tr_script_kernel(TrState* st, TrScript sc) {
+constexpr int TRSCRIPT_THREADS = 64;      // warp 0 advances the transcript, warp 1 prefetches and expands (see tr_absorb_stream_2w)
+__global__ void __launch_bounds__(TRSCRIPT_THREADS) tr_script_kernel(TrState* st, TrScript sc) {
     __shared__ __align__(16) unsigned char trbuf[TR_SCRATCH_BYTES];
-    __shared__ u32 tile[512];
-    __shared__ u32 kw[32 * SHA_KW_STRIDE];
-    const int lane = threadIdx.x;
+    __shared__ u32 tile[2 * 512];
+    __shared__ u32 kw[2 * 32 * SHA_KW_STRIDE];
+    __shared__ u32 bc[1];
+    ZKB_STAMP_BEGIN
     Tr tr;
     tr.buf = trbuf; tr.buflen = 0; tr.total = 0;
-    if (lane == 0) tr_load(tr, st, trbuf);
-    __syncwarp();
+    if (threadIdx.x == 0) tr_load(tr, st, trbuf);
     for (u32 o = 0; o < sc.nops; o++) {
         const TrOp& op = sc.ops[o];
         if (op.kind == TROP_BYTES) {
-            if (lane == 0) tr_absorb_bytes(tr, sc.inl + op.inline_off, op.n);
+            if (threadIdx.x == 0) tr_absorb_bytes(tr, sc.inl + op.inline_off, op.n);
         } else if (op.kind == TROP_SQUEEZE) {
-            if (lane == 0) {
+            if (threadIdx.x == 0) {
                 u32* dst = const_cast<u32*>(op.ptr);
                 for (u32 i = 0; i < op.n; i++) dst[i] = tr_squeeze(tr);
             }
         } else if (op.kind == TROP_WORD_DEV_N) {
-            if (lane == 0) tr_absorb_u32(tr, op.ptr[0]);
+            if (threadIdx.x == 0) tr_absorb_u32(tr, op.ptr[0]);
         } else if (op.kind == TROP_BYTES_DEV_N) {
-            if (lane == 0) {
+            if (threadIdx.x == 0) {
                 u32 nb = op.ptr[0];
                 if (nb > 255) nb = 255;
                 tr_absorb_bytes(tr, reinterpret_cast<const unsigned char*>(op.ptr + 1), nb);
@@ -103,14 +104,15 @@ __global__ void __launch_bounds__(32) tr_script_kernel(TrState* st, TrScript sc)
             const u32 kind = op.kind, n = op.n;
             const u32* p1 = op.ptr;
             const u32* p2 = op.ptr2;
-            tr_absorb_stream_warp(tr, total, [=](u32 g) -> u32 {
+            tr_absorb_stream_2w(tr, total, [=](u32 g) -> u32 {
                 if (kind == TROP_WORDS_DEV) return g < n ? p1[g] : 0u;
                 if (kind == TROP_PAIRS_DEV) return (g & 1) ? p2[g >> 1] : p1[g >> 1];
                 return p1[g];
-            }, tile, kw);
+            }, reinterpret_cast<u32*>(trbuf), tile, kw, bc);
         }
     }
-    if (lane == 0) tr_store(tr, st);
+    if (threadIdx.x == 0) tr_store(tr, st);
+    ZKB_STAMP_END(st, 0);
 }
 
 // blake3(prefix || words) by one CTA, result to `root_out` (8 words); optionally absorbed into

@@ -118,6 +118,52 @@ int32_t zkb_profile_read(zkb_ctx* c, float* ms, size_t cap, size_t* n) {
     });
 }
 
+#ifdef ZKB_STAMP
+// Experiment build only: copies the stamp records out (5 x u64 each: key, t0, t1, kind, smid) and resets the ring.
+extern "C" int32_t zkb_dbg_stamps(uint64_t* out, size_t cap, size_t* n) {
+    unsigned cnt = 0;
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(&cnt, zkb::g_stamp_n, 4);
+    if (cnt > zkb::STAMP_CAP) cnt = zkb::STAMP_CAP;
+    std::vector<zkb::StampRec> h(cnt);
+    if (cnt) cudaMemcpyFromSymbol(h.data(), zkb::g_stamps, sizeof(zkb::StampRec) * cnt);
+    size_t k = 0;
+    for (; k < cnt && k < cap; k++) {
+        out[5 * k] = (uint64_t)h[k].key; out[5 * k + 1] = h[k].t0; out[5 * k + 2] = h[k].t1; out[5 * k + 3] = h[k].kind; out[5 * k + 4] = h[k].smid;
+    }
+    *n = k;
+    unsigned zero = 0;
+    cudaMemcpyToSymbol(zkb::g_stamp_n, &zero, 4);
+    return 0;
+}
+#endif
+int32_t zkb_trace_enable(zkb_ctx* c, int32_t on) {
+    if (!c) return ZKB_E_ARG;
+    c->trace = on != 0;
+    c->trace_clear();
+    return ZKB_OK;
+}
+int32_t zkb_trace_dump(zkb_ctx* c, zkb_ctx* base, const char* path) {
+    if (!c || !path) return ZKB_E_ARG;
+    ZKB_TRY(c, {
+        c->use();
+        ZKB_CUDA(cudaStreamSynchronize(c->stream));
+        FILE* f = fopen(path, "w");
+        if (!f) throw zkb::ArgFail{ZKB_E_ARG, "cannot open the trace file"};
+        const zkb_ctx* b = (base && !base->trace_log.empty()) ? base : c;
+        fprintf(f, "index,site,ms\n");
+        for (size_t i = 0; i < c->trace_log.size(); i++) {
+            float t = 0;
+            cudaError_t e = cudaEventElapsedTime(&t, b->trace_log[0].ev, c->trace_log[i].ev);
+            if (e != cudaSuccess) { cudaGetLastError(); t = -1.f; }
+            const char* file = c->trace_log[i].file;
+            const char* slash = strrchr(file, '/');
+            fprintf(f, "%zu,%s:%d,%.4f\n", i, slash ? slash + 1 : file, c->trace_log[i].line, t);
+        }
+        fclose(f);
+    });
+}
+
 int32_t zkb_profile_ranges(zkb_ctx* c, double* ms, double* bytes, uint64_t* count) {
     if (!c || !ms || !bytes || !count) return ZKB_E_ARG;
     ZKB_TRY(c, {

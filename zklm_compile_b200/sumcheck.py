@@ -96,6 +96,14 @@ class Context:
         check(self.h, _lib.lib().zkb_profile_ranges(self.h, ms, by, cnt))
         return {"fold_eq_matvec": (ms[0], by[0], cnt[0]), "matvec_forward": (ms[1], by[1], cnt[1])}
 
+    def trace(self, on: bool):
+        """Launch trace: an event behind every launch of this context (also inside layer graphs)."""
+        check(self.h, _lib.lib().zkb_trace_enable(self.h, C.c_int32(1 if on else 0)))
+
+    def trace_dump(self, path: str, base: "Context | None" = None):
+        """Write `index,site,ms` lines; ms counts from the first traced launch of `base` (default: own)."""
+        check(self.h, _lib.lib().zkb_trace_dump(self.h, base.h if base is not None else None, path.encode()))
+
     @property
     def launches(self) -> int:
         return int(_lib.lib().zkb_launch_count(self.h))
