@@ -25,17 +25,29 @@ __device__ __forceinline__ u32 sqrt31(u32 a) {
 // Single CTA.  out[i] = gamma[i] * x'[i] * r with r = sqrt(d / sum x'^2); x' = x except that
 // x'[0] = x[0] + delta for the first delta in 0, +1, -1, +2, -2, ... that makes d / sum_sq a
 // quadratic residue.  scalars[0] = delta (two's complement), scalars[1] = sum_sq of x'.
-// Vectors are written zero-padded to n_pad.
+// Vectors are written zero-padded to n_pad.  With `addend`, the input is x + addend (the residual
+// add in front of the second norm), which is also written, zero-padded, to sum_out; every thread
+// reads back only elements it wrote itself.
 __global__ void __launch_bounds__(1024) rmsnorm_forward_kernel(const u32* __restrict__ x, const u32* __restrict__ gamma, u32 d, u32 n_pad,
-                                                               u32* out, u32* x_used, u32* scalars, u32* status) {
+                                                               u32* out, u32* x_used, u32* scalars, u32* status,
+                                                               const u32* __restrict__ addend = nullptr, u32* sum_out = nullptr) {
     __shared__ u32 red[32];
     __shared__ u32 sh[3];   // r, x0', ok
     u32 acc = 0;
-    for (u32 i = threadIdx.x; i < d; i += blockDim.x) acc = add31(acc, mul31(x[i], x[i]));
+    if (addend) {
+        for (u32 i = threadIdx.x; i < n_pad; i += blockDim.x) {
+            const u32 v = i < d ? add31(x[i], addend[i]) : 0u;
+            sum_out[i] = v;
+            acc = add31(acc, mul31(v, v));
+        }
+    } else {
+        for (u32 i = threadIdx.x; i < d; i += blockDim.x) acc = add31(acc, mul31(x[i], x[i]));
+    }
     u32 w[1] = {acc};
     block_sum_words<1>(w, red);
+    const u32* xin = addend ? sum_out : x;     // plain pointer: sum_out was written above, by the same threads that read it
     if (threadIdx.x == 0) {
-        const u32 sum_sq = w[0], x0 = x[0];
+        const u32 sum_sq = w[0], x0 = xin[0];
         u32 ok = 0, r = 0, nx0 = x0, ssq = sum_sq;
         int delta = 0;
         if (sum_sq != 0) {
@@ -61,7 +73,7 @@ __global__ void __launch_bounds__(1024) rmsnorm_forward_kernel(const u32* __rest
     __syncthreads();
     const u32 r = sh[0], nx0 = sh[1];
     for (u32 i = threadIdx.x; i < n_pad; i += blockDim.x) {
-        u32 xi = i < d ? (i == 0 ? nx0 : x[i]) : 0u;
+        u32 xi = i < d ? (i == 0 ? nx0 : xin[i]) : 0u;
         x_used[i] = xi;
         out[i] = i < d ? mul31(mul31(gamma[i], xi), r) : 0u;
     }
@@ -70,11 +82,13 @@ __global__ void __launch_bounds__(1024) rmsnorm_forward_kernel(const u32* __rest
 __device__ __forceinline__ long long centered(u32 v) { return v > ZKB_P / 2 ? (long long)v - (long long)ZKB_P : (long long)v; }
 __device__ __forceinline__ u32 to_field_i64(long long x) { return x >= 0 ? (u32)((unsigned long long)x % ZKB_P) : sub31(0u, (u32)((unsigned long long)(-x) % ZKB_P)); }
 
-// q = requantize(raw); t = table[q]; prod = other . t  (all zero-padded to n_pad), in two launches,
-// so that the expensive part (64-bit divisions, table gathers) can use the whole GPU: first the
-// largest magnitude (one CTA, loads only), then the element-wise part.
-__global__ void __launch_bounds__(1024) absmax_kernel(const u32* __restrict__ raw, u32 n, unsigned long long* out) {
-    __shared__ unsigned long long mx_s[32];
+// q = requantize(raw); t = table[q]; prod = other . t  (all zero-padded to n_pad).
+// Every CTA first finds the largest magnitude of the whole vector by itself (n is a few thousand
+// words, read from L2), so no separate single-CTA launch sits in the forward chain; CTA 0 records it.
+__global__ void __launch_bounds__(256) requant_lookup_mul_apply_kernel(const u32* __restrict__ raw, u32 n, u32 n_pad, unsigned long long* max_abs_out,
+                                                const u32* __restrict__ table_out, u32 n_table, const u32* __restrict__ other,
+                                                u32* q_out, u32* t_out, u32* prod_out, u32* status) {
+    __shared__ unsigned long long mx_s[8];
     unsigned long long mx = 1;
     for (u32 i = threadIdx.x; i < n; i += blockDim.x) {
         long long s = centered(raw[i]);
@@ -87,16 +101,10 @@ __global__ void __launch_bounds__(1024) absmax_kernel(const u32* __restrict__ ra
     }
     if ((threadIdx.x & 31) == 0) mx_s[threadIdx.x >> 5] = mx;
     __syncthreads();
-    if (threadIdx.x == 0) {
-        unsigned long long m = 1;
-        for (u32 wv = 0; wv < (blockDim.x + 31) / 32; wv++) m = mx_s[wv] > m ? mx_s[wv] : m;
-        *out = m;
-    }
-}
-__global__ void requant_lookup_mul_apply_kernel(const u32* __restrict__ raw, u32 n, u32 n_pad, const unsigned long long* __restrict__ max_abs_p,
-                                                const u32* __restrict__ table_out, u32 n_table, const u32* __restrict__ other,
-                                                u32* q_out, u32* t_out, u32* prod_out, u32* status) {
-    const long long max_abs = (long long)*max_abs_p;
+    mx = 1;
+    for (u32 wv = 0; wv < (blockDim.x + 31) / 32; wv++) mx = mx_s[wv] > mx ? mx_s[wv] : mx;
+    if (blockIdx.x == 0 && threadIdx.x == 0) *max_abs_out = mx;
+    const long long max_abs = (long long)mx;
     for (u32 i = blockIdx.x * blockDim.x + threadIdx.x; i < n_pad; i += gridDim.x * blockDim.x) {
         u32 q = 0, t = 0, pr = 0;
         if (i < n) {

@@ -133,15 +133,13 @@ inline void qwen_forward(zkb_qwen_layer* L) {
         ZKB_CUDA(cudaMemcpyAsync(L->attn_out, L->v, (size_t)aodp * 4, cudaMemcpyDeviceToDevice, c->stream));
     }
     unsigned long long* mx = reinterpret_cast<unsigned long long*>(L->n1_scalars + 4);   // two 8-byte slots after the scalars
-    absmax_kernel<<<1, c->single_cta_threads(), 0, c->stream>>>(L->g_raw, aod, mx);
-    ZKB_LAUNCHED(c);
     requant_lookup_mul_apply_kernel<<<grid_for(c, aodp), 256, 0, c->stream>>>(L->g_raw, aod, aodp, mx, L->sigmoid, L->n_table, L->attn_out,
                                                                              L->g_q, L->g_sig, L->gated_attn, c->status);
     ZKB_LAUNCHED(c);
     matvec_forward(c, L->w[W_O], L->gated_attn, dm, aod, L->gated_out, dmp, false);
-    add_vec_kernel<<<grid_for(c, dmp), 256, 0, c->stream>>>(L->x, L->gated_out, dm, dmp, L->h);
-    ZKB_LAUNCHED(c);
-    rmsnorm_forward_kernel<<<1, c->single_cta_threads(), 0, c->stream>>>(L->h, L->w[W_NORM2], dm, dmp, L->norm2_out, L->norm2_x, L->n2_scalars, c->status);
+    // h = x + gated_out and the second norm in one launch
+    rmsnorm_forward_kernel<<<1, c->single_cta_threads(), 0, c->stream>>>(L->x, L->w[W_NORM2], dm, dmp, L->norm2_out, L->norm2_x, L->n2_scalars, c->status,
+                                                                        L->gated_out, L->h);
     ZKB_LAUNCHED(c);
     {
         const u32* Wm[2] = {L->w[W_GATE], L->w[W_UP]};
@@ -150,8 +148,6 @@ inline void qwen_forward(zkb_qwen_layer* L) {
         matvec_forward_batch(c, 2, Wm, ym, mm, L->norm2_out, dm);
     }
     unsigned long long* mx2 = reinterpret_cast<unsigned long long*>(L->n2_scalars + 4);
-    absmax_kernel<<<1, c->single_cta_threads(), 0, c->stream>>>(L->gate_raw, d.d_ff, mx2);
-    ZKB_LAUNCHED(c);
     requant_lookup_mul_apply_kernel<<<grid_for(c, dffp), 256, 0, c->stream>>>(L->gate_raw, d.d_ff, dffp, mx2, L->silu, L->n_table, L->up,
                                                                               L->gate_q, L->gate_silu, L->swiglu, c->status);
     ZKB_LAUNCHED(c);
