@@ -10,7 +10,8 @@ import os
 import subprocess
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libzkb200.so")
+# ZKB200_LIB selects another build of the same library (e.g. an instrumented one); there is still no fallback.
+LIB_PATH = os.environ.get("ZKB200_LIB") or os.path.join(_HERE, "libzkb200.so")
 HEADER_PATH = os.path.join(os.path.dirname(_HERE), "include", "zkb200.h")
 
 u32p = C.POINTER(C.c_uint32)

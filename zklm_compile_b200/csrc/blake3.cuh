@@ -23,14 +23,18 @@ __device__ __forceinline__ u32 b3_rotr(u32 x, int n) { return __funnelshift_r(x,
     a = a + b + (my); d = b3_rotr(d ^ a, 8);  \
     c = c + d;        b = b3_rotr(b ^ c, 7);
 
-// Compression; writes the first 8 output words (the chaining value / the first 32 digest bytes).
-__device__ __noinline__ void b3_compress(const u32* cv, const u32* m, u32 counter_lo, u32 counter_hi, u32 blen, u32 flags, u32* out) {
-    u32 s0 = cv[0], s1 = cv[1], s2 = cv[2], s3 = cv[3], s4 = cv[4], s5 = cv[5], s6 = cv[6], s7 = cv[7];
+// Compression; returns the first 8 output words (the chaining value / the first 32 digest bytes).
+// Chaining value and message travel by value, in registers: through pointers they would live in
+// local memory, one more round trip per block for a thread that hashes a chunk alone.
+struct B3Cv { u32 v[8]; };
+struct B3Msg { u32 w[16]; };
+__device__ __noinline__ B3Cv b3_compress(B3Cv cv, B3Msg m, u32 counter_lo, u32 counter_hi, u32 blen, u32 flags) {
+    u32 s0 = cv.v[0], s1 = cv.v[1], s2 = cv.v[2], s3 = cv.v[3], s4 = cv.v[4], s5 = cv.v[5], s6 = cv.v[6], s7 = cv.v[7];
     u32 s8 = 0x6a09e667u, s9 = 0xbb67ae85u, s10 = 0x3c6ef372u, s11 = 0xa54ff53au;
     u32 s12 = counter_lo, s13 = counter_hi, s14 = blen, s15 = flags;
     u32 w[16];
 #pragma unroll
-    for (int i = 0; i < 16; i++) w[i] = m[i];
+    for (int i = 0; i < 16; i++) w[i] = m.w[i];
 #pragma unroll
     for (int r = 0; r < 7; r++) {
         B3_G(s0, s4, s8, s12, w[0], w[1]);   B3_G(s1, s5, s9, s13, w[2], w[3]);
@@ -43,8 +47,10 @@ __device__ __noinline__ void b3_compress(const u32* cv, const u32* m, u32 counte
             for (int i = 0; i < 16; i++) w[i] = t[i];
         }
     }
-    out[0] = s0 ^ s8;  out[1] = s1 ^ s9;  out[2] = s2 ^ s10; out[3] = s3 ^ s11;
-    out[4] = s4 ^ s12; out[5] = s5 ^ s13; out[6] = s6 ^ s14; out[7] = s7 ^ s15;
+    B3Cv o;
+    o.v[0] = s0 ^ s8;  o.v[1] = s1 ^ s9;  o.v[2] = s2 ^ s10; o.v[3] = s3 ^ s11;
+    o.v[4] = s4 ^ s12; o.v[5] = s5 ^ s13; o.v[6] = s6 ^ s14; o.v[7] = s7 ^ s15;
+    return o;
 }
 
 struct B3Prefix { unsigned char b[64]; u32 len; };
@@ -71,45 +77,81 @@ __device__ __forceinline__ u32 b3_stream_word(const B3Prefix& pre, const u32* __
     return w;
 }
 
-// Chaining value of chunk `ci` (or the root digest when it is the only chunk).
-__device__ inline void b3_chunk_cv(const B3Prefix& pre, const u32* __restrict__ words, size_t total, size_t ci, bool only_chunk, u32* out8) {
-    u32 cv[8];
+// The 16 message words of the block that starts at stream position bs.  A block that lies wholly
+// inside the words (all but the first and the last of a vector) is 17 independent loads and 16
+// independent funnel shifts; per-word position arithmetic would be a dependent chain of its own,
+// and a lone thread pays about 11 cycles for every dependent instruction.
+__device__ __forceinline__ B3Msg b3_block_words(const B3Prefix& pre, const u32* __restrict__ words, size_t bs, size_t total) {
+    B3Msg m;
+    if (bs >= pre.len && bs + 64 <= total) {
+        const size_t d = bs - pre.len;
+        const u32 sh = (u32)(d & 3) * 8;
+        const u32* p = words + (d >> 2);
+        if (sh == 0) {
 #pragma unroll
-    for (int i = 0; i < 8; i++) cv[i] = B3_IV[i];
+            for (int k = 0; k < 16; k++) m.w[k] = p[k];
+        } else {
+            u32 t[17];
+#pragma unroll
+            for (int k = 0; k < 17; k++) t[k] = p[k];      // p[16] exists: byte d + 63 is inside the words
+#pragma unroll
+            for (int k = 0; k < 16; k++) m.w[k] = __funnelshift_r(t[k], t[k + 1], sh);
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < 16; k++) m.w[k] = b3_stream_word(pre, words, bs + 4 * k, total);
+    }
+    return m;
+}
+
+// Chaining value of chunk `ci` (or the root digest when it is the only chunk).  The message words
+// of block b + 1 are fetched before block b is compressed, so that the 16 blocks of a chunk cost
+// one exposed memory latency, not sixteen.
+__device__ inline void b3_chunk_cv(const B3Prefix& pre, const u32* __restrict__ words, size_t total, size_t ci, bool only_chunk, u32* out8) {
+    B3Cv cv;
+#pragma unroll
+    for (int i = 0; i < 8; i++) cv.v[i] = B3_IV[i];
     size_t start = ci * 1024;
     size_t len = total - start < 1024 ? total - start : 1024;
     u32 nblocks = len == 0 ? 1u : (u32)((len + 63) / 64);
+    B3Msg cur = b3_block_words(pre, words, start, total), nxt = cur;
     for (u32 b = 0; b < nblocks; b++) {
-        u32 m[16];
-        size_t bs = start + (size_t)b * 64;
-#pragma unroll
-        for (int k = 0; k < 16; k++) m[k] = b3_stream_word(pre, words, bs + 4 * k, total);
+        if (b + 1 < nblocks) nxt = b3_block_words(pre, words, start + (size_t)(b + 1) * 64, total);
         u32 blen = (u32)(len - (size_t)b * 64 < 64 ? len - (size_t)b * 64 : 64);
         u32 fl = (b == 0 ? B3_CHUNK_START : 0) | (b + 1 == nblocks ? B3_CHUNK_END : 0);
         if (only_chunk && b + 1 == nblocks) fl |= B3_ROOT;
-        b3_compress(cv, m, (u32)ci, (u32)(ci >> 32), blen, fl, cv);
+        cv = b3_compress(cv, cur, (u32)ci, (u32)(ci >> 32), blen, fl);
+        cur = nxt;
     }
 #pragma unroll
-    for (int i = 0; i < 8; i++) out8[i] = cv[i];
+    for (int i = 0; i < 8; i++) out8[i] = cv.v[i];
 }
 
 __device__ __forceinline__ void b3_parent(const u32* left8, const u32* right8, bool root, u32* out8) {
-    u32 m[16], cv[8];
+    B3Msg m;
+    B3Cv cv;
 #pragma unroll
-    for (int i = 0; i < 8; i++) { m[i] = left8[i]; m[8 + i] = right8[i]; cv[i] = B3_IV[i]; }
-    b3_compress(cv, m, 0, 0, 64, B3_PARENT | (root ? B3_ROOT : 0), out8);
+    for (int i = 0; i < 8; i++) { m.w[i] = left8[i]; m.w[8 + i] = right8[i]; cv.v[i] = B3_IV[i]; }
+    cv = b3_compress(cv, m, 0, 0, 64, B3_PARENT | (root ? B3_ROOT : 0));
+#pragma unroll
+    for (int i = 0; i < 8; i++) out8[i] = cv.v[i];
 }
 
-// Whole hash by one CTA: `cvs` is scratch for n_chunks * 8 words (shared or global memory).
-// Result (8 LE words = 32 digest bytes) in cvs[0..8) after the call; all threads must call.
+// Whole hash by one CTA: `cvs` is scratch for n_chunks * 8 words in global memory.  Result (8 LE
+// words = 32 digest bytes) in cvs[0..8) after the call; all threads must call.  Up to
+// B3_SMEM_CHUNKS chunk values are merged in shared memory (a level is then two CTA barriers, not
+// two round trips to L2).
+constexpr int B3_SMEM_CHUNKS = 128;
 __device__ inline void b3_hash_block(const B3Prefix& pre, const u32* __restrict__ words, size_t n_words, u32* cvs) {
+    __shared__ u32 cvs_sh[B3_SMEM_CHUNKS * 8];
     size_t total = pre.len + n_words * 4;
     size_t n_chunks = total == 0 ? 1 : (total + 1023) / 1024;
+    u32* lv = n_chunks <= (size_t)B3_SMEM_CHUNKS ? cvs_sh : cvs;
     for (size_t c = threadIdx.x; c < n_chunks; c += blockDim.x) {
         u32 cv[8];
         b3_chunk_cv(pre, words, total, c, n_chunks == 1, cv);
 #pragma unroll
-        for (int i = 0; i < 8; i++) cvs[c * 8 + i] = cv[i];
+        for (int i = 0; i < 8; i++) lv[c * 8 + i] = cv[i];
     }
     __syncthreads();
     size_t n = n_chunks;
@@ -121,20 +163,24 @@ __device__ inline void b3_hash_block(const B3Prefix& pre, const u32* __restrict_
             size_t t = base + threadIdx.x;
             bool act = t < next;
             if (act) {
-                if (t < pairs) b3_parent(cvs + 2 * t * 8, cvs + (2 * t + 1) * 8, next == 1, outv);
+                if (t < pairs) b3_parent(lv + 2 * t * 8, lv + (2 * t + 1) * 8, next == 1, outv);
                 else {
 #pragma unroll
-                    for (int i = 0; i < 8; i++) outv[i] = cvs[2 * t * 8 + i];
+                    for (int i = 0; i < 8; i++) outv[i] = lv[2 * t * 8 + i];
                 }
             }
             __syncthreads();
             if (act) {
 #pragma unroll
-                for (int i = 0; i < 8; i++) cvs[t * 8 + i] = outv[i];
+                for (int i = 0; i < 8; i++) lv[t * 8 + i] = outv[i];
             }
             __syncthreads();
         }
         n = next;
+    }
+    if (lv != cvs) {
+        if (threadIdx.x < 8) cvs[threadIdx.x] = lv[threadIdx.x];
+        __syncthreads();
     }
 }
 
