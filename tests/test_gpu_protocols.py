@@ -246,6 +246,34 @@ def _check_layer(ctx, cfg, weights, x, silu, sigm, idx):
     layer.close()
 
 
+def test_launch_trace_of_a_replayed_layer_graph(tmp_path):
+    """With the launch trace on, a layer proof has the same bytes, and the dump holds one line per
+    traced launch of the captured graph with non-decreasing times (the events are event-record
+    nodes of the graph, refreshed by every replay)."""
+    G = load_qwen_golden()
+    case = G["cases"][0]
+    c = zk.Context(0)
+    c.trace(True)
+    ih = hashlib.sha256(b"model-input").digest()
+    layer = zq.QwenLayer(c, case["config"], case["weights"], c.upload(G["silu"]), c.upload(G["sigmoid"]))
+    x = np.array(case["x"], np.uint32)
+    layer.forward(x)
+    _, eproof, _ = O.qwen_layer_prove(case["config"], case["weights"], x, G["silu"], G["sigmoid"], 0, ih)
+    for _ in range(3):                      # launch by launch, captured, replayed
+        assert layer.prove(0, ih) == eproof
+    path = str(tmp_path / "trace.csv")
+    c.trace_dump(path)
+    lines = open(path).read().strip().split("\n")
+    assert lines[0] == "index,site,ms"
+    rows = [l.split(",") for l in lines[1:]]
+    assert len(rows) > 50 and all(".cuh:" in r[1] or ".cu:" in r[1] for r in rows)
+    proof_rows = [float(r[2]) for r in rows if float(r[2]) >= 0]
+    assert proof_rows == sorted(proof_rows) and proof_rows[-1] > proof_rows[0]
+    c.trace(False)
+    layer.close()
+    c.close()
+
+
 def test_qwen_layer_golden_cases(ctx):
     G = load_qwen_golden()
     for ci, case in enumerate(G["cases"]):
