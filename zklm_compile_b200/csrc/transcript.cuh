@@ -212,15 +212,22 @@ __device__ __forceinline__ void tr_absorb_u32(Tr& t, u32 v) {
 // plus at most one compression, instead of N rounds of per-byte bookkeeping.
 template <int N>
 __device__ __forceinline__ void tr_absorb_words(Tr& t, const u32* w) {
+    static_assert(N <= 16, "at most one block boundary inside");
     if ((t.buflen & 3) == 0) {
         u32* bw = reinterpret_cast<u32*>(t.buf);
-        u32 pos = t.buflen >> 2;
+        const u32 pos = t.buflen >> 2;
+        const u32 room = 16 - pos;                     // words that still fit into the open block (1..16)
 #pragma unroll
-        for (int i = 0; i < N; i++) {
-            bw[pos++] = w[i];
-            if (pos == 16) { t.buflen = 64; tr_flush_block(t); pos = 0; }
+        for (int i = 0; i < N; i++) if ((u32)i < room) bw[pos + i] = w[i];
+        if ((u32)N >= room) {
+            t.buflen = 64;
+            tr_flush_block(t);
+#pragma unroll
+            for (int i = 0; i < N; i++) if ((u32)i >= room) bw[i - room] = w[i];
+            t.buflen = ((u32)N - room) << 2;
+        } else {
+            t.buflen = (pos + N) << 2;
         }
-        t.buflen = pos << 2;
         t.total += 4 * N;
     } else {
 #pragma unroll
@@ -237,19 +244,29 @@ __device__ inline void tr_absorb_bytes(Tr& t, const unsigned char* p, u32 n) {
     for (u32 i = 0; i < n; i++) tr_absorb_byte(t, p[i]);
 }
 
-// Pad, compress, and restart the stream with the 32-byte digest as its first bytes.
+// Pad, compress, and restart the stream with the 32-byte digest as its first bytes.  Written
+// without loops whose trip count depends on the position: on a lone thread every dependent
+// instruction costs about 11 cycles, so the zero fill is fourteen predicated stores, not a counted loop.
 __device__ __forceinline__ void tr_finalize_reseed(Tr& t, u32 digest_be[8]) {
     u64 bits = t.total * 8;
     u32 n = t.buflen;
-    t.buf[n++] = 0x80;
-    while (n & 3) t.buf[n++] = 0;
     u32* bw = reinterpret_cast<u32*>(t.buf);
-    if (n > 56) {
-        for (u32 i = n >> 2; i < 16; i++) bw[i] = 0;
-        tr_flush_block(t);
-        n = 0;
+    if ((n & 3) == 0) {
+        bw[n >> 2] = 0x00000080u;                      // 0x80 and three zero bytes
+        n += 4;
+    } else {
+        t.buf[n++] = 0x80;
+        while (n & 3) t.buf[n++] = 0;
     }
-    for (u32 i = n >> 2; i < 14; i++) bw[i] = 0;
+    u32 first = n >> 2;                                // first word still to be zeroed
+    if (n > 56) {
+#pragma unroll
+        for (u32 i = 14; i < 16; i++) if (i >= first) bw[i] = 0;
+        tr_flush_block(t);
+        first = 0;
+    }
+#pragma unroll
+    for (u32 i = 0; i < 14; i++) if (i >= first) bw[i] = 0;
     bw[14] = bswap32((u32)(bits >> 32));
     bw[15] = bswap32((u32)bits);
     tr_flush_block(t);
