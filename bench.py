@@ -63,17 +63,33 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.rows.append([c.strip() for c in line.split(",")])
 
-    def stop(self):
+    def mark(self):
+        """Index of the next sample: brackets the timed region when the sampler was started earlier."""
+        return len(self.rows)
+
+    def stop(self, first=0, last=None):
+        """Summary of the samples [first, last) (the timed region); if nvidia-smi delivered none in
+        that window (it is a fraction of a second long), of all samples since start(), which the
+        caller makes under the same load (the warm-up steps), and `window` says so."""
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        whole = first == 0 and last is None
+        if last is None:
+            last = len(self.rows)
+        if last <= first:                       # let one more sample arrive before giving up on the window
+            time.sleep(0.1)
+            last = len(self.rows)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
+        rows, window = self.rows[first:last], "whole run (warm-up, timed region, end-to-end leg)" if whole else "timed region"
+        if not rows:
+            rows, window = self.rows, "warm-up and timed region"
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        for r in rows:
             if len(r) < 9:
                 continue
             try:
@@ -84,7 +100,7 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(nm)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "window": window, "reasons": sorted(reasons)}
 
 
 def load_peaks():
@@ -423,18 +439,20 @@ def run_qwen(zk, args, rank, world, local, dist, barrier, max_over_ranks):
                 proofs = sharding.merge_reverse(gathered)
         return proofs
 
+    sampler = ClockSampler(local)
+    sampler.start()                             # before the warm-up: nvidia-smi takes a while to deliver its first sample
     for _ in range(args.warmup):
         ref = step(False)
-    sampler = ClockSampler(local)
-    sampler.start()
     ctx0.sync(); barrier()
     launches0 = sum(c.launches for c in model.ctxs) if model else 0
+    s_first = sampler.mark()
     ctx0.timer_start()
     for _ in range(args.steps):
         out = step(False)
     ms_total = ctx0.timer_stop_ms()
+    s_last = sampler.mark()
     barrier()
-    clocks = sampler.stop()
+    clocks = sampler.stop(s_first, s_last)
     launches = (sum(c.launches for c in model.ctxs) if model else 0) - launches0
     # Per-launch figures of the two kernels that stream the weights: two more steps with CUDA events
     # around those kernels on two layers (one of each shape), outside the timed region because the

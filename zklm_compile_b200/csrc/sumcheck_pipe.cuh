@@ -20,8 +20,15 @@ constexpr int PIPE_THREADS = 512;                                 // at most; 12
 constexpr int PIPE_MAX_WORKER_WARPS = PIPE_THREADS / 32 - 1;      // 15
 constexpr int PIPE_NW = 36;                                       // nine EF coefficient sums
 
-// Barrier 1 among the worker warps only (all threads but warp 0); blockDim.x is a multiple of 32.
-__device__ __forceinline__ void pipe_worker_barrier() { asm volatile("bar.sync 1, %0;" ::"r"((int)blockDim.x - 32) : "memory"); }
+// Roles.  Warp 0 hashes.  Warps 4, 8, 12 would share warp 0's scheduler (warp w issues on sub-
+// partition w mod 4), its instruction cache and its issue slots; they only join the CTA barriers,
+// so the hash chain has a sub-partition to itself.  The other warps are the workers, numbered
+// 0, 1, 2, ... in warp order.
+__device__ __forceinline__ bool pipe_is_worker(int warp) { return (warp & 3) != 0; }
+__device__ __forceinline__ int pipe_worker_index(int warp) { return warp - 1 - (warp >> 2); }
+__device__ __forceinline__ int pipe_worker_warps() { const int last = (int)(blockDim.x >> 5) - 1; return last - (last >> 2); }
+// Barrier 1 among the worker warps only; blockDim.x is a multiple of 32.
+__device__ __forceinline__ void pipe_worker_barrier() { asm volatile("bar.sync 1, %0;" ::"r"(pipe_worker_warps() * 32) : "memory"); }
 
 // Coefficient sums of the next round over one pair index: quarters (a, b, c, d) of f and g.
 __device__ __forceinline__ void pipe_accum(Fe* C, Fe fa, Fe fb, Fe fc, Fe fd, Fe ga, Fe gb, Fe gc, Fe gd) {
@@ -33,14 +40,14 @@ __device__ __forceinline__ void pipe_accum(Fe* C, Fe fa, Fe fb, Fe fc, Fe fd, Fe
     C[6] = C[6] + pf * pg;  C[7] = C[7] + pf * qg + pg * qf;  C[8] = C[8] + qf * qg;
 }
 
-// Workers only (threads 32..blockDim.x-1; at least two worker warps, so that 36 threads can add the rows).  Tables of size n at (rf, rg); if `fold`, they are first
+// Workers only (see pipe_is_worker; at least two worker warps, so that 36 threads can add the rows).  Tables of size n at (rf, rg); if `fold`, they are first
 // folded with r into size n / 2 at (wf, wg) (in place allowed) and the sums are taken over the
 // folded tables.  Leaves the 36 summed words in out[] (shared memory) when the result size is >= 4.
 __device__ __forceinline__ void pipe_worker_pass(const Fe* rf, const Fe* rg, Fe* wf, Fe* wg, size_t n, bool fold, Fe r,
                                                  u32 (*cw)[PIPE_NW], u32* out) {
-    const int wid = threadIdx.x - 32;
-    const size_t workers = blockDim.x - 32;
-    const int worker_warps = (int)(workers >> 5);
+    const int worker_warps = pipe_worker_warps();
+    const int wid = pipe_worker_index(threadIdx.x >> 5) * 32 + (threadIdx.x & 31);
+    const size_t workers = (size_t)worker_warps * 32;
     const size_t m = fold ? n / 2 : n;              // size of the tables the sums run over
     Fe C[9];
 #pragma unroll
@@ -78,7 +85,7 @@ __device__ __forceinline__ void pipe_worker_pass(const Fe* rf, const Fe* rg, Fe*
         u32 w[PIPE_NW];
 #pragma unroll
         for (int i = 0; i < 9; i++) to_words(C[i], w + 4 * i);
-        const int lane = threadIdx.x & 31, warp = (threadIdx.x >> 5) - 1;
+        const int lane = threadIdx.x & 31, warp = pipe_worker_index(threadIdx.x >> 5);
 #pragma unroll
         for (int k = 0; k < PIPE_NW; k++) {
 #pragma unroll
@@ -140,7 +147,7 @@ __global__ void __launch_bounds__(PIPE_THREADS) sc_tail_product_pipe_kernel(ScTa
         if (threadIdx.x == 0) {
             Fe rn = sc_finish_round<SC_PRODUCT, Fe, Fe>(w, io, k, tr);
             to_words(rn, r_sh);
-        } else if (threadIdx.x >= 32) {
+        } else if (pipe_is_worker(threadIdx.x >> 5)) {
             if (first) pipe_worker_pass(rf, rg, wf, wg, n, false, r, cw, csum[k & 1]);
             else       pipe_worker_pass(rf, rg, wf, wg, 2 * n, true, r, cw, csum[k & 1]);
         }
