@@ -38,8 +38,16 @@ enum {
     ZKB_E_NOT_QR = 5,       /* "compute_r: d/sum_sq is not a quadratic residue" (transformer/mod.rs:182) */
     ZKB_E_LENGTH = 6,       /* a length assertion of the reference failed (matmul.rs:161, 861) */
     ZKB_E_TOO_LARGE = 7,    /* request exceeds a documented fixed capacity */
-    ZKB_E_TIMEOUT = 8       /* a peer GPU of a split sumcheck did not answer within the exchange's time limit */
+    ZKB_E_TIMEOUT = 8,      /* a peer GPU of a split sumcheck did not answer within the exchange's time limit */
+    ZKB_E_DIV_ZERO = 9      /* batch_inverse met a zero element: p3's `.inverse()` panics there (lookup.rs:336, 358) */
 };
+
+/* Alignment.  Host pointers need no particular alignment.  Device pointers passed by the caller
+ * (the `on_device` / `w_on_device` / `*_dev` arguments) must be 4-byte aligned; those that kernels
+ * read with 16-byte loads must be 16-byte aligned, and each such argument says so below.  A
+ * misaligned device pointer is refused on the host with ZKB_E_ARG before anything is launched
+ * (on the GPU it would be a fault that loses the whole CUDA context).  Memory from cudaMalloc or
+ * zkb_buf_alloc is always aligned enough; sub-slices of a pool are the caller's responsibility. */
 
 /* Sumcheck prover kinds; one per reference function. */
 enum {
@@ -58,6 +66,12 @@ int32_t zkb_ctx_create(int32_t device, zkb_ctx** out);
 void zkb_ctx_destroy(zkb_ctx* ctx);
 const char* zkb_last_error(const zkb_ctx* ctx);
 int32_t zkb_ctx_sync(zkb_ctx* ctx);
+/* Tuning options of one context, for measurements (none is needed in production; value 0 restores
+ * the built-in choice).  ZKB_OPT_PLAIN_TAIL: nonzero = every sumcheck ends in the plain
+ * single-CTA tail instead of the pipelined one.  ZKB_OPT_SINGLE_CTA_THREADS /
+ * ZKB_OPT_PIPE_THREADS: thread counts of the single-CTA kernels and of the pipelined tail. */
+enum { ZKB_OPT_PLAIN_TAIL = 0, ZKB_OPT_SINGLE_CTA_THREADS = 1, ZKB_OPT_PIPE_THREADS = 2 };
+int32_t zkb_ctx_set_option(zkb_ctx* ctx, int32_t option, int32_t value);
 /* The context's cudaStream_t (as an opaque pointer), for callers that enqueue their own work in order with the library's. */
 void* zkb_ctx_stream(zkb_ctx* ctx);
 /* CUDA-event stopwatch on the context's stream (for benchmarks; device time, not wall clock). */
@@ -109,7 +123,9 @@ int32_t zkb_tr_import(zkb_transcript* tr, const uint8_t state[ZKB_TR_STATE_BYTES
 /* ---- sumcheck provers ----
  * tables[i] holds 2^num_vars elements (u32 each for base-field inputs, 4 u32 each for EF
  * inputs; which is fixed by `kind`).  `on_device` != 0: tables are device pointers and are
- * left untouched.  Outputs (host memory):
+ * left untouched; EF tables on the device must be 16-byte aligned (ZKB_E_ARG otherwise),
+ * base-field tables only 4-byte (16-byte alignment selects the faster vectorised launches).
+ * Outputs (host memory):
  *   round_polys  num_vars x (stored evals per round) x w   u32
  *   challenges   num_vars x w                               u32
  *   finals       (number of tables, min 2) x w              u32   (f(s), g(s)[, h(s)]; f(s)=1 for ONES)
@@ -126,7 +142,26 @@ int32_t zkb_commit_weights_fast(zkb_ctx* ctx, const uint32_t* w, size_t n, int32
 /* eq_evals / eq_evals_ef: r has k (ef: 4k) words, out 2^k (ef: 4 * 2^k) words   m31_ops.rs:30-50, 175-191
  * (replaces eq_evals_gpu / MetalKernels::eq_butterfly, m31_ops.rs:54-78, gpu/metal_kernels.rs:232-253) */
 int32_t zkb_eq_evals(zkb_ctx* ctx, const uint32_t* r, uint32_t k, int32_t ef, uint32_t* out);
-/* fold_eq_matvec / fold_eq_matvec_ef: out[j] = sum_i eq(r)[i] W[i][j], zero-padded to n_pad    matmul.rs:76-128, 743-835 */
+/* mle_evaluate (m31_ops.rs:11-26): MLE of `evals` (n <= 2^k values, the rest of the hypercube is
+ * zero) at `point` (k base-field coordinates, host memory, point[0] = most significant index bit).
+ * on_device != 0: evals is a device pointer.  One pass over the table. */
+int32_t zkb_mle_eval_base(zkb_ctx* ctx, const uint32_t* evals, size_t n, const uint32_t* point, uint32_t k, int32_t on_device,
+                          uint32_t* out);
+/* mle_evaluate_ef (m31_ops.rs:155-171): the same at an extension-field point (4k words).
+ * evals_ef = 0: base-field evals (the reference's signature); evals_ef != 0: evals are EF elements
+ * (4 words each; what the reference's verifier folds after a sumcheck).  A device pointer to EF
+ * evals must be 16-byte aligned. */
+int32_t zkb_mle_eval_ef(zkb_ctx* ctx, const uint32_t* evals, size_t n, int32_t evals_ef, const uint32_t* point, uint32_t k,
+                        int32_t on_device, uint32_t out[4]);
+/* batch_inverse / batch_inverse_ef (lookup.rs:322-368; replaces MetalKernels::batch_inverse,
+ * gpu/metal_kernels.rs:212-229, called at lookup.rs:491-542): out[i] = 1 / vals[i].
+ * on_device != 0: vals and out are device pointers (out may equal vals; EF: both 16-byte
+ * aligned).  A zero element gives ZKB_E_DIV_ZERO (the reference panics there). */
+int32_t zkb_batch_inverse_base(zkb_ctx* ctx, const uint32_t* vals, size_t n, int32_t on_device, uint32_t* out);
+int32_t zkb_batch_inverse_ef(zkb_ctx* ctx, const uint32_t* vals, size_t n, int32_t on_device, uint32_t* out);
+/* fold_eq_matvec / fold_eq_matvec_ef: out[j] = sum_i eq(r)[i] W[i][j], zero-padded to n_pad    matmul.rs:76-128, 743-835
+ * W on the device (w_on_device != 0) with n a multiple of 4 must be 16-byte aligned; the same holds for
+ * every `W` / `w_on_device` pair below. */
 int32_t zkb_fold_eq_matvec(zkb_ctx* ctx, const uint32_t* W, size_t m, size_t n, const uint32_t* r, uint32_t log_m, int32_t ef,
                            int32_t w_on_device, uint32_t* out);
 /* matmul_forward: y = W x mod p                                        transformer/mod.rs:140-163 */
@@ -248,7 +283,9 @@ int32_t zkb_ctx_set_shared(zkb_ctx* ctx, int32_t on);
  * Set-up: every rank calls zkb_xch_create and zkb_xch_handle, the caller carries the 64-byte
  * handles between the processes (e.g. an all-gather), every rank calls zkb_xch_connect with
  * all of them.  A rank whose peer does not answer within the time limit (default 4 s) gets
- * ZKB_E_TIMEOUT instead of a proof; the exchange object is then unusable. */
+ * ZKB_E_TIMEOUT instead of a proof.  The time-out is sticky: every later call on that exchange
+ * fails at once, so after a time-out every rank must destroy its zkb_xch and the ranks must set
+ * up a new one together (the context itself stays usable). */
 typedef struct zkb_xch zkb_xch;
 int32_t zkb_xch_create(zkb_ctx* ctx, uint32_t world, uint32_t rank, zkb_xch** out);
 int32_t zkb_xch_handle(zkb_xch* xch, uint8_t handle[64]);
@@ -309,7 +346,8 @@ int32_t zkb_basefold_commit_and_prove(zkb_ctx* ctx, zkb_transcript* tr, const ui
  * with eq an array of at least m M31^4 elements (4 u32 each), W an m x n row-major u32 matrix
  * and out n_pad M31^4 elements (n_pad = n rounded up to a power of two) - the same values as
  * zkb_fold_eq_matvec with ef = 1 fed the eq table of r.  All three pointers are device memory
- * of the CURRENT device; `stream` is a cudaStream_t (NULL = default stream); work is only
+ * of the CURRENT device; W_dev must be 16-byte aligned when n is a multiple of 4 (a caller that
+ * carves W out of its own arena must place it so; ZKB_E_ARG otherwise); `stream` is a cudaStream_t (NULL = default stream); work is only
  * enqueued.  It calls no cudaMalloc / cudaFree: its 64-bit accumulators live in a fixed
  * 512 KiB device array inside the library (present on every GPU that loads it), which limits
  * n_pad to 16384 columns - wider matrices are refused with ZKB_E_TOO_LARGE and a message in

@@ -14,12 +14,13 @@ import pytest
 
 import zklm_compile_b200 as zk
 from zklm_compile_b200 import protocols as zp
+from oracle import pyoracle as O
 
 pytestmark = pytest.mark.gpu
 P = (1 << 31) - 1
 
 
-def _run_case(ctx, m, n, seed):
+def _run_case(ctx, m, n, seed, oracle=False):
     rng = np.random.default_rng(seed)
     w = rng.integers(0, P, m * n, dtype=np.int64).astype(np.uint32)
     log_m = zp.log2_ceil(m)
@@ -33,13 +34,16 @@ def _run_case(ctx, m, n, seed):
     zp.fold_eq_matvec_ef_noalloc(w_dev, m, n, eq_dev, out_dev, stream=ctx.stream)
     got = out_dev.download().reshape(n_pad, 4)
     assert got.tolist() == expected.tolist(), f"allocation-free fold differs from the regular fold for {m} x {n}"
+    if oracle:                             # and directly against the CPU restatement of fold_eq_matvec_ef (matmul.rs:743-835)
+        assert got.tolist() == O.fold_eq_matvec_ef(w, m, n, r).tolist(), f"allocation-free fold differs from the oracle for {m} x {n}"
 
 
 def test_noalloc_fold_matches_regular_fold_on_consecutive_calls():
     ctx = zk.Context(0)
     try:
-        _run_case(ctx, 300, 2100, 1)      # first call on the device: also resolves the scratch address
+        _run_case(ctx, 300, 2100, 1, oracle=True)   # first call on the device: also resolves the scratch address
         _run_case(ctx, 64, 40, 2)         # much narrower: stale accumulators beyond 64 columns must not matter
+        _run_case(ctx, 77, 1023, 4, oracle=True)    # column count not a multiple of 4: the scalar row loads
         _run_case(ctx, 129, 16384, 3)     # exactly the capacity
         _run_case(ctx, 300, 2100, 1)      # and the first shape again
     finally:

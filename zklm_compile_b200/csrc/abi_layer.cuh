@@ -32,7 +32,6 @@ int32_t zkb_qwen_layer_create(zkb_ctx* c, const uint64_t dims[7], const uint32_t
         ZKB_CUDA(cudaEventCreateWithFlags(&L->fwd_done, cudaEventDisableTiming));
         ZKB_CUDA(cudaEventCreateWithFlags(&L->own_idle, cudaEventDisableTiming));
         ZKB_CUDA(cudaMalloc(&L->roots_dev, 64 * 4));
-        if (const char* e = getenv("ZKB200_NO_GRAPH")) L->use_graph = !(e[0] && e[0] != '0');
         ZKB_CUDA(cudaMalloc(&L->seed_dev, 128));
         ZKB_CUDA(cudaHostAlloc(&L->seed_host, 128, cudaHostAllocDefault));
         static const int widx[8] = {W_Q, W_K, W_V, W_O, W_GPROJ, W_GATE, W_UP, W_DOWN};
@@ -144,7 +143,6 @@ int32_t zkb_qwen_layer_forward_async(zkb_qwen_layer* L, zkb_qwen_layer* prev, co
     zkb_ctx* c = L->ctx;
     ZKB_TRY(c, {
         c->use();
-        clear_status(c);
         const size_t bytes = (size_t)L->dm.d_model * 4;
         // with a shared forward stream the kernels below go there; the context's own stream is put
         // back before returning (a context is driven by one host thread at a time)
@@ -153,6 +151,7 @@ int32_t zkb_qwen_layer_forward_async(zkb_qwen_layer* L, zkb_qwen_layer* prev, co
         if (L->fwd_stream) ZKB_CUDA(cudaStreamWaitEvent(S, L->own_idle, 0));      // not before the layer's previous proof has finished with the trace
         struct Restore { zkb_ctx* c; cudaStream_t s; ~Restore() { c->stream = s; } } restore{c, own};
         c->stream = S;
+        clear_status(c);               // on the stream the forward kernels run on, so that the clear cannot overtake or erase their status writes
         if (prev) {
             if (prev->dm.d_model != L->dm.d_model) throw ArgFail{ZKB_E_ARG, "layer widths differ"};
             if (!(L->fwd_stream && prev->fwd_stream == L->fwd_stream)) ZKB_CUDA(cudaStreamWaitEvent(S, prev->fwd_done, 0));

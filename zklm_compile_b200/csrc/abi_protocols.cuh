@@ -72,6 +72,7 @@ int32_t zkb_fold_eq_matvec(zkb_ctx* c, const uint32_t* W, size_t m, size_t n, co
         c->use();
         const int w = ef ? 4 : 1;
         const size_t m_pad = size_t(1) << log_m, n_pad = size_t(1) << log2_ceil_u(n);
+        if (w_on_device && n % 4 == 0) need_align16(W, "W");
         const u32* dW = w_on_device ? W : up_pad(c, W, m * n, m * n);
         u32* dr = up_pad(c, r, (size_t)log_m * w, (size_t)log_m * w + 4);
         u32* eq = (u32*)c->scratch(m_pad * 4 * w);
@@ -101,6 +102,7 @@ int32_t zkb_matvec_forward(zkb_ctx* c, const uint32_t* W, const uint32_t* x, siz
     if (!c || !W || !x || !y || m == 0 || n == 0) return ZKB_E_ARG;
     ZKB_TRY(c, {
         c->use();
+        if (w_on_device && n % 4 == 0) need_align16(W, "W");
         const u32* dW = w_on_device ? W : up_pad(c, W, m * n, m * n);
         u32* dx = up_pad(c, x, n, n + 4);
         u32* dy = (u32*)c->scratch(m * 4);
@@ -120,6 +122,7 @@ int32_t zkb_prove_matmul_succinct_ef_bind(zkb_ctx* c, zkb_transcript* t, const u
         c->use();
         c->rec_reset();
         const size_t n_pad = size_t(1) << log2_ceil_u(n);
+        if (w_on_device && n % 4 == 0) need_align16(W, "W");
         const u32* dW = w_on_device ? W : up_pad(c, W, m * n, m * n);
         u32* dx = up_pad(c, x, n, n_pad);
         u32* dy = up_pad(c, y, m, m);
@@ -144,6 +147,7 @@ int32_t zkb_prove_matmul_succinct(zkb_ctx* c, zkb_transcript* t, const uint32_t*
         c->use();
         c->rec_reset();
         const size_t n_pad = size_t(1) << log2_ceil_u(n);
+        if (w_on_device && n % 4 == 0) need_align16(W, "W");
         const u32* dW = w_on_device ? W : up_pad(c, W, m * n, m * n);
         u32* dx = up_pad(c, x, n, n_pad);
         u32* dy = up_pad(c, y, m, m);

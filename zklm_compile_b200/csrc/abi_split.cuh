@@ -132,8 +132,10 @@ int32_t zkb_sumcheck_prove_split(zkb_ctx* c, zkb_xch* x, zkb_transcript* t, int3
         const u32* dev_tabs[3] = {nullptr, nullptr, nullptr};
         for (int i = 0; i < ki.nt; i++) {
             if (!tables[i]) throw ArgFail{ZKB_E_ARG, "null table"};
-            if (on_device) dev_tabs[i] = tables[i];
-            else {
+            if (on_device) {
+                if (ki.in_w[i] == 4) need_align16(tables[i], "an extension-field table");
+                dev_tabs[i] = tables[i];
+            } else {
                 u32* d = (u32*)c->scratch(n * 4 * ki.in_w[i]);
                 ZKB_CUDA(cudaMemcpyAsync(d, tables[i], n * 4 * ki.in_w[i], cudaMemcpyHostToDevice, c->stream));
                 dev_tabs[i] = d;
@@ -145,11 +147,12 @@ int32_t zkb_sumcheck_prove_split(zkb_ctx* c, zkb_xch* x, zkb_transcript* t, int3
         h.sticky = x->local + XCH_BOX_WORDS;
         h.timeout_ns = x->timeout_ns;
         ZKB_CUDA(cudaMemcpyAsync(x->dev, &h, sizeof(h), cudaMemcpyHostToDevice, c->stream));
-        x->seq += local_vars + 1;                 // one exchange per local round, one gather
         c->rec_reset();
         ScOpts o;
         o.xch = x->dev; o.xch_world = x->world;
         ScRec r = sumcheck_enqueue(c, t->dev, kind, dev_tabs, num_vars, o);
+        x->seq += local_vars + 1;                 // one exchange per local round, one gather; only once the launches are queued,
+                                                  // so that a call that fails before launching leaves the ranks in step
         size_t sticky_off = c->rec_alloc(1);
         ZKB_CUDA(cudaMemcpyAsync(c->rec_dev + sticky_off, h.sticky, 4, cudaMemcpyDeviceToDevice, c->stream));
         c->rec_fetch();

@@ -116,14 +116,11 @@ struct zkb_ctx {
     // context's latency-critical single-CTA kernel (a transcript step, a sumcheck tail) never
     // has to wait for a wide kernel to drain before it finds an SM.
     bool polite = false;
-    int single_cta_threads() const {
-        static const int env = [] { const char* e = getenv("ZKB200_SINGLE_THREADS"); return e ? atoi(e) : 0; }();
-        return env ? env : (polite ? 512 : 1024);
-    }
-    int pipe_threads(int full) const {
-        static const int env = [] { const char* e = getenv("ZKB200_PIPE_THREADS"); return e ? atoi(e) : 0; }();
-        return env ? env : (polite ? full / 2 : full);
-    }
+    // Tuning options (zkb_ctx_set_option): 0 = the built-in choice.
+    int opt_single_threads = 0, opt_pipe_threads = 0;
+    bool opt_plain_tail = false;
+    int single_cta_threads() const { return opt_single_threads ? opt_single_threads : (polite ? 512 : 1024); }
+    int pipe_threads(int full) const { return opt_pipe_threads ? opt_pipe_threads : (polite ? full / 2 : full); }
     int wide_ctas_per_sm(int greedy, int shared) const { return polite ? shared : greedy; }
 
     // While a stream capture is open nothing may be allocated; arena_epoch changes whenever the

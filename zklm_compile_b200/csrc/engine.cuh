@@ -59,11 +59,6 @@ inline int grid_for(zkb_ctx* c, size_t items, int per_cta = 256, int ctas_per_sm
 }
 #define ZKB_LAUNCHED(c) (c)->launched(__FILE__, __LINE__)
 
-// ZKB200_PLAIN_TAIL=1 in the environment selects the plain tail everywhere (for comparisons).
-inline bool pipe_tail_enabled() {
-    static const bool on = [] { const char* e = getenv("ZKB200_PLAIN_TAIL"); return !(e && e[0] && e[0] != '0'); }();
-    return on;
-}
 
 template <int KIND, class SrcT, class ChalT>
 void run_sumcheck(zkb_ctx* c, ScTables tb, u32 num_vars, ScIO io, bool dynamic) {
@@ -111,7 +106,7 @@ void run_sumcheck(zkb_ctx* c, ScTables tb, u32 num_vars, ScIO io, bool dynamic) 
     }
     // product sumchecks over EF tables: the tail that overlaps the table work with the hash chain
     constexpr bool pipe_t = KIND == SC_PRODUCT && std::is_same<ChalT, Fe>::value;
-    const bool pipe = pipe_t && pipe_tail_enabled() && !io.xch && !dynamic && !io.dyn_nv && (!in_src || std::is_same<SrcT, Fe>::value);
+    const bool pipe = pipe_t && !c->opt_plain_tail && !io.xch && !dynamic && !io.dyn_nv && (!in_src || std::is_same<SrcT, Fe>::value);
     if (pipe) {
         if constexpr (pipe_t) sc_tail_product_pipe_kernel<<<1, c->pipe_threads(PIPE_THREADS), 0, c->stream>>>(tb, size, round, num_vars, pending ? 1 : 0, io);
     } else if (in_src)

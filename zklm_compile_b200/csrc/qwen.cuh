@@ -262,8 +262,8 @@ inline void qwen_prove_enqueue_inner(zkb_qwen_layer* L, u32 layer_idx, const uin
     if (L->proofs_enqueued >= 1) {
         const uint64_t launches0 = c->launches;
         cudaGraph_t graph = nullptr;
-        c->capturing = true;
         ZKB_CUDA(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+        c->capturing = true;               // only once the capture is really open: a failed begin must not leave the flag set
         bool fine = true;
         std::string why;
         try {

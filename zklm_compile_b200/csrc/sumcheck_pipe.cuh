@@ -108,7 +108,7 @@ __global__ void __launch_bounds__(PIPE_THREADS) sc_tail_product_pipe_kernel(ScTa
                                                                                int pending, ScIO io) {
     __shared__ u32 red[32 * 16];
     __shared__ __align__(16) unsigned char trbuf[TR_SCRATCH_BYTES];
-    __shared__ u32 r_sh[4];
+    __shared__ u32 r_sh[2][4];                       // indexed by round parity: round k+1's challenge never overwrites r_k while a slow warp still reads it
     __shared__ u32 cw[PIPE_MAX_WORKER_WARPS][PIPE_NW];
     __shared__ u32 csum[2][PIPE_NW];
     __shared__ u32 w_sh[12];
@@ -146,7 +146,7 @@ __global__ void __launch_bounds__(PIPE_THREADS) sc_tail_product_pipe_kernel(ScTa
         // thread 0 hashes round k; the workers prepare round k + 1 as polynomials in r_k
         if (threadIdx.x == 0) {
             Fe rn = sc_finish_round<SC_PRODUCT, Fe, Fe>(w, io, k, tr);
-            to_words(rn, r_sh);
+            to_words(rn, r_sh[k & 1]);
         } else if (pipe_is_worker(threadIdx.x >> 5)) {
             if (first) pipe_worker_pass(rf, rg, wf, wg, n, false, r, cw, csum[k & 1]);
             else       pipe_worker_pass(rf, rg, wf, wg, 2 * n, true, r, cw, csum[k & 1]);
@@ -154,7 +154,7 @@ __global__ void __launch_bounds__(PIPE_THREADS) sc_tail_product_pipe_kernel(ScTa
         __syncthreads();
         if (!first) { rf = wf; rg = wg; }            // the fold above wrote dst
         first = false;
-        from_words(r, r_sh);                         // r_k
+        from_words(r, r_sh[k & 1]);                  // r_k
         if (n == 2) break;                           // round k was the last one
         if (threadIdx.x < 32) {                      // three lanes evaluate the three quadratics, lane 0 collects
             if (threadIdx.x < 3) {

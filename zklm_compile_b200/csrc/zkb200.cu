@@ -17,6 +17,12 @@ using namespace zkb;
     catch (const ArgFail& e) { if (ctxptr) (ctxptr)->err = e.msg; return e.code; }   \
     catch (const std::bad_alloc&) { if (ctxptr) (ctxptr)->err = "host allocation failed"; return ZKB_E_CUDA; }
 
+// Pointers that kernels read with 16-byte loads: checked on the host, before anything is
+// launched, because a misaligned address on the device is a sticky context error, not a status.
+static inline void need_align16(const void* p, const char* what) {
+    if ((uintptr_t)p & 15) throw ArgFail{ZKB_E_ARG, std::string(what) + " must be 16-byte aligned (it is read with 16-byte loads)"};
+}
+
 extern "C" {
 
 int32_t zkb_ctx_create(int32_t device, zkb_ctx** out) {
@@ -334,6 +340,22 @@ int32_t zkb_ctx_set_shared(zkb_ctx* c, int32_t on) {
     return ZKB_OK;
 }
 
+int32_t zkb_ctx_set_option(zkb_ctx* c, int32_t option, int32_t value) {
+    if (!c) return ZKB_E_ARG;
+    switch (option) {
+        case ZKB_OPT_PLAIN_TAIL: c->opt_plain_tail = value != 0; break;
+        case ZKB_OPT_SINGLE_CTA_THREADS:
+            if (value != 0 && (value < 64 || value > 1024 || value % 32)) { c->err = "single-CTA thread count must be 0 or a multiple of 32 in [64, 1024]"; return ZKB_E_ARG; }
+            c->opt_single_threads = value; break;
+        case ZKB_OPT_PIPE_THREADS:
+            if (value != 0 && (value < 96 || value > PIPE_THREADS || value % 32)) { c->err = "pipelined-tail thread count must be 0 or a multiple of 32 in [96, 512]"; return ZKB_E_ARG; }
+            c->opt_pipe_threads = value; break;
+        default: c->err = "unknown option"; return ZKB_E_ARG;
+    }
+    c->arena_epoch++;                  // captured graphs hold the old launch shapes
+    return ZKB_OK;
+}
+
 int32_t zkb_sumcheck_prove(zkb_ctx* c, zkb_transcript* t, int32_t kind, const uint32_t* const* tables,
                            uint32_t num_vars, int32_t on_device, uint32_t* round_polys, uint32_t* challenges,
                            uint32_t* finals) {
@@ -346,8 +368,10 @@ int32_t zkb_sumcheck_prove(zkb_ctx* c, zkb_transcript* t, int32_t kind, const ui
         const u32* dev_tabs[3] = {nullptr, nullptr, nullptr};
         for (int i = 0; i < ki.nt; i++) {
             if (!tables[i]) throw ArgFail{ZKB_E_ARG, "null table"};
-            if (on_device) dev_tabs[i] = tables[i];
-            else {
+            if (on_device) {
+                if (ki.in_w[i] == 4) need_align16(tables[i], "an extension-field table");
+                dev_tabs[i] = tables[i];
+            } else {
                 u32* d = (u32*)c->scratch(n * 4 * ki.in_w[i]);
                 ZKB_CUDA(cudaMemcpyAsync(d, tables[i], n * 4 * ki.in_w[i], cudaMemcpyHostToDevice, c->stream));
                 dev_tabs[i] = d;
@@ -378,6 +402,7 @@ int32_t zkb_sumcheck_prove(zkb_ctx* c, zkb_transcript* t, int32_t kind, const ui
 }  // extern "C"
 
 #include "abi_protocols.cuh"
+#include "abi_field.cuh"
 #include "abi_layer.cuh"
 #include "abi_pcs.cuh"
 #include "abi_split.cuh"
@@ -408,6 +433,10 @@ void set_err(char* err, size_t cap, const std::string& msg) {
 extern "C" int32_t zkb_fold_eq_matvec_ef_noalloc(const uint32_t* W_dev, size_t m, size_t n, const uint32_t* eq_dev, uint32_t* out_dev,
                                                  void* stream, char* err, size_t err_cap) {
     if (!W_dev || !eq_dev || !out_dev || m == 0 || n == 0) { set_err(err, err_cap, "null pointer or empty matrix"); return ZKB_E_ARG; }
+    if (n % 4 == 0 && ((uintptr_t)W_dev & 15)) {
+        set_err(err, err_cap, "zkb_fold_eq_matvec_ef_noalloc: W_dev must be 16-byte aligned when n is a multiple of 4 (rows are read with 16-byte loads)");
+        return ZKB_E_ARG;
+    }
     const size_t n_pad = size_t(1) << log2_ceil_u(n);
     if (n_pad > ZKB_NOALLOC_MAX_COLS) {
         set_err(err, err_cap, "zkb_fold_eq_matvec_ef_noalloc: " + std::to_string(n) + " columns pad to " + std::to_string(n_pad) +

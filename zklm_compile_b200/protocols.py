@@ -63,6 +63,48 @@ def eq_evals_ef(ctx: Context, r) -> np.ndarray:
     return out
 
 
+def mle_evaluate(ctx: Context, evals, point) -> int:
+    """m31_ops.rs:11-26; evals: host array or DeviceBuffer of n <= 2^k values, point: k coordinates."""
+    pt, pp = _a(point)
+    out = C.c_uint32()
+    if isinstance(evals, DeviceBuffer):
+        pe, n, on = evals.ptr, evals.n, 1
+    else:
+        e, pe = _a(evals)
+        n, on = e.size, 0
+    check(ctx.h, _lib.lib().zkb_mle_eval_base(ctx.h, pe, C.c_size_t(n), pp, C.c_uint32(pt.size), C.c_int32(on), C.byref(out)))
+    return out.value
+
+
+def mle_evaluate_ef(ctx: Context, evals, point, evals_ef: bool = False) -> np.ndarray:
+    """m31_ops.rs:155-171; point is (k, 4); with evals_ef the table holds EF elements (n, 4)."""
+    pt, pp = _a(point)
+    w = 4 if evals_ef else 1
+    out = np.zeros(4, np.uint32)
+    if isinstance(evals, DeviceBuffer):
+        pe, n, on = evals.ptr, evals.n // w, 1
+    else:
+        e, pe = _a(evals)
+        n, on = e.size // w, 0
+    check(ctx.h, _lib.lib().zkb_mle_eval_ef(ctx.h, pe, C.c_size_t(n), C.c_int32(int(evals_ef)), pp, C.c_uint32(pt.size // 4), C.c_int32(on),
+                                             out.ctypes.data_as(u32p)))
+    return out
+
+
+def batch_inverse(ctx: Context, vals, ef: bool = False):
+    """lookup.rs:322-345 (ef=False) / :348-368 (ef=True).  Host array in, host array out; a
+    DeviceBuffer is inverted in place (as the reference's Metal hook does, lookup.rs:491-542)."""
+    fn = _lib.lib().zkb_batch_inverse_ef if ef else _lib.lib().zkb_batch_inverse_base
+    w = 4 if ef else 1
+    if isinstance(vals, DeviceBuffer):
+        check(ctx.h, fn(ctx.h, vals.ptr, C.c_size_t(vals.n // w), C.c_int32(1), vals.ptr))
+        return vals
+    v, pv = _a(vals)
+    out = np.zeros_like(v)
+    check(ctx.h, fn(ctx.h, pv, C.c_size_t(v.size // w), C.c_int32(0), out.ctypes.data_as(u32p)))
+    return out
+
+
 def fold_eq_matvec(ctx: Context, w_flat, m: int, n: int, r_point, ef: bool = False) -> np.ndarray:
     """matmul.rs:76-128 (ef=False) / :743-835 (ef=True)."""
     r, pr = _a(r_point)

@@ -63,6 +63,12 @@ class Context:
         of every SM free (see zkb_ctx_set_shared in include/zkb200.h)."""
         check(self.h, _lib.lib().zkb_ctx_set_shared(self.h, C.c_int32(1 if on else 0)))
 
+    OPT_PLAIN_TAIL, OPT_SINGLE_CTA_THREADS, OPT_PIPE_THREADS = 0, 1, 2
+
+    def set_option(self, option: int, value: int):
+        """Tuning options for measurements (zkb_ctx_set_option in include/zkb200.h); 0 = built-in choice."""
+        check(self.h, _lib.lib().zkb_ctx_set_option(self.h, C.c_int32(option), C.c_int32(value)))
+
     @property
     def stream(self) -> int:
         """The context's cudaStream_t as an integer handle."""
