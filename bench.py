@@ -146,32 +146,68 @@ def synth_input(d_model):
     return np.where(a < 0, a + P, a).astype(np.uint32)
 
 
-def cpu_qwen_leg(n_layers_total, sample_layers, threads):
-    """The reference's algorithm on the host cores through the C++ restatement (no Rust toolchain
-    on this box): `sample_layers` layers of the same shapes proved concurrently, one per thread,
-    as the reference's rayon layer fan-out does; scaled to the full layer count."""
+def sample_digest(proofs_by_layer):
+    """SHA-256 over the proofs of layers 0, 1, ... (in that order) of a sample, so that the two arms'
+    lines can be compared with each other."""
+    import hashlib
+    h = hashlib.sha256()
+    for p in proofs_by_layer:
+        h.update(p)
+    return h.hexdigest()
+
+
+def cpu_qwen_leg(n_layers_total, sample_layers, threads, gpu_proofs_by_layer=None):
+    """The reference's algorithm on the host cores through the C++ restatement (no Rust toolchain on
+    this box), structured as the reference runs it: weights loaded and committed beforehand (untimed,
+    pipeline/mod.rs:224-229), then the forward pass layer after layer with the matrix rows split over
+    the cores (pipeline/forward.rs:24, transformer/mod.rs:141-150), then the layer proofs concurrently,
+    one per thread (pipeline/prove.rs:158-180).  The sample is the first `sample_layers` layers of the
+    very workload the GPU arm proves: same weights, same chained activations, same input hash; when
+    the GPU's proofs are passed in they must be byte-identical.  Scaled to the full layer count."""
     from concurrent.futures import ThreadPoolExecutor
     from oracle import pyoracle as O
-    from zklm_compile_b200 import tables
+    from zklm_compile_b200 import qwen as zq, tables
     silu, sigm = tables.build_silu_table(1000), tables.build_sigmoid_table(1000)
     x = synth_input(2560)
-    ih = bytes(32)
-    work = []
+    ih = zq.hash_values(x)
+    layers = []
     for i in range(sample_layers):
         cfg = qwen4b_layer_config(i)
-        work.append((cfg, synth_weights(cfg, i), i))
-    O.lib()
-
-    def one(w):
-        cfg, weights, i = w
-        return len(O.qwen_layer_prove(cfg, weights, x, silu, sigm, i, ih)[1])
-
+        layers.append(O.QwenLayer(cfg, synth_weights(cfg, i), silu, sigm))
     t0 = time.perf_counter()
+    O.set_threads(threads)
+    cur = x
+    for L in layers:
+        cur = L.forward(cur)
+    t_fwd = time.perf_counter() - t0
+    O.set_threads(1)
+    t1 = time.perf_counter()
     with ThreadPoolExecutor(threads) as pool:
-        sizes = list(pool.map(one, work))
-    dt = time.perf_counter() - t0
-    waves = -(-n_layers_total // sample_layers)
-    return dt * 1e3 * waves, dt * 1e3, sum(sizes)
+        proofs = list(pool.map(lambda i: layers[i].prove_trace(i, ih), range(sample_layers)))
+    t_prove = time.perf_counter() - t1
+    checked = 0
+    if gpu_proofs_by_layer is not None:
+        for i, p in enumerate(proofs):
+            assert gpu_proofs_by_layer[i] == p, f"layer {i}: the GPU proof differs from the CPU restatement's"
+            checked += 1
+    scale = n_layers_total / sample_layers
+    waves = -(-n_layers_total // threads)
+    per_wave = t_prove / -(-sample_layers // threads)
+    full_ms = (t_fwd * scale + per_wave * waves) * 1e3
+    return {"full_ms": full_ms, "sample_ms": (t_fwd + t_prove) * 1e3, "forward_ms": t_fwd * 1e3, "prove_ms": t_prove * 1e3,
+            "proof_bytes": sum(len(p) for p in proofs), "checked": checked, "sha256": sample_digest(proofs)}
+
+
+def cpu_qwen_summary(r, sample, threads, n_layers):
+    return {"value": round(r["full_ms"], 1), "unit": "ms", "cores": threads, "kind": "port",
+            "sample": f"layers 0..{sample - 1} of the same workload (same weights, chained activations and input hash): forward chain "
+                      f"{r['forward_ms']:.0f} ms with matrix rows over {threads} threads, then {sample} layer proofs concurrently, one thread "
+                      f"each, {r['prove_ms']:.0f} ms; scaled to {n_layers} layers ({n_layers}/{sample} x forward + "
+                      f"ceil({n_layers}/{threads}) proof waves); weights committed beforehand as in the reference; C++ restatement built "
+                      f"-O3 (reference Rust binary: unavailable on this box)",
+            "proofs_compared_with_gpu": r["checked"], "sample_proof_sha256": r["sha256"],
+            "published_reference_ms": PUBLISHED_QWEN4B_MS,
+            "port_over_published": round(r["full_ms"] / PUBLISHED_QWEN4B_MS, 2)}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -506,7 +542,7 @@ def run_qwen(zk, args, rank, world, local, dist, barrier, max_over_ranks):
                                               "a time on the critical path)"),
            "roofline_fold": roof("fold_eq_matvec", "fold_eq_matvec_kernel<4> (the one pass over W inside each matmul proof; launches of "
                                                    "different layers overlap, so per-launch times include sharing HBM)"),
-           "ctx0": ctx0, "model": model}
+           "ctx0": ctx0, "model": model, "proofs": ref if rank == 0 else None}
     return res
 
 
@@ -557,12 +593,9 @@ def main():
             return
         if qwen:
             sample = args.cpu_layers or min(cores, 8, args.layers)
-            full_ms, sample_ms, _ = cpu_qwen_leg(args.layers, sample, sample)
-            value, ms = full_ms, full_ms
-            cpu = {"value": round(full_ms, 1), "unit": "ms", "cores": sample, "kind": "port",
-                   "sample": f"{sample} layers of the workload proved concurrently (one thread each, like the reference's rayon layer "
-                             f"fan-out) in {sample_ms:.0f} ms, scaled by ceil({args.layers}/{sample}) waves; forward + prove per layer; "
-                             "C++ restatement (reference Rust binary: unavailable on this box)"}
+            r = cpu_qwen_leg(args.layers, sample, min(cores, sample))
+            value = ms = r["full_ms"]
+            cpu = cpu_qwen_summary(r, sample, min(cores, sample), args.layers)
         else:
             gbps, ms = cpu_sumcheck_leg(args.n_cpu, max(1, min(args.steps, 3)), min(args.warmup, 1))
             value = gbps
@@ -571,7 +604,8 @@ def main():
                              "C++ restatement (reference Rust binary: unavailable on this box)"}
         print(json.dumps({"impl": "reference", "metric": metric, "value": round(value, 4), "unit": unit, "n_gpus": args.gpus, "steps": 1,
                           "warmup": 0, "ms_per_step": round(ms, 3), "higher_is_better": hib, "scaling": "strong" if qwen else "weak",
-                          "vs_baseline": None, "dtype": "u32 (M31 / M31^4)", "data": "synthetic", "config": config, "cpu_baseline": cpu,
+                          "vs_baseline": (round(value / PUBLISHED_QWEN4B_MS, 4) if qwen and args.layers == 32 else None),
+                          "dtype": "u32 (M31 / M31^4)", "data": "synthetic", "config": config, "cpu_baseline": cpu,
                           "e2e": {"value": round(value, 4), "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
         return
 
@@ -608,6 +642,8 @@ def main():
                      "e2e": {"value": round(r["e2e_wall_ms"], 3), "unit": "ms", "device_ms": round(r["e2e_ms"], 3),
                              "h2d_bytes_per_step": 2560 * 4, "d2h_bytes_per_step": r["proof_bytes"]},
                      "gpu_launches": int(r["launches"]), "clocks": r["clocks"], "proof_bytes": r["proof_bytes"], "setup_s": r["setup_s"],
+                     "proof_sha256": sample_digest(r["proofs"]) if r["proofs"] is not None else None,
+                     "proof_sha256_note": "SHA-256 over the proofs as returned (reverse layer order); identical at every N",
                      "note": "one step = forward pass + 32 layer proofs; bounded by the serial SHA-256 transcript chain of each layer, "
                              "not by HBM; vs_baseline = value / 376 ms published for an Apple M4 Max CPU"})
         if r["model"]:
@@ -635,13 +671,17 @@ def main():
         line["basefold_microbench"] = run_basefold(zk, micro_ctx, args.n_basefold)
         line["dense4m"] = {"ef": run_mlp(zk, micro_ctx, 5, 3, True), "base": run_mlp(zk, micro_ctx, 5, 3, False)}
     cpu = None
+    gpu_proofs_by_layer = None
+    if qwen and rank == 0 and r["proofs"] is not None and len(r["proofs"]) == args.layers:
+        gpu_proofs_by_layer = r["proofs"][::-1]
+        k = min(cores, 8, args.layers)
+        line["sample_proof_sha256"] = {"layers": k, "sha256": sample_digest(gpu_proofs_by_layer[:k]),
+                                       "note": "over the proofs of layers 0..k-1 in layer order: the reference arm prints the same digest"}
     if rank == 0 and world == 1 and not args.no_cpu:
         if qwen:
             sample = args.cpu_layers or min(cores, 8, args.layers)
-            full_ms, sample_ms, _ = cpu_qwen_leg(args.layers, sample, sample)
-            cpu = {"value": round(full_ms, 1), "unit": "ms", "cores": sample, "kind": "port",
-                   "sample": f"{sample} layers proved concurrently, one thread each, in {sample_ms:.0f} ms, scaled by "
-                             f"ceil({args.layers}/{sample}) waves; forward + prove per layer; C++ restatement of the reference"}
+            r = cpu_qwen_leg(args.layers, sample, min(cores, sample), gpu_proofs_by_layer=gpu_proofs_by_layer)
+            cpu = cpu_qwen_summary(r, sample, min(cores, sample), args.layers)
         else:
             gbps, ms = cpu_sumcheck_leg(args.n_cpu, 2, 1)
             cpu = {"value": round(gbps, 4), "unit": "GB/s", "cores": 1, "kind": "port", "ms_per_step": round(ms, 2),

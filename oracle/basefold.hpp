@@ -90,14 +90,17 @@ inline VF basefold_encode(const VF& coeffs, size_t log_n, const FoldableTables& 
     size_t chunk = 2;
     for (size_t level = 0; level < log_n; level++) {
         const F* t = tb.t_level(level);
-        size_t t_len = size_t(1) << level, half = chunk / 2;
-        for (size_t c0 = 0; c0 < cw.size(); c0 += chunk)
-            for (size_t j = 0; j < half; j++) {
-                F rhs = cw[c0 + j + half] * t[j % t_len];
+        const size_t half = chunk / 2;
+        // butterfly b of this level: chunk b / half, offset b % half (every butterfly touches its own two slots)
+        par_rows(cw.size() / 2, [&](size_t lo, size_t hi, int) {
+            for (size_t b = lo; b < hi; b++) {
+                const size_t c0 = (b >> level) << (level + 1), j = b & (half - 1);     // half = t_len = 2^level
+                F rhs = cw[c0 + j + half] * t[j];
                 F left = cw[c0 + j];
                 cw[c0 + j] = left + rhs;
                 cw[c0 + j + half] = left - rhs;
             }
+        });
         chunk *= 2;
     }
     return cw;
@@ -107,10 +110,12 @@ inline VF basefold_encode(const VF& coeffs, size_t log_n, const FoldableTables& 
 inline size_t fold_codeword_inplace(F* cw, size_t n, F alpha, const F* weights, size_t w_len) {
     const F two_inv(1073741824u);
     size_t half = n / 2;
-    for (size_t j = 0; j < half; j++) {
-        F l = cw[j], r = cw[j + half];
-        cw[j] = (l + r) * two_inv + alpha * ((l - r) * weights[j % w_len]);
-    }
+    par_rows(half, [&](size_t lo, size_t hi, int) {
+        for (size_t j = lo; j < hi; j++) {
+            F l = cw[j], r = cw[j + half];
+            cw[j] = (l + r) * two_inv + alpha * ((l - r) * weights[j % w_len]);
+        }
+    });
     return half;
 }
 

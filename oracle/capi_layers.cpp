@@ -228,4 +228,62 @@ size_t zko_qwen_layer_prove(const uint64_t* dims, const uint32_t* const* weights
     return emit(serialize(p), out, cap);
 }
 
+
+// A layer kept between calls: weights converted once and committed once, as the reference's
+// server does at load time (server.rs:46-94); the reference's prove_time excludes the
+// commitments (pipeline/mod.rs:224-229), so whoever times forward + prove uses this handle.
+struct OracleLayer {
+    ModelConfig c;
+    QwenLayerWeights W;
+    QwenLayerCommitments com;
+    LookupTable silu, sigm;
+    QwenForwardTrace trace;      // of the most recent zko_qwen_layer_forward_h
+    bool have_trace = false;
+};
+void* zko_qwen_layer_new(const uint64_t* dims, const uint32_t* const* weights, const uint32_t* silu_out, const uint32_t* sigmoid_out,
+                         size_t n_table) {
+    OracleLayer* L = new OracleLayer();
+    L->c = cfg_of(dims);
+    L->W = weights_of(L->c, weights);
+    L->silu = table_from_outputs(std::vector<uint32_t>(silu_out, silu_out + n_table));
+    L->sigm = table_from_outputs(std::vector<uint32_t>(sigmoid_out, sigmoid_out + n_table));
+    L->com = commit_qwen_layer(L->W);
+    return L;
+}
+void zko_qwen_layer_free(void* h) { delete static_cast<OracleLayer*>(h); }
+size_t zko_qwen_layer_prove_h(void* h, const uint32_t* x, uint32_t layer_idx, const uint8_t* input_hash, uint32_t* y, uint8_t* out,
+                              size_t cap, int verify, int* accepted) {
+    OracleLayer& L = *static_cast<OracleLayer*>(h);
+    VF X = vf(x, L.c.d_model);
+    QwenForwardTrace t = qwen_forward(X, L.W, L.c, L.silu, L.sigm);
+    out_f(t.output, y);
+    std::string seed = "qwen-layer-" + std::to_string(layer_idx);
+    Transcript tr(seed);
+    tr.absorb_bytes(input_hash, 32);
+    QwenLayerProofEF p = prove_qwen_layer_precommitted_ef(t, L.W, L.c, L.com, L.silu, L.sigm, tr);
+    if (verify) {
+        Transcript vt(seed);
+        vt.absorb_bytes(input_hash, 32);
+        *accepted = verify_qwen_layer_ef(p, X, t.output, L.W, L.c, L.silu, L.sigm, vt) ? 1 : 0;
+    }
+    return emit(serialize(p), out, cap);
+}
+// The two halves of the call above, as the reference runs them: the forward pass of every layer
+// first (pipeline/forward.rs:24), then the layer proofs (pipeline/prove.rs:158-180).
+void zko_qwen_layer_forward_h(void* h, const uint32_t* x, uint32_t* y) {
+    OracleLayer& L = *static_cast<OracleLayer*>(h);
+    L.trace = qwen_forward(vf(x, L.c.d_model), L.W, L.c, L.silu, L.sigm);
+    L.have_trace = true;
+    out_f(L.trace.output, y);
+}
+size_t zko_qwen_layer_prove_trace_h(void* h, uint32_t layer_idx, const uint8_t* input_hash, uint8_t* out, size_t cap) {
+    OracleLayer& L = *static_cast<OracleLayer*>(h);
+    if (!L.have_trace) return 0;
+    Transcript tr("qwen-layer-" + std::to_string(layer_idx));
+    tr.absorb_bytes(input_hash, 32);
+    return emit(serialize(prove_qwen_layer_precommitted_ef(L.trace, L.W, L.c, L.com, L.silu, L.sigm, tr)), out, cap);
+}
+// Worker threads of the row-parallel matrix loops (matmul.hpp); 1 = serial.
+void zko_set_threads(int n) { matrix_threads() = n < 1 ? 1 : n; }
+
 }  // extern "C"

@@ -14,6 +14,7 @@
 #include <cstddef>
 #include <vector>
 #include <array>
+#include <thread>
 
 namespace zko {
 
@@ -124,6 +125,25 @@ inline EF inverse(EF a) {
 }
 
 using VF = std::vector<F>;
+
 using VEF = std::vector<EF>;
+
+// Data-parallel helper.  The reference splits these loops over rayon workers: matrix rows
+// (transformer/mod.rs:141-150, matmul.rs:81-120, 770-832), Merkle layers of at least 256 nodes
+// (pcs.rs:158-190).  Here a plain thread count, set by whoever times the oracle (1 = serial, the
+// default).  Results do not depend on it.
+inline int& matrix_threads() { static int n = 1; return n; }
+template <class Fn>
+inline void par_rows(size_t rows, Fn fn) {          // fn(lo, hi, worker)
+    const int T = matrix_threads();
+    if (T <= 1 || rows < 64) { fn(size_t(0), rows, 0); return; }
+    std::vector<std::thread> th;
+    const size_t per = (rows + T - 1) / T;
+    for (int t = 0; t < T; t++) {
+        size_t lo = size_t(t) * per, hi = lo + per < rows ? lo + per : rows;
+        if (lo < hi) th.emplace_back(fn, lo, hi, t);
+    }
+    for (auto& x : th) x.join();
+}
 
 }  // namespace zko

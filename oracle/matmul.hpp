@@ -8,37 +8,95 @@
 
 namespace zko {
 
+// Products of canonical values are below 2^62; folding once (2^31 == 1 mod p) leaves a term below
+// 2^32, so a 64-bit accumulator takes 2^31 of them before it has to be reduced.
+#if defined(__x86_64__) && defined(__GNUC__) && !defined(__clang__)
+#define ZKO_CLONES __attribute__((target_clones("avx2", "default")))
+#else
+#define ZKO_CLONES
+#endif
+ZKO_CLONES static uint64_t dot_fold(const uint32_t* w, const uint32_t* x, size_t n) {
+    uint64_t acc = 0;
+    for (size_t j = 0; j < n; j++) {
+        uint64_t p = uint64_t(w[j]) * x[j];
+        acc += (p & P31) + (p >> 31);
+    }
+    return acc;
+}
+ZKO_CLONES static void macc_row(uint64_t* a, const uint32_t* w, size_t n, uint32_t e) {
+    for (size_t j = 0; j < n; j++) {
+        uint64_t p = uint64_t(e) * w[j];
+        a[j] += (p & P31) + (p >> 31);
+    }
+}
+ZKO_CLONES static void macc_row4(uint64_t* a0, uint64_t* a1, uint64_t* a2, uint64_t* a3, const uint32_t* w, size_t n, uint32_t e0,
+                                 uint32_t e1, uint32_t e2, uint32_t e3) {
+    for (size_t j = 0; j < n; j++) {
+        const uint64_t x = w[j];
+        uint64_t p0 = e0 * x, p1 = e1 * x, p2 = e2 * x, p3 = e3 * x;
+        a0[j] += (p0 & P31) + (p0 >> 31);
+        a1[j] += (p1 & P31) + (p1 >> 31);
+        a2[j] += (p2 & P31) + (p2 >> 31);
+        a3[j] += (p3 & P31) + (p3 >> 31);
+    }
+}
+static_assert(sizeof(F) == 4, "F is a bare u32: vectors of F are read as u32 arrays");
+
 // transformer/mod.rs:140-163 — y[i] = sum_j W[i,j] x[j] (+ bias), exact mod p.
 inline VF matmul_forward(const VF& w, const VF& x, size_t m, size_t n, const VF* bias = nullptr) {
     VF y(m);
-    for (size_t i = 0; i < m; i++) {
-        unsigned __int128 acc = 0;
-        for (size_t j = 0; j < n; j++) acc += uint64_t(w[i * n + j].v) * x[j].v;
-        F v = F(uint32_t(uint64_t(acc % P31)));
-        if (bias) v += (*bias)[i];
-        y[i] = v;
-    }
+    const uint32_t* wp = reinterpret_cast<const uint32_t*>(w.data());
+    const uint32_t* xp = reinterpret_cast<const uint32_t*>(x.data());
+    par_rows(m, [&](size_t lo, size_t hi, int) {
+        for (size_t i = lo; i < hi; i++) {
+            F v = F(reduce64(dot_fold(wp + i * n, xp, n)));
+            if (bias) v += (*bias)[i];
+            y[i] = v;
+        }
+    });
     return y;
 }
 
-// matmul.rs:76-128 — w_partial[j] = sum_i eq_r[i] W[i,j], zero-padded to n_pad.
+// matmul.rs:76-128 — w_partial[j] = sum_i eq_r[i] W[i,j], zero-padded to n_pad; per-worker partial
+// vectors merged at the end, as the reference does.
 inline VF fold_eq_matvec(const VF& w, size_t m, size_t n, size_t n_pad, const VF& r_point) {
     size_t m_pad = size_t(1) << r_point.size();
     VF eq = eq_evals(r_point);
-    VF out(n_pad, F::zero());
     size_t rows = m < m_pad ? m : m_pad;
-    for (size_t i = 0; i < rows; i++)
-        for (size_t j = 0; j < n; j++) out[j] += eq[i] * w[i * n + j];
+    const uint32_t* wp = reinterpret_cast<const uint32_t*>(w.data());
+    const int T = matrix_threads() > 1 ? matrix_threads() : 1;
+    std::vector<std::vector<uint64_t>> part(T);
+    par_rows(rows, [&](size_t lo, size_t hi, int t) {
+        part[t].assign(n, 0);
+        for (size_t i = lo; i < hi; i++) macc_row(part[t].data(), wp + i * n, n, eq[i].v);
+    });
+    VF out(n_pad, F::zero());
+    for (auto& pt : part)
+        for (size_t j = 0; j < pt.size(); j++) out[j] += F(reduce64(pt[j]));
     return out;
 }
 // matmul.rs:743-835 — EF weights eq_r[i], base-field W; four independent base accumulators.
 inline VEF fold_eq_matvec_ef(const VF& w, size_t m, size_t n, size_t n_pad, const VEF& r_point) {
     size_t m_pad = size_t(1) << r_point.size();
     VEF eq = eq_evals_ef(r_point);
-    VEF out(n_pad, EF::zero());
     size_t rows = m < m_pad ? m : m_pad;
-    for (size_t i = 0; i < rows; i++)
-        for (size_t j = 0; j < n; j++) out[j] += eq[i] * w[i * n + j];
+    const uint32_t* wp = reinterpret_cast<const uint32_t*>(w.data());
+    const int T = matrix_threads() > 1 ? matrix_threads() : 1;
+    std::vector<std::vector<uint64_t>> part(T);
+    par_rows(rows, [&](size_t lo, size_t hi, int t) {
+        part[t].assign(4 * n, 0);
+        uint64_t* a = part[t].data();
+        for (size_t i = lo; i < hi; i++) {
+            auto e = eq[i].arr();
+            macc_row4(a, a + n, a + 2 * n, a + 3 * n, wp + i * n, n, e[0], e[1], e[2], e[3]);
+        }
+    });
+    VEF out(n_pad, EF::zero());
+    for (auto& pt : part) {
+        if (pt.empty()) continue;
+        for (size_t j = 0; j < n; j++)
+            out[j] += EF(C(F(reduce64(pt[j])), F(reduce64(pt[n + j]))), C(F(reduce64(pt[2 * n + j])), F(reduce64(pt[3 * n + j]))));
+    }
     return out;
 }
 

@@ -110,12 +110,18 @@ inline Digest hash_node_aes(const Digest& l, const Digest& r) {
 }
 // pcs.rs:125-134
 inline Digest hash_node_blake3(const Digest& l, const Digest& r) {
-    uint8_t buf[32];
-    memcpy(buf, l.data(), 16);
-    memcpy(buf + 16, r.data(), 16);
-    auto full = blake3(buf, 32);
+    // blake3 of a 32-byte message is one compression: a single chunk of one block that is also the
+    // root (the general path in hash.hpp computes the same; tests/test_oracle_pcs.py checks it
+    // against the blake3 wheel).
+    uint32_t block[16] = {0}, out[16];
+    for (int i = 0; i < 4; i++) {
+        block[i] = uint32_t(l[4 * i]) | uint32_t(l[4 * i + 1]) << 8 | uint32_t(l[4 * i + 2]) << 16 | uint32_t(l[4 * i + 3]) << 24;
+        block[4 + i] = uint32_t(r[4 * i]) | uint32_t(r[4 * i + 1]) << 8 | uint32_t(r[4 * i + 2]) << 16 | uint32_t(r[4 * i + 3]) << 24;
+    }
+    b3::compress(b3::IV, block, 0, 32, b3::CHUNK_START | b3::CHUNK_END | b3::ROOT, out);
     Digest o;
-    memcpy(o.data(), full.data(), 16);
+    for (int i = 0; i < 4; i++)
+        for (int b = 0; b < 4; b++) o[4 * i + b] = uint8_t(out[i] >> (8 * b));
     return o;
 }
 inline Digest hash_node(const Digest& l, const Digest& r, int kind) {
@@ -144,12 +150,16 @@ struct MerkleTree {
         for (size_t i = 0; i < n; i++) values[i] = w[i].v;
         layers.emplace_back();
         std::vector<Digest> first(n_pad / 2);
-        for (size_t i = 0; i < n_pad / 2; i++) first[i] = hash_node(hash_leaf(values[2 * i]), hash_leaf(values[2 * i + 1]), kind);
+        par_rows(n_pad / 2, [&](size_t lo, size_t hi, int) {
+            for (size_t i = lo; i < hi; i++) first[i] = hash_node(hash_leaf(values[2 * i]), hash_leaf(values[2 * i + 1]), kind);
+        });
         layers.push_back(std::move(first));
         while (layers.back().size() > 1) {
             const auto& prev = layers.back();
             std::vector<Digest> next(prev.size() / 2);
-            for (size_t i = 0; i < next.size(); i++) next[i] = hash_node(prev[2 * i], prev[2 * i + 1], kind);
+            par_rows(next.size(), [&](size_t lo, size_t hi, int) {
+                for (size_t i = lo; i < hi; i++) next[i] = hash_node(prev[2 * i], prev[2 * i + 1], kind);
+            });
             layers.push_back(std::move(next));
         }
     }

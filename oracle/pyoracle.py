@@ -362,6 +362,60 @@ def qwen_layer_prove(config: dict, weights: dict, x, silu_out, sigmoid_out, laye
     return y, bytes(buf[:n]), (bool(acc.value) if verify else None)
 
 
+class QwenLayer:
+    """A layer whose weights are converted and committed once (what the reference's server does at
+    load time); `prove` then costs forward + prove only, which is what the reference's
+    prove_time_ms covers (pipeline/mod.rs:224-229)."""
+
+    def __init__(self, config: dict, weights: dict, silu_out, sigmoid_out):
+        dims = (C.c_uint64 * 7)(*[int(config.get(k, 0)) for k in DIM_NAMES])
+        keep = [np.ascontiguousarray(weights[k], dtype=np.uint32) for k in WEIGHT_NAMES]
+        wp = (u32p * 10)(*[a.ctypes.data_as(u32p) for a in keep])
+        S, ps = _u32(silu_out); G, pg = _u32(sigmoid_out)
+        lib().zko_qwen_layer_new.restype = C.c_void_p
+        self.h = C.c_void_p(lib().zko_qwen_layer_new(dims, wp, ps, pg, C.c_size_t(S.size)))
+        self.d_model = int(config["d_model"])
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            lib().zko_qwen_layer_free(self.h)
+            self.h = None
+
+    def prove(self, x, layer_idx: int, input_hash: bytes, verify=False):
+        """Forward + prove; returns (y, proof bytes, accepted or None)."""
+        X, px = _u32(x)
+        y = np.zeros(self.d_model, np.uint32)
+        acc = C.c_int(-1)
+        cap = 1 << 24
+        buf = (C.c_uint8 * cap)()
+        lib().zko_qwen_layer_prove_h.restype = C.c_size_t
+        n = lib().zko_qwen_layer_prove_h(self.h, px, C.c_uint32(layer_idx), _u8(input_hash), y.ctypes.data_as(u32p), buf, C.c_size_t(cap),
+                                         C.c_int(int(verify)), C.byref(acc))
+        return y, bytes(buf[:n]), (bool(acc.value) if verify else None)
+
+
+def _layer_forward(self, x):
+    """qwen_forward_indexed alone (keeps the trace for prove_trace); returns the layer output."""
+    X, px = _u32(x)
+    y = np.zeros(self.d_model, np.uint32)
+    lib().zko_qwen_layer_forward_h(self.h, px, y.ctypes.data_as(u32p))
+    return y
+
+
+def _layer_prove_trace(self, layer_idx: int, input_hash: bytes) -> bytes:
+    """prove_qwen_layer_precommitted_ef on the trace of the last forward."""
+    return _bytes_call(lib().zko_qwen_layer_prove_trace_h, self.h, C.c_uint32(layer_idx), _u8(input_hash), cap=1 << 22)
+
+
+QwenLayer.forward = _layer_forward
+QwenLayer.prove_trace = _layer_prove_trace
+
+
+def set_threads(n: int):
+    """Worker threads of the row-parallel matrix loops (the reference uses rayon there); 1 = serial."""
+    lib().zko_set_threads(C.c_int(int(n)))
+
+
 # ---- Merkle tree and Basefold (oracle/pcs.hpp, oracle/basefold.hpp) ------------------------------
 NODE_BLAKE3, NODE_AES_MMO = 0, 1
 
