@@ -41,6 +41,34 @@ def algorithmic_bytes(n):
     return per, sum(per)
 
 
+def schedule_bytes(n, launches):
+    """Bytes each launch of OUR schedule has to move for two tables of N = 2^n elements (they equal
+    the DRAM traffic ncu measures, see profiles/): launch 0 reads the base tables for the round-0
+    message (8 N), launch 1 reads them again for the round-1 message (8 N), launch 2 reads them a
+    third time, folds r_0 and r_1 at once and writes the quarter-length EF tables (8 N + 8 N), and
+    launch k >= 3 folds r_(k-1): reads two EF tables of N / 2^(k-1) elements and writes them at half
+    length (96 N / 2^k).  In all 56 N per sumcheck against 72 N in the per-round formula above
+    (which has the first fold write half-length EF tables) and 80 N when round 0 is a separate pass."""
+    N = 1 << n
+    per = [8 * N, 8 * N, 16 * N]
+    for k in range(3, launches):
+        per.append(96 * N >> k)
+    return per[:launches]
+
+
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) over the schedule bytes above, from the ncu
+# captures summarised in profiles/sumcheck_kernels_product_ef.md (n = 25, one launch of each kernel).
+NCU_TRAFFIC_RATIO = {0: None, 1: None, 2: None, "ef": None}
+
+
+def fill_random(rng, dst):
+    """Uniform values in [0, p) into a (pinned) u32 array, chunk by chunk."""
+    chunk = 1 << 24
+    for off in range(0, dst.size, chunk):
+        m = min(chunk, dst.size - off)
+        dst[off:off + m] = rng.integers(0, P, m, dtype=np.uint32)
+
+
 class ClockSampler:
     """Samples SM clocks / throttle reasons with nvidia-smi while the timed region runs."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
@@ -181,18 +209,21 @@ def cpu_qwen_leg(n_layers_total, sample_layers, threads, gpu_proofs_by_layer=Non
         cur = L.forward(cur)
     t_fwd = time.perf_counter() - t0
     O.set_threads(1)
+    conc = min(threads, sample_layers)           # layer proofs in flight; the other cores go to the matrix loops inside them
+    O.set_threads(max(1, threads // conc))
     t1 = time.perf_counter()
-    with ThreadPoolExecutor(threads) as pool:
+    with ThreadPoolExecutor(conc) as pool:
         proofs = list(pool.map(lambda i: layers[i].prove_trace(i, ih), range(sample_layers)))
     t_prove = time.perf_counter() - t1
+    O.set_threads(1)
     checked = 0
     if gpu_proofs_by_layer is not None:
         for i, p in enumerate(proofs):
             assert gpu_proofs_by_layer[i] == p, f"layer {i}: the GPU proof differs from the CPU restatement's"
             checked += 1
     scale = n_layers_total / sample_layers
-    waves = -(-n_layers_total // threads)
-    per_wave = t_prove / -(-sample_layers // threads)
+    waves = -(-n_layers_total // conc)
+    per_wave = t_prove / -(-sample_layers // conc)
     full_ms = (t_fwd * scale + per_wave * waves) * 1e3
     return {"full_ms": full_ms, "sample_ms": (t_fwd + t_prove) * 1e3, "forward_ms": t_fwd * 1e3, "prove_ms": t_prove * 1e3,
             "proof_bytes": sum(len(p) for p in proofs), "checked": checked, "sha256": sample_digest(proofs)}
@@ -201,10 +232,10 @@ def cpu_qwen_leg(n_layers_total, sample_layers, threads, gpu_proofs_by_layer=Non
 def cpu_qwen_summary(r, sample, threads, n_layers):
     return {"value": round(r["full_ms"], 1), "unit": "ms", "cores": threads, "kind": "port",
             "sample": f"layers 0..{sample - 1} of the same workload (same weights, chained activations and input hash): forward chain "
-                      f"{r['forward_ms']:.0f} ms with matrix rows over {threads} threads, then {sample} layer proofs concurrently, one thread "
-                      f"each, {r['prove_ms']:.0f} ms; scaled to {n_layers} layers ({n_layers}/{sample} x forward + "
-                      f"ceil({n_layers}/{threads}) proof waves); weights committed beforehand as in the reference; C++ restatement built "
-                      f"-O3 (reference Rust binary: unavailable on this box)",
+                      f"{r['forward_ms']:.0f} ms with matrix rows over {threads} threads, then {sample} layer proofs concurrently with "
+                      f"{max(1, threads // min(threads, sample))} thread(s) each, {r['prove_ms']:.0f} ms; scaled to {n_layers} layers "
+                      f"({n_layers}/{sample} x forward + ceil({n_layers}/{min(threads, sample)}) proof waves); weights committed beforehand as in "
+                      f"the reference; C++ restatement built -O3 (reference Rust binary: unavailable on this box)",
             "proofs_compared_with_gpu": r["checked"], "sample_proof_sha256": r["sha256"],
             "published_reference_ms": PUBLISHED_QWEN4B_MS,
             "port_over_published": round(r["full_ms"] / PUBLISHED_QWEN4B_MS, 2)}
@@ -229,18 +260,41 @@ def cpu_sumcheck_leg(n_cpu, steps, warmup):
     return algorithmic_bytes(n_cpu)[1] / dt / 1e9, dt * 1e3
 
 
+def sumcheck_roofline(n_local, prof, peak, src, world=1):
+    """Per-launch GB/s of one (per-GPU) product sumcheck from the CUDA-event times of its launches
+    (prof[i] = ms of launch i; the last entry is the single-CTA tail) and the roofline object of the
+    launch that takes the most time."""
+    multi = len(prof) - 1                       # multi-CTA launches
+    sched = schedule_bytes(n_local, multi)
+    rows = [(sched[i] / (prof[i] * 1e-3) / 1e9, prof[i], i) for i in range(multi) if prof[i] > 0]
+    dom = max(rows, key=lambda t: t[1]) if rows else (0.0, 0.0, 0)
+    names = {0: "sc_product_base_kernel<Fe,false> (round-0 message: reads both base tables)",
+             1: "sc_product_base_kernel<Fe,true,false> (round-1 message from nine coefficient sums: reads both base tables)",
+             2: "sc_product_base_fold2_kernel (reads both base tables, folds r_0 and r_1, writes the quarter-length EF tables, round-2 message)"}
+    kname = names.get(dom[2], f"sc_round_kernel<PRODUCT,Fe,Fe,fold> (launch {dom[2]}: folds r_{dom[2] - 1}, round-{dom[2]} message)")
+    ratio = NCU_TRAFFIC_RATIO.get(dom[2] if dom[2] < 3 else "ef")
+    l2 = 126e6
+    big = [r for r in rows if sched[r[2]] > 2 * l2]
+    return {"bound": "hbm", "achieved": round(dom[0], 1), "peak": peak, "unit": "GB/s", "frac": round(dom[0] / peak, 4) if peak else None,
+            "traffic": int(ratio * sched[dom[2]]) if ratio else None,
+            "traffic_source": "bytes of the launch x the dram/bytes ratio ncu measured on this kernel at n = 25 (profiles/)" if ratio else None,
+            "peak_source": src, "kernel": f"{kname}: {sched[dom[2]]} bytes in {dom[1]:.4f} ms" + (f" on one of {world} GPUs" if world > 1 else ""),
+            "bytes_definition": "bytes the launch must move in this schedule (equal to its DRAM traffic); the whole sumcheck moves 56 * 2^n "
+                                "bytes where the per-round formula of the metric counts 72 * 2^n",
+            "per_launch_gbps": [round(t[0], 1) for t in rows[:14]], "per_launch_ms": [round(t, 4) for t in prof[:16]],
+            "per_launch_frac": [round(t[0] / peak, 3) for t in rows[:14]] if peak else None,
+            "min_frac_of_launches_larger_than_L2": round(min(r[0] for r in big) / peak, 3) if big and peak else None,
+            "tail_ms": round(prof[-1], 4) if prof else None}
+
+
 def run_sumcheck(zk, ctx, n, steps, warmup, rank, with_e2e, barrier=lambda: None, max_over_ranks=lambda x: x, world=1):
     """Returns the measured fields of the microbench (value in GB/s over the 72 * 2^n algorithmic bytes)."""
     N = 1 << n
     rng = np.random.default_rng(20251125 + rank)
     f_host, g_host = ctx.pinned_u32(N), ctx.pinned_u32(N)
-    chunk = 1 << 24
-    for off in range(0, N, chunk):
-        m = min(chunk, N - off)
-        f_host[off:off + m] = rng.integers(0, P, m, dtype=np.int64).astype(np.uint32)
-        g_host[off:off + m] = rng.integers(0, P, m, dtype=np.int64).astype(np.uint32)
+    fill_random(rng, f_host); fill_random(rng, g_host)
     f_dev, g_dev = ctx.upload(f_host), ctx.upload(g_host)
-    per_launch_bytes, total_bytes = algorithmic_bytes(n)
+    _, total_bytes = algorithmic_bytes(n)
 
     def step(tabs):
         return zk.prove_product_ef(tabs[0], tabs[1], n, zk.Transcript(ctx, b"bench-product"))
@@ -262,19 +316,12 @@ def run_sumcheck(zk, ctx, n, steps, warmup, rank, with_e2e, barrier=lambda: None
     assert out[0].round_polys.tolist() == ref[0].round_polys.tolist()
     ms_step = max_over_ranks(ms_total / steps)
     prof = (prof_acc / steps).tolist()
-    fold = [(per_launch_bytes[i - 1] / (prof[i] * 1e-3) / 1e9, prof[i], i) for i in range(1, len(prof) - 1) if prof[i] > 0]
-    dom = max(fold, key=lambda t: t[1]) if fold else (0.0, 0.0, 0)
     peak, src = load_peaks()
     res = {"n": n, "value_gbps": round(world * total_bytes / (ms_step * 1e-3) / 1e9, 2), "ms_per_step": round(ms_step, 4),
-           "gpu_launches": int(launches), "algorithmic_bytes_per_step": total_bytes,
-           "roofline": {"bound": "hbm", "achieved": round(dom[0], 1), "peak": peak, "unit": "GB/s", "frac": round(dom[0] / peak, 4),
-                        "traffic": int(1.04 * per_launch_bytes[dom[2] - 1]) if dom[2] == 1 else int(0.95 * per_launch_bytes[dom[2] - 1]) if dom[2] else None,
-                        "traffic_source": "algorithmic bytes x the dram/algorithmic ratio ncu measured on this kernel at n = 25 "
-                                          "(1.04 for the round-1 launch, 0.95 for EF rounds)",
-                        "peak_source": src,
-                        "kernel": f"sc_round_kernel fold launch {dom[2]} (folds round {dom[2] - 1}): "
-                                  f"{per_launch_bytes[dom[2] - 1] if dom[2] else 0} algorithmic bytes in {dom[1]:.4f} ms",
-                        "per_launch_gbps": [round(t[0], 1) for t in fold[:12]], "per_launch_ms": [round(t, 4) for t in prof[:14]]}}
+           "frac_of_peak_whole_sumcheck": round(total_bytes / (ms_step * 1e-3) / 1e9 / peak, 4),
+           "value_by_schedule_bytes_gbps": round(world * 56 * N / (ms_step * 1e-3) / 1e9, 2),
+           "gpu_launches": int(launches), "algorithmic_bytes_per_step": total_bytes, "schedule_bytes_per_step": 56 * N,
+           "roofline": sumcheck_roofline(n, prof, peak, src)}
     if with_e2e:
         for _ in range(2):
             step((f_host, g_host))
@@ -291,6 +338,7 @@ def run_sumcheck(zk, ctx, n, steps, warmup, rank, with_e2e, barrier=lambda: None
                       "ms_per_step": round(ms_e2e_step, 3), "wall_ms_per_step": round(wall / steps, 3),
                       "h2d_bytes_per_step": 2 * N * 4, "d2h_bytes_per_step": (n * 12 + 8) * 4}
     f_dev.free(); g_dev.free()
+    ctx.host_free(f_host); ctx.host_free(g_host)
     return res
 
 
@@ -301,15 +349,12 @@ def run_sumcheck_split(zk, ctx, n, steps, warmup, rank, world, with_e2e, barrier
     from zklm_compile_b200 import split as zs
     xch = zs.Exchange(ctx, world, rank)
     N_local = (1 << n) // world
+    n_local = n - (world.bit_length() - 1)
     rng = np.random.default_rng(20251125 + rank)
     f_host, g_host = ctx.pinned_u32(N_local), ctx.pinned_u32(N_local)
-    chunk = 1 << 24
-    for off in range(0, N_local, chunk):
-        m = min(chunk, N_local - off)
-        f_host[off:off + m] = rng.integers(0, P, m, dtype=np.int64).astype(np.uint32)
-        g_host[off:off + m] = rng.integers(0, P, m, dtype=np.int64).astype(np.uint32)
+    fill_random(rng, f_host); fill_random(rng, g_host)
     f_dev, g_dev = ctx.upload(f_host), ctx.upload(g_host)
-    per_launch_bytes, total_bytes = algorithmic_bytes(n)
+    _, total_bytes = algorithmic_bytes(n)
 
     def step(tabs):
         return zs.sumcheck_prove_split(zk.SC_PRODUCT_EF, list(tabs), n, zk.Transcript(ctx, b"bench-product"), xch)
@@ -337,17 +382,11 @@ def run_sumcheck_split(zk, ctx, n, steps, warmup, rank, world, with_e2e, barrier
         assert len(set(allv)) == 1, "ranks disagree on the proof"
     ms_step = max_over_ranks(ms_total / steps)
     prof = (prof_acc / steps).tolist()
-    fold = [(per_launch_bytes[i - 1] / world / (prof[i] * 1e-3) / 1e9, prof[i], i) for i in range(1, len(prof) - 1) if prof[i] > 0]
-    dom = max(fold, key=lambda t: t[1]) if fold else (0.0, 0.0, 0)
     peak, src = load_peaks()
+    roof = sumcheck_roofline(n_local, prof, peak, src, world)
+    roof["kernel"] += "; each launch also exchanges the round's partial sums with the peers through NVLink peer stores"
     res = {"n": n, "value_gbps": round(total_bytes / (ms_step * 1e-3) / 1e9, 2), "ms_per_step": round(ms_step, 4),
-           "gpu_launches": int(launches), "algorithmic_bytes_per_step": total_bytes,
-           "roofline": {"bound": "hbm", "achieved": round(dom[0], 1), "peak": peak, "unit": "GB/s", "frac": round(dom[0] / peak, 4),
-                        "traffic": None, "peak_source": src,
-                        "kernel": f"sc_round_kernel fold launch {dom[2]} on one of {world} GPUs (its slice: "
-                                  f"{(per_launch_bytes[dom[2] - 1] if dom[2] else 0) // world} algorithmic bytes in {dom[1]:.4f} ms); "
-                                  "each launch also exchanges the round's partial sums with the peers",
-                        "per_launch_gbps_per_gpu": [round(t[0], 1) for t in fold[:12]], "per_launch_ms": [round(t, 4) for t in prof[:14]]}}
+           "gpu_launches": int(launches), "algorithmic_bytes_per_step": total_bytes, "proof_sha256": digest, "roofline": roof}
     if with_e2e:
         for _ in range(2):
             step((f_host, g_host))
@@ -364,6 +403,7 @@ def run_sumcheck_split(zk, ctx, n, steps, warmup, rank, world, with_e2e, barrier
                       "d2h_bytes_per_step": (n * 12 + 8) * 4 * world}
     barrier()
     f_dev.free(); g_dev.free()
+    ctx.host_free(f_host); ctx.host_free(g_host)
     xch.close()
     return res
 
@@ -554,7 +594,7 @@ def main():
     ap.add_argument("--workload", default="qwen4b", choices=["qwen4b", "sumcheck"])
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--n", "--log-n", dest="n", type=int, default=28, help="sumcheck workload: log2 of the table length")
-    ap.add_argument("--n-micro", type=int, default=26, help="log2 table length of the attached sumcheck microbench")
+    ap.add_argument("--n-micro", type=int, default=28, help="log2 table length of the attached sumcheck microbench (2^20, 2^24 and 2^26 are always attached too)")
     ap.add_argument("--n-cpu", type=int, default=24, help="sumcheck workload: log2 table length of the CPU sample")
     ap.add_argument("--cpu-layers", type=int, default=0, help="qwen4b: layers in the CPU sample (default: host cores, max 8)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
@@ -593,9 +633,9 @@ def main():
             return
         if qwen:
             sample = args.cpu_layers or min(cores, 8, args.layers)
-            r = cpu_qwen_leg(args.layers, sample, min(cores, sample))
+            r = cpu_qwen_leg(args.layers, sample, cores)
             value = ms = r["full_ms"]
-            cpu = cpu_qwen_summary(r, sample, min(cores, sample), args.layers)
+            cpu = cpu_qwen_summary(r, sample, cores, args.layers)
         else:
             gbps, ms = cpu_sumcheck_leg(args.n_cpu, max(1, min(args.steps, 3)), min(args.warmup, 1))
             value = gbps
@@ -665,9 +705,15 @@ def main():
             line["basefold_microbench"] = run_basefold(zk, micro_ctx, args.n_basefold)
             line["dense4m"] = {"ef": run_mlp(zk, micro_ctx, 5, 3, True), "base": run_mlp(zk, micro_ctx, 5, 3, False)}
     if qwen and not args.no_micro and rank == 0:
-        m = run_sumcheck(zk, micro_ctx, args.n_micro, 5, 3, 0, False)
-        line["sumcheck_microbench"] = {"metric": "sumcheck fold HBM GB/s", "n": m["n"], "value": m["value_gbps"], "unit": "GB/s",
-                                       "ms_per_step": m["ms_per_step"], "roofline": m["roofline"]}
+        # the "sumcheck fold HBM GB/s" half of the metric: the microbench configuration's four sizes on one GPU
+        sizes = {}
+        for nn in sorted({20, 24, 26, args.n_micro}):
+            m = run_sumcheck(zk, micro_ctx, nn, 5, 3, 0, False)
+            sizes[nn] = {"metric": "sumcheck fold HBM GB/s", "n": m["n"], "value": m["value_gbps"], "unit": "GB/s",
+                         "ms_per_step": m["ms_per_step"], "frac_of_peak_whole_sumcheck": m["frac_of_peak_whole_sumcheck"],
+                         "value_by_schedule_bytes_gbps": m["value_by_schedule_bytes_gbps"], "roofline": m["roofline"]}
+        line["sumcheck_microbench"] = sizes.pop(args.n_micro)
+        line["sumcheck_microbench_other_sizes"] = {str(k): v for k, v in sizes.items()}
         line["basefold_microbench"] = run_basefold(zk, micro_ctx, args.n_basefold)
         line["dense4m"] = {"ef": run_mlp(zk, micro_ctx, 5, 3, True), "base": run_mlp(zk, micro_ctx, 5, 3, False)}
     cpu = None
@@ -680,8 +726,8 @@ def main():
     if rank == 0 and world == 1 and not args.no_cpu:
         if qwen:
             sample = args.cpu_layers or min(cores, 8, args.layers)
-            r = cpu_qwen_leg(args.layers, sample, min(cores, sample), gpu_proofs_by_layer=gpu_proofs_by_layer)
-            cpu = cpu_qwen_summary(r, sample, min(cores, sample), args.layers)
+            r = cpu_qwen_leg(args.layers, sample, cores, gpu_proofs_by_layer=gpu_proofs_by_layer)
+            cpu = cpu_qwen_summary(r, sample, cores, args.layers)
         else:
             gbps, ms = cpu_sumcheck_leg(args.n_cpu, 2, 1)
             cpu = {"value": round(gbps, 4), "unit": "GB/s", "cores": 1, "kind": "port", "ms_per_step": round(ms, 2),

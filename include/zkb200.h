@@ -69,8 +69,11 @@ int32_t zkb_ctx_sync(zkb_ctx* ctx);
 /* Tuning options of one context, for measurements (none is needed in production; value 0 restores
  * the built-in choice).  ZKB_OPT_PLAIN_TAIL: nonzero = every sumcheck ends in the plain
  * single-CTA tail instead of the pipelined one.  ZKB_OPT_SINGLE_CTA_THREADS /
- * ZKB_OPT_PIPE_THREADS: thread counts of the single-CTA kernels and of the pipelined tail. */
-enum { ZKB_OPT_PLAIN_TAIL = 0, ZKB_OPT_SINGLE_CTA_THREADS = 1, ZKB_OPT_PIPE_THREADS = 2 };
+ * ZKB_OPT_PIPE_THREADS: thread counts of the single-CTA kernels and of the pipelined tail.
+ * ZKB_OPT_NO_FUSED_FOLD: nonzero = product sumchecks over base-field tables fold one challenge per
+ * launch (they normally fold the first two challenges in one pass over the base tables).
+ * ZKB_OPT_FOLD2_VEC: pair indices per thread (1, 2 or 4) of that two-challenge pass. */
+enum { ZKB_OPT_PLAIN_TAIL = 0, ZKB_OPT_SINGLE_CTA_THREADS = 1, ZKB_OPT_PIPE_THREADS = 2, ZKB_OPT_NO_FUSED_FOLD = 3, ZKB_OPT_FOLD2_VEC = 4 };
 int32_t zkb_ctx_set_option(zkb_ctx* ctx, int32_t option, int32_t value);
 /* The context's cudaStream_t (as an opaque pointer), for callers that enqueue their own work in order with the library's. */
 void* zkb_ctx_stream(zkb_ctx* ctx);

@@ -156,6 +156,16 @@ def test_context_options_keep_the_proof_bytes(ctx):
             proof, fs, gs = zk.prove_product_ef_full(f, g, nv, zk.Transcript(c2, b"opt"))
             assert proof.round_polys.reshape(nv, -1).tolist() == ref[0].tolist()
             assert fs.tolist() == ref[2][0].tolist() and gs.tolist() == ref[2][1].tolist()
+        # product sumcheck over base-field tables: two challenges folded per pass (default), one per pass, and
+        # the vector widths of the two-challenge pass all give the same proof
+        nv2 = 17
+        fb, gb = _rand(rng, 1 << nv2), _rand(rng, 1 << nv2)
+        refb = O.prove("product_ef", O.Transcript(b"opt2"), [fb, gb], nv2)
+        for opt, val in [(c2.OPT_NO_FUSED_FOLD, 1), (c2.OPT_NO_FUSED_FOLD, 0), (c2.OPT_FOLD2_VEC, 1), (c2.OPT_FOLD2_VEC, 4), (c2.OPT_FOLD2_VEC, 2)]:
+            c2.set_option(opt, val)
+            proof, fs, gs = zk.prove_product_ef(fb, gb, nv2, zk.Transcript(c2, b"opt2"))
+            assert proof.round_polys.reshape(nv2, -1).tolist() == refb[0].tolist() and proof.challenges.tolist() == refb[1].tolist()
+            assert fs.tolist() == refb[2][0].tolist() and gs.tolist() == refb[2][1].tolist()
         with pytest.raises(zk.ZkbError):
             c2.set_option(c2.OPT_PIPE_THREADS, 100)
         with pytest.raises(zk.ZkbError):

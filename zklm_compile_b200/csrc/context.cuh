@@ -117,8 +117,8 @@ struct zkb_ctx {
     // has to wait for a wide kernel to drain before it finds an SM.
     bool polite = false;
     // Tuning options (zkb_ctx_set_option): 0 = the built-in choice.
-    int opt_single_threads = 0, opt_pipe_threads = 0;
-    bool opt_plain_tail = false;
+    int opt_single_threads = 0, opt_pipe_threads = 0, opt_fold2_vec = 0;
+    bool opt_plain_tail = false, opt_no_fused2 = false;
     int single_cta_threads() const { return opt_single_threads ? opt_single_threads : (polite ? 512 : 1024); }
     int pipe_threads(int full) const { return opt_pipe_threads ? opt_pipe_threads : (polite ? full / 2 : full); }
     int wide_ctas_per_sm(int greedy, int shared) const { return polite ? shared : greedy; }

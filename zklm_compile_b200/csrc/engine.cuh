@@ -60,8 +60,11 @@ inline int grid_for(zkb_ctx* c, size_t items, int per_cta = 256, int ctas_per_sm
 #define ZKB_LAUNCHED(c) (c)->launched(__FILE__, __LINE__)
 
 
+// fused2: product sumcheck over base tables with EF challenges whose destination tables were sized
+// for the two-challenge fold (a quarter of the input): round 1 is a message-only launch and the
+// first tables written are those folded with r_0 and r_1 (sc_product_base_fold2_kernel).
 template <int KIND, class SrcT, class ChalT>
-void run_sumcheck(zkb_ctx* c, ScTables tb, u32 num_vars, ScIO io, bool dynamic) {
+void run_sumcheck(zkb_ctx* c, ScTables tb, u32 num_vars, ScIO io, bool dynamic, bool fused2 = false) {
     // split over several GPUs: the tables are this GPU's slice of 2^local_vars elements
     const u32 local_vars = io.xch ? io.xch_local_vars : num_vars;
     size_t size = size_t(1) << local_vars;
@@ -88,10 +91,26 @@ void run_sumcheck(zkb_ctx* c, ScTables tb, u32 num_vars, ScIO io, bool dynamic) 
                 else sc_round_kernel<KIND, SrcT, ChalT, false><<<grid, 256, 0, c->stream>>>(tb, half, round, io);
             } else sc_round_kernel<KIND, SrcT, ChalT, false><<<grid, 256, 0, c->stream>>>(tb, half, round, io);
         } else if (in_src) {
+            bool done = false;
             if constexpr (base_product_t && std::is_same<ChalT, Fe>::value) {
-                if (base_product) sc_product_base_kernel<Fe, true><<<vgrid, 256, 0, c->stream>>>(tb, half, round, io);
-                else sc_round_kernel<KIND, SrcT, ChalT, true><<<grid, 256, 0, c->stream>>>(tb, half, round, io);
-            } else sc_round_kernel<KIND, SrcT, ChalT, true><<<grid, 256, 0, c->stream>>>(tb, half, round, io);
+                if (base_product && fused2) {
+                    // round 1: message only; round 2: both challenges folded in, tables shrink to a quarter
+                    sc_product_base_kernel<Fe, true, false><<<vgrid, 256, 0, c->stream>>>(tb, half, round, io);
+                    ZKB_LAUNCHED(c);
+                    c->prof_mark();
+                    round++;
+                    const size_t E = size / 8;
+                    const int vec = c->opt_fold2_vec ? c->opt_fold2_vec : 2;
+                    const size_t want2 = (E / vec + 255) / 256;
+                    const int g2 = (int)(want2 < (size_t)max_grid ? want2 : (size_t)max_grid);
+                    if (vec == 1) sc_product_base_fold2_kernel<1><<<g2, 256, 0, c->stream>>>(tb, E, round, io);
+                    else if (vec == 4) sc_product_base_fold2_kernel<4><<<g2, 256, 0, c->stream>>>(tb, E, round, io);
+                    else sc_product_base_fold2_kernel<2><<<g2, 256, 0, c->stream>>>(tb, E, round, io);
+                    size /= 2;                          // two folds in all: one here, one below
+                    done = true;
+                } else if (base_product) { sc_product_base_kernel<Fe, true><<<vgrid, 256, 0, c->stream>>>(tb, half, round, io); done = true; }
+            }
+            if (!done) sc_round_kernel<KIND, SrcT, ChalT, true><<<grid, 256, 0, c->stream>>>(tb, half, round, io);
             for (int t = 0; t < 3; t++) tb.src[t] = tb.dst[t];
             in_src = false;
             size /= 2;
@@ -136,7 +155,11 @@ inline ScRec sumcheck_enqueue(zkb_ctx* c, TrState* tr, int kind, const u32* cons
     const size_t n = size_t(1) << local_vars;      // elements per table held by this GPU
     const bool ef_inputs = ki.in_w[0] == 4;
     ScTables tb{};
-    const size_t dst_elems = n / 2 > 2 ? n / 2 : 2;
+    // product sumcheck over 16-byte aligned base tables with EF challenges, at least 2^15 elements:
+    // the two-challenge fold applies and the folded tables need a quarter of the input length
+    const bool fused2 = kind == ZKB_SC_PRODUCT_EF && !o.dyn_nv && local_vars >= 15 && !c->opt_no_fused2 &&
+                        ((((uintptr_t)tables_dev[0]) | ((uintptr_t)tables_dev[1])) & 15) == 0;
+    const size_t dst_elems = fused2 ? n / 4 : (n / 2 > 2 ? n / 2 : 2);
     for (int t = 0; t < ki.nt; t++) {
         tb.src[t] = tables_dev[t];
         if (o.clobber[t] && ki.in_w[t] == 4) tb.dst[t] = const_cast<u32*>(tables_dev[t]);
@@ -168,7 +191,7 @@ inline ScRec sumcheck_enqueue(zkb_ctx* c, TrState* tr, int kind, const u32* cons
         case ZKB_SC_PRODUCT:              run_sumcheck<SC_PRODUCT, Fp, Fp>(c, tb, num_vars, io, dyn); break;
         case ZKB_SC_TRIPLE:               run_sumcheck<SC_TRIPLE, Fp, Fp>(c, tb, num_vars, io, dyn); break;
         case ZKB_SC_PRODUCT_ONES:         run_sumcheck<SC_ONES, Fp, Fp>(c, tb, num_vars, io, dyn); break;
-        case ZKB_SC_PRODUCT_EF:           run_sumcheck<SC_PRODUCT, Fp, Fe>(c, tb, num_vars, io, dyn); break;
+        case ZKB_SC_PRODUCT_EF:           run_sumcheck<SC_PRODUCT, Fp, Fe>(c, tb, num_vars, io, dyn, fused2); break;
         case ZKB_SC_PRODUCT_EF_FULL:
         case ZKB_SC_PRODUCT_EF_MIXED:     run_sumcheck<SC_PRODUCT, Fe, Fe>(c, tb, num_vars, io, dyn); break;
         case ZKB_SC_TRIPLE_EF_FULL:       run_sumcheck<SC_TRIPLE, Fe, Fe>(c, tb, num_vars, io, dyn); break;

@@ -255,7 +255,9 @@ __device__ __forceinline__ void ld4(const void* base, size_t j, u32* o) {
     o[0] = t.x; o[1] = t.y; o[2] = t.z; o[3] = t.w;
 }
 
-template <class ChalT, bool FOLD>
+// WRITE = false (with FOLD): the folded tables are not materialised - the launch only produces
+// the round message (the fused launch below folds two challenges at once from the base tables).
+template <class ChalT, bool FOLD, bool WRITE = true>
 __global__ void __launch_bounds__(256) sc_product_base_kernel(ScTables tb, size_t half, u32 round, ScIO io) {
     constexpr int NACC = FOLD ? 9 : 3;
     __shared__ u32 red[32 * 16];
@@ -288,13 +290,14 @@ __global__ void __launch_bounds__(256) sc_product_base_kernel(ScTables tb, size_
             for (int v = 0; v < 4; v++) {
                 const u32 ef = sub31(fb[v], fa[v]), eg = sub31(gb[v], ga[v]);       // lo = a + r e
                 const u32 hf = sub31(fd[v], fc[v]), hg = sub31(gd[v], gc[v]);       // hi = c + r h
-                // folded tables (EF = base + r * base)
-                Fe lf = r * Fp{ef}; lf.x = add31(lf.x, fa[v]);
-                Fe lg = r * Fp{eg}; lg.x = add31(lg.x, ga[v]);
-                Fe uf = r * Fp{hf}; uf.x = add31(uf.x, fc[v]);
-                Fe ug = r * Fp{hg}; ug.x = add31(ug.x, gc[v]);
-                st_el<Fe>(tb.dst[0], j + v, lf); st_el<Fe>(tb.dst[0], j + half + v, uf);
-                st_el<Fe>(tb.dst[1], j + v, lg); st_el<Fe>(tb.dst[1], j + half + v, ug);
+                if constexpr (WRITE) {      // folded tables (EF = base + r * base)
+                    Fe lf = r * Fp{ef}; lf.x = add31(lf.x, fa[v]);
+                    Fe lg = r * Fp{eg}; lg.x = add31(lg.x, ga[v]);
+                    Fe uf = r * Fp{hf}; uf.x = add31(uf.x, fc[v]);
+                    Fe ug = r * Fp{hg}; ug.x = add31(ug.x, gc[v]);
+                    st_el<Fe>(tb.dst[0], j + v, lf); st_el<Fe>(tb.dst[0], j + half + v, uf);
+                    st_el<Fe>(tb.dst[1], j + v, lg); st_el<Fe>(tb.dst[1], j + half + v, ug);
+                }
                 // coefficient sums
                 acc[0] += fold62((u64)fa[v] * ga[v]);
                 acc[1] += fold62((u64)fa[v] * eg + (u64)ga[v] * ef);
@@ -349,6 +352,98 @@ __global__ void __launch_bounds__(256) sc_product_base_kernel(ScTables tb, size_
         } else {
             sc_finish_round<SC_PRODUCT, Fp, ChalT>(t, io, round, tr);
         }
+        tr_store(tr, io.tr);
+        *io.counter = 0;
+    }
+}
+
+// ---- product sumcheck over base-field tables: two challenges folded in one pass -----------------
+// Rounds 0 and 1 only need the base tables (round 1's message comes from the coefficient sums
+// above), so the first extension-field tables that are ever written are the ones folded with BOTH
+// r_0 and r_1: a quarter of the input length instead of a half.  For the table index
+// i = j + q0 E + q1 2E + q2 4E (E = an eighth of the table, j < E) the two folds give
+//     T2[j + q0 E] = t00 + r0 (t01 - t00) + r1 (t10 - t00) + r0 r1 (t11 - t10 - t01 + t00),  t_{q1 q2} = T[i],
+// three EF x base products whose coordinates are summed in 64 bits and folded once.  In the same
+// pass the message of round 2 is accumulated over the pairs (T2[j], T2[j + E]).  Against folding
+// round by round this launch and the one before it move 24 N bytes instead of 48 N (N = table length).
+__device__ __forceinline__ Fe fold2_el(u32 t00, u32 t01, u32 t10, u32 t11, Fe r0, Fe r1, Fe r01) {
+    const u32 b = sub31(t01, t00), c = sub31(t10, t00), d = sub31(sub31(t11, t10), b);
+    Fe o;
+    o.x = red64((u64)r0.x * b + (u64)r1.x * c + (u64)r01.x * d + t00);
+    o.y = red64((u64)r0.y * b + (u64)r1.y * c + (u64)r01.y * d);
+    o.z = red64((u64)r0.z * b + (u64)r1.z * c + (u64)r01.z * d);
+    o.w = red64((u64)r0.w * b + (u64)r1.w * c + (u64)r01.w * d);
+    return o;
+}
+template <int VEC> struct LdVec;
+template <> struct LdVec<1> { static __device__ __forceinline__ void ld(const u32* p, u32* o) { o[0] = *p; } };
+template <> struct LdVec<2> { static __device__ __forceinline__ void ld(const u32* p, u32* o) { uint2 t = *reinterpret_cast<const uint2*>(p); o[0] = t.x; o[1] = t.y; } };
+template <> struct LdVec<4> { static __device__ __forceinline__ void ld(const u32* p, u32* o) { uint4 t = *reinterpret_cast<const uint4*>(p); o[0] = t.x; o[1] = t.y; o[2] = t.z; o[3] = t.w; } };
+
+// tables: 8 E base-field words each; dst: 2 E extension-field elements each; `round` is the round
+// whose message is produced (2); challenges of rounds round-2 and round-1 are read from io.chal.
+template <int VEC>
+__global__ void __launch_bounds__(256) sc_product_base_fold2_kernel(ScTables tb, size_t E, u32 round, ScIO io) {
+    __shared__ u32 red[32 * 16];
+    __shared__ __align__(16) unsigned char trbuf[TR_SCRATCH_BYTES];
+    __shared__ bool is_last;
+    Fe r0, r1;
+    from_words(r0, io.chal + (size_t)(round - 2) * 4);
+    from_words(r1, io.chal + (size_t)(round - 1) * 4);
+    const Fe r01 = r0 * r1;
+    Fe acc[3] = {fe_zero(), fe_zero(), fe_zero()};
+    const size_t stride = (size_t)gridDim.x * blockDim.x * VEC;
+    for (size_t j = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC; j < E; j += stride) {
+        Fe lo[2][VEC], hi[2][VEC];
+#pragma unroll
+        for (int t = 0; t < 2; t++) {
+            const u32* src = reinterpret_cast<const u32*>(tb.src[t]) + j;
+            u32 q[8][VEC];
+#pragma unroll
+            for (int k = 0; k < 8; k++) LdVec<VEC>::ld(src + (size_t)k * E, q[k]);
+#pragma unroll
+            for (int v = 0; v < VEC; v++) {
+                // q index = q0 + 2 q1 + 4 q2: t_{q1 q2} of the lower element is q[2 q1 + 4 q2], of the upper one q[1 + 2 q1 + 4 q2]
+                lo[t][v] = fold2_el(q[0][v], q[4][v], q[2][v], q[6][v], r0, r1, r01);
+                hi[t][v] = fold2_el(q[1][v], q[5][v], q[3][v], q[7][v], r0, r1, r01);
+                st_el<Fe>(tb.dst[t], j + v, lo[t][v]);
+                st_el<Fe>(tb.dst[t], j + E + v, hi[t][v]);
+            }
+        }
+#pragma unroll
+        for (int v = 0; v < VEC; v++) {
+            acc[0] = acc[0] + lo[0][v] * lo[1][v];
+            acc[1] = acc[1] + hi[0][v] * hi[1][v];
+            acc[2] = acc[2] + dbl_minus(hi[0][v], lo[0][v]) * dbl_minus(hi[1][v], lo[1][v]);
+        }
+    }
+    u32 w[12];
+#pragma unroll
+    for (int k = 0; k < 3; k++) to_words(acc[k], w + 4 * k);
+    block_sum_words<12>(w, red);
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int k = 0; k < 12; k++) io.partials[(size_t)blockIdx.x * 16 + k] = w[k];
+        __threadfence();
+        unsigned int ticket = atomicAdd(io.counter, 1u);
+        is_last = (ticket == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    u32 t[12];
+#pragma unroll
+    for (int k = 0; k < 12; k++) t[k] = 0;
+    for (u32 b = threadIdx.x; b < gridDim.x; b += blockDim.x) {
+#pragma unroll
+        for (int k = 0; k < 12; k++) t[k] = add31(t[k], __ldcg(io.partials + (size_t)b * 16 + k));
+    }
+    block_sum_words<12>(t, red);
+    if (io.xch && threadIdx.x < 32) xch_allreduce_warp<12>(*io.xch, io.xch->seq + round, t);
+    if (threadIdx.x == 0) {
+        Tr tr;
+        tr_load(tr, io.tr, trbuf);
+        sc_finish_round<SC_PRODUCT, Fe, Fe>(t, io, round, tr);
         tr_store(tr, io.tr);
         *io.counter = 0;
     }

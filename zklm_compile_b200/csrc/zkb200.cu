@@ -350,6 +350,10 @@ int32_t zkb_ctx_set_option(zkb_ctx* c, int32_t option, int32_t value) {
         case ZKB_OPT_PIPE_THREADS:
             if (value != 0 && (value < 96 || value > PIPE_THREADS || value % 32)) { c->err = "pipelined-tail thread count must be 0 or a multiple of 32 in [96, 512]"; return ZKB_E_ARG; }
             c->opt_pipe_threads = value; break;
+        case ZKB_OPT_NO_FUSED_FOLD: c->opt_no_fused2 = value != 0; break;
+        case ZKB_OPT_FOLD2_VEC:
+            if (value != 0 && value != 1 && value != 2 && value != 4) { c->err = "fold2 vector width must be 0, 1, 2 or 4"; return ZKB_E_ARG; }
+            c->opt_fold2_vec = value; break;
         default: c->err = "unknown option"; return ZKB_E_ARG;
     }
     c->arena_epoch++;                  // captured graphs hold the old launch shapes

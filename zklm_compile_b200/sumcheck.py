@@ -63,7 +63,7 @@ class Context:
         of every SM free (see zkb_ctx_set_shared in include/zkb200.h)."""
         check(self.h, _lib.lib().zkb_ctx_set_shared(self.h, C.c_int32(1 if on else 0)))
 
-    OPT_PLAIN_TAIL, OPT_SINGLE_CTA_THREADS, OPT_PIPE_THREADS = 0, 1, 2
+    OPT_PLAIN_TAIL, OPT_SINGLE_CTA_THREADS, OPT_PIPE_THREADS, OPT_NO_FUSED_FOLD, OPT_FOLD2_VEC = 0, 1, 2, 3, 4
 
     def set_option(self, option: int, value: int):
         """Tuning options for measurements (zkb_ctx_set_option in include/zkb200.h); 0 = built-in choice."""
@@ -121,10 +121,14 @@ class Context:
         return buf
 
     def pinned_u32(self, n_u32: int) -> np.ndarray:
-        """numpy view of page-locked host memory (freed with the process)."""
+        """numpy view of page-locked host memory (freed with the process, or earlier by host_free)."""
         p = C.c_void_p()
         check(self.h, _lib.lib().zkb_host_alloc(self.h, C.c_size_t(n_u32 * 4), C.byref(p)))
         return np.ctypeslib.as_array(C.cast(p, u32p), shape=(n_u32,))
+
+    def host_free(self, arr: np.ndarray):
+        """Release an array obtained from pinned_u32; the array must not be used afterwards."""
+        check(self.h, _lib.lib().zkb_host_free(self.h, C.c_void_p(arr.ctypes.data)))
 
     def alloc(self, n_u32: int, shape=None) -> "DeviceBuffer":
         return DeviceBuffer(self, n_u32, shape or (n_u32,))
