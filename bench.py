@@ -61,12 +61,27 @@ def schedule_bytes(n, launches):
 NCU_TRAFFIC_RATIO = {0: None, 1: None, 2: None, "ef": None}
 
 
-def fill_random(rng, dst):
-    """Uniform values in [0, p) into a (pinned) u32 array, chunk by chunk."""
-    chunk = 1 << 24
+def table_values(seed, first, count, step=1):
+    """Elements first, first + step, ... of the synthetic table `seed`: SplitMix64 of the element index,
+    reduced mod p (uniform in [0, p) up to 2^-33).  Counter-based, so that every GPU of a split
+    sumcheck can produce exactly its own slice of the same table."""
+    with np.errstate(over="ignore"):
+        z = (np.arange(count, dtype=np.uint64) * np.uint64(step) + np.uint64(first)) * np.uint64(0x9E3779B97F4A7C15) + np.uint64(seed)
+        z = (z ^ (z >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+        z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+        z ^= z >> np.uint64(31)
+    return (z % np.uint64(P)).astype(np.uint32)
+
+
+def fill_table(seed, dst, rank=0, world=1):
+    """This rank's slice (elements j = rank mod world) of table `seed` into a (pinned) u32 array."""
+    chunk = 1 << 22
     for off in range(0, dst.size, chunk):
         m = min(chunk, dst.size - off)
-        dst[off:off + m] = rng.integers(0, P, m, dtype=np.uint32)
+        dst[off:off + m] = table_values(seed, (off * world) + rank, m, world)
+
+
+TABLE_SEED_F, TABLE_SEED_G = 0x5EEDF00D, 0x5EED600D
 
 
 class ClockSampler:
@@ -290,9 +305,8 @@ def sumcheck_roofline(n_local, prof, peak, src, world=1):
 def run_sumcheck(zk, ctx, n, steps, warmup, rank, with_e2e, barrier=lambda: None, max_over_ranks=lambda x: x, world=1):
     """Returns the measured fields of the microbench (value in GB/s over the 72 * 2^n algorithmic bytes)."""
     N = 1 << n
-    rng = np.random.default_rng(20251125 + rank)
     f_host, g_host = ctx.pinned_u32(N), ctx.pinned_u32(N)
-    fill_random(rng, f_host); fill_random(rng, g_host)
+    fill_table(TABLE_SEED_F, f_host); fill_table(TABLE_SEED_G, g_host)
     f_dev, g_dev = ctx.upload(f_host), ctx.upload(g_host)
     _, total_bytes = algorithmic_bytes(n)
 
@@ -317,7 +331,9 @@ def run_sumcheck(zk, ctx, n, steps, warmup, rank, with_e2e, barrier=lambda: None
     ms_step = max_over_ranks(ms_total / steps)
     prof = (prof_acc / steps).tolist()
     peak, src = load_peaks()
+    import hashlib
     res = {"n": n, "value_gbps": round(world * total_bytes / (ms_step * 1e-3) / 1e9, 2), "ms_per_step": round(ms_step, 4),
+           "proof_sha256": hashlib.sha256(out[0].round_polys.tobytes() + out[0].challenges.tobytes()).hexdigest(),
            "frac_of_peak_whole_sumcheck": round(total_bytes / (ms_step * 1e-3) / 1e9 / peak, 4),
            "value_by_schedule_bytes_gbps": round(world * 56 * N / (ms_step * 1e-3) / 1e9, 2),
            "gpu_launches": int(launches), "algorithmic_bytes_per_step": total_bytes, "schedule_bytes_per_step": 56 * N,
@@ -350,9 +366,8 @@ def run_sumcheck_split(zk, ctx, n, steps, warmup, rank, world, with_e2e, barrier
     xch = zs.Exchange(ctx, world, rank)
     N_local = (1 << n) // world
     n_local = n - (world.bit_length() - 1)
-    rng = np.random.default_rng(20251125 + rank)
     f_host, g_host = ctx.pinned_u32(N_local), ctx.pinned_u32(N_local)
-    fill_random(rng, f_host); fill_random(rng, g_host)
+    fill_table(TABLE_SEED_F, f_host, rank, world); fill_table(TABLE_SEED_G, g_host, rank, world)
     f_dev, g_dev = ctx.upload(f_host), ctx.upload(g_host)
     _, total_bytes = algorithmic_bytes(n)
 
@@ -375,7 +390,7 @@ def run_sumcheck_split(zk, ctx, n, steps, warmup, rank, world, with_e2e, barrier
     ctx.profile(False)
     assert out[0].round_polys.tolist() == ref[0].round_polys.tolist()
     # every rank must hold the same proof
-    digest = hashlib.sha256(out[0].round_polys.tobytes() + out[0].challenges.tobytes()).hexdigest()
+    digest = hashlib.sha256(np.ascontiguousarray(out[0].round_polys).tobytes() + np.ascontiguousarray(out[0].challenges).tobytes()).hexdigest()
     if dist is not None:
         allv = [None] * world
         dist.all_gather_object(allv, digest)
@@ -490,27 +505,39 @@ def run_qwen(zk, args, rank, world, local, dist, barrier, max_over_ranks):
     x_pinned = ctx0.pinned_u32(d_model)
     x_pinned[:] = x
     x_dev = ctx0.upload(x)
-    act = torch.empty(d_model, dtype=torch.int32, device=f"cuda:{local}") if world > 1 else None
+    act = act_buf = out_view = gatherer = None
+    if world > 1:
+        # the activation crosses from rank to rank device to device (NCCL send / recv of d_model words straight from
+        # the last layer's output buffer into a device tensor the next rank's first layer reads); the proofs come
+        # back to rank 0 in one gather of fixed-size byte tensors
+        act = torch.empty(d_model, dtype=torch.int32, device=f"cuda:{local}")
+        act_buf = zk.DeviceBuffer.wrap(ctx0, act.data_ptr(), d_model)
+        if model:
+            class _Out:                         # the last layer's output as a tensor, without a copy
+                __cuda_array_interface__ = {"shape": (d_model,), "typestr": "<i4", "data": (model.layers[-1].output_address(), False),
+                                            "version": 2, "strides": None}
+            out_view = torch.as_tensor(_Out(), device=f"cuda:{local}")
+        gatherer = sharding.ProofGather(dist, rank, world, 49152 * max(1, -(-L // world)) + 4096, device=f"cuda:{local}")
+
+    def hand_over():
+        if rank + 1 < world and hi < L:
+            dist.send(out_view, dst=rank + 1)
 
     def step(host_input):
         """forward (activation hops rank to rank) + prove my layers + gather on rank 0."""
         if model and world == 1:
             proofs = model.forward_and_prove(x_pinned if host_input else x_dev, ih)
         elif model:
-            def hand_over(y):
-                if rank + 1 < world and hi < L:
-                    dist.send(torch.from_numpy(y.astype(np.int32)).to(f"cuda:{local}"), dst=rank + 1)
             if rank == 0:
-                proofs = model.forward_and_prove(x_pinned if host_input else x_dev, ih, on_forward_done=hand_over)
+                proofs = model.forward_and_prove(x_pinned if host_input else x_dev, ih, on_forward_finished=hand_over)
             else:
                 dist.recv(act, src=rank - 1)
-                torch.cuda.synchronize()
-                proofs = model.forward_and_prove(act.cpu().numpy().astype(np.uint32), ih, on_forward_done=hand_over)
+                torch.cuda.current_stream().synchronize()
+                proofs = model.forward_and_prove(act_buf, ih, on_forward_finished=hand_over)
         else:
             proofs = []
         if world > 1:
-            gathered = [None] * world if rank == 0 else None
-            dist.gather_object(proofs, gathered, dst=0)
+            gathered = gatherer.gather(proofs)
             if rank == 0:
                 proofs = sharding.merge_reverse(gathered)
         return proofs
@@ -704,13 +731,23 @@ def main():
         if not args.no_micro and rank == 0:
             line["basefold_microbench"] = run_basefold(zk, micro_ctx, args.n_basefold)
             line["dense4m"] = {"ef": run_mlp(zk, micro_ctx, 5, 3, True), "base": run_mlp(zk, micro_ctx, 5, 3, False)}
+    if qwen and world > 1 and not args.no_micro:
+        # the workload that does scale with the GPUs: ONE product sumcheck of 2^n-element tables split over all of them
+        # (every rank takes part); its proof hash equals the single-GPU microbench's at the same n
+        sr = run_sumcheck_split(zk, micro_ctx, args.n_micro, 5, 3, rank, world, False, barrier, max_over_ranks, dist)
+        if rank == 0:
+            line["sumcheck_split"] = {"metric": "sumcheck fold HBM GB/s, one sumcheck split over the GPUs", "n": sr["n"], "n_gpus": world,
+                                      "value": sr["value_gbps"], "unit": "GB/s", "ms_per_step": sr["ms_per_step"], "scaling": "strong",
+                                      "proof_sha256": sr["proof_sha256"], "roofline": sr["roofline"],
+                                      "exchange": "per-round partial sums written into the peers' mailboxes by the round kernels themselves "
+                                                  "(plain peer stores over NVLink), no collective call per round"}
     if qwen and not args.no_micro and rank == 0:
         # the "sumcheck fold HBM GB/s" half of the metric: the microbench configuration's four sizes on one GPU
         sizes = {}
         for nn in sorted({20, 24, 26, args.n_micro}):
             m = run_sumcheck(zk, micro_ctx, nn, 5, 3, 0, False)
             sizes[nn] = {"metric": "sumcheck fold HBM GB/s", "n": m["n"], "value": m["value_gbps"], "unit": "GB/s",
-                         "ms_per_step": m["ms_per_step"], "frac_of_peak_whole_sumcheck": m["frac_of_peak_whole_sumcheck"],
+                         "ms_per_step": m["ms_per_step"], "proof_sha256": m["proof_sha256"], "frac_of_peak_whole_sumcheck": m["frac_of_peak_whole_sumcheck"],
                          "value_by_schedule_bytes_gbps": m["value_by_schedule_bytes_gbps"], "roofline": m["roofline"]}
         line["sumcheck_microbench"] = sizes.pop(args.n_micro)
         line["sumcheck_microbench_other_sizes"] = {str(k): v for k, v in sizes.items()}

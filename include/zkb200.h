@@ -246,6 +246,10 @@ int32_t zkb_qwen_layer_set_forward_stream(zkb_qwen_layer* layer, void* stream);
 /* Waits for the layer's (asynchronous) forward pass only - not for a proof queued behind it -
  * and copies the layer output (d_model words) to the host. */
 int32_t zkb_qwen_layer_read_output(zkb_qwen_layer* layer, uint32_t* y_host);
+/* Host-side wait for the layer's (asynchronous) forward pass only; afterwards the output at
+ * zkb_qwen_layer_output_dev may be read on any stream or sent to another GPU while the layer's
+ * proof is still running. */
+int32_t zkb_qwen_layer_wait_forward(zkb_qwen_layer* layer);
 const uint32_t* zkb_qwen_layer_output_dev(const zkb_qwen_layer* layer);
 /* The launch sequence of a layer proof depends only on the layer's shapes and binding mode, so
  * from the second proof on it is replayed from a CUDA graph captured on the layer's stream

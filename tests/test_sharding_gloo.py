@@ -30,6 +30,15 @@ def test_merge_reverse():
     assert sharding.merge_reverse([[b"1", b"0"], [b"3", b"2"]]) == [b"3", b"2", b"1", b"0"]
 
 
+def test_pack_unpack_proofs_roundtrip():
+    buf = torch.empty(256, dtype=torch.uint8)
+    for proofs in ([], [b""], [b"abc", b"", b"\x00" * 40]):
+        sharding.pack_proofs(proofs, buf)
+        assert sharding.unpack_proofs(buf) == proofs
+    with pytest.raises(ValueError):
+        sharding.pack_proofs([b"x" * 300], buf)
+
+
 def _fake_layer(x, idx):
     """Stand-in for forward + prove of one layer: deterministic in (input, layer index)."""
     y = (x * 3 + idx + 1) % 2147483647
@@ -53,8 +62,7 @@ def _worker(rank, world, port, L, out_q):
         proofs.append(p)
     if rank + 1 < world:
         sharding.send_activation(dist, torch.from_numpy(x), rank + 1)
-    gathered = [None] * world if rank == 0 else None
-    dist.gather_object(proofs[::-1], gathered, dst=0)
+    gathered = sharding.ProofGather(dist, rank, world, 4096).gather(proofs[::-1])
     if rank == 0:
         out_q.put(sharding.merge_reverse(gathered))
     dist.barrier()

@@ -196,6 +196,17 @@ int32_t zkb_qwen_layer_read_output(zkb_qwen_layer* L, uint32_t* y_host) {
         ZKB_CUDA(cudaMemcpy(y_host, L->out, (size_t)L->dm.d_model * 4, cudaMemcpyDeviceToHost));
     });
 }
+// Wait (on the host) until this layer's forward pass has finished on the GPU - not for a proof
+// queued behind it.  Afterwards the output at zkb_qwen_layer_output_dev may be read by work on
+// any stream or handed to another GPU.
+int32_t zkb_qwen_layer_wait_forward(zkb_qwen_layer* L) {
+    if (!L) return ZKB_E_ARG;
+    zkb_ctx* c = L->ctx;
+    ZKB_TRY(c, {
+        c->use();
+        ZKB_CUDA(cudaEventSynchronize(L->fwd_done));
+    });
+}
 // Device address of the layer output (d_model words), so the next layer can read it in place.
 const uint32_t* zkb_qwen_layer_output_dev(const zkb_qwen_layer* L) { return L ? L->out : nullptr; }
 

@@ -110,6 +110,16 @@ class QwenLayer:
         check(self.ctx.h, _lib.lib().zkb_qwen_layer_read_output(self.h, y.ctypes.data_as(u32p)))
         return y
 
+    def wait_forward(self):
+        """Host-side wait for this layer's asynchronous forward pass (not for its proof)."""
+        check(self.ctx.h, _lib.lib().zkb_qwen_layer_wait_forward(self.h))
+
+    def output_address(self) -> int:
+        """Device address of the layer output (d_model u32 words)."""
+        fn = _lib.lib().zkb_qwen_layer_output_dev
+        fn.restype = C.c_void_p
+        return int(fn(self.h))
+
     def output(self) -> np.ndarray:
         _lib.lib().zkb_qwen_layer_output_dev.restype = u32p
         src = _lib.lib().zkb_qwen_layer_output_dev(self.h)
@@ -198,12 +208,14 @@ class QwenModel:
         proofs = [l.prove_end() for l in self.layers]
         return proofs[::-1]
 
-    def forward_and_prove(self, x, input_hash: bytes = None, on_forward_done=None):
+    def forward_and_prove(self, x, input_hash: bytes = None, on_forward_done=None, on_forward_finished=None):
         """Forward pass and all layer proofs with the two overlapped: every layer's proof is
         enqueued right behind its own forward, the forward of the next layer only waits (on the
         GPU) for the previous layer's forward.  Returns the proofs in reverse layer order.
-        `on_forward_done(output)` is called as soon as the last layer's forward has finished,
-        while the proofs are still running (used to hand the activation to the next GPU)."""
+        `on_forward_done(output)` is called with the host copy of the output as soon as the last
+        layer's forward has finished, while the proofs are still running; `on_forward_finished()` is
+        called at the same moment without any copy (the output then sits at
+        `layers[-1].output_address()` on the device: used to hand the activation to the next GPU)."""
         import threading
         if isinstance(x, DeviceBuffer):
             if input_hash is None:
@@ -238,9 +250,12 @@ class QwenModel:
             futures = []
         else:
             futures = [self.pool.submit(task, i) for i in range(n)]
-        if on_forward_done is not None:
+        if on_forward_done is not None or on_forward_finished is not None:
             issued[n - 1].wait()
-            if not failed:
+            if not failed and on_forward_finished is not None:
+                self.layers[-1].wait_forward()
+                on_forward_finished()
+            if not failed and on_forward_done is not None:
                 on_forward_done(self.layers[-1].read_output_after_forward())
         for f in futures:
             f.result()

@@ -144,12 +144,25 @@ class DeviceBuffer:
         self.ptr = u32p()
         check(ctx.h, _lib.lib().zkb_buf_alloc(ctx.h, C.c_size_t(self.n), C.byref(self.ptr)))
 
+    @classmethod
+    def wrap(cls, ctx: "Context", address: int, n_u32: int) -> "DeviceBuffer":
+        """View of `n_u32` words of device memory owned by somebody else (e.g. a tensor another
+        library received into); never freed by this object."""
+        b = cls.__new__(cls)
+        b.ctx, b.n, b.shape = ctx, int(n_u32), (int(n_u32),)
+        b.ptr = C.cast(C.c_void_p(address), u32p)
+        b._borrowed = True
+        return b
+
     def download(self) -> np.ndarray:
         out = np.empty(self.n, np.uint32)
         check(self.ctx.h, _lib.lib().zkb_buf_download_u32(self.ctx.h, self.ptr, C.c_size_t(self.n), out.ctypes.data_as(u32p)))
         return out.reshape(self.shape)
 
     def free(self):
+        if getattr(self, "_borrowed", False):
+            self.ptr = u32p()
+            return
         if self.ptr and self.ctx.h.value:
             check(self.ctx.h, _lib.lib().zkb_buf_free(self.ctx.h, self.ptr))
             self.ptr = u32p()
