@@ -358,6 +358,26 @@ def run_sumcheck(zk, ctx, n, steps, warmup, rank, with_e2e, barrier=lambda: None
     return res
 
 
+def nccl_allreduce_us(dist, local, reps=200):
+    """Device time of one NCCL all-reduce (sum) of 12 u64 words - the size of a round's three EF partial
+    sums as unreduced limbs - measured back to back with CUDA events on torch's stream."""
+    import torch
+    t = torch.ones(12, dtype=torch.int64, device=f"cuda:{local}")
+    for _ in range(20):
+        dist.all_reduce(t)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        dist.all_reduce(t)
+    b.record()
+    torch.cuda.synchronize()
+    us = a.elapsed_time(b) * 1e3 / reps
+    m = torch.tensor([us], dtype=torch.float64, device=f"cuda:{local}")
+    dist.all_reduce(m, op=dist.ReduceOp.MAX)
+    return round(float(m.item()), 2)
+
+
 def run_sumcheck_split(zk, ctx, n, steps, warmup, rank, world, with_e2e, barrier, max_over_ranks, dist):
     """One product sumcheck over two 2^n-element tables split over `world` GPUs (rank g owns the
     elements j = g mod world); strong scaling: value = 72 * 2^n bytes / time of the slowest rank."""
@@ -735,10 +755,22 @@ def main():
         # the workload that does scale with the GPUs: ONE product sumcheck of 2^n-element tables split over all of them
         # (every rank takes part); its proof hash equals the single-GPU microbench's at the same n
         sr = run_sumcheck_split(zk, micro_ctx, args.n_micro, 5, 3, rank, world, False, barrier, max_over_ranks, dist)
+        # what the in-kernel exchange costs, and what the same exchange would cost as one NCCL all-reduce per round:
+        # (a) the same per-GPU slice proved alone (no peers) on every rank, (b) 12-word u64 all-reduces back to back
+        n_loc = args.n_micro - (world.bit_length() - 1)
+        alone = run_sumcheck(zk, micro_ctx, n_loc, 5, 3, rank, False, barrier, max_over_ranks)
+        nccl_us = nccl_allreduce_us(dist, local)
         if rank == 0:
             line["sumcheck_split"] = {"metric": "sumcheck fold HBM GB/s, one sumcheck split over the GPUs", "n": sr["n"], "n_gpus": world,
                                       "value": sr["value_gbps"], "unit": "GB/s", "ms_per_step": sr["ms_per_step"], "scaling": "strong",
                                       "proof_sha256": sr["proof_sha256"], "roofline": sr["roofline"],
+                                      "per_gpu_slice_alone_ms": alone["ms_per_step"],
+                                      "exchange_overhead_us_per_round": round((sr["ms_per_step"] - alone["ms_per_step"]) * 1e3 / args.n_micro, 2),
+                                      "nccl_allreduce_12xu64_us": nccl_us,
+                                      "exchange_note": "overhead = (split sumcheck - the same per-GPU slice proved alone) / rounds, the last log2(N) "
+                                                       "rounds and the plain instead of the pipelined tail included; the NCCL figure is one "
+                                                       "all-reduce of 12 u64 (a round's three EF sums) timed back to back on the device, which a "
+                                                       "per-round NCCL exchange would add to every round on top of two extra launches",
                                       "exchange": "per-round partial sums written into the peers' mailboxes by the round kernels themselves "
                                                   "(plain peer stores over NVLink), no collective call per round"}
     if qwen and not args.no_micro and rank == 0:
