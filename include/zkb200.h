@@ -66,6 +66,13 @@ int32_t zkb_ctx_create(int32_t device, zkb_ctx** out);
 void zkb_ctx_destroy(zkb_ctx* ctx);
 const char* zkb_last_error(const zkb_ctx* ctx);
 int32_t zkb_ctx_sync(zkb_ctx* ctx);
+/* A context keeps a scratch arena on the device that grows to what its largest proof needed and is
+ * reused from then on (nothing is allocated per proof).  zkb_ctx_scratch_bytes reports its size;
+ * zkb_ctx_trim waits for the context's stream and gives the arena back to the device - for a caller
+ * that proves more layers than fit side by side (the reference bounds the same working set by
+ * proving in chunks, pipeline/prove.rs:112-151). */
+int32_t zkb_ctx_trim(zkb_ctx* ctx);
+uint64_t zkb_ctx_scratch_bytes(const zkb_ctx* ctx);
 /* Tuning options of one context, for measurements (none is needed in production; value 0 restores
  * the built-in choice).  ZKB_OPT_PLAIN_TAIL: nonzero = every sumcheck ends in the plain
  * single-CTA tail instead of the pipelined one.  ZKB_OPT_SINGLE_CTA_THREADS /

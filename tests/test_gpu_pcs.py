@@ -132,3 +132,36 @@ def test_qwen_layer_with_basefold_binding_bytes(ctx, mode, kind):
     assert len(proof) == len(eproof) and proof == eproof
     assert layer.prove(3, ih) == eproof
     layer.close()
+
+
+def test_qwen_model_shared_contexts_prove_in_waves_pcs_full():
+    """Five layers on two contexts (layer i uses context i mod 2), pcs-full binding: the layers are
+    proved in waves of two, the Basefold scratch of one matmul is reused by the next, and every
+    proof equals the oracle's; afterwards the arenas can be given back."""
+    from zklm_compile_b200 import qwen as zq
+    from tests.util import load_qwen_golden, rand_layer
+    G = load_qwen_golden()
+    shapes = [dict(d_model=64, d_ff=96, heads=2, kv=2, d_head=16, v_heads=4, v_d_head=16), dict(d_model=64, d_ff=96, heads=4, kv=2, d_head=16)]
+    layers = [rand_layer(50 + i, **shapes[i % 2]) for i in range(5)]
+    x = layers[0][2]
+    model = zq.QwenModel(0, [l[0] for l in layers], [l[1] for l in layers], G["silu"], G["sigmoid"], first_layer=7, n_contexts=2)
+    assert len(model._own_ctxs) == 2 and model.ctxs[0] is model.ctxs[2] is model.ctxs[4]
+    for l in model.layers:
+        l.set_binding(2, 0)
+        l.use_graph(False)
+    ih = zq.hash_values(x)
+    cur, exp = x, []
+    with O.features(2, 0):
+        for i, (cfg, w, _) in enumerate(layers):
+            cur, pr, ok = O.qwen_layer_prove(cfg, w, cur, G["silu"], G["sigmoid"], 7 + i, ih, verify=True)
+            assert ok
+            exp.append(pr)
+    for _ in range(2):
+        assert model.forward_and_prove(x) == exp[::-1]
+    assert model.output().tolist() == cur.tolist()
+    assert all(c.scratch_bytes > 0 for c in model._own_ctxs)
+    for c in model._own_ctxs:
+        c.trim()
+        assert c.scratch_bytes == 0
+    assert model.forward_and_prove(x) == exp[::-1]      # the arena grows again
+    model.close()

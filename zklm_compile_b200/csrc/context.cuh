@@ -128,11 +128,12 @@ struct zkb_ctx {
     bool capturing = false;
     uint64_t arena_epoch = 0;
 
+    size_t cur_chunk = 0;               // chunks before it are full (or were skipped), chunks after it are empty
     void* scratch(size_t bytes) {
         bytes = (bytes + 255) & ~size_t(255);
-        if (!chunks.empty()) {
-            Chunk& c = chunks.back();
-            if (c.used + bytes <= c.cap) { void* p = c.base + c.used; c.used += bytes; return p; }
+        for (size_t i = cur_chunk; i < chunks.size(); i++) {
+            Chunk& c = chunks[i];
+            if (c.used + bytes <= c.cap) { void* p = c.base + c.used; c.used += bytes; cur_chunk = i; return p; }
         }
         if (capturing) throw zkb::ArgFail{ZKB_E_TOO_LARGE, "scratch arena would have to grow during a stream capture"};
         arena_epoch++;
@@ -141,10 +142,22 @@ struct zkb_ctx {
         char* p = nullptr;
         ZKB_CUDA(cudaMalloc(&p, cap));
         chunks.push_back(Chunk{p, cap, bytes});
+        cur_chunk = chunks.size() - 1;
         return p;
+    }
+    // A section whose scratch is dead once its kernels have been enqueued (work on one stream runs in
+    // order, so whatever is enqueued later may reuse the memory): mark, allocate, release.
+    struct ScratchMark { size_t chunk, used; };
+    ScratchMark scratch_mark() const { return ScratchMark{cur_chunk, chunks.empty() ? 0 : chunks[cur_chunk].used}; }
+    void scratch_release(ScratchMark m) {
+        if (chunks.empty()) return;
+        for (size_t i = m.chunk + 1; i < chunks.size(); i++) chunks[i].used = 0;
+        chunks[m.chunk].used = m.used;
+        cur_chunk = m.chunk;
     }
     // Rewind everything; if the arena fragmented into several chunks, replace them by one.
     void scratch_reset() {
+        cur_chunk = 0;
         if (chunks.size() > 1) {
             arena_epoch++;
             ZKB_CUDA(cudaStreamSynchronize(stream));
@@ -158,6 +171,15 @@ struct zkb_ctx {
             chunks[0].used = 0;
         }
     }
+    // Give the arena's memory back to the device (the next proof allocates it again).
+    void scratch_trim() {
+        ZKB_CUDA(cudaStreamSynchronize(stream));
+        for (auto& c : chunks) cudaFree(c.base);
+        chunks.clear();
+        cur_chunk = 0;
+        arena_epoch++;
+    }
+    size_t scratch_capacity() const { size_t t = 0; for (auto& c : chunks) t += c.cap; return t; }
     void prof_mark() {
         if (!profile) return;
         if (prof_used == prof_events.size()) {

@@ -162,6 +162,9 @@ inline MatmulRec prove_matmul_succinct_ef(zkb_ctx* c, TrState* tr, const u32* W,
         CoefSrc src = bind == BIND_PCS_FULL ? CoefSrc{W, m, n, R.log_n} : CoefSrc{(const u32*)w_partial, 1, (u32)(4 * n_pad), R.log_n + 2};
         const u32 bf_log = bind == BIND_PCS_FULL ? R.log_m + R.log_n : R.log_n + 2;
         const size_t num_coeffs = bind == BIND_PCS_FULL ? (size_t)m * n : 4 * n_pad;
+        // codeword, trees and evaluation buffer (about 60 bytes per coefficient) are dead once the opening is
+        // enqueued: everything the proof keeps goes to the record, so the next protocol step reuses the memory
+        const auto mark = c->scratch_mark();
         u32* bf_point = (u32*)c->scratch((bf_log + 1) * 4);
         ScriptBuilder sb;
         sb.squeeze(bf_point, bf_log);
@@ -169,6 +172,7 @@ inline MatmulRec prove_matmul_succinct_ef(zkb_ctx* c, TrState* tr, const u32* W,
         R.bf = basefold_enqueue(c, tr, src, num_coeffs, bf_log, bf_point, bf_log, node_kind);
         sb.words_dev(c->rec_dev + R.bf.root_off, 4, 8);
         sb.run(c, tr);
+        c->scratch_release(mark);
     }
     R.eval = prove_mle_eval_ef_ef(c, tr, w_partial, (const Fe*)(c->rec_dev + R.sc.chal), R.log_n);
     return R;

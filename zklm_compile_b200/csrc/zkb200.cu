@@ -340,6 +340,12 @@ int32_t zkb_ctx_set_shared(zkb_ctx* c, int32_t on) {
     return ZKB_OK;
 }
 
+int32_t zkb_ctx_trim(zkb_ctx* c) {
+    if (!c) return ZKB_E_ARG;
+    ZKB_TRY(c, { c->use(); c->scratch_trim(); });
+}
+uint64_t zkb_ctx_scratch_bytes(const zkb_ctx* c) { return c ? (uint64_t)c->scratch_capacity() : 0; }
+
 int32_t zkb_ctx_set_option(zkb_ctx* c, int32_t option, int32_t value) {
     if (!c) return ZKB_E_ARG;
     switch (option) {

@@ -156,12 +156,21 @@ class QwenModel:
     i -> dict (so that only one layer's host copy is alive at a time); `first_layer` is the
     global index of this stack's first layer when a model is sharded over several GPUs."""
 
-    def __init__(self, device: int, configs, weights, silu_out, sigmoid_out, first_layer: int = 0, shared_shapes: bool = False):
+    def __init__(self, device: int, configs, weights, silu_out, sigmoid_out, first_layer: int = 0, shared_shapes: bool = False,
+                 n_contexts: int = None):
+        """`n_contexts` < number of layers makes the layers share that many contexts (layer i uses
+        context i mod n_contexts) and proves them in waves of n_contexts, which bounds the scratch
+        memory alive at once - what the reference's chunked fan-out does for pcs-full
+        (rust/zk_ml_prover/src/pipeline/prove.rs:112-151)."""
         self.device = device
         self.first_layer = first_layer
-        self.ctxs = [Context(device) for _ in configs]
+        configs = list(configs)
+        self.n_contexts = min(n_contexts or len(configs), max(1, len(configs)))
+        pool_ctxs = [Context(device) for _ in range(self.n_contexts)]
+        self.ctxs = [pool_ctxs[i % self.n_contexts] for i in range(len(configs))]
+        self._own_ctxs = pool_ctxs
         if shared_shapes:                # measured slower on B200 for the 32-layer 4B shape (34.9 vs 32.7 ms): off by default
-            for c in self.ctxs:
+            for c in pool_ctxs:
                 c.set_shared(True)
         self.tables = (self.ctxs[0].upload(silu_out), self.ctxs[0].upload(sigmoid_out))
         self.layers = []
@@ -200,6 +209,14 @@ class QwenModel:
         (pipeline/prove.rs:183-188).  Enqueued from a few host threads, then collected."""
         n = len(self.layers)
         begin = lambda i: self.layers[i].prove_begin(self.first_layer + i, self.input_hash)
+        if self.n_contexts < n:                                 # shared contexts: one wave of layers at a time
+            proofs = []
+            for w0 in range(0, n, self.n_contexts):
+                wave = range(w0, min(n, w0 + self.n_contexts))
+                for i in wave:
+                    begin(i)
+                proofs += [self.layers[i].prove_end() for i in wave]
+            return proofs[::-1]
         if any(l.graph_state() == 1 for l in self.layers):      # one-off graph captures: one at a time
             for i in range(n):
                 begin(i)
@@ -224,6 +241,14 @@ class QwenModel:
         else:
             self.input_hash = input_hash if input_hash is not None else hash_values(x)
         n = len(self.layers)
+        if self.n_contexts < n:          # shared contexts: the whole forward pass first, then the proofs in waves
+            self.forward(x, input_hash)
+            if on_forward_finished is not None:
+                self.layers[-1].ctx.sync()
+                on_forward_finished()
+            if on_forward_done is not None:
+                on_forward_done(self.output())
+            return self.prove()
         issued = [threading.Event() for _ in range(n)]
         failed = []
 
@@ -272,5 +297,5 @@ class QwenModel:
             self._fwd_stream = C.c_void_p()
         for t in self.tables:
             t.free()
-        for c in self.ctxs:
+        for c in self._own_ctxs:
             c.close()

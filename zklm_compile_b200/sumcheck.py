@@ -63,6 +63,17 @@ class Context:
         of every SM free (see zkb_ctx_set_shared in include/zkb200.h)."""
         check(self.h, _lib.lib().zkb_ctx_set_shared(self.h, C.c_int32(1 if on else 0)))
 
+    def trim(self):
+        """Give the context's scratch arena back to the device (the next proof allocates it again)."""
+        check(self.h, _lib.lib().zkb_ctx_trim(self.h))
+
+    @property
+    def scratch_bytes(self) -> int:
+        fn = _lib.lib().zkb_ctx_scratch_bytes
+        fn.restype = C.c_uint64
+        fn.argtypes = [C.c_void_p]
+        return int(fn(self.h))
+
     OPT_PLAIN_TAIL, OPT_SINGLE_CTA_THREADS, OPT_PIPE_THREADS, OPT_NO_FUSED_FOLD, OPT_FOLD2_VEC = 0, 1, 2, 3, 4
 
     def set_option(self, option: int, value: int):
