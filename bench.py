@@ -58,7 +58,7 @@ def schedule_bytes(n, launches):
 
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) over the schedule bytes above, from the ncu
 # captures summarised in profiles/sumcheck_kernels_product_ef.md (n = 25, one launch of each kernel).
-NCU_TRAFFIC_RATIO = {0: None, 1: None, 2: None, "ef": None}
+NCU_TRAFFIC_RATIO = {0: 1.02, 1: 1.02, 2: 0.92, "ef": 0.90}
 
 
 def table_values(seed, first, count, step=1):
@@ -923,7 +923,8 @@ def main():
                                                        "per-round NCCL exchange would add to every round on top of two extra launches",
                                       "exchange": "per-round partial sums written into the peers' mailboxes by the round kernels themselves "
                                                   "(plain peer stores over NVLink), no collective call per round"}
-    if qwen and not args.no_micro and rank == 0:
+    if qwen and not args.no_micro and rank == 0 and world == 1:
+        # (at N > 1 the other GPUs would idle through these single-GPU legs: the split sumcheck above carries the metric there)
         # the "sumcheck fold HBM GB/s" half of the metric: the microbench configuration's four sizes on one GPU
         sizes = {}
         for nn in sorted({20, 24, 26, args.n_micro}):

@@ -352,6 +352,40 @@ int32_t zkb_basefold_encode(zkb_ctx* ctx, const uint32_t* coeffs, size_t n, int3
 int32_t zkb_basefold_commit_and_prove(zkb_ctx* ctx, zkb_transcript* tr, const uint32_t* coeffs, size_t n, const uint32_t* point,
                                       uint32_t n_point, int32_t on_device, int32_t node_hash, uint8_t* out, size_t cap, size_t* len);
 
+/* ---- op-list mode (MLP / GPT-2 shaped models; base-field challenges) ----------------------------
+ * The reference proves such models as a list of ops on one transcript "structured-ml-proof", in
+ * reverse op order (pipeline/forward.rs:24-520, pipeline/prove.rs:36, 191-648).  A zkb_oplist keeps
+ * the weights of its ops resident on the GPU (committed once when the op is added); ops are added in
+ * forward order; zkb_oplist_prove runs the forward pass and the proofs on the device and returns
+ * bincode(Vec<SerializedLayerProof>) (protocol.rs:653-694) in the reference's push order.
+ *   linear      y = W x + b; SerializedLayerProof::Matmul(prove_matmul_succinct)          prove.rs:196-235
+ *   relu        SerializedLayerProof::Relu (two triple sumchecks, MLE-eval proofs)         prove.rs:237-340
+ *   layernorm   layernorm_forward_simple + prove_layernorm_sqr -> LayerNormSqr              gpt2.rs:912-953, layernorm.rs:522-695
+ *   gelu        LogUp lookup of the requantised activation -> Gelu(GeluProof)               prove.rs:362-392, gelu.rs:64-72
+ *               (the reference receives the requantised pairs from its Python driver; here
+ *               requantize_to_i16_field and the table lookup run on the device)
+ *   attention   seq_len = 1: output = V, PassThrough with the output hash absorbed            prove.rs:394-411
+ *   save / add_saved / set_input / passthrough: SaveCommitment, Add, SegmentBoundary, PassThrough (prove.rs:439-489, 635-646)
+ *   set_input_requant: set_input whose new activation is requantize_to_i16_field of the current one
+ *               (stands in for the float re-quantisation the reference's Python driver does between segments). */
+typedef struct zkb_oplist zkb_oplist;
+enum { ZKB_OP_RELU = 1, ZKB_OP_ATTENTION_SEQ1 = 2, ZKB_OP_PASSTHROUGH = 3, ZKB_OP_SAVE = 4, ZKB_OP_ADD_SAVED = 5, ZKB_OP_SET_INPUT_REQUANT = 6 };
+int32_t zkb_oplist_create(zkb_ctx* ctx, uint32_t input_len, zkb_oplist** out);
+void zkb_oplist_destroy(zkb_oplist* list);
+int32_t zkb_oplist_add_linear(zkb_oplist* list, const char* name, const uint32_t* W, const uint32_t* bias /* or NULL */, size_t m, size_t n);
+/* kind = ZKB_OP_*; aux = the buffer name of save / add_saved (the reference derives the Add proof's
+ * save_name from the op name: "add_X" -> "save_X", prove.rs:445). */
+int32_t zkb_oplist_add_simple(zkb_oplist* list, int32_t kind, const char* name, const char* aux);
+int32_t zkb_oplist_add_layernorm(zkb_oplist* list, const char* name, const uint32_t* gamma, const uint32_t* beta, size_t d);
+int32_t zkb_oplist_add_gelu(zkb_oplist* list, const char* name, const uint32_t* table_out_dev, uint32_t n_table);
+int32_t zkb_oplist_add_set_input(zkb_oplist* list, const char* name, const uint32_t* values, size_t n);
+uint32_t zkb_oplist_output_len(const zkb_oplist* list);
+/* forward pass only (x: input_len host words); zkb_oplist_activation then reads the activation after op `op_index`. */
+int32_t zkb_oplist_forward(zkb_oplist* list, const uint32_t* x);
+int32_t zkb_oplist_activation(zkb_oplist* list, uint32_t op_index, uint32_t* out, size_t cap, size_t* len);
+/* forward pass + all proofs */
+int32_t zkb_oplist_prove(zkb_oplist* list, const uint32_t* x, uint8_t* out, size_t cap, size_t* len);
+
 /* ---- allocation-free weight fold ----
  * No counterpart in the reference: it exists for callers that must not allocate device memory
  * once they are running (a serving loop with a fixed memory plan, a host that forbids cudaMalloc

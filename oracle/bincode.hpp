@@ -21,6 +21,7 @@ struct Bin {
     void vec_u32(const std::vector<uint32_t>& v) { u64(v.size()); for (uint32_t x : v) u32(x); }
     void vec_ef(const std::vector<EFElement>& v) { u64(v.size()); for (auto& e : v) ef(e); }
     template <size_t N> void bytes(const std::array<uint8_t, N>& a) { b.insert(b.end(), a.begin(), a.end()); }
+    void str(const std::string& t) { u64(t.size()); b.insert(b.end(), t.begin(), t.end()); }
 
     void put(const SumcheckProof& p) {                      // sumcheck.rs:57-65
         u64(p.round_polys.size());

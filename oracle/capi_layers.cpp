@@ -2,7 +2,7 @@
 //
 // C entry points for the matmul / MLE-eval / element-wise / RMSNorm / LogUp / Qwen-layer
 // restatements.  Proofs come back as bincode bytes (oracle/bincode.hpp).
-#include "qwen_verify.hpp"
+#include "oplist.hpp"
 #include <cstring>
 
 using namespace zko;
@@ -283,6 +283,69 @@ size_t zko_qwen_layer_prove_trace_h(void* h, uint32_t layer_idx, const uint8_t* 
     tr.absorb_bytes(input_hash, 32);
     return emit(serialize(prove_qwen_layer_precommitted_ef(L.trace, L.W, L.c, L.com, L.silu, L.sigm, tr)), out, cap);
 }
+// ---- op lists (oplist.hpp): built call by call, then forward + prove in one go -------------------
+struct OracleOpList { std::vector<Op> ops; };
+void* zko_oplist_new() { return new OracleOpList(); }
+void zko_oplist_free(void* h) { delete static_cast<OracleOpList*>(h); }
+static Op& new_op(void* h, const char* type, const char* name) {
+    auto& L = *static_cast<OracleOpList*>(h);
+    L.ops.emplace_back();
+    L.ops.back().type = type; L.ops.back().name = name;
+    return L.ops.back();
+}
+void zko_oplist_linear(void* h, const char* name, const uint32_t* w, const uint32_t* b, size_t m, size_t n) {
+    Op& o = new_op(h, "linear", name);
+    o.m = m; o.n = n; o.w = vf(w, m * n); o.b = b ? vf(b, m) : VF();
+}
+void zko_oplist_simple(void* h, const char* type, const char* name, const char* aux) {   // relu, attention, passthrough, save (aux = save_name), add_saved (aux = add_name)
+    Op& o = new_op(h, type, name);
+    if (o.type == "save") o.save_name = aux;
+    if (o.type == "add_saved") o.add_name = aux;
+}
+void zko_oplist_layernorm(void* h, const char* name, const uint32_t* gamma, const uint32_t* beta, size_t d) {
+    Op& o = new_op(h, "layernorm", name);
+    o.gamma = vf(gamma, d); o.beta = vf(beta, d);
+}
+void zko_oplist_gelu(void* h, const char* name, const uint32_t* in, const uint32_t* out, size_t n, const uint32_t* table_out, size_t n_table) {
+    Op& o = new_op(h, "gelu", name);
+    o.gelu_in = vf(in, n); o.gelu_out = vf(out, n);
+    o.table_out.assign(table_out, table_out + n_table);
+}
+void zko_oplist_set_input(void* h, const char* name, const uint32_t* v, size_t n) {
+    Op& o = new_op(h, "set_input", name);
+    o.new_input = vf(v, n);
+}
+// Forward pass only: the activation after op `upto` (0-based) into out (returns its length).
+size_t zko_oplist_forward(void* h, const uint32_t* x, size_t n, size_t upto, uint32_t* out, size_t cap) {
+    auto& L = *static_cast<OracleOpList*>(h);
+    std::vector<Op> head(L.ops.begin(), L.ops.begin() + (upto + 1 < L.ops.size() ? upto + 1 : L.ops.size()));
+    auto layers = oplist_forward(head, vf(x, n));
+    const VF& y = layers.back().output;
+    if (y.size() <= cap) out_f(y, out);
+    return y.size();
+}
+// Forward + prove: bincode(Vec<SerializedLayerProof>) in the reference's push order.
+size_t zko_oplist_prove(void* h, const uint32_t* x, size_t n, uint8_t* out, size_t cap) {
+    auto& L = *static_cast<OracleOpList*>(h);
+    auto layers = oplist_forward(L.ops, vf(x, n));
+    return emit(oplist_prove(layers), out, cap);
+}
+// prove + verify round trip of the squared LayerNorm (1 = accepted); tamper flips one proof field.
+int zko_layernorm_sqr_roundtrip(const uint32_t* x, const uint32_t* gamma, const uint32_t* beta, size_t d, int tamper) {
+    VF X = vf(x, d), G = vf(gamma, d), B = vf(beta, d);
+    LnForward f = layernorm_forward_simple(X, G, B);
+    VF xu = X;
+    if (f.perturbation != 0) xu[0] = xu[0] + (f.perturbation > 0 ? F(uint32_t(f.perturbation)) : F::zero() - F(uint32_t(-f.perturbation)));
+    Transcript pt("ln"), vt("ln");
+    LayerNormSqrProof p = prove_layernorm_sqr(xu, G, B, f.y, f.mu, pt);
+    if (tamper == 1) p.s_h ^= 1;
+    if (tamper == 2) p.mu ^= 1;
+    if (tamper == 3) p.g_sq_fin[1] ^= 1;
+    VF y = f.y;
+    if (tamper == 4) y[0] = y[0] + F::one();
+    return verify_layernorm_sqr(p, y, B, d, vt) ? 1 : 0;
+}
+
 // Worker threads of the row-parallel matrix loops (matmul.hpp); 1 = serial.
 void zko_set_threads(int n) { matrix_threads() = n < 1 ? 1 : n; }
 

@@ -411,6 +411,70 @@ QwenLayer.forward = _layer_forward
 QwenLayer.prove_trace = _layer_prove_trace
 
 
+class OpList:
+    """The reference's op-list mode (pipeline/forward.rs + pipeline/prove.rs:191-648, oracle/oplist.hpp):
+    ops are added in forward order; `prove(x)` runs the forward pass and returns
+    bincode(Vec<SerializedLayerProof>) with the proofs in the reference's (reverse) push order."""
+
+    def __init__(self):
+        lib().zko_oplist_new.restype = C.c_void_p
+        self.h = C.c_void_p(lib().zko_oplist_new())
+        self.n_ops = 0
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            lib().zko_oplist_free(self.h)
+            self.h = None
+
+    def linear(self, name, w, b, m, n):
+        W, pw = _u32(w)
+        if b is None:
+            lib().zko_oplist_linear(self.h, name.encode(), pw, None, C.c_size_t(m), C.c_size_t(n))
+        else:
+            B, pb = _u32(b)
+            lib().zko_oplist_linear(self.h, name.encode(), pw, pb, C.c_size_t(m), C.c_size_t(n))
+        self.n_ops += 1
+
+    def simple(self, kind, name, aux=""):
+        """relu, attention (seq_len 1), passthrough, save (aux = save_name), add_saved (aux = add_name)."""
+        lib().zko_oplist_simple(self.h, kind.encode(), name.encode(), aux.encode())
+        self.n_ops += 1
+
+    def layernorm(self, name, gamma, beta):
+        G, pg = _u32(gamma); B, pb = _u32(beta)
+        lib().zko_oplist_layernorm(self.h, name.encode(), pg, pb, C.c_size_t(G.size))
+        self.n_ops += 1
+
+    def gelu(self, name, inputs, outputs, table_out):
+        I, pi = _u32(inputs); Oo, po = _u32(outputs); T, pt = _u32(table_out)
+        lib().zko_oplist_gelu(self.h, name.encode(), pi, po, C.c_size_t(I.size), pt, C.c_size_t(T.size))
+        self.n_ops += 1
+
+    def set_input(self, name, values):
+        V, pv = _u32(values)
+        lib().zko_oplist_set_input(self.h, name.encode(), pv, C.c_size_t(V.size))
+        self.n_ops += 1
+
+    def forward(self, x, upto=None):
+        """Activation after op `upto` (default: the last one)."""
+        X, px = _u32(x)
+        upto = self.n_ops - 1 if upto is None else upto
+        cap = 1 << 20
+        out = np.zeros(cap, np.uint32)
+        lib().zko_oplist_forward.restype = C.c_size_t
+        n = lib().zko_oplist_forward(self.h, px, C.c_size_t(X.size), C.c_size_t(upto), out.ctypes.data_as(u32p), C.c_size_t(cap))
+        return out[:n].copy()
+
+    def prove(self, x) -> bytes:
+        X, px = _u32(x)
+        return _bytes_call(lib().zko_oplist_prove, self.h, px, C.c_size_t(X.size), cap=1 << 24)
+
+
+def layernorm_sqr_roundtrip(x, gamma, beta, tamper=0) -> bool:
+    X, px = _u32(x); G, pg = _u32(gamma); B, pb = _u32(beta)
+    return bool(lib().zko_layernorm_sqr_roundtrip(px, pg, pb, C.c_size_t(X.size), C.c_int(tamper)))
+
+
 def set_threads(n: int):
     """Worker threads of the row-parallel matrix loops (the reference uses rayon there); 1 = serial."""
     lib().zko_set_threads(C.c_int(int(n)))

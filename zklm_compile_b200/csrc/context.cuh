@@ -22,6 +22,19 @@ struct CudaFail { std::string msg; };
 
 struct ArgFail { int32_t code; std::string msg; };
 
+// Launch with programmatic stream serialisation: the kernel may begin before the previous kernel of
+// the stream has finished (see pdl_wait in m31.cuh).
+template <class... KArgs, class... Args>
+inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = 0; cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    ZKB_CUDA(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...));
+}
+
 }  // namespace zkb
 
 struct zkb_ctx {

@@ -243,6 +243,23 @@ __global__ void __launch_bounds__(256) matvec_forward_kernel(MatvecBatch mb, con
     const int sub = warp % WPR;                         // which part of the row
     constexpr int RPC = 8 / WPR;                        // rows per CTA
     const size_t m = mb.first[mb.count];
+    // Launched as a programmatic dependent: the weights do not depend on the kernel before this one
+    // (only x does), so while that kernel is still running every CTA pulls the rows of its first
+    // pass into L2; then it waits for x.
+    pdl_launch_dependents();
+    {
+        const size_t i0 = (size_t)blockIdx.x * RPC;
+        const size_t lines_per_row = (n * 4 + 127) / 128;
+        for (size_t q = threadIdx.x; q < (size_t)RPC * lines_per_row; q += blockDim.x) {
+            const size_t i = i0 + q / lines_per_row;
+            if (i < m) {
+                u32 t = 0;
+                while (t + 1 < mb.count && i >= mb.first[t + 1]) t++;
+                prefetch_l2(reinterpret_cast<const char*>(mb.W[t] + (i - mb.first[t]) * n) + (q % lines_per_row) * 128);
+            }
+        }
+    }
+    pdl_wait();
     for (size_t i0 = (size_t)blockIdx.x * RPC; i0 < m; i0 += (size_t)gridDim.x * RPC) {
         const size_t i = i0 + warp / WPR;
         u64 acc = 0;

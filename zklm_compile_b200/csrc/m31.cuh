@@ -110,6 +110,15 @@ ZKB_HD Fe lerp(Fp a, Fp b, Fe r) {
 ZKB_HD Fp dbl_minus(Fp hi, Fp lo) { return hi + hi - lo; }   // value at t = 2
 ZKB_HD Fe dbl_minus(Fe hi, Fe lo) { return hi + hi - lo; }
 
+// Programmatic dependent launch.  A kernel launched with the attribute (zkb::launch_pdl) may start
+// while its predecessor in the stream is still running: everything before pdl_wait() must not
+// touch what the predecessor writes (weights may be prefetched, nothing else), everything after it
+// sees the predecessor's memory complete.  pdl_launch_dependents() lets the successor start early.
+// Without the launch attribute both are no-ops.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
 // 16-byte vector load / store of an EF element.
 __device__ __forceinline__ Fe ld_fe(const Fe* p) {
     uint4 t = *reinterpret_cast<const uint4*>(p);

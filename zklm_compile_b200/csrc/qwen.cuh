@@ -82,10 +82,10 @@ inline void launch_matvec_forward(zkb_ctx* c, const MatvecBatch& mb, const u32* 
     int grid = (int)(ctas < cap ? ctas : cap);
     if (grid < 1) grid = 1;
     switch (wpr) {
-        case 1: matvec_forward_kernel<1><<<grid, 256, 0, c->stream>>>(mb, x, n); break;
-        case 2: matvec_forward_kernel<2><<<grid, 256, 0, c->stream>>>(mb, x, n); break;
-        case 4: matvec_forward_kernel<4><<<grid, 256, 0, c->stream>>>(mb, x, n); break;
-        default: matvec_forward_kernel<8><<<grid, 256, 0, c->stream>>>(mb, x, n); break;
+        case 1: launch_pdl(matvec_forward_kernel<1>, dim3(grid), dim3(256), c->stream, mb, x, n); break;
+        case 2: launch_pdl(matvec_forward_kernel<2>, dim3(grid), dim3(256), c->stream, mb, x, n); break;
+        case 4: launch_pdl(matvec_forward_kernel<4>, dim3(grid), dim3(256), c->stream, mb, x, n); break;
+        default: launch_pdl(matvec_forward_kernel<8>, dim3(grid), dim3(256), c->stream, mb, x, n); break;
     }
 }
 // y = W x for one matrix; the tail y[m..m_pad) is zeroed unless the caller keeps it zero itself.
@@ -116,7 +116,8 @@ inline void qwen_forward(zkb_qwen_layer* L) {
     zkb_ctx* c = L->ctx;
     const QwenDims& d = L->dm;
     const u32 dm = d.d_model, dmp = (u32)pad_pow2(dm), aod = d.aod(), aodp = (u32)pad_pow2(aod), dffp = (u32)pad_pow2(d.d_ff);
-    rmsnorm_forward_kernel<<<1, c->single_cta_threads(), 0, c->stream>>>(L->x, L->w[W_NORM1], dm, dmp, L->norm1_out, L->norm1_x, L->n1_scalars, c->status);
+    launch_pdl(rmsnorm_forward_kernel, dim3(1), dim3(c->single_cta_threads()), c->stream, (const u32*)L->x, (const u32*)L->w[W_NORM1], dm, dmp,
+               L->norm1_out, L->norm1_x, L->n1_scalars, c->status, (const u32*)nullptr, (u32*)nullptr);
     ZKB_LAUNCHED(c);
     // The trace buffers were zeroed when the layer was created and nothing writes their padded
     // tails, so no launch has to clear them.  q, k, v and the gate projection share norm1_out.
@@ -127,19 +128,20 @@ inline void qwen_forward(zkb_qwen_layer* L) {
         matvec_forward_batch(c, 4, Wm, ym, mm, L->norm1_out, dm);
     }
     if (d.is_gqa()) {
-        replicate_heads_kernel<<<grid_for(c, aodp), 256, 0, c->stream>>>(L->v, d.nq, d.nq / d.nkv, d.d_head, aodp, L->attn_out);
-        ZKB_LAUNCHED(c);
+        launch_pdl(replicate_heads_kernel, dim3(grid_for(c, aodp)), dim3(256), c->stream, (const u32*)L->v, d.nq, d.nq / d.nkv, d.d_head, aodp, L->attn_out);
     } else {
-        ZKB_CUDA(cudaMemcpyAsync(L->attn_out, L->v, (size_t)aodp * 4, cudaMemcpyDeviceToDevice, c->stream));
+        // attn_out = v (qwen.rs:272-284 with one group per head): a kernel rather than a copy, so the chain of dependent launches is not broken
+        launch_pdl(replicate_heads_kernel, dim3(grid_for(c, aodp)), dim3(256), c->stream, (const u32*)L->v, aod / d.d_head, 1u, d.d_head, aodp, L->attn_out);
     }
+    ZKB_LAUNCHED(c);
     unsigned long long* mx = reinterpret_cast<unsigned long long*>(L->n1_scalars + 4);   // two 8-byte slots after the scalars
-    requant_lookup_mul_apply_kernel<<<grid_for(c, aodp), 256, 0, c->stream>>>(L->g_raw, aod, aodp, mx, L->sigmoid, L->n_table, L->attn_out,
-                                                                             L->g_q, L->g_sig, L->gated_attn, c->status);
+    launch_pdl(requant_lookup_mul_apply_kernel, dim3(grid_for(c, aodp)), dim3(256), c->stream, (const u32*)L->g_raw, aod, aodp, mx, L->sigmoid, L->n_table,
+               (const u32*)L->attn_out, L->g_q, L->g_sig, L->gated_attn, c->status);
     ZKB_LAUNCHED(c);
     matvec_forward(c, L->w[W_O], L->gated_attn, dm, aod, L->gated_out, dmp, false);
     // h = x + gated_out and the second norm in one launch
-    rmsnorm_forward_kernel<<<1, c->single_cta_threads(), 0, c->stream>>>(L->x, L->w[W_NORM2], dm, dmp, L->norm2_out, L->norm2_x, L->n2_scalars, c->status,
-                                                                        L->gated_out, L->h);
+    launch_pdl(rmsnorm_forward_kernel, dim3(1), dim3(c->single_cta_threads()), c->stream, (const u32*)L->x, (const u32*)L->w[W_NORM2], dm, dmp,
+               L->norm2_out, L->norm2_x, L->n2_scalars, c->status, (const u32*)L->gated_out, L->h);
     ZKB_LAUNCHED(c);
     {
         const u32* Wm[2] = {L->w[W_GATE], L->w[W_UP]};
@@ -148,11 +150,11 @@ inline void qwen_forward(zkb_qwen_layer* L) {
         matvec_forward_batch(c, 2, Wm, ym, mm, L->norm2_out, dm);
     }
     unsigned long long* mx2 = reinterpret_cast<unsigned long long*>(L->n2_scalars + 4);
-    requant_lookup_mul_apply_kernel<<<grid_for(c, dffp), 256, 0, c->stream>>>(L->gate_raw, d.d_ff, dffp, mx2, L->silu, L->n_table, L->up,
-                                                                              L->gate_q, L->gate_silu, L->swiglu, c->status);
+    launch_pdl(requant_lookup_mul_apply_kernel, dim3(grid_for(c, dffp)), dim3(256), c->stream, (const u32*)L->gate_raw, d.d_ff, dffp, mx2, L->silu, L->n_table,
+               (const u32*)L->up, L->gate_q, L->gate_silu, L->swiglu, c->status);
     ZKB_LAUNCHED(c);
     matvec_forward(c, L->w[W_DOWN], L->swiglu, dm, d.d_ff, L->down, dmp, false);
-    add_vec_kernel<<<grid_for(c, dmp), 256, 0, c->stream>>>(L->h, L->down, dm, dmp, L->out);
+    launch_pdl(add_vec_kernel, dim3(grid_for(c, dmp)), dim3(256), c->stream, (const u32*)L->h, (const u32*)L->down, dm, dmp, L->out);
     ZKB_LAUNCHED(c);
     ZKB_CUDA(cudaGetLastError());
     L->have_trace = true;

@@ -1,5 +1,6 @@
 // C ABI of the backend (see include/zkb200.h) and the host-side launch logic.
 #include "qwen.cuh"
+#include "oplist.cuh"
 #include "basefold.cuh"
 #include <cstdlib>
 #include <cstring>
@@ -416,6 +417,7 @@ int32_t zkb_sumcheck_prove(zkb_ctx* c, zkb_transcript* t, int32_t kind, const ui
 #include "abi_layer.cuh"
 #include "abi_pcs.cuh"
 #include "abi_split.cuh"
+#include "abi_oplist.cuh"
 
 // =============================================================================================
 // Allocation-free weight fold
