@@ -180,6 +180,13 @@ int32_t zkb_matvec_forward(zkb_ctx* ctx, const uint32_t* W, const uint32_t* x, s
 int32_t zkb_rmsnorm_forward(zkb_ctx* ctx, const uint32_t* x, const uint32_t* gamma, size_t d, uint32_t* out, uint32_t* x_used,
                             int32_t* delta);
 
+/* requantize_to_i16_field (transformer/mod.rs:293-324): q[i] = the int16-range requantisation of the
+ * centred value raw[i] (scaled by 32767 / max |raw| when that maximum exceeds 32767), and, when a
+ * table is given (device-resident output column of 65536 or 256 entries), t[i] = table[q[i]]
+ * (qwen.rs:286-316).  raw: host or device; q_out, t_out: host.  A value outside the table is ZKB_E_ARG. */
+int32_t zkb_requantize_lookup(zkb_ctx* ctx, const uint32_t* raw, size_t n, int32_t on_device, const uint32_t* table_out_dev,
+                              uint32_t n_table, uint32_t* q_out, uint32_t* t_out);
+
 /* ---- sub-protocol provers: host inputs, proof returned as the reference's bincode bytes.
  * *len receives the proof length; ZKB_E_TOO_LARGE if it exceeds cap. ---- */
 /* prove_matmul_succinct_ef -> SuccinctMatmulProofEF                    matmul.rs:963-997 */

@@ -172,3 +172,21 @@ def test_context_options_keep_the_proof_bytes(ctx):
             c2.set_option(77, 1)
     finally:
         c2.close()
+
+
+def test_requantize_lookup_matches_host_statement(ctx):
+    """zkb_requantize_lookup against the numpy statement of requantize_to_i16_field
+    (transformer/mod.rs:293-324) and a table lookup: small values pass through, large ones are scaled."""
+    from zklm_compile_b200 import tables
+    rng = np.random.default_rng(31)
+    gelu = tables.build_gelu_table(1000)
+    tdev = ctx.upload(gelu)
+    for n, lim in [(1, 5), (1000, 100), (1024, 1 << 20), (4099, 1 << 30)]:
+        v = np.mod(rng.integers(-lim, lim + 1, n), P).astype(np.uint32)
+        q, t = zp.requantize_lookup(ctx, v, tdev)
+        exp = tables.requantize_to_i16_field(v)
+        assert q.tolist() == exp.tolist()
+        s = np.where(exp > P // 2, exp.astype(np.int64) - P, exp.astype(np.int64))
+        assert t.tolist() == gelu[np.mod(s, gelu.size)].tolist()
+        assert zp.requantize_lookup(ctx, v).tolist() == exp.tolist()
+    tdev.free()

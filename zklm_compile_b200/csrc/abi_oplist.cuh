@@ -209,6 +209,30 @@ std::vector<uint8_t> ol_prove(OL* L, uint32_t* status_out) {
 
 extern "C" {
 
+// requantize_to_i16_field (transformer/mod.rs:293-324) and, with a table, the activation lookup
+// (qwen.rs:286-316: table[requantised value]) of a vector, on the device.
+int32_t zkb_requantize_lookup(zkb_ctx* c, const uint32_t* raw, size_t n, int32_t on_device, const uint32_t* table_out_dev, uint32_t n_table,
+                              uint32_t* q_out, uint32_t* t_out) {
+    if (!c || !raw || !q_out || n == 0 || n > (size_t(1) << 28) || (table_out_dev && n_table != 256 && n_table != 65536) ||
+        (table_out_dev && !t_out)) return ZKB_E_ARG;
+    ZKB_TRY(c, {
+        c->use();
+        clear_status(c);
+        const u32* d = on_device ? raw : up_pad(c, raw, n, n);
+        u32* q = (u32*)c->scratch(n * 4);
+        u32* t = table_out_dev ? (u32*)c->scratch(n * 4) : nullptr;
+        requant_lookup_kernel<<<grid_for(c, n), 256, 0, c->stream>>>(d, (u32)n, (u32)n, table_out_dev, n_table, q, t, c->status);
+        ZKB_LAUNCHED(c);
+        ZKB_CUDA(cudaGetLastError());
+        ZKB_CUDA(cudaMemcpyAsync(q_out, q, n * 4, cudaMemcpyDeviceToHost, c->stream));
+        if (t) ZKB_CUDA(cudaMemcpyAsync(t_out, t, n * 4, cudaMemcpyDeviceToHost, c->stream));
+        uint32_t st = c->read_status();
+        c->scratch_reset();
+        int32_t rc = status_to_code(c, st);
+        if (rc) return rc;
+    });
+}
+
 int32_t zkb_oplist_create(zkb_ctx* c, uint32_t input_len, zkb_oplist** out) {
     if (!c || !out || input_len == 0) return ZKB_E_ARG;
     *out = nullptr;

@@ -9,7 +9,6 @@ import numpy as np
 
 from . import protocols as zp
 from .sumcheck import Context, Transcript
-from .tables import requantize_to_i16_field, table_inputs
 
 
 class DenseChain:
@@ -19,19 +18,16 @@ class DenseChain:
         self.dims = list(dims)
         self.w = [ctx.upload(np.ascontiguousarray(w, dtype=np.uint32).reshape(-1)) for w in weights]
         self.table_out = np.ascontiguousarray(table_out, dtype=np.uint32)
-        self._tin = table_inputs(self.table_out.size)
+        self._table_dev = ctx.upload(self.table_out)
 
     def forward(self, x):
         """Returns the trace [(x_l, y_l, q_l, a_l)]: y = W x, q = requantised y, a = table[q]."""
-        P = (1 << 31) - 1
         trace, cur = [], np.ascontiguousarray(x, dtype=np.uint32)
         for l, w in enumerate(self.w):
             m, n = self.dims[l + 1], self.dims[l]
             y = zp.matmul_forward(self.ctx, w, cur, m, n)
             if l + 1 < len(self.w):
-                q = requantize_to_i16_field(y)
-                signed = np.where(q > P // 2, q.astype(np.int64) - P, q.astype(np.int64))
-                a = self.table_out[np.mod(signed, self.table_out.size)]
+                q, a = zp.requantize_lookup(self.ctx, y, self._table_dev)      # on the device (requantize_to_i16_field + table lookup)
                 trace.append((cur, y, q, a))
                 cur = a
             else:
@@ -53,3 +49,4 @@ class DenseChain:
         for w in self.w:
             w.free()
         self.w = []
+        self._table_dev.free()

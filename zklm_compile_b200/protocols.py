@@ -105,6 +105,18 @@ def batch_inverse(ctx: Context, vals, ef: bool = False):
     return out
 
 
+def requantize_lookup(ctx: Context, raw, table_out: DeviceBuffer = None):
+    """transformer/mod.rs:293-324 (+ the activation lookup of qwen.rs:286-316 when a table is given).
+    Returns q, or (q, table[q])."""
+    r, pr = _a(raw)
+    q = np.zeros(r.size, np.uint32)
+    t = np.zeros(r.size, np.uint32) if table_out is not None else None
+    check(ctx.h, _lib.lib().zkb_requantize_lookup(ctx.h, pr, C.c_size_t(r.size), C.c_int32(0), table_out.ptr if table_out is not None else None,
+                                                   C.c_uint32(table_out.n if table_out is not None else 0), q.ctypes.data_as(u32p),
+                                                   t.ctypes.data_as(u32p) if t is not None else None))
+    return q if t is None else (q, t)
+
+
 def fold_eq_matvec(ctx: Context, w_flat, m: int, n: int, r_point, ef: bool = False) -> np.ndarray:
     """matmul.rs:76-128 (ef=False) / :743-835 (ef=True)."""
     r, pr = _a(r_point)
