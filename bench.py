@@ -590,10 +590,26 @@ def run_oplist_legs(zk, ctx, with_cpu, cores):
               "published_ms_apple_m4_max": 24.7, "published_over_this": round(24.7 / r["ms_per_step_wall"], 2)})
     out["dense4m_published_shape"] = r
 
-    rng = np.random.default_rng(12)
-    D, F, V, NL = 768, 3072, 50257, 12
+    # the same four 1024 x 1024 linears as the EF chain of run_mlp, as the reference's pipeline would take them:
+    # linear, gelu, set_input, ..., linear (a set_input segment boundary after every gelu: verification.rs:429-437, 509-530)
     gelu_h = tables.build_gelu_table(1000)
     gelu_d = ctx.upload(gelu_h)
+    rng = np.random.default_rng(4)
+    ws = [_i8(rng, 1024 * 1024) for _ in range(4)]
+    x = _i8(rng, 1024)
+    p = _OpListPair(ctx, x, with_cpu)
+    for l in range(4):
+        p.linear(f"fc{l}", ws[l], None, 1024, 1024)
+        if l < 3:
+            p.gelu(f"gelu{l}", gelu_h, gelu_d)
+            p.set_input_requant(f"seg{l + 1}")
+    r = p.measure(10, 3, 3)
+    r["workload"] = ("Dense-4M, four 1024x1024 linears: linear, gelu, set_input, ..., linear in op-list mode (base-field challenges, "
+                     "one transcript, reverse order)")
+    out["dense4m_oplist"] = r
+
+    rng = np.random.default_rng(12)
+    D, F, V, NL = 768, 3072, 50257, 12
     x = _i8(rng, D)
     t_setup = time.perf_counter()
     p = _OpListPair(ctx, x, with_cpu)

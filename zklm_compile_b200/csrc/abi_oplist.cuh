@@ -85,12 +85,44 @@ struct OlProofRec {
     std::string text;
 };
 
+// Record offset of the content digest of (v, n); the digests of one proof are computed up front by ol_hash_all.
 size_t ol_hash(OL* L, const zkb::u32* v, zkb::u32 n) {
+    for (size_t j = 0; j < L->hash_jobs.size(); j++)
+        if (L->hash_jobs[j].v == v && L->hash_jobs[j].n == n) return L->hash_base + 8 * j;
+    throw ArgFail{ZKB_E_ARG, "op list: content digest not scheduled"};
+}
+void ol_hash_all(OL* L) {
     zkb_ctx* c = L->ctx;
-    size_t off = c->rec_alloc(8);
-    hash_values_kernel<<<1, TRSCRIPT_THREADS, 0, c->stream>>>(v, n, c->rec_dev + off);
+    if (L->hash_jobs_nops != L->ops.size()) {            // first proof, or ops were added since the last one
+        L->hash_jobs.clear();
+        auto want = [&](const zkb::u32* v, zkb::u32 n) {
+            for (const HashJob& j : L->hash_jobs) if (j.v == v && j.n == n) return;
+            L->hash_jobs.push_back(HashJob{v, n, 0});
+        };
+        for (size_t idx = 0; idx < L->ops.size(); idx++) {
+            const OL::Op& op = L->ops[idx];
+            switch (op.kind) {
+                case OL::ATTENTION: case OL::PASSTHROUGH: case OL::SAVE: want(op.out, op.out_len); break;
+                case OL::SET_INPUT: case OL::SET_INPUT_REQUANT:
+                    want(op.out, op.out_len);
+                    if (idx > 0) want(L->ops[idx - 1].out, L->ops[idx - 1].out_len);
+                    break;
+                default: break;
+            }
+        }
+        if (!L->hash_jobs.empty()) {
+            void* d = nullptr;
+            ZKB_CUDA(cudaMalloc(&d, L->hash_jobs.size() * sizeof(HashJob)));
+            L->owned.push_back(d);
+            L->hash_jobs_dev = (HashJob*)d;
+            ZKB_CUDA(cudaMemcpyAsync(d, L->hash_jobs.data(), L->hash_jobs.size() * sizeof(HashJob), cudaMemcpyHostToDevice, c->stream));
+        }
+        L->hash_jobs_nops = L->ops.size();
+    }
+    if (L->hash_jobs.empty()) return;
+    L->hash_base = c->rec_alloc(8 * L->hash_jobs.size());
+    hash_values_multi_kernel<<<(unsigned)L->hash_jobs.size(), TRSCRIPT_THREADS, 0, c->stream>>>(L->hash_jobs_dev, c->rec_dev + L->hash_base);
     ZKB_LAUNCHED(c);
-    return off;
 }
 
 // prove_all_ops, sequential branch (pipeline/prove.rs:191-648): enqueue everything, fetch the record once, serialise.
@@ -101,6 +133,7 @@ std::vector<uint8_t> ol_prove(OL* L, uint32_t* status_out) {
     tr_init_kernel<<<1, 1, 0, c->stream>>>(tr);
     ZKB_LAUNCHED(c);
     { ScriptBuilder sb; sb.str("structured-ml-proof"); sb.run(c, tr); }
+    ol_hash_all(L);
     std::vector<OlProofRec> recs;
     const zkb::u32* chain_point = nullptr;        // s_point of the last pushed proof when that proof is a matmul
     for (size_t idx = L->ops.size(); idx-- > 0;) {

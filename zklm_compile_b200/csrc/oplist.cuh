@@ -151,6 +151,28 @@ __global__ void __launch_bounds__(TRSCRIPT_THREADS) hash_values_kernel(const u32
     }
 }
 
+// The same digest for a list of vectors, one CTA each: the content digests of an op list (save,
+// set_input, attention, passthrough) depend only on the forward pass, not on the transcript, so they
+// are all computed side by side in one launch instead of one after another between the proofs.
+struct HashJob { const u32* v; u32 n; u32 _pad; };
+__global__ void __launch_bounds__(TRSCRIPT_THREADS) hash_values_multi_kernel(const HashJob* __restrict__ jobs, u32* digests_out) {
+    __shared__ __align__(16) unsigned char trbuf[TR_SCRATCH_BYTES];
+    __shared__ u32 tile[2 * 512];
+    __shared__ u32 kw[2 * 32 * SHA_KW_STRIDE];
+    __shared__ u32 bc[1];
+    const u32* v = jobs[blockIdx.x].v;
+    const u32 n = jobs[blockIdx.x].n;
+    Tr tr;
+    tr.buf = trbuf; tr.buflen = 0; tr.total = 0;
+    if (threadIdx.x == 0) { tr_iv(tr.h); tr_absorb_u32(tr, n); }
+    tr_absorb_stream_2w(tr, n, [=](u32 g) -> u32 { return v[g]; }, reinterpret_cast<u32*>(trbuf), tile, kw, bc);
+    if (threadIdx.x == 0) {
+        u32 d[8];
+        tr_finalize_reseed(tr, d);
+        for (int i = 0; i < 8; i++) digests_out[8 * blockIdx.x + i] = bswap32(d[i]);
+    }
+}
+
 // ---- squared LayerNorm (layernorm.rs:522-695) ----------------------------------------------------------
 struct LayerNormRec {
     u32 k = 0;
@@ -333,5 +355,9 @@ struct zkb_oplist {
     zkb::u32 x_cap = 0;
     std::vector<void*> owned;                  // device allocations to free
     zkb::u32 cur_len = 0;                      // running activation length while ops are added
+    std::vector<zkb::HashJob> hash_jobs;       // distinct (vector, length) pairs whose content digest a proof needs
+    zkb::HashJob* hash_jobs_dev = nullptr;
+    size_t hash_jobs_nops = 0;                 // number of ops the job list was built for
+    size_t hash_base = 0;                      // record offset of the digests of the current proof
     bool len_known = false;
 };

@@ -332,22 +332,9 @@ __device__ __forceinline__ void tr_squeeze_el(Tr& t, Fe& r) { r = tr_squeeze_fe(
 // call load).  `tr` is meaningful in lane 0 only; tile (512 words) and kw (32 * SHA_KW_STRIDE
 // words) are shared-memory scratch.  Must be called by all 32 lanes of one warp.
 template <class Load>
-__device__ __forceinline__ void tr_absorb_stream_warp(Tr& tr, u32 total, Load load, u32* tile, u32* kw) {
+__device__ __forceinline__ void tr_absorb_stream_warp_aligned(Tr& tr, u32 total, Load load, u32* bufw, u32 have, u32* tile, u32* kw) {
     const int lane = threadIdx.x & 31;
-    __syncwarp();                      // lane 0's earlier writes to the stream buffer become visible
-    const u32 buflen = __shfl_sync(0xffffffffu, tr.buflen, 0);
-    u32* bufw = reinterpret_cast<u32*>(__shfl_sync(0xffffffffu, (unsigned long long)tr.buf, 0));
-    if (buflen & 3) {                  // byte-misaligned stream: plain path
-        for (u32 base = 0; base < total; base += 512) {
-            u32 m = total - base < 512 ? total - base : 512;
-            for (u32 i = lane; i < m; i += 32) tile[i] = load(base + i);
-            __syncwarp();
-            if (lane == 0) for (u32 i = 0; i < m; i++) tr_absorb_u32(tr, tile[i]);
-            __syncwarp();
-        }
-        return;
-    }
-    u32 have = buflen >> 2, pos = 0;
+    u32 pos = 0;
     while (have + (total - pos) >= 16) {
         u32 nb = (have + (total - pos)) / 16;
         if (nb > 32) nb = 32;
@@ -372,6 +359,29 @@ __device__ __forceinline__ void tr_absorb_stream_warp(Tr& tr, u32 total, Load lo
     __syncwarp();
     if (lane == 0) { tr.buflen = (have + rest) * 4; tr.total += (u64)total * 4; }
 }
+// A stream that holds 4 * have + s bytes (s = 1..3) takes the words shifted by s bytes: stream word i
+// is the funnel shift of data words i - 1 and i, the s pending bytes standing in for word -1, and the
+// top s bytes of the last word stay pending.  The blocks are then hashed exactly like aligned ones.
+template <class Load>
+__device__ __forceinline__ void tr_absorb_stream_warp(Tr& tr, u32 total, Load load, u32* tile, u32* kw) {
+    const int lane = threadIdx.x & 31;
+    __syncwarp();                      // lane 0's earlier writes to the stream buffer become visible
+    const u32 buflen = __shfl_sync(0xffffffffu, tr.buflen, 0);
+    u32* bufw = reinterpret_cast<u32*>(__shfl_sync(0xffffffffu, (unsigned long long)tr.buf, 0));
+    const u32 s = buflen & 3, have = buflen >> 2;
+    if (s == 0) { tr_absorb_stream_warp_aligned(tr, total, load, bufw, have, tile, kw); return; }
+    if (total == 0) return;
+    const u32 sh = 8 * s;
+    const u32 pend = bufw[have] << (32 - sh);
+    __syncwarp();
+    tr_absorb_stream_warp_aligned(tr, total, [=](u32 g) -> u32 { return __funnelshift_l(g ? load(g - 1) : pend, load(g), sh); },
+                                  bufw, have, tile, kw);
+    if (lane == 0) {
+        bufw[tr.buflen >> 2] = load(total - 1) >> (32 - sh);
+        tr.buflen += s;
+    }
+    __syncwarp();
+}
 
 // The same absorb for a CTA of two warps with the loads and the schedule expansion taken off the
 // hash chain: while lane 0 of warp 0 runs the rounds of one batch (up to 32 blocks, about 35 us),
@@ -380,24 +390,16 @@ __device__ __forceinline__ void tr_absorb_stream_warp(Tr& tr, u32 total, Load lo
 // identical arguments; `tr` is meaningful in thread 0; `bufw` is the stream buffer (shared
 // memory) that tr.buf points to; tile holds 2 x 512 words, kw 2 x 32 x SHA_KW_STRIDE, bc 1 word.
 template <class Load>
-__device__ __forceinline__ void tr_absorb_stream_2w(Tr& tr, u32 total, Load load, u32* bufw, u32* tile, u32* kw, u32* bc) {
+__device__ __forceinline__ void tr_absorb_stream_2w_aligned(Tr& tr, u32 total, Load load, u32* bufw, u32 have, u32* tile, u32* kw) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (threadIdx.x == 0) bc[0] = tr.buflen;
-    __syncthreads();                   // also: thread 0's earlier writes to the stream buffer become visible
-    const u32 buflen = bc[0];
-    if (buflen & 3) {                  // byte-misaligned stream: plain path on warp 0
-        if (warp == 0) tr_absorb_stream_warp(tr, total, load, tile, kw);
-        __syncthreads();
-        return;
-    }
-    auto produce = [&](u32 slot, u32 have, u32 pos, u32 nb) {   // warp 1: words [pos, ...) after `have` buffered ones
+    auto produce = [&](u32 slot, u32 have_, u32 pos, u32 nb) {   // warp 1: words [pos, ...) after `have_` buffered ones
         u32* t = tile + slot * 512;
         u32* k = kw + slot * 32 * SHA_KW_STRIDE;
-        for (u32 j = lane; j < nb * 16; j += 32) t[j] = bswap32(j < have ? bufw[j] : load(pos + j - have));
+        for (u32 j = lane; j < nb * 16; j += 32) t[j] = bswap32(j < have_ ? bufw[j] : load(pos + j - have_));
         __syncwarp();
         if ((u32)lane < nb) sha256_expand_kw(t + lane * 16, k + lane * SHA_KW_STRIDE);
     };
-    u32 have = buflen >> 2, pos = 0;
+    u32 pos = 0;
     u32 nb = (have + total) / 16;
     if (nb > 32) nb = 32;
     if (nb && warp == 1) produce(0, have, 0, nb);
@@ -424,6 +426,26 @@ __device__ __forceinline__ void tr_absorb_stream_2w(Tr& tr, u32 total, Load load
     const u32 rest = total - pos;      // fewer than 16 - have words: they stay in the stream buffer
     if (warp == 0) for (u32 j = lane; j < rest; j += 32) bufw[have + j] = load(pos + j);
     if (threadIdx.x == 0) { tr.buflen = (have + rest) * 4; tr.total += (u64)total * 4; }
+    __syncthreads();
+}
+template <class Load>
+__device__ __forceinline__ void tr_absorb_stream_2w(Tr& tr, u32 total, Load load, u32* bufw, u32* tile, u32* kw, u32* bc) {
+    if (threadIdx.x == 0) bc[0] = tr.buflen;
+    __syncthreads();                   // also: thread 0's earlier writes to the stream buffer become visible
+    const u32 buflen = bc[0];
+    const u32 s = buflen & 3, have = buflen >> 2;
+    if (s == 0) { tr_absorb_stream_2w_aligned(tr, total, load, bufw, have, tile, kw); return; }
+    if (total == 0) { __syncthreads(); return; }
+    // byte-misaligned stream (a label of odd length in front, for instance): the same pipeline over funnel-shifted words
+    const u32 sh = 8 * s;
+    const u32 pend = bufw[have] << (32 - sh);
+    __syncthreads();                   // every thread holds the pending bytes before the buffer is written again
+    tr_absorb_stream_2w_aligned(tr, total, [=](u32 g) -> u32 { return __funnelshift_l(g ? load(g - 1) : pend, load(g), sh); },
+                                bufw, have, tile, kw);
+    if (threadIdx.x == 0) {
+        bufw[tr.buflen >> 2] = load(total - 1) >> (32 - sh);
+        tr.buflen += s;
+    }
     __syncthreads();
 }
 
