@@ -463,9 +463,20 @@ def run_basefold(zk, ctx, n, reps=3):
     for _ in range(reps):
         ctx.timer_start(); zp.basefold_encode(ctx, coeffs, out=cw); t_enc.append(ctx.timer_stop_ms())
     enc_ms = min(t_enc)
-    enc_bytes = n * 2 * (2 * N * 4)
+    # what the fused passes move: 12 levels in the first pass, up to 6 in each later one; every pass reads and writes
+    # one half-codeword (2^n words), the last one writes both halves; each level's twiddle table is read once
+    passes, lv = 1, min(n, 12)
+    while lv < n:
+        rem = n - lv
+        lv += rem if rem <= 6 else ((rem + 1) // 2 if rem < 12 else 6)
+        passes += 1
+    enc_bytes = (2 * passes + 1) * N * 4 + (N - 1) * 4
+    peak = load_peaks()[0]
     out["encode_ms"] = round(enc_ms, 4)
-    out["encode_algorithmic_GBps"] = round(enc_bytes / enc_ms / 1e6, 1)
+    out["encode_passes"] = passes
+    out["encode_roofline"] = {"bound": "hbm", "achieved": round(enc_bytes / enc_ms / 1e6, 1), "peak": peak, "unit": "GB/s",
+                              "frac": round(enc_bytes / enc_ms / 1e6 / peak, 4), "traffic": None, "algorithmic_bytes": enc_bytes,
+                              "unfused_level_by_level_bytes": n * 2 * (2 * N * 4)}
     for name, kind in (("blake3", 0), ("aes_mmo", 1)):
         t_mk, t_all = [], []
         for _ in range(reps):
@@ -473,9 +484,20 @@ def run_basefold(zk, ctx, n, reps=3):
             tr = zk.Transcript(ctx, b"bench-basefold")
             ctx.timer_start(); blob = zp.basefold_commit_and_prove(ctx, tr, coeffs, point, kind); t_all.append(ctx.timer_stop_ms())
         mk_bytes = 2 * N * 4 + (2 * N - 1) * 16
-        out["node_hash"][name] = {"merkle_ms": round(min(t_mk), 4), "merkle_GBps": round(mk_bytes / min(t_mk) / 1e6, 1),
-                                  "merkle_Mnodes_per_s": round((2 * N - 1) / min(t_mk) / 1e3, 1),
-                                  "commit_and_prove_ms": round(min(t_all), 3), "proof_bytes": len(blob)}
+        ctx.set_option(ctx.OPT_BASEFOLD_IN_ORDER, 1)
+        t_ord = []
+        for _ in range(reps):
+            tr = zk.Transcript(ctx, b"bench-basefold")
+            ctx.timer_start(); blob2 = zp.basefold_commit_and_prove(ctx, tr, coeffs, point, kind); t_ord.append(ctx.timer_stop_ms())
+        ctx.set_option(ctx.OPT_BASEFOLD_IN_ORDER, 0)
+        assert blob2 == blob
+        out["node_hash"][name] = {"merkle_ms": round(min(t_mk), 4), "merkle_Mnodes_per_s": round((2 * N - 1) / min(t_mk) / 1e3, 1),
+                                  "merkle_roofline": {"bound": "integer issue (one compression per node); HBM figure for reference",
+                                                      "achieved": round(mk_bytes / min(t_mk) / 1e6, 1), "peak": peak, "unit": "GB/s",
+                                                      "frac": round(mk_bytes / min(t_mk) / 1e6 / peak, 4), "traffic": None,
+                                                      "algorithmic_bytes": mk_bytes},
+                                  "commit_and_prove_ms": round(min(t_all), 3), "commit_and_prove_in_order_ms": round(min(t_ord), 3),
+                                  "proof_bytes": len(blob), "proof_sha256": hashlib.sha256(blob).hexdigest()}
     for b in (coeffs, point, cw):
         b.free()
     return out
@@ -877,7 +899,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="qwen4b", choices=["qwen4b", "sumcheck", "qwen9b"])
+    ap.add_argument("--workload", default="qwen4b", choices=["qwen4b", "sumcheck", "qwen9b", "oplist"])
     ap.add_argument("--chunk", type=int, default=8, help="qwen9b: layers proved at a time per GPU (contexts per GPU)")
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--n", "--log-n", dest="n", type=int, default=28, help="sumcheck workload: log2 of the table length")
@@ -899,6 +921,25 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     cores = os.cpu_count() or 1
     qwen = args.workload == "qwen4b"
+    if args.workload == "oplist":
+        # configs 1 and 3 alone (one GPU; an op list is one transcript, so more GPUs would be replicas): the legs that
+        # the default line carries as dense4m_* and gpt2_124m_oplist, printed as a line of their own
+        if rank == 0 and args.impl == "ours":
+            import zklm_compile_b200 as zk
+            ctx = zk.Context(local)
+            legs = run_oplist_legs(zk, ctx, not args.no_cpu, cores)
+            g = legs["gpt2_124m_oplist"]
+            print(json.dumps({"metric": "op-list prove ms (GPT-2-124M shape, 182 ops, seq_len 1, base-field challenges)", "value": g["ms_per_step_wall"],
+                              "unit": "ms", "n_gpus": 1, "steps": 5, "warmup": 3, "ms_per_step": g["ms_per_step_wall"], "higher_is_better": False,
+                              "scaling": "weak", "vs_baseline": round(g["ms_per_step_wall"] / 253.0, 4), "dtype": "u32 (M31)", "data": "synthetic",
+                              "config": {"workload": g["workload"]}, "gpu_launches": g["gpu_launches_per_step"] * 5,
+                              "e2e": {"value": g["ms_per_step_wall"], "unit": "ms", "h2d_bytes_per_step": 768 * 4, "d2h_bytes_per_step": g["proof_bytes"],
+                                      "note": "the timed call takes the input from host memory and returns the proof bytes on the host"},
+                              "cpu_baseline": ({"value": g["cpu_port_ms"], "unit": "ms", "cores": cores, "kind": "port",
+                                                "sample": "the same 182-op list, 2 runs"} if "cpu_port_ms" in g else None), **legs}))
+        elif rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "the op-list workload's CPU port time is part of the default arm's line (cpu_port_ms)"}))
+        return
     if args.workload == "qwen9b":
         if args.impl == "reference":
             if rank == 0:

@@ -79,8 +79,12 @@ uint64_t zkb_ctx_scratch_bytes(const zkb_ctx* ctx);
  * ZKB_OPT_PIPE_THREADS: thread counts of the single-CTA kernels and of the pipelined tail.
  * ZKB_OPT_NO_FUSED_FOLD: nonzero = product sumchecks over base-field tables fold one challenge per
  * launch (they normally fold the first two challenges in one pass over the base tables).
- * ZKB_OPT_FOLD2_VEC: pair indices per thread (1, 2 or 4) of that two-challenge pass. */
-enum { ZKB_OPT_PLAIN_TAIL = 0, ZKB_OPT_SINGLE_CTA_THREADS = 1, ZKB_OPT_PIPE_THREADS = 2, ZKB_OPT_NO_FUSED_FOLD = 3, ZKB_OPT_FOLD2_VEC = 4 };
+ * ZKB_OPT_FOLD2_VEC: pair indices per thread (1, 2 or 4) of that two-challenge pass.
+ * ZKB_OPT_BASEFOLD_IN_ORDER: nonzero = a Basefold opening runs fold, tree and transcript step of
+ * each round one after another on the context's stream (normally the folds and trees of all rounds
+ * whose challenge is a coordinate of the point run ahead on a second stream). */
+enum { ZKB_OPT_PLAIN_TAIL = 0, ZKB_OPT_SINGLE_CTA_THREADS = 1, ZKB_OPT_PIPE_THREADS = 2, ZKB_OPT_NO_FUSED_FOLD = 3, ZKB_OPT_FOLD2_VEC = 4,
+       ZKB_OPT_BASEFOLD_IN_ORDER = 5 };
 int32_t zkb_ctx_set_option(zkb_ctx* ctx, int32_t option, int32_t value);
 /* The context's cudaStream_t (as an opaque pointer), for callers that enqueue their own work in order with the library's. */
 void* zkb_ctx_stream(zkb_ctx* ctx);

@@ -69,6 +69,23 @@ def test_basefold_commit_and_prove_bytes(ctx, kind, n):
     assert tg.squeeze() == to.squeeze()          # transcripts left in the same state
 
 
+@pytest.mark.parametrize("kind", KINDS)
+def test_basefold_in_order_and_run_ahead_schedules_agree(ctx, kind):
+    """The opening normally runs its folds and trees ahead of the transcript chain on a second stream;
+    with ZKB_OPT_BASEFOLD_IN_ORDER everything stays on one stream.  Same bytes, same transcript state,
+    also when openings follow one another on the same context (buffers reused)."""
+    n = (1 << 17) - 3
+    c, pt = rnd(41, n), rnd(42, 17)
+    exp = O.basefold_commit_and_prove(O.Transcript(b"bf-sched"), c, pt, kind)
+    for in_order in (0, 1, 0):
+        ctx.set_option(ctx.OPT_BASEFOLD_IN_ORDER, in_order)
+        tg = zk.Transcript(ctx, b"bf-sched")
+        try:
+            assert zp.basefold_commit_and_prove(ctx, tg, c, pt, kind) == exp
+        finally:
+            ctx.set_option(ctx.OPT_BASEFOLD_IN_ORDER, 0)
+
+
 def test_basefold_short_point_squeezes_challenges(ctx):
     c = rnd(5, 700)
     pt = rnd(6, 4)

@@ -317,12 +317,25 @@ inline BfPending basefold_enqueue(zkb_ctx* c, TrState* tr, CoefSrc src, size_t n
     const size_t n_pad = size_t(1) << log_n;
     BfPending pd;
     pd.log_n = log_n; pd.num_coeffs = num_coeffs;
+    // Every fold challenge that is a coordinate of the point is known before the opening starts (it is
+    // absorbed, not squeezed: basefold.rs:508-513), so the folds and trees of those rounds do not wait for
+    // the transcript: they run ahead on a second stream, each round into buffers of its own, while the
+    // context's stream runs the hash chain (root absorb, 24 query squeezes) and the path gathers behind them.
+    const bool ahead = n_point >= log_n && !c->opt_bf_in_order && !c->capturing;
     u32* cwA = (u32*)c->scratch(2 * n_pad * 4);
-    u32* cwB = (u32*)c->scratch(n_pad * 4);
+    u32* cwB = ahead ? nullptr : (u32*)c->scratch(n_pad * 4);
     u32* eval = (u32*)c->scratch((n_pad / 2 + 4) * 4);
     uint4* treeA = (uint4*)c->scratch(mk_node_count(log_n + 1) * 16 + 16);
-    uint4* treeB = (uint4*)c->scratch(mk_node_count(log_n) * 16 + 16);
+    uint4* treeB = ahead ? nullptr : (uint4*)c->scratch(mk_node_count(log_n) * 16 + 16);
     u32* alpha = (u32*)c->scratch((log_n + 1) * 4);
+    std::vector<u32*> cws;
+    std::vector<uint4*> trees;
+    if (ahead) {
+        for (u32 round = 0; round < log_n; round++) {
+            cws.push_back((u32*)c->scratch((size_t(4) << (log_n - round)) + 16));
+            trees.push_back((uint4*)c->scratch(mk_node_count(log_n - round) * 16 + 16));
+        }
+    }
 
     c->prof_mark();
     bf_encode(c, src, log_n, tb, cwA);
@@ -330,12 +343,19 @@ inline BfPending basefold_enqueue(zkb_ctx* c, TrState* tr, CoefSrc src, size_t n
     MkFold none{};
     mk_build(c, kind, MK_VALUES, cwA, 2 * n_pad, log_n + 1, treeA, none);
     c->prof_mark();
+    cudaStream_t main_stream = c->stream, side = nullptr;
+    if (ahead) {
+        side = c->side_stream();
+        cudaEvent_t fork = c->side_event(log_n);
+        ZKB_CUDA(cudaEventRecord(fork, main_stream));
+        ZKB_CUDA(cudaStreamWaitEvent(side, fork, 0));
+    }
     pd.root_off = c->rec_alloc(4);
     bf_begin_kernel<<<1, 1, 0, c->stream>>>(tr, treeA + mk_layer_offset(log_n + 1, log_n + 1), point_dev, n_point, alpha, c->rec_dev + pd.root_off);
     ZKB_LAUNCHED(c);
 
-    u32* prev_cw = cwA; u32* next_cw = cwB;
-    uint4* prev_tree = treeA; uint4* next_tree = treeB;
+    u32* prev_cw = cwA; u32* next_cw = ahead ? cws[0] : cwB;
+    uint4* prev_tree = treeA; uint4* next_tree = ahead ? trees[0] : treeB;
     for (u32 round = 0; round < log_n; round++) {
         const u32 h_prev = log_n + 1 - round;
         const size_t half = size_t(1) << (h_prev - 1);
@@ -344,11 +364,19 @@ inline BfPending basefold_enqueue(zkb_ctx* c, TrState* tr, CoefSrc src, size_t n
         f.prev = prev_cw; f.out = next_cw;
         f.weights = tb.w_flat + ((size_t(1) << fold_level) - 1);
         f.w_len = size_t(1) << fold_level;
-        f.alpha = alpha + round;
+        f.alpha = ahead ? point_dev + round : alpha + round;
         f.eval_src = eval; f.eval_dst = eval; f.eval_half = half / 2;
         f.coef = src.p; f.coef_rows = src.rows; f.coef_cols = src.cols; f.coef_log_cols_pad = src.log_cols_pad;
         f.eval_from_coef = round == 0;
-        mk_build(c, kind, MK_FOLD, nullptr, half, h_prev - 1, next_tree, f);
+        if (ahead) {
+            c->stream = side;
+            try { mk_build(c, kind, MK_FOLD, nullptr, half, h_prev - 1, next_tree, f); } catch (...) { c->stream = main_stream; throw; }
+            c->stream = main_stream;
+            ZKB_CUDA(cudaEventRecord(c->side_event(round), side));
+            ZKB_CUDA(cudaStreamWaitEvent(main_stream, c->side_event(round), 0));
+        } else {
+            mk_build(c, kind, MK_FOLD, nullptr, half, h_prev - 1, next_tree, f);
+        }
         c->prof_mark();
         BfRound rp{};
         rp.tr = tr; rp.point = point_dev; rp.n_point = n_point; rp.round = round; rp.log_n = log_n;
@@ -361,8 +389,13 @@ inline BfPending basefold_enqueue(zkb_ctx* c, TrState* tr, CoefSrc src, size_t n
         bf_round_kernel<<<1, 256, 0, c->stream>>>(rp);
         ZKB_LAUNCHED(c);
         c->prof_mark();
-        std::swap(prev_cw, next_cw);
-        std::swap(prev_tree, next_tree);
+        if (ahead) {
+            prev_cw = next_cw; prev_tree = next_tree;
+            if (round + 1 < log_n) { next_cw = cws[round + 1]; next_tree = trees[round + 1]; }
+        } else {
+            std::swap(prev_cw, next_cw);
+            std::swap(prev_tree, next_tree);
+        }
     }
     pd.final_off = c->rec_alloc(1);
     ZKB_CUDA(cudaMemcpyAsync(c->rec_dev + pd.final_off, eval, 4, cudaMemcpyDeviceToDevice, c->stream));

@@ -131,7 +131,23 @@ struct zkb_ctx {
     bool polite = false;
     // Tuning options (zkb_ctx_set_option): 0 = the built-in choice.
     int opt_single_threads = 0, opt_pipe_threads = 0, opt_fold2_vec = 0;
-    bool opt_plain_tail = false, opt_no_fused2 = false;
+    bool opt_plain_tail = false, opt_no_fused2 = false, opt_bf_in_order = false;
+    // Second stream for work that does not depend on the transcript (the fold / tree chain of a Basefold
+    // opening), joined to `stream` through events; created on first use.
+    cudaStream_t side = nullptr;
+    std::vector<cudaEvent_t> side_ev;
+    cudaStream_t side_stream() {
+        if (!side) ZKB_CUDA(cudaStreamCreateWithFlags(&side, cudaStreamNonBlocking));
+        return side;
+    }
+    cudaEvent_t side_event(size_t i) {
+        while (side_ev.size() <= i) {
+            cudaEvent_t e;
+            ZKB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+            side_ev.push_back(e);
+        }
+        return side_ev[i];
+    }
     int single_cta_threads() const { return opt_single_threads ? opt_single_threads : (polite ? 512 : 1024); }
     int pipe_threads(int full) const { return opt_pipe_threads ? opt_pipe_threads : (polite ? full / 2 : full); }
     int wide_ctas_per_sm(int greedy, int shared) const { return polite ? shared : greedy; }

@@ -33,8 +33,7 @@ __global__ void __launch_bounds__(1024) rmsnorm_forward_kernel(const u32* __rest
                                                                const u32* __restrict__ addend = nullptr, u32* sum_out = nullptr) {
     __shared__ u32 red[32];
     __shared__ u32 sh[3];   // r, x0', ok
-    pdl_wait();                  // the input comes from the kernel before this one
-    pdl_launch_dependents();     // only now: the next matvec may start pulling its weights into L2 while this small kernel runs
+    pdl_small_prologue();
     u32 acc = 0;
     if (addend) {
         for (u32 i = threadIdx.x; i < n_pad; i += blockDim.x) {
@@ -91,8 +90,7 @@ __global__ void __launch_bounds__(256) requant_lookup_mul_apply_kernel(const u32
                                                 const u32* __restrict__ table_out, u32 n_table, const u32* __restrict__ other,
                                                 u32* q_out, u32* t_out, u32* prod_out, u32* status) {
     __shared__ unsigned long long mx_s[8];
-    pdl_wait();                  // the input comes from the kernel before this one
-    pdl_launch_dependents();     // only now: the next matvec may start pulling its weights into L2 while this small kernel runs
+    pdl_small_prologue();
     unsigned long long mx = 1;
     for (u32 i = threadIdx.x; i < n; i += blockDim.x) {
         long long s = centered(raw[i]);
@@ -131,15 +129,13 @@ __global__ void __launch_bounds__(256) requant_lookup_mul_apply_kernel(const u32
 
 // out = a + b (n valid, zero-padded to n_pad)
 __global__ void add_vec_kernel(const u32* __restrict__ a, const u32* __restrict__ b, u32 n, u32 n_pad, u32* out) {
-    pdl_wait();                  // the input comes from the kernel before this one
-    pdl_launch_dependents();     // only now: the next matvec may start pulling its weights into L2 while this small kernel runs
+    pdl_small_prologue();
     for (u32 i = blockIdx.x * blockDim.x + threadIdx.x; i < n_pad; i += gridDim.x * blockDim.x)
         out[i] = i < n ? add31(a[i], b[i]) : 0u;
 }
 // GQA head replication at seq_len = 1 (qwen.rs:272-284): out[h*d_head + d] = v[(h / group) * d_head + d]
 __global__ void replicate_heads_kernel(const u32* __restrict__ v, u32 num_q_heads, u32 group, u32 d_head, u32 n_pad, u32* out) {
-    pdl_wait();                  // the input comes from the kernel before this one
-    pdl_launch_dependents();     // only now: the next matvec may start pulling its weights into L2 while this small kernel runs
+    pdl_small_prologue();
     for (u32 i = blockIdx.x * blockDim.x + threadIdx.x; i < n_pad; i += gridDim.x * blockDim.x) {
         u32 h = i / d_head, d = i % d_head;
         out[i] = h < num_q_heads ? v[(h / group) * d_head + d] : 0u;

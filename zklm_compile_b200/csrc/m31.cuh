@@ -118,6 +118,14 @@ ZKB_HD Fe dbl_minus(Fe hi, Fe lo) { return hi + hi - lo; }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+// First statements of the small kernels of a forward chain (norm, requantise, lookup, add), whose
+// input comes from the kernel before them and whose successor is a matvec that prefetches its weights.
+// (Releasing the successor before the wait, so that it becomes resident while the matvec in front is
+// still draining, measured slower: 170 against 162 us per layer of the 4B shape.)
+__device__ __forceinline__ void pdl_small_prologue() {
+    pdl_wait();                  // the input comes from the kernel before this one
+    pdl_launch_dependents();     // only now: the next matvec may start pulling its weights into L2 while this small kernel runs
+}
 
 // 16-byte vector load / store of an EF element.
 __device__ __forceinline__ Fe ld_fe(const Fe* p) {

@@ -81,6 +81,8 @@ void zkb_ctx_destroy(zkb_ctx* c) {
     if (c->rec_host) cudaFreeHost(c->rec_host);
     if (c->t0) cudaEventDestroy(c->t0);
     if (c->t1) cudaEventDestroy(c->t1);
+    for (cudaEvent_t e : c->side_ev) cudaEventDestroy(e);
+    if (c->side) cudaStreamDestroy(c->side);
     if (c->stream) cudaStreamDestroy(c->stream);
     delete c;
 }
@@ -358,6 +360,7 @@ int32_t zkb_ctx_set_option(zkb_ctx* c, int32_t option, int32_t value) {
             if (value != 0 && (value < 96 || value > PIPE_THREADS || value % 32)) { c->err = "pipelined-tail thread count must be 0 or a multiple of 32 in [96, 512]"; return ZKB_E_ARG; }
             c->opt_pipe_threads = value; break;
         case ZKB_OPT_NO_FUSED_FOLD: c->opt_no_fused2 = value != 0; break;
+        case ZKB_OPT_BASEFOLD_IN_ORDER: c->opt_bf_in_order = value != 0; break;
         case ZKB_OPT_FOLD2_VEC:
             if (value != 0 && value != 1 && value != 2 && value != 4) { c->err = "fold2 vector width must be 0, 1, 2 or 4"; return ZKB_E_ARG; }
             c->opt_fold2_vec = value; break;
