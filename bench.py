@@ -147,6 +147,28 @@ class ClockSampler:
                 "samples": len(sm), "window": window, "reasons": sorted(reasons)}
 
 
+_STDOUT_FD = None
+
+
+def claim_stdout():
+    """Keep the process's stdout for the one JSON line: whatever libraries print there from now on
+    (NCCL's version banner, for instance) goes to stderr instead."""
+    global _STDOUT_FD
+    if _STDOUT_FD is None:
+        sys.stdout.flush()
+        _STDOUT_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit_line(text):
+    sys.stdout.flush()
+    if _STDOUT_FD is None:
+        sys.stdout.write(text + "\n")
+        sys.stdout.flush()
+    else:
+        os.write(_STDOUT_FD, (text + "\n").encode())
+
+
 def load_peaks():
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
@@ -913,6 +935,7 @@ def main():
     ap.add_argument("--no-micro", action="store_true")
     ap.add_argument("--replicas", action="store_true", help="sumcheck workload at N > 1: N independent sumchecks instead of one split sumcheck")
     args = ap.parse_args()
+    claim_stdout()
     if args.impl == "ours":
         args.warmup = max(args.warmup, 3)
 
@@ -929,7 +952,7 @@ def main():
             ctx = zk.Context(local)
             legs = run_oplist_legs(zk, ctx, not args.no_cpu, cores)
             g = legs["gpt2_124m_oplist"]
-            print(json.dumps({"metric": "op-list prove ms (GPT-2-124M shape, 182 ops, seq_len 1, base-field challenges)", "value": g["ms_per_step_wall"],
+            emit_line(json.dumps({"metric": "op-list prove ms (GPT-2-124M shape, 182 ops, seq_len 1, base-field challenges)", "value": g["ms_per_step_wall"],
                               "unit": "ms", "n_gpus": 1, "steps": 5, "warmup": 3, "ms_per_step": g["ms_per_step_wall"], "higher_is_better": False,
                               "scaling": "weak", "vs_baseline": round(g["ms_per_step_wall"] / 253.0, 4), "dtype": "u32 (M31)", "data": "synthetic",
                               "config": {"workload": g["workload"]}, "gpu_launches": g["gpu_launches_per_step"] * 5,
@@ -938,12 +961,12 @@ def main():
                               "cpu_baseline": ({"value": g["cpu_port_ms"], "unit": "ms", "cores": cores, "kind": "port",
                                                 "sample": "the same 182-op list, 2 runs"} if "cpu_port_ms" in g else None), **legs}))
         elif rank == 0:
-            print(json.dumps({"impl": "reference", "unavailable": "the op-list workload's CPU port time is part of the default arm's line (cpu_port_ms)"}))
+            emit_line(json.dumps({"impl": "reference", "unavailable": "the op-list workload's CPU port time is part of the default arm's line (cpu_port_ms)"}))
         return
     if args.workload == "qwen9b":
         if args.impl == "reference":
             if rank == 0:
-                print(json.dumps({"impl": "reference", "unavailable": "the CPU restatement needs about a minute per 2^26-coefficient Basefold "
+                emit_line(json.dumps({"impl": "reference", "unavailable": "the CPU restatement needs about a minute per 2^26-coefficient Basefold "
                                   "(96 of them per proof at this shape): no bounded sample of this workload fits the time limit; the reference "
                                   "itself publishes 17.8 s for the 9B shape without pcs-full and 14.3 s for the 0.8B model with it (M4 Max)"}))
             return
@@ -971,7 +994,7 @@ def main():
         r = run_qwen9b(zk, args, rank, world, local, dist, barrier9, max9)
         if rank == 0:
             wb = 4 * sum(sum(layer_sizes(qwen9b_layer_config(i)).values()) for i in range(args.layers))
-            print(json.dumps({"metric": "end-to-end prove ms (Qwen3.5-9B shape, 32 layers, seq_len 1, EF challenges, pcs-full weight binding)",
+            emit_line(json.dumps({"metric": "end-to-end prove ms (Qwen3.5-9B shape, 32 layers, seq_len 1, EF challenges, pcs-full weight binding)",
                               "value": round(r["ms_per_step"], 2), "unit": "ms", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                               "ms_per_step": round(r["ms_per_step"], 2), "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
                               "dtype": "u32 (M31 / M31^4)", "data": "synthetic",
@@ -1021,7 +1044,7 @@ def main():
             cpu = {"value": round(gbps, 4), "unit": "GB/s", "cores": 1, "kind": "port",
                    "sample": f"same workload at 2^{args.n_cpu} elements per table; prove_product_ef is single-threaded in the reference; "
                              "C++ restatement (reference Rust binary: unavailable on this box)"}
-        print(json.dumps({"impl": "reference", "metric": metric, "value": round(value, 4), "unit": unit, "n_gpus": args.gpus, "steps": 1,
+        emit_line(json.dumps({"impl": "reference", "metric": metric, "value": round(value, 4), "unit": unit, "n_gpus": args.gpus, "steps": 1,
                           "warmup": 0, "ms_per_step": round(ms, 3), "higher_is_better": hib, "scaling": "strong" if qwen else "weak",
                           "vs_baseline": (round(value / PUBLISHED_QWEN4B_MS, 4) if qwen and args.layers == 32 else None),
                           "dtype": "u32 (M31 / M31^4)", "data": "synthetic", "config": config, "cpu_baseline": cpu,
@@ -1137,7 +1160,7 @@ def main():
                    "sample": f"same workload at 2^{args.n_cpu} elements per table, 2 timed runs; single-threaded as in the reference"}
     line["cpu_baseline"] = cpu
     if rank == 0:
-        print(json.dumps(line))
+        emit_line(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
 
