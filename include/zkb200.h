@@ -82,9 +82,16 @@ uint64_t zkb_ctx_scratch_bytes(const zkb_ctx* ctx);
  * ZKB_OPT_FOLD2_VEC: pair indices per thread (1, 2 or 4) of that two-challenge pass.
  * ZKB_OPT_BASEFOLD_IN_ORDER: nonzero = a Basefold opening runs fold, tree and transcript step of
  * each round one after another on the context's stream (normally the folds and trees of all rounds
- * whose challenge is a coordinate of the point run ahead on a second stream). */
+ * whose challenge is a coordinate of the point run ahead on a second stream).
+ * ZKB_OPT_MATVEC_PREFETCH_ROWS: 0..8, rows per CTA that a forward matvec prefetches into L2 before it
+ * waits for its input vector (default 8: the CTA's whole first pass; here 0 is a value, not "default").
+ * ZKB_OPT_MATVEC_RING: nonzero = forward matvecs whose rows are a multiple of 16 bytes (at most 64 KB)
+ * go through a shared-memory ring filled by bulk asynchronous copies, one persistent CTA per SM, instead of
+ * the kernel that stages rows in registers (measured slower on the 4B shape: 5.49 against 5.22 ms for the
+ * forward chain, so it is off unless asked for). */
 enum { ZKB_OPT_PLAIN_TAIL = 0, ZKB_OPT_SINGLE_CTA_THREADS = 1, ZKB_OPT_PIPE_THREADS = 2, ZKB_OPT_NO_FUSED_FOLD = 3, ZKB_OPT_FOLD2_VEC = 4,
-       ZKB_OPT_BASEFOLD_IN_ORDER = 5 };
+       ZKB_OPT_BASEFOLD_IN_ORDER = 5, ZKB_OPT_MATVEC_PREFETCH_ROWS = 6,
+       ZKB_OPT_MATVEC_RING = 7 };
 int32_t zkb_ctx_set_option(zkb_ctx* ctx, int32_t option, int32_t value);
 /* The context's cudaStream_t (as an opaque pointer), for callers that enqueue their own work in order with the library's. */
 void* zkb_ctx_stream(zkb_ctx* ctx);

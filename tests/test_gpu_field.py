@@ -190,3 +190,20 @@ def test_requantize_lookup_matches_host_statement(ctx):
         assert t.tolist() == gelu[np.mod(s, gelu.size)].tolist()
         assert zp.requantize_lookup(ctx, v).tolist() == exp.tolist()
     tdev.free()
+
+
+@pytest.mark.parametrize("m,n", [(1, 128), (5, 132), (77, 1024), (300, 2560), (1030, 768), (37, 9728), (9, 12288), (2051, 256), (64, 16384), (3, 20000), (50, 130)])
+def test_matvec_forward_ring_and_register_kernels(ctx, m, n):
+    """y = W x through both forward-matvec kernels: the register-staged one (the default) and the
+    shared-memory ring filled by bulk copies (ZKB_OPT_MATVEC_RING; rows of a multiple of 16 bytes up to
+    64 KB, tiles of 16 .. 1 rows, ragged last tile, more tiles than SMs; n = 130 and n = 20000 fall back)."""
+    rng = np.random.default_rng(m * 7 + n)
+    w = rng.integers(0, P, m * n, dtype=np.int64).astype(np.uint32)
+    x = rng.integers(0, P, n, dtype=np.int64).astype(np.uint32)
+    exp = O.matmul_forward(w, x, m, n)
+    for ring in (0, 1):
+        ctx.set_option(ctx.OPT_MATVEC_RING, ring)
+        try:
+            assert zp.matmul_forward(ctx, w, x, m, n).tolist() == exp.tolist()
+        finally:
+            ctx.set_option(ctx.OPT_MATVEC_RING, 0)

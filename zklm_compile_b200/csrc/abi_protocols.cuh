@@ -25,6 +25,7 @@ int32_t status_to_code(zkb_ctx* c, uint32_t st) {
         case ST_ALPHA_COLLISION: c->err = "alpha collision with lookup encoding"; return ZKB_E_ALPHA_COLLISION;
         case ST_NOT_QR: c->err = "rmsnorm_forward: could not find QR perturbation in 200 attempts"; return ZKB_E_NOT_QR;
         case ST_LOOKUP_KEY: c->err = "lookup_fast: key not found"; return ZKB_E_ARG;
+        case ST_COPY_TIMEOUT: c->err = "forward matvec: a bulk copy into shared memory did not complete within its wait limit"; return ZKB_E_CUDA;
     }
     c->err = "device status " + std::to_string(st);
     return ZKB_E_CUDA;
@@ -103,14 +104,17 @@ int32_t zkb_matvec_forward(zkb_ctx* c, const uint32_t* W, const uint32_t* x, siz
     ZKB_TRY(c, {
         c->use();
         if (w_on_device && n % 4 == 0) need_align16(W, "W");
+        clear_status(c);
         const u32* dW = w_on_device ? W : up_pad(c, W, m * n, m * n);
         u32* dx = up_pad(c, x, n, n + 4);
         u32* dy = (u32*)c->scratch(m * 4);
         matvec_forward(c, dW, dx, (u32)m, (u32)n, dy, (u32)m);
         ZKB_CUDA(cudaGetLastError());
         ZKB_CUDA(cudaMemcpyAsync(y, dy, m * 4, cudaMemcpyDeviceToHost, c->stream));
-        ZKB_CUDA(cudaStreamSynchronize(c->stream));
+        uint32_t st = c->read_status();
         c->scratch_reset();
+        int32_t rc = status_to_code(c, st);
+        if (rc) return rc;
     });
 }
 

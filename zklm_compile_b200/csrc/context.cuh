@@ -25,6 +25,16 @@ struct ArgFail { int32_t code; std::string msg; };
 // Launch with programmatic stream serialisation: the kernel may begin before the previous kernel of
 // the stream has finished (see pdl_wait in m31.cuh).
 template <class... KArgs, class... Args>
+inline void launch_pdl_smem(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    ZKB_CUDA(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...));
+}
+template <class... KArgs, class... Args>
 inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t stream, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = 0; cfg.stream = stream;
@@ -132,6 +142,8 @@ struct zkb_ctx {
     // Tuning options (zkb_ctx_set_option): 0 = the built-in choice.
     int opt_single_threads = 0, opt_pipe_threads = 0, opt_fold2_vec = 0;
     bool opt_plain_tail = false, opt_no_fused2 = false, opt_bf_in_order = false;
+    bool opt_mv_ring = false;            // forward matvec: the bulk-copy ring kernel instead of the register-staged one
+    int opt_mv_prefetch = 8;             // rows per CTA whose lines a forward matvec prefetches into L2 before it waits for its input
     // Second stream for work that does not depend on the transcript (the fold / tree chain of a Basefold
     // opening), joined to `stream` through events; created on first use.
     cudaStream_t side = nullptr;

@@ -237,7 +237,7 @@ __device__ __forceinline__ u64 matvec_row_part(const u32* __restrict__ row, cons
 }
 
 template <int WPR>
-__global__ void __launch_bounds__(256) matvec_forward_kernel(MatvecBatch mb, const u32* __restrict__ x, size_t n) {
+__global__ void __launch_bounds__(256) matvec_forward_kernel(MatvecBatch mb, const u32* __restrict__ x, size_t n, int pf_rows) {
     __shared__ u32 part[8];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int sub = warp % WPR;                         // which part of the row
@@ -250,7 +250,8 @@ __global__ void __launch_bounds__(256) matvec_forward_kernel(MatvecBatch mb, con
     {
         const size_t i0 = (size_t)blockIdx.x * RPC;
         const size_t lines_per_row = (n * 4 + 127) / 128;
-        for (size_t q = threadIdx.x; q < (size_t)RPC * lines_per_row; q += blockDim.x) {
+        const size_t pf = (size_t)(pf_rows < RPC ? pf_rows : RPC);
+        for (size_t q = threadIdx.x; q < pf * lines_per_row; q += blockDim.x) {
             const size_t i = i0 + q / lines_per_row;
             if (i < m) {
                 u32 t = 0;
@@ -284,6 +285,168 @@ __global__ void __launch_bounds__(256) matvec_forward_kernel(MatvecBatch mb, con
             }
             __syncthreads();
         }
+    }
+}
+
+// ---- forward matvec through a shared-memory ring filled by bulk asynchronous copies ---------------------
+// One persistent CTA per SM: warp MVB_CONSUMER_WARPS issues one bulk copy (cp.async.bulk, global ->
+// this CTA's shared memory, completion counted on an mbarrier) per tile of R whole rows into a ring of
+// S stages; the other warps multiply tiles out of shared memory against x, which also sits there.
+// The bytes in flight per SM are the ring (up to ~160 KB), not what fits the registers of the
+// resident warps, which is what bounds the register-staged kernel above.  Rows of one tile are
+// split over MVB_CONSUMER_WARPS / R warps; the last of them to finish adds the partial sums (an
+// arrival counter per row in shared memory, no CTA-wide barrier).  The copies of the first tiles are
+// issued before the wait on the previous kernel (the weights do not depend on it, only x does).
+// Every wait on an mbarrier is bounded; when one runs out the kernel records ST_COPY_TIMEOUT and the
+// issuing thread still waits (bounded again) for its copies in flight before it returns.
+constexpr int MVB_CONSUMER_WARPS = 16;
+constexpr int MVB_THREADS = (MVB_CONSUMER_WARPS + 1) * 32;
+constexpr unsigned long long MVB_WAIT_LIMIT_NS = 2000000000ull;
+constexpr u32 ST_COPY_TIMEOUT = 10;
+
+__device__ __forceinline__ u32 smem_addr(const void* p) { return (u32)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned long long* b, u32 count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(b)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(unsigned long long* b, u32 bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(b)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* b) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(b)) : "memory");
+}
+// Bounded by wall time (two seconds on the global timer, looked at every 256 tries), not by a try count:
+// how long one try_wait may suspend the thread is up to the hardware.
+__device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* b, u32 parity) {
+    unsigned long long t0 = 0;
+    for (u32 it = 0;; it++) {
+        u32 ok;
+        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(smem_addr(b)), "r"(parity) : "memory");
+        if (ok) return true;
+        if ((it & 255) == 255) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > MVB_WAIT_LIMIT_NS) return false;
+        }
+    }
+}
+// global -> shared memory of this CTA, `bytes` a multiple of 16, both addresses 16-byte aligned
+__device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, u32 bytes, unsigned long long* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_addr(dst)), "l"(src), "r"(bytes), "r"(smem_addr(bar)) : "memory");
+}
+
+struct MvbShape { u32 n, R, S, n_al; };     // columns, rows per tile, stages, x length rounded up to 32 words
+__host__ __device__ inline size_t mvb_smem_bytes(const MvbShape& sh) {
+    return (size_t)sh.n_al * 4 + (size_t)sh.S * sh.R * sh.n * 4 + (size_t)sh.S * 16 + (size_t)sh.S * (MVB_CONSUMER_WARPS + 8) * 4 + 64;
+}
+// tile g of the batch: matrix t, first row r0, rows in it
+__device__ __forceinline__ void mvb_locate(const MatvecBatch& mb, u32 R, u32 g, u32& t, u32& r0, u32& rows) {
+    t = 0;
+    for (;;) {
+        const u32 m_t = mb.first[t + 1] - mb.first[t];
+        const u32 tiles_t = (m_t + R - 1) / R;
+        if (g < tiles_t || t + 1 >= mb.count) { r0 = g * R; rows = m_t - r0 < R ? m_t - r0 : R; return; }
+        g -= tiles_t;
+        t++;
+    }
+}
+__global__ void __launch_bounds__(MVB_THREADS, 1) matvec_forward_bulk_kernel(MatvecBatch mb, const u32* __restrict__ x, MvbShape sh, u32 n_tiles, u32* status) {
+    extern __shared__ __align__(128) unsigned char mvb_smem[];
+    u32* xs = reinterpret_cast<u32*>(mvb_smem);
+    u32* ring = xs + sh.n_al;
+    const u32 stage_words = sh.R * sh.n;
+    unsigned long long* full = reinterpret_cast<unsigned long long*>(ring + (size_t)sh.S * stage_words);
+    unsigned long long* empty = full + sh.S;
+    u32* part = reinterpret_cast<u32*>(empty + sh.S);            // [S][MVB_CONSUMER_WARPS]
+    u32* cnt = part + sh.S * MVB_CONSUMER_WARPS;                 // [S][8]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (u32 s = 0; s < sh.S; s++) { mbar_init(full + s, 1); mbar_init(empty + s, MVB_CONSUMER_WARPS); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    for (u32 i = threadIdx.x; i < sh.S * 8; i += blockDim.x) cnt[i] = 0;
+    __syncthreads();
+    pdl_launch_dependents();
+    if (warp == MVB_CONSUMER_WARPS) {
+        if (lane == 0) {
+            u32 k = 0;
+            bool ok = true;
+            for (u32 g = blockIdx.x; g < n_tiles; g += gridDim.x, k++) {
+                const u32 s = k % sh.S, ph = (k / sh.S) & 1;
+                if (!mbar_wait_bounded(empty + s, ph ^ 1)) { atomicExch(status, ST_COPY_TIMEOUT); ok = false; break; }
+                u32 t, r0, rows;
+                mvb_locate(mb, sh.R, g, t, r0, rows);
+                const u32 bytes = rows * sh.n * 4;
+                mbar_arrive_expect_tx(full + s, bytes);
+                bulk_copy_g2s(ring + (size_t)s * stage_words, mb.W[t] + (size_t)r0 * sh.n, bytes, full + s);
+            }
+            // no copy of this thread may still be in flight when it leaves: wait for the last use of every stage
+            for (u32 j = 0; j < sh.S && j < k; j++) {
+                const u32 kk = k - 1 - j, s = kk % sh.S, ph = (kk / sh.S) & 1;
+                if (!mbar_wait_bounded(full + s, ph) && ok) { atomicExch(status, ST_COPY_TIMEOUT); ok = false; }
+            }
+        }
+        return;
+    }
+    pdl_wait();                                   // x comes from the kernel before this one
+    {
+        const uint4* xg = reinterpret_cast<const uint4*>(x);
+        uint4* xv = reinterpret_cast<uint4*>(xs);
+        for (u32 i = threadIdx.x; i < sh.n / 4; i += MVB_CONSUMER_WARPS * 32) xv[i] = __ldg(xg + i);
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(MVB_CONSUMER_WARPS * 32) : "memory");
+    const u32 wpr = MVB_CONSUMER_WARPS / sh.R;    // warps per row
+    const u32 row_in_tile = warp / wpr, sub = warp % wpr;
+    const u32 groups = sh.n / 4, per = (groups + wpr - 1) / wpr;
+    const u32 g0 = sub * per, g1 = g0 + per < groups ? g0 + per : groups;
+    u32 k = 0;
+    for (u32 g = blockIdx.x; g < n_tiles; g += gridDim.x, k++) {
+        const u32 s = k % sh.S, ph = (k / sh.S) & 1;
+        if (!mbar_wait_bounded(full + s, ph)) { if (lane == 0) atomicExch(status, ST_COPY_TIMEOUT); break; }
+        u32 t, r0, rows;
+        mvb_locate(mb, sh.R, g, t, r0, rows);
+        if (row_in_tile < rows) {
+            const uint4* rw = reinterpret_cast<const uint4*>(ring + (size_t)s * stage_words + (size_t)row_in_tile * sh.n);
+            const uint4* xv = reinterpret_cast<const uint4*>(xs);
+            u64 acc = 0;
+            u32 gi = g0 + lane;
+            for (; gi + 96 < g1; gi += 128) {
+                const uint4 w0 = rw[gi], w1 = rw[gi + 32], w2 = rw[gi + 64], w3 = rw[gi + 96];
+                const uint4 v0 = xv[gi], v1 = xv[gi + 32], v2 = xv[gi + 64], v3 = xv[gi + 96];
+                acc += part_reduce((u64)w0.x * v0.x + (u64)w0.y * v0.y) + part_reduce((u64)w0.z * v0.z + (u64)w0.w * v0.w);
+                acc += part_reduce((u64)w1.x * v1.x + (u64)w1.y * v1.y) + part_reduce((u64)w1.z * v1.z + (u64)w1.w * v1.w);
+                acc += part_reduce((u64)w2.x * v2.x + (u64)w2.y * v2.y) + part_reduce((u64)w2.z * v2.z + (u64)w2.w * v2.w);
+                acc += part_reduce((u64)w3.x * v3.x + (u64)w3.y * v3.y) + part_reduce((u64)w3.z * v3.z + (u64)w3.w * v3.w);
+                acc = part_reduce(acc);
+            }
+            for (; gi < g1; gi += 32) {
+                const uint4 w0 = rw[gi], v0 = xv[gi];
+                acc = part_reduce(acc + part_reduce((u64)w0.x * v0.x + (u64)w0.y * v0.y) + part_reduce((u64)w0.z * v0.z + (u64)w0.w * v0.w));
+            }
+            u32 r = red64(acc);
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) r = add31(r, __shfl_down_sync(0xffffffffu, r, off));
+            if (lane == 0) {
+                if (wpr == 1) {
+                    mb.y[t][r0 + row_in_tile] = r;
+                } else {
+                    volatile u32* pv = part + s * MVB_CONSUMER_WARPS;
+                    pv[warp] = r;
+                    __threadfence_block();
+                    if (atomicAdd(cnt + s * 8 + row_in_tile, 1u) == wpr - 1) {
+                        __threadfence_block();
+                        u32 v = 0;
+                        for (u32 q = 0; q < wpr; q++) v = add31(v, pv[row_in_tile * wpr + q]);
+                        mb.y[t][r0 + row_in_tile] = v;
+                        cnt[s * 8 + row_in_tile] = 0;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty + s);    // this warp has read everything it needs from the stage
     }
 }
 

@@ -71,7 +71,37 @@ namespace zkb {
 inline size_t pad_pow2(size_t n) { return size_t(1) << log2_ceil_u(n); }
 
 // Warps per row: enough to give every SM about 32 warps even for short matrices.
+// The bulk-copy ring kernel, when asked for (ZKB_OPT_MATVEC_RING) and the shape allows it: whole rows of a multiple of 16 bytes, at most 64 KB each,
+// 16-byte aligned matrices and input.  Returns false when the register-staged kernel has to run.
+inline bool launch_matvec_forward_bulk(zkb_ctx* c, const MatvecBatch& mb, const u32* x, size_t n) {
+    if (!c->opt_mv_ring || n % 4 || n * 4 > 65536 || n < 128 || ((uintptr_t)x & 15)) return false;
+    for (u32 t = 0; t < mb.count; t++) if ((uintptr_t)mb.W[t] & 15) return false;
+    MvbShape sh{};
+    sh.n = (u32)n;
+    sh.n_al = (u32)((n + 31) & ~size_t(31));
+    sh.R = 16;
+    while (sh.R > 1 && (size_t)sh.R * n * 4 > 40960) sh.R /= 2;
+    const size_t stage = (size_t)sh.R * n * 4, budget = 200 * 1024;
+    if ((size_t)sh.n_al * 4 + 2 * stage + 1024 > budget) return false;
+    sh.S = (u32)((budget - (size_t)sh.n_al * 4 - 1024) / stage);
+    if (sh.S > 4) sh.S = 4;
+    u32 n_tiles = 0;
+    for (u32 t = 0; t < mb.count; t++) n_tiles += (mb.first[t + 1] - mb.first[t] + sh.R - 1) / sh.R;
+    static std::mutex mu;
+    static std::map<int, bool> ready;
+    {
+        std::lock_guard<std::mutex> g(mu);
+        if (!ready[c->device]) {
+            ZKB_CUDA(cudaFuncSetAttribute(matvec_forward_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+            ready[c->device] = true;
+        }
+    }
+    const u32 grid = n_tiles < (u32)c->sm_count ? n_tiles : (u32)c->sm_count;
+    launch_pdl_smem(matvec_forward_bulk_kernel, dim3(grid), dim3(MVB_THREADS), mvb_smem_bytes(sh), c->stream, mb, x, sh, n_tiles, c->status);
+    return true;
+}
 inline void launch_matvec_forward(zkb_ctx* c, const MatvecBatch& mb, const u32* x, size_t n) {
+    if (launch_matvec_forward_bulk(c, mb, x, n)) return;
     const size_t m = mb.first[mb.count];
     const size_t want_warps = (size_t)c->sm_count * 32;
     int wpr = 1;
@@ -82,10 +112,10 @@ inline void launch_matvec_forward(zkb_ctx* c, const MatvecBatch& mb, const u32* 
     int grid = (int)(ctas < cap ? ctas : cap);
     if (grid < 1) grid = 1;
     switch (wpr) {
-        case 1: launch_pdl(matvec_forward_kernel<1>, dim3(grid), dim3(256), c->stream, mb, x, n); break;
-        case 2: launch_pdl(matvec_forward_kernel<2>, dim3(grid), dim3(256), c->stream, mb, x, n); break;
-        case 4: launch_pdl(matvec_forward_kernel<4>, dim3(grid), dim3(256), c->stream, mb, x, n); break;
-        default: launch_pdl(matvec_forward_kernel<8>, dim3(grid), dim3(256), c->stream, mb, x, n); break;
+        case 1: launch_pdl(matvec_forward_kernel<1>, dim3(grid), dim3(256), c->stream, mb, x, n, c->opt_mv_prefetch); break;
+        case 2: launch_pdl(matvec_forward_kernel<2>, dim3(grid), dim3(256), c->stream, mb, x, n, c->opt_mv_prefetch); break;
+        case 4: launch_pdl(matvec_forward_kernel<4>, dim3(grid), dim3(256), c->stream, mb, x, n, c->opt_mv_prefetch); break;
+        default: launch_pdl(matvec_forward_kernel<8>, dim3(grid), dim3(256), c->stream, mb, x, n, c->opt_mv_prefetch); break;
     }
 }
 // y = W x for one matrix; the tail y[m..m_pad) is zeroed unless the caller keeps it zero itself.

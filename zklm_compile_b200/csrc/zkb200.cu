@@ -361,6 +361,11 @@ int32_t zkb_ctx_set_option(zkb_ctx* c, int32_t option, int32_t value) {
             c->opt_pipe_threads = value; break;
         case ZKB_OPT_NO_FUSED_FOLD: c->opt_no_fused2 = value != 0; break;
         case ZKB_OPT_BASEFOLD_IN_ORDER: c->opt_bf_in_order = value != 0; break;
+        case ZKB_OPT_MATVEC_RING: c->opt_mv_ring = value != 0; break;
+        case ZKB_OPT_MATVEC_PREFETCH_ROWS:
+            if (value < 0 || value > 8) return ZKB_E_ARG;
+            c->opt_mv_prefetch = (int)value;
+            break;
         case ZKB_OPT_FOLD2_VEC:
             if (value != 0 && value != 1 && value != 2 && value != 4) { c->err = "fold2 vector width must be 0, 1, 2 or 4"; return ZKB_E_ARG; }
             c->opt_fold2_vec = value; break;
