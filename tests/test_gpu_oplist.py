@@ -158,4 +158,11 @@ def test_op_list_argument_errors(env):
         g.add_saved("add_x", "never_saved")
     with pytest.raises(zk.ZkbError):
         g.attention_seq1("attn")                               # 16 is not a multiple of 3
+    # a failed add leaves the list as it was: it still takes ops of the old activation length and proves
+    x = _w(rng, 16)
+    w = _w(rng, 4 * 16)
+    g.linear("fc", w, None, 4, 16)
+    o = O.OpList()
+    o.linear("fc", w, None, 4, 16)
+    assert g.prove(x) == o.prove(x)
     g.close()

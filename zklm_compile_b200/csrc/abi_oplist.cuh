@@ -27,6 +27,12 @@ OL::Op& ol_push(OL* L, OL::Kind kind, const char* name, zkb::u32 out_len, bool o
     L->cur_len = out_len;
     return L->ops.back();
 }
+// An add_* call that fails half way (an allocation, a length check) leaves the list as it was.
+struct OlTxn {
+    OL* L; size_t n_ops; zkb::u32 len; bool done = false;
+    explicit OlTxn(OL* l) : L(l), n_ops(l->ops.size()), len(l->cur_len) {}
+    ~OlTxn() { if (!done) { L->ops.erase(L->ops.begin() + (std::ptrdiff_t)n_ops, L->ops.end()); L->cur_len = len; } }
+};
 const zkb::u32* ol_input_of(const OL* L, size_t idx) { return idx == 0 ? L->x : L->ops[idx - 1].out; }
 
 // The forward pass (pipeline/forward.rs:24-520) over the resident ops; the input is already in L->x.
@@ -292,6 +298,7 @@ int32_t zkb_oplist_add_linear(zkb_oplist* L, const char* name, const uint32_t* W
     ZKB_TRY(c, {
         c->use();
         if (n != L->cur_len) throw ArgFail{ZKB_E_LENGTH, "linear: column count differs from the activation length"};
+        OlTxn txn(L);
         OL::Op& op = ol_push(L, OL::LINEAR, name, (u32)m, true);
         op.m = (u32)m; op.n = (u32)n;
         op.w = ol_upload(L, W, m * n, m * n);
@@ -302,6 +309,7 @@ int32_t zkb_oplist_add_linear(zkb_oplist* L, const char* name, const uint32_t* W
         ZKB_CUDA(cudaMemcpyAsync(op.root, root, 32, cudaMemcpyDeviceToHost, c->stream));
         ZKB_CUDA(cudaStreamSynchronize(c->stream));
         c->scratch_reset();
+        txn.done = true;
     });
 }
 int32_t zkb_oplist_add_simple(zkb_oplist* L, int32_t kind, const char* name, const char* aux) {
@@ -310,6 +318,7 @@ int32_t zkb_oplist_add_simple(zkb_oplist* L, int32_t kind, const char* name, con
     ZKB_TRY(c, {
         c->use();
         const u32 n = L->cur_len;
+        OlTxn txn(L);
         switch (kind) {
             case ZKB_OP_RELU: ol_push(L, OL::RELU, name, n, true); break;
             case ZKB_OP_ATTENTION_SEQ1:
@@ -331,6 +340,7 @@ int32_t zkb_oplist_add_simple(zkb_oplist* L, int32_t kind, const char* name, con
             case ZKB_OP_SET_INPUT_REQUANT: ol_push(L, OL::SET_INPUT_REQUANT, name, n, true); break;
             default: throw ArgFail{ZKB_E_ARG, "unknown op kind"};
         }
+        txn.done = true;
     });
 }
 int32_t zkb_oplist_add_layernorm(zkb_oplist* L, const char* name, const uint32_t* gamma, const uint32_t* beta, size_t d) {
@@ -339,12 +349,14 @@ int32_t zkb_oplist_add_layernorm(zkb_oplist* L, const char* name, const uint32_t
     ZKB_TRY(c, {
         c->use();
         if (d != L->cur_len) throw ArgFail{ZKB_E_LENGTH, "layernorm: width differs from the activation length"};
+        OlTxn txn(L);
         OL::Op& op = ol_push(L, OL::LAYERNORM, name, (u32)d, true);
         op.gamma = ol_upload(L, gamma, d, d);
         op.beta = ol_upload(L, beta, d, d);
         op.aux0 = ol_alloc(L, pad_pow2(d));
         op.aux1 = ol_alloc(L, pad_pow2(d));
         op.scalars = ol_alloc(L, 8);
+        txn.done = true;
     });
 }
 int32_t zkb_oplist_add_gelu(zkb_oplist* L, const char* name, const uint32_t* table_out_dev, uint32_t n_table) {
@@ -352,9 +364,11 @@ int32_t zkb_oplist_add_gelu(zkb_oplist* L, const char* name, const uint32_t* tab
     zkb_ctx* c = L->ctx;
     ZKB_TRY(c, {
         c->use();
+        OlTxn txn(L);
         OL::Op& op = ol_push(L, OL::GELU, name, L->cur_len, true);
         op.table = table_out_dev; op.n_table = n_table;
         op.aux0 = ol_alloc(L, pad_pow2(op.out_len));
+        txn.done = true;
     });
 }
 int32_t zkb_oplist_add_set_input(zkb_oplist* L, const char* name, const uint32_t* values, size_t n) {
@@ -362,8 +376,10 @@ int32_t zkb_oplist_add_set_input(zkb_oplist* L, const char* name, const uint32_t
     zkb_ctx* c = L->ctx;
     ZKB_TRY(c, {
         c->use();
+        OlTxn txn(L);
         OL::Op& op = ol_push(L, OL::SET_INPUT, name, (u32)n, false);
         op.out = ol_upload(L, values, n, pad_pow2(n));
+        txn.done = true;
     });
 }
 uint32_t zkb_oplist_output_len(const zkb_oplist* L) { return L ? L->cur_len : 0; }
