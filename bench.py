@@ -506,6 +506,16 @@ def run_basefold(zk, ctx, n, reps=3):
             tr = zk.Transcript(ctx, b"bench-basefold")
             ctx.timer_start(); blob = zp.basefold_commit_and_prove(ctx, tr, coeffs, point, kind); t_all.append(ctx.timer_stop_ms())
         mk_bytes = 2 * N * 4 + (2 * N - 1) * 16
+        # the verifier (basefold.rs:611-748) on the same bytes: host proof bytes in, decision out
+        host_point = point.download()
+        claimed = int.from_bytes(blob[-12:-8], "little")
+        t_ver = []
+        for _ in range(reps):
+            tv = zk.Transcript(ctx, b"bench-basefold")
+            tv.absorb_bytes(blob[:16])
+            t0 = time.perf_counter()
+            assert zp.basefold_verify_opening(ctx, tv, blob, host_point, claimed, kind)
+            t_ver.append((time.perf_counter() - t0) * 1e3)
         ctx.set_option(ctx.OPT_BASEFOLD_IN_ORDER, 1)
         t_ord = []
         for _ in range(reps):
@@ -519,6 +529,7 @@ def run_basefold(zk, ctx, n, reps=3):
                                                       "frac": round(mk_bytes / min(t_mk) / 1e6 / peak, 4), "traffic": None,
                                                       "algorithmic_bytes": mk_bytes},
                                   "commit_and_prove_ms": round(min(t_all), 3), "commit_and_prove_in_order_ms": round(min(t_ord), 3),
+                                  "verify_opening_ms_wall": round(min(t_ver), 3),
                                   "proof_bytes": len(blob), "proof_sha256": hashlib.sha256(blob).hexdigest()}
     for b in (coeffs, point, cw):
         b.free()

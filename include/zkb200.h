@@ -369,6 +369,15 @@ int32_t zkb_basefold_encode(zkb_ctx* ctx, const uint32_t* coeffs, size_t n, int3
  * bincode(BasefoldOpeningProof).  The transcript advances exactly as in the reference. */
 int32_t zkb_basefold_commit_and_prove(zkb_ctx* ctx, zkb_transcript* tr, const uint32_t* coeffs, size_t n, const uint32_t* point,
                                       uint32_t n_point, int32_t on_device, int32_t node_hash, uint8_t* out, size_t cap, size_t* len);
+/* verify_opening (basefold.rs:611-748, with verify_batch_opening, pcs.rs:345-438): checks the opening
+ * proof in `bytes` (bincode(BasefoldCommitment) followed by bincode(BasefoldOpeningProof), exactly what
+ * zkb_basefold_commit_and_prove returns) against `claimed` = the polynomial's value at `point` (host,
+ * n_point coordinates).  As with the reference function, the caller absorbs the commitment root into
+ * the transcript first; the transcript then advances as the prover's did.  *accepted = 1 / 0.
+ * Bytes that do not decode give ZKB_E_ARG, a batch proof with more than 256 opened positions
+ * ZKB_E_TOO_LARGE (an honest one has 48 and 24). */
+int32_t zkb_basefold_verify_opening(zkb_ctx* ctx, zkb_transcript* tr, const uint8_t* bytes, size_t len, const uint32_t* point,
+                                    uint32_t n_point, uint32_t claimed, int32_t node_hash, int32_t* accepted);
 
 /* ---- op-list mode (MLP / GPT-2 shaped models; base-field challenges) ----------------------------
  * The reference proves such models as a list of ops on one transcript "structured-ml-proof", in

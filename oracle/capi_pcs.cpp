@@ -91,6 +91,43 @@ int zko_basefold_roundtrip(const uint32_t* c, size_t n, const uint32_t* point, s
     return basefold_verify_opening(r.first, claimed, pnt, r.second, vt, kind) ? 1 : 0;
 }
 
+// Decode bincode(BasefoldCommitment) || bincode(BasefoldOpeningProof) and run verify_opening on it.
+// The caller has absorbed the commitment root.  1 accept, 0 reject, -1 the bytes do not decode.
+int zko_basefold_verify_bytes(void* t, const uint8_t* b, size_t n, const uint32_t* point, size_t n_point, uint32_t claimed, int kind) {
+    size_t at = 0;
+    bool ok = true;
+    auto u64v = [&]() -> uint64_t { if (at + 8 > n) { ok = false; return 0; } uint64_t v = 0; for (int i = 0; i < 8; i++) v |= uint64_t(b[at + i]) << (8 * i); at += 8; return v; };
+    auto u32v = [&]() -> uint32_t { if (at + 4 > n) { ok = false; return 0; } uint32_t v = 0; for (int i = 0; i < 4; i++) v |= uint32_t(b[at + i]) << (8 * i); at += 4; return v; };
+    auto dig = [&]() -> Digest { Digest d{}; if (at + 16 > n) { ok = false; return d; } memcpy(d.data(), b + at, 16); at += 16; return d; };
+    auto batch = [&]() -> BatchMerkleProof {
+        BatchMerkleProof p;
+        uint64_t ni = u64v(); if (!ok || ni > (1u << 20)) { ok = false; return p; }
+        for (uint64_t i = 0; i < ni; i++) p.indices.push_back(u32v());
+        uint64_t nv = u64v(); if (!ok || nv > (1u << 20)) { ok = false; return p; }
+        for (uint64_t i = 0; i < nv; i++) p.values.push_back(u32v());
+        uint64_t nl = u64v(); if (!ok || nl > 64) { ok = false; return p; }
+        for (uint64_t l = 0; l < nl && ok; l++) {
+            uint64_t cnt = u64v(); if (!ok || cnt > (1u << 20)) { ok = false; return p; }
+            std::vector<Digest> lv;
+            for (uint64_t i = 0; i < cnt; i++) lv.push_back(dig());
+            p.auth_nodes.push_back(std::move(lv));
+        }
+        return p;
+    };
+    BasefoldCommitment c;
+    c.root = dig(); c.num_coeffs = u64v(); c.log_n = u64v();
+    BasefoldOpeningProof pr;
+    uint64_t nr = u64v(); if (!ok || nr > 64) return -1;
+    for (uint64_t i = 0; i < nr; i++) pr.fold_roots.push_back(dig());
+    uint64_t nq = u64v(); if (!ok || nq > 64) return -1;
+    for (uint64_t i = 0; i < nq && ok; i++) { FoldLevelQueries q; q.prev_batch_proof = batch(); q.folded_batch_proof = batch(); pr.fold_queries.push_back(std::move(q)); }
+    pr.final_value = u32v();
+    uint64_t nf = u64v();
+    for (uint64_t i = 0; i < nf && ok; i++) pr.final_coeffs.push_back(u32v());
+    if (!ok || at != n || c.log_n < 1 || c.log_n > 28) return -1;
+    return basefold_verify_opening(c, F(claimed), vf(point, n_point), pr, T(t), kind) ? 1 : 0;
+}
+
 // Process-wide stand-ins for the reference's cargo features and target architecture.
 void zko_set_features(int bind_mode, int node_kind) { features().bind_mode = bind_mode; features().node_kind = node_kind; }
 

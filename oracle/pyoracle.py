@@ -546,6 +546,13 @@ def basefold_commit_and_prove(tr, coeffs, point, kind: int) -> bytes:
                        cap=1 << 22)
 
 
+def basefold_verify_bytes(tr, blob: bytes, point, claimed: int, kind: int) -> int:
+    """verify_opening on bincode(BasefoldCommitment) || bincode(BasefoldOpeningProof); the caller has absorbed the
+    commitment root.  1 accept, 0 reject, -1 undecodable."""
+    Pt, pp = _u32(point)
+    return int(lib().zko_basefold_verify_bytes(tr.h, _u8(blob), C.c_size_t(len(blob)), pp, C.c_size_t(Pt.size), C.c_uint32(int(claimed)), C.c_int(kind)))
+
+
 def basefold_roundtrip(coeffs, point, kind: int, tamper=0) -> int:
     Cf, pc = _u32(coeffs); Pt, pp = _u32(point)
     return int(lib().zko_basefold_roundtrip(pc, C.c_size_t(Cf.size), pp, C.c_size_t(Pt.size), C.c_int(kind), C.c_int(tamper)))

@@ -86,6 +86,83 @@ def test_basefold_in_order_and_run_ahead_schedules_agree(ctx, kind):
             ctx.set_option(ctx.OPT_BASEFOLD_IN_ORDER, 0)
 
 
+def _verify_both(ctx, blob, point, claimed, kind, label=b"bf-verify"):
+    """(GPU decision, oracle decision); undecodable bytes are -1 on both sides."""
+    to = O.Transcript(label)
+    to.absorb_bytes(blob[:16])
+    exp = O.basefold_verify_bytes(to, blob, point, claimed, kind)
+    tg = zk.Transcript(ctx, label)
+    tg.absorb_bytes(blob[:16])
+    try:
+        got = int(zp.basefold_verify_opening(ctx, tg, blob, point, claimed, kind))
+    except zk.ZkbError as e:
+        assert e.code == 2
+        got = -1
+    return got, exp, tg, to
+
+
+@pytest.mark.parametrize("kind", KINDS)
+@pytest.mark.parametrize("n", [2, 5, 300, 1 << 14, (1 << 17) - 3])
+def test_basefold_verifier_accepts_what_the_prover_emits(ctx, kind, n):
+    """verify_opening on the GPU (basefold.rs:611-748) accepts the prover's proofs, leaves the transcript
+    where the prover's is, and agrees with the oracle's verifier; wrong claims and points are rejected."""
+    c = rnd(500 + n, n)
+    log_n = 1 if n <= 1 else (n - 1).bit_length()
+    pt = rnd(600 + n, log_n)
+    tp = zk.Transcript(ctx, b"bf-verify")
+    blob = zp.basefold_commit_and_prove(ctx, tp, c, pt, kind)
+    padded = np.zeros(1 << log_n, np.uint32)
+    padded[:n] = c
+    claimed = O.mle_evaluate(padded, pt)
+    assert int.from_bytes(blob[-12:-8], "little") == claimed
+    got, exp, tg, to = _verify_both(ctx, blob, pt, claimed, kind)
+    assert (got, exp) == (1, 1)
+    assert tg.squeeze() == tp.squeeze() == to.squeeze()
+    assert _verify_both(ctx, blob, pt, (claimed + 1) % P, kind)[:2] == (0, 0)
+    # another point: rejected through the fold relation, except for coordinate 0, which the relation cannot see
+    # (round 0 folds the two identical halves of [c || c], so l - r = 0 there) - the oracle says the same
+    pt2 = pt.copy()
+    pt2[log_n // 2] = (int(pt2[log_n // 2]) + 1) % P
+    got, exp = _verify_both(ctx, blob, pt2, claimed, kind)[:2]
+    assert got == exp == (0 if log_n // 2 >= 1 else 1)
+    # a proof made with the other node hash does not verify
+    assert _verify_both(ctx, blob, pt, claimed, 1 - kind)[:2] == (0, 0)
+
+
+@pytest.mark.parametrize("kind", KINDS)
+def test_basefold_verifier_rejects_tampered_proofs_like_the_oracle(ctx, kind):
+    """Every single-byte change of a proof is judged as the oracle's restatement of the reference
+    verifier judges it: changed roots, opened values, sibling digests, indices, lengths, final value."""
+    n, log_n = 3000, 12
+    c, pt = rnd(71, n), rnd(72, log_n)
+    blob = zp.basefold_commit_and_prove(ctx, zk.Transcript(ctx, b"bf-verify"), c, pt, kind)
+    claimed = int.from_bytes(blob[-12:-8], "little")
+    assert _verify_both(ctx, blob, pt, claimed, kind)[:2] == (1, 1)
+    rng = np.random.default_rng(5)
+    spots = [0, 15, 16, 24, 32, 40, 41, 60, len(blob) - 1, len(blob) - 9, len(blob) - 12]
+    spots += [int(v) for v in rng.integers(0, len(blob), 120)]
+    seen = set()
+    for pos in spots:
+        bad = bytearray(blob)
+        bad[pos] ^= 1 << int(rng.integers(0, 8))
+        bad = bytes(bad)
+        got, exp, _, _ = _verify_both(ctx, bad, pt, claimed, kind)
+        assert got == exp, f"byte {pos}: GPU {got}, oracle {exp}"
+        seen.add(exp)
+    assert 0 in seen and -1 in seen            # both rejected and undecodable cases were met
+    # dropping the last fold round: rejected, not an error
+    assert _verify_both(ctx, blob[:-1], pt, claimed, kind)[:2] == (-1, -1)
+
+
+def test_basefold_verifier_short_point(ctx):
+    c, pt = rnd(5, 700), rnd(6, 4)
+    tp = zk.Transcript(ctx, b"bf-verify")
+    blob = zp.basefold_commit_and_prove(ctx, tp, c, pt)
+    claimed = int.from_bytes(blob[-12:-8], "little")
+    got, exp, tg, to = _verify_both(ctx, blob, pt, claimed, O.NODE_BLAKE3)
+    assert (got, exp) == (1, 1) and tg.squeeze() == tp.squeeze()
+
+
 def test_basefold_short_point_squeezes_challenges(ctx):
     c = rnd(5, 700)
     pt = rnd(6, 4)

@@ -132,4 +132,27 @@ int32_t zkb_basefold_commit_and_prove(zkb_ctx* c, zkb_transcript* tr, const uint
     });
 }
 
+// verify_opening (basefold.rs:611-748).  The caller has absorbed the commitment root, as the reference's callers do.
+int32_t zkb_basefold_verify_opening(zkb_ctx* c, zkb_transcript* tr, const uint8_t* bytes, size_t len, const uint32_t* point, uint32_t n_point,
+                                    uint32_t claimed, int32_t node_hash, int32_t* accepted) {
+    if (!c || !tr || !bytes || (!point && n_point) || !accepted) return ZKB_E_ARG;
+    *accepted = 0;
+    ZKB_TRY(c, {
+        c->use();
+        BvParsed pr;
+        if (!bv_parse(bytes, len, pr)) throw ArgFail{ZKB_E_ARG, "basefold: the bytes do not decode as a commitment followed by an opening proof"};
+        if (pr.too_large) throw ArgFail{ZKB_E_TOO_LARGE, "basefold: more than 256 opened positions in one batch proof"};
+        if (pr.trees.empty()) return ZKB_OK;                      // wrong number of fold rounds: rejected before the transcript is touched
+        const u32* pt = up_pad(c, point, n_point, (size_t)n_point + 1);
+        BvRun run = basefold_verify_enqueue(c, tr->dev, pr, pt, n_point, node_hash);
+        std::vector<u32> res(run.n_results);
+        ZKB_CUDA(cudaMemcpyAsync(res.data(), run.result_dev, (size_t)run.n_results * 4, cudaMemcpyDeviceToHost, c->stream));
+        ZKB_CUDA(cudaStreamSynchronize(c->stream));
+        c->scratch_reset();
+        bool ok = pr.final_value % ZKB_P == claimed % ZKB_P;
+        for (u32 v : res) ok = ok && v == 1;
+        *accepted = ok ? 1 : 0;
+    });
+}
+
 }  // extern "C"

@@ -2,6 +2,7 @@
 #include "qwen.cuh"
 #include "oplist.cuh"
 #include "basefold.cuh"
+#include "verify.cuh"
 #include <cstdlib>
 #include <cstring>
 #include <mutex>

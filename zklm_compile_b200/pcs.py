@@ -79,3 +79,14 @@ def basefold_commit_and_prove(ctx: Context, tr: Transcript, coeffs, point, node_
         npt = pt.size
     return _proof_call(ctx, _lib.lib().zkb_basefold_commit_and_prove, ctx.h, tr.h, p, C.c_size_t(n), pp, C.c_uint32(npt),
                        C.c_int32(dev), C.c_int32(node_hash), cap=1 << 22)
+
+
+def basefold_verify_opening(ctx: Context, tr: Transcript, blob: bytes, point, claimed: int, node_hash: int = NODE_BLAKE3) -> bool:
+    """verify_opening, basefold.rs:611-748, on the bytes basefold_commit_and_prove returns.  The caller
+    absorbs the commitment root (blob[:16]) into `tr` first, as the reference's callers do."""
+    pt, pp = _a(point)
+    ok = C.c_int32(0)
+    buf = (C.c_uint8 * len(blob)).from_buffer_copy(blob)
+    check(ctx.h, _lib.lib().zkb_basefold_verify_opening(ctx.h, tr.h, buf, C.c_size_t(len(blob)), pp, C.c_uint32(pt.size),
+                                                        C.c_uint32(int(claimed)), C.c_int32(node_hash), C.byref(ok)))
+    return bool(ok.value)
