@@ -295,6 +295,14 @@ int32_t zkb_qwen_layer_prove_begin(zkb_qwen_layer* layer, uint32_t layer_idx, co
 int32_t zkb_qwen_layer_prove_end(zkb_qwen_layer* layer, uint8_t* out, size_t cap, size_t* len);
 int32_t zkb_qwen_layer_prove(zkb_qwen_layer* layer, uint32_t layer_idx, const uint8_t input_hash[32], uint8_t* out, size_t cap,
                              size_t* len);
+/* verify_qwen_layer_ef_indexed (transformer/qwen.rs:932-1097) for the proof bytes zkb_qwen_layer_prove returns.
+ * Like the reference's verifier it works on a forward pass of its own: call zkb_qwen_layer_forward with the
+ * layer's input first; the layer object then holds the trace the proof is checked against.  y_expected
+ * (d_model words, host memory; may be NULL) is compared with that pass's output.  The transcript is replayed
+ * on the device (the sumcheck rounds, the MLE-eval proofs, the LogUp sums, a Basefold opening when the matmul
+ * proofs carry one); *accepted = 1 / 0.  Bytes that do not decode give ZKB_E_ARG. */
+int32_t zkb_qwen_layer_verify(zkb_qwen_layer* layer, uint32_t layer_idx, const uint8_t input_hash[32], const uint8_t* proof, size_t len,
+                              const uint32_t* y_expected, int32_t* accepted);
 
 /* Tells a context that it shares the GPU with many other contexts that run at the same time (one
  * per layer of a model).  Its kernels then leave half of every SM free: single-CTA kernels use

@@ -3,6 +3,7 @@
 // C entry points for the matmul / MLE-eval / element-wise / RMSNorm / LogUp / Qwen-layer
 // restatements.  Proofs come back as bincode bytes (oracle/bincode.hpp).
 #include "oplist.hpp"
+#include "unbincode.hpp"
 #include <cstring>
 
 using namespace zko;
@@ -282,6 +283,19 @@ size_t zko_qwen_layer_prove_trace_h(void* h, uint32_t layer_idx, const uint8_t* 
     Transcript tr("qwen-layer-" + std::to_string(layer_idx));
     tr.absorb_bytes(input_hash, 32);
     return emit(serialize(prove_qwen_layer_precommitted_ef(L.trace, L.W, L.c, L.com, L.silu, L.sigm, tr)), out, cap);
+}
+// Decode a layer proof and run the restated verifier on it (the layer's own forward pass of x supplies the
+// trace).  1 accept, 0 reject, -1 the bytes do not decode.
+int zko_qwen_layer_verify_bytes_h(void* h, const uint32_t* x, uint32_t layer_idx, const uint8_t* input_hash, const uint32_t* y_expected,
+                                  const uint8_t* bytes, size_t len) {
+    OracleLayer& L = *static_cast<OracleLayer*>(h);
+    QwenLayerProofEF p;
+    Rd rd{bytes, len};
+    if (!rd.get(p)) return -1;
+    Transcript vt("qwen-layer-" + std::to_string(layer_idx));
+    vt.absorb_bytes(input_hash, 32);
+    VF X = vf(x, L.c.d_model), Y = vf(y_expected, L.c.d_model);
+    return verify_qwen_layer_ef(p, X, Y, L.W, L.c, L.silu, L.sigm, vt) ? 1 : 0;
 }
 // ---- op lists (oplist.hpp): built call by call, then forward + prove in one go -------------------
 struct OracleOpList { std::vector<Op> ops; };

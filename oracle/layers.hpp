@@ -72,6 +72,8 @@ inline AddProofEF prove_add_ef(const VF& a, const VF& b, const VF& c, const VEF&
 // elementwise.rs:598-642
 inline bool verify_add_ef(const AddProofEF& p, const VEF& point, Transcript& tr) {
     tr.absorb_bytes(p.c_commitment.root);
+    if (p.a_sumcheck.round_polys.empty() || p.a_sumcheck.round_polys[0].size() < 2 || p.b_sumcheck.round_polys.empty() ||
+        p.b_sumcheck.round_polys[0].size() < 2) return false;          // the reference indexes out of bounds and panics
     EF a_eval = ef_of(p.a_sumcheck.round_polys[0][0]) + ef_of(p.a_sumcheck.round_polys[0][1]);
     VEF sa, sb;
     if (!verify_product_ef_with_challenges(a_eval, p.a_sumcheck, ef_of(p.a_fin_eq), ef_of(p.a_fin), tr, &sa)) return false;

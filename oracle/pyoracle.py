@@ -381,6 +381,11 @@ class QwenLayer:
             lib().zko_qwen_layer_free(self.h)
             self.h = None
 
+    def verify_bytes(self, x, layer_idx, input_hash, y_expected, proof: bytes) -> int:
+        """The restated verify_qwen_layer_ef_indexed on proof bytes: 1 accept, 0 reject, -1 undecodable."""
+        X, px = _u32(x); Y, py = _u32(y_expected)
+        return int(lib().zko_qwen_layer_verify_bytes_h(self.h, px, C.c_uint32(layer_idx), _u8(input_hash), py, _u8(proof), C.c_size_t(len(proof))))
+
     def prove(self, x, layer_idx: int, input_hash: bytes, verify=False):
         """Forward + prove; returns (y, proof bytes, accepted or None)."""
         X, px = _u32(x)

@@ -294,11 +294,12 @@ inline bool verify_product_ef_with_challenges(EF claimed, const SumcheckProofEF&
         const auto& raw = p.round_polys[i];
         EF s0, s1, s2;
         if (raw.size() == 2) { s0 = ef_of(raw[0]); s1 = claim - s0; s2 = ef_of(raw[1]); }
-        else { s0 = ef_of(raw[0]); s1 = ef_of(raw[1]); s2 = ef_of(raw[2]); }
+        else if (raw.size() >= 3) { s0 = ef_of(raw[0]); s1 = ef_of(raw[1]); s2 = ef_of(raw[2]); }
+        else return false;                                   // the reference indexes out of bounds and panics
         if (s0 + s1 != claim) return false;
         tr.absorb_ef(s0); tr.absorb_ef(s1); tr.absorb_ef(s2);
         EF r = tr.squeeze_ef();
-        if (!p.challenges.empty() && r.arr() != p.challenges[i]) return false;
+        if (!p.challenges.empty() && (i >= p.challenges.size() || r.arr() != p.challenges[i])) return false;
         if (derived) derived->push_back(r);
         claim = interpolate_quadratic_ef(s0, s1, s2, r);
     }
@@ -312,11 +313,12 @@ inline bool verify_triple_ef_with_challenges(EF claimed, const SumcheckProofEF& 
         const auto& raw = p.round_polys[i];
         EF s0, s1, s2, s3;
         if (raw.size() == 3) { s0 = ef_of(raw[0]); s1 = claim - s0; s2 = ef_of(raw[1]); s3 = ef_of(raw[2]); }
-        else { s0 = ef_of(raw[0]); s1 = ef_of(raw[1]); s2 = ef_of(raw[2]); s3 = ef_of(raw[3]); }
+        else if (raw.size() >= 4) { s0 = ef_of(raw[0]); s1 = ef_of(raw[1]); s2 = ef_of(raw[2]); s3 = ef_of(raw[3]); }
+        else return false;                                   // the reference indexes out of bounds and panics
         if (s0 + s1 != claim) return false;
         tr.absorb_ef(s0); tr.absorb_ef(s1); tr.absorb_ef(s2); tr.absorb_ef(s3);
         EF r = tr.squeeze_ef();
-        if (!p.challenges.empty() && r.arr() != p.challenges[i]) return false;
+        if (!p.challenges.empty() && (i >= p.challenges.size() || r.arr() != p.challenges[i])) return false;
         if (derived) derived->push_back(r);
         claim = interpolate_cubic_ef({s0, s1, s2, s3}, r);
     }

@@ -179,3 +179,23 @@ def test_base_field_rmsnorm_roundtrip(d):
     assert not O.rmsnorm_base_roundtrip(xu, gamma, y, delta, tamper=1)
     wrong = y.copy(); wrong[1] = (int(wrong[1]) + 1) % P
     assert not O.rmsnorm_base_roundtrip(xu, gamma, wrong, delta)
+
+
+def test_layer_proof_bytes_decode_and_verify():
+    """oracle/unbincode.hpp is the inverse of oracle/bincode.hpp for QwenLayerProofEF: the restated verifier
+    accepts the decoded bytes of its own prover, rejects another layer index, and a truncated or extended
+    byte string does not decode."""
+    import hashlib
+    from tests.util import load_qwen_golden, rand_layer
+    G = load_qwen_golden()
+    cfg, weights, x = rand_layer(1, d_model=64, d_ff=96, heads=2, kv=2, d_head=16, v_heads=4, v_d_head=16)
+    ih = hashlib.sha256(b"decode").digest()
+    L = O.QwenLayer(cfg, weights, G["silu"], G["sigmoid"])
+    y, proof, ok = L.prove(x, 2, ih, verify=True)
+    assert ok
+    assert L.verify_bytes(x, 2, ih, y, proof) == 1
+    assert L.verify_bytes(x, 3, ih, y, proof) == 0
+    assert L.verify_bytes(x, 2, ih, y, proof[:-1]) == -1 and L.verify_bytes(x, 2, ih, y, proof + b"\0") == -1
+    bad = bytearray(proof)
+    bad[40] ^= 1                               # inside the first round polynomial of the first norm's variance sumcheck
+    assert L.verify_bytes(x, 2, ih, y, bytes(bad)) == 0

@@ -41,7 +41,8 @@ struct BvParsed {
     uint64_t num_coeffs = 0;
     bool too_large = false;
 };
-inline bool bv_parse(const uint8_t* bytes, size_t len, BvParsed& out) {
+// With `used`, trailing bytes are allowed and the number of bytes decoded is returned there.
+inline bool bv_parse(const uint8_t* bytes, size_t len, BvParsed& out, size_t* used = nullptr) {
     BvReader r{bytes, len};
     for (int i = 0; i < 4; i++) out.words.push_back(r.u32v());
     out.num_coeffs = r.u64();
@@ -53,7 +54,11 @@ inline bool bv_parse(const uint8_t* bytes, size_t len, BvParsed& out) {
     for (uint64_t i = 0; i < n_roots; i++) for (int k = 0; k < 4; k++) out.words.push_back(r.u32v());
     const uint64_t n_q = r.u64();
     if (!r.ok || n_q > 64) return false;
-    if (n_roots != log_n || n_q != log_n) { out.trees.clear(); return r.ok; }      // wrong number of fold rounds: rejected, not malformed
+    if (n_roots != log_n || n_q != log_n) {      // wrong number of fold rounds: rejected, not malformed (the rest is not decoded)
+        out.trees.clear();
+        if (used) return false;                  // embedded in a larger proof: where it ends is unknown
+        return r.ok;
+    }
     for (uint64_t round = 0; round < n_q; round++) {
         for (int tree = 0; tree < 2; tree++) {
             BvTree t{};
@@ -89,7 +94,9 @@ inline bool bv_parse(const uint8_t* bytes, size_t len, BvParsed& out) {
     }
     out.final_value = r.u32v();
     const uint64_t n_final = r.u64();
+    if (n_final > (1u << 20)) return false;
     for (uint64_t i = 0; i < n_final && r.ok; i++) r.u32v();
+    if (used) { *used = r.at; return r.ok; }
     return r.ok && r.at == len;
 }
 

@@ -3,6 +3,7 @@
 #include "oplist.cuh"
 #include "basefold.cuh"
 #include "verify.cuh"
+#include "verify_layer.cuh"
 #include <cstdlib>
 #include <cstring>
 #include <mutex>

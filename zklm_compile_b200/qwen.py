@@ -144,6 +144,17 @@ class QwenLayer:
         check(self.ctx.h, st)
         return C.string_at(buf, n.value)
 
+    def verify(self, layer_idx: int, input_hash: bytes, proof: bytes, y_expected=None) -> bool:
+        """verify_qwen_layer_ef_indexed (qwen.rs:932-1097) against the trace of the last forward pass."""
+        buf = (C.c_uint8 * len(proof)).from_buffer_copy(proof)
+        ok = C.c_int32(0)
+        ye = None
+        if y_expected is not None:
+            y = np.ascontiguousarray(y_expected, dtype=np.uint32)
+            ye = y.ctypes.data_as(u32p)
+        check(self.ctx.h, _lib.lib().zkb_qwen_layer_verify(self.h, C.c_uint32(layer_idx), (C.c_uint8 * 32).from_buffer_copy(input_hash), buf, C.c_size_t(len(proof)), ye, C.byref(ok)))
+        return bool(ok.value)
+
     def prove(self, layer_idx: int, input_hash: bytes) -> bytes:
         """QwenLayerProofEF as bincode bytes; `forward` must have run."""
         self.prove_begin(layer_idx, input_hash)
