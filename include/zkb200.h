@@ -303,6 +303,11 @@ int32_t zkb_qwen_layer_prove(zkb_qwen_layer* layer, uint32_t layer_idx, const ui
  * proofs carry one); *accepted = 1 / 0.  Bytes that do not decode give ZKB_E_ARG. */
 int32_t zkb_qwen_layer_verify(zkb_qwen_layer* layer, uint32_t layer_idx, const uint8_t input_hash[32], const uint8_t* proof, size_t len,
                               const uint32_t* y_expected, int32_t* accepted);
+/* The same in two halves, so that the layers of a model (one context each) are checked side by side: begin decodes and
+ * enqueues without waiting (y_expected is read before it returns), end waits and gives the verdict. */
+int32_t zkb_qwen_layer_verify_begin(zkb_qwen_layer* layer, uint32_t layer_idx, const uint8_t input_hash[32], const uint8_t* proof, size_t len,
+                                    const uint32_t* y_expected);
+int32_t zkb_qwen_layer_verify_end(zkb_qwen_layer* layer, int32_t* accepted);
 
 /* Tells a context that it shares the GPU with many other contexts that run at the same time (one
  * per layer of a model).  Its kernels then leave half of every SM free: single-CTA kernels use

@@ -41,6 +41,15 @@ def _layer_case(env, cfg, weights, x, layer_idx):
         for attempt in range(3):                # launch by launch, captured, replayed
             got = layer.prove(layer_idx, ih)
             assert len(got) == len(eproof) and got == eproof, f"layer proof differs from the oracle (attempt {attempt})"
+        # the GPU verifier at the real size: accepts the proof, rejects it for another layer index and with one bit changed
+        assert layer.verify(layer_idx, ih, got, y) is True
+        assert layer.verify(layer_idx + 1, ih, got, y) is False
+        bad = bytearray(got)
+        bad[len(bad) // 2] ^= 4
+        try:
+            assert layer.verify(layer_idx, ih, bytes(bad), y) is False
+        except zk.ZkbError as e:
+            assert e.code == 2
         return hashlib.sha256(eproof).hexdigest()
     finally:
         layer.close()

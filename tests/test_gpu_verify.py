@@ -107,3 +107,31 @@ def test_layer_verifier_with_basefold_bound_matmuls(env, bind, kind):
             got, exp = _both(gl, ol, x, 1, ih, y, bytes(bad))
             assert got == exp, f"byte {int(pos)}: GPU {got}, oracle {exp}"
     gl.close()
+
+
+def test_model_verifier_checks_all_layers_side_by_side(env):
+    """QwenModel.forward_and_verify: the proofs of a three-layer stack as forward_and_prove returns them are
+    accepted; one changed proof, a swapped order or a wrong claimed output are rejected."""
+    c, G, _, _ = env
+    cfgs, ws = [], []
+    for i in range(3):
+        cfg, w, x = rand_layer(20 + i, **SHAPES["gdn" if i % 2 == 0 else "gqa"])
+        cfgs.append(cfg); ws.append(w)
+    _, _, x = rand_layer(19, **SHAPES["gdn"])
+    model = zq.QwenModel(0, cfgs, ws, G["silu"], G["sigmoid"])
+    ih = zq.hash_values(x)
+    proofs = model.forward_and_prove(x, ih)
+    y = model.output()
+    assert model.forward_and_verify(x, proofs, ih, y) is True
+    assert model.forward_and_verify(x, proofs, ih) is True
+    assert model.forward_and_verify(x, proofs[::-1], ih, y) is False
+    y2 = y.copy(); y2[0] = (int(y2[0]) + 1) % P
+    assert model.forward_and_verify(x, proofs, ih, y2) is False
+    bad = bytearray(proofs[1]); bad[200] ^= 1
+    try:
+        assert model.forward_and_verify(x, [proofs[0], bytes(bad), proofs[2]], ih, y) is False
+    except zk.ZkbError as e:
+        assert e.code == 2
+    assert model.forward_and_verify(x, proofs, ih, y) is True
+    assert model.forward_and_prove(x, ih) == proofs               # and the prover still works on the same model
+    model.close()

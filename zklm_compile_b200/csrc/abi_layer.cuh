@@ -243,23 +243,42 @@ int32_t zkb_qwen_layer_prove(zkb_qwen_layer* L, uint32_t layer_idx, const uint8_
 // verify_qwen_layer_ef_indexed (qwen.rs:932-1097): the layer object must hold the forward trace of the input
 // the proof is about (zkb_qwen_layer_forward).  y_expected (d_model words, host; may be null) is compared with the
 // layer's output as the reference compares its recomputed output with the claimed one.
-int32_t zkb_qwen_layer_verify(zkb_qwen_layer* L, uint32_t layer_idx, const uint8_t input_hash[32], const uint8_t* proof, size_t len,
-                              const uint32_t* y_expected, int32_t* accepted) {
-    if (!L || !input_hash || !proof || !accepted) return ZKB_E_ARG;
-    *accepted = 0;
+int32_t zkb_qwen_layer_verify_begin(zkb_qwen_layer* L, uint32_t layer_idx, const uint8_t input_hash[32], const uint8_t* proof, size_t len,
+                                    const uint32_t* y_expected) {
+    if (!L || !input_hash || !proof) return ZKB_E_ARG;
     zkb_ctx* c = L->ctx;
+    L->v_active = false;
     ZKB_TRY(c, {
         c->use();
         clear_status(c);
         LvResult r = qwen_verify_enqueue(L, layer_idx, input_hash, proof, len, y_expected);
-        std::vector<u32> flags(r.n_ok);
-        ZKB_CUDA(cudaMemcpyAsync(flags.data(), r.ok_dev, (size_t)r.n_ok * 4, cudaMemcpyDeviceToHost, c->stream));
+        L->v_ok_dev = r.ok_dev; L->v_n_ok = r.n_ok; L->v_host_ok = r.host_ok; L->v_active = true;
+    });
+}
+int32_t zkb_qwen_layer_verify_end(zkb_qwen_layer* L, int32_t* accepted) {
+    if (!L || !accepted) return ZKB_E_ARG;
+    *accepted = 0;
+    zkb_ctx* c = L->ctx;
+    ZKB_TRY(c, {
+        c->use();
+        if (!L->v_active) throw ArgFail{ZKB_E_ARG, "zkb_qwen_layer_verify_end: no verification was begun"};
+        L->v_active = false;
+        std::vector<u32> flags(L->v_n_ok);
+        ZKB_CUDA(cudaMemcpyAsync(flags.data(), L->v_ok_dev, (size_t)L->v_n_ok * 4, cudaMemcpyDeviceToHost, c->stream));
         ZKB_CUDA(cudaStreamSynchronize(c->stream));
         c->scratch_reset();
-        bool ok = r.host_ok;
+        bool ok = L->v_host_ok;
         for (u32 v : flags) ok = ok && v == 1;
         *accepted = ok ? 1 : 0;
     });
+}
+int32_t zkb_qwen_layer_verify(zkb_qwen_layer* L, uint32_t layer_idx, const uint8_t input_hash[32], const uint8_t* proof, size_t len,
+                              const uint32_t* y_expected, int32_t* accepted) {
+    if (!accepted) return ZKB_E_ARG;
+    *accepted = 0;
+    int32_t rc = zkb_qwen_layer_verify_begin(L, layer_idx, input_hash, proof, len, y_expected);
+    if (rc) return rc;
+    return zkb_qwen_layer_verify_end(L, accepted);
 }
 
 }  // extern "C"

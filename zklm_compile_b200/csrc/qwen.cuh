@@ -51,6 +51,10 @@ struct zkb_qwen_layer {
     // pending proof
     struct Pending;
     Pending* pending = nullptr;
+    // pending verification (zkb_qwen_layer_verify_begin): the check words on the device and what the host decided while decoding
+    zkb::u32* v_ok_dev = nullptr;
+    zkb::u32 v_n_ok = 0;
+    bool v_host_ok = false, v_active = false;
     // Transcript seed of the proof being enqueued, device-resident so that the launch sequence does
     // not depend on it: [byte count, "qwen-layer-{idx}" bytes, 32 bytes of input hash].
     zkb::u32* seed_dev = nullptr;

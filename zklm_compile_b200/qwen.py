@@ -155,6 +155,20 @@ class QwenLayer:
         check(self.ctx.h, _lib.lib().zkb_qwen_layer_verify(self.h, C.c_uint32(layer_idx), (C.c_uint8 * 32).from_buffer_copy(input_hash), buf, C.c_size_t(len(proof)), ye, C.byref(ok)))
         return bool(ok.value)
 
+    def verify_begin(self, layer_idx: int, input_hash: bytes, proof: bytes, y_expected=None):
+        buf = (C.c_uint8 * len(proof)).from_buffer_copy(proof)
+        ye = None
+        if y_expected is not None:
+            y = np.ascontiguousarray(y_expected, dtype=np.uint32)
+            ye = y.ctypes.data_as(u32p)
+        check(self.ctx.h, _lib.lib().zkb_qwen_layer_verify_begin(self.h, C.c_uint32(layer_idx), (C.c_uint8 * 32).from_buffer_copy(input_hash), buf,
+                                                                 C.c_size_t(len(proof)), ye))
+
+    def verify_end(self) -> bool:
+        ok = C.c_int32(0)
+        check(self.ctx.h, _lib.lib().zkb_qwen_layer_verify_end(self.h, C.byref(ok)))
+        return bool(ok.value)
+
     def prove(self, layer_idx: int, input_hash: bytes) -> bytes:
         """QwenLayerProofEF as bincode bytes; `forward` must have run."""
         self.prove_begin(layer_idx, input_hash)
@@ -297,6 +311,34 @@ class QwenModel:
             f.result()
         proofs = [l.prove_end() for l in self.layers]
         return proofs[::-1]
+
+    def forward_and_verify(self, x, proofs, input_hash: bytes = None, y_expected=None) -> bool:
+        """verify_qwen_layer_ef_indexed for every layer (qwen.rs:932-1097): the forward pass is run again, each
+        layer's proof (`proofs` in the order forward_and_prove returns them: last layer first) is checked against
+        that pass's trace, all layers side by side on their own contexts.  `y_expected` is the claimed model output."""
+        if self.n_contexts < len(self.layers):
+            raise ValueError("forward_and_verify needs one context per layer")
+        if len(proofs) != len(self.layers):
+            return False
+        if isinstance(x, DeviceBuffer):
+            if input_hash is None:
+                raise ValueError("input_hash is required with a device-resident input")
+            self.input_hash = input_hash
+        else:
+            self.input_hash = input_hash if input_hash is not None else hash_values(x)
+        by_layer = proofs[::-1]
+        n = len(self.layers)
+        self.layers[0].forward_async(x=x)
+        for i in range(1, n):
+            self.layers[i].forward_async(prev=self.layers[i - 1])
+
+        def task(i):
+            self.layers[i].verify_begin(self.first_layer + i, self.input_hash, by_layer[i], y_expected if i == n - 1 else None)
+
+        for f in [self.pool.submit(task, i) for i in range(n)]:
+            f.result()
+        verdicts = [l.verify_end() for l in self.layers]
+        return all(verdicts)
 
     def close(self):
         self.pool.shutdown()
