@@ -735,9 +735,15 @@ def run_qwen(zk, args, rank, world, local, dist, barrier, max_over_ranks):
             out_view = torch.as_tensor(_Out(), device=f"cuda:{local}")
         gatherer = sharding.ProofGather(dist, rank, world, 49152 * max(1, -(-L // world)) + 4096, device=f"cuda:{local}")
 
+    # The hop is ordered on the device, not by the host: send and recv are issued with the model's forward stream as
+    # torch's current stream, so the send waits (on the GPU) for the last forward kernel enqueued before it and the next
+    # rank's first forward kernel waits (on the GPU) for the recv; no host synchronisation sits on the forward chain.
+    fwd = torch.cuda.ExternalStream(model.forward_stream, device=f"cuda:{local}") if (world > 1 and model) else None
+
     def hand_over():
         if rank + 1 < world and hi < L:
-            dist.send(out_view, dst=rank + 1)
+            with torch.cuda.stream(fwd):
+                dist.send(out_view, dst=rank + 1)
 
     def step(host_input):
         """forward (activation hops rank to rank) + prove my layers + gather on rank 0."""
@@ -745,11 +751,11 @@ def run_qwen(zk, args, rank, world, local, dist, barrier, max_over_ranks):
             proofs = model.forward_and_prove(x_pinned if host_input else x_dev, ih)
         elif model:
             if rank == 0:
-                proofs = model.forward_and_prove(x_pinned if host_input else x_dev, ih, on_forward_finished=hand_over)
+                proofs = model.forward_and_prove(x_pinned if host_input else x_dev, ih, on_forward_enqueued=hand_over)
             else:
-                dist.recv(act, src=rank - 1)
-                torch.cuda.current_stream().synchronize()
-                proofs = model.forward_and_prove(act_buf, ih, on_forward_finished=hand_over)
+                with torch.cuda.stream(fwd):
+                    dist.recv(act, src=rank - 1)
+                proofs = model.forward_and_prove(act_buf, ih, on_forward_enqueued=hand_over)
         else:
             proofs = []
         if world > 1:
@@ -887,17 +893,20 @@ def run_qwen9b(zk, args, rank, world, local, dist, barrier, max_over_ranks):
             out_view = torch.as_tensor(_Out(), device=f"cuda:{local}")
         gatherer = sharding.ProofGather(dist, rank, world, (8 << 20) * max(1, -(-L // world)), device=f"cuda:{local}")
 
-    def hand_over():
+    fwd = torch.cuda.ExternalStream(model.forward_stream, device=f"cuda:{local}") if (world > 1 and model) else None
+
+    def hand_over():                    # ordered on the device behind the last forward kernel (see run_qwen)
         if rank + 1 < world and hi < L:
-            dist.send(out_view, dst=rank + 1)
+            with torch.cuda.stream(fwd):
+                dist.send(out_view, dst=rank + 1)
 
     def step():
         if model and rank == 0:
-            proofs = model.forward_and_prove(x_pinned, ih, on_forward_finished=hand_over if world > 1 else None)
+            proofs = model.forward_and_prove(x_pinned, ih, on_forward_enqueued=hand_over if world > 1 else None)
         elif model:
-            dist.recv(act, src=rank - 1)
-            torch.cuda.current_stream().synchronize()
-            proofs = model.forward_and_prove(act_buf, ih, on_forward_finished=hand_over)
+            with torch.cuda.stream(fwd):
+                dist.recv(act, src=rank - 1)
+            proofs = model.forward_and_prove(act_buf, ih, on_forward_enqueued=hand_over)
         else:
             proofs = []
         if world > 1:

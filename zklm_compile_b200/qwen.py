@@ -250,14 +250,23 @@ class QwenModel:
         proofs = [l.prove_end() for l in self.layers]
         return proofs[::-1]
 
-    def forward_and_prove(self, x, input_hash: bytes = None, on_forward_done=None, on_forward_finished=None):
+    @property
+    def forward_stream(self) -> int:
+        """The cudaStream_t (as an integer) that all forward passes of this model run on, for callers that order their
+        own work with it on the device (e.g. a send of the last layer's output to the next GPU)."""
+        return int(self._fwd_stream.value or 0)
+
+    def forward_and_prove(self, x, input_hash: bytes = None, on_forward_done=None, on_forward_finished=None, on_forward_enqueued=None):
         """Forward pass and all layer proofs with the two overlapped: every layer's proof is
         enqueued right behind its own forward, the forward of the next layer only waits (on the
         GPU) for the previous layer's forward.  Returns the proofs in reverse layer order.
         `on_forward_done(output)` is called with the host copy of the output as soon as the last
         layer's forward has finished, while the proofs are still running; `on_forward_finished()` is
         called at the same moment without any copy (the output then sits at
-        `layers[-1].output_address()` on the device: used to hand the activation to the next GPU)."""
+        `layers[-1].output_address()` on the device: used to hand the activation to the next GPU);
+        `on_forward_enqueued()` is called even earlier, as soon as the last layer's forward has been
+        *enqueued* on `forward_stream` - work the caller then puts on that stream runs right behind it on the
+        device, with no host wait in between."""
         import threading
         if isinstance(x, DeviceBuffer):
             if input_hash is None:
@@ -268,6 +277,8 @@ class QwenModel:
         n = len(self.layers)
         if self.n_contexts < n:          # shared contexts: the whole forward pass first, then the proofs in waves
             self.forward(x, input_hash)
+            if on_forward_enqueued is not None:
+                on_forward_enqueued()
             if on_forward_finished is not None:
                 self.layers[-1].ctx.sync()
                 on_forward_finished()
@@ -300,8 +311,10 @@ class QwenModel:
             futures = []
         else:
             futures = [self.pool.submit(task, i) for i in range(n)]
-        if on_forward_done is not None or on_forward_finished is not None:
+        if on_forward_done is not None or on_forward_finished is not None or on_forward_enqueued is not None:
             issued[n - 1].wait()
+            if not failed and on_forward_enqueued is not None:
+                on_forward_enqueued()
             if not failed and on_forward_finished is not None:
                 self.layers[-1].wait_forward()
                 on_forward_finished()
