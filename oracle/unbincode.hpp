@@ -2,7 +2,7 @@
 //
 // The inverse of bincode.hpp for the extension-field layer proof: QwenLayerProofEF (qwen.rs:711-737)
 // and the structs inside it, decoded from the bytes the provers emit, so that the restated verifier
-// can judge byte strings (honest or tampered) and be compared with the GPU verifier.
+// can be run on byte strings (honest or tampered) and be compared with the GPU verifier.
 #pragma once
 #include "bincode.hpp"
 #include "qwen_verify.hpp"
