@@ -88,10 +88,13 @@ uint64_t zkb_ctx_scratch_bytes(const zkb_ctx* ctx);
  * ZKB_OPT_MATVEC_RING: nonzero = forward matvecs whose rows are a multiple of 16 bytes (at most 64 KB)
  * go through a shared-memory ring filled by bulk asynchronous copies, one persistent CTA per SM, instead of
  * the kernel that stages rows in registers (measured slower on the 4B shape: 5.49 against 5.22 ms for the
- * forward chain, so it is off unless asked for). */
+ * forward chain, so it is off unless asked for).
+ * ZKB_OPT_SHARED_SM_HASH: nonzero = the single-CTA kernels that advance the transcript do not reserve an SM's
+ * shared memory for themselves (normally they ask for 200 KB they do not use, so that other contexts' kernels
+ * do not share their SM). */
 enum { ZKB_OPT_PLAIN_TAIL = 0, ZKB_OPT_SINGLE_CTA_THREADS = 1, ZKB_OPT_PIPE_THREADS = 2, ZKB_OPT_NO_FUSED_FOLD = 3, ZKB_OPT_FOLD2_VEC = 4,
        ZKB_OPT_BASEFOLD_IN_ORDER = 5, ZKB_OPT_MATVEC_PREFETCH_ROWS = 6,
-       ZKB_OPT_MATVEC_RING = 7 };
+       ZKB_OPT_MATVEC_RING = 7, ZKB_OPT_SHARED_SM_HASH = 8 };
 int32_t zkb_ctx_set_option(zkb_ctx* ctx, int32_t option, int32_t value);
 /* The context's cudaStream_t (as an opaque pointer), for callers that enqueue their own work in order with the library's. */
 void* zkb_ctx_stream(zkb_ctx* ctx);

@@ -386,7 +386,7 @@ inline BfPending basefold_enqueue(zkb_ctx* c, TrState* tr, CoefSrc src, size_t n
         size_t off = c->rec_alloc(bf_round_words(h_prev));
         rp.rec = c->rec_dev + off;
         pd.round_off.push_back(off);
-        bf_round_kernel<<<1, 256, 0, c->stream>>>(rp);
+        bf_round_kernel<<<1, 256, exclusive_smem(bf_round_kernel, c), c->stream>>>(rp);
         ZKB_LAUNCHED(c);
         c->prof_mark();
         if (ahead) {

@@ -272,7 +272,7 @@ inline BvRun basefold_verify_enqueue(zkb_ctx* c, TrState* tr, const BvParsed& pr
     if (kind == NODE_AES_MMO) bf_verify_batch_kernel<NODE_AES_MMO><<<n_trees, 128, 0, side>>>(words, trees, run.result_dev);
     else bf_verify_batch_kernel<NODE_BLAKE3><<<n_trees, 128, 0, side>>>(words, trees, run.result_dev);
     ZKB_LAUNCHED(c);
-    bf_verify_chain_kernel<<<1, 32, 0, main_stream>>>(tr, words, log_n, point_dev, n_point, alpha, qidx);
+    bf_verify_chain_kernel<<<1, 32, exclusive_smem(bf_verify_chain_kernel, c), main_stream>>>(tr, words, log_n, point_dev, n_point, alpha, qidx);
     ZKB_LAUNCHED(c);
     const u32 items = log_n * BF_QUERIES;
     bf_verify_fold_kernel<<<(items + 7) / 8, 256, 0, main_stream>>>(words, trees, log_n, alpha, qidx, tb.w_flat, run.result_dev + n_trees);

@@ -301,7 +301,7 @@ inline Fe* lv_sumcheck(LvRun& R, const LvSumcheck& s, u32 degree, u32 claim_off,
     R.require(s.n_rounds <= 40);
     Fe* out = R.slot(s.n_rounds ? s.n_rounds : 1);
     LvScArgs a{s.off, s.n_rounds, degree, claim_off, claim_slot, fin_off, n_fin, s.chal_off, s.n_chal, out, post_squeezes};
-    lv_sumcheck_kernel<<<1, 32, 0, R.c->stream>>>(R.tr, R.pw, a, R.flag());
+    lv_sumcheck_kernel<<<1, 32, exclusive_smem(lv_sumcheck_kernel, R.c), R.c->stream>>>(R.tr, R.pw, a, R.flag());
     ZKB_LAUNCHED(R.c);
     return out;
 }
