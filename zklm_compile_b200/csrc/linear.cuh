@@ -89,7 +89,7 @@ __global__ void __launch_bounds__(128 * FOLD_GROUPS, 2) fold_eq_matvec_kernel(co
             for (int q = 0; q < FOLD_UNROLL; q++) {
                 const u32* rp = W + (row + (size_t)q * FOLD_GROUPS) * n;
                 if (vec) {
-                    uint4 t = *reinterpret_cast<const uint4*>(rp + j0);
+                    uint4 t = __ldcs(reinterpret_cast<const uint4*>(rp + j0));     // read once: evict first, keep L2 for the small tables of the other layers' tails
                     w[q][0] = t.x; w[q][1] = t.y; w[q][2] = t.z; w[q][3] = t.w;
                 } else {
 #pragma unroll
@@ -215,7 +215,7 @@ __device__ __forceinline__ u64 matvec_row_part(const u32* __restrict__ row, cons
         const uint4* xv = reinterpret_cast<const uint4*>(x);
         size_t gidx = g0 + lane;
         for (; gidx + 96 < g1; gidx += 128) {
-            uint4 w0 = rw[gidx], w1 = rw[gidx + 32], w2 = rw[gidx + 64], w3 = rw[gidx + 96];
+            uint4 w0 = __ldcs(rw + gidx), w1 = __ldcs(rw + gidx + 32), w2 = __ldcs(rw + gidx + 64), w3 = __ldcs(rw + gidx + 96);
             uint4 v0 = __ldg(xv + gidx), v1 = __ldg(xv + gidx + 32), v2 = __ldg(xv + gidx + 64), v3 = __ldg(xv + gidx + 96);
             acc += part_reduce((u64)w0.x * v0.x + (u64)w0.y * v0.y) + part_reduce((u64)w0.z * v0.z + (u64)w0.w * v0.w);
             acc += part_reduce((u64)w1.x * v1.x + (u64)w1.y * v1.y) + part_reduce((u64)w1.z * v1.z + (u64)w1.w * v1.w);
