@@ -84,7 +84,7 @@ uint64_t zkb_ctx_scratch_bytes(const zkb_ctx* ctx);
  * each round one after another on the context's stream (normally the folds and trees of all rounds
  * whose challenge is a coordinate of the point run ahead on a second stream).
  * ZKB_OPT_MATVEC_PREFETCH_ROWS: 0..8, rows per CTA that a forward matvec prefetches into L2 before it
- * waits for its input vector (default 8: the CTA's whole first pass; here 0 is a value, not "default").
+ * waits for its input vector (default 2; 8 is the CTA's whole first pass; here 0 is a value, not "default").
  * ZKB_OPT_MATVEC_RING: nonzero = forward matvecs whose rows are a multiple of 16 bytes (at most 64 KB)
  * go through a shared-memory ring filled by bulk asynchronous copies, one persistent CTA per SM, instead of
  * the kernel that stages rows in registers (measured slower on the 4B shape: 5.49 against 5.22 ms for the

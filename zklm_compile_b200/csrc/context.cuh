@@ -143,7 +143,7 @@ struct zkb_ctx {
     int opt_single_threads = 0, opt_pipe_threads = 0, opt_fold2_vec = 0;
     bool opt_plain_tail = false, opt_no_fused2 = false, opt_bf_in_order = false, opt_shared_sm = false;
     bool opt_mv_ring = false;            // forward matvec: the bulk-copy ring kernel instead of the register-staged one
-    int opt_mv_prefetch = 8;             // rows per CTA whose lines a forward matvec prefetches into L2 before it waits for its input
+    int opt_mv_prefetch = 2;             // rows per CTA whose lines a forward matvec prefetches into L2 before it waits for its input (0 .. 8 measured: 2 is best)
     // Second stream for work that does not depend on the transcript (the fold / tree chain of a Basefold
     // opening), joined to `stream` through events; created on first use.
     cudaStream_t side = nullptr;
