@@ -67,3 +67,42 @@ def test_short_output_buffer_reports_length_and_context_survives(ctx):
     assert zp.prove_matmul_succinct_ef(w, x, y, 8, 8, t2) == O.prove_matmul_succinct(o2, w, x, y, 8, 8, ef=True)
     # and the Merkle / Basefold entry points accept the smallest inputs
     assert zpc.merkle_root(ctx, np.array([5], np.uint32)) == O.merkle_root(np.array([5], np.uint32), 0)
+
+
+def test_verifier_entry_points_refuse_bad_arguments(ctx):
+    """The verifiers answer malformed input with a status code, never with a verdict: null pointers, bytes
+    that do not decode, an unknown node hash, a layer that has no forward trace yet, an end without a begin."""
+    import hashlib
+    from zklm_compile_b200 import qwen as zq
+    from tests.util import load_qwen_golden, rand_layer
+    L = _lib.lib()
+    ok = C.c_int32(7)
+    tr = zk.Transcript(ctx, b"v")
+    pt = np.ones(4, np.uint32)
+    junk = (C.c_uint8 * 40)(*range(40))
+    assert L.zkb_basefold_verify_opening(ctx.h, tr.h, None, C.c_size_t(0), pt.ctypes.data_as(u32p), C.c_uint32(4), C.c_uint32(0), C.c_int32(0), C.byref(ok)) == 2
+    assert L.zkb_basefold_verify_opening(ctx.h, tr.h, junk, C.c_size_t(40), pt.ctypes.data_as(u32p), C.c_uint32(4), C.c_uint32(0), C.c_int32(0), C.byref(ok)) == 2
+    assert ok.value == 0 and b"decode" in L.zkb_last_error(ctx.h)
+    c = np.arange(1, 65, dtype=np.uint32)
+    point = np.arange(3, 9, dtype=np.uint32)
+    blob = zpc.basefold_commit_and_prove(ctx, zk.Transcript(ctx, b"v"), c, point)
+    buf = (C.c_uint8 * len(blob)).from_buffer_copy(blob)
+    assert L.zkb_basefold_verify_opening(ctx.h, tr.h, buf, C.c_size_t(len(blob)), point.ctypes.data_as(u32p), C.c_uint32(6), C.c_uint32(0), C.c_int32(5),
+                                         C.byref(ok)) == 2                     # unknown node hash
+
+    G = load_qwen_golden()
+    cfg, weights, x = rand_layer(1, d_model=64, d_ff=96, heads=2, kv=2, d_head=16, v_heads=4, v_d_head=16)
+    layer = zq.QwenLayer(ctx, cfg, weights, ctx.upload(G["silu"]), ctx.upload(G["sigmoid"]))
+    ih = hashlib.sha256(b"e").digest()
+    with pytest.raises(zk.ZkbError) as e:
+        layer.verify(0, ih, bytes(100))                                          # no forward pass yet
+    assert e.value.code == 2
+    y = layer.forward(x)
+    with pytest.raises(zk.ZkbError) as e:
+        layer.verify(0, ih, bytes(100), y)                                       # a hundred zero bytes are not a proof
+    assert e.value.code == 2
+    with pytest.raises(zk.ZkbError):
+        layer.verify_end()                                                       # nothing was begun
+    proof = layer.prove(0, ih)
+    assert layer.verify(0, ih, proof, y) is True                                 # and the layer is still usable
+    layer.close()
