@@ -89,9 +89,9 @@ uint64_t zkb_ctx_scratch_bytes(const zkb_ctx* ctx);
  * go through a shared-memory ring filled by bulk asynchronous copies, one persistent CTA per SM, instead of
  * the kernel that stages rows in registers (measured slower on the 4B shape: 5.49 against 5.22 ms for the
  * forward chain, so it is off unless asked for).
- * ZKB_OPT_SHARED_SM_HASH: nonzero = the single-CTA kernels that advance the transcript do not reserve an SM's
+ * ZKB_OPT_SHARED_SM_HASH: 1 = the single-CTA kernels that advance the transcript do not reserve an SM's
  * shared memory for themselves (normally they ask for 200 KB they do not use, so that other contexts' kernels
- * do not share their SM). */
+ * do not share their SM); 16 .. 200 = they reserve that many KB. */
 enum { ZKB_OPT_PLAIN_TAIL = 0, ZKB_OPT_SINGLE_CTA_THREADS = 1, ZKB_OPT_PIPE_THREADS = 2, ZKB_OPT_NO_FUSED_FOLD = 3, ZKB_OPT_FOLD2_VEC = 4,
        ZKB_OPT_BASEFOLD_IN_ORDER = 5, ZKB_OPT_MATVEC_PREFETCH_ROWS = 6,
        ZKB_OPT_MATVEC_RING = 7, ZKB_OPT_SHARED_SM_HASH = 8 };

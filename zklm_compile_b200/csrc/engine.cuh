@@ -210,17 +210,18 @@ inline ScRec sumcheck_enqueue(zkb_ctx* c, TrState* tr, int kind, const u32* cons
 constexpr size_t EXCLUSIVE_SMEM = 200 * 1024;
 template <class K>
 inline size_t exclusive_smem(K kernel, zkb_ctx* c) {
-    if (c->opt_shared_sm) return 0;
+    if (c->opt_shared_sm == 1) return 0;
+    const size_t want = c->opt_shared_sm >= 16 ? (size_t)c->opt_shared_sm * 1024 : EXCLUSIVE_SMEM;
     const int device = c->device;
     static std::mutex mu;
     static std::map<std::pair<const void*, int>, bool> done;
     std::lock_guard<std::mutex> g(mu);
     auto key = std::make_pair((const void*)kernel, device);
     if (!done[key]) {
-        ZKB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)EXCLUSIVE_SMEM));
+        ZKB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         done[key] = true;
     }
-    return EXCLUSIVE_SMEM;
+    return want;
 }
 struct ScriptBuilder {
     TrScript s{};

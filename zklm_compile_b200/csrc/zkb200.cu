@@ -364,7 +364,10 @@ int32_t zkb_ctx_set_option(zkb_ctx* c, int32_t option, int32_t value) {
         case ZKB_OPT_NO_FUSED_FOLD: c->opt_no_fused2 = value != 0; break;
         case ZKB_OPT_BASEFOLD_IN_ORDER: c->opt_bf_in_order = value != 0; break;
         case ZKB_OPT_MATVEC_RING: c->opt_mv_ring = value != 0; break;
-        case ZKB_OPT_SHARED_SM_HASH: c->opt_shared_sm = value != 0; break;
+        case ZKB_OPT_SHARED_SM_HASH:
+            if (value != 0 && value != 1 && (value < 16 || value > 200)) return ZKB_E_ARG;
+            c->opt_shared_sm = (int)value;
+            break;
         case ZKB_OPT_MATVEC_PREFETCH_ROWS:
             if (value < 0 || value > 8) return ZKB_E_ARG;
             c->opt_mv_prefetch = (int)value;
