@@ -135,3 +135,24 @@ def test_model_verifier_checks_all_layers_side_by_side(env):
     assert model.forward_and_verify(x, proofs, ih, y) is True
     assert model.forward_and_prove(x, ih) == proofs               # and the prover still works on the same model
     model.close()
+
+
+def test_graph_replay_comes_back_after_the_arena_was_trimmed(env):
+    """zkb_ctx_trim frees the scratch arena; the next proofs let it grow back launch by launch, then the launch
+    sequence is captured again and replayed (graph state 2), with the same proof bytes throughout."""
+    gl, ol, x = _layer(env, "gdn", seed=6)
+    c = env[0]
+    ih = hashlib.sha256(b"trim").digest()
+    gl.forward(x)
+    ref = gl.prove(0, ih)
+    for _ in range(4):
+        assert gl.prove(0, ih) == ref
+    assert gl.graph_state() == 2
+    c.trim()
+    assert gl.graph_state() != 2
+    states = []
+    for _ in range(5):
+        assert gl.prove(0, ih) == ref
+        states.append(gl.graph_state())
+    assert states[-1] == 2, states
+    gl.close()

@@ -100,7 +100,7 @@ int32_t zkb_qwen_layer_use_graph(zkb_qwen_layer* L, int32_t on) {
 int32_t zkb_qwen_layer_graph_state(const zkb_qwen_layer* L) {
     if (!L || !L->use_graph || L->ctx->profile) return 0;
     if (L->graph_exec && L->graph_epoch == L->ctx->arena_epoch && L->graph_bind == L->bind_mode && L->graph_hash == L->node_hash) return 2;
-    return L->proofs_enqueued >= 1 ? 1 : 0;
+    return (L->proofs_enqueued >= 1 && L->eager_epoch == L->ctx->arena_epoch && L->capture_failures < 3) ? 1 : 0;
 }
 // Weight binding used by the layer's eight matmul proofs from now on.
 int32_t zkb_qwen_layer_set_binding(zkb_qwen_layer* L, int32_t bind_mode, int32_t node_hash) {

@@ -68,6 +68,10 @@ struct zkb_qwen_layer {
     int graph_bind = -1, graph_hash = -1;
     uint64_t proofs_enqueued = 0;
     bool use_graph = true;
+    // A capture is only tried when the arena has not changed since the last proof that was enqueued launch by launch
+    // (after zkb_ctx_trim, or a change of shapes, the arena first has to grow back to its final size).
+    uint64_t eager_epoch = ~0ull;
+    int capture_failures = 0;
 };
 
 namespace zkb {
@@ -295,7 +299,7 @@ inline void qwen_prove_enqueue_inner(zkb_qwen_layer* L, u32 layer_idx, const uin
         return;
     }
     qwen_graph_drop(L);
-    if (L->proofs_enqueued >= 1) {
+    if (L->proofs_enqueued >= 1 && L->eager_epoch == c->arena_epoch && L->capture_failures < 3) {
         const uint64_t launches0 = c->launches;
         cudaGraph_t graph = nullptr;
         ZKB_CUDA(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
@@ -326,9 +330,9 @@ inline void qwen_prove_enqueue_inner(zkb_qwen_layer* L, u32 layer_idx, const uin
         } else if (graph) {
             cudaGraphDestroy(graph);
         }
-        // capture did not work out (e.g. the arena had to grow): clear the sticky error, go on eagerly
+        // capture did not work out (e.g. the arena had to grow): clear the sticky error, go on eagerly; a later proof tries again
         cudaGetLastError();
-        L->use_graph = false;
+        L->capture_failures++;
         c->launches = launches0;
         c->rec_reset();
         c->scratch_reset();
@@ -337,6 +341,7 @@ inline void qwen_prove_enqueue_inner(zkb_qwen_layer* L, u32 layer_idx, const uin
         L->pending = new zkb_qwen_layer::Pending();
     }
     qwen_prove_launches(L, *L->pending);
+    L->eager_epoch = c->arena_epoch;
     L->proofs_enqueued++;
 }
 inline void qwen_prove_enqueue(zkb_qwen_layer* L, u32 layer_idx, const uint8_t input_hash[32]) {
