@@ -144,6 +144,24 @@ int32_t zkb_tr_squeeze_ef(zkb_transcript* tr, uint32_t out[4]);                 
 int32_t zkb_tr_export(zkb_transcript* tr, uint8_t state[ZKB_TR_STATE_BYTES]);
 int32_t zkb_tr_import(zkb_transcript* tr, const uint8_t state[ZKB_TR_STATE_BYTES]);
 
+/* ---- weights in the reference's wire format, kept resident ----
+ * zkb_weightset_preload takes the preload block of the reference's server mode (server.rs:33-94):
+ *   [count u32] then per matrix [name_len u32][name, UTF-8][m u32][n u32][m * n u32 LE]
+ * copies every matrix to device memory (through pinned staging buffers, the copy to the GPU overlapping
+ * the host copy of the next piece), computes its commit_weights_fast root on the GPU and keeps both by name,
+ * as the server's HashMap<String, PreloadedLinear> does (a later matrix of the same name replaces the
+ * earlier one).  The caps are the reference's (at most 65536 matrices, names up to 4096 bytes, dimensions up
+ * to 2^24, 2^30 elements per matrix); a violation, a block that ends early or a name that is not UTF-8 gives
+ * ZKB_E_ARG and nothing stays allocated.  *consumed (may be NULL) = bytes of the block that were read: the
+ * requests follow from there.  Pointers from zkb_weightset_get are device pointers (row-major u32, 16-byte
+ * aligned) valid until zkb_weightset_destroy; they can be passed wherever `W` with w_on_device != 0 is taken. */
+typedef struct zkb_weightset zkb_weightset;
+int32_t zkb_weightset_preload(zkb_ctx* ctx, const uint8_t* block, size_t len, zkb_weightset** out, size_t* consumed);
+uint32_t zkb_weightset_count(const zkb_weightset* ws);
+uint64_t zkb_weightset_bytes(const zkb_weightset* ws);
+int32_t zkb_weightset_get(const zkb_weightset* ws, const char* name, const uint32_t** w_dev, size_t* m, size_t* n, uint8_t root[32]);
+void zkb_weightset_destroy(zkb_weightset* ws);
+
 /* ---- sumcheck provers ----
  * tables[i] holds 2^num_vars elements (u32 each for base-field inputs, 4 u32 each for EF
  * inputs; which is fixed by `kind`).  `on_device` != 0: tables are device pointers and are

@@ -432,6 +432,7 @@ int32_t zkb_sumcheck_prove(zkb_ctx* c, zkb_transcript* t, int32_t kind, const ui
 #include "abi_pcs.cuh"
 #include "abi_split.cuh"
 #include "abi_oplist.cuh"
+#include "abi_weights.cuh"
 
 // =============================================================================================
 // Allocation-free weight fold
