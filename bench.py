@@ -720,7 +720,67 @@ def run_oplist_legs(zk, ctx, with_cpu, cores):
                       "the prover, are the integer requantisation of the running activation here (on the device; the CPU port "
                       "gets the same values from its own forward pass)"})
     out["gpt2_124m_oplist"] = r
+    out["attention_rows_gpt2_head_shape"] = run_attention_leg(zk, ctx, with_cpu, cores)
     return out
+
+
+def run_attention_leg(zk, ctx, with_cpu, cores, nh=12, s=128, d=64):
+    """Row-decomposed attention at seq_len >= 2 (proving/attention.rs:116-276) at the GPT-2-124M head shape: 12 heads,
+    128 positions, d_head 64, exp table of scale 100; q, k in {-1, 0, 1} so that every score is a table input, v uniform.
+    One CTA per (head, row) proves the row on its own transcript; the caller's transcript then absorbs all scores and
+    outputs, one SHA-256 block after the other, which is the floor of the call."""
+    from zklm_compile_b200 import attention as za, tables
+    rng = np.random.default_rng(31)
+    n = nh * s * d
+    P = (1 << 31) - 1
+    q = np.mod(rng.integers(-1, 2, n), P).astype(np.uint32)
+    k = np.mod(rng.integers(-1, 2, n), P).astype(np.uint32)
+    v = rng.integers(0, P, n).astype(np.uint32)
+    t = tables.build_exp_table(100)
+    dq, dk, dv, dt = (ctx.upload(a) for a in (q, k, v, t))
+
+    def timed(fn, reps=5, warm=3):
+        best = []
+        for i in range(warm + reps):
+            tr = zk.Transcript(ctx, b"structured-ml-proof")
+            t0 = time.perf_counter()
+            pr = fn(tr)
+            t1 = time.perf_counter()
+            if i >= warm:
+                best.append(1e3 * (t1 - t0))
+        return float(np.median(best)), pr
+
+    host_ms, proof = timed(lambda tr: za.prove_row_attention(q, k, v, nh, s, d, t, tr))
+    dev_ms, proof_d = timed(lambda tr: za.prove_row_attention(dq, dk, dv, nh, s, d, dt, tr))
+    ctx.set_option(zk.Context.OPT_BASEFOLD_IN_ORDER, 1)
+    inorder_ms, _ = timed(lambda tr: za.prove_row_attention(dq, dk, dv, nh, s, d, dt, tr))
+    ctx.set_option(zk.Context.OPT_BASEFOLD_IN_ORDER, 0)
+    fwd = []
+    for i in range(6):
+        ctx.timer_start()
+        o = za.row_attention_forward(ctx, dq, dk, dv, nh, s, d, dt)
+        fwd.append(ctx.timer_stop_ms())
+        o.free()
+    absorbed = nh * s * (s + d) * 4
+    r = {"workload": f"row attention, {nh} heads x {s} positions x d_head {d} (GPT-2-124M head shape), exp table scale 100, base-field challenges",
+         "rows": nh * s, "prove_ms_host_inputs": round(host_ms, 3), "prove_ms_device_inputs": round(dev_ms, 3),
+         "prove_ms_rows_then_transcript": round(inorder_ms, 3), "forward_ms": round(float(np.median(fwd[2:])), 3),
+         "proof_bytes": len(proof), "same_proof_from_device_inputs": proof == proof_d,
+         "caller_transcript_bytes_absorbed": absorbed, "caller_transcript_sha256_blocks": absorbed // 64,
+         "h2d_bytes": 3 * n * 4 + t.size * 4, "gpu_launches_per_call": 3}
+    if with_cpu:
+        from oracle import pyoracle as O
+        O.set_threads(cores)
+        ts = []
+        for i in range(2):
+            t0 = time.perf_counter()
+            e, st = O.prove_row_attention(O.Transcript(b"structured-ml-proof"), q, k, v, nh, s, d, t)
+            ts.append(1e3 * (time.perf_counter() - t0))
+        r.update({"cpu_port_ms": round(min(ts), 1), "cpu_port_threads": cores, "proof_identical_to_cpu_port": e == proof,
+                  "cpu_port_over_this": round(min(ts) / host_ms, 2)})
+    for b in (dq, dk, dv, dt):
+        b.free()
+    return r
 
 
 def run_qwen(zk, args, rank, world, local, dist, barrier, max_over_ranks):

@@ -91,10 +91,12 @@ uint64_t zkb_ctx_scratch_bytes(const zkb_ctx* ctx);
  * forward chain, so it is off unless asked for).
  * ZKB_OPT_SHARED_SM_HASH: 1 = the single-CTA kernels that advance the transcript do not reserve an SM's
  * shared memory for themselves (normally they ask for 200 KB they do not use, so that other contexts' kernels
- * do not share their SM); 16 .. 200 = they reserve that many KB. */
+ * do not share their SM); 16 .. 200 = they reserve that many KB.
+ * ZKB_OPT_ATTENTION_THREADS: threads per (head, row) CTA of the row-attention kernels: 64, 128 or 256; 0 = chosen
+ * from seq_len and d_head (fewer threads let more rows share an SM; a row's critical path is its one-thread hash chain). */
 enum { ZKB_OPT_PLAIN_TAIL = 0, ZKB_OPT_SINGLE_CTA_THREADS = 1, ZKB_OPT_PIPE_THREADS = 2, ZKB_OPT_NO_FUSED_FOLD = 3, ZKB_OPT_FOLD2_VEC = 4,
        ZKB_OPT_BASEFOLD_IN_ORDER = 5, ZKB_OPT_MATVEC_PREFETCH_ROWS = 6,
-       ZKB_OPT_MATVEC_RING = 7, ZKB_OPT_SHARED_SM_HASH = 8 };
+       ZKB_OPT_MATVEC_RING = 7, ZKB_OPT_SHARED_SM_HASH = 8, ZKB_OPT_ATTENTION_THREADS = 9 };
 int32_t zkb_ctx_set_option(zkb_ctx* ctx, int32_t option, int32_t value);
 /* The context's cudaStream_t (as an opaque pointer), for callers that enqueue their own work in order with the library's. */
 void* zkb_ctx_stream(zkb_ctx* ctx);
@@ -143,6 +145,26 @@ int32_t zkb_tr_squeeze_ef(zkb_transcript* tr, uint32_t out[4]);                 
 #define ZKB_TR_STATE_BYTES 112
 int32_t zkb_tr_export(zkb_transcript* tr, uint8_t state[ZKB_TR_STATE_BYTES]);
 int32_t zkb_tr_import(zkb_transcript* tr, const uint8_t state[ZKB_TR_STATE_BYTES]);
+
+/* ---- row-decomposed attention at seq_len >= 2 ----
+ * prove_row_attention (proving/attention.rs:116-276), as the op-list prover calls it for an "attention" op
+ * (pipeline/prove.rs:419-425), and the op's forward pass (pipeline/forward.rs:233-276).
+ *   q, k, v     (num_heads, seq_len, d_head) row-major canonical M31 values
+ *   table_out   output column of the exp table in table order (65536 entries, input raw as i16 -
+ *               lookup.rs build_exp_table - or 256 entries, input raw as i8, as the reference's tests build it)
+ *   on_device   0: all pointers are host memory; 1: q, k, v, table_out (and attn_out / out) are device pointers
+ * Forward: out[h][i] = sum_l y[l] V[h][l], y = e / sum(e), e[j] = table(Q[h][i] . K[h][j]).
+ * Prove: `tr` absorbs num_heads, seq_len, d_head, every (head, row) is proved on a transcript of its own
+ * ("row-attn-h{h}-r{i}": score matmul, softmax = LogUp of e + sum sumcheck + division sumcheck, output matmul),
+ * one CTA per row, then `tr` absorbs every row's scores and outputs.  `out` receives bincode(RowAttentionProof)
+ * with seq1_consistency = None; attn_out (may be NULL) the op's output.  seq_len <= 1024, d_head <= 256.
+ * ZKB_E_ARG with a message when a score is not an input of the table or a row's sum of e is zero (the
+ * reference panics on both: attention.rs:105-108). */
+int32_t zkb_row_attention_forward(zkb_ctx* ctx, const uint32_t* q, const uint32_t* k, const uint32_t* v, size_t num_heads, size_t seq_len,
+                                  size_t d_head, const uint32_t* table_out, size_t n_table, int32_t on_device, uint32_t* out);
+int32_t zkb_prove_row_attention(zkb_ctx* ctx, zkb_transcript* tr, const uint32_t* q, const uint32_t* k, const uint32_t* v, size_t num_heads,
+                                size_t seq_len, size_t d_head, const uint32_t* table_out, size_t n_table, int32_t on_device,
+                                uint32_t* attn_out, uint8_t* out, size_t cap, size_t* len);
 
 /* ---- weights in the reference's wire format, kept resident ----
  * zkb_weightset_preload takes the preload block of the reference's server mode (server.rs:33-94):
@@ -426,6 +448,7 @@ int32_t zkb_basefold_verify_opening(zkb_ctx* ctx, zkb_transcript* tr, const uint
  *               (the reference receives the requantised pairs from its Python driver; here
  *               requantize_to_i16_field and the table lookup run on the device)
  *   attention   seq_len = 1: output = V, PassThrough with the output hash absorbed            prove.rs:394-411
+ *               seq_len >= 2: zkb_oplist_add_attention, row proofs                              prove.rs:419-432
  *   save / add_saved / set_input / passthrough: SaveCommitment, Add, SegmentBoundary, PassThrough (prove.rs:439-489, 635-646)
  *   set_input_requant: set_input whose new activation is requantize_to_i16_field of the current one
  *               (stands in for the float re-quantisation the reference's Python driver does between segments). */
@@ -439,6 +462,12 @@ int32_t zkb_oplist_add_linear(zkb_oplist* list, const char* name, const uint32_t
 int32_t zkb_oplist_add_simple(zkb_oplist* list, int32_t kind, const char* name, const char* aux);
 int32_t zkb_oplist_add_layernorm(zkb_oplist* list, const char* name, const uint32_t* gamma, const uint32_t* beta, size_t d);
 int32_t zkb_oplist_add_gelu(zkb_oplist* list, const char* name, const uint32_t* table_out_dev, uint32_t n_table);
+/* "attention" at seq_len >= 2 (forward.rs:202-306, prove.rs:419-432): the activation is Q | K | V, each (num_heads, seq_len, d_head),
+ * or starts with Q when k_values and v_values (host, num_heads * seq_len * d_head words each; both or neither) are given, as the
+ * reference takes them from the request.  table_out_dev: the exp table's output column on the device (build_exp_table(exp_scale));
+ * it must stay valid while the list lives.  The proof is SerializedLayerProof::Attention(RowAttentionProof), see zkb_prove_row_attention. */
+int32_t zkb_oplist_add_attention(zkb_oplist* list, const char* name, size_t num_heads, size_t seq_len, size_t d_head,
+                                 const uint32_t* table_out_dev, uint32_t n_table, const uint32_t* k_values, const uint32_t* v_values);
 int32_t zkb_oplist_add_set_input(zkb_oplist* list, const char* name, const uint32_t* values, size_t n);
 uint32_t zkb_oplist_output_len(const zkb_oplist* list);
 /* forward pass only (x: input_len host words); zkb_oplist_activation then reads the activation after op `op_index`. */

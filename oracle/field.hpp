@@ -133,15 +133,17 @@ using VEF = std::vector<EF>;
 // (pcs.rs:158-190).  Here a plain thread count, set by whoever times the oracle (1 = serial, the
 // default).  Results do not depend on it.
 inline int& matrix_threads() { static int n = 1; return n; }
+inline bool& par_nested() { static thread_local bool n = false; return n; }
 template <class Fn>
 inline void par_rows(size_t rows, Fn fn) {          // fn(lo, hi, worker)
+    bool& nested = par_nested();                    // a worker's own par_rows calls run in that worker
     const int T = matrix_threads();
-    if (T <= 1 || rows < 64) { fn(size_t(0), rows, 0); return; }
+    if (T <= 1 || rows < 64 || nested) { fn(size_t(0), rows, 0); return; }
     std::vector<std::thread> th;
     const size_t per = (rows + T - 1) / T;
     for (int t = 0; t < T; t++) {
         size_t lo = size_t(t) * per, hi = lo + per < rows ? lo + per : rows;
-        if (lo < hi) th.emplace_back(fn, lo, hi, t);
+        if (lo < hi) th.emplace_back([&fn, lo, hi, t] { par_nested() = true; fn(lo, hi, t); });
     }
     for (auto& x : th) x.join();
 }

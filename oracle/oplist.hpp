@@ -10,6 +10,7 @@
 // Ops: linear (with bias), relu, layernorm, gelu (caller-supplied requantised pairs), attention at
 // seq_len = 1 (pass-through), save, add_saved, set_input, passthrough.
 #pragma once
+#include "attention.hpp"
 #include "qwen_verify.hpp"
 #include <map>
 
@@ -226,6 +227,8 @@ struct Op {
     std::vector<uint32_t> table_out;   // gelu: output column of the 65536- (or 256-) entry table
     std::string save_name, add_name;
     VF new_input;               // set_input
+    size_t heads = 0, seq = 0, d_head = 0;   // attention_rows (seq_len >= 2): table_out = the exp table, att_k / att_v when given by the request
+    VF att_k, att_v;
 };
 struct LayerData {
     std::string type, name;
@@ -233,6 +236,7 @@ struct LayerData {
     VF input, output;           // activation before / after the op
     VF pre_relu;
     LnForward ln; VF ln_x;
+    VF att_q, att_k, att_v;
 };
 inline std::array<uint8_t, 32> hash_values(const VF& v) {     // common.rs:78-85
     std::vector<uint8_t> buf;
@@ -270,6 +274,15 @@ inline std::vector<LayerData> oplist_forward(const std::vector<Op>& ops, const V
         } else if (op.type == "attention") {                   // seq_len = 1: softmax of one score is 1, the output is V
             size_t third = cur.size() / 3;
             cur = VF(cur.begin() + 2 * third, cur.end());
+        } else if (op.type == "attention_rows") {              // forward.rs:202-306 at seq_len >= 2
+            size_t total = op.heads * op.seq * op.d_head;
+            if (op.att_k.empty() ? cur.size() != 3 * total : cur.size() < total) throw std::runtime_error("attention: activation length");
+            L.att_q = VF(cur.begin(), cur.begin() + total);
+            L.att_k = op.att_k.empty() ? VF(cur.begin() + total, cur.begin() + 2 * total) : op.att_k;
+            L.att_v = op.att_k.empty() ? VF(cur.begin() + 2 * total, cur.begin() + 3 * total) : op.att_v;
+            bool ok = true;
+            cur = row_attention_forward(L.att_q, L.att_k, L.att_v, op.heads, op.seq, op.d_head, table_from_outputs(op.table_out), &ok);
+            if (!ok) throw std::runtime_error("attention: a score outside the exp table or a zero denominator");
         } else if (op.type == "save") {
             saved[op.save_name] = cur;
         } else if (op.type == "add_saved") {
@@ -347,6 +360,10 @@ inline std::vector<uint8_t> oplist_prove(const std::vector<LayerData>& layers) {
         } else if (L.type == "gelu") {
             LookupProof p = prove_lookup(table_from_outputs(op.table_out), op.gelu_in, op.gelu_out, tr);
             tag(4); body.put(p);
+        } else if (L.type == "attention_rows") {               // prove.rs:419-432
+            bool ok = true;
+            SeqAttentionProof p = prove_row_attention(L.att_q, L.att_k, L.att_v, op.heads, op.seq, op.d_head, table_from_outputs(op.table_out), tr, &ok);
+            tag(5); put(body, p);
         } else if (L.type == "attention" || L.type == "passthrough") {
             tr.absorb_bytes(hash_values(L.output));
             tag(16);

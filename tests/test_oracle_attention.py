@@ -1,0 +1,74 @@
+"""Row attention at seq_len >= 2: the CPU restatement against the reference's own tests
+(rust/zk_ml_prover/src/proving/attention.rs:651-870: prove -> verify round trips on the same shapes and
+inputs, tampered proofs rejected) and against an independent numpy forward pass."""
+import numpy as np
+import pytest
+
+from oracle import pyoracle as po
+from zklm_compile_b200 import tables
+
+P = (1 << 31) - 1
+
+
+def small_exp_table(scale=100):
+    """attention.rs:605-629: 256 entries, input raw as i8."""
+    x = np.arange(256, dtype=np.uint8).astype(np.int8).astype(np.float64) / scale
+    return tables.i16_to_field(tables.quantize_i16(np.exp(x), float(scale)))
+
+
+def make_qkv(nh, s, d, mq=3, mk=2, mv=4):
+    """attention.rs:632-649"""
+    n = nh * s * d
+    i = np.arange(n)
+    return ((i % mq) + 1).astype(np.uint32), ((i % mk) + 1).astype(np.uint32), ((i % mv) + 1).astype(np.uint32)
+
+
+def numpy_forward(q, k, v, nh, s, d, table):
+    n_table = table.size
+    q = q.reshape(nh, s, d).astype(object); k = k.reshape(nh, s, d).astype(object); v = v.reshape(nh, s, d).astype(object)
+    out = np.zeros((nh, s, d), dtype=np.uint32)
+    for h in range(nh):
+        for i in range(s):
+            sc = [int(sum(k[h, j, l] * q[h, i, l] for l in range(d)) % P) for j in range(s)]
+            e = [int(table[x if x < n_table // 2 else x + n_table - P]) for x in sc]
+            inv = pow(sum(e) % P, P - 2, P)
+            y = [ei * inv % P for ei in e]
+            for c in range(d):
+                out[h, i, c] = sum(y[l] * int(v[h, l, c]) for l in range(s)) % P
+    return out.reshape(-1)
+
+
+@pytest.mark.parametrize("nh,s,d,mods", [(2, 4, 4, (3, 2, 4)), (4, 16, 8, (2, 2, 3)), (1, 64, 16, (1, 1, 3)), (3, 5, 3, (2, 2, 5))])
+def test_round_trip_on_the_reference_test_shapes(nh, s, d, mods):
+    t = small_exp_table()
+    q, k, v = make_qkv(nh, s, d, *mods)
+    assert po.row_attention_roundtrip(q, k, v, nh, s, d, t) == 1
+    for tamper in (1, 2, 3, 4):
+        assert po.row_attention_roundtrip(q, k, v, nh, s, d, t, tamper) == 0, tamper
+
+
+def test_forward_matches_numpy_and_the_proof_carries_it():
+    nh, s, d = 2, 6, 4
+    t = tables.build_exp_table(100)
+    rng = np.random.default_rng(5)
+    q = rng.integers(0, 7, nh * s * d).astype(np.uint32)
+    k = np.mod(rng.integers(-6, 7, nh * s * d), P).astype(np.uint32)     # negative scores reach the table's upper half
+    v = rng.integers(0, P, nh * s * d).astype(np.uint32)
+    out, st = po.row_attention_forward(q, k, v, nh, s, d, t)
+    assert st == 0
+    assert np.array_equal(out, numpy_forward(q, k, v, nh, s, d, t))
+    proof, st = po.prove_row_attention(po.Transcript(b"x"), q, k, v, nh, s, d, t)
+    assert st == 0
+    # every row's output words appear in the proof, in order
+    for r in range(nh * s):
+        assert out[r * d:(r + 1) * d].astype("<u4").tobytes() in proof
+    assert po.row_attention_roundtrip(q, k, v, nh, s, d, t) == 1
+
+
+def test_score_outside_the_table_is_reported():
+    t = small_exp_table()
+    q = np.full(8, 20, np.uint32); k = np.full(8, 20, np.uint32); v = np.ones(8, np.uint32)   # score 800 > 127
+    _, st = po.row_attention_forward(q, k, v, 1, 2, 4, t)
+    assert st == 8
+    proof, st = po.prove_row_attention(po.Transcript(b"x"), q, k, v, 1, 2, 4, t)
+    assert st == 8 and proof == b""

@@ -64,6 +64,12 @@ void ol_forward(OL* L) {
                 pad_copy_kernel<<<grid_for(c, n_pad), 256, 0, c->stream>>>(in + 2 * (size_t)op.out_len, op.out_len, n_pad, op.out);
                 ZKB_LAUNCHED(c);
                 break;
+            case OL::ATTENTION_ROWS: {
+                const size_t total = (size_t)op.heads * op.seq * op.d_head;
+                attention_forward_enqueue(c, in, op.aux0 ? op.aux0 : in + total, op.aux1 ? op.aux1 : in + 2 * total, op.heads, op.seq, op.d_head,
+                                          op.table, op.n_table, op.out);
+                break;
+            }
             case OL::ADD_SAVED:
                 add_vec_kernel<<<grid_for(c, n_pad), 256, 0, c->stream>>>(in, L->ops[op.save_of].out, op.out_len, n_pad, op.out);
                 ZKB_LAUNCHED(c);
@@ -87,6 +93,7 @@ struct OlProofRec {
     MatmulRec mm; ReluRec relu; LayerNormRec ln; LookupRec lk;
     size_t lk_io = 0;         // record offset of the lookup's inputs and outputs (2 n words)
     size_t h0 = 0, h1 = 0;    // record offsets of digests (8 words each)
+    AttRun att; zkb::u32 att_heads = 0; size_t att_host = 0;   // attention at seq_len >= 2: word offset of its records in the staging buffer
     bool h0_zero = false;
     std::string text;
 };
@@ -140,6 +147,12 @@ std::vector<uint8_t> ol_prove(OL* L, uint32_t* status_out) {
     ZKB_LAUNCHED(c);
     { ScriptBuilder sb; sb.str("structured-ml-proof"); sb.run(c, tr); }
     ol_hash_all(L);
+    // the attention ops' row records come back through one page-locked buffer, sized before anything is enqueued
+    size_t att_words = 0;
+    for (const OL::Op& op : L->ops)
+        if (op.kind == OL::ATTENTION_ROWS) att_words += (size_t)op.heads * op.seq * (att_layout(op.seq, op.d_head).words + op.seq + op.d_head);
+    zkb::u32* att_stage = att_words ? (zkb::u32*)c->stage_host(att_words * 4) : nullptr;
+    size_t att_used = 0;
     std::vector<OlProofRec> recs;
     const zkb::u32* chain_point = nullptr;        // s_point of the last pushed proof when that proof is a matmul
     for (size_t idx = L->ops.size(); idx-- > 0;) {
@@ -179,6 +192,16 @@ std::vector<uint8_t> ol_prove(OL* L, uint32_t* status_out) {
                 ScriptBuilder sb;
                 sb.words_dev(c->rec_dev + R.h0, 8);
                 sb.run(c, tr);
+                break;
+            }
+            case OL::ATTENTION_ROWS: {
+                R.tag = 5;
+                const size_t total = (size_t)op.heads * op.seq * op.d_head;
+                const size_t rec_words = (size_t)op.heads * op.seq * att_layout(op.seq, op.d_head).words;
+                R.att_host = att_used; R.att_heads = op.heads;
+                R.att = attention_prove_enqueue(c, tr, in, op.aux0 ? op.aux0 : in + total, op.aux1 ? op.aux1 : in + 2 * total, op.heads, op.seq,
+                                                op.d_head, op.table, op.n_table, nullptr, att_stage + att_used, att_stage + att_used + rec_words);
+                att_used += rec_words + (size_t)op.heads * op.seq * (op.seq + op.d_head);
                 break;
             }
             case OL::ADD_SAVED: {
@@ -231,6 +254,17 @@ std::vector<uint8_t> ol_prove(OL* L, uint32_t* status_out) {
             case 1: put_relu(s, R.relu); break;
             case 3: put_layernorm_sqr(s, R.ln); break;
             case 4: put_lookup_base(s, R.lk, s.rec + R.lk_io, s.rec + R.lk_io + R.lk.n); break;
+            case 5: {
+                const zkb::u32* hrec = att_stage + R.att_host;
+                const zkb::u32* hbind = hrec + (size_t)R.att.rows * R.att.L.words;
+                AttSer count{nullptr};
+                count.proof(R.att.L, R.att_heads, hrec, hbind);
+                const size_t at = s.b.size();
+                s.b.resize(at + count.n);
+                AttSer w{s.b.data() + at};
+                w.proof(R.att.L, R.att_heads, hrec, hbind);
+                break;
+            }
             case 6: s.u64le(R.text.size()); for (char ch : R.text) s.u8((uint8_t)ch); break;
             case 7:
                 if (R.h0_zero) for (int i = 0; i < 8; i++) s.u32le(0); else s.words(R.h0, 8);
@@ -368,6 +402,25 @@ int32_t zkb_oplist_add_gelu(zkb_oplist* L, const char* name, const uint32_t* tab
         OL::Op& op = ol_push(L, OL::GELU, name, L->cur_len, true);
         op.table = table_out_dev; op.n_table = n_table;
         op.aux0 = ol_alloc(L, pad_pow2(op.out_len));
+        txn.done = true;
+    });
+}
+int32_t zkb_oplist_add_attention(zkb_oplist* L, const char* name, size_t num_heads, size_t seq_len, size_t d_head, const uint32_t* table_out_dev,
+                                 uint32_t n_table, const uint32_t* k_values, const uint32_t* v_values) {
+    if (!L || !table_out_dev || (k_values == nullptr) != (v_values == nullptr)) return ZKB_E_ARG;
+    zkb_ctx* c = L->ctx;
+    ZKB_TRY(c, {
+        c->use();
+        att_check_dims(num_heads, seq_len, d_head, n_table);
+        if (seq_len < 2) throw ArgFail{ZKB_E_ARG, "attention: seq_len = 1 is ZKB_OP_ATTENTION_SEQ1"};
+        const size_t total = num_heads * seq_len * d_head;
+        if (k_values ? L->cur_len < total : L->cur_len != 3 * total)
+            throw ArgFail{ZKB_E_LENGTH, "attention: the activation is not Q | K | V of (num_heads, seq_len, d_head) (or Q alone when K and V are given)"};
+        OlTxn txn(L);
+        OL::Op& op = ol_push(L, OL::ATTENTION_ROWS, name, (u32)total, true);
+        op.heads = (u32)num_heads; op.seq = (u32)seq_len; op.d_head = (u32)d_head;
+        op.table = table_out_dev; op.n_table = n_table;
+        if (k_values) { op.aux0 = ol_upload(L, k_values, total, total); op.aux1 = ol_upload(L, v_values, total, total); }
         txn.done = true;
     });
 }

@@ -25,6 +25,7 @@ int32_t status_to_code(zkb_ctx* c, uint32_t st) {
         case ST_ALPHA_COLLISION: c->err = "alpha collision with lookup encoding"; return ZKB_E_ALPHA_COLLISION;
         case ST_NOT_QR: c->err = "rmsnorm_forward: could not find QR perturbation in 200 attempts"; return ZKB_E_NOT_QR;
         case ST_LOOKUP_KEY: c->err = "lookup_fast: key not found"; return ZKB_E_ARG;
+        case ST_ATT_ZERO_SUM: c->err = "attention: the softmax denominator is zero"; return ZKB_E_ARG;
         case ST_COPY_TIMEOUT: c->err = "forward matvec: a bulk copy into shared memory did not complete within its wait limit"; return ZKB_E_CUDA;
     }
     c->err = "device status " + std::to_string(st);

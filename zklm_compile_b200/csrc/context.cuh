@@ -142,11 +142,24 @@ struct zkb_ctx {
     // Tuning options (zkb_ctx_set_option): 0 = the built-in choice.
     int opt_single_threads = 0, opt_pipe_threads = 0, opt_fold2_vec = 0;
     bool opt_plain_tail = false, opt_no_fused2 = false, opt_bf_in_order = false;
+    int opt_att_threads = 0;             // threads per row CTA of the attention kernels (0: chosen from the shape)
     int opt_shared_sm = 0;               // 0: hash-chain kernels reserve 200 KB of shared memory, 1: none, 16 .. 200: that many KB
     bool opt_mv_ring = false;            // forward matvec: the bulk-copy ring kernel instead of the register-staged one
     int opt_mv_prefetch = 2;             // rows per CTA whose lines a forward matvec prefetches into L2 before it waits for its input (0 .. 8 measured: 2 is best)
     // Second stream for work that does not depend on the transcript (the fold / tree chain of a Basefold
     // opening), joined to `stream` through events; created on first use.
+    // Page-locked staging for results that are larger than the record buffer; grows, freed with the context.
+    void* stage = nullptr;
+    size_t stage_cap = 0;
+    void* stage_host(size_t bytes) {
+        if (bytes > stage_cap) {
+            if (stage) { ZKB_CUDA(cudaStreamSynchronize(stream)); cudaFreeHost(stage); stage = nullptr; stage_cap = 0; }
+            size_t cap = bytes + (bytes >> 2);
+            ZKB_CUDA(cudaHostAlloc(&stage, cap, cudaHostAllocDefault));
+            stage_cap = cap;
+        }
+        return stage;
+    }
     cudaStream_t side = nullptr;
     std::vector<cudaEvent_t> side_ev;
     cudaStream_t side_stream() {

@@ -3,6 +3,7 @@
 #include "oplist.cuh"
 #include "basefold.cuh"
 #include "verify.cuh"
+#include "attention.cuh"
 #include "verify_layer.cuh"
 #include <cstdlib>
 #include <cstring>
@@ -85,6 +86,7 @@ void zkb_ctx_destroy(zkb_ctx* c) {
     if (c->t1) cudaEventDestroy(c->t1);
     for (cudaEvent_t e : c->side_ev) cudaEventDestroy(e);
     if (c->side) cudaStreamDestroy(c->side);
+    if (c->stage) cudaFreeHost(c->stage);
     if (c->stream) cudaStreamDestroy(c->stream);
     delete c;
 }
@@ -368,6 +370,10 @@ int32_t zkb_ctx_set_option(zkb_ctx* c, int32_t option, int32_t value) {
             if (value != 0 && value != 1 && (value < 16 || value > 200)) return ZKB_E_ARG;
             c->opt_shared_sm = (int)value;
             break;
+        case ZKB_OPT_ATTENTION_THREADS:
+            if (value != 0 && value != 64 && value != 128 && value != 256) return ZKB_E_ARG;
+            c->opt_att_threads = (int)value;
+            break;
         case ZKB_OPT_MATVEC_PREFETCH_ROWS:
             if (value < 0 || value > 8) return ZKB_E_ARG;
             c->opt_mv_prefetch = (int)value;
@@ -433,6 +439,7 @@ int32_t zkb_sumcheck_prove(zkb_ctx* c, zkb_transcript* t, int32_t kind, const ui
 #include "abi_split.cuh"
 #include "abi_oplist.cuh"
 #include "abi_weights.cuh"
+#include "abi_attention.cuh"
 
 // =============================================================================================
 // Allocation-free weight fold

@@ -74,7 +74,7 @@ class Context:
         fn.argtypes = [C.c_void_p]
         return int(fn(self.h))
 
-    OPT_PLAIN_TAIL, OPT_SINGLE_CTA_THREADS, OPT_PIPE_THREADS, OPT_NO_FUSED_FOLD, OPT_FOLD2_VEC, OPT_BASEFOLD_IN_ORDER, OPT_MATVEC_PREFETCH_ROWS, OPT_MATVEC_RING, OPT_SHARED_SM_HASH = 0, 1, 2, 3, 4, 5, 6, 7, 8
+    OPT_PLAIN_TAIL, OPT_SINGLE_CTA_THREADS, OPT_PIPE_THREADS, OPT_NO_FUSED_FOLD, OPT_FOLD2_VEC, OPT_BASEFOLD_IN_ORDER, OPT_MATVEC_PREFETCH_ROWS, OPT_MATVEC_RING, OPT_SHARED_SM_HASH, OPT_ATTENTION_THREADS = 0, 1, 2, 3, 4, 5, 6, 7, 8, 9
 
     def set_option(self, option: int, value: int):
         """Tuning options for measurements (zkb_ctx_set_option in include/zkb200.h); 0 = built-in choice."""
