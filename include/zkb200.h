@@ -165,6 +165,15 @@ int32_t zkb_row_attention_forward(zkb_ctx* ctx, const uint32_t* q, const uint32_
 int32_t zkb_prove_row_attention(zkb_ctx* ctx, zkb_transcript* tr, const uint32_t* q, const uint32_t* k, const uint32_t* v, size_t num_heads,
                                 size_t seq_len, size_t d_head, const uint32_t* table_out, size_t n_table, int32_t on_device,
                                 uint32_t* attn_out, uint8_t* out, size_t cap, size_t* len);
+/* Grouped-query form, prove_row_attention_gqa (attention.rs:386-500; the "gqa_attention" op, prove.rs:572-584, forward.rs:555-660):
+ * q has num_heads heads, k and v have num_kv_heads (a divisor of num_heads); query head h reads K/V head h / (num_heads / num_kv_heads);
+ * the rows' transcripts are labelled "gqa-h{h}-r{i}" and `tr` absorbs num_heads, num_kv_heads, seq_len, d_head.  num_kv_heads = 0 is
+ * the plain form above. */
+int32_t zkb_row_attention_gqa_forward(zkb_ctx* ctx, const uint32_t* q, const uint32_t* k, const uint32_t* v, size_t num_heads, size_t num_kv_heads,
+                                      size_t seq_len, size_t d_head, const uint32_t* table_out, size_t n_table, int32_t on_device, uint32_t* out);
+int32_t zkb_prove_row_attention_gqa(zkb_ctx* ctx, zkb_transcript* tr, const uint32_t* q, const uint32_t* k, const uint32_t* v, size_t num_heads,
+                                    size_t num_kv_heads, size_t seq_len, size_t d_head, const uint32_t* table_out, size_t n_table,
+                                    int32_t on_device, uint32_t* attn_out, uint8_t* out, size_t cap, size_t* len);
 
 /* ---- weights in the reference's wire format, kept resident ----
  * zkb_weightset_preload takes the preload block of the reference's server mode (server.rs:33-94):
@@ -465,8 +474,10 @@ int32_t zkb_oplist_add_gelu(zkb_oplist* list, const char* name, const uint32_t* 
 /* "attention" at seq_len >= 2 (forward.rs:202-306, prove.rs:419-432): the activation is Q | K | V, each (num_heads, seq_len, d_head),
  * or starts with Q when k_values and v_values (host, num_heads * seq_len * d_head words each; both or neither) are given, as the
  * reference takes them from the request.  table_out_dev: the exp table's output column on the device (build_exp_table(exp_scale));
- * it must stay valid while the list lives.  The proof is SerializedLayerProof::Attention(RowAttentionProof), see zkb_prove_row_attention. */
-int32_t zkb_oplist_add_attention(zkb_oplist* list, const char* name, size_t num_heads, size_t seq_len, size_t d_head,
+ * it must stay valid while the list lives.  The proof is SerializedLayerProof::Attention(RowAttentionProof), see zkb_prove_row_attention.
+ * num_kv_heads != 0: the "gqa_attention" op (forward.rs:555-660, prove.rs:572-584): the activation starts with Q (num_heads heads) | K | V
+ * (num_kv_heads heads each), the proof is SerializedLayerProof::GqaAttention. */
+int32_t zkb_oplist_add_attention(zkb_oplist* list, const char* name, size_t num_heads, size_t num_kv_heads, size_t seq_len, size_t d_head,
                                  const uint32_t* table_out_dev, uint32_t n_table, const uint32_t* k_values, const uint32_t* v_values);
 int32_t zkb_oplist_add_set_input(zkb_oplist* list, const char* name, const uint32_t* values, size_t n);
 uint32_t zkb_oplist_output_len(const zkb_oplist* list);

@@ -112,8 +112,8 @@ inline uint32_t exp_lookup(const LookupTable& t, F s, bool* ok) {
 }
 // One row of attention.rs:160-262: k_head, v_head are seq_len x d_head, q_row has d_head entries.
 inline RowProof prove_attention_row(size_t h, size_t i, const VF& k_head, const VF& v_head, const VF& q_row, size_t seq_len, size_t d_head,
-                                    const LookupTable& exp_table, bool* ok) {
-    Transcript tr("row-attn-h" + std::to_string(h) + "-r" + std::to_string(i));
+                                    const LookupTable& exp_table, bool* ok, const char* label = "row-attn-h") {
+    Transcript tr(label + std::to_string(h) + "-r" + std::to_string(i));
     VF scores(seq_len, F::zero());
     for (size_t j = 0; j < seq_len; j++) { F acc = F::zero(); for (size_t l = 0; l < d_head; l++) acc += k_head[j * d_head + l] * q_row[l]; scores[j] = acc; }
     RowProof rp;
@@ -137,8 +137,9 @@ inline RowProof prove_attention_row(size_t h, size_t i, const VF& k_head, const 
     return rp;
 }
 // One row of attention.rs:311-362
-inline bool verify_attention_row(const RowProof& rp, size_t h, size_t i, const VF& k_head, const VF& v_head, size_t seq_len, size_t d_head) {
-    Transcript tr("row-attn-h" + std::to_string(h) + "-r" + std::to_string(i));
+inline bool verify_attention_row(const RowProof& rp, size_t h, size_t i, const VF& k_head, const VF& v_head, size_t seq_len, size_t d_head,
+                                 const char* label = "row-attn-h") {
+    Transcript tr(label + std::to_string(h) + "-r" + std::to_string(i));
     VF scores, output;
     for (uint32_t v : rp.scores) scores.push_back(F(v));
     for (uint32_t v : rp.output) output.push_back(F(v));
@@ -157,21 +158,28 @@ struct SeqAttentionProof {
     std::vector<std::vector<RowProof>> row_proofs;
     size_t num_heads = 0, seq_len = 0, d_head = 0;
 };
+// num_kv_heads = 0: prove_row_attention.  Otherwise prove_row_attention_gqa (attention.rs:386-500): k, v have num_kv_heads heads, query
+// head h reads K/V head h / (num_heads / num_kv_heads), the rows' labels are "gqa-h{h}-r{i}" and num_kv_heads is absorbed as well.
 inline SeqAttentionProof prove_row_attention(const VF& q, const VF& k, const VF& v, size_t num_heads, size_t seq_len, size_t d_head,
-                                             const LookupTable& exp_table, Transcript& tr, bool* ok) {
+                                             const LookupTable& exp_table, Transcript& tr, bool* ok, size_t num_kv_heads = 0) {
     size_t hs = seq_len * d_head;
-    tr.absorb(uint32_t(num_heads)); tr.absorb(uint32_t(seq_len)); tr.absorb(uint32_t(d_head));
+    const size_t hpg = num_kv_heads ? num_heads / num_kv_heads : 1;
+    const char* label = num_kv_heads ? "gqa-h" : "row-attn-h";
+    tr.absorb(uint32_t(num_heads));
+    if (num_kv_heads) tr.absorb(uint32_t(num_kv_heads));
+    tr.absorb(uint32_t(seq_len)); tr.absorb(uint32_t(d_head));
     SeqAttentionProof P;
     P.num_heads = num_heads; P.seq_len = seq_len; P.d_head = d_head;
     P.row_proofs.resize(num_heads);
     for (size_t h = 0; h < num_heads; h++) {
-        VF kh(k.begin() + h * hs, k.begin() + (h + 1) * hs), vh(v.begin() + h * hs, v.begin() + (h + 1) * hs);
+        const size_t g = h / hpg;
+        VF kh(k.begin() + g * hs, k.begin() + (g + 1) * hs), vh(v.begin() + g * hs, v.begin() + (g + 1) * hs);
         P.row_proofs[h].resize(seq_len);
         par_rows(seq_len, [&](size_t lo, size_t hi, int) {
             for (size_t i = lo; i < hi; i++) {
                 VF qr(q.begin() + h * hs + i * d_head, q.begin() + h * hs + (i + 1) * d_head);
                 bool row_ok = true;
-                P.row_proofs[h][i] = prove_attention_row(h, i, kh, vh, qr, seq_len, d_head, exp_table, &row_ok);
+                P.row_proofs[h][i] = prove_attention_row(h, i, kh, vh, qr, seq_len, d_head, exp_table, &row_ok, label);
                 if (!row_ok) *ok = false;
             }
         });
@@ -179,36 +187,44 @@ inline SeqAttentionProof prove_row_attention(const VF& q, const VF& k, const VF&
     for (auto& hp : P.row_proofs) for (auto& rp : hp) { for (uint32_t x : rp.scores) tr.absorb(x); for (uint32_t x : rp.output) tr.absorb(x); }
     return P;
 }
-// attention.rs:279-385
-inline bool verify_row_attention(const SeqAttentionProof& P, const VF& k, const VF& v, Transcript& tr) {
+// attention.rs:279-385 (and :503-590 with num_kv_heads)
+inline bool verify_row_attention(const SeqAttentionProof& P, const VF& k, const VF& v, Transcript& tr, size_t num_kv_heads = 0) {
     size_t hs = P.seq_len * P.d_head;
-    tr.absorb(uint32_t(P.num_heads)); tr.absorb(uint32_t(P.seq_len)); tr.absorb(uint32_t(P.d_head));
+    const size_t hpg = num_kv_heads ? P.num_heads / num_kv_heads : 1;
+    const char* label = num_kv_heads ? "gqa-h" : "row-attn-h";
+    tr.absorb(uint32_t(P.num_heads));
+    if (num_kv_heads) tr.absorb(uint32_t(num_kv_heads));
+    tr.absorb(uint32_t(P.seq_len)); tr.absorb(uint32_t(P.d_head));
     if (P.row_proofs.size() != P.num_heads) return false;
     for (size_t h = 0; h < P.num_heads; h++) {
         if (P.row_proofs[h].size() != P.seq_len) return false;
-        VF kh(k.begin() + h * hs, k.begin() + (h + 1) * hs), vh(v.begin() + h * hs, v.begin() + (h + 1) * hs);
-        for (size_t i = 0; i < P.seq_len; i++) if (!verify_attention_row(P.row_proofs[h][i], h, i, kh, vh, P.seq_len, P.d_head)) return false;
+        const size_t g = h / hpg;
+        VF kh(k.begin() + g * hs, k.begin() + (g + 1) * hs), vh(v.begin() + g * hs, v.begin() + (g + 1) * hs);
+        for (size_t i = 0; i < P.seq_len; i++) if (!verify_attention_row(P.row_proofs[h][i], h, i, kh, vh, P.seq_len, P.d_head, label)) return false;
     }
     for (auto& hp : P.row_proofs) for (auto& rp : hp) { for (uint32_t x : rp.scores) tr.absorb(x); for (uint32_t x : rp.output) tr.absorb(x); }
     return true;
 }
 // The forward pass of the op (pipeline/forward.rs:233-276): out[h][i] = softmax_table(Q[h][i] K[h]^T) V[h].
-inline VF row_attention_forward(const VF& q, const VF& k, const VF& v, size_t num_heads, size_t seq_len, size_t d_head, const LookupTable& t, bool* ok) {
+inline VF row_attention_forward(const VF& q, const VF& k, const VF& v, size_t num_heads, size_t seq_len, size_t d_head, const LookupTable& t, bool* ok,
+                                size_t num_kv_heads = 0) {
     size_t hs = seq_len * d_head;
+    const size_t hpg = num_kv_heads ? num_heads / num_kv_heads : 1;
     VF out(num_heads * hs, F::zero());
     for (size_t h = 0; h < num_heads; h++) for (size_t i = 0; i < seq_len; i++) {
+        const size_t g = h / hpg;
         VF e(seq_len);
         F sum = F::zero();
         for (size_t j = 0; j < seq_len; j++) {
             F acc = F::zero();
-            for (size_t l = 0; l < d_head; l++) acc += k[h * hs + j * d_head + l] * q[h * hs + i * d_head + l];
+            for (size_t l = 0; l < d_head; l++) acc += k[g * hs + j * d_head + l] * q[h * hs + i * d_head + l];
             e[j] = F(exp_lookup(t, acc, ok)); sum += e[j];
         }
         if (sum == F::zero()) *ok = false;
         F inv_s = inverse(sum);
         for (size_t j = 0; j < d_head; j++) {
             F acc = F::zero();
-            for (size_t l = 0; l < seq_len; l++) acc += e[l] * inv_s * v[h * hs + l * d_head + j];
+            for (size_t l = 0; l < seq_len; l++) acc += e[l] * inv_s * v[g * hs + l * d_head + j];
             out[h * hs + i * d_head + j] = acc;
         }
     }

@@ -326,12 +326,13 @@ void zko_oplist_gelu(void* h, const char* name, const uint32_t* in, const uint32
     o.gelu_in = vf(in, n); o.gelu_out = vf(out, n);
     o.table_out.assign(table_out, table_out + n_table);
 }
-void zko_oplist_attention(void* h, const char* name, size_t heads, size_t seq, size_t d_head, const uint32_t* table_out, size_t n_table,
-                          const uint32_t* k, const uint32_t* v) {
+void zko_oplist_attention(void* h, const char* name, size_t heads, size_t kv_heads, size_t seq, size_t d_head, const uint32_t* table_out,
+                          size_t n_table, const uint32_t* k, const uint32_t* v) {
     Op& o = new_op(h, "attention_rows", name);
-    o.heads = heads; o.seq = seq; o.d_head = d_head;
+    o.heads = heads; o.kv_heads = kv_heads; o.seq = seq; o.d_head = d_head;
     o.table_out.assign(table_out, table_out + n_table);
-    if (k) { o.att_k = vf(k, heads * seq * d_head); o.att_v = vf(v, heads * seq * d_head); }
+    const size_t nkv = (kv_heads ? kv_heads : heads) * seq * d_head;
+    if (k) { o.att_k = vf(k, nkv); o.att_v = vf(v, nkv); }
 }
 void zko_oplist_set_input(void* h, const char* name, const uint32_t* v, size_t n) {
     Op& o = new_op(h, "set_input", name);
@@ -371,16 +372,17 @@ int zko_layernorm_sqr_roundtrip(const uint32_t* x, const uint32_t* gamma, const 
 // Worker threads of the row-parallel matrix loops (matmul.hpp); 1 = serial.
 void zko_set_threads(int n) { matrix_threads() = n < 1 ? 1 : n; }
 
-// ---- row attention, seq_len >= 2 (attention.rs:116-385).  q, k, v: (num_heads, seq_len, d_head) flat.
+// ---- row attention, seq_len >= 2 (attention.rs:116-385; with num_kv_heads != 0 the GQA form, :386-590).
+// q: (num_heads, seq_len, d_head); k, v: (num_kv_heads or num_heads, seq_len, d_head).
 // status: 0 ok, 8 a score outside the exp table's domain or a zero softmax denominator (the reference panics on either).
-size_t zko_prove_row_attention(void* t, const uint32_t* q, const uint32_t* k, const uint32_t* v, size_t num_heads, size_t seq_len, size_t d_head,
-                               const uint32_t* table_out, size_t n_table, uint8_t* out, size_t cap, int* status) {
-    size_t n = num_heads * seq_len * d_head;
+size_t zko_prove_row_attention(void* t, const uint32_t* q, const uint32_t* k, const uint32_t* v, size_t num_heads, size_t num_kv_heads, size_t seq_len,
+                               size_t d_head, const uint32_t* table_out, size_t n_table, uint8_t* out, size_t cap, int* status) {
+    size_t n = num_heads * seq_len * d_head, nkv = (num_kv_heads ? num_kv_heads : num_heads) * seq_len * d_head;
     bool ok = true;
     *status = 0;
     LookupTable tb = table_from_outputs(std::vector<uint32_t>(table_out, table_out + n_table));
     try {
-        SeqAttentionProof P = prove_row_attention(vf(q, n), vf(k, n), vf(v, n), num_heads, seq_len, d_head, tb, T(t), &ok);
+        SeqAttentionProof P = prove_row_attention(vf(q, n), vf(k, nkv), vf(v, nkv), num_heads, seq_len, d_head, tb, T(t), &ok, num_kv_heads);
         if (!ok) { *status = 8; return 0; }
         Bin b; put(b, P);
         return emit(b.b, out, cap);
@@ -389,29 +391,29 @@ size_t zko_prove_row_attention(void* t, const uint32_t* q, const uint32_t* k, co
         return 0;
     }
 }
-int zko_row_attention_forward(const uint32_t* q, const uint32_t* k, const uint32_t* v, size_t num_heads, size_t seq_len, size_t d_head,
-                              const uint32_t* table_out, size_t n_table, uint32_t* out) {
-    size_t n = num_heads * seq_len * d_head;
+int zko_row_attention_forward(const uint32_t* q, const uint32_t* k, const uint32_t* v, size_t num_heads, size_t num_kv_heads, size_t seq_len,
+                              size_t d_head, const uint32_t* table_out, size_t n_table, uint32_t* out) {
+    size_t n = num_heads * seq_len * d_head, nkv = (num_kv_heads ? num_kv_heads : num_heads) * seq_len * d_head;
     bool ok = true;
     LookupTable tb = table_from_outputs(std::vector<uint32_t>(table_out, table_out + n_table));
-    out_f(row_attention_forward(vf(q, n), vf(k, n), vf(v, n), num_heads, seq_len, d_head, tb, &ok), out);
+    out_f(row_attention_forward(vf(q, n), vf(k, nkv), vf(v, nkv), num_heads, seq_len, d_head, tb, &ok, num_kv_heads), out);
     return ok ? 0 : 8;
 }
 // prove -> verify on fresh transcripts; tamper: 1 a score, 2 an output word, 3 the softmax sum, 4 a y value's matmul final
-int zko_row_attention_roundtrip(const uint32_t* q, const uint32_t* k, const uint32_t* v, size_t num_heads, size_t seq_len, size_t d_head,
-                                const uint32_t* table_out, size_t n_table, int tamper) {
-    size_t n = num_heads * seq_len * d_head;
+int zko_row_attention_roundtrip(const uint32_t* q, const uint32_t* k, const uint32_t* v, size_t num_heads, size_t num_kv_heads, size_t seq_len,
+                                size_t d_head, const uint32_t* table_out, size_t n_table, int tamper) {
+    size_t n = num_heads * seq_len * d_head, nkv = (num_kv_heads ? num_kv_heads : num_heads) * seq_len * d_head;
     bool ok = true;
     LookupTable tb = table_from_outputs(std::vector<uint32_t>(table_out, table_out + n_table));
     Transcript pt("attn"), vt("attn");
-    SeqAttentionProof P = prove_row_attention(vf(q, n), vf(k, n), vf(v, n), num_heads, seq_len, d_head, tb, pt, &ok);
+    SeqAttentionProof P = prove_row_attention(vf(q, n), vf(k, nkv), vf(v, nkv), num_heads, seq_len, d_head, tb, pt, &ok, num_kv_heads);
     if (!ok) return -1;
     RowProof& rp = P.row_proofs[num_heads - 1][seq_len - 1];
     if (tamper == 1) rp.scores[0] ^= 1;
     if (tamper == 2) rp.output[0] ^= 1;
     if (tamper == 3) rp.softmax_proof.sum_value ^= 1;
     if (tamper == 4) rp.output_proof.x_at_s ^= 1;
-    bool good = verify_row_attention(P, vf(k, n), vf(v, n), vt);
+    bool good = verify_row_attention(P, vf(k, nkv), vf(v, nkv), vt, num_kv_heads);
     return good && pt.squeeze().v == vt.squeeze().v;
 }
 

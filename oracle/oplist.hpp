@@ -227,7 +227,7 @@ struct Op {
     std::vector<uint32_t> table_out;   // gelu: output column of the 65536- (or 256-) entry table
     std::string save_name, add_name;
     VF new_input;               // set_input
-    size_t heads = 0, seq = 0, d_head = 0;   // attention_rows (seq_len >= 2): table_out = the exp table, att_k / att_v when given by the request
+    size_t heads = 0, kv_heads = 0, seq = 0, d_head = 0;   // attention_rows (seq_len >= 2; kv_heads != 0: gqa_attention): table_out = the exp table, att_k / att_v when given by the request
     VF att_k, att_v;
 };
 struct LayerData {
@@ -274,14 +274,16 @@ inline std::vector<LayerData> oplist_forward(const std::vector<Op>& ops, const V
         } else if (op.type == "attention") {                   // seq_len = 1: softmax of one score is 1, the output is V
             size_t third = cur.size() / 3;
             cur = VF(cur.begin() + 2 * third, cur.end());
-        } else if (op.type == "attention_rows") {              // forward.rs:202-306 at seq_len >= 2
-            size_t total = op.heads * op.seq * op.d_head;
-            if (op.att_k.empty() ? cur.size() != 3 * total : cur.size() < total) throw std::runtime_error("attention: activation length");
+        } else if (op.type == "attention_rows") {              // forward.rs:202-306 (attention), :555-660 (gqa_attention) at seq_len >= 2
+            size_t total = op.heads * op.seq * op.d_head, total_kv = (op.kv_heads ? op.kv_heads : op.heads) * op.seq * op.d_head;
+            bool ext = !op.att_k.empty();
+            if (ext ? cur.size() < total : (op.kv_heads ? cur.size() < total + 2 * total_kv : cur.size() != 3 * total))
+                throw std::runtime_error("attention: activation length");
             L.att_q = VF(cur.begin(), cur.begin() + total);
-            L.att_k = op.att_k.empty() ? VF(cur.begin() + total, cur.begin() + 2 * total) : op.att_k;
-            L.att_v = op.att_k.empty() ? VF(cur.begin() + 2 * total, cur.begin() + 3 * total) : op.att_v;
+            L.att_k = ext ? op.att_k : VF(cur.begin() + total, cur.begin() + total + total_kv);
+            L.att_v = ext ? op.att_v : VF(cur.begin() + total + total_kv, cur.begin() + total + 2 * total_kv);
             bool ok = true;
-            cur = row_attention_forward(L.att_q, L.att_k, L.att_v, op.heads, op.seq, op.d_head, table_from_outputs(op.table_out), &ok);
+            cur = row_attention_forward(L.att_q, L.att_k, L.att_v, op.heads, op.seq, op.d_head, table_from_outputs(op.table_out), &ok, op.kv_heads);
             if (!ok) throw std::runtime_error("attention: a score outside the exp table or a zero denominator");
         } else if (op.type == "save") {
             saved[op.save_name] = cur;
@@ -362,8 +364,9 @@ inline std::vector<uint8_t> oplist_prove(const std::vector<LayerData>& layers) {
             tag(4); body.put(p);
         } else if (L.type == "attention_rows") {               // prove.rs:419-432
             bool ok = true;
-            SeqAttentionProof p = prove_row_attention(L.att_q, L.att_k, L.att_v, op.heads, op.seq, op.d_head, table_from_outputs(op.table_out), tr, &ok);
-            tag(5); put(body, p);
+            SeqAttentionProof p = prove_row_attention(L.att_q, L.att_k, L.att_v, op.heads, op.seq, op.d_head, table_from_outputs(op.table_out), tr, &ok,
+                                                      op.kv_heads);
+            tag(op.kv_heads ? 12 : 5); put(body, p);               // Attention / GqaAttention (prove.rs:419-432, 572-584)
         } else if (L.type == "attention" || L.type == "passthrough") {
             tr.absorb_bytes(hash_values(L.output));
             tag(16);

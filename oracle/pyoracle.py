@@ -455,13 +455,14 @@ class OpList:
         lib().zko_oplist_gelu(self.h, name.encode(), pi, po, C.c_size_t(I.size), pt, C.c_size_t(T.size))
         self.n_ops += 1
 
-    def attention(self, name, num_heads, seq_len, d_head, table_out, k_values=None, v_values=None):
+    def attention(self, name, num_heads, seq_len, d_head, table_out, k_values=None, v_values=None, num_kv_heads=0):
         """"attention" at seq_len >= 2: the activation is Q | K | V, or Q alone with K and V given here."""
         T, pt = _u32(table_out)
         pk = pv = None
         if k_values is not None:
             K, pk = _u32(k_values); V, pv = _u32(v_values)
-        lib().zko_oplist_attention(self.h, name.encode(), C.c_size_t(num_heads), C.c_size_t(seq_len), C.c_size_t(d_head), pt, C.c_size_t(T.size), pk, pv)
+        lib().zko_oplist_attention(self.h, name.encode(), C.c_size_t(num_heads), C.c_size_t(num_kv_heads), C.c_size_t(seq_len), C.c_size_t(d_head), pt,
+                                   C.c_size_t(T.size), pk, pv)
         self.n_ops += 1
 
     def set_input(self, name, values):
@@ -614,30 +615,31 @@ def prove_lookup(tr, table_out, inputs, outputs):
     return bytes(buf[:n]), st.value
 
 
-def prove_row_attention(tr, q, k, v, num_heads: int, seq_len: int, d_head: int, table_out):
-    """prove_row_attention (attention.rs:116-276) -> (bincode bytes of RowAttentionProof, status)."""
+def prove_row_attention(tr, q, k, v, num_heads: int, seq_len: int, d_head: int, table_out, num_kv_heads: int = 0):
+    """prove_row_attention (attention.rs:116-276), or prove_row_attention_gqa (:386-500) when num_kv_heads != 0
+    -> (bincode bytes of RowAttentionProof, status)."""
     Q, pq = _u32(q); K, pk = _u32(k); V, pv = _u32(v); T, pt = _u32(table_out)
     st = C.c_int(0)
     cap = (1 << 16) + num_heads * seq_len * (4 * (5 * seq_len + d_head) + 8192)
     buf = (C.c_uint8 * cap)()
     lib().zko_prove_row_attention.restype = C.c_size_t
-    n = lib().zko_prove_row_attention(tr.h, pq, pk, pv, C.c_size_t(num_heads), C.c_size_t(seq_len), C.c_size_t(d_head), pt, C.c_size_t(T.size),
+    n = lib().zko_prove_row_attention(tr.h, pq, pk, pv, C.c_size_t(num_heads), C.c_size_t(num_kv_heads), C.c_size_t(seq_len), C.c_size_t(d_head), pt, C.c_size_t(T.size),
                                       buf, C.c_size_t(cap), C.byref(st))
     return bytes(buf[:n]), st.value
 
 
-def row_attention_forward(q, k, v, num_heads: int, seq_len: int, d_head: int, table_out):
+def row_attention_forward(q, k, v, num_heads: int, seq_len: int, d_head: int, table_out, num_kv_heads: int = 0):
     """The attention op's forward pass at seq_len >= 2 (pipeline/forward.rs:233-276) -> (values, status)."""
     Q, pq = _u32(q); K, pk = _u32(k); V, pv = _u32(v); T, pt = _u32(table_out)
     out = np.zeros(Q.size, dtype=np.uint32)
-    st = lib().zko_row_attention_forward(pq, pk, pv, C.c_size_t(num_heads), C.c_size_t(seq_len), C.c_size_t(d_head), pt, C.c_size_t(T.size),
+    st = lib().zko_row_attention_forward(pq, pk, pv, C.c_size_t(num_heads), C.c_size_t(num_kv_heads), C.c_size_t(seq_len), C.c_size_t(d_head), pt, C.c_size_t(T.size),
                                          out.ctypes.data_as(C.POINTER(C.c_uint32)))
     return out, st
 
 
-def row_attention_roundtrip(q, k, v, num_heads: int, seq_len: int, d_head: int, table_out, tamper=0) -> int:
+def row_attention_roundtrip(q, k, v, num_heads: int, seq_len: int, d_head: int, table_out, tamper=0, num_kv_heads: int = 0) -> int:
     Q, pq = _u32(q); K, pk = _u32(k); V, pv = _u32(v); T, pt = _u32(table_out)
-    return int(lib().zko_row_attention_roundtrip(pq, pk, pv, C.c_size_t(num_heads), C.c_size_t(seq_len), C.c_size_t(d_head), pt, C.c_size_t(T.size),
+    return int(lib().zko_row_attention_roundtrip(pq, pk, pv, C.c_size_t(num_heads), C.c_size_t(num_kv_heads), C.c_size_t(seq_len), C.c_size_t(d_head), pt, C.c_size_t(T.size),
                                                  C.c_int(tamper)))
 
 

@@ -173,3 +173,46 @@ def test_oplist_attention_length_checks(ctx):
         g.attention("a", 2, 8, 4, dt, np.zeros(64, np.uint32), np.zeros(64, np.uint32))   # 50 < 64 words of Q
     g.attention("a", 2, 4, 2, dt, np.ones(16, np.uint32), np.ones(16, np.uint32))           # Q = the first 16 words
     g.close()
+
+
+# ---- grouped-query attention (attention.rs:386-500) -------------------------------------------------------------
+@pytest.mark.parametrize("nq,nkv,s,d", [(4, 2, 4, 4), (4, 1, 8, 4), (2, 2, 5, 3), (12, 4, 64, 16)])
+def test_gqa_proof_bytes_equal_the_oracle(ctx, nq, nkv, s, d):
+    rng = np.random.default_rng(nq * 100 + nkv * 10 + s)
+    t = tables.build_exp_table(100)
+    q = np.mod(rng.integers(-2, 3, nq * s * d), P).astype(np.uint32)
+    k = np.mod(rng.integers(-2, 3, nkv * s * d), P).astype(np.uint32)
+    v = rng.integers(0, P, nkv * s * d).astype(np.uint32)
+    tg = zk.Transcript(ctx, b"gqa")
+    got, out = za.prove_row_attention_gqa(q, k, v, nq, nkv, s, d, t, tg, want_output=True)
+    to = O.Transcript(b"gqa")
+    exp, st = O.prove_row_attention(to, q, k, v, nq, s, d, t, nkv)
+    assert st == 0 and got == exp and tg.squeeze() == to.squeeze()
+    fwd, st = O.row_attention_forward(q, k, v, nq, s, d, t, nkv)
+    assert np.array_equal(out, fwd)
+    assert np.array_equal(za.row_attention_forward(ctx, q, k, v, nq, s, d, t, nkv), fwd)
+
+
+def test_gqa_head_counts_must_divide(ctx):
+    t = tables.build_exp_table(100)
+    with pytest.raises(zk.ZkbError, match="divisible"):
+        za.row_attention_forward(ctx, np.ones(3 * 8, np.uint32), np.ones(2 * 8, np.uint32), np.ones(2 * 8, np.uint32), 3, 2, 4, t, 2)
+
+
+def test_oplist_with_gqa_attention(ctx):
+    from zklm_compile_b200 import oplist as zo
+    rng = np.random.default_rng(23)
+    nq, nkv, s, d, d_in = 4, 2, 4, 4, 20
+    tq, tkv = nq * s * d, nkv * s * d
+    t = tables.build_exp_table(100)
+    dt = ctx.upload(t)
+    x = rng.integers(0, 2, d_in).astype(np.uint32)
+    m1 = tq + 2 * tkv
+    w1 = _small_linear(rng, m1, d_in)
+    w2 = rng.integers(0, P, (7, tq)).astype(np.uint32)
+    g = zo.OpList(ctx, d_in); o = O.OpList()
+    g.linear("qkv", w1, None, m1, d_in); o.linear("qkv", w1, None, m1, d_in)
+    g.attention("gqa", nq, s, d, dt, num_kv_heads=nkv); o.attention("gqa", nq, s, d, t, num_kv_heads=nkv)
+    g.linear("o_proj", w2, None, 7, tq); o.linear("o_proj", w2, None, 7, tq)
+    assert g.prove(x) == o.prove(x)
+    g.close()

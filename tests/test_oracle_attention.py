@@ -72,3 +72,22 @@ def test_score_outside_the_table_is_reported():
     assert st == 8
     proof, st = po.prove_row_attention(po.Transcript(b"x"), q, k, v, 1, 2, 4, t)
     assert st == 8 and proof == b""
+
+
+def test_gqa_round_trips():
+    """attention.rs:737-820: 4 query heads over 2 KV heads, MQA (1 KV head), and GQA with equal head counts."""
+    t = small_exp_table()
+    s, d = 4, 4
+    for nq, nkv in [(4, 2), (4, 1), (2, 2)]:
+        i = np.arange(nq * s * d); j = np.arange(nkv * s * d)
+        q = ((i % 3) + 1).astype(np.uint32); k = ((j % 2) + 1).astype(np.uint32); v = ((j % 4) + 1).astype(np.uint32)
+        assert po.row_attention_roundtrip(q, k, v, nq, s, d, t, 0, nkv) == 1
+        for tamper in (1, 2, 3, 4):
+            assert po.row_attention_roundtrip(q, k, v, nq, s, d, t, tamper, nkv) == 0
+    # with equal head counts GQA computes what MHA computes (attention.rs:799-819); labels and the absorbed header differ
+    i = np.arange(2 * s * d)
+    q = ((i % 3) + 1).astype(np.uint32); k = ((i % 2) + 1).astype(np.uint32); v = ((i % 4) + 1).astype(np.uint32)
+    assert np.array_equal(po.row_attention_forward(q, k, v, 2, s, d, t, 2)[0], po.row_attention_forward(q, k, v, 2, s, d, t)[0])
+    a, _ = po.prove_row_attention(po.Transcript(b"x"), q, k, v, 2, s, d, t, 2)
+    b, _ = po.prove_row_attention(po.Transcript(b"x"), q, k, v, 2, s, d, t)
+    assert len(a) == len(b) and a != b

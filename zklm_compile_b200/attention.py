@@ -31,22 +31,24 @@ def _inputs(q, k, v, exp_table):
     return keep, [p for _, p, _ in keep], int(all(dev)), n_table
 
 
-def row_attention_forward(ctx: Context, q, k, v, num_heads: int, seq_len: int, d_head: int, exp_table) -> np.ndarray:
-    """out[h][i] = softmax_table(Q[h][i] K[h]^T) V[h] over M31 (forward.rs:233-276)."""
+def row_attention_forward(ctx: Context, q, k, v, num_heads: int, seq_len: int, d_head: int, exp_table, num_kv_heads: int = 0) -> np.ndarray:
+    """out[h][i] = softmax_table(Q[h][i] K[g]^T) V[g] over M31, g = h (forward.rs:233-276) or, with num_kv_heads,
+    g = h // (num_heads // num_kv_heads) (forward.rs:594-640)."""
     keep, ptrs, on_dev, n_table = _inputs(q, k, v, exp_table)
     n = num_heads * seq_len * d_head
     if on_dev:
         out = DeviceBuffer(ctx, n, (n,))
-        check(ctx.h, _lib.lib().zkb_row_attention_forward(ctx.h, *ptrs[:3], C.c_size_t(num_heads), C.c_size_t(seq_len), C.c_size_t(d_head),
-                                                          ptrs[3], C.c_size_t(n_table), C.c_int32(1), out.ptr))
+        check(ctx.h, _lib.lib().zkb_row_attention_gqa_forward(ctx.h, *ptrs[:3], C.c_size_t(num_heads), C.c_size_t(num_kv_heads), C.c_size_t(seq_len),
+                                                              C.c_size_t(d_head), ptrs[3], C.c_size_t(n_table), C.c_int32(1), out.ptr))
         return out
     out = np.zeros(n, np.uint32)
-    check(ctx.h, _lib.lib().zkb_row_attention_forward(ctx.h, *ptrs[:3], C.c_size_t(num_heads), C.c_size_t(seq_len), C.c_size_t(d_head),
-                                                      ptrs[3], C.c_size_t(n_table), C.c_int32(0), out.ctypes.data_as(u32p)))
+    check(ctx.h, _lib.lib().zkb_row_attention_gqa_forward(ctx.h, *ptrs[:3], C.c_size_t(num_heads), C.c_size_t(num_kv_heads), C.c_size_t(seq_len),
+                                                          C.c_size_t(d_head), ptrs[3], C.c_size_t(n_table), C.c_int32(0), out.ctypes.data_as(u32p)))
     return out
 
 
-def prove_row_attention(q, k, v, num_heads: int, seq_len: int, d_head: int, exp_table, transcript: Transcript, want_output: bool = False):
+def prove_row_attention(q, k, v, num_heads: int, seq_len: int, d_head: int, exp_table, transcript: Transcript, want_output: bool = False,
+                        num_kv_heads: int = 0):
     """attention.rs:116-276 -> bincode(RowAttentionProof) [, the op's output]."""
     ctx = transcript.ctx
     keep, ptrs, on_dev, n_table = _inputs(q, k, v, exp_table)
@@ -61,11 +63,17 @@ def prove_row_attention(q, k, v, num_heads: int, seq_len: int, d_head: int, exp_
     cap = proof_size_bound(num_heads, seq_len, d_head)
     buf = (C.c_uint8 * cap)()
     ln = C.c_size_t()
-    st = _lib.lib().zkb_prove_row_attention(ctx.h, transcript.h, *ptrs[:3], C.c_size_t(num_heads), C.c_size_t(seq_len), C.c_size_t(d_head),
-                                            ptrs[3], C.c_size_t(n_table), C.c_int32(on_dev), pout, buf, C.c_size_t(cap), C.byref(ln))
+    st = _lib.lib().zkb_prove_row_attention_gqa(ctx.h, transcript.h, *ptrs[:3], C.c_size_t(num_heads), C.c_size_t(num_kv_heads), C.c_size_t(seq_len),
+                                                C.c_size_t(d_head), ptrs[3], C.c_size_t(n_table), C.c_int32(on_dev), pout, buf, C.c_size_t(cap), C.byref(ln))
     check(ctx.h, st)
     proof = C.string_at(buf, ln.value)
     return (proof, out) if want_output else proof
+
+
+def prove_row_attention_gqa(q, k, v, num_q_heads: int, num_kv_heads: int, seq_len: int, d_head: int, exp_table, transcript: Transcript,
+                            want_output: bool = False):
+    """attention.rs:386-500, the reference's argument order."""
+    return prove_row_attention(q, k, v, num_q_heads, seq_len, d_head, exp_table, transcript, want_output, num_kv_heads)
 
 
 def proof_size_bound(num_heads: int, seq_len: int, d_head: int) -> int:

@@ -65,9 +65,9 @@ void ol_forward(OL* L) {
                 ZKB_LAUNCHED(c);
                 break;
             case OL::ATTENTION_ROWS: {
-                const size_t total = (size_t)op.heads * op.seq * op.d_head;
-                attention_forward_enqueue(c, in, op.aux0 ? op.aux0 : in + total, op.aux1 ? op.aux1 : in + 2 * total, op.heads, op.seq, op.d_head,
-                                          op.table, op.n_table, op.out);
+                const size_t total = (size_t)op.heads * op.seq * op.d_head, total_kv = (size_t)(op.kv_heads ? op.kv_heads : op.heads) * op.seq * op.d_head;
+                attention_forward_enqueue(c, in, op.aux0 ? op.aux0 : in + total, op.aux1 ? op.aux1 : in + total + total_kv, op.heads, op.kv_heads, op.seq,
+                                          op.d_head, op.table, op.n_table, op.out);
                 break;
             }
             case OL::ADD_SAVED:
@@ -195,12 +195,12 @@ std::vector<uint8_t> ol_prove(OL* L, uint32_t* status_out) {
                 break;
             }
             case OL::ATTENTION_ROWS: {
-                R.tag = 5;
-                const size_t total = (size_t)op.heads * op.seq * op.d_head;
+                R.tag = op.kv_heads ? 12 : 5;                          // Attention / GqaAttention (prove.rs:419-432, 572-584)
+                const size_t total = (size_t)op.heads * op.seq * op.d_head, total_kv = (size_t)(op.kv_heads ? op.kv_heads : op.heads) * op.seq * op.d_head;
                 const size_t rec_words = (size_t)op.heads * op.seq * att_layout(op.seq, op.d_head).words;
                 R.att_host = att_used; R.att_heads = op.heads;
-                R.att = attention_prove_enqueue(c, tr, in, op.aux0 ? op.aux0 : in + total, op.aux1 ? op.aux1 : in + 2 * total, op.heads, op.seq,
-                                                op.d_head, op.table, op.n_table, nullptr, att_stage + att_used, att_stage + att_used + rec_words);
+                R.att = attention_prove_enqueue(c, tr, in, op.aux0 ? op.aux0 : in + total, op.aux1 ? op.aux1 : in + total + total_kv, op.heads, op.kv_heads,
+                                                op.seq, op.d_head, op.table, op.n_table, nullptr, att_stage + att_used, att_stage + att_used + rec_words);
                 att_used += rec_words + (size_t)op.heads * op.seq * (op.seq + op.d_head);
                 break;
             }
@@ -254,7 +254,7 @@ std::vector<uint8_t> ol_prove(OL* L, uint32_t* status_out) {
             case 1: put_relu(s, R.relu); break;
             case 3: put_layernorm_sqr(s, R.ln); break;
             case 4: put_lookup_base(s, R.lk, s.rec + R.lk_io, s.rec + R.lk_io + R.lk.n); break;
-            case 5: {
+            case 5: case 12: {
                 const zkb::u32* hrec = att_stage + R.att_host;
                 const zkb::u32* hbind = hrec + (size_t)R.att.rows * R.att.L.words;
                 AttSer count{nullptr};
@@ -405,22 +405,24 @@ int32_t zkb_oplist_add_gelu(zkb_oplist* L, const char* name, const uint32_t* tab
         txn.done = true;
     });
 }
-int32_t zkb_oplist_add_attention(zkb_oplist* L, const char* name, size_t num_heads, size_t seq_len, size_t d_head, const uint32_t* table_out_dev,
-                                 uint32_t n_table, const uint32_t* k_values, const uint32_t* v_values) {
+int32_t zkb_oplist_add_attention(zkb_oplist* L, const char* name, size_t num_heads, size_t num_kv_heads, size_t seq_len, size_t d_head,
+                                 const uint32_t* table_out_dev, uint32_t n_table, const uint32_t* k_values, const uint32_t* v_values) {
     if (!L || !table_out_dev || (k_values == nullptr) != (v_values == nullptr)) return ZKB_E_ARG;
     zkb_ctx* c = L->ctx;
     ZKB_TRY(c, {
         c->use();
         att_check_dims(num_heads, seq_len, d_head, n_table);
         if (seq_len < 2) throw ArgFail{ZKB_E_ARG, "attention: seq_len = 1 is ZKB_OP_ATTENTION_SEQ1"};
-        const size_t total = num_heads * seq_len * d_head;
-        if (k_values ? L->cur_len < total : L->cur_len != 3 * total)
-            throw ArgFail{ZKB_E_LENGTH, "attention: the activation is not Q | K | V of (num_heads, seq_len, d_head) (or Q alone when K and V are given)"};
+        att_heads_per_group(num_heads, num_kv_heads);
+        const size_t total = num_heads * seq_len * d_head, total_kv = (num_kv_heads ? num_kv_heads : num_heads) * seq_len * d_head;
+        // "attention" asserts Q | K | V exactly (forward.rs:219-221); "gqa_attention" slices what it needs (forward.rs:564-574)
+        if (k_values ? L->cur_len < total : (num_kv_heads ? L->cur_len < total + 2 * total_kv : L->cur_len != 3 * total))
+            throw ArgFail{ZKB_E_LENGTH, "attention: the activation is not Q | K | V of (heads, seq_len, d_head) (or Q alone when K and V are given)"};
         OlTxn txn(L);
         OL::Op& op = ol_push(L, OL::ATTENTION_ROWS, name, (u32)total, true);
-        op.heads = (u32)num_heads; op.seq = (u32)seq_len; op.d_head = (u32)d_head;
+        op.heads = (u32)num_heads; op.kv_heads = (u32)num_kv_heads; op.seq = (u32)seq_len; op.d_head = (u32)d_head;
         op.table = table_out_dev; op.n_table = n_table;
-        if (k_values) { op.aux0 = ol_upload(L, k_values, total, total); op.aux1 = ol_upload(L, v_values, total, total); }
+        if (k_values) { op.aux0 = ol_upload(L, k_values, total_kv, total_kv); op.aux1 = ol_upload(L, v_values, total_kv, total_kv); }
         txn.done = true;
     });
 }

@@ -212,6 +212,8 @@ struct AttArgs {
     u32* rec;                                            // per row: L.words
     u32* status;
     int prove;                                           // 0: forward pass only
+    u32 hpg;                                             // query heads per K/V head (1 unless GQA)
+    int gqa;                                             // rows are labelled "gqa-h{h}-r{i}" (attention.rs:427) instead of "row-attn-h{h}-r{i}"
 };
 
 __global__ void __launch_bounds__(ATT_THREADS) attention_row_kernel(AttArgs A, AttLayout L, B3Prefix pre_w, B3Prefix pre_dig) {
@@ -237,8 +239,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_row_kernel(AttArgs A, A
     unsigned char* trbuf = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(misc + 64) + 15) & ~uintptr_t(15));
 
     const u32 row = blockIdx.x, h = row / S, i = row - h * S;
-    const u32* kh = A.k + (size_t)h * S * D;
-    const u32* vh = A.v + (size_t)h * S * D;
+    const u32* kh = A.k + (size_t)(h / A.hpg) * S * D;
+    const u32* vh = A.v + (size_t)(h / A.hpg) * S * D;
     const u32* qrow = A.q + ((size_t)h * S + i) * D;
     u32* rec = A.rec ? A.rec + (size_t)row * L.words : nullptr;
     u32* bind = A.bind ? A.bind + (size_t)row * (S + D) : nullptr;
@@ -288,8 +290,9 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_row_kernel(AttArgs A, A
     if (tid == 0) {
         tr_iv(tr.h);
         tr.buflen = 0; tr.total = 0; tr.buf = trbuf;
-        const char lab[] = "row-attn-h";
-        for (int b = 0; b < 10; b++) tr_absorb_byte(tr, (unsigned char)lab[b]);
+        const char lab[] = "row-attn-h", lab_gqa[] = "gqa-h";
+        if (A.gqa) { for (int b = 0; b < 5; b++) tr_absorb_byte(tr, (unsigned char)lab_gqa[b]); }
+        else { for (int b = 0; b < 10; b++) tr_absorb_byte(tr, (unsigned char)lab[b]); }
         att_absorb_decimal(tr, h);
         tr_absorb_byte(tr, '-'); tr_absorb_byte(tr, 'r');
         att_absorb_decimal(tr, i);
@@ -439,16 +442,22 @@ inline void att_launch(zkb_ctx* c, cudaStream_t stream, const AttArgs& A, const 
     ZKB_LAUNCHED(c);
 }
 // The op's forward pass over all (head, row) pairs.  q, k, v, table_out, attn_out: device pointers.
-inline void attention_forward_enqueue(zkb_ctx* c, const u32* q, const u32* k, const u32* v, u32 num_heads, u32 S, u32 D,
+// num_kv_heads = 0: k, v have num_heads heads; otherwise grouped-query attention (k, v have num_kv_heads heads).
+inline u32 att_heads_per_group(size_t num_heads, size_t num_kv_heads) {
+    if (!num_kv_heads) return 1;
+    if (num_heads % num_kv_heads) throw ArgFail{ZKB_E_ARG, "attention: num_q_heads must be divisible by num_kv_heads"};
+    return (u32)(num_heads / num_kv_heads);
+}
+inline void attention_forward_enqueue(zkb_ctx* c, const u32* q, const u32* k, const u32* v, u32 num_heads, u32 num_kv_heads, u32 S, u32 D,
                                       const u32* table_out, u32 n_table, u32* attn_out) {
-    AttArgs A{q, k, v, table_out, n_table, attn_out, nullptr, nullptr, c->status, 0};
+    AttArgs A{q, k, v, table_out, n_table, attn_out, nullptr, nullptr, c->status, 0, att_heads_per_group(num_heads, num_kv_heads), num_kv_heads != 0};
     att_launch(c, c->stream, A, att_layout(S, D), num_heads * S);
 }
 // The whole proof: the forward pass writes the scores | outputs stream, after which the row proofs (every SM but
 // one, for milliseconds) and the caller's transcript absorbing that stream (one thread, one SM, one SHA-256 block
 // after the other) do not depend on each other, so the rows run on the context's second stream.
 // host_rec / host_bind: page-locked destinations of the records and of the scores | outputs stream.
-inline AttRun attention_prove_enqueue(zkb_ctx* c, TrState* tr, const u32* q, const u32* k, const u32* v, u32 num_heads, u32 S, u32 D,
+inline AttRun attention_prove_enqueue(zkb_ctx* c, TrState* tr, const u32* q, const u32* k, const u32* v, u32 num_heads, u32 num_kv_heads, u32 S, u32 D,
                                       const u32* table_out, u32 n_table, u32* attn_out, u32* host_rec, u32* host_bind) {
     AttRun R;
     R.L = att_layout(S, D);
@@ -456,7 +465,9 @@ inline AttRun attention_prove_enqueue(zkb_ctx* c, TrState* tr, const u32* q, con
     R.rec = (u32*)c->scratch((size_t)R.rows * R.L.words * 4);
     R.bind = (u32*)c->scratch((size_t)R.rows * (S + D) * 4);
     const bool in_order = c->opt_bf_in_order || c->capturing;
-    AttArgs F{q, k, v, table_out, n_table, attn_out, R.bind, nullptr, c->status, 0};
+    const u32 hpg = att_heads_per_group(num_heads, num_kv_heads);
+    const int gqa = num_kv_heads != 0;
+    AttArgs F{q, k, v, table_out, n_table, attn_out, R.bind, nullptr, c->status, 0, hpg, gqa};
     att_launch(c, c->stream, F, R.L, R.rows);
     ZKB_CUDA(cudaMemcpyAsync(host_bind, R.bind, (size_t)R.rows * (S + D) * 4, cudaMemcpyDeviceToHost, c->stream));
     cudaStream_t rows_stream = in_order ? c->stream : c->side_stream();
@@ -464,13 +475,15 @@ inline AttRun attention_prove_enqueue(zkb_ctx* c, TrState* tr, const u32* q, con
         ZKB_CUDA(cudaEventRecord(c->side_event(0), c->stream));
         ZKB_CUDA(cudaStreamWaitEvent(rows_stream, c->side_event(0), 0));
     }
-    AttArgs A{q, k, v, table_out, n_table, nullptr, nullptr, R.rec, c->status, 1};
+    AttArgs A{q, k, v, table_out, n_table, nullptr, nullptr, R.rec, c->status, 1, hpg, gqa};
     att_launch(c, rows_stream, A, R.L, R.rows);
     ZKB_CUDA(cudaMemcpyAsync(host_rec, R.rec, (size_t)R.rows * R.L.words * 4, cudaMemcpyDeviceToHost, rows_stream));
     if (!in_order) ZKB_CUDA(cudaEventRecord(c->side_event(1), rows_stream));
     {   // the dimensions, then every row's scores and outputs (attention.rs:140-143, 254-265)
         ScriptBuilder sb;
-        sb.word(num_heads); sb.word(S); sb.word(D);
+        sb.word(num_heads);
+        if (gqa) sb.word(num_kv_heads);                         // attention.rs:403-406
+        sb.word(S); sb.word(D);
         sb.words_dev(R.bind, (u32)((size_t)R.rows * (S + D)));
         sb.run(c, tr);
     }

@@ -345,7 +345,7 @@ struct zkb_oplist {
         zkb::u32* out = nullptr;               // activation after the op
         zkb::u32* aux0 = nullptr;              // relu: pre-activation; layernorm: xc; gelu: requantised input
         zkb::u32* aux1 = nullptr;              // layernorm: perturbed x
-        zkb::u32 heads = 0, seq = 0, d_head = 0;                    // attention at seq_len >= 2 (table = exp table; aux0 / aux1 = K / V when given by the caller)
+        zkb::u32 heads = 0, kv_heads = 0, seq = 0, d_head = 0;      // attention at seq_len >= 2, kv_heads != 0: gqa_attention (table = exp table; aux0 / aux1 = K / V when given by the caller)
         zkb::u32* scalars = nullptr;           // layernorm: {perturbation, mu, sum_sq, r}
         int save_of = -1;                      // add_saved: index of the matching save op
     };

@@ -67,14 +67,16 @@ class OpList:
         check(self.ctx.h, _lib.lib().zkb_oplist_add_gelu(self.h, name.encode(), table_out.ptr, C.c_uint32(table_out.n)))
         self.n_ops += 1
 
-    def attention(self, name: str, num_heads: int, seq_len: int, d_head: int, exp_table: DeviceBuffer, k_values=None, v_values=None):
-        """"attention" at seq_len >= 2 (pipeline/forward.rs:202-306): the activation is Q | K | V, or Q alone with K and V given here."""
+    def attention(self, name: str, num_heads: int, seq_len: int, d_head: int, exp_table: DeviceBuffer, k_values=None, v_values=None,
+                  num_kv_heads: int = 0):
+        """"attention" at seq_len >= 2 (pipeline/forward.rs:202-306): the activation is Q | K | V, or Q alone with K and V given here;
+        with num_kv_heads the "gqa_attention" op (forward.rs:555-660)."""
         self._keep.append(exp_table)
         pk = pv = None
         if k_values is not None:
             K, pk = _a(k_values); V, pv = _a(v_values)
-        check(self.ctx.h, _lib.lib().zkb_oplist_add_attention(self.h, name.encode(), C.c_size_t(num_heads), C.c_size_t(seq_len), C.c_size_t(d_head),
-                                                             exp_table.ptr, C.c_uint32(exp_table.n), pk, pv))
+        check(self.ctx.h, _lib.lib().zkb_oplist_add_attention(self.h, name.encode(), C.c_size_t(num_heads), C.c_size_t(num_kv_heads), C.c_size_t(seq_len),
+                                                             C.c_size_t(d_head), exp_table.ptr, C.c_uint32(exp_table.n), pk, pv))
         self.n_ops += 1
 
     def set_input(self, name: str, values):
