@@ -1033,7 +1033,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="qwen4b", choices=["qwen4b", "sumcheck", "qwen9b", "oplist"])
+    ap.add_argument("--workload", default="qwen4b", choices=["qwen4b", "sumcheck", "qwen9b", "oplist", "attention"])
     ap.add_argument("--chunk", type=int, default=8, help="qwen9b: layers proved at a time per GPU (contexts per GPU)")
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--n", "--log-n", dest="n", type=int, default=28, help="sumcheck workload: log2 of the table length")
@@ -1056,6 +1056,25 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     cores = os.cpu_count() or 1
     qwen = args.workload == "qwen4b"
+    if args.workload == "attention":
+        # row attention alone (one GPU: the rows of one call share the caller's transcript)
+        if rank == 0 and args.impl == "ours":
+            import zklm_compile_b200 as zk
+            ctx = zk.Context(local)
+            g = run_attention_leg(zk, ctx, not args.no_cpu, cores)
+            emit_line(json.dumps({"metric": "row-attention prove ms (12 heads x 128 positions x d_head 64, base-field challenges)",
+                              "value": g["prove_ms_device_inputs"], "unit": "ms", "n_gpus": 1, "steps": 5, "warmup": 3,
+                              "ms_per_step": g["prove_ms_device_inputs"], "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+                              "dtype": "u32 (M31)", "data": "synthetic", "config": {"workload": g["workload"]},
+                              "gpu_launches": g["gpu_launches_per_call"] * 5,
+                              "e2e": {"value": g["prove_ms_host_inputs"], "unit": "ms", "h2d_bytes_per_step": g["h2d_bytes"],
+                                      "d2h_bytes_per_step": g["proof_bytes"]},
+                              "cpu_baseline": ({"value": g["cpu_port_ms"], "unit": "ms", "cores": cores, "kind": "port",
+                                                "sample": "the same call, 2 runs"} if "cpu_port_ms" in g else None),
+                              "attention_rows_gpt2_head_shape": g}))
+        elif rank == 0:
+            emit_line(json.dumps({"impl": "reference", "unavailable": "the attention workload's CPU port time is part of the default arm's line (cpu_port_ms)"}))
+        return
     if args.workload == "oplist":
         # configs 1 and 3 alone (one GPU; an op list is one transcript, so more GPUs would be replicas): the legs that
         # the default line carries as dense4m_* and gpt2_124m_oplist, printed as a line of their own

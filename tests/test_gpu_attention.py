@@ -88,6 +88,24 @@ def test_longest_supported_row(ctx):
     assert hashlib.sha256(got).digest() == hashlib.sha256(exp).digest() and sg == so
 
 
+def test_threads_per_row_and_stream_order_do_not_change_the_bytes(ctx):
+    rng = np.random.default_rng(6)
+    t = tables.build_exp_table(100)
+    nh, s, d = 3, 40, 24
+    q, k, v = qkv(rng, nh, s, d, -1, 2)
+    exp, st = O.prove_row_attention(O.Transcript(b"opt"), q, k, v, nh, s, d, t)
+    try:
+        for threads, in_order in [(64, 0), (128, 0), (256, 0), (0, 1)]:
+            ctx.set_option(zk.Context.OPT_ATTENTION_THREADS, threads)
+            ctx.set_option(zk.Context.OPT_BASEFOLD_IN_ORDER, in_order)
+            assert za.prove_row_attention(q, k, v, nh, s, d, t, zk.Transcript(ctx, b"opt")) == exp, (threads, in_order)
+        with pytest.raises(zk.ZkbError):
+            ctx.set_option(zk.Context.OPT_ATTENTION_THREADS, 96)
+    finally:
+        ctx.set_option(zk.Context.OPT_ATTENTION_THREADS, 0)
+        ctx.set_option(zk.Context.OPT_BASEFOLD_IN_ORDER, 0)
+
+
 def test_device_resident_inputs(ctx):
     rng = np.random.default_rng(4)
     t = tables.build_exp_table(100)
