@@ -146,6 +146,27 @@ int32_t zkb_tr_squeeze_ef(zkb_transcript* tr, uint32_t out[4]);                 
 int32_t zkb_tr_export(zkb_transcript* tr, uint8_t state[ZKB_TR_STATE_BYTES]);
 int32_t zkb_tr_import(zkb_transcript* tr, const uint8_t state[ZKB_TR_STATE_BYTES]);
 
+/* ---- batch Basefold: k polynomials, possibly of different sizes, opened with one fold chain (basefold.rs:769-1590) ----
+ * zkb_basefold_batch_precommit = batch_precommit_multi_height (basefold.rs:1183-1216): polynomial i has n_coeffs[i] coefficients and
+ * the caller's log_ns[i] (n_coeffs[i] <= 2^log_ns[i]; ZKB_E_LENGTH otherwise).  All are encoded with the tables of the largest log_n and
+ * their Merkle trees built; codewords and trees stay in device memory until zkb_basefold_batch_destroy (the transcript-independent half,
+ * done once at load time).  on_device != 0: the coefficient pointers are device memory that must stay valid (they are read again for the
+ * final value); otherwise they are copied.  At most 4096 polynomials.
+ * zkb_basefold_batch_prove = batch_prove_with_precommit (basefold.rs:1221-1378): absorbs the roots (by size, descending; ties in input
+ * order), squeezes rho, builds the rho-weighted sum of the largest codewords, squeezes the whole fold point, and runs one fold chain in
+ * which smaller codewords join when the chain reaches their length, with the joined trees opened at that round's positions.
+ * individual_openings != 0 (all polynomials of one size, ZKB_E_ARG otherwise) also opens every tree at the final positions: the result is
+ * then batch_commit_and_prove (basefold.rs:801-956).  out = bincode(Vec<BasefoldCommitment>) in input order followed by
+ * bincode(BasefoldBatchProof); poly indices inside the proof are positions in the size-sorted order, as in the reference. */
+typedef struct zkb_bf_batch zkb_bf_batch;
+int32_t zkb_basefold_batch_precommit(zkb_ctx* ctx, const uint32_t* const* coeffs, const size_t* n_coeffs, const uint32_t* log_ns, size_t k,
+                                     int32_t on_device, int32_t node_hash, zkb_bf_batch** out);
+size_t zkb_basefold_batch_count(const zkb_bf_batch* batch);
+uint64_t zkb_basefold_batch_device_bytes(const zkb_bf_batch* batch);
+int32_t zkb_basefold_batch_commitment(const zkb_bf_batch* batch, size_t index, uint8_t root[16], uint64_t* num_coeffs, uint64_t* log_n);
+int32_t zkb_basefold_batch_prove(zkb_bf_batch* batch, zkb_transcript* tr, int32_t individual_openings, uint8_t* out, size_t cap, size_t* len);
+void zkb_basefold_batch_destroy(zkb_bf_batch* batch);
+
 /* ---- row-decomposed attention at seq_len >= 2 ----
  * prove_row_attention (proving/attention.rs:116-276), as the op-list prover calls it for an "attention" op
  * (pipeline/prove.rs:419-425), and the op's forward pass (pipeline/forward.rs:233-276).

@@ -7,7 +7,7 @@
 //                          final_value: u32, final_coeffs: Vec<u32> }                        basefold.rs:50-64
 //   FoldLevelQueries     { prev_batch_proof, folded_batch_proof }                            basefold.rs:73-81
 //   BatchMerkleProof     { indices: Vec<u32>, values: Vec<u32>, auth_nodes: Vec<Vec<[u8;16]>> }   pcs.rs:43-53
-#include "bincode.hpp"
+#include "basefold_batch.hpp"
 #include <cstring>
 
 using namespace zko;
@@ -130,5 +130,39 @@ int zko_basefold_verify_bytes(void* t, const uint8_t* b, size_t n, const uint32_
 
 // Process-wide stand-ins for the reference's cargo features and target architecture.
 void zko_set_features(int bind_mode, int node_kind) { features().bind_mode = bind_mode; features().node_kind = node_kind; }
+
+
+// ---- batch Basefold (basefold.rs:769-1590).  Polynomial i has n[i] coefficients at flat[off[i]...] and the caller's log_n[i].
+// bincode(Vec<BasefoldCommitment>) (input order) followed by bincode(BasefoldBatchProof).
+static std::vector<BatchPoly> batch_polys(const uint32_t* flat, const uint64_t* n, const uint64_t* log_n, size_t k) {
+    std::vector<BatchPoly> bp;
+    size_t off = 0;
+    for (size_t i = 0; i < k; i++) { bp.push_back({vf(flat + off, n[i]), size_t(log_n[i])}); off += n[i]; }
+    return bp;
+}
+size_t zko_basefold_batch_prove(void* t, const uint32_t* flat, const uint64_t* n, const uint64_t* log_n, size_t k, int individual_openings, int kind,
+                                uint8_t* out, size_t cap) {
+    BatchPrecommit pre = batch_precommit_multi_height(batch_polys(flat, n, log_n, k), kind);
+    BasefoldBatchProof P = batch_prove_with_precommit(pre, T(t), individual_openings != 0);
+    Bin b;
+    b.u64(pre.commitments.size());
+    for (auto& c : pre.commitments) b.put(c);
+    put(b, P);
+    return emit(b.b, out, cap);
+}
+// prove -> verify with fresh transcripts of one label.  tamper: 1 a fold root (basefold.rs:1889-1921), 2 an opened value of the first
+// round, 3 the batched root, 4 a value in an add-round opening (needs polynomials of different sizes), 5 an individual root.
+int zko_basefold_batch_roundtrip(const uint32_t* flat, const uint64_t* n, const uint64_t* log_n, size_t k, int individual_openings, int kind, int tamper) {
+    Transcript pt("batch"), vt("batch");
+    BatchPrecommit pre = batch_precommit_multi_height(batch_polys(flat, n, log_n, k), kind);
+    BasefoldBatchProof P = batch_prove_with_precommit(pre, pt, individual_openings != 0);
+    if (tamper == 1) P.fold_roots[0].fill(0xDE);
+    if (tamper == 2) P.fold_queries[0].prev_batch_proof.values[0] ^= 2;
+    if (tamper == 3) P.batched_root[3] ^= 1;
+    if (tamper == 4) { if (P.add_round_openings.empty()) return -1; P.add_round_openings[0].second[0].second.values[0] ^= 4; }
+    if (tamper == 5) P.roots[k - 1][0] ^= 1;
+    bool ok = batch_verify_opening(pre.commitments, P, vt, kind);
+    return ok && pt.squeeze().v == vt.squeeze().v;
+}
 
 }  // extern "C"

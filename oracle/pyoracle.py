@@ -615,6 +615,27 @@ def prove_lookup(tr, table_out, inputs, outputs):
     return bytes(buf[:n]), st.value
 
 
+def _batch_args(polys, log_ns):
+    flat = np.concatenate([np.ascontiguousarray(p, dtype=np.uint32).reshape(-1) for p in polys]) if polys else np.zeros(0, np.uint32)
+    n = np.array([np.asarray(p).size for p in polys], dtype=np.uint64)
+    ln = np.array(log_ns, dtype=np.uint64)
+    return flat, n, ln
+
+
+def basefold_batch_prove(tr, polys, log_ns, individual_openings=False, kind=0) -> bytes:
+    """batch_precommit_multi_height + batch_prove_with_precommit (basefold.rs:1183-1378; with individual_openings and equal sizes:
+    batch_commit_and_prove, :801-956) -> bincode(Vec<BasefoldCommitment>) || bincode(BasefoldBatchProof)."""
+    flat, n, ln = _batch_args(polys, log_ns)
+    return _bytes_call(lib().zko_basefold_batch_prove, tr.h, flat.ctypes.data_as(u32p), n.ctypes.data_as(C.POINTER(C.c_uint64)),
+                       ln.ctypes.data_as(C.POINTER(C.c_uint64)), C.c_size_t(len(polys)), C.c_int(int(individual_openings)), C.c_int(kind), cap=1 << 24)
+
+
+def basefold_batch_roundtrip(polys, log_ns, individual_openings=False, kind=0, tamper=0) -> int:
+    flat, n, ln = _batch_args(polys, log_ns)
+    return int(lib().zko_basefold_batch_roundtrip(flat.ctypes.data_as(u32p), n.ctypes.data_as(C.POINTER(C.c_uint64)), ln.ctypes.data_as(C.POINTER(C.c_uint64)),
+                                                  C.c_size_t(len(polys)), C.c_int(int(individual_openings)), C.c_int(kind), C.c_int(tamper)))
+
+
 def prove_row_attention(tr, q, k, v, num_heads: int, seq_len: int, d_head: int, table_out, num_kv_heads: int = 0):
     """prove_row_attention (attention.rs:116-276), or prove_row_attention_gqa (:386-500) when num_kv_heads != 0
     -> (bincode bytes of RowAttentionProof, status)."""

@@ -120,6 +120,9 @@ struct MkFold {
     size_t w_len, eval_half;
     // first round only: coefficients are read through a row-padded view of a matrix
     const u32* coef; u32 coef_rows, coef_cols, coef_log_cols_pad; int eval_from_coef;
+    // batch openings: values added to the folded codeword before it is stored and hashed (the already scaled sum of the
+    // codewords that join the chain at this length), or null
+    const u32* add;
 };
 
 __device__ __forceinline__ u32 coef_at(const u32* __restrict__ p, u32 rows, u32 cols, u32 log_cols_pad, size_t i) {
@@ -159,6 +162,7 @@ __global__ void __launch_bounds__(MK_THREADS) mk_tile_kernel(const u32* __restri
             Fp l{fold.prev[j]}, r{fold.prev[j + half]};
             Fp w{fold.weights[j & (fold.w_len - 1)]};
             Fp f = (l + r) * two_inv + alpha * ((l - r) * w);
+            if (fold.add) f = f + Fp{fold.add[j]};
             fold.out[j] = f.v;
             bufA[i] = make_uint4(f.v, 0, 0, 0);
             if (fold.eval_dst && j < fold.eval_half) {

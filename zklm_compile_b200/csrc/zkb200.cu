@@ -440,6 +440,7 @@ int32_t zkb_sumcheck_prove(zkb_ctx* c, zkb_transcript* t, int32_t kind, const ui
 #include "abi_oplist.cuh"
 #include "abi_weights.cuh"
 #include "abi_attention.cuh"
+#include "abi_pcs_batch.cuh"
 
 // =============================================================================================
 // Allocation-free weight fold

@@ -90,3 +90,56 @@ def basefold_verify_opening(ctx: Context, tr: Transcript, blob: bytes, point, cl
     check(ctx.h, _lib.lib().zkb_basefold_verify_opening(ctx.h, tr.h, buf, C.c_size_t(len(blob)), pp, C.c_uint32(pt.size),
                                                         C.c_uint32(int(claimed)), C.c_int32(node_hash), C.byref(ok)))
     return bool(ok.value)
+
+
+class BasefoldBatch:
+    """Batch Basefold over polynomials of possibly different sizes (basefold.rs:1144-1378).
+
+    Construction is `batch_precommit_multi_height`: every polynomial is encoded (with the largest one's tables) and its
+    Merkle tree built, both kept in device memory - the transcript-independent half, done once at load time.  `prove(tr)` is
+    `batch_prove_with_precommit`: one fold chain over the rho-weighted sum of the codewords, the smaller ones joining when the
+    chain reaches their length.  With `individual_openings` (equal sizes only) the result is `batch_commit_and_prove`
+    (basefold.rs:801-956).  Returns bincode(Vec<BasefoldCommitment>) (input order) || bincode(BasefoldBatchProof)."""
+
+    def __init__(self, ctx: Context, polys, log_ns, node_hash: int = NODE_BLAKE3):
+        self.ctx = ctx
+        self.h = C.c_void_p()
+        k = len(polys)
+        keep = [_src(p) for p in polys]
+        dev = [d for _, _, _, d in keep]
+        if any(dev) and not all(dev):
+            raise ValueError("the polynomials are either all DeviceBuffers or all host arrays")
+        self._keep = keep if all(dev) and k else None             # device polynomials are borrowed, not copied
+        ptrs = (u32p * max(k, 1))(*[p for _, p, _, _ in keep])
+        ns = (C.c_size_t * max(k, 1))(*[n for _, _, n, _ in keep])
+        lns = (C.c_uint32 * max(k, 1))(*[int(x) for x in log_ns])
+        check(ctx.h, _lib.lib().zkb_basefold_batch_precommit(ctx.h, ptrs, ns, lns, C.c_size_t(k), C.c_int32(int(all(dev) and k > 0)),
+                                                             C.c_int32(node_hash), C.byref(self.h)))
+        self.k = k
+
+    def commitment(self, i: int):
+        root = (C.c_uint8 * 16)()
+        n = C.c_uint64(); ln = C.c_uint64()
+        check(self.ctx.h, _lib.lib().zkb_basefold_batch_commitment(self.h, C.c_size_t(i), root, C.byref(n), C.byref(ln)))
+        return bytes(root), n.value, ln.value
+
+    @property
+    def device_bytes(self) -> int:
+        f = _lib.lib().zkb_basefold_batch_device_bytes
+        f.restype = C.c_uint64
+        return int(f(self.h))
+
+    def prove(self, tr: Transcript, individual_openings: bool = False) -> bytes:
+        return _proof_call(self.ctx, _lib.lib().zkb_basefold_batch_prove, self.h, tr.h, C.c_int32(int(individual_openings)), cap=1 << 22)
+
+    def close(self):
+        if self.h.value and self.ctx.h.value:
+            _lib.lib().zkb_basefold_batch_destroy.restype = None
+            _lib.lib().zkb_basefold_batch_destroy(self.h)
+            self.h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
