@@ -536,6 +536,58 @@ def run_basefold(zk, ctx, n, reps=3):
     return out
 
 
+def run_basefold_batch(zk, ctx, with_cpu, cores, reps=3):
+    """Batch Basefold (basefold.rs:1144-1378) over the eight weight matrices of a Qwen3.5-4B-shape attention layer, each as a flat
+    polynomial of m * n coefficients: precommit once (encodings and trees resident), then one fold chain per proof - against
+    eight separate commit_and_prove calls on the same matrices, which is what pcs-full binding does per layer."""
+    from zklm_compile_b200 import pcs as zp
+    cfg = qwen4b_layer_config(3)
+    sizes = layer_sizes(cfg)
+    names = ["w_q", "w_k", "w_v", "w_o", "w_g_proj", "w_gate", "w_up", "w_down"]
+    w = synth_weights(cfg, 3)
+    polys = [ctx.upload(w[n]) for n in names]
+    log_ns = [max(1, (sizes[n] - 1).bit_length()) for n in names]
+    ctx.timer_start()
+    b = zp.BasefoldBatch(ctx, polys, log_ns)
+    pre_ms = ctx.timer_stop_ms()
+    t = []
+    for _ in range(reps + 1):
+        tr = zk.Transcript(ctx, b"bench-batch")
+        ctx.timer_start(); blob = b.prove(tr); t.append(ctx.timer_stop_ms())
+    rng = np.random.default_rng(5)
+    points = [ctx.upload(rng.integers(0, P, ln, dtype=np.int64).astype(np.uint32)) for ln in log_ns]
+    ts = []
+    for _ in range(reps):
+        tot = 0.0
+        for poly, pt in zip(polys, points):
+            tr = zk.Transcript(ctx, b"bench-batch")
+            ctx.timer_start(); zp.basefold_commit_and_prove(ctx, tr, poly, pt); tot += ctx.timer_stop_ms()
+        ts.append(tot)
+    out = {"workload": "batch Basefold over the 8 weight matrices of a Qwen3.5-4B-shape attention layer (flat polynomials, blake3 nodes)",
+           "coefficients": [sizes[n] for n in names], "log_ns": log_ns, "precommit_ms_once": round(pre_ms, 2),
+           "precommit_device_bytes": b.device_bytes, "batch_prove_ms": round(min(t[1:]), 3), "proof_bytes": len(blob),
+           "proof_sha256": hashlib.sha256(blob).hexdigest(), "eight_separate_commit_and_prove_ms": round(min(ts), 2),
+           "separate_over_batch": round(min(ts) / min(t[1:]), 2)}
+    b.close()
+    if with_cpu:
+        # bounded sample: the same eight shapes with every dimension count divided by 64 (2^16 .. 2^19 coefficients)
+        from oracle import pyoracle as O
+        O.set_threads(cores)
+        small = [w[n][: max(1, sizes[n] // 64)] for n in names]
+        sl = [max(1, (p.size - 1).bit_length()) for p in small]
+        t0 = time.perf_counter()
+        e = O.basefold_batch_prove(O.Transcript(b"bench-batch"), small, sl)
+        cpu_ms = (time.perf_counter() - t0) * 1e3
+        bs = zp.BasefoldBatch(ctx, small, sl)
+        g = bs.prove(zk.Transcript(ctx, b"bench-batch"))
+        bs.close()
+        out.update({"cpu_port_ms_at_1_64_size": round(cpu_ms, 1), "cpu_port_threads": cores, "cpu_port_includes": "precommit and proof",
+                    "identical_to_cpu_port_at_1_64_size": g == e})
+    for x in polys + points:
+        x.free()
+    return out
+
+
 def run_mlp(zk, ctx, steps, warmup, ef=True):
     """Dense-4M shape: four 1024 x 1024 linears with a GELU lookup between them, input length 1024,
     forward + proofs on one transcript per step; host input, proofs back on the host."""
@@ -721,6 +773,7 @@ def run_oplist_legs(zk, ctx, with_cpu, cores):
                       "gets the same values from its own forward pass)"})
     out["gpt2_124m_oplist"] = r
     out["attention_rows_gpt2_head_shape"] = run_attention_leg(zk, ctx, with_cpu, cores)
+    out["basefold_batch_4b_attention_layer"] = run_basefold_batch(zk, ctx, with_cpu, cores)
     return out
 
 
