@@ -8,6 +8,7 @@
 //   FoldLevelQueries     { prev_batch_proof, folded_batch_proof }                            basefold.rs:73-81
 //   BatchMerkleProof     { indices: Vec<u32>, values: Vec<u32>, auth_nodes: Vec<Vec<[u8;16]>> }   pcs.rs:43-53
 #include "basefold_batch.hpp"
+#include "unbincode.hpp"
 #include <cstring>
 
 using namespace zko;
@@ -163,6 +164,44 @@ int zko_basefold_batch_roundtrip(const uint32_t* flat, const uint64_t* n, const 
     if (tamper == 5) P.roots[k - 1][0] ^= 1;
     bool ok = batch_verify_opening(pre.commitments, P, vt, kind);
     return ok && pt.squeeze().v == vt.squeeze().v;
+}
+
+// Decode bincode(Vec<BasefoldCommitment>) || bincode(BasefoldBatchProof) and run batch_verify_opening (basefold.rs:959-1137) on it.
+// 1 accept, 0 reject, -1 the bytes do not decode.  final_value_out (optional) receives the proof's final value, which the
+// reference's verifier does not check.
+int zko_basefold_batch_verify_bytes(void* t, const uint8_t* b, size_t n, int kind, uint32_t* final_value_out) {
+    Rd r{b, n};
+    size_t k = r.len(32);
+    std::vector<BasefoldCommitment> cs(k);
+    for (auto& c : cs) { r.bytes(c.root); c.num_coeffs = r.u64(); c.log_n = r.u64(); }
+    BasefoldBatchProof P;
+    P.num_polys = r.u64();
+    size_t m = r.len(8);
+    for (size_t i = 0; i < m && r.ok; i++) P.poly_log_ns.push_back(r.u64());
+    m = r.len(16);
+    P.roots.assign(m, Digest{});
+    for (auto& d : P.roots) r.bytes(d);
+    r.bytes(P.batched_root);
+    m = r.len(16);
+    P.fold_roots.assign(m, Digest{});
+    for (auto& d : P.fold_roots) r.bytes(d);
+    m = r.len(48);
+    for (size_t i = 0; i < m && r.ok; i++) { P.fold_queries.emplace_back(); r.get(P.fold_queries.back().prev_batch_proof); r.get(P.fold_queries.back().folded_batch_proof); }
+    m = r.len(24);
+    for (size_t i = 0; i < m && r.ok; i++) { P.query_openings.emplace_back(); r.get(P.query_openings.back()); }
+    P.final_value = r.u32();
+    m = r.len(16);
+    for (size_t i = 0; i < m && r.ok; i++) {
+        uint64_t round = r.u64();
+        size_t cnt = r.len(32);
+        std::vector<std::pair<uint64_t, BatchMerkleProof>> v;
+        for (size_t j = 0; j < cnt && r.ok; j++) { uint64_t pi = r.u64(); BatchMerkleProof bp; r.get(bp); v.emplace_back(pi, std::move(bp)); }
+        P.add_round_openings.emplace_back(round, std::move(v));
+    }
+    if (!r.ok || r.at != n) return -1;
+    for (uint64_t l : P.poly_log_ns) if (l < 1 || l > 28) return 0;
+    if (final_value_out) *final_value_out = P.final_value;
+    return batch_verify_opening(cs, P, T(t), kind) ? 1 : 0;
 }
 
 }  // extern "C"

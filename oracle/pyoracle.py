@@ -630,6 +630,15 @@ def basefold_batch_prove(tr, polys, log_ns, individual_openings=False, kind=0) -
                        ln.ctypes.data_as(C.POINTER(C.c_uint64)), C.c_size_t(len(polys)), C.c_int(int(individual_openings)), C.c_int(kind), cap=1 << 24)
 
 
+def basefold_batch_verify_bytes(tr, blob: bytes, kind=0):
+    """batch_verify_opening (basefold.rs:959-1137) on bincode(Vec<BasefoldCommitment>) || bincode(BasefoldBatchProof)
+    -> (1 accept / 0 reject / -1 undecodable, the proof's final value)."""
+    buf = (C.c_uint8 * len(blob)).from_buffer_copy(blob)
+    fv = C.c_uint32(0)
+    rc = lib().zko_basefold_batch_verify_bytes(tr.h, buf, C.c_size_t(len(blob)), C.c_int(kind), C.byref(fv))
+    return int(rc), fv.value
+
+
 def basefold_batch_roundtrip(polys, log_ns, individual_openings=False, kind=0, tamper=0) -> int:
     flat, n, ln = _batch_args(polys, log_ns)
     return int(lib().zko_basefold_batch_roundtrip(flat.ctypes.data_as(u32p), n.ctypes.data_as(C.POINTER(C.c_uint64)), ln.ctypes.data_as(C.POINTER(C.c_uint64)),

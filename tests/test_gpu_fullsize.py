@@ -119,3 +119,48 @@ def test_basefold_2_26_properties(env):
     assert blob[:16] == zpc.merkle_root(c, cw)
     for b in (coeffs, point, cw):
         b.free()
+
+
+def test_batch_basefold_of_a_4b_layer_is_accepted_by_the_restated_verifier(env):
+    """Batch Basefold at the real size (the eight weight matrices of a 4B-shape attention layer, 2^22 .. 2^25 coefficients, far beyond
+    what the CPU prover restatement does in test time): the restated batch_verify_opening accepts the GPU's bytes and ends in the same
+    transcript state, rejects them with one opened value changed, and the final value is the rho-weighted sum of the polynomials'
+    multilinear evaluations (computed with the separately tested MLE kernel; the reference's verifier does not check it)."""
+    from zklm_compile_b200 import pcs as zpc
+    c = env[0]
+    cfg = bench.qwen4b_layer_config(3)
+    sizes = bench.layer_sizes(cfg)
+    names = ["w_q", "w_k", "w_v", "w_o", "w_g_proj", "w_gate", "w_up", "w_down"]
+    w = bench.synth_weights(cfg, 3)
+    log_ns = [max(1, (sizes[n] - 1).bit_length()) for n in names]
+    polys = [c.upload(w[n]) for n in names]
+    b = zpc.BasefoldBatch(c, polys, log_ns)
+    tg = zk.Transcript(c, b"batch-4b")
+    blob = b.prove(tg)
+    to = O.Transcript(b"batch-4b")
+    O.set_threads(8)
+    rc, final_value = O.basefold_batch_verify_bytes(to, blob)
+    O.set_threads(1)
+    assert rc == 1 and tg.squeeze() == to.squeeze()
+    # the transcript gives rho and the fold point back: replay the public part on the oracle's transcript type
+    k = len(names)
+    order = sorted(range(k), key=lambda i: -log_ns[i])            # stable, like the prover's sort
+    tr = O.Transcript(b"batch-4b")
+    for i in order:
+        tr.absorb_bytes(b.commitment(i)[0])
+    rho = tr.squeeze()
+    at = 8 + 32 * k + 8 + 8 + 8 * k + 8 + 16 * k
+    tr.absorb_bytes(blob[at:at + 16])
+    point = [tr.squeeze() for _ in range(max(log_ns))]
+    acc, pw = 0, 1
+    for i in order:
+        acc = (acc + pw * zp.mle_evaluate(c, polys[i], np.array(point[:log_ns[i]], np.uint32))) % P
+        pw = pw * rho % P
+    assert acc == final_value
+    bad = bytearray(blob)
+    at_values = blob.index((48).to_bytes(8, "little"), at + 16 + 8 + 16 * max(log_ns)) + 8 + 4 * 48 + 8     # first opened value of round 0
+    bad[at_values] ^= 1
+    assert O.basefold_batch_verify_bytes(O.Transcript(b"batch-4b"), bytes(bad))[0] == 0
+    b.close()
+    for x in polys:
+        x.free()

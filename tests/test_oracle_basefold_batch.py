@@ -63,3 +63,18 @@ def test_bincode_structure():
     b2 = po.basefold_batch_prove(po.Transcript(b"multi-height-test"), [polys[2], polys[0], polys[1]], [4, 8, 6])
     assert b2[8 + 96:] == b[8 + 96:]
     assert b2[8:8 + 32] == b[8 + 64:8 + 96] and b2[8 + 32:8 + 64] == b[8:8 + 32]
+
+
+def test_verify_from_bytes():
+    polys, log_ns = multi_height_polys()
+    b = po.basefold_batch_prove(po.Transcript(b"v"), polys, log_ns)
+    assert po.basefold_batch_verify_bytes(po.Transcript(b"v"), b)[0] == 1
+    assert po.basefold_batch_verify_bytes(po.Transcript(b"other"), b)[0] == 0
+    assert po.basefold_batch_verify_bytes(po.Transcript(b"v"), b[:-3])[0] == -1
+    rejected = 0
+    for at in range(8, len(b), 97):
+        bad = bytearray(b); bad[at] ^= 1
+        rejected += po.basefold_batch_verify_bytes(po.Transcript(b"v"), bytes(bad))[0] != 1
+    # what the reference's verifier does not read may change unnoticed: the commitments (only the proof's own roots are absorbed),
+    # the final value, values repeated for duplicate positions
+    assert rejected > 0.85 * len(range(8, len(b), 97))
