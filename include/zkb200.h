@@ -166,6 +166,10 @@ uint64_t zkb_basefold_batch_device_bytes(const zkb_bf_batch* batch);
 int32_t zkb_basefold_batch_commitment(const zkb_bf_batch* batch, size_t index, uint8_t root[16], uint64_t* num_coeffs, uint64_t* log_n);
 int32_t zkb_basefold_batch_prove(zkb_bf_batch* batch, zkb_transcript* tr, int32_t individual_openings, uint8_t* out, size_t cap, size_t* len);
 void zkb_basefold_batch_destroy(zkb_bf_batch* batch);
+/* batch_verify_opening (basefold.rs:959-1137) on those bytes: *accepted = 1 / 0.  Like the reference's verifier it checks the roots'
+ * transcript, every Merkle opening and the fold relation with the joined polynomials' contributions at 24 positions per round, not the
+ * final value.  ZKB_E_ARG when the bytes do not decode. */
+int32_t zkb_basefold_batch_verify_opening(zkb_ctx* ctx, zkb_transcript* tr, const uint8_t* bytes, size_t len, int32_t node_hash, int32_t* accepted);
 
 /* ---- row-decomposed attention at seq_len >= 2 ----
  * prove_row_attention (proving/attention.rs:116-276), as the op-list prover calls it for an "attention" op

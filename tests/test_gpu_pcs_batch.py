@@ -95,3 +95,56 @@ def test_argument_errors(ctx):
         b.prove(zk.Transcript(ctx, b"x"), True)
     assert b.prove(zk.Transcript(ctx, b"x")) == O.basefold_batch_prove(O.Transcript(b"x"), [p, p[:4]], [4, 2])
     b.close()
+
+
+# ---- the verifier (basefold.rs:959-1137) ------------------------------------------------------------------------
+def _judge_gpu(ctx, blob, kind, label):
+    try:
+        return int(pcs.basefold_batch_verify_opening(ctx, zk.Transcript(ctx, label), blob, kind))
+    except zk.ZkbError as e:
+        assert e.code == 2
+        return -1
+
+
+@pytest.mark.parametrize("kind", [0, 1])
+@pytest.mark.parametrize("case", ["multi", "same"])
+def test_batch_verifier_judges_like_the_restated_one(ctx, kind, case):
+    rng = np.random.default_rng(77)
+    if case == "multi":
+        polys = [rng.integers(0, P, n).astype(np.uint32) for n in (200, 64, 256, 50, 9)]
+        log_ns, individual = [8, 6, 8, 6, 4], False
+    else:
+        polys = [rng.integers(0, P, 128).astype(np.uint32) for _ in range(3)]
+        log_ns, individual = [7, 7, 7], True
+    b = pcs.BasefoldBatch(ctx, polys, log_ns, kind)
+    blob = b.prove(zk.Transcript(ctx, b"bv"), individual)
+    b.close()
+    tg, to = zk.Transcript(ctx, b"bv"), O.Transcript(b"bv")
+    assert pcs.basefold_batch_verify_opening(ctx, tg, blob, kind) is True
+    assert O.basefold_batch_verify_bytes(to, blob, kind)[0] == 1
+    assert tg.squeeze() == to.squeeze()
+    assert pcs.basefold_batch_verify_opening(ctx, zk.Transcript(ctx, b"other"), blob, kind) is False
+    # single low-bit changes all over the proof part (the commitments in front are not read by either verifier except for the
+    # individual openings' roots; their length fields are left alone): the two verifiers agree on every one
+    start = 8 + 32 * len(polys)
+    n_rejected = 0
+    for at in list(range(start, len(blob), 61)) + list(range(8, start, 32)):
+        bad = bytearray(blob)
+        bad[at] ^= 1
+        exp = O.basefold_batch_verify_bytes(O.Transcript(b"bv"), bytes(bad), kind)[0]
+        got = _judge_gpu(ctx, bytes(bad), kind, b"bv")
+        assert got == exp, (at, got, exp)
+        n_rejected += exp != 1
+    assert n_rejected > 100
+    assert _judge_gpu(ctx, blob[:-5], kind, b"bv") == -1 and _judge_gpu(ctx, blob + b"\\0", kind, b"bv") == -1
+
+
+def test_batch_verifier_at_2_17(ctx):
+    rng = np.random.default_rng(3)
+    polys = [rng.integers(0, P, n).astype(np.uint32) for n in (100000, 30000, 131072, 5)]
+    log_ns = [17, 15, 17, 3]
+    b = pcs.BasefoldBatch(ctx, polys, log_ns)
+    blob = b.prove(zk.Transcript(ctx, b"big"))
+    b.close()
+    assert pcs.basefold_batch_verify_opening(ctx, zk.Transcript(ctx, b"big"), blob) is True
+    assert O.basefold_batch_verify_bytes(O.Transcript(b"big"), blob)[0] == 1

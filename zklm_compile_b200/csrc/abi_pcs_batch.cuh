@@ -391,4 +391,26 @@ int32_t zkb_basefold_batch_prove(zkb_bf_batch* B, zkb_transcript* t, int32_t ind
     });
 }
 
+// batch_verify_opening (basefold.rs:959-1137) on the bytes zkb_basefold_batch_prove returns.  The transcript ends where the prover's does.
+int32_t zkb_basefold_batch_verify_opening(zkb_ctx* c, zkb_transcript* tr, const uint8_t* bytes, size_t len, int32_t node_hash, int32_t* accepted) {
+    if (!c || !tr || !bytes || !accepted) return ZKB_E_ARG;
+    *accepted = 0;
+    ZKB_TRY(c, {
+        c->use();
+        BbvParsed pr;
+        if (!bbv_parse(bytes, len, pr)) throw ArgFail{ZKB_E_ARG, "batch basefold: the bytes do not decode as commitments followed by a batch proof"};
+        if (pr.too_large) throw ArgFail{ZKB_E_TOO_LARGE, "basefold: more than 256 opened positions in one batch proof"};
+        if (pr.trivially_true) { *accepted = 1; return ZKB_OK; }
+        if (pr.reject) return ZKB_OK;                             // decided from the shape, before the transcript is touched
+        BvRun run = basefold_batch_verify_enqueue(c, tr->dev, pr, node_hash);
+        std::vector<u32> res(run.n_results);
+        ZKB_CUDA(cudaMemcpyAsync(res.data(), run.result_dev, (size_t)run.n_results * 4, cudaMemcpyDeviceToHost, c->stream));
+        ZKB_CUDA(cudaStreamSynchronize(c->stream));
+        c->scratch_reset();
+        bool ok = true;
+        for (u32 v : res) ok = ok && v == 1;
+        *accepted = ok ? 1 : 0;
+    });
+}
+
 }  // extern "C"

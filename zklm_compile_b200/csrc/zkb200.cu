@@ -3,6 +3,7 @@
 #include "oplist.cuh"
 #include "basefold.cuh"
 #include "verify.cuh"
+#include "verify_batch.cuh"
 #include "attention.cuh"
 #include "verify_layer.cuh"
 #include <cstdlib>

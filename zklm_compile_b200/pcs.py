@@ -92,6 +92,14 @@ def basefold_verify_opening(ctx: Context, tr: Transcript, blob: bytes, point, cl
     return bool(ok.value)
 
 
+def basefold_batch_verify_opening(ctx: Context, tr: Transcript, blob: bytes, node_hash: int = NODE_BLAKE3) -> bool:
+    """batch_verify_opening, basefold.rs:959-1137, on the bytes BasefoldBatch.prove returns."""
+    ok = C.c_int32(0)
+    buf = (C.c_uint8 * len(blob)).from_buffer_copy(blob)
+    check(ctx.h, _lib.lib().zkb_basefold_batch_verify_opening(ctx.h, tr.h, buf, C.c_size_t(len(blob)), C.c_int32(node_hash), C.byref(ok)))
+    return bool(ok.value)
+
+
 class BasefoldBatch:
     """Batch Basefold over polynomials of possibly different sizes (basefold.rs:1144-1378).
 
