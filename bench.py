@@ -814,11 +814,17 @@ def run_attention_leg(zk, ctx, with_cpu, cores, nh=12, s=128, d=64):
         o = za.row_attention_forward(ctx, dq, dk, dv, nh, s, d, dt)
         fwd.append(ctx.timer_stop_ms())
         o.free()
+    ver = []
+    for i in range(4):
+        tv = zk.Transcript(ctx, b"structured-ml-proof")
+        t0 = time.perf_counter()
+        assert za.verify_row_attention(proof, dk, dv, nh, s, d, tv)
+        ver.append(1e3 * (time.perf_counter() - t0))
     absorbed = nh * s * (s + d) * 4
     r = {"workload": f"row attention, {nh} heads x {s} positions x d_head {d} (GPT-2-124M head shape), exp table scale 100, base-field challenges",
          "rows": nh * s, "prove_ms_host_inputs": round(host_ms, 3), "prove_ms_device_inputs": round(dev_ms, 3),
          "prove_ms_rows_then_transcript": round(inorder_ms, 3), "forward_ms": round(float(np.median(fwd[2:])), 3),
-         "proof_bytes": len(proof), "same_proof_from_device_inputs": proof == proof_d,
+         "proof_bytes": len(proof), "same_proof_from_device_inputs": proof == proof_d, "verify_ms_host_proof_bytes": round(min(ver[1:]), 3),
          "caller_transcript_bytes_absorbed": absorbed, "caller_transcript_sha256_blocks": absorbed // 64,
          "h2d_bytes": 3 * n * 4 + t.size * 4, "gpu_launches_per_call": 3}
     if with_cpu:

@@ -200,6 +200,14 @@ int32_t zkb_prove_row_attention_gqa(zkb_ctx* ctx, zkb_transcript* tr, const uint
                                     size_t num_kv_heads, size_t seq_len, size_t d_head, const uint32_t* table_out, size_t n_table,
                                     int32_t on_device, uint32_t* attn_out, uint8_t* out, size_t cap, size_t* len);
 
+/* verify_row_attention / verify_row_attention_gqa (attention.rs:279-385, 503-590) on the bytes the prover returns: *accepted = 1 / 0.  k, v as for
+ * the prover (num_kv_heads = 0: the plain form).  Every row is checked by one CTA: the row's transcript replayed, the three sumchecks of the
+ * softmax and the two matmul sumchecks verified, K(r, s) and V^T(r, s) recomputed from k and v; `tr` absorbs what the prover's absorbed.  As
+ * in the reference neither q nor the exp table is read, the lookup's inputs are not compared with the scores, and attn_weights / y_values
+ * are not looked at.  A proof whose vectors do not have the lengths the prover produces is rejected; ZKB_E_ARG when the bytes do not decode. */
+int32_t zkb_verify_row_attention(zkb_ctx* ctx, zkb_transcript* tr, const uint8_t* proof, size_t len, const uint32_t* k, const uint32_t* v,
+                                 size_t num_heads, size_t num_kv_heads, size_t seq_len, size_t d_head, int32_t on_device, int32_t* accepted);
+
 /* ---- weights in the reference's wire format, kept resident ----
  * zkb_weightset_preload takes the preload block of the reference's server mode (server.rs:33-94):
  *   [count u32] then per matrix [name_len u32][name, UTF-8][m u32][n u32][m * n u32 LE]

@@ -60,7 +60,7 @@ inline bool verify_softmax(const SoftmaxProof& p, size_t num_elements, Transcrip
     tr.absorb(p.sum_value);
     F ones_at_s(p.sum_finals[0]), e_at_s(p.sum_finals[1]);
     if (p.sum_proof.round_polys.size() != log_n) return false;
-    if (!verify_product_with_challenges(sum, p.sum_proof, ones_at_s, e_at_s, tr)) return false;
+    if (!verify_product(sum, p.sum_proof, ones_at_s, e_at_s, tr)) return false;                 // softmax.rs:183
     if (ones_at_s != F::one()) return false;
     VF r_point = tr.squeeze_many(log_n);
     VF e_vals;
@@ -69,7 +69,7 @@ inline bool verify_softmax(const SoftmaxProof& p, size_t num_elements, Transcrip
     F eq_at_s2(p.output_finals[0]), y_at_s2(p.output_finals[1]), s_at_s2(p.output_finals[2]);
     if (p.output_proof.round_polys.size() != log_n) return false;
     for (auto& rp : p.output_proof.round_polys) if (rp.size() < 4) return false;
-    if (!verify_triple_with_challenges(e_at_r, p.output_proof, eq_at_s2, y_at_s2, s_at_s2, tr)) return false;
+    if (!verify_triple(e_at_r, p.output_proof, eq_at_s2, y_at_s2, s_at_s2, tr)) return false;   // softmax.rs:213
     VF s_point;
     for (uint32_t v : p.output_proof.challenges) s_point.push_back(F(v));
     if (compute_eq_at_point(r_point, s_point) != eq_at_s2) return false;
@@ -88,7 +88,7 @@ inline bool verify_matmul(const MatmulProof& p, const VF& w, const VF& y, size_t
     F claim = mle_evaluate(y_pad, r);
     F w_at_rs(p.w_at_rs), x_at_s(p.x_at_s);
     if (p.sumcheck_proof.round_polys.size() != log_n) return false;
-    if (!verify_product_with_challenges(claim, p.sumcheck_proof, w_at_rs, x_at_s, tr)) return false;
+    if (!verify_product(claim, p.sumcheck_proof, w_at_rs, x_at_s, tr)) return false;             // matmul.rs:227
     VF w_pad(m_pad * n_pad, F::zero());
     for (size_t i = 0; i < m; i++) for (size_t j = 0; j < n; j++) w_pad[i * n_pad + j] = w[i * n + j];
     VF point = r;

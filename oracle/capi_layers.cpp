@@ -417,4 +417,52 @@ int zko_row_attention_roundtrip(const uint32_t* q, const uint32_t* k, const uint
     return good && pt.squeeze().v == vt.squeeze().v;
 }
 
+// Decode bincode(RowAttentionProof) and run verify_row_attention (attention.rs:279-385; GQA :503-590) on it with the caller's dimensions.
+// 1 accept, 0 reject, -1 the bytes do not decode.
+static void rd_sumcheck(Rd& r, SumcheckProof& p) {
+    size_t k = r.len(8);
+    p.round_polys.clear();
+    for (size_t i = 0; i < k && r.ok; i++) { p.round_polys.emplace_back(); r.vec_u32(p.round_polys.back()); }
+    r.vec_u32(p.challenges);
+}
+static void rd_matmul(Rd& r, MatmulProof& p) { rd_sumcheck(r, p.sumcheck_proof); p.w_at_rs = r.u32(); p.x_at_s = r.u32(); r.vec_u32(p.r_point); r.vec_u32(p.s_point); }
+int zko_row_attention_verify_bytes(void* t, const uint8_t* b, size_t n, const uint32_t* k, const uint32_t* v, size_t num_heads, size_t num_kv_heads,
+                                   size_t seq_len, size_t d_head) {
+    Rd r{b, n};
+    SeqAttentionProof P;
+    size_t nh = r.len(8);
+    for (size_t h = 0; h < nh && r.ok; h++) {
+        size_t ns = r.len(8);
+        P.row_proofs.emplace_back();
+        for (size_t i = 0; i < ns && r.ok; i++) {
+            RowProof rp;
+            rd_matmul(r, rp.score_proof);
+            LookupProof& lk = rp.softmax_proof.exp_lookup_proof;
+            r.get(lk.table_commitment); r.get(lk.multiplicity_commitment);
+            rd_sumcheck(r, lk.sumcheck_proof);
+            lk.fin_ones = r.u32(); lk.fin_h = r.u32(); lk.alpha = r.u32(); lk.beta = r.u32();
+            r.vec_u32(lk.inputs); r.vec_u32(lk.outputs); r.vec_u32(lk.multiplicities);
+            r.bytes(lk.external_data_digest);
+            SoftmaxProof& sp = rp.softmax_proof;
+            sp.sum_value = r.u32();
+            rd_sumcheck(r, sp.sum_proof); sp.sum_finals[0] = r.u32(); sp.sum_finals[1] = r.u32();
+            rd_sumcheck(r, sp.output_proof); for (int j = 0; j < 3; j++) sp.output_finals[j] = r.u32();
+            sp.inv_s = r.u32();
+            r.vec_u32(sp.e_values); r.vec_u32(sp.y_values);
+            rd_matmul(r, rp.output_proof);
+            r.vec_u32(rp.scores); r.vec_u32(rp.attn_weights); r.vec_u32(rp.output);
+            P.row_proofs.back().push_back(std::move(rp));
+        }
+    }
+    P.num_heads = r.u64(); P.seq_len = r.u64(); P.d_head = r.u64();
+    uint8_t opt = r.u8();
+    if (opt == 1) { r.u32(); r.u32(); r.u8(); } else if (opt != 0) return -1;
+    if (!r.ok || r.at != n) return -1;
+    // the caller's dimensions are those of k and v; a proof that declares others, or holds a different number of rows, makes the reference index out of range
+    if (P.num_heads != num_heads || P.seq_len != seq_len || P.d_head != d_head || P.row_proofs.size() != num_heads) return 0;
+    for (auto& hp : P.row_proofs) if (hp.size() != seq_len) return 0;
+    size_t nkv = (num_kv_heads ? num_kv_heads : num_heads) * seq_len * d_head;
+    return verify_row_attention(P, vf(k, nkv), vf(v, nkv), T(t), num_kv_heads) ? 1 : 0;
+}
+
 }  // extern "C"

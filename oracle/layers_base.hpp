@@ -170,7 +170,7 @@ inline bool verify_lookup(const LookupProof& p, size_t num_lookups, Transcript& 
     tr.absorb_bytes(p.multiplicity_commitment.root);
     if (p.sumcheck_proof.round_polys.size() != log_n) return false;
     // sumcheck.rs verify_product with the ones-sumcheck's two stored evaluations [s0, s2]
-    if (!verify_product_with_challenges(F::zero(), p.sumcheck_proof, F(p.fin_ones), F(p.fin_h), tr)) return false;
+    if (!verify_product(F::zero(), p.sumcheck_proof, F(p.fin_ones), F(p.fin_h), tr)) return false;   // lookup.rs:857
     return F(p.fin_ones) == F::one();
 }
 

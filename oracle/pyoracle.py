@@ -658,6 +658,14 @@ def prove_row_attention(tr, q, k, v, num_heads: int, seq_len: int, d_head: int, 
     return bytes(buf[:n]), st.value
 
 
+def row_attention_verify_bytes(tr, blob: bytes, k, v, num_heads: int, seq_len: int, d_head: int, num_kv_heads: int = 0) -> int:
+    """verify_row_attention (attention.rs:279-385, GQA :503-590) on bincode(RowAttentionProof): 1 accept, 0 reject, -1 undecodable."""
+    K, pk = _u32(k); V, pv = _u32(v)
+    buf = (C.c_uint8 * len(blob)).from_buffer_copy(blob)
+    return int(lib().zko_row_attention_verify_bytes(tr.h, buf, C.c_size_t(len(blob)), pk, pv, C.c_size_t(num_heads), C.c_size_t(num_kv_heads),
+                                                    C.c_size_t(seq_len), C.c_size_t(d_head)))
+
+
 def row_attention_forward(q, k, v, num_heads: int, seq_len: int, d_head: int, table_out, num_kv_heads: int = 0):
     """The attention op's forward pass at seq_len >= 2 (pipeline/forward.rs:233-276) -> (values, status)."""
     Q, pq = _u32(q); K, pk = _u32(k); V, pv = _u32(v); T, pt = _u32(table_out)

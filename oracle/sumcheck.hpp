@@ -167,6 +167,18 @@ inline bool verify_triple_with_challenges(F claimed, const SumcheckProof& p, F f
     return claim == f_at_s * g_at_s * h_at_s;
 }
 
+// sumcheck.rs:981-1014, 1054-1119: the variants without the point - the proof's `challenges` field is not looked at.
+inline bool verify_product(F claimed, const SumcheckProof& p, F f_at_s, F g_at_s, Transcript& tr) {
+    SumcheckProof q;
+    q.round_polys = p.round_polys;
+    return verify_product_with_challenges(claimed, q, f_at_s, g_at_s, tr);
+}
+inline bool verify_triple(F claimed, const SumcheckProof& p, F f_at_s, F g_at_s, F h_at_s, Transcript& tr) {
+    SumcheckProof q;
+    q.round_polys = p.round_polys;
+    return verify_triple_with_challenges(claimed, q, f_at_s, g_at_s, h_at_s, tr);
+}
+
 // ---------------------------------------------------------------- extension field provers
 struct ProdEF { SumcheckProofEF proof; EF f_at_s, g_at_s; };
 struct TripEF { SumcheckProofEF proof; EF f_at_s, g_at_s, h_at_s; };

@@ -234,3 +234,59 @@ def test_oplist_with_gqa_attention(ctx):
     g.linear("o_proj", w2, None, 7, tq); o.linear("o_proj", w2, None, 7, tq)
     assert g.prove(x) == o.prove(x)
     g.close()
+
+
+# ---- the verifier (attention.rs:279-385, 503-590) -----------------------------------------------------------------
+def _judge(ctx, blob, k, v, nh, s, d, nkv, label):
+    try:
+        return int(za.verify_row_attention(blob, k, v, nh, s, d, zk.Transcript(ctx, label), nkv))
+    except zk.ZkbError as e:
+        assert e.code == 2
+        return -1
+
+
+@pytest.mark.parametrize("nh,nkv,s,d,n_table", [(2, 0, 6, 4, 65536), (4, 2, 5, 3, 65536), (1, 0, 16, 8, 256)])
+def test_verifier_judges_like_the_restated_one(ctx, nh, nkv, s, d, n_table):
+    rng = np.random.default_rng(nh + s + d)
+    t = tables.build_exp_table(100) if n_table == 65536 else small_exp_table()
+    kvh = nkv or nh
+    q = np.mod(rng.integers(-2, 3, nh * s * d), P).astype(np.uint32)
+    k = np.mod(rng.integers(-2, 3, kvh * s * d), P).astype(np.uint32)
+    v = rng.integers(0, P, kvh * s * d).astype(np.uint32)
+    proof = za.prove_row_attention(q, k, v, nh, s, d, t, zk.Transcript(ctx, b"av"), num_kv_heads=nkv)
+    tg, to = zk.Transcript(ctx, b"av"), O.Transcript(b"av")
+    assert za.verify_row_attention(proof, k, v, nh, s, d, tg, nkv) is True
+    assert O.row_attention_verify_bytes(to, proof, k, v, nh, s, d, nkv) == 1
+    assert tg.squeeze() == to.squeeze()
+    # other K / V, other head grouping, other dimensions: rejected by both
+    k2 = k.copy(); k2[3] = (int(k2[3]) + 1) % P
+    v2 = v.copy(); v2[-1] ^= 1
+    for kk, vv in ((k2, v), (k, v2)):
+        assert _judge(ctx, proof, kk, vv, nh, s, d, nkv, b"av") == O.row_attention_verify_bytes(O.Transcript(b"av"), proof, kk, vv, nh, s, d, nkv) == 0
+    assert _judge(ctx, proof, k, v, nh, s, d, nkv, b"av2") == 1        # rows have transcripts of their own: the caller's label does not enter them
+    # one low bit changed, all over the proof: the two verifiers agree on every position
+    n_rej = n_acc = 0
+    for at in range(0, len(proof), 7):
+        bad = bytearray(proof)
+        bad[at] ^= 1
+        exp = O.row_attention_verify_bytes(O.Transcript(b"av"), bytes(bad), k, v, nh, s, d, nkv)
+        got = _judge(ctx, bytes(bad), k, v, nh, s, d, nkv, b"av")
+        assert got == exp, (at, got, exp)
+        n_rej += exp == 0
+        n_acc += exp == 1
+    assert n_rej > 300 and n_acc > 10       # accepted: fields the reference's verifier does not read (challenges of the plain sumchecks, y_values, ...)
+
+
+def test_verifier_at_the_bench_shape(ctx):
+    rng = np.random.default_rng(12)
+    t = tables.build_exp_table(100)
+    nh, s, d = 12, 128, 64
+    n = nh * s * d
+    q = np.mod(rng.integers(-1, 2, n), P).astype(np.uint32); k = np.mod(rng.integers(-1, 2, n), P).astype(np.uint32)
+    v = rng.integers(0, P, n).astype(np.uint32)
+    proof = za.prove_row_attention(q, k, v, nh, s, d, t, zk.Transcript(ctx, b"big"))
+    dk, dv = ctx.upload(k), ctx.upload(v)
+    assert za.verify_row_attention(proof, dk, dv, nh, s, d, zk.Transcript(ctx, b"big")) is True
+    bad = bytearray(proof)
+    bad[len(bad) // 2] ^= 1
+    assert _judge(ctx, bytes(bad), dk, dv, nh, s, d, 0, b"big") == O.row_attention_verify_bytes(O.Transcript(b"big"), bytes(bad), k, v, nh, s, d)

@@ -76,6 +76,19 @@ def prove_row_attention_gqa(q, k, v, num_q_heads: int, num_kv_heads: int, seq_le
     return prove_row_attention(q, k, v, num_q_heads, seq_len, d_head, exp_table, transcript, want_output, num_kv_heads)
 
 
+def verify_row_attention(proof: bytes, k, v, num_heads: int, seq_len: int, d_head: int, transcript: Transcript, num_kv_heads: int = 0) -> bool:
+    """attention.rs:279-385 (GQA: :503-590) on bincode(RowAttentionProof); as in the reference, q and the exp table are not needed."""
+    ctx = transcript.ctx
+    kk, pk, dk = _ptr(k); vv, pv, dv = _ptr(v)
+    if dk != dv:
+        raise ValueError("k and v are either both DeviceBuffers or both host arrays")
+    ok = C.c_int32(0)
+    buf = (C.c_uint8 * len(proof)).from_buffer_copy(proof)
+    check(ctx.h, _lib.lib().zkb_verify_row_attention(ctx.h, transcript.h, buf, C.c_size_t(len(proof)), pk, pv, C.c_size_t(num_heads),
+                                                     C.c_size_t(num_kv_heads), C.c_size_t(seq_len), C.c_size_t(d_head), C.c_int32(int(dk)), C.byref(ok)))
+    return bool(ok.value)
+
+
 def proof_size_bound(num_heads: int, seq_len: int, d_head: int) -> int:
     """Upper bound of the bincode size, for callers that allocate the output buffer themselves."""
     ls = max(1, (seq_len - 1).bit_length()); ld = max(1, (d_head - 1).bit_length())

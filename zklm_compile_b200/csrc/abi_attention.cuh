@@ -81,4 +81,33 @@ int32_t zkb_prove_row_attention(zkb_ctx* c, zkb_transcript* t, const uint32_t* q
     return zkb_prove_row_attention_gqa(c, t, q, k, v, num_heads, 0, seq_len, d_head, table_out, n_table, on_device, attn_out, out, cap, len);
 }
 
+// verify_row_attention / verify_row_attention_gqa (attention.rs:279-385, 503-590) on bincode(RowAttentionProof).  As in the reference, q
+// and the exp table are not needed: the verifier recomputes K(r, s) and V^T(r, s) from k and v and replays each row's transcript.
+int32_t zkb_verify_row_attention(zkb_ctx* c, zkb_transcript* t, const uint8_t* proof, size_t len, const uint32_t* k, const uint32_t* v,
+                                 size_t num_heads, size_t num_kv_heads, size_t seq_len, size_t d_head, int32_t on_device, int32_t* accepted) {
+    if (!c || !t || !proof || !k || !v || !accepted) return ZKB_E_ARG;
+    *accepted = 0;
+    ZKB_TRY(c, {
+        c->use();
+        att_check_dims(num_heads, seq_len, d_head, 65536);
+        if (seq_len < 2) throw ArgFail{ZKB_E_ARG, "attention: seq_len = 1 has no row proofs"};
+        att_heads_per_group(num_heads, num_kv_heads);
+        AvParsed pr;
+        if (!av_parse(proof, len, (u32)num_heads, (u32)seq_len, (u32)d_head, pr))
+            throw ArgFail{ZKB_E_ARG, "attention: the bytes do not decode as a RowAttentionProof"};
+        if (pr.reject) return ZKB_OK;                             // dimensions or vector lengths the prover does not produce
+        const size_t n_kv = (num_kv_heads ? num_kv_heads : num_heads) * seq_len * d_head;
+        const u32* dk = on_device ? k : up_pad(c, k, n_kv, n_kv);
+        const u32* dv = on_device ? v : up_pad(c, v, n_kv, n_kv);
+        AvRun run = attention_verify_enqueue(c, t->dev, pr, dk, dv, (u32)num_kv_heads);
+        std::vector<u32> res(run.rows);
+        ZKB_CUDA(cudaMemcpyAsync(res.data(), run.result_dev, (size_t)run.rows * 4, cudaMemcpyDeviceToHost, c->stream));
+        ZKB_CUDA(cudaStreamSynchronize(c->stream));
+        c->scratch_reset();
+        bool ok = true;
+        for (u32 r : res) ok = ok && r == 1;
+        *accepted = ok ? 1 : 0;
+    });
+}
+
 }  // extern "C"

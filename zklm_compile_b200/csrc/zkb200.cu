@@ -5,6 +5,7 @@
 #include "verify.cuh"
 #include "verify_batch.cuh"
 #include "attention.cuh"
+#include "verify_attention.cuh"
 #include "verify_layer.cuh"
 #include <cstdlib>
 #include <cstring>
