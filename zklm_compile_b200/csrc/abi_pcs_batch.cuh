@@ -134,6 +134,14 @@ BfbPending bfb_enqueue(zkb_bf_batch* B, TrState* tr, bool individual) {
         ZKB_CUDA(cudaEventRecord(fork, main_stream));
         ZKB_CUDA(cudaStreamWaitEvent(work, fork, 0));
     }
+    // final value: sum_i rho^i MLE_i(fold_point[..log_n_i]) (:1357-1362).  It needs only the fold point, so it goes in front of the rounds on
+    // the main stream, where it runs while the second stream folds and hashes the first (largest) rounds.
+    u32* evals = (u32*)c->scratch((size_t)k * 4 + 16);
+    for (u32 i = 0; i < k; i++)
+        mle_eval_enqueue<Fp, Fp>(c, (const Fp*)B->e[i].coeffs, B->e[i].n, (const Fp*)fold_point, B->e[i].log_n, (Fp*)(evals + i));
+    pd.final_off = c->rec_alloc(1);
+    bfb_final_value_kernel<<<1, 1, 0, c->stream>>>(coef, evals, k, c->rec_dev + pd.final_off);
+    ZKB_LAUNCHED(c);
     u32* prev_cw = cw0;
     uint4* prev_tree = tree0;
     size_t next_group = 1;
@@ -191,13 +199,6 @@ BfbPending bfb_enqueue(zkb_bf_batch* B, TrState* tr, bool individual) {
         } catch (...) { c->stream = main_stream; throw; }
         prev_cw = next_cw; prev_tree = next_tree;
     }
-    // final value: sum_i rho^i MLE_i(fold_point[..log_n_i]) (:1357-1362)
-    u32* evals = (u32*)c->scratch((size_t)k * 4 + 16);
-    for (u32 i = 0; i < k; i++)
-        mle_eval_enqueue<Fp, Fp>(c, (const Fp*)B->e[i].coeffs, B->e[i].n, (const Fp*)fold_point, B->e[i].log_n, (Fp*)(evals + i));
-    pd.final_off = c->rec_alloc(1);
-    bfb_final_value_kernel<<<1, 1, 0, c->stream>>>(coef, evals, k, c->rec_dev + pd.final_off);
-    ZKB_LAUNCHED(c);
     pd.final_idx_off = c->rec_alloc(BF_QUERIES);
     bfb_final_kernel<<<1, 1, 0, c->stream>>>(tr, (u32(1) << log_n) - 1, c->rec_dev + pd.final_idx_off);
     ZKB_LAUNCHED(c);
