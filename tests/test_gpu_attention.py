@@ -237,7 +237,7 @@ def test_oplist_with_gqa_attention(ctx):
 
 
 # ---- the verifier (attention.rs:279-385, 503-590) -----------------------------------------------------------------
-def _judge(ctx, blob, k, v, nh, s, d, nkv, label):
+def _decision(ctx, blob, k, v, nh, s, d, nkv, label):
     try:
         return int(za.verify_row_attention(blob, k, v, nh, s, d, zk.Transcript(ctx, label), nkv))
     except zk.ZkbError as e:
@@ -246,7 +246,7 @@ def _judge(ctx, blob, k, v, nh, s, d, nkv, label):
 
 
 @pytest.mark.parametrize("nh,nkv,s,d,n_table", [(2, 0, 6, 4, 65536), (4, 2, 5, 3, 65536), (1, 0, 16, 8, 256)])
-def test_verifier_judges_like_the_restated_one(ctx, nh, nkv, s, d, n_table):
+def test_verifier_decides_like_the_restated_one(ctx, nh, nkv, s, d, n_table):
     rng = np.random.default_rng(nh + s + d)
     t = tables.build_exp_table(100) if n_table == 65536 else small_exp_table()
     kvh = nkv or nh
@@ -262,15 +262,15 @@ def test_verifier_judges_like_the_restated_one(ctx, nh, nkv, s, d, n_table):
     k2 = k.copy(); k2[3] = (int(k2[3]) + 1) % P
     v2 = v.copy(); v2[-1] ^= 1
     for kk, vv in ((k2, v), (k, v2)):
-        assert _judge(ctx, proof, kk, vv, nh, s, d, nkv, b"av") == O.row_attention_verify_bytes(O.Transcript(b"av"), proof, kk, vv, nh, s, d, nkv) == 0
-    assert _judge(ctx, proof, k, v, nh, s, d, nkv, b"av2") == 1        # rows have transcripts of their own: the caller's label does not enter them
+        assert _decision(ctx, proof, kk, vv, nh, s, d, nkv, b"av") == O.row_attention_verify_bytes(O.Transcript(b"av"), proof, kk, vv, nh, s, d, nkv) == 0
+    assert _decision(ctx, proof, k, v, nh, s, d, nkv, b"av2") == 1        # rows have transcripts of their own: the caller's label does not enter them
     # one low bit changed, all over the proof: the two verifiers agree on every position
     n_rej = n_acc = 0
     for at in range(0, len(proof), 7):
         bad = bytearray(proof)
         bad[at] ^= 1
         exp = O.row_attention_verify_bytes(O.Transcript(b"av"), bytes(bad), k, v, nh, s, d, nkv)
-        got = _judge(ctx, bytes(bad), k, v, nh, s, d, nkv, b"av")
+        got = _decision(ctx, bytes(bad), k, v, nh, s, d, nkv, b"av")
         assert got == exp, (at, got, exp)
         n_rej += exp == 0
         n_acc += exp == 1
@@ -289,4 +289,4 @@ def test_verifier_at_the_bench_shape(ctx):
     assert za.verify_row_attention(proof, dk, dv, nh, s, d, zk.Transcript(ctx, b"big")) is True
     bad = bytearray(proof)
     bad[len(bad) // 2] ^= 1
-    assert _judge(ctx, bytes(bad), dk, dv, nh, s, d, 0, b"big") == O.row_attention_verify_bytes(O.Transcript(b"big"), bytes(bad), k, v, nh, s, d)
+    assert _decision(ctx, bytes(bad), dk, dv, nh, s, d, 0, b"big") == O.row_attention_verify_bytes(O.Transcript(b"big"), bytes(bad), k, v, nh, s, d)

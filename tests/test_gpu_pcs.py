@@ -131,8 +131,8 @@ def test_basefold_verifier_accepts_what_the_prover_emits(ctx, kind, n):
 
 @pytest.mark.parametrize("kind", KINDS)
 def test_basefold_verifier_rejects_tampered_proofs_like_the_oracle(ctx, kind):
-    """Every single-byte change of a proof is judged as the oracle's restatement of the reference
-    verifier judges it: changed roots, opened values, sibling digests, indices, lengths, final value."""
+    """Every single-byte change of a proof is decided as the oracle's restatement of the reference
+    verifier decides it: changed roots, opened values, sibling digests, indices, lengths, final value."""
     n, log_n = 3000, 12
     c, pt = rnd(71, n), rnd(72, log_n)
     blob = zp.basefold_commit_and_prove(ctx, zk.Transcript(ctx, b"bf-verify"), c, pt, kind)

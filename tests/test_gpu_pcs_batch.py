@@ -98,7 +98,7 @@ def test_argument_errors(ctx):
 
 
 # ---- the verifier (basefold.rs:959-1137) ------------------------------------------------------------------------
-def _judge_gpu(ctx, blob, kind, label):
+def _gpu_decision(ctx, blob, kind, label):
     try:
         return int(pcs.basefold_batch_verify_opening(ctx, zk.Transcript(ctx, label), blob, kind))
     except zk.ZkbError as e:
@@ -108,7 +108,7 @@ def _judge_gpu(ctx, blob, kind, label):
 
 @pytest.mark.parametrize("kind", [0, 1])
 @pytest.mark.parametrize("case", ["multi", "same"])
-def test_batch_verifier_judges_like_the_restated_one(ctx, kind, case):
+def test_batch_verifier_decides_like_the_restated_one(ctx, kind, case):
     rng = np.random.default_rng(77)
     if case == "multi":
         polys = [rng.integers(0, P, n).astype(np.uint32) for n in (200, 64, 256, 50, 9)]
@@ -132,11 +132,11 @@ def test_batch_verifier_judges_like_the_restated_one(ctx, kind, case):
         bad = bytearray(blob)
         bad[at] ^= 1
         exp = O.basefold_batch_verify_bytes(O.Transcript(b"bv"), bytes(bad), kind)[0]
-        got = _judge_gpu(ctx, bytes(bad), kind, b"bv")
+        got = _gpu_decision(ctx, bytes(bad), kind, b"bv")
         assert got == exp, (at, got, exp)
         n_rejected += exp != 1
     assert n_rejected > 100
-    assert _judge_gpu(ctx, blob[:-5], kind, b"bv") == -1 and _judge_gpu(ctx, blob + b"\\0", kind, b"bv") == -1
+    assert _gpu_decision(ctx, blob[:-5], kind, b"bv") == -1 and _gpu_decision(ctx, blob + b"\\0", kind, b"bv") == -1
 
 
 def test_batch_verifier_at_2_17(ctx):

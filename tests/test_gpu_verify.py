@@ -1,5 +1,5 @@
 """The layer verifier on the GPU (verify_qwen_layer_ef_indexed, transformer/qwen.rs:932-1097): it accepts
-every proof the prover emits, and judges tampered bytes exactly as the oracle's restatement of the
+every proof the prover emits, and decides on tampered bytes exactly as the oracle's restatement of the
 reference verifier does (which decodes the same bytes and replays the transcript on the CPU)."""
 import hashlib
 
@@ -68,7 +68,7 @@ def test_layer_verifier_accepts_honest_proofs_and_rejects_wrong_statements(env, 
 
 
 @pytest.mark.parametrize("shape", ["gdn", "gqa"])
-def test_layer_verifier_judges_tampered_bytes_like_the_oracle(env, shape):
+def test_layer_verifier_decides_tampered_bytes_like_the_oracle(env, shape):
     gl, ol, x = _layer(env, shape, seed=3)
     ih = hashlib.sha256(b"tamper").digest()
     y = gl.forward(x)

@@ -89,9 +89,9 @@ inline bool launch_matvec_forward_bulk(zkb_ctx* c, const MatvecBatch& mb, const 
     sh.n_al = (u32)((n + 31) & ~size_t(31));
     sh.R = 16;
     while (sh.R > 1 && (size_t)sh.R * n * 4 > 40960) sh.R /= 2;
-    const size_t stage = (size_t)sh.R * n * 4, budget = 200 * 1024;
-    if ((size_t)sh.n_al * 4 + 2 * stage + 1024 > budget) return false;
-    sh.S = (u32)((budget - (size_t)sh.n_al * 4 - 1024) / stage);
+    const size_t stage = (size_t)sh.R * n * 4, smem_limit = 200 * 1024;
+    if ((size_t)sh.n_al * 4 + 2 * stage + 1024 > smem_limit) return false;
+    sh.S = (u32)((smem_limit - (size_t)sh.n_al * 4 - 1024) / stage);
     if (sh.S > 4) sh.S = 4;
     u32 n_tiles = 0;
     for (u32 t = 0; t < mb.count; t++) n_tiles += (mb.first[t + 1] - mb.first[t] + sh.R - 1) / sh.R;
