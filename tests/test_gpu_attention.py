@@ -59,6 +59,21 @@ def test_proof_bytes_equal_the_oracle(ctx, nh, s, d):
     assert np.array_equal(za.row_attention_forward(ctx, q, k, v, nh, s, d, t), fwd)
 
 
+def test_forward_against_the_reference_python_restatement(ctx):
+    """tests/golden/attention_forward.json: outputs of the reference's own attention_full (tests/reference/attention.py)."""
+    import json, os
+    g = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "attention_forward.json")))
+    for c in g["cases"]:
+        q, k, v = (np.array(c[x], np.uint32) for x in "qkv")
+        nh, s, d = c["num_heads"], c["seq_len"], c["d_head"]
+        t = tables.build_exp_table(c["exp_scale"])
+        assert za.row_attention_forward(ctx, q, k, v, nh, s, d, t).tolist() == c["out"]
+        proof, out = za.prove_row_attention(q, k, v, nh, s, d, t, zk.Transcript(ctx, b"g"), want_output=True)
+        assert out.tolist() == c["out"]
+        for r in range(nh * s):                                  # the rows' outputs inside the proof are those values
+            assert np.array(c["out"][r * d:(r + 1) * d], "<u4").tobytes() in proof
+
+
 def test_the_reference_test_inputs_with_the_256_entry_table(ctx):
     """attention.rs:632-671: q = i % 3 + 1, k = i % 2 + 1, v = i % 4 + 1 on (2, 4, 4)."""
     t = small_exp_table()

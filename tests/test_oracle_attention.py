@@ -10,6 +10,27 @@ from zklm_compile_b200 import tables
 P = (1 << 31) - 1
 
 
+def golden():
+    import json, os
+    return json.load(open(os.path.join(os.path.dirname(__file__), "golden", "attention_forward.json")))
+
+
+def test_forward_and_exp_table_against_the_reference_python_restatement():
+    """tests/golden/attention_forward.json was produced by the reference's own attention_full / exp_table
+    (tests/reference/attention.py, reference.py; generator: tests/golden/make_golden_attention.py)."""
+    import hashlib
+    g = golden()
+    for scale, rec in g["exp_tables"].items():
+        t = tables.build_exp_table(int(scale))
+        assert t.size == rec["rows"]
+        assert hashlib.sha256(t.astype("<u4").tobytes()).hexdigest() == rec["sha256_outputs_le_u32"]
+        assert hashlib.sha256(tables.table_inputs(65536).astype("<u4").tobytes()).hexdigest() == rec["sha256_inputs_le_u32"]
+    for c in g["cases"]:
+        q, k, v = (np.array(c[x], np.uint32) for x in "qkv")
+        out, st = po.row_attention_forward(q, k, v, c["num_heads"], c["seq_len"], c["d_head"], tables.build_exp_table(c["exp_scale"]))
+        assert st == 0 and out.tolist() == c["out"]
+
+
 def small_exp_table(scale=100):
     """attention.rs:605-629: 256 entries, input raw as i8."""
     x = np.arange(256, dtype=np.uint8).astype(np.int8).astype(np.float64) / scale
