@@ -1,8 +1,10 @@
 /* A caller of the C ABI written in plain C (what a cgo / bindgen / FFI user of include/zkb200.h sees):
  * it proves one product sumcheck with EF challenges (prove_product_ef, sumcheck.rs:1204-1258), one
- * succinct matmul proof (matmul.rs:963-997) and checks a Basefold opening with the verifier
- * (basefold.rs:368-396, 611-748), and prints everything as hex so that the test can compare it with
- * what the oracle computes from the same seeded inputs.
+ * succinct matmul proof (matmul.rs:963-997), checks a Basefold opening with the verifier
+ * (basefold.rs:368-396, 611-748), opens two polynomials of different sizes with one batch Basefold
+ * (basefold.rs:1183-1378, 959-1137) and proves and verifies a small row attention (attention.rs:116-385),
+ * and prints everything as hex so that the test can compare it with what the oracle computes from the
+ * same seeded inputs.
  *
  *   caller <num_vars> <m> <n>
  */
@@ -92,6 +94,42 @@ int main(int argc, char** argv) {
     memcpy(&claimed, out + plen - 12, 4);
     CHECK(zkb_basefold_verify_opening(ctx, tv2, out, plen, point, nv, claimed, ZKB_NODE_BLAKE3, &ok));
     printf("verify_same_transcript %d\n", ok);
+
+    /* batch Basefold: f (2^nv coefficients) and the first 2^(nv-2) - 3 values of g, one fold chain; then its verifier */
+    {
+        const uint32_t* polys2[2] = {f, g};
+        const size_t ns[2] = {len, (len >> 2) - 3};
+        const uint32_t lns[2] = {nv, nv - 2};
+        zkb_bf_batch* batch = NULL;
+        CHECK(zkb_basefold_batch_precommit(ctx, polys2, ns, lns, 2, 0, ZKB_NODE_BLAKE3, &batch));
+        zkb_transcript* tb = NULL;
+        CHECK(zkb_tr_new(ctx, (const uint8_t*)"c-batch", 7, &tb));
+        CHECK(zkb_basefold_batch_prove(batch, tb, 0, out, cap, &plen));
+        hex("batch", out, plen);
+        zkb_transcript* tbv = NULL;
+        CHECK(zkb_tr_new(ctx, (const uint8_t*)"c-batch", 7, &tbv));
+        CHECK(zkb_basefold_batch_verify_opening(ctx, tbv, out, plen, ZKB_NODE_BLAKE3, &ok));
+        printf("batch_verify %d\n", ok);
+        zkb_basefold_batch_destroy(batch);
+        zkb_tr_free(tb); zkb_tr_free(tbv);
+    }
+
+    /* row attention, 2 heads x 4 positions x d_head 4, over a 256-entry table (any table of positive outputs serves the protocol) */
+    {
+        uint32_t table[256], q[32], k[32], v[32], att[32];
+        for (uint32_t i = 0; i < 256; i++) table[i] = (i * 7u + 1u) % 1000u + 1u;
+        for (int i = 0; i < 32; i++) { q[i] = next_u32() % 3u; k[i] = next_u32() % 3u; v[i] = next_u32(); }
+        zkb_transcript* ta = NULL;
+        CHECK(zkb_tr_new(ctx, (const uint8_t*)"c-attn", 6, &ta));
+        CHECK(zkb_prove_row_attention(ctx, ta, q, k, v, 2, 4, 4, table, 256, 0, att, out, cap, &plen));
+        hex("attention", out, plen);
+        hex("attention_out", att, sizeof att);
+        zkb_transcript* tav = NULL;
+        CHECK(zkb_tr_new(ctx, (const uint8_t*)"c-attn", 6, &tav));
+        CHECK(zkb_verify_row_attention(ctx, tav, out, plen, k, v, 2, 0, 4, 4, 0, &ok));
+        printf("attention_verify %d\n", ok);
+        zkb_tr_free(ta); zkb_tr_free(tav);
+    }
 
     zkb_tr_free(tr); zkb_tr_free(tv); zkb_tr_free(tp); zkb_tr_free(tv2);
     zkb_ctx_destroy(ctx);

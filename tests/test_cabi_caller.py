@@ -63,3 +63,13 @@ def test_c_caller_proofs_equal_the_oracle(caller, nv, m, n):
     point = g.vec(nv)
     assert got["basefold"] == O.basefold_commit_and_prove(tr, f, point, O.NODE_BLAKE3).hex()
     assert got["verify_other_transcript"] == "0" and got["verify_same_transcript"] == "1"
+    assert got["batch"] == O.basefold_batch_prove(O.Transcript(b"c-batch"), [f, gg[:(1 << (nv - 2)) - 3]], [nv, nv - 2]).hex()
+    assert got["batch_verify"] == "1"
+    table = ((np.arange(256, dtype=np.uint64) * 7 + 1) % 1000 + 1).astype(np.uint32)
+    q, k, v = np.zeros(32, np.uint32), np.zeros(32, np.uint32), np.zeros(32, np.uint32)
+    for i in range(32):
+        q[i] = g.next() % 3; k[i] = g.next() % 3; v[i] = g.next()
+    proof, st = O.prove_row_attention(O.Transcript(b"c-attn"), q, k, v, 2, 4, 4, table)
+    assert st == 0 and got["attention"] == proof.hex()
+    assert got["attention_out"] == O.row_attention_forward(q, k, v, 2, 4, 4, table)[0].astype("<u4").tobytes().hex()
+    assert got["attention_verify"] == "1"
