@@ -33,6 +33,8 @@ struct BvReader {
     const uint8_t* p; size_t n, at = 0; bool ok = true;
     uint64_t u64() { if (at + 8 > n) { ok = false; return 0; } uint64_t v = 0; for (int i = 0; i < 8; i++) v |= (uint64_t)p[at + i] << (8 * i); at += 8; return v; }
     uint32_t u32v() { if (at + 4 > n) { ok = false; return 0; } uint32_t v = 0; for (int i = 0; i < 4; i++) v |= (uint32_t)p[at + i] << (8 * i); at += 4; return v; }
+    // a declared element count that the remaining bytes cannot hold ends the decode (nothing is allocated for it)
+    bool fits(uint64_t count, size_t bytes_each) { if (!ok || count > (n - at) / bytes_each) { ok = false; return false; } return true; }
 };
 struct BvParsed {
     std::vector<u32> words;            // [commitment root 4][fold roots 4 each][per tree: indices, values, counts, digests]
@@ -50,7 +52,7 @@ inline bool bv_parse(const uint8_t* bytes, size_t len, BvParsed& out, size_t* us
     if (!r.ok || log_n < 1 || log_n > 28) return false;
     out.log_n = (u32)log_n;
     const uint64_t n_roots = r.u64();
-    if (!r.ok || n_roots > 64) return false;
+    if (!r.ok || n_roots > 64 || !r.fits(n_roots, 16)) return false;
     for (uint64_t i = 0; i < n_roots; i++) for (int k = 0; k < 4; k++) out.words.push_back(r.u32v());
     const uint64_t n_q = r.u64();
     if (!r.ok || n_q > 64) return false;
@@ -63,12 +65,12 @@ inline bool bv_parse(const uint8_t* bytes, size_t len, BvParsed& out, size_t* us
         for (int tree = 0; tree < 2; tree++) {
             BvTree t{};
             const uint64_t ni = r.u64();
-            if (!r.ok || ni > (1u << 20)) return false;
+            if (!r.ok || ni > (1u << 20) || !r.fits(ni, 4)) return false;
             if (ni > BV_MAX_OPENED) out.too_large = true;
             t.idx_off = (u32)out.words.size(); t.n_idx = (u32)ni;
             for (uint64_t i = 0; i < ni; i++) out.words.push_back(r.u32v());
             const uint64_t nv = r.u64();
-            if (!r.ok || nv > (1u << 20)) return false;
+            if (!r.ok || nv > (1u << 20) || !r.fits(nv, 4)) return false;
             t.val_off = (u32)out.words.size(); t.n_val = (u32)nv;
             for (uint64_t i = 0; i < nv; i++) out.words.push_back(r.u32v());
             const uint64_t nl = r.u64();
@@ -77,7 +79,7 @@ inline bool bv_parse(const uint8_t* bytes, size_t len, BvParsed& out, size_t* us
             std::vector<u32> counts, digs;
             for (uint64_t l = 0; l < nl; l++) {
                 const uint64_t cnt = r.u64();
-                if (!r.ok || cnt > (1u << 20)) return false;
+                if (!r.ok || cnt > (1u << 20) || !r.fits(cnt, 16)) return false;
                 counts.push_back((u32)cnt);
                 for (uint64_t i = 0; i < cnt * 4; i++) digs.push_back(r.u32v());
             }
@@ -94,7 +96,7 @@ inline bool bv_parse(const uint8_t* bytes, size_t len, BvParsed& out, size_t* us
     }
     out.final_value = r.u32v();
     const uint64_t n_final = r.u64();
-    if (n_final > (1u << 20)) return false;
+    if (n_final > (1u << 20) || !r.fits(n_final, 4)) return false;
     for (uint64_t i = 0; i < n_final && r.ok; i++) r.u32v();
     if (used) { *used = r.at; return r.ok; }
     return r.ok && r.at == len;

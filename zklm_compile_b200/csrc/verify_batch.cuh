@@ -25,12 +25,12 @@ struct BbvParsed {
 // One BatchMerkleProof (pcs.rs:43-53) appended to words; false when the bytes end early or a length is absurd.
 inline bool bbv_read_tree(BvReader& r, BbvParsed& out, BvTree& t) {
     const uint64_t ni = r.u64();
-    if (!r.ok || ni > (1u << 20)) return false;
+    if (!r.ok || ni > (1u << 20) || !r.fits(ni, 4)) return false;
     if (ni > BV_MAX_OPENED) out.too_large = true;
     t.idx_off = (u32)out.words.size(); t.n_idx = (u32)ni;
     for (uint64_t i = 0; i < ni; i++) out.words.push_back(r.u32v());
     const uint64_t nv = r.u64();
-    if (!r.ok || nv > (1u << 20)) return false;
+    if (!r.ok || nv > (1u << 20) || !r.fits(nv, 4)) return false;
     t.val_off = (u32)out.words.size(); t.n_val = (u32)nv;
     for (uint64_t i = 0; i < nv; i++) out.words.push_back(r.u32v());
     const uint64_t nl = r.u64();
@@ -39,7 +39,7 @@ inline bool bbv_read_tree(BvReader& r, BbvParsed& out, BvTree& t) {
     std::vector<u32> counts, digs;
     for (uint64_t l = 0; l < nl; l++) {
         const uint64_t cnt = r.u64();
-        if (!r.ok || cnt > (1u << 20)) return false;
+        if (!r.ok || cnt > (1u << 20) || !r.fits(cnt, 16)) return false;
         counts.push_back((u32)cnt);
         for (uint64_t i = 0; i < cnt * 4; i++) digs.push_back(r.u32v());
     }
@@ -55,22 +55,22 @@ inline bool bbv_parse(const uint8_t* bytes, size_t len, BbvParsed& out) {
     BvReader r{bytes, len};
     struct Commit { u32 root[4]; uint64_t log_n; };
     const uint64_t kc = r.u64();
-    if (!r.ok || kc > 4096) return false;
+    if (!r.ok || kc > 4096 || !r.fits(kc, 32)) return false;
     std::vector<Commit> commits(kc);
     for (auto& c : commits) { for (int i = 0; i < 4; i++) c.root[i] = r.u32v(); r.u64(); c.log_n = r.u64(); }
     const uint64_t num_polys = r.u64();
     const uint64_t n_logs = r.u64();
-    if (!r.ok || n_logs > 4096) return false;
+    if (!r.ok || n_logs > 4096 || !r.fits(n_logs, 8)) return false;
     std::vector<uint64_t> logs(n_logs);
     for (auto& l : logs) l = r.u64();
     const uint64_t n_roots = r.u64();
-    if (!r.ok || n_roots > 4096) return false;
+    if (!r.ok || n_roots > 4096 || !r.fits(n_roots, 16)) return false;
     out.roots_off = (u32)out.words.size();
     for (uint64_t i = 0; i < n_roots * 4; i++) out.words.push_back(r.u32v());
     out.batched_off = (u32)out.words.size();
     for (int i = 0; i < 4; i++) out.words.push_back(r.u32v());
     const uint64_t n_fold = r.u64();
-    if (!r.ok || n_fold > 64) return false;
+    if (!r.ok || n_fold > 64 || !r.fits(n_fold, 16)) return false;
     out.fold_off = (u32)out.words.size();
     for (uint64_t i = 0; i < n_fold * 4; i++) out.words.push_back(r.u32v());
     const uint64_t n_q = r.u64();
