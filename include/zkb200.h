@@ -512,6 +512,9 @@ int32_t zkb_oplist_add_gelu(zkb_oplist* list, const char* name, const uint32_t* 
  * (num_kv_heads heads each), the proof is SerializedLayerProof::GqaAttention. */
 int32_t zkb_oplist_add_attention(zkb_oplist* list, const char* name, size_t num_heads, size_t num_kv_heads, size_t seq_len, size_t d_head,
                                  const uint32_t* table_out_dev, uint32_t n_table, const uint32_t* k_values, const uint32_t* v_values);
+/* Replaces K and V of attention op `op_index` (0-based position in the list) that was added with k_values / v_values: the next
+ * forward pass and proof use the new ones (the reference's requests carry K and V with every op, protocol.rs:714-722). */
+int32_t zkb_oplist_set_attention_kv(zkb_oplist* list, uint32_t op_index, const uint32_t* k_values, const uint32_t* v_values);
 int32_t zkb_oplist_add_set_input(zkb_oplist* list, const char* name, const uint32_t* values, size_t n);
 uint32_t zkb_oplist_output_len(const zkb_oplist* list);
 /* forward pass only (x: input_len host words); zkb_oplist_activation then reads the activation after op `op_index`. */

@@ -191,6 +191,16 @@ def test_oplist_with_row_attention(ctx, external_kv):
     got, exp = g.prove(x), o.prove(x)
     assert got == exp
     assert g.prove(x) == exp                                  # a second proof on the same list (staging and scratch reused)
+    if external_kv:                                           # the next request brings other K and V
+        kv2 = (np.mod(rng.integers(-3, 4, total), P).astype(np.uint32), rng.integers(0, P, total).astype(np.uint32))
+        g.set_attention_kv(2, *kv2)
+        o2 = O.OpList()
+        o2.linear("c_attn", w1, b1, m1, d_in); o2.simple("save", "save_res", "res"); o2.attention("attn", nh, s, d, t, *kv2)
+        o2.linear("c_proj", w2, None, d_out, total)
+        assert g.prove(x) == o2.prove(x)
+    else:
+        with pytest.raises(zk.ZkbError):
+            g.set_attention_kv(2, np.zeros(total, np.uint32), np.zeros(total, np.uint32))
     g.close()
 
 

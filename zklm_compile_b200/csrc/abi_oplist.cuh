@@ -426,6 +426,20 @@ int32_t zkb_oplist_add_attention(zkb_oplist* L, const char* name, size_t num_hea
         txn.done = true;
     });
 }
+// New K and V for an attention op that was added with its own (the reference's request carries them with every op, protocol.rs:714-722).
+int32_t zkb_oplist_set_attention_kv(zkb_oplist* L, uint32_t op_index, const uint32_t* k_values, const uint32_t* v_values) {
+    if (!L || !k_values || !v_values || op_index >= L->ops.size()) return ZKB_E_ARG;
+    zkb_ctx* c = L->ctx;
+    ZKB_TRY(c, {
+        c->use();
+        OL::Op& op = L->ops[op_index];
+        if (op.kind != OL::ATTENTION_ROWS || !op.aux0 || !op.aux1) throw ArgFail{ZKB_E_ARG, "not an attention op that holds its own K and V"};
+        const size_t total_kv = (size_t)(op.kv_heads ? op.kv_heads : op.heads) * op.seq * op.d_head;
+        ZKB_CUDA(cudaMemcpyAsync(op.aux0, k_values, total_kv * 4, cudaMemcpyHostToDevice, c->stream));
+        ZKB_CUDA(cudaMemcpyAsync(op.aux1, v_values, total_kv * 4, cudaMemcpyHostToDevice, c->stream));
+        ZKB_CUDA(cudaStreamSynchronize(c->stream));
+    });
+}
 int32_t zkb_oplist_add_set_input(zkb_oplist* L, const char* name, const uint32_t* values, size_t n) {
     if (!L || !values || n == 0) return ZKB_E_ARG;
     zkb_ctx* c = L->ctx;

@@ -79,6 +79,11 @@ class OpList:
                                                              C.c_size_t(d_head), exp_table.ptr, C.c_uint32(exp_table.n), pk, pv))
         self.n_ops += 1
 
+    def set_attention_kv(self, op_index: int, k_values, v_values):
+        """New K / V for the attention op at position `op_index` that was added with its own."""
+        K, pk = _a(k_values); V, pv = _a(v_values)
+        check(self.ctx.h, _lib.lib().zkb_oplist_set_attention_kv(self.h, C.c_uint32(op_index), pk, pv))
+
     def set_input(self, name: str, values):
         V, pv = _a(values)
         check(self.ctx.h, _lib.lib().zkb_oplist_add_set_input(self.h, name.encode(), pv, C.c_size_t(V.size)))
