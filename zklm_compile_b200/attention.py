@@ -92,5 +92,5 @@ def verify_row_attention(proof: bytes, k, v, num_heads: int, seq_len: int, d_hea
 def proof_size_bound(num_heads: int, seq_len: int, d_head: int) -> int:
     """Upper bound of the bincode size, for callers that allocate the output buffer themselves."""
     ls = max(1, (seq_len - 1).bit_length()); ld = max(1, (d_head - 1).bit_length())
-    per_row = 4 * (5 * seq_len + d_head) + 16 * (7 * ls + 3 * ld + 8) * 4 + 1024
+    per_row = 4 * (6 * seq_len + d_head) + 16 * (7 * ls + 3 * ld + 8) * 4 + 1024      # six vectors of seq_len words, one of d_head, five sumchecks
     return num_heads * seq_len * per_row + 64
