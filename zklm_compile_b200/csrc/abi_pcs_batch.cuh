@@ -15,13 +15,19 @@ namespace zkb {
 __global__ void bfb_coeffs_kernel(const u32* __restrict__ rho, u32 k, u32* coef) {        // [1, rho, rho^2, ...] (:1239-1242)
     for (u32 i = blockIdx.x * blockDim.x + threadIdx.x; i < k; i += gridDim.x * blockDim.x) coef[i] = pow31(rho[0], i);
 }
-// out[j] = sum_{i in [first, first + count)} coef[i] * cws[i][j], j < len
+// out[j] = sum_{i in [first, first + count)} coef[i] * cws[i][j], j < len.  Codewords and out are cudaMalloc'd and len is a power of
+// two >= 4 (a codeword has 2 * 2^log_n >= 4 words), so every thread moves 16-byte vectors; the codewords are read once (evict first).
 __global__ void __launch_bounds__(256) bfb_lincomb_kernel(const u32* const* __restrict__ cws, const u32* __restrict__ coef, u32 first, u32 count,
                                                           size_t len, u32* __restrict__ out) {
-    for (size_t j = (size_t)blockIdx.x * blockDim.x + threadIdx.x; j < len; j += (size_t)gridDim.x * blockDim.x) {
-        u64 acc = 0;
-        for (u32 i = first; i < first + count; i++) acc += (u64)mul31(coef[i], __ldcs(cws[i] + j));
-        out[j] = red64(acc);
+    const size_t n4 = len >> 2;
+    for (size_t j = (size_t)blockIdx.x * blockDim.x + threadIdx.x; j < n4; j += (size_t)gridDim.x * blockDim.x) {
+        u64 a0 = 0, a1 = 0, a2 = 0, a3 = 0;
+        for (u32 i = first; i < first + count; i++) {
+            const u32 c = coef[i];
+            const uint4 v = __ldcs(reinterpret_cast<const uint4*>(cws[i]) + j);
+            a0 += (u64)mul31(c, v.x); a1 += (u64)mul31(c, v.y); a2 += (u64)mul31(c, v.z); a3 += (u64)mul31(c, v.w);
+        }
+        reinterpret_cast<uint4*>(out)[j] = make_uint4(red64(a0), red64(a1), red64(a2), red64(a3));
     }
 }
 // Absorb the batched root, squeeze the whole fold point, absorb its first coordinate (:1277-1291).
@@ -118,7 +124,7 @@ BfbPending bfb_enqueue(zkb_bf_batch* B, TrState* tr, bool individual) {
     const size_t cw_len0 = size_t(2) << log_n;
     u32* cw0 = (u32*)c->scratch(cw_len0 * 4);
     uint4* tree0 = (uint4*)c->scratch(mk_node_count(log_n + 1) * 16 + 16);
-    bfb_lincomb_kernel<<<grid_for(c, cw_len0), 256, 0, c->stream>>>(B->cw_ptrs_dev, coef, groups[0].s, groups[0].e - groups[0].s, cw_len0, cw0);
+    bfb_lincomb_kernel<<<grid_for(c, cw_len0 / 4), 256, 0, c->stream>>>(B->cw_ptrs_dev, coef, groups[0].s, groups[0].e - groups[0].s, cw_len0, cw0);
     ZKB_LAUNCHED(c);
     MkFold none{};
     mk_build(c, kind, MK_VALUES, cw0, cw_len0, log_n + 1, tree0, none);
@@ -168,7 +174,7 @@ BfbPending bfb_enqueue(zkb_bf_batch* B, TrState* tr, bool individual) {
             }
             if (count) {
                 u32* add = (u32*)c->scratch(half * 4 + 16);
-                bfb_lincomb_kernel<<<grid_for(c, half), 256, 0, c->stream>>>(B->cw_ptrs_dev, coef, first, count, half, add);
+                bfb_lincomb_kernel<<<grid_for(c, half / 4 ? half / 4 : 1), 256, 0, c->stream>>>(B->cw_ptrs_dev, coef, first, count, half, add);
                 ZKB_LAUNCHED(c);
                 f.add = add;
             }
