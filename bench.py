@@ -1130,6 +1130,13 @@ def main():
                                       "d2h_bytes_per_step": g["proof_bytes"]},
                               "cpu_baseline": ({"value": g["cpu_port_ms"], "unit": "ms", "cores": cores, "kind": "port",
                                                 "sample": "the same call, 2 runs"} if "cpu_port_ms" in g else None),
+                              "roofline": {"bound": "hbm", "achieved": round(3 * 12 * 128 * 64 * 4 / max(g["prove_ms_rows_then_transcript"] - g["prove_ms_device_inputs"], 1e-3) / 1e6, 2),
+                                           "peak": load_peaks()[0], "unit": "GB/s",
+                                           "frac": round(3 * 12 * 128 * 64 * 4 / max(g["prove_ms_rows_then_transcript"] - g["prove_ms_device_inputs"], 1e-3) / 1e6 / load_peaks()[0], 6),
+                                           "traffic": 1666560, "traffic_source": "ncu dram__bytes_read + write of one launch (profiles/attention_row_kernel_12x128x64.md)",
+                                           "kernel": "attention_row_kernel: q, k, v are its only DRAM reads (algorithmic bytes 3 * heads * seq * d_head * 4); its duration is taken "
+                                                     "as the time the call gains from running it beside the caller's transcript (in-order minus overlapped)",
+                                           "note": "neither this kernel nor the call is bandwidth-bound: both are one-thread SHA-256 chains (DESIGN.md, 'Row attention')"},
                               "attention_rows_gpt2_head_shape": g}))
         elif rank == 0:
             emit_line(json.dumps({"impl": "reference", "unavailable": "the attention workload's CPU port time is part of the default arm's line (cpu_port_ms)"}))
