@@ -315,3 +315,32 @@ def test_verifier_at_the_bench_shape(ctx):
     bad = bytearray(proof)
     bad[len(bad) // 2] ^= 1
     assert _decision(ctx, bytes(bad), dk, dv, nh, s, d, 0, b"big") == O.row_attention_verify_bytes(O.Transcript(b"big"), bytes(bad), k, v, nh, s, d)
+
+
+def test_caller_keeps_its_transcript(ctx):
+    """tr = NULL: only the rows are proved / checked; the proof is the same bytes, and a caller that absorbs the dimensions and the
+    rows' scores and outputs itself ends in the state the library's transcript ends in."""
+    rng = np.random.default_rng(17)
+    t = tables.build_exp_table(100)
+    for nh, nkv, s, d in [(3, 0, 9, 5), (4, 2, 6, 4)]:
+        kvh = nkv or nh
+        q = np.mod(rng.integers(-2, 3, nh * s * d), P).astype(np.uint32)
+        k = np.mod(rng.integers(-2, 3, kvh * s * d), P).astype(np.uint32)
+        v = rng.integers(0, P, kvh * s * d).astype(np.uint32)
+        tg = zk.Transcript(ctx, b"own")
+        full = za.prove_row_attention(q, k, v, nh, s, d, t, tg, num_kv_heads=nkv)
+        rows_only, out = za.prove_row_attention(q, k, v, nh, s, d, t, ctx, want_output=True, num_kv_heads=nkv)
+        assert rows_only == full
+        assert np.array_equal(out, O.row_attention_forward(q, k, v, nh, s, d, t, nkv)[0])
+        mine = zk.Transcript(ctx, b"own")
+        mine.absorb_bytes(za.caller_transcript_stream(rows_only, nh, s, d, nkv))
+        assert mine.squeeze() == tg.squeeze()
+        assert za.verify_row_attention(full, k, v, nh, s, d, ctx, nkv) is True
+        bad = bytearray(full)
+        bad[len(bad) // 3] ^= 1
+        exp = O.row_attention_verify_bytes(O.Transcript(b"own"), bytes(bad), k, v, nh, s, d, nkv)
+        try:
+            got = int(za.verify_row_attention(bytes(bad), k, v, nh, s, d, ctx, nkv))
+        except zk.ZkbError:
+            got = -1
+        assert got == exp

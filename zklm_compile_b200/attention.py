@@ -49,8 +49,11 @@ def row_attention_forward(ctx: Context, q, k, v, num_heads: int, seq_len: int, d
 
 def prove_row_attention(q, k, v, num_heads: int, seq_len: int, d_head: int, exp_table, transcript: Transcript, want_output: bool = False,
                         num_kv_heads: int = 0):
-    """attention.rs:116-276 -> bincode(RowAttentionProof) [, the op's output]."""
-    ctx = transcript.ctx
+    """attention.rs:116-276 -> bincode(RowAttentionProof) [, the op's output].
+    `transcript` may be a Context instead of a Transcript: then only the rows are proved and the caller absorbs the dimensions and
+    every row's scores and outputs into its own transcript (`caller_transcript_stream` gives that byte stream)."""
+    ctx = transcript.ctx if isinstance(transcript, Transcript) else transcript
+    tr_h = transcript.h if isinstance(transcript, Transcript) else None
     keep, ptrs, on_dev, n_table = _inputs(q, k, v, exp_table)
     n = num_heads * seq_len * d_head
     out = None
@@ -63,7 +66,7 @@ def prove_row_attention(q, k, v, num_heads: int, seq_len: int, d_head: int, exp_
     cap = proof_size_bound(num_heads, seq_len, d_head)
     buf = (C.c_uint8 * cap)()
     ln = C.c_size_t()
-    st = _lib.lib().zkb_prove_row_attention_gqa(ctx.h, transcript.h, *ptrs[:3], C.c_size_t(num_heads), C.c_size_t(num_kv_heads), C.c_size_t(seq_len),
+    st = _lib.lib().zkb_prove_row_attention_gqa(ctx.h, tr_h, *ptrs[:3], C.c_size_t(num_heads), C.c_size_t(num_kv_heads), C.c_size_t(seq_len),
                                                 C.c_size_t(d_head), ptrs[3], C.c_size_t(n_table), C.c_int32(on_dev), pout, buf, C.c_size_t(cap), C.byref(ln))
     check(ctx.h, st)
     proof = C.string_at(buf, ln.value)
@@ -77,16 +80,56 @@ def prove_row_attention_gqa(q, k, v, num_q_heads: int, num_kv_heads: int, seq_le
 
 
 def verify_row_attention(proof: bytes, k, v, num_heads: int, seq_len: int, d_head: int, transcript: Transcript, num_kv_heads: int = 0) -> bool:
-    """attention.rs:279-385 (GQA: :503-590) on bincode(RowAttentionProof); as in the reference, q and the exp table are not needed."""
-    ctx = transcript.ctx
+    """attention.rs:279-385 (GQA: :503-590) on bincode(RowAttentionProof); as in the reference, q and the exp table are not needed.
+    `transcript` may be a Context: the rows are checked and the caller's transcript is left to the caller."""
+    ctx = transcript.ctx if isinstance(transcript, Transcript) else transcript
+    tr_h = transcript.h if isinstance(transcript, Transcript) else None
     kk, pk, dk = _ptr(k); vv, pv, dv = _ptr(v)
     if dk != dv:
         raise ValueError("k and v are either both DeviceBuffers or both host arrays")
     ok = C.c_int32(0)
     buf = (C.c_uint8 * len(proof)).from_buffer_copy(proof)
-    check(ctx.h, _lib.lib().zkb_verify_row_attention(ctx.h, transcript.h, buf, C.c_size_t(len(proof)), pk, pv, C.c_size_t(num_heads),
+    check(ctx.h, _lib.lib().zkb_verify_row_attention(ctx.h, tr_h, buf, C.c_size_t(len(proof)), pk, pv, C.c_size_t(num_heads),
                                                      C.c_size_t(num_kv_heads), C.c_size_t(seq_len), C.c_size_t(d_head), C.c_int32(int(dk)), C.byref(ok)))
     return bool(ok.value)
+
+
+def caller_transcript_stream(proof: bytes, num_heads: int, seq_len: int, d_head: int, num_kv_heads: int = 0) -> bytes:
+    """What the caller's transcript absorbs around a row-attention proof (attention.rs:140-143, 254-265; GQA :403-406): the dimensions as
+    u32 LE, then every row's scores and outputs, read from the proof bytes.  For callers that keep their transcript on the host."""
+    import struct
+    out = [struct.pack("<I", num_heads)]
+    if num_kv_heads:
+        out.append(struct.pack("<I", num_kv_heads))
+    out.append(struct.pack("<II", seq_len, d_head))
+    at = 8
+    u64 = lambda: struct.unpack_from("<Q", proof, at)[0]
+
+    def skip_vec():
+        nonlocal at
+        n = u64(); at += 8 + 4 * n
+
+    def skip_sumcheck():
+        nonlocal at
+        rounds = u64(); at += 8
+        for _ in range(rounds):
+            skip_vec()
+        skip_vec()
+
+    for _ in range(num_heads):
+        at += 8                                            # rows of this head
+        for _ in range(seq_len):
+            skip_sumcheck(); at += 8; skip_vec(); skip_vec()                   # score_proof
+            at += 2 * (32 + 8 + 8 + 4); skip_sumcheck(); at += 16               # lookup: commitments, sumcheck, finals, alpha, beta
+            skip_vec(); skip_vec(); skip_vec(); at += 32                        # inputs, outputs, multiplicities, digest
+            at += 4; skip_sumcheck(); at += 8; skip_sumcheck(); at += 12 + 4    # sum, sum proof + finals, output proof + finals, inv_s
+            skip_vec(); skip_vec()                                              # e_values, y_values
+            skip_sumcheck(); at += 8; skip_vec(); skip_vec()                   # output_proof
+            n = u64(); scores = proof[at + 8:at + 8 + 4 * n]; at += 8 + 4 * n
+            skip_vec()                                                          # attn_weights
+            n = u64(); outp = proof[at + 8:at + 8 + 4 * n]; at += 8 + 4 * n
+            out.append(scores); out.append(outp)
+    return b"".join(out)
 
 
 def proof_size_bound(num_heads: int, seq_len: int, d_head: int) -> int:

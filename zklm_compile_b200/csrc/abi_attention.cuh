@@ -46,7 +46,7 @@ int32_t zkb_row_attention_forward(zkb_ctx* c, const uint32_t* q, const uint32_t*
 int32_t zkb_prove_row_attention_gqa(zkb_ctx* c, zkb_transcript* t, const uint32_t* q, const uint32_t* k, const uint32_t* v, size_t num_heads,
                                     size_t num_kv_heads, size_t seq_len, size_t d_head, const uint32_t* table_out, size_t n_table,
                                     int32_t on_device, uint32_t* attn_out, uint8_t* out, size_t cap, size_t* len) {
-    if (!c || !t || !q || !k || !v || !table_out) return ZKB_E_ARG;
+    if (!c || !q || !k || !v || !table_out) return ZKB_E_ARG;
     ZKB_TRY(c, {
         c->use();
         att_check_dims(num_heads, seq_len, d_head, n_table);
@@ -58,7 +58,7 @@ int32_t zkb_prove_row_attention_gqa(zkb_ctx* c, zkb_transcript* t, const uint32_
         u32* dout = (on_device && attn_out) ? attn_out : (u32*)c->scratch(n * 4);
         const size_t rec_words = num_heads * seq_len * (size_t)att_layout((u32)seq_len, (u32)d_head).words, bind_words = num_heads * seq_len * (seq_len + d_head);
         u32* host = (u32*)c->stage_host((rec_words + bind_words) * 4);
-        AttRun R = attention_prove_enqueue(c, t->dev, d.q, d.k, d.v, (u32)num_heads, (u32)num_kv_heads, (u32)seq_len, (u32)d_head, d.table, (u32)n_table, dout,
+        AttRun R = attention_prove_enqueue(c, t ? t->dev : nullptr, d.q, d.k, d.v, (u32)num_heads, (u32)num_kv_heads, (u32)seq_len, (u32)d_head, d.table, (u32)n_table, dout,
                                            host, host + rec_words);
         ZKB_CUDA(cudaGetLastError());
         if (attn_out && !on_device) ZKB_CUDA(cudaMemcpyAsync(attn_out, dout, n * 4, cudaMemcpyDeviceToHost, c->stream));
@@ -85,7 +85,7 @@ int32_t zkb_prove_row_attention(zkb_ctx* c, zkb_transcript* t, const uint32_t* q
 // and the exp table are not needed: the verifier recomputes K(r, s) and V^T(r, s) from k and v and replays each row's transcript.
 int32_t zkb_verify_row_attention(zkb_ctx* c, zkb_transcript* t, const uint8_t* proof, size_t len, const uint32_t* k, const uint32_t* v,
                                  size_t num_heads, size_t num_kv_heads, size_t seq_len, size_t d_head, int32_t on_device, int32_t* accepted) {
-    if (!c || !t || !proof || !k || !v || !accepted) return ZKB_E_ARG;
+    if (!c || !proof || !k || !v || !accepted) return ZKB_E_ARG;
     *accepted = 0;
     ZKB_TRY(c, {
         c->use();
@@ -99,7 +99,7 @@ int32_t zkb_verify_row_attention(zkb_ctx* c, zkb_transcript* t, const uint8_t* p
         const size_t n_kv = (num_kv_heads ? num_kv_heads : num_heads) * seq_len * d_head;
         const u32* dk = on_device ? k : up_pad(c, k, n_kv, n_kv);
         const u32* dv = on_device ? v : up_pad(c, v, n_kv, n_kv);
-        AvRun run = attention_verify_enqueue(c, t->dev, pr, dk, dv, (u32)num_kv_heads);
+        AvRun run = attention_verify_enqueue(c, t ? t->dev : nullptr, pr, dk, dv, (u32)num_kv_heads);
         std::vector<u32> res(run.rows);
         ZKB_CUDA(cudaMemcpyAsync(res.data(), run.result_dev, (size_t)run.rows * 4, cudaMemcpyDeviceToHost, c->stream));
         ZKB_CUDA(cudaStreamSynchronize(c->stream));

@@ -467,6 +467,15 @@ inline AttRun attention_prove_enqueue(zkb_ctx* c, TrState* tr, const u32* q, con
     const bool in_order = c->opt_bf_in_order || c->capturing;
     const u32 hpg = att_heads_per_group(num_heads, num_kv_heads);
     const int gqa = num_kv_heads != 0;
+    if (!tr) {
+        // The caller keeps its transcript and absorbs the dimensions, scores and outputs itself (attention.rs:140-143, 254-265: they are
+        // in the proof it gets back): one launch computes the rows' forward values and proves them, and no serial hash runs on the GPU.
+        AttArgs A{q, k, v, table_out, n_table, attn_out, R.bind, R.rec, c->status, 1, hpg, gqa};
+        att_launch(c, c->stream, A, R.L, R.rows);
+        ZKB_CUDA(cudaMemcpyAsync(host_bind, R.bind, (size_t)R.rows * (S + D) * 4, cudaMemcpyDeviceToHost, c->stream));
+        ZKB_CUDA(cudaMemcpyAsync(host_rec, R.rec, (size_t)R.rows * R.L.words * 4, cudaMemcpyDeviceToHost, c->stream));
+        return R;
+    }
     AttArgs F{q, k, v, table_out, n_table, attn_out, R.bind, nullptr, c->status, 0, hpg, gqa};
     att_launch(c, c->stream, F, R.L, R.rows);
     ZKB_CUDA(cudaMemcpyAsync(host_bind, R.bind, (size_t)R.rows * (S + D) * 4, cudaMemcpyDeviceToHost, c->stream));

@@ -359,7 +359,7 @@ inline AvRun attention_verify_enqueue(zkb_ctx* c, TrState* tr, const AvParsed& p
     memcpy(pre, "lookup-external-data-v1", 23);
     u64 n64 = L.S;
     memcpy(pre + 23, &n64, 8);
-    const bool in_order = c->opt_bf_in_order || c->capturing;
+    const bool in_order = c->opt_bf_in_order || c->capturing || !tr;       // without a transcript to advance there is nothing to overlap
     cudaStream_t rows_stream = in_order ? c->stream : c->side_stream();
     if (!in_order) {
         ZKB_CUDA(cudaEventRecord(c->side_event(0), c->stream));
@@ -370,7 +370,7 @@ inline AvRun attention_verify_enqueue(zkb_ctx* c, TrState* tr, const AvParsed& p
     attention_verify_kernel<<<run.rows, threads, smem, rows_stream>>>(A, L, b3_prefix(pre, 31));
     ZKB_LAUNCHED(c);
     if (!in_order) ZKB_CUDA(cudaEventRecord(c->side_event(1), rows_stream));
-    {
+    if (tr) {
         ScriptBuilder sb;
         sb.word(pr.num_heads);
         if (num_kv_heads) sb.word(num_kv_heads);
