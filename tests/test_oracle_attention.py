@@ -112,3 +112,22 @@ def test_gqa_round_trips():
     a, _ = po.prove_row_attention(po.Transcript(b"x"), q, k, v, 2, s, d, t, 2)
     b, _ = po.prove_row_attention(po.Transcript(b"x"), q, k, v, 2, s, d, t)
     assert len(a) == len(b) and a != b
+
+
+def test_caller_transcript_stream_is_what_the_prover_absorbs():
+    """zklm_compile_b200.attention.caller_transcript_stream (host helper for callers that keep their transcript): absorbing its bytes
+    leaves a transcript where prove_row_attention leaves it (attention.rs:140-143, 254-265; GQA :403-406)."""
+    from zklm_compile_b200 import attention as za
+    t = tables.build_exp_table(100)
+    rng = np.random.default_rng(3)
+    for nh, nkv, s, d in [(2, 0, 6, 4), (4, 2, 5, 3), (1, 0, 2, 1)]:
+        kvh = nkv or nh
+        q = np.mod(rng.integers(-2, 3, nh * s * d), P).astype(np.uint32)
+        k = np.mod(rng.integers(-2, 3, kvh * s * d), P).astype(np.uint32)
+        v = rng.integers(0, P, kvh * s * d).astype(np.uint32)
+        tr = po.Transcript(b"x")
+        proof, st = po.prove_row_attention(tr, q, k, v, nh, s, d, t, nkv)
+        assert st == 0
+        mine = po.Transcript(b"x")
+        mine.absorb_bytes(za.caller_transcript_stream(proof, nh, s, d, nkv))
+        assert mine.squeeze() == tr.squeeze()
