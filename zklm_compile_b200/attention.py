@@ -64,10 +64,12 @@ def prove_row_attention(q, k, v, num_heads: int, seq_len: int, d_head: int, exp_
         else:
             out = np.zeros(n, np.uint32); pout = out.ctypes.data_as(u32p)
     cap = proof_size_bound(num_heads, seq_len, d_head)
-    buf = (C.c_uint8 * cap)()
+    buf = getattr(ctx, "_attention_out", None)            # the output buffer is kept with the context: a fresh one of this size costs
+    if buf is None or len(buf) < cap:                     # a millisecond of page faults, comparable to the rows' proof itself
+        buf = ctx._attention_out = (C.c_uint8 * cap)()
     ln = C.c_size_t()
     st = _lib.lib().zkb_prove_row_attention_gqa(ctx.h, tr_h, *ptrs[:3], C.c_size_t(num_heads), C.c_size_t(num_kv_heads), C.c_size_t(seq_len),
-                                                C.c_size_t(d_head), ptrs[3], C.c_size_t(n_table), C.c_int32(on_dev), pout, buf, C.c_size_t(cap), C.byref(ln))
+                                                C.c_size_t(d_head), ptrs[3], C.c_size_t(n_table), C.c_int32(on_dev), pout, buf, C.c_size_t(len(buf)), C.byref(ln))
     check(ctx.h, st)
     proof = C.string_at(buf, ln.value)
     return (proof, out) if want_output else proof
